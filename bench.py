@@ -1,0 +1,358 @@
+#!/usr/bin/env python
+"""Headline benchmark: Evoformer-48 training step, bf16, N_seq=128, N_res=256, activation checkpoint per block.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--parallelism dap|dp] [--impl ours|reference]
+
+For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
+``--parallelism dap`` (default) runs ONE sample over N GPUs with Dynamic Axial Parallelism (strong
+scaling, the reference's headline configuration); ``dp`` runs one sample per GPU (weak scaling).
+
+A step is: forward through 48 Evoformer blocks + single-representation projection, MSE loss against
+random targets, backward with per-block recomputation, gradient reduction over ranks, Adam update.
+Inputs are synthetic (m, z ~ N(0,1); 10% of MSA rows masked); weights are random-init.
+
+Prints one JSON line (rank 0).  ``value`` is the step time in seconds (device-timed, max over ranks);
+``e2e`` repeats the measurement through the public API with the inputs copied from pinned host memory
+every step and the loss read back to the host.
+
+``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` (with the import
+stand-ins under ``baseline/stubs`` for the third-party packages that are not installed) through its own
+public API: ``init_dap`` + ``fastfold.model.fastnn.EvoformerStack`` + ``torch.optim.Adam``.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+S_MSA, N_RES, C_M, C_Z, C_S, N_BLOCKS = 128, 256, 256, 128, 384, 48
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--parallelism", default="dap", choices=["dap", "dp"])
+    ap.add_argument("--blocks", type=int, default=N_BLOCKS, help="(debug) number of Evoformer blocks; the metric is defined at 48")
+    ap.add_argument("--no-graph", action="store_true", help="disable CUDA-graph replay of the step")
+    ap.add_argument("--msa", type=int, default=S_MSA)
+    ap.add_argument("--res", type=int, default=N_RES)
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+                power.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(torch, S, N, device, dtype, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    m = torch.randn(S, N, C_M, generator=g)
+    z = torch.randn(N, N, C_Z, generator=g)
+    msa_mask = torch.ones(S, N)
+    rows = torch.randperm(S, generator=g)[: max(1, S // 10)]
+    msa_mask[rows] = 0.0
+    pair_mask = torch.ones(N, N)
+    tm = torch.randn(S, N, C_M, generator=g)
+    tz = torch.randn(N, N, C_Z, generator=g)
+    ts = torch.randn(N, C_S, generator=g)
+    host = [m.to(dtype), z.to(dtype), msa_mask.to(dtype), pair_mask.to(dtype), tm.to(dtype), tz.to(dtype), ts.to(dtype)]
+    if device.type == "cuda":
+        host = [t.pin_memory() for t in host]
+    return host
+
+
+def randomize_zero_weights(torch, model, seed):
+    """AlphaFold zero-initialises the last linear of every residual branch; give those small random values so the
+    benchmark exercises non-degenerate arithmetic (random-init weights of the architecture, as the config says)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2 and float(p.abs().sum()) == 0.0:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+
+
+def mse_loss(out, tm, tz, ts):
+    om, oz, s = out
+    return ((om.float() - tm.float()) ** 2).mean() + ((oz.float() - tz.float()) ** 2).mean() + ((s.float() - ts.float()) ** 2).mean()
+
+
+def max_over_ranks(torch, dist, value, device):
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        t = torch.tensor([value], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return value
+
+
+def fence(torch, dist):
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    import fastfold_b200
+    from fastfold_b200.parallel import init_dap, core
+    from fastfold_b200.models.fastnn import EvoformerStack
+    from fastfold_b200.runtime import FlatAdamTrainer
+    from fastfold_b200.ops import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    dap = world if args.parallelism == "dap" else 1
+    init_dap(dap)
+    use_cuda = torch.cuda.is_available()
+    device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
+    dtype = torch.bfloat16
+    torch.manual_seed(1234)
+    S, N = args.msa, args.res
+    model = EvoformerStack(C_M, C_Z, C_S, args.blocks, blocks_per_ckpt=1)
+    randomize_zero_weights(torch, model, 99)
+    model = model.to(device=device, dtype=dtype).train()
+    host = make_inputs(torch, S, N, device, dtype, seed=7 + core.get_dp_rank())
+    dev_in = [t.to(device, non_blocking=True) for t in host]
+
+    def loss_fn(mod, m, z, mm, pm, tm, tz, ts):
+        return mse_loss(mod(m, z, mm, pm, None), tm, tz, ts)
+
+    trainer = FlatAdamTrainer(model, loss_fn, lr=1e-3, eps=1e-8, use_graph=use_cuda and not args.no_graph,
+                              replicated_param_filter=lambda n: n.startswith("linear."))
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device) if use_cuda else None
+
+    _lib.LAUNCHES[0] = 0
+    for _ in range(args.warmup):
+        trainer.step(*dev_in)
+    launches_per_step = trainer.launches_per_step if trainer.launches_per_step else None
+    fence(torch, dist)
+    sampler = ClockSampler(torch.cuda.current_device() if use_cuda else 0)
+    if use_cuda:
+        sampler.start()
+    # ---- device-timed region: K steps, inputs resident on the device ----
+    if use_cuda:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fence(torch, dist)
+        e0.record()
+        for _ in range(args.steps):
+            flush.zero_()
+            trainer.step(*dev_in)
+        e1.record()
+        fence(torch, dist)
+        ms = e0.elapsed_time(e1)
+    else:
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            trainer.step(*dev_in)
+        ms = (time.perf_counter() - t0) * 1e3
+    ms_per_step = max_over_ranks(torch, dist, ms / args.steps, device)
+    # ---- end-to-end region: H2D of the inputs and D2H of the loss every step ----
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    fence(torch, dist)
+    if use_cuda:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    t0 = time.perf_counter()
+    last = None
+    for _ in range(args.steps):
+        if use_cuda:
+            flush.zero_()
+        batch = [t.to(device, non_blocking=True) for t in host]
+        loss = trainer.step(*batch)
+        last = float(loss.float().cpu())          # device -> host read of the step's result
+    if use_cuda:
+        e1.record()
+        fence(torch, dist)
+        e2e_ms = e0.elapsed_time(e1)
+    else:
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+    e2e_per_step = max_over_ranks(torch, dist, e2e_ms / args.steps, device)
+    clocks = sampler.stop() if use_cuda else {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+    status = _lib.read_status() if use_cuda else [0]
+    if core.get_rank() == 0:
+        per_step = launches_per_step if launches_per_step is not None else _lib.LAUNCHES[0] // max(1, args.warmup + 2 * args.steps)
+        out = {
+            "metric": "evoformer48_train_step_time", "value": ms_per_step / 1e3, "unit": "s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
+            "scaling": "strong" if args.parallelism == "dap" else "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (m,z~N(0,1), 10% MSA rows masked, random-init weights)", "impl": "ours",
+            "config": {"model": "Evoformer stack, %d blocks, c_m=256 c_z=128, activation checkpoint per block, MSE loss, Adam" % args.blocks,
+                       "global_batch": 1 if args.parallelism == "dap" else world, "seq_len": N, "n_seq": S,
+                       "parallelism": ("dap%d" % world) if args.parallelism == "dap" else ("dp%d" % world),
+                       "l2": "256 MiB buffer written between timed steps", "cuda_graph": bool(trainer.graph is not None)},
+            "clocks": clocks,
+            "e2e": {"value": e2e_per_step / 1e3, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "gpu_launches": int(per_step) * args.steps,
+            "loss": last, "device_status": status[0],
+        }
+        print(json.dumps(out), flush=True)
+    core.shutdown()
+
+
+def run_reference(args):
+    def unavailable(why):
+        if int(os.environ.get("RANK", 0)) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+        return 0
+
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "fastfold")):
+        return unavailable("baseline/_ref/fastfold is missing (reference package not installed)")
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "stubs"))
+    sys.path.insert(0, ref)
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        return unavailable("the reference has no CPU path (its kernels are CUDA/Triton only)")
+    try:
+        from fastfold.distributed import init_dap
+        from fastfold.model.fastnn import EvoformerStack
+    except Exception as e:  # pragma: no cover
+        return unavailable("import of the reference failed: %r" % (e,))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.parallelism == "dp" and world > 1:
+        return unavailable("the reference's data parallelism lives in ColossalAI's engine, which is not installed")
+    init_dap(world)
+    device = torch.device("cuda", torch.cuda.current_device())
+    dtype = torch.bfloat16
+    torch.manual_seed(1234)
+    S, N = args.msa, args.res
+    model = EvoformerStack(c_m=C_M, c_z=C_Z, c_s=C_S, no_blocks=args.blocks, blocks_per_ckpt=1)
+    randomize_zero_weights(torch, model, 99)
+    model = model.to(device=device, dtype=dtype).train()
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-8)
+    host = make_inputs(torch, S, N, device, dtype, seed=7)
+    dev_in = [t.to(device, non_blocking=True) for t in host]
+
+    def step(m, z, mm, pm, tm, tz, ts):
+        opt.zero_grad(set_to_none=True)
+        out = model(m, z, mm, pm, None)
+        loss = mse_loss(out, tm, tz, ts)
+        loss.backward()
+        if world > 1:   # weights are replicated over the DAP group: sum their gradients
+            for p in model.parameters():
+                if p.grad is not None:
+                    dist.all_reduce(p.grad)
+        opt.step()
+        return loss.detach()
+
+    try:
+        for _ in range(args.warmup):
+            step(*dev_in)
+        torch.cuda.synchronize()
+    except Exception as e:
+        return unavailable("the reference failed during warm-up: %s" % (repr(e)[:300],))
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fence(torch, dist)
+    e0.record()
+    for _ in range(args.steps):
+        flush.zero_()
+        step(*dev_in)
+    e1.record()
+    fence(torch, dist)
+    ms_per_step = max_over_ranks(torch, dist, e0.elapsed_time(e1) / args.steps, device)
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fence(torch, dist)
+    e0.record()
+    last = None
+    for _ in range(args.steps):
+        flush.zero_()
+        batch = [t.to(device, non_blocking=True) for t in host]
+        last = float(step(*batch).float().cpu())
+    e1.record()
+    fence(torch, dist)
+    e2e_per_step = max_over_ranks(torch, dist, e0.elapsed_time(e1) / args.steps, device)
+    clocks = sampler.stop()
+    if int(os.environ.get("RANK", 0)) == 0:
+        out = {
+            "metric": "evoformer48_train_step_time", "value": ms_per_step / 1e3, "unit": "s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (m,z~N(0,1), 10% MSA rows masked, random-init weights)", "impl": "reference",
+            "config": {"model": "Evoformer stack, %d blocks, c_m=256 c_z=128, activation checkpoint per block, MSE loss, Adam" % args.blocks,
+                       "global_batch": 1, "seq_len": N, "n_seq": S, "parallelism": "dap%d" % world,
+                       "l2": "256 MiB buffer written between timed steps", "kernels": "reference Triton LayerNorm/softmax + cuBLAS + NCCL"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_per_step / 1e3, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "loss": last,
+        }
+        print(json.dumps(out), flush=True)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    args = parse()
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        # convenience: re-launch under torchrun when called plainly with --gpus N
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus), "--master-addr",
+               "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29541"), os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    if args.impl == "reference":
+        sys.exit(run_reference(args) or 0)
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

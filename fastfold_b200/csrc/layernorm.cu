@@ -1,0 +1,367 @@
+// LayerNorm over the last dimension, forward and backward, for bf16 / fp16 /
+// fp32 activations with fp32 statistics.
+//
+// The op is bandwidth-bound, so the design is about bytes: one warp owns one
+// row, the row is read once with 16-byte loads and kept in registers for the
+// mean, the variance (two-pass in registers, no cancellation) and the
+// normalisation; the backward kernel reads x and dy once, writes dx once and
+// folds the per-column sums for dgamma / dbeta into per-block partials that a
+// second tiny kernel reduces.  Rows up to 1024 elements take the register path
+// (c_m = 256, c_z = 128, c_s = 384, c_e = c_t = 64 all do); longer rows fall to
+// a looped path.  The optional `transposed input` variant normalises over the
+// leading dimension of a [C, rows] tensor and writes [rows, C]: it is the
+// LayerNorm that follows the per-channel triangle-multiplication GEMM, whose
+// output is channel-major.
+//
+// Replaces fastfold/model/fastnn/kernel/cuda_native/csrc/layer_norm_cuda_kernel.cu
+// (forward :61-152, gamma/beta partial sums :224-333, input gradient :335-443)
+// and the Triton twins in kernel/triton/layer_norm.py.
+#include "common.cuh"
+
+namespace ffb {
+
+constexpr int LN_WARPS = 4;
+
+template <typename T, int VPL>  // VPL = values per lane (multiple of 8 for 16-bit types, 4 for fp32)
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                              const T* __restrict__ beta, T* __restrict__ y,
+                                                              float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                              long long rows, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int NV = VPL / VEC;
+  float v[VPL];
+  const T* xr = x + row * C;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c0 = (i * 32 + lane) * VEC;
+    if (c0 < C) {
+      uint4 u = *reinterpret_cast<const uint4*>(xr + c0);
+      const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        v[i * VEC + j] = to_f<T>(e[j]);
+        s += v[i * VEC + j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v[i * VEC + j] = 0.f;
+    }
+  }
+  const float mean = warp_sum(s) / C;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c0 = (i * 32 + lane) * VEC;
+    if (c0 < C) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float d = v[i * VEC + j] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / C + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  T* yr = y + row * C;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c0 = (i * 32 + lane) * VEC;
+    if (c0 < C) {
+      uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0);
+      uint4 ub = *reinterpret_cast<const uint4*>(beta + c0);
+      const T* ge = reinterpret_cast<const T*>(&ug);
+      const T* be = reinterpret_cast<const T*>(&ub);
+      uint4 uo;
+      T* oe = reinterpret_cast<T*>(&uo);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) oe[j] = from_f<T>((v[i * VEC + j] - mean) * rstd * to_f<T>(ge[j]) + to_f<T>(be[j]));
+      *reinterpret_cast<uint4*>(yr + c0) = uo;
+    }
+  }
+}
+
+// Any C, any alignment: three passes over the row from global memory / L2.
+template <typename T>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_generic_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                                      const T* __restrict__ beta, T* __restrict__ y,
+                                                                      float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                      long long rows, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * C;
+  float s = 0.f;
+  for (int c = lane; c < C; c += 32) s += to_f<T>(xr[c]);
+  const float mean = warp_sum(s) / C;
+  float q = 0.f;
+  for (int c = lane; c < C; c += 32) {
+    const float d = to_f<T>(xr[c]) - mean;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(warp_sum(q) / C + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  T* yr = y + row * C;
+  for (int c = lane; c < C; c += 32) yr[c] = from_f<T>((to_f<T>(xr[c]) - mean) * rstd * to_f<T>(gamma[c]) + to_f<T>(beta[c]));
+}
+
+// Backward.  Block = LN_WARPS warps, each block walks rows blockIdx.x, +gridDim.x, ...
+// Per-lane column ownership is fixed, so dgamma/dbeta partial sums stay in
+// registers over the whole walk and are combined across the block's warps at
+// the end: part[blockIdx.x][0][c] = sum dy*xhat, part[blockIdx.x][1][c] = sum dy.
+template <typename T, int VPL>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                              const T* __restrict__ gamma, const float* __restrict__ mean,
+                                                              const float* __restrict__ rstd, T* __restrict__ dx,
+                                                              float* __restrict__ part, long long rows, int C) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int NV = VPL / VEC;
+  __shared__ float red[LN_WARPS][2];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  float g[VPL], dg[VPL], db[VPL];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c0 = (i * 32 + lane) * VEC;
+    if (c0 < C) {
+      uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0);
+      const T* ge = reinterpret_cast<const T*>(&ug);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) g[i * VEC + j] = to_f<T>(ge[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) g[i * VEC + j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) dg[i * VEC + j] = db[i * VEC + j] = 0.f;
+  }
+  (void)red;
+  for (long long row = (long long)blockIdx.x * LN_WARPS + warp; row < rows; row += (long long)gridDim.x * LN_WARPS) {
+    const float mu = mean[row], rs = rstd[row];
+    float xh[VPL], d[VPL];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c0 = (i * 32 + lane) * VEC;
+      if (c0 < C) {
+        uint4 ux = *reinterpret_cast<const uint4*>(x + row * C + c0);
+        uint4 ud = *reinterpret_cast<const uint4*>(dy + row * C + c0);
+        const T* xe = reinterpret_cast<const T*>(&ux);
+        const T* de = reinterpret_cast<const T*>(&ud);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          const int k = i * VEC + j;
+          xh[k] = (to_f<T>(xe[j]) - mu) * rs;
+          d[k] = to_f<T>(de[j]);
+          dg[k] += d[k] * xh[k];
+          db[k] += d[k];
+          const float gd = g[k] * d[k];
+          s1 += gd;
+          s2 += gd * xh[k];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) xh[i * VEC + j] = d[i * VEC + j] = 0.f;
+      }
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c0 = (i * 32 + lane) * VEC;
+      if (c0 < C) {
+        uint4 uo;
+        T* oe = reinterpret_cast<T*>(&uo);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          const int k = i * VEC + j;
+          oe[j] = from_f<T>(rs * (g[k] * d[k] - s1 - xh[k] * s2));
+        }
+        *reinterpret_cast<uint4*>(dx + row * C + c0) = uo;
+      }
+    }
+  }
+  // combine the block's warps through global atomics on the block's partial row
+  float* p0 = part + (long long)blockIdx.x * 2 * C;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c0 = (i * 32 + lane) * VEC;
+    if (c0 < C) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        atomicAdd(p0 + c0 + j, dg[i * VEC + j]);
+        atomicAdd(p0 + C + c0 + j, db[i * VEC + j]);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                                      const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+                                      float* __restrict__ part, long long rows, int C) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  float* p0 = part + (long long)blockIdx.x * 2 * C;
+  for (long long row = (long long)blockIdx.x * LN_WARPS + warp; row < rows; row += (long long)gridDim.x * LN_WARPS) {
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane; c < C; c += 32) {
+      const float xh = (to_f<T>(x[row * C + c]) - mu) * rs;
+      const float d = to_f<T>(dy[row * C + c]);
+      const float gd = to_f<T>(gamma[c]) * d;
+      s1 += gd;
+      s2 += gd * xh;
+      atomicAdd(p0 + c, d * xh);
+      atomicAdd(p0 + C + c, d);
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+    for (int c = lane; c < C; c += 32) {
+      const float xh = (to_f<T>(x[row * C + c]) - mu) * rs;
+      const float d = to_f<T>(dy[row * C + c]);
+      dx[row * C + c] = from_f<T>(rs * (to_f<T>(gamma[c]) * d - s1 - xh * s2));
+    }
+  }
+}
+
+// dgamma[c] = sum_b part[b][0][c], dbeta[c] = sum_b part[b][1][c]
+template <typename T>
+__global__ void ln_bwd_reduce_kernel(const float* __restrict__ part, int nblocks, int C, T* __restrict__ dgamma,
+                                     T* __restrict__ dbeta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * C) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += part[(long long)b * 2 * C + c];
+  if (c < C) dgamma[c] = from_f<T>(s);
+  else dbeta[c - C] = from_f<T>(s);
+}
+
+// LayerNorm over the leading dimension of x[C][rows] (row index contiguous),
+// output y[rows][C].  One thread per row for the statistics (coalesced across
+// the warp), staged through shared memory so that the [rows, C] writes are
+// 16-byte coalesced too.  C <= 256, bf16.
+constexpr int LNT_ROWS = 32;
+__global__ void __launch_bounds__(256) ln_fwd_transposed_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma,
+                                                               const bf16* __restrict__ beta, bf16* __restrict__ y,
+                                                               float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                               long long rows, int C, float eps) {
+  extern __shared__ float tile[];  // [C][LNT_ROWS + 1]
+  __shared__ float s_mean[LNT_ROWS], s_rstd[LNT_ROWS];
+  const long long r0 = (long long)blockIdx.x * LNT_ROWS;
+  const int tx = threadIdx.x & 31;   // row within the tile
+  const int ty = threadIdx.x >> 5;   // 0..7
+  for (int c = ty; c < C; c += 8) {
+    const long long r = r0 + tx;
+    tile[c * (LNT_ROWS + 1) + tx] = (r < rows) ? __bfloat162float(x[(long long)c * rows + r]) : 0.f;
+  }
+  __syncthreads();
+  if (ty == 0) {
+    float s = 0.f;
+    for (int c = 0; c < C; ++c) s += tile[c * (LNT_ROWS + 1) + tx];
+    const float mu = s / C;
+    float q = 0.f;
+    for (int c = 0; c < C; ++c) {
+      const float d = tile[c * (LNT_ROWS + 1) + tx] - mu;
+      q += d * d;
+    }
+    const float rs = rsqrtf(q / C + eps);
+    s_mean[tx] = mu;
+    s_rstd[tx] = rs;
+    if (r0 + tx < rows) {
+      if (mean_out) mean_out[r0 + tx] = mu;
+      if (rstd_out) rstd_out[r0 + tx] = rs;
+    }
+  }
+  __syncthreads();
+  // write: consecutive threads -> consecutive channels of one row
+  for (int idx = threadIdx.x; idx < LNT_ROWS * C; idx += blockDim.x) {
+    const int r = idx / C, c = idx - r * C;
+    if (r0 + r < rows)
+      y[(r0 + r) * C + c] = __float2bfloat16((tile[c * (LNT_ROWS + 1) + r] - s_mean[r]) * s_rstd[r] * __bfloat162float(gamma[c]) +
+                                             __bfloat162float(beta[c]));
+  }
+}
+
+template <typename T>
+static int ln_fwd_dispatch(const T* x, const T* g, const T* b, T* y, float* mean, float* rstd, long long rows, int C, float eps,
+                           cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(T);
+  const dim3 grid((unsigned)((rows + LN_WARPS - 1) / LN_WARPS));
+  const bool aligned = (C % VEC == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                                           reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(b)) % 16 == 0);
+  if (aligned && C <= 32 * VEC) ln_fwd_kernel<T, VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
+  else if (aligned && C <= 64 * VEC) ln_fwd_kernel<T, 2 * VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
+  else if (aligned && C <= 128 * VEC) ln_fwd_kernel<T, 4 * VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
+  else ln_fwd_generic_kernel<T><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+template <typename T>
+static int ln_bwd_dispatch(const T* dy, const T* x, const T* g, const float* mean, const float* rstd, T* dx, float* part,
+                           int nblocks, T* dgamma, T* dbeta, long long rows, int C, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(T);
+  if (cudaMemsetAsync(part, 0, sizeof(float) * 2 * C * nblocks, st) != cudaSuccess) return -1;
+  const bool aligned = (C % VEC == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
+                                           reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(g)) % 16 == 0);
+  if (aligned && C <= 32 * VEC) ln_bwd_kernel<T, VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
+  else if (aligned && C <= 64 * VEC) ln_bwd_kernel<T, 2 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
+  else if (aligned && C <= 128 * VEC) ln_bwd_kernel<T, 4 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
+  else ln_bwd_generic_kernel<T><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
+  ln_bwd_reduce_kernel<T><<<(2 * C + 127) / 128, 128, 0, st>>>(part, nblocks, C, dgamma, dbeta);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace ffb
+
+using namespace ffb;
+
+extern "C" {
+
+// dtype: 0 = fp32, 1 = fp16, 2 = bf16
+int ffb_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, long long rows,
+                      int C, float eps, int dtype, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (rows <= 0) return 0;
+  switch (dtype) {
+    case 0: return ln_fwd_dispatch<float>((const float*)x, (const float*)gamma, (const float*)beta, (float*)y, mean, rstd, rows, C, eps, st);
+    case 1: return ln_fwd_dispatch<__half>((const __half*)x, (const __half*)gamma, (const __half*)beta, (__half*)y, mean, rstd, rows, C, eps, st);
+    case 2: return ln_fwd_dispatch<bf16>((const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps, st);
+  }
+  return -2;
+}
+
+// part: fp32 workspace of 2 * C * nblocks floats (zeroed here).
+int ffb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                      float* part, int nblocks, void* dgamma, void* dbeta, long long rows, int C, int dtype, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (rows <= 0) return 0;
+  switch (dtype) {
+    case 0: return ln_bwd_dispatch<float>((const float*)dy, (const float*)x, (const float*)gamma, mean, rstd, (float*)dx, part, nblocks, (float*)dgamma, (float*)dbeta, rows, C, st);
+    case 1: return ln_bwd_dispatch<__half>((const __half*)dy, (const __half*)x, (const __half*)gamma, mean, rstd, (__half*)dx, part, nblocks, (__half*)dgamma, (__half*)dbeta, rows, C, st);
+    case 2: return ln_bwd_dispatch<bf16>((const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part, nblocks, (bf16*)dgamma, (bf16*)dbeta, rows, C, st);
+  }
+  return -2;
+}
+
+// x: [C][rows] bf16 -> y: [rows][C] bf16, normalised over C (C <= 256).
+int ffb_layernorm_fwd_transposed(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                                 long long rows, int C, float eps, void* stream) {
+  if (C > 256) return -2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t smem = sizeof(float) * C * (LNT_ROWS + 1);
+  ln_fwd_transposed_kernel<<<(unsigned)((rows + LNT_ROWS - 1) / LNT_ROWS), 256, smem, st>>>(
+      (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // extern "C"

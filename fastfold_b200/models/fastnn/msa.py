@@ -1,0 +1,149 @@
+"""MSA half of the Evoformer / extra-MSA blocks (names as in fastfold/model/fastnn/msa.py)."""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ... import ops as K
+from ...parallel import core
+from ...parallel.comm import gather, scatter, row_to_col, col_to_row
+from ...parallel.comm_async import all_to_all_async, all_to_all_async_opp
+from ...utils.checkpointing import checkpoint_blocks
+from .ops import (ChunkMSARowAttentionWithPairBias, ChunkMSAColumnGlobalAttention, ChunkTransition, GlobalAttention,
+                  OutProductMean, SelfAttention, Transition, _fusable)
+from .triangle import PairCore, pad_amount
+
+
+class MSARowAttentionWithPairBias(ChunkMSARowAttentionWithPairBias):
+    """Row-wise gated self attention with pair bias (Algorithm 7); ``M_raw [1, S/P, N, c_m]``."""
+
+    def __init__(self, d_node, d_pair, c=32, n_head=8, p_drop=0.15):
+        super().__init__(d_node=d_node, d_pair=d_pair, c=c, n_head=n_head, p_drop=p_drop)
+
+
+class MSAColumnAttention(nn.Module):
+    """Column-wise gated self attention (Algorithm 8); ``M_raw [1, S, N/P, c_m]``."""
+
+    def __init__(self, d_node, c=32, n_head=8):
+        super().__init__()
+        self.d_node, self.c, self.n_head = d_node, c, n_head
+        self.layernormM = K.LayerNorm(d_node)
+        self.attention = SelfAttention(qkv_dim=d_node, c=c, n_head=n_head, out_dim=d_node, gating=True)
+
+    def forward(self, M_raw, M_mask):
+        M = self.layernormM(M_raw.transpose(-2, -3).contiguous())
+        out, _ = self.attention(M, M_mask.transpose(-1, -2).contiguous())
+        return M_raw + out.transpose(-2, -3)
+
+
+class MSAColumnGlobalAttention(ChunkMSAColumnGlobalAttention):
+    pass
+
+
+class MSACore(nn.Module):
+    def __init__(self, d_node, d_pair, p_drop=0.15):
+        super().__init__()
+        self.MSARowAttentionWithPairBias = MSARowAttentionWithPairBias(d_node=d_node, d_pair=d_pair, p_drop=p_drop)
+        self.MSAColumnAttention = MSAColumnAttention(d_node=d_node)
+        self.MSATransition = Transition(d=d_node)
+
+    def forward(self, node, pair, node_mask, dropmask=None):
+        node_mask_row = scatter(node_mask, dim=1)
+        node = self.MSARowAttentionWithPairBias(node, pair, node_mask_row, dropmask)
+        node = row_to_col(node)
+        node_mask_col = scatter(node_mask, dim=2)
+        node = self.MSAColumnAttention(node, node_mask_col)
+        node = self.MSATransition(node)
+        return node
+
+
+class ExtraMSACore(nn.Module):
+    def __init__(self, d_node, d_pair, p_drop=0.15):
+        super().__init__()
+        self.MSARowAttentionWithPairBias = ChunkMSARowAttentionWithPairBias(d_node=d_node, d_pair=d_pair, p_drop=p_drop, c=8)
+        self.MSAColumnAttention = ChunkMSAColumnGlobalAttention(d_node=d_node, c=8)
+        self.MSATransition = ChunkTransition(d=d_node)
+
+    def forward(self, node, pair, node_mask, dropmask=None):
+        node_mask_row = scatter(node_mask, dim=1)
+        node = self.MSARowAttentionWithPairBias(node, pair, node_mask_row, dropmask)
+        node = row_to_col(node)
+        node_mask_col = scatter(node_mask, dim=2)
+        node = self.MSAColumnAttention(node, node_mask_col)
+        node = self.MSATransition(node)
+        return node
+
+    def inplace(self, node, pair, node_mask, dropmask=None):
+        node[0] = self.forward(node[0], pair[0] if isinstance(pair, list) else pair, node_mask, dropmask)
+        return node
+
+
+class ExtraMSABlock(nn.Module):
+    """One extra-MSA block under DAP; pads both the sequence-count and the residue axis to the DAP size."""
+
+    def __init__(self, c_m, c_z, first_block, last_block, is_multimer=False):
+        super().__init__()
+        self.first_block, self.last_block = first_block, last_block
+        self.msa_stack = ExtraMSACore(c_m, c_z, p_drop=0.15)
+        self.communication = OutProductMean(n_feat=c_m, n_feat_out=c_z, n_feat_proj=32)
+        self.pair_stack = PairCore(d_pair=c_z)
+        self.is_multimer = is_multimer
+
+    def forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
+        P = core.get_dap_size()
+        cnt_pad = pad_amount(msa_mask.size(-2), P)
+        len_pad = pad_amount(pair_mask.size(-1), P)
+        if self.first_block:
+            m = F.pad(m.unsqueeze(0), (0, 0, 0, len_pad, 0, cnt_pad))
+            z = F.pad(z.unsqueeze(0), (0, 0, 0, len_pad, 0, len_pad))
+            m = scatter(m, dim=1) if not self.is_multimer else scatter(m, dim=2)
+            z = scatter(z, dim=1)
+        msa_mask = F.pad(msa_mask.unsqueeze(0), (0, len_pad, 0, cnt_pad))
+        pair_mask = F.pad(pair_mask.unsqueeze(0), (0, len_pad, 0, len_pad))
+        d_msa = None if _drop is None else _drop.get("msa_row")
+        if not self.is_multimer:
+            m = self.msa_stack(m, z, msa_mask, d_msa)
+            z = self.communication(m, msa_mask, z)
+            m, work = all_to_all_async(m, 1, 2)
+            z = self.pair_stack(z, pair_mask, _drop)
+            m = all_to_all_async_opp(m, work, 1, 2)
+        else:
+            z = self.communication(m, msa_mask, z)
+            z_ori = z
+            m, work = all_to_all_async(m, 1, 2)
+            z = self.pair_stack(z, pair_mask, _drop)
+            m = all_to_all_async_opp(m, work, 1, 2)
+            m = self.msa_stack(m, z_ori, msa_mask, d_msa)
+        if self.last_block:
+            m = gather(m, dim=1) if not self.is_multimer else gather(m, dim=2)
+            z = gather(z, dim=1)
+            m = m[:, :m.shape[1] - cnt_pad, :m.shape[2] - len_pad, :].squeeze(0)
+            z = z[:, :z.shape[1] - len_pad, :z.shape[2] - len_pad, :].squeeze(0)
+        return m, z
+
+    def inplace(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
+        m[0], z[0] = self.forward(m[0], z[0], msa_mask, pair_mask, chunk_size, _mask_trans, _drop)
+        return m, z
+
+
+class ExtraMSAStack(nn.Module):
+    """Algorithm 18; returns the updated pair representation only."""
+
+    def __init__(self, c_m, c_z, no_blocks, clear_cache_between_blocks=False, is_multimer=False, blocks_per_ckpt=None, **kwargs):
+        super().__init__()
+        self.clear_cache_between_blocks = clear_cache_between_blocks
+        self.blocks_per_ckpt = blocks_per_ckpt
+        self.blocks = nn.ModuleList([
+            ExtraMSABlock(c_m=c_m, c_z=c_z, first_block=(i == 0), last_block=(i == no_blocks - 1), is_multimer=is_multimer)
+            for i in range(no_blocks)
+        ])
+
+    def forward(self, m, z, chunk_size=None, msa_mask=None, pair_mask=None, _mask_trans=True):
+        from .evoformer import run_blocks
+        m, z = run_blocks(self.blocks, m, z, msa_mask, pair_mask, chunk_size, _mask_trans, self.training,
+                          self.blocks_per_ckpt if self.training else None, c_m=m.shape[-1], c_z=z.shape[-1])
+        return z
+
+    def inplace(self, m, z, chunk_size=None, msa_mask=None, pair_mask=None, _mask_trans=True):
+        z[0] = self.forward(m[0], z[0], chunk_size, msa_mask, pair_mask, _mask_trans)
+        m[0] = None
+        return z

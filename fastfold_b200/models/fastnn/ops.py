@@ -1,0 +1,610 @@
+"""Building blocks of the fast (DAP-aware) trunk.
+
+Module and parameter names follow the reference's ``fastfold/model/fastnn/ops.py``
+so that its pickled models and ``inject_fastnn`` name map stay valid
+(``to_qkv``, ``gating_linear``, ``gating_bias``, ``o_linear``, ``out_bias``,
+``left_right_projection``, ``left_right_gate``, ``output_gate``,
+``output_projection``, ``output_bias``, ``layernorm1/2``, ``linear_b`` ...).
+The implementation is new: each forward is a short chain of fused kernels
+(``fastfold_b200.ops``), with a fully fused no-grad variant (GEMM epilogues
+carry bias, gate, mask, dropout and residual) used for inference and for the
+first pass of activation checkpointing, and a variant that saves what the
+hand-written backward kernels need when gradients are required.
+
+``set_chunk_size`` keeps the reference's meaning (ops.py:31-42, 98, 164, 326):
+attention in groups of ``C`` rows, transitions in ``48*C`` rows, outer product
+in ``C`` columns, triangle multiplication slab by slab.  Results do not depend
+on it; it only bounds transient memory.
+"""
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ... import ops as K
+from ...ops.attention import attention_core
+from ...parallel import comm, core
+from ...parallel.comm import gather, scatter
+from ...parallel.comm_async import (gather_async, gather_async_opp, broadcast_async, broadcast_async_opp)
+from .initializer import glorot_uniform_af
+
+CHUNK_SIZE = None
+DEBUG = False
+
+
+def set_chunk_size(chunk_size):
+    global CHUNK_SIZE
+    CHUNK_SIZE = chunk_size
+
+
+def get_chunk_size():
+    return CHUNK_SIZE
+
+
+def _fusable(x):
+    """True when the no-grad, fully fused bf16 CUDA path applies."""
+    return x.is_cuda and x.dtype == torch.bfloat16 and not torch.is_grad_enabled()
+
+
+def _mask_idx(x, mask):
+    from ...ops.fused_ops import _mask_index
+    m2, div, mod = _mask_index(x, mask)
+    return (m2.contiguous(), div, mod)
+
+
+def _apply_dropout(mask, p, training):
+    """Reference call style: a tensor of ones goes in, dropout is applied to it (ops.py:405, msa.py:70)."""
+    if mask is None or not training:
+        return None
+    return mask
+
+
+def make_dropout_mask(shape, p, device, dtype, generator=None):
+    """Bernoulli keep-mask scaled by 1/(1-p)."""
+    keep = torch.rand(shape, device=device, generator=generator) >= p
+    return keep.to(dtype) / (1.0 - p)
+
+
+class DropoutRowwise(nn.Module):
+    def __init__(self, p):
+        super().__init__()
+        self.p = p
+
+    def forward(self, x):
+        return x * F.dropout(torch.ones_like(x[:, 0:1, :, :]), p=self.p, training=self.training)
+
+
+class DropoutColumnwise(nn.Module):
+    def __init__(self, p):
+        super().__init__()
+        self.p = p
+
+    def forward(self, x):
+        return x * F.dropout(torch.ones_like(x[:, :, 0:1, :]), p=self.p, training=self.training)
+
+
+class Linear(nn.Linear):
+    """nn.Linear with AlphaFold initialisers, evaluated by the tcgen05 GEMM on CUDA bf16 tensors."""
+
+    def __init__(self, feature_in, feature_out, initializer="linear", use_bias=True, bias_init=0.0):
+        super().__init__(feature_in, feature_out, bias=use_bias)
+        self.use_bias = use_bias
+        if initializer == "linear":
+            glorot_uniform_af(self.weight, gain=1.0)
+        elif initializer == "relu":
+            glorot_uniform_af(self.weight, gain=2.0)
+        elif initializer in ("zeros", "zero"):
+            nn.init.zeros_(self.weight)
+        if self.use_bias:
+            with torch.no_grad():
+                self.bias.fill_(bias_init)
+
+    def forward(self, x, act=None):
+        return K.linear(x, self.weight, self.bias, act)
+
+
+# ---------------------------------------------------------------------------
+# Transition
+# ---------------------------------------------------------------------------
+class Transition(nn.Module):
+    def __init__(self, d, n=4):
+        super().__init__()
+        self.norm = K.LayerNorm(d)
+        self.linear1 = Linear(d, n * d, initializer="relu")
+        self.linear2 = Linear(n * d, d, initializer="zeros")
+
+    def _one(self, src):
+        x = self.norm(src)
+        h = self.linear1(x, act="relu")
+        if _fusable(src):
+            s2 = src.reshape(-1, src.shape[-1])
+            out = K.gemm(h.reshape(-1, h.shape[-1]), self.linear2.weight, bias=self.linear2.bias, resid=s2)
+            return out.reshape(src.shape)
+        return src + self.linear2(h)
+
+    def forward(self, src):
+        if CHUNK_SIZE is None:
+            return self._one(src)
+        step = CHUNK_SIZE * 48
+        out = torch.empty_like(src)
+        for ax in range(0, src.shape[1], step):
+            out[:, ax:ax + step] = self._one(src[:, ax:ax + step])
+        return out
+
+    def inplace(self, src):
+        step = src[0].shape[1] if CHUNK_SIZE is None else CHUNK_SIZE * 48
+        for ax in range(0, src[0].shape[1], step):
+            src[0][:, ax:ax + step] = self._one(src[0][:, ax:ax + step])
+        return src
+
+
+ChunkTransition = Transition
+
+
+# ---------------------------------------------------------------------------
+# Outer product mean
+# ---------------------------------------------------------------------------
+class OutProductMean(nn.Module):
+    def __init__(self, n_feat=64, n_feat_out=128, n_feat_proj=32):
+        super().__init__()
+        self.layernormM = K.LayerNorm(n_feat)
+        self.linear_a = Linear(n_feat, n_feat_proj)
+        self.linear_b = Linear(n_feat, n_feat_proj)
+        self.o_linear = Linear(n_feat_proj * n_feat_proj, n_feat_out, initializer="zero", use_bias=True)
+        self.n_feat_proj = n_feat_proj
+
+    def _outer(self, left, right_all, inv_norm, Z_raw):
+        """left [1,S,ni,d], right_all [1,S,N,e] -> Z_raw + o_linear(outer) * inv_norm."""
+        S, ni, d = left.shape[1], left.shape[2], left.shape[3]
+        N, e = right_all.shape[2], right_all.shape[3]
+        l2 = left.reshape(S, ni * d)
+        r2 = right_all.reshape(S, N * e)
+        if left.is_cuda and left.dtype == torch.bfloat16 and (ni * d) % 8 == 0 and (N * e) % 64 == 0 and ni * d >= 64:
+            if torch.is_grad_enabled() and (l2.requires_grad or r2.requires_grad):
+                o = _OuterProduct.apply(l2, r2)
+            else:
+                o = K.gemm(l2, r2, a_mn=True, b_mn=True)          # [(i d), (j e)], contraction over S
+        else:
+            o = torch.matmul(l2.t(), r2)
+        o = o.reshape(ni, d, N, e).permute(0, 2, 1, 3).reshape(1, ni, N, d * e)
+        if _fusable(o):
+            out = K.gemm(o.reshape(ni * N, d * e), self.o_linear.weight, bias=self.o_linear.bias,
+                         rowscale=inv_norm.reshape(-1), resid=Z_raw.reshape(ni * N, -1))
+            return out.reshape(Z_raw.shape)
+        return Z_raw + self.o_linear(o) * inv_norm.to(o.dtype)
+
+    def forward(self, M, M_mask, Z_raw):
+        M = self.layernormM(M)
+        right_act = self.linear_b(M)
+        M_mask = M_mask.unsqueeze(-1)
+        M_mask_col = scatter(M_mask, dim=2)
+        # mask before the gather: identical result, and the gathered operand is ready to use
+        right_act = right_act * M_mask_col.to(right_act.dtype)
+        right_act_all, work = gather_async(right_act, dim=2)
+        left_act = self.linear_a(M) * M_mask_col.to(M.dtype)
+        norm = torch.einsum("bsid,bsjd->bijd", M_mask_col.float(), M_mask.float()) + 1e-3
+        inv_norm = 1.0 / norm
+        right_act_all = gather_async_opp(right_act_all, work, dim=2)
+        if CHUNK_SIZE is None:
+            return self._outer(left_act, right_act_all, inv_norm, Z_raw)
+        out = torch.empty_like(Z_raw)
+        for ax in range(0, left_act.shape[2], CHUNK_SIZE):
+            out[:, ax:ax + CHUNK_SIZE] = self._outer(left_act[:, :, ax:ax + CHUNK_SIZE].contiguous(), right_act_all,
+                                                     inv_norm[:, ax:ax + CHUNK_SIZE], Z_raw[:, ax:ax + CHUNK_SIZE])
+        return out
+
+    def inplace(self, M, M_mask, Z_raw):
+        Z_raw[0] = self.forward(M, M_mask, Z_raw[0])
+        return Z_raw
+
+
+class _OuterProduct(torch.autograd.Function):
+    """o[(i d), (j e)] = sum_s l[s, (i d)] r[s, (j e)] with both gradients on the tcgen05 kernel."""
+
+    @staticmethod
+    def forward(ctx, l2, r2):
+        ctx.save_for_backward(l2, r2)
+        return K.gemm(l2, r2, a_mn=True, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, do):
+        l2, r2 = ctx.saved_tensors
+        do = do.contiguous()
+        dl = dr = None
+        if ctx.needs_input_grad[0]:
+            dl = K.gemm(r2, do)                      # [S, (i d)] = r2 [S, (j e)] x do [(i d), (j e)]^T
+        if ctx.needs_input_grad[1]:
+            dr = K.gemm(l2, do, b_mn=True)           # [S, (j e)] = l2 [S, (i d)] x do [(i d), (j e)]
+        return dl, dr
+
+
+# ---------------------------------------------------------------------------
+# Gated self attention
+# ---------------------------------------------------------------------------
+class SelfAttention(nn.Module):
+    """Multi-head gated self attention on ``[b1, b2, n, c]`` (attention along ``n``)."""
+
+    def __init__(self, qkv_dim, c, n_head, out_dim, gating=True, last_bias_fuse=False):
+        super().__init__()
+        self.qkv_dim, self.c, self.n_head, self.out_dim = qkv_dim, c, n_head, out_dim
+        self.gating = gating
+        self.last_bias_fuse = last_bias_fuse
+        self.scaling = self.c ** (-0.5)
+        self.to_qkv = Linear(qkv_dim, 3 * n_head * c, initializer="linear", use_bias=False)
+        if gating:
+            self.gating_bias = nn.Parameter(torch.ones((n_head * c,)))
+            self.gating_linear = Linear(qkv_dim, n_head * c, initializer="zero", use_bias=False)
+        self.o_linear = Linear(n_head * c, out_dim, initializer="zero", use_bias=(not last_bias_fuse))
+
+    def _bias(self, nonbatched_bias):
+        if nonbatched_bias is None:
+            return None
+        if nonbatched_bias[-1] == -1:
+            return nonbatched_bias[0]
+        b = gather_async_opp(*nonbatched_bias, dim=1)
+        return b.permute(0, 3, 1, 2).contiguous()          # 'b q k h -> b h q k'
+
+    def _one(self, x, mask, bias, tail):
+        b1, b2, n, _ = x.shape
+        H, d = self.n_head, self.c
+        qkv = self.to_qkv(x).reshape(b1, b2, n, 3, H, d)
+        q, k, v = (qkv[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
+        o = attention_core(q, k, v, mask, None if bias is None else bias.unsqueeze(1), self.scaling)
+        o = o.permute(0, 1, 3, 2, 4).reshape(b1, b2, n, H * d)
+        fused = _fusable(x)
+        if self.gating:
+            if fused:
+                o = K.gemm(x.reshape(-1, x.shape[-1]), self.gating_linear.weight, bias=self.gating_bias, act="sigmoid",
+                           mul=o.reshape(-1, H * d)).reshape(b1, b2, n, H * d)
+            else:
+                o = K.bias_sigmod_ele(self.gating_linear(x), self.gating_bias, o)
+        if tail is not None and fused:
+            out_bias, dmask, resid = tail
+            out = K.gemm(o.reshape(-1, H * d), self.o_linear.weight, bias=out_bias if out_bias is not None else self.o_linear.bias,
+                         dmask=dmask, resid=resid.reshape(-1, resid.shape[-1]))
+            return out.reshape(resid.shape), True
+        return self.o_linear(o), False
+
+    def forward(self, in_data, mask, nonbatched_bias=None, tail=None):
+        """``tail=(out_bias, (mask2d, div, mod) or None, residual)`` lets the output projection absorb the
+        bias / dropout / residual that follow it; the second return value says whether it did."""
+        bias = self._bias(nonbatched_bias)
+        if CHUNK_SIZE is None or CHUNK_SIZE >= in_data.shape[1]:
+            return self._one(in_data, mask, bias, tail)
+        outs = []
+        for ax in range(0, in_data.shape[1], CHUNK_SIZE):
+            o, _ = self._one(in_data[:, ax:ax + CHUNK_SIZE], mask[:, ax:ax + CHUNK_SIZE], bias, None)
+            outs.append(o)
+        return torch.cat(outs, dim=1), False
+
+
+class GlobalAttention(nn.Module):
+    """Column-wise global attention of the extra-MSA stack: one mean-pooled query per column."""
+
+    def __init__(self, qkv_dim, c, n_head, out_dim):
+        super().__init__()
+        self.qkv_dim, self.c, self.n_head, self.out_dim = qkv_dim, c, n_head, out_dim
+        self.scaling = self.c ** (-0.5)
+        self.eps = 1e-10
+        self.inf = 1e9
+        self.to_q = Linear(qkv_dim, c * n_head, use_bias=False)
+        self.to_kv = Linear(qkv_dim, 2 * c, initializer="linear", use_bias=False)
+        self.gating_bias = nn.Parameter(torch.ones((n_head * c,)))
+        self.gating_linear = Linear(qkv_dim, n_head * c, initializer="zero", use_bias=False)
+        self.o_linear = Linear(n_head * c, out_dim, initializer="zero")
+
+    def _one(self, m, mask):
+        mk = mask.to(m.dtype)
+        q = torch.sum(m * mk.unsqueeze(-1), dim=-2) / (torch.sum(mk, dim=-1)[..., None] + self.eps)
+        q = self.to_q(q * self.scaling)
+        q = q.view(q.shape[:-1] + (self.n_head, -1))                     # [b1, b2, H, c]
+        k, v = self.to_kv(m).chunk(2, dim=-1)                            # [b1, b2, S, c]
+        logits = torch.matmul(q, k.transpose(-1, -2))                    # [b1, b2, H, S]
+        weights = K.fused_softmax(logits, mk)
+        o = torch.matmul(weights, v)                                     # [b1, b2, H, c]
+        o = o.reshape(o.shape[:-2] + (self.n_head * self.c,))
+        gate = self.gating_linear(m)
+        o = K.bias_sigmod_ele(gate, self.gating_bias, o.unsqueeze(-2).expand_as(gate).contiguous())
+        return self.o_linear(o)
+
+    def forward(self, m, mask):
+        if CHUNK_SIZE is None:
+            return self._one(m, mask)
+        outs = [self._one(m[:, ax:ax + CHUNK_SIZE], mask[:, ax:ax + CHUNK_SIZE]) for ax in range(0, m.shape[1], CHUNK_SIZE)]
+        return torch.cat(outs, dim=1)
+
+
+# ---------------------------------------------------------------------------
+# Triangle multiplication
+# ---------------------------------------------------------------------------
+class _TriangleMultiplication(nn.Module):
+    """Shared body of the outgoing / incoming triangular multiplicative update.
+
+    outgoing (z row-sharded  [1, N/P, N, c]): ab[i, j] = sum_k a[i, k] * b[j, k]; the right operand is
+        all-gathered along rows.
+    incoming (z column-sharded [1, N, N/P, c]): ab[i, j] = sum_k a[k, i] * b[k, j]; the left operand is
+        all-gathered along columns.
+    The per-channel contraction runs as one batched tcgen05 GEMM over channel-major operands
+    (K-major for outgoing, MN-major for incoming).
+    """
+    outgoing = True
+
+    def __init__(self, d_pair, p_drop, c=128):
+        super().__init__()
+        self.d_pair, self.c, self.p_drop = d_pair, c, p_drop
+        self.layernorm1 = K.LayerNorm(d_pair)
+        self.left_right_projection = Linear(d_pair, 2 * c)
+        self.left_right_gate = Linear(d_pair, 2 * c, initializer="zeros", bias_init=1.0)
+        self.output_gate = Linear(d_pair, d_pair, initializer="zeros", bias_init=1.0)
+        self.layernorm2 = K.LayerNorm(c)
+        self.output_projection = Linear(d_pair, d_pair, initializer="zeros", use_bias=False)
+        self.output_bias = nn.Parameter(torch.zeros((d_pair,)))
+        self._glu_cache = None
+
+    # -- helpers ------------------------------------------------------------
+    def _glu_weights(self):
+        """Projection and gate weights interleaved row-wise so that the GEMM epilogue sees (value, gate) pairs."""
+        wp, wg = self.left_right_projection.weight, self.left_right_gate.weight
+        key = (wp._version, wg._version, wp.data_ptr(), wg.data_ptr(), wp.dtype)
+        if self._glu_cache is None or self._glu_cache[0] != key:
+            w = torch.stack([wp.detach(), wg.detach()], dim=1).reshape(-1, wp.shape[1]).contiguous()
+            b = torch.stack([self.left_right_projection.bias.detach(), self.left_right_gate.bias.detach()], dim=1).reshape(-1).contiguous()
+            self._glu_cache = (key, w, b)
+        return self._glu_cache[1], self._glu_cache[2]
+
+    def _contract(self, left, right):
+        """left/right: [1, A, B, c] channel-last -> ab [1, i, j, c]."""
+        c = left.shape[-1]
+        if self.outgoing:
+            lt = left[0].permute(2, 0, 1).contiguous()       # [c, i, k]
+            rt = right[0].permute(2, 0, 1).contiguous()      # [c, j, k]
+            p = K.bmm_nt(lt, rt)                             # [c, i, j]
+        else:
+            lt = left[0].permute(2, 0, 1).contiguous()       # [c, k, i]
+            rt = right[0].permute(2, 0, 1).contiguous()      # [c, k, j]
+            p = _bmm_tn(lt, rt)                              # [c, i, j]
+        return p.permute(1, 2, 0).unsqueeze(0)
+
+    def _fused_nograd(self, Z_raw, Z_mask, dropmask):
+        """Inference / checkpoint first pass: 7 kernels, no transposed copies."""
+        c = self.c
+        A, B = Z_raw.shape[1], Z_raw.shape[2]
+        Z = self.layernorm1(Z_raw)
+        z2 = Z.reshape(A * B, -1)
+        w, b = self._glu_weights()
+        lr_t = K.gemm(z2, w, bias=b, glu=True, rowscale=Z_mask.reshape(-1), trans_out=True)      # [2c, A*B]
+        left_t = lr_t[:c].reshape(c, A, B)
+        right_t = lr_t[c:].reshape(c, A, B)
+        g = K.gemm(z2, self.output_gate.weight, bias=self.output_gate.bias, act="sigmoid")
+        P = core.get_dap_size()
+        if self.outgoing:
+            if P > 1:
+                right_t = comm._gather(right_t.contiguous(), dim=1)                             # [c, N, k]
+            p = K.gemm(left_t, right_t)                                                        # [c, i, j]
+        else:
+            if P > 1:
+                left_t = comm._gather(left_t.contiguous(), dim=2)                               # [c, k, N]
+            p = K.gemm(left_t, right_t, a_mn=True, b_mn=True)                                  # [c, i, j]
+        n_i, n_j = p.shape[1], p.shape[2]
+        ab = K.layer_norm_transposed(p.reshape(c, n_i * n_j), self.layernorm2.weight, self.layernorm2.bias, self.layernorm2.eps)
+        out = K.gemm(ab, self.output_projection.weight, bias=self.output_bias, mul=g,
+                     dmask=None if dropmask is None else _mask_idx(Z_raw, dropmask), resid=Z_raw.reshape(A * B, -1))
+        return out.reshape(Z_raw.shape)
+
+    def _chunked(self, Z_raw, Z_mask):
+        """Slab-by-slab evaluation for long sequences: the gathered operand is never materialised.
+
+        Every rank in turn broadcasts its projected slab (double-buffered, asynchronous); the receiver
+        contracts it with its own operand and fills the matching block of output columns (outgoing) or
+        rows (incoming).  Same result as the dense path; cf. the reference's broadcast pipeline
+        (ops.py:414-498, 543-630), which additionally re-projects the slab for every output chunk.
+        """
+        c = self.c
+        P, rank = core.get_dap_size(), core.get_dap_rank()
+        Z = self.layernorm1(Z_raw)
+        proj = K.glu_mask(self.left_right_projection(Z), self.left_right_gate(Z), Z_mask)
+        left, right = proj[..., :c], proj[..., c:]
+        g = self.output_gate(Z, act="sigmoid")
+        del Z
+        mine = (right if self.outgoing else left)[0].permute(2, 0, 1).contiguous()       # channel-major slab
+        other = (left if self.outgoing else right)[0].permute(2, 0, 1).contiguous()
+        out = torch.empty_like(Z_raw)
+        bufs = [torch.empty_like(mine), torch.empty_like(mine)]
+        pending = None
+        for r in range(P + 1):
+            nxt = None
+            if r < P:
+                buf = mine if r == rank else bufs[r % 2]
+                nxt = (r, *broadcast_async(r, buf)) if P > 1 else (r, mine, None)
+            if pending is not None:
+                pr, slab, work = pending
+                slab = broadcast_async_opp(slab, work)
+                if self.outgoing:
+                    p = K.gemm(other, slab)                                   # [c, i, j_r]
+                    w = p.shape[2]
+                    ab = K.layer_norm(p.permute(1, 2, 0).contiguous(), self.layernorm2.weight, self.layernorm2.bias, self.layernorm2.eps)
+                    sl = (slice(None), slice(None), slice(pr * w, (pr + 1) * w))
+                else:
+                    p = K.gemm(slab, other, a_mn=True, b_mn=True)             # [c, i_r, j]
+                    w = p.shape[1]
+                    ab = K.layer_norm(p.permute(1, 2, 0).contiguous(), self.layernorm2.weight, self.layernorm2.bias, self.layernorm2.eps)
+                    sl = (slice(None), slice(pr * w, (pr + 1) * w), slice(None))
+                ab = self.output_projection(ab).unsqueeze(0)
+                out[sl] = Z_raw[sl] + g[sl] * (ab + self.output_bias)
+            pending = nxt
+        return out
+
+    def forward(self, Z_raw, Z_mask, dropmask=None):
+        training = self.training
+        if dropmask is None and training and self.p_drop > 0:
+            dropmask = F.dropout(torch.ones_like(Z_raw[:, 0:1, :, :]), p=self.p_drop, training=True)
+        if not training:
+            dropmask = None
+        if CHUNK_SIZE is not None and not torch.is_grad_enabled():
+            return self._chunked(Z_raw, Z_mask)
+        can_fuse = _fusable(Z_raw) and (Z_raw.shape[1] * Z_raw.shape[2]) % 8 == 0 and Z_raw.shape[1] % 8 == 0 and Z_raw.shape[2] % 8 == 0
+        if can_fuse:
+            return self._fused_nograd(Z_raw, Z_mask, dropmask)
+        c = self.c
+        Z = self.layernorm1(Z_raw)
+        proj = K.glu_mask(self.left_right_projection(Z), self.left_right_gate(Z), Z_mask)
+        left, right = proj[..., :c], proj[..., c:]
+        if self.outgoing:
+            right, work = gather_async(right.contiguous(), dim=1)
+            g = self.output_gate(Z, act="sigmoid")
+            right = gather_async_opp(right, work, dim=1)
+        else:
+            left, work = gather_async(left.contiguous(), dim=2)
+            g = self.output_gate(Z, act="sigmoid")
+            left = gather_async_opp(left, work, dim=2)
+        ab = self._contract(left, right)
+        ab = self.output_projection(self.layernorm2(ab.contiguous()))
+        return K.bias_ele_dropout_residual(ab, self.output_bias, g, dropmask, Z_raw, prob=0.0, training=training)
+
+    def inplace(self, Z_raw, Z_mask, dropmask=None):
+        Z_raw[0] = self.forward(Z_raw[0], Z_mask, dropmask)
+        return Z_raw
+
+
+class _BmmTN(torch.autograd.Function):
+    """out[b] = A[b]^T @ B[b] for A [b, K, M], B [b, K, N] (both contraction-strided)."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return K.gemm(a, b, a_mn=True, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, dout):
+        a, b = ctx.saved_tensors
+        dout = dout.contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = K.gemm(b, dout)                  # [K, M] = b [K, N] x dout [M, N]^T
+        if ctx.needs_input_grad[1]:
+            db = K.gemm(a, dout, b_mn=True)       # [K, N] = a [K, M] x dout [M, N]
+        return da, db
+
+
+def _bmm_tn(a, b):
+    ok = (a.is_cuda and a.dtype == torch.bfloat16 and a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0 and a.shape[-2] % 8 == 0
+          and a.shape[-1] >= 64 and b.shape[-1] >= 64)
+    if not ok:
+        return torch.matmul(a.transpose(-1, -2), b)
+    if torch.is_grad_enabled() and (a.requires_grad or b.requires_grad):
+        return _BmmTN.apply(a, b)
+    return K.gemm(a, b, a_mn=True, b_mn=True)
+
+
+class AsyncChunkTriangleMultiplicationOutgoing(_TriangleMultiplication):
+    outgoing = True
+
+
+class AsyncChunkTriangleMultiplicationIncoming(_TriangleMultiplication):
+    outgoing = False
+
+
+# ---------------------------------------------------------------------------
+# Triangle attention
+# ---------------------------------------------------------------------------
+class _TriangleAttention(nn.Module):
+    starting = True
+
+    def __init__(self, d_pair, p_drop, c=32, n_head=4):
+        super().__init__()
+        self.d_pair, self.c, self.n_head, self.p_drop = d_pair, c, n_head, p_drop
+        self.layernorm1 = K.LayerNorm(d_pair)
+        self.linear_b = Linear(d_pair, n_head, initializer="linear", use_bias=False)
+        self.attention = SelfAttention(qkv_dim=d_pair, c=c, n_head=n_head, out_dim=d_pair, gating=True, last_bias_fuse=True)
+        self.out_bias = nn.Parameter(torch.zeros((d_pair,)))
+
+    def forward(self, Z_raw, Z_mask, dropmask=None):
+        training = self.training
+        if self.starting:
+            Zin, mask = Z_raw, Z_mask
+            if dropmask is None and training and self.p_drop > 0:
+                dropmask = F.dropout(torch.ones_like(Z_raw[:, 0:1, :, :]), p=self.p_drop, training=True)
+        else:
+            Zin, mask = Z_raw.transpose(-2, -3).contiguous(), Z_mask.transpose(-1, -2).contiguous()
+            if dropmask is None and training and self.p_drop > 0:
+                dropmask = F.dropout(torch.ones_like(Z_raw[:, :, 0:1, :]), p=self.p_drop, training=True)
+        if not training:
+            dropmask = None
+        Z = self.layernorm1(Zin)
+        b = self.linear_b(Z)
+        b, work = gather_async(b, dim=1)
+        tail = None
+        if self.starting and _fusable(Z_raw):
+            tail = (self.out_bias, None if dropmask is None else _mask_idx(Z_raw, dropmask), Z_raw)
+        out, done = self.attention(Z, mask, (b, work), tail=tail)
+        if done:
+            return out
+        if not self.starting:
+            out = out.transpose(-2, -3)
+        return K.bias_dropout_add(out.contiguous(), self.out_bias, dropmask, Z_raw, prob=0.0, training=training)
+
+    def inplace(self, Z_raw, Z_mask, dropmask=None):
+        Z_raw[0] = self.forward(Z_raw[0], Z_mask, dropmask)
+        return Z_raw
+
+
+class ChunkTriangleAttentionStartingNode(_TriangleAttention):
+    starting = True
+
+
+class ChunkTriangleAttentionEndingNode(_TriangleAttention):
+    starting = False
+
+
+# ---------------------------------------------------------------------------
+# MSA attentions
+# ---------------------------------------------------------------------------
+class ChunkMSARowAttentionWithPairBias(nn.Module):
+    def __init__(self, d_node, d_pair, c=32, n_head=8, p_drop=0.15):
+        super().__init__()
+        self.d_node, self.d_pair, self.c, self.n_head, self.p_drop = d_node, d_pair, c, n_head, p_drop
+        self.layernormM = K.LayerNorm(d_node)
+        self.layernormZ = K.LayerNorm(d_pair)
+        self.linear_b_weights = nn.Parameter(torch.nn.init.normal_(torch.zeros([n_head, d_pair]), std=1.0 / math.sqrt(d_pair)))
+        self.attention = SelfAttention(qkv_dim=d_node, c=c, n_head=n_head, out_dim=d_node, gating=True, last_bias_fuse=True)
+        self.out_bias = nn.Parameter(torch.zeros((d_node,)))
+
+    def forward(self, M_raw, Z, M_mask, dropmask=None):
+        training = self.training
+        if dropmask is None and training and self.p_drop > 0:
+            dropmask = F.dropout(torch.ones_like(M_raw[:, 0:1, :, :]), p=self.p_drop, training=True)
+        if not training:
+            dropmask = None
+        M = self.layernormM(M_raw)
+        Zn = self.layernormZ(Z)
+        b = K.linear(Zn, self.linear_b_weights)
+        b, work = gather_async(b, dim=1)
+        tail = None
+        if _fusable(M_raw):
+            tail = (self.out_bias, None if dropmask is None else _mask_idx(M_raw, dropmask), M_raw)
+        out, done = self.attention(M, M_mask, (b, work), tail=tail)
+        if done:
+            return out
+        return K.bias_dropout_add(out, self.out_bias, dropmask, M_raw, prob=0.0, training=training)
+
+    def inplace(self, M_raw, Z, M_mask, dropmask=None):
+        M_raw[0] = self.forward(M_raw[0], Z, M_mask, dropmask)
+        return M_raw
+
+
+class ChunkMSAColumnGlobalAttention(nn.Module):
+    def __init__(self, d_node, c=8, n_head=8):
+        super().__init__()
+        self.d_node, self.c, self.n_head = d_node, c, n_head
+        self.layernormM = K.LayerNorm(d_node)
+        self.global_attention = GlobalAttention(qkv_dim=d_node, c=c, n_head=n_head, out_dim=d_node)
+
+    def forward(self, M_raw, M_mask):
+        M = self.layernormM(M_raw.transpose(-2, -3).contiguous())
+        M = self.global_attention(M, M_mask.transpose(-1, -2).contiguous())
+        return M_raw + M.transpose(-2, -3)
+
+    def inplace(self, M_raw, M_mask):
+        M_raw[0] = self.forward(M_raw[0], M_mask)
+        return M_raw

@@ -1,0 +1,68 @@
+"""Pair half of the Evoformer block (names as in fastfold/model/fastnn/triangle.py)."""
+import torch.nn as nn
+
+from ...parallel.comm import scatter, row_to_col, col_to_row
+from .ops import (AsyncChunkTriangleMultiplicationOutgoing, AsyncChunkTriangleMultiplicationIncoming,
+                  ChunkTriangleAttentionStartingNode, ChunkTriangleAttentionEndingNode, ChunkTransition)
+
+
+def pad_amount(n, P):
+    """Rows/columns to add so that ``n`` divides by the DAP size (0 when it already does).
+
+    The reference always pads by at least one (fastfold/model/fastnn/evoformer.py:42-43) because it
+    strips the padding with ``[:-pad]``; padded positions are masked, so the outputs are the same.
+    """
+    return (-n) % P
+
+
+class TriangleMultiplicationOutgoing(AsyncChunkTriangleMultiplicationOutgoing):
+    pass
+
+
+class TriangleMultiplicationIncoming(AsyncChunkTriangleMultiplicationIncoming):
+    pass
+
+
+class TriangleAttentionStartingNode(ChunkTriangleAttentionStartingNode):
+    pass
+
+
+class TriangleAttentionEndingNode(ChunkTriangleAttentionEndingNode):
+    pass
+
+
+class PairCore(nn.Module):
+    """tri-mul out -> a2a -> tri-mul in -> a2a -> tri-att start -> a2a -> tri-att end -> transition -> a2a."""
+
+    def __init__(self, d_pair, p_drop=0.25):
+        super().__init__()
+        self.d_pair = d_pair
+        self.n_head = 4
+        self.hidden_c = int(d_pair / self.n_head)
+        self.TriangleMultiplicationOutgoing = AsyncChunkTriangleMultiplicationOutgoing(d_pair, p_drop=p_drop, c=d_pair)
+        self.TriangleMultiplicationIncoming = AsyncChunkTriangleMultiplicationIncoming(d_pair, p_drop=p_drop, c=d_pair)
+        self.TriangleAttentionStartingNode = ChunkTriangleAttentionStartingNode(d_pair, p_drop=p_drop, c=self.hidden_c, n_head=self.n_head)
+        self.TriangleAttentionEndingNode = ChunkTriangleAttentionEndingNode(d_pair, p_drop=p_drop, c=self.hidden_c, n_head=self.n_head)
+        self.PairTransition = ChunkTransition(d=d_pair)
+
+    def forward(self, pair, pair_mask, _drop=None):
+        d = _drop or {}
+        pair_mask_row = scatter(pair_mask, dim=1)
+        pair_mask_col = scatter(pair_mask, dim=2)
+        pair = self.TriangleMultiplicationOutgoing(pair, pair_mask_row, d.get("tri_mul_out"))
+        pair = row_to_col(pair)
+        dm = d.get("tri_mul_in")
+        if dm is not None:
+            dm = scatter(dm, dim=2)
+        pair = self.TriangleMultiplicationIncoming(pair, pair_mask_col, dm)
+        pair = col_to_row(pair)
+        pair = self.TriangleAttentionStartingNode(pair, pair_mask_row, d.get("tri_att_start"))
+        pair = row_to_col(pair)
+        pair = self.TriangleAttentionEndingNode(pair, pair_mask_col, d.get("tri_att_end"))
+        pair = self.PairTransition(pair)
+        pair = col_to_row(pair)
+        return pair
+
+    def inplace(self, pair, pair_mask, _drop=None):
+        pair[0] = self.forward(pair[0], pair_mask, _drop)
+        return pair

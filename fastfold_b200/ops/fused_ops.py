@@ -1,0 +1,240 @@
+"""Fused elementwise regions (csrc/elementwise.cu) with hand-written gradients.
+
+API of the reference's ``fastfold.model.fastnn.kernel`` JIT ops
+(kernel/jit/fused_ops.py:5-22) is kept:
+
+* ``bias_sigmod_ele(y, bias, z)``            -> ``sigmoid(y + bias) * z``
+* ``bias_dropout_add(x, bias, dropmask, residual, prob, training)``
+* ``bias_ele_dropout_residual(ab, b, g, dropout_mask, Z_raw, prob, training)``
+
+In the reference ``dropmask`` is a tensor of ones shaped like one slice of the
+activation and the op applies ``F.dropout`` to it.  Here the same call works
+(ones in, dropout applied inside), and in addition a ready-made mask (values in
+``{0, 1/(1-p)}``) can be passed with ``prob=0``: the trunk draws all masks of a
+step up front so that activation-checkpoint recomputation and every DAP rank
+see identical masks without touching RNG state.
+"""
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+
+def _bf16_cuda(*ts):
+    return all(t is None or (t.is_cuda and t.dtype == torch.bfloat16) for t in ts)
+
+
+def _rows_c(t):
+    C = t.shape[-1]
+    return t.numel() // C, C
+
+
+def _mask_index(x, mask):
+    """Maps a broadcastable mask ([.., 1, N, C] or [.., N, 1, C]) to (mask2d, div, mod) over flattened rows."""
+    C = x.shape[-1]
+    a, b = x.shape[-3], x.shape[-2]
+    assert mask.shape[-1] == C
+    lead = 1
+    for s in mask.shape[:-3]:
+        lead *= s
+    assert lead == 1, "dropout mask must not have leading batch extent"
+    ma, mb = (mask.shape[-3] if mask.dim() >= 3 else 1), mask.shape[-2]
+    if ma == 1 and mb == b:          # shared along rows: mask index = row % b
+        return mask.reshape(b, C), 1, b
+    if ma == a and mb == 1:          # shared along columns: mask index = row // b
+        return mask.reshape(a, C), b, a
+    if ma == 1 and mb == 1:
+        return mask.reshape(1, C), 1, 1
+    raise ValueError("unsupported dropout mask shape %s for activation %s" % (tuple(mask.shape), tuple(x.shape)))
+
+
+# ---------------------------------------------------------------------------
+class _BiasSigmoidMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, bias, o):
+        lib = _lib.get()
+        gc, oc, bc = g.contiguous(), o.contiguous(), bias.contiguous()
+        rows, C = _rows_c(gc)
+        y = torch.empty_like(gc)
+        _lib.check(lib.ffb_bias_sigmoid_mul_fwd(_lib.ptr(gc), _lib.ptr(bc), _lib.ptr(oc), _lib.ptr(y), rows, C, _lib.stream_ptr()),
+                   "bias_sigmoid_mul_fwd")
+        ctx.save_for_backward(gc, bc, oc)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.get()
+        gc, bc, oc = ctx.saved_tensors
+        rows, C = _rows_c(gc)
+        dg = torch.empty_like(gc)
+        do = torch.empty_like(oc)
+        dyc = dy.contiguous()
+        _lib.check(lib.ffb_bias_sigmoid_mul_bwd(_lib.ptr(dyc), _lib.ptr(gc), _lib.ptr(bc), _lib.ptr(oc), _lib.ptr(dg), _lib.ptr(do),
+                                                rows, C, _lib.stream_ptr()), "bias_sigmoid_mul_bwd")
+        db = colsum(dg.reshape(rows, C)).to(bc.dtype) if ctx.needs_input_grad[1] else None
+        return dg, db, do
+
+
+def bias_sigmod_ele(y, bias, z):
+    if _bf16_cuda(y, bias, z) and y.shape == z.shape and y.shape[-1] % 8 == 0 and bias.numel() == y.shape[-1]:
+        return _BiasSigmoidMul.apply(y, bias, z)
+    return torch.sigmoid(y + bias) * z
+
+
+# ---------------------------------------------------------------------------
+class _BiasDropoutAdd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias, m2, div, mod, resid):
+        lib = _lib.get()
+        xc, rc = x.contiguous(), resid.contiguous()
+        rows, C = _rows_c(xc)
+        y = torch.empty_like(xc)
+        _lib.check(lib.ffb_bias_dropout_add_fwd(_lib.ptr(xc), _lib.ptr(bias), _lib.ptr(m2), _lib.ptr(rc), _lib.ptr(y), rows, C,
+                                                div, mod, _lib.stream_ptr()), "bias_dropout_add_fwd")
+        ctx.save_for_backward(m2)
+        ctx.dm = (div, mod)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.get()
+        (m2,) = ctx.saved_tensors
+        dyc = dy.contiguous()
+        rows, C = _rows_c(dyc)
+        if m2 is not None:
+            dx = torch.empty_like(dyc)
+            _lib.check(lib.ffb_mask_mul(_lib.ptr(dyc), _lib.ptr(m2), _lib.ptr(dx), rows, C, ctx.dm[0], ctx.dm[1], _lib.stream_ptr()),
+                       "mask_mul")
+        else:
+            dx = dyc
+        db = colsum(dx.reshape(rows, C)).to(dyc.dtype) if (ctx.has_bias and ctx.needs_input_grad[1]) else None
+        return dx, db, None, None, None, dyc
+
+
+def bias_dropout_add(x, bias, dropmask, residual, prob, training=True):
+    if dropmask is not None and training and prob > 0.0:
+        dropmask = F.dropout(dropmask, p=prob, training=True)
+    elif dropmask is not None and not training:
+        dropmask = None
+    if _bf16_cuda(x, bias, dropmask, residual) and x.shape == residual.shape and x.shape[-1] % 8 == 0 and x.dim() >= 3:
+        if dropmask is not None:
+            m2, div, mod = _mask_index(x, dropmask)
+            m2 = m2.contiguous()
+        else:
+            m2, div, mod = None, 1, 1
+        return _BiasDropoutAdd.apply(x, bias.contiguous() if bias is not None else None, m2, div, mod, residual)
+    out = x if bias is None else x + bias
+    if dropmask is not None:
+        out = out * dropmask
+    return residual + out
+
+
+# ---------------------------------------------------------------------------
+class _BiasEleDropoutRes(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ab, b, g, m2, div, mod, resid):
+        lib = _lib.get()
+        abc, gc, rc, bc = ab.contiguous(), g.contiguous(), resid.contiguous(), b.contiguous()
+        rows, C = _rows_c(abc)
+        y = torch.empty_like(abc)
+        _lib.check(lib.ffb_bias_ele_dropout_res_fwd(_lib.ptr(abc), _lib.ptr(bc), _lib.ptr(gc), _lib.ptr(m2), _lib.ptr(rc), _lib.ptr(y),
+                                                    rows, C, div, mod, _lib.stream_ptr()), "bias_ele_dropout_res_fwd")
+        ctx.save_for_backward(abc, bc, gc, m2)
+        ctx.dm = (div, mod)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.get()
+        abc, bc, gc, m2 = ctx.saved_tensors
+        dyc = dy.contiguous()
+        rows, C = _rows_c(dyc)
+        dab = torch.empty_like(abc)
+        dg = torch.empty_like(gc)
+        _lib.check(lib.ffb_bias_ele_dropout_res_bwd(_lib.ptr(dyc), _lib.ptr(abc), _lib.ptr(bc), _lib.ptr(gc), _lib.ptr(m2),
+                                                    _lib.ptr(dab), _lib.ptr(dg), rows, C, ctx.dm[0], ctx.dm[1], _lib.stream_ptr()),
+                   "bias_ele_dropout_res_bwd")
+        db = colsum(dab.reshape(rows, C)).to(bc.dtype) if ctx.needs_input_grad[1] else None
+        return dab, db, dg, None, None, None, dyc
+
+
+def bias_ele_dropout_residual(ab, b, g, dropout_mask, Z_raw, prob, training=True):
+    if dropout_mask is not None and training and prob > 0.0:
+        dropout_mask = F.dropout(dropout_mask, p=prob, training=True)
+    elif dropout_mask is not None and not training:
+        dropout_mask = None
+    if _bf16_cuda(ab, b, g, dropout_mask, Z_raw) and ab.shape == Z_raw.shape == g.shape and ab.shape[-1] % 8 == 0 and ab.dim() >= 3:
+        if dropout_mask is not None:
+            m2, div, mod = _mask_index(ab, dropout_mask)
+            m2 = m2.contiguous()
+        else:
+            m2, div, mod = None, 1, 1
+        return _BiasEleDropoutRes.apply(ab, b, g, m2, div, mod, Z_raw)
+    out = g * (ab + b)
+    if dropout_mask is not None:
+        out = out * dropout_mask
+    return Z_raw + out
+
+
+# ---------------------------------------------------------------------------
+class _GluMask(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, p, q, rowmask):
+        lib = _lib.get()
+        pc, qc = p.contiguous(), q.contiguous()
+        rows, C = _rows_c(pc)
+        y = torch.empty_like(pc)
+        rm = rowmask.to(torch.bfloat16).contiguous() if rowmask is not None else None
+        _lib.check(lib.ffb_glu_mask_fwd(_lib.ptr(pc), _lib.ptr(qc), _lib.ptr(rm), _lib.ptr(y), rows, C, _lib.stream_ptr()), "glu_mask_fwd")
+        ctx.save_for_backward(pc, qc, rm)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.get()
+        pc, qc, rm = ctx.saved_tensors
+        rows, C = _rows_c(pc)
+        dyc = dy.contiguous()
+        dp = torch.empty_like(pc)
+        dq = torch.empty_like(qc)
+        _lib.check(lib.ffb_glu_mask_bwd(_lib.ptr(dyc), _lib.ptr(pc), _lib.ptr(qc), _lib.ptr(rm), _lib.ptr(dp), _lib.ptr(dq), rows, C,
+                                        _lib.stream_ptr()), "glu_mask_bwd")
+        return dp, dq, None
+
+
+def glu_mask(p, q, rowmask=None):
+    """``rowmask[..., None] * p * sigmoid(q)``; ``rowmask`` has the shape of ``p`` without its last dim."""
+    if _bf16_cuda(p, q) and p.shape == q.shape and p.shape[-1] % 8 == 0 and (rowmask is None or rowmask.numel() == p.numel() // p.shape[-1]):
+        return _GluMask.apply(p, q, rowmask)
+    out = p * torch.sigmoid(q)
+    if rowmask is not None:
+        out = out * rowmask.unsqueeze(-1).to(out.dtype)
+    return out
+
+
+# ---------------------------------------------------------------------------
+def act_backward(dy2, y2, act):
+    """dy * act'(pre-activation), expressed through the saved activation output."""
+    mode = 1 if act == "relu" else 2
+    if _bf16_cuda(dy2, y2) and dy2.shape[-1] % 8 == 0:
+        lib = _lib.get()
+        dyc, yc = dy2.contiguous(), y2.contiguous()
+        rows, C = _rows_c(dyc)
+        dx = torch.empty_like(dyc)
+        _lib.check(lib.ffb_act_bwd(_lib.ptr(dyc), _lib.ptr(yc), _lib.ptr(dx), rows, C, mode, _lib.stream_ptr()), "act_bwd")
+        return dx
+    if mode == 1:
+        return dy2 * (y2 > 0).to(dy2.dtype)
+    return dy2 * y2 * (1 - y2)
+
+
+def colsum(x2):
+    """fp32 column sums of a 2-D tensor."""
+    if x2.is_cuda and x2.dtype == torch.bfloat16 and x2.shape[-1] % 2 == 0:
+        lib = _lib.get()
+        xc = x2.contiguous()
+        out = torch.zeros(xc.shape[-1], device=xc.device, dtype=torch.float32)
+        _lib.check(lib.ffb_colsum(_lib.ptr(xc), _lib.ptr(out), xc.shape[0], xc.shape[1], _lib.stream_ptr()), "colsum")
+        return out
+    return x2.float().sum(dim=0)

@@ -1,0 +1,260 @@
+"""bf16 matrix products on the tcgen05 GEMM kernel (csrc/gemm_tcgen05.cu).
+
+``gemm`` is the raw launcher (operands in either storage order, fused
+epilogue); ``linear`` and ``bmm`` are autograd-aware wrappers whose backward
+also runs on the same kernel (data gradient with the weight read MN-major,
+weight gradient with both operands MN-major and split-K fp32 accumulation).
+On CPU tensors everything is computed with PyTorch in fp32, which is also the
+oracle the GPU tests compare against.
+
+Stands in for the cuBLAS calls behind ``torch.matmul`` / ``nn.Linear`` /
+``torch.einsum`` in the reference (fastfold/model/fastnn/ops.py:79-82,
+143-160, 275-324, 393-404).
+"""
+import torch
+
+from . import _lib
+from ._lib import ACT_NONE, ACT_RELU, ACT_SIGMOID, OUT_BF16, OUT_F32, OUT_F32_ATOMIC
+
+_ACT = {None: ACT_NONE, "none": ACT_NONE, "relu": ACT_RELU, "sigmoid": ACT_SIGMOID}
+
+
+def _as3d(t):
+    return t if t.dim() == 3 else t.unsqueeze(0)
+
+
+def gemm_ref(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=False, rowscale=None, mul=None,
+             dmask=None, resid=None, trans_out=False, out_dtype=None):
+    """fp32 PyTorch statement of what the kernel computes (same argument meaning as ``gemm``)."""
+    A = a.float().transpose(-1, -2) if a_mn else a.float()
+    B = b.float().transpose(-1, -2) if b_mn else b.float()
+    v = alpha * torch.matmul(A, B.transpose(-1, -2))
+    if bias is not None:
+        v = v + bias.float()
+    if _ACT[act] == ACT_RELU:
+        v = torch.relu(v)
+    elif _ACT[act] == ACT_SIGMOID:
+        v = torch.sigmoid(v)
+    if glu:
+        v = v[..., 0::2] * torch.sigmoid(v[..., 1::2])
+    if mul is not None:
+        v = v * mul.float()
+    if rowscale is not None:
+        v = v * rowscale.float().unsqueeze(-1)
+    if dmask is not None:
+        m, div, mod = dmask
+        rows = torch.arange(v.shape[-2], device=v.device)
+        v = v * m.float()[(rows // div) % mod]
+    if resid is not None:
+        v = v + resid.float()
+    if trans_out:
+        v = v.transpose(-1, -2)
+    return v.to(out_dtype or a.dtype)
+
+
+def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=False, rowscale=None, mul=None,
+         dmask=None, resid=None, trans_out=False, out=None, out_dtype=None, splits=1, accumulate=False, bn=0):
+    """``C = epilogue(alpha * A @ B^T)`` with A ``[.., M, K]`` and B ``[.., N, K]``.
+
+    ``a_mn`` / ``b_mn``: the operand is stored with the contraction index
+    strided, i.e. A is given as ``[.., K, M]`` / B as ``[.., K, N]``.
+    Epilogue order: ``+bias -> act -> glu -> *mul -> *rowscale -> *dmask -> +resid``.
+    ``dmask=(mask[mod, N], div, mod)`` picks mask row ``(m // div) % mod``.
+    ``accumulate=True`` adds into an fp32 ``out`` with atomics (allows ``splits > 1``).
+    A leading batch dimension may be present on either operand (a 2-D operand is
+    shared by all batches).
+    """
+    if not a.is_cuda:
+        r = gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, alpha=alpha, bias=bias, act=act, glu=glu, rowscale=rowscale, mul=mul,
+                     dmask=dmask, resid=resid, trans_out=trans_out, out_dtype=out_dtype)
+        if out is not None:
+            if accumulate:
+                out.add_(r.to(out.dtype))
+            else:
+                out.copy_(r)
+            return out
+        return r
+    lib = _lib.get()
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "tcgen05 GEMM takes bf16 operands"
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    if b.stride(-1) != 1:
+        b = b.contiguous()
+    batch = 1
+    if a.dim() == 3:
+        batch = a.shape[0]
+    if b.dim() == 3:
+        batch = max(batch, b.shape[0])
+    a3, b3 = _as3d(a), _as3d(b)
+    if a_mn:
+        K, M = a3.shape[1], a3.shape[2]
+    else:
+        M, K = a3.shape[1], a3.shape[2]
+    if b_mn:
+        Kb, N = b3.shape[1], b3.shape[2]
+    else:
+        N, Kb = b3.shape[1], b3.shape[2]
+    assert K == Kb, "contraction extents differ: %d vs %d" % (K, Kb)
+    n_out = N // 2 if glu else N
+    batched = a.dim() == 3 or b.dim() == 3
+    oshape = (n_out, M) if trans_out else (M, n_out)
+    if batched:
+        oshape = (batch,) + oshape
+    if out is None:
+        odt = out_dtype or torch.bfloat16
+        out = torch.empty(oshape, device=a.device, dtype=odt)
+    else:
+        assert tuple(out.shape) == tuple(oshape), "out has shape %s, expected %s" % (tuple(out.shape), oshape)
+        assert out.stride(-1) == 1
+    if out.dtype == torch.bfloat16:
+        assert not accumulate
+        mode = OUT_BF16
+    else:
+        assert out.dtype == torch.float32
+        mode = OUT_F32_ATOMIC if accumulate else OUT_F32
+    g = _lib.GemmArgs()
+    g.M, g.N, g.K = M, N, K
+    g.splits = splits if accumulate else 1
+    g.out_mode = mode
+    g.trans_out = 1 if trans_out else 0
+    g.act = _ACT[act]
+    g.glu = 1 if glu else 0
+    g.alpha = float(alpha)
+    g.C = out.data_ptr()
+    g.ldc = out.stride(-2)
+    g.c_bstride = out.stride(0) if batched else 0
+    keep = [a, b, out]
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+        assert bias.numel() == N
+        g.bias = bias.data_ptr()
+        keep.append(bias)
+    if rowscale is not None:
+        rowscale = rowscale.to(torch.float32).contiguous()
+        g.rowscale = rowscale.data_ptr()
+        g.rs_bstride = M if (batched and rowscale.dim() == 2) else 0
+        keep.append(rowscale)
+    if mul is not None:
+        assert mul.dtype == torch.bfloat16 and mul.stride(-1) == 1
+        g.mul = mul.data_ptr()
+        g.ldmul = mul.stride(-2)
+        g.mul_bstride = mul.stride(0) if (batched and mul.dim() == 3) else 0
+    if dmask is not None:
+        m, div, mod = dmask
+        assert m.dtype == torch.bfloat16 and m.stride(-1) == 1 and m.shape[-1] == n_out
+        g.dmask = m.data_ptr()
+        g.lddm = m.stride(-2) if m.dim() >= 2 else 0
+        g.dm_div, g.dm_mod = int(div), int(mod)
+    else:
+        g.dm_div, g.dm_mod = 1, 1
+    if resid is not None:
+        assert resid.dtype == torch.bfloat16 and resid.stride(-1) == 1
+        g.resid = resid.data_ptr()
+        g.ldres = resid.stride(-2)
+        g.res_bstride = resid.stride(0) if (batched and resid.dim() == 3) else 0
+    rc = lib.ffb_gemm_bf16(_lib.ptr(a3), _lib.ptr(b3), 1 if a_mn else 0, 1 if b_mn else 0, a3.stride(1), b3.stride(1),
+                           a3.stride(0) if a.dim() == 3 else 0, b3.stride(0) if b.dim() == 3 else 0, batch, bn, g,
+                           _lib.stream_ptr())
+    _lib.check(rc, "ffb_gemm_bf16(M=%d,N=%d,K=%d,batch=%d)" % (M, N, K, batch))
+    return out
+
+
+def _wgrad_splits(tokens, n_out_tiles):
+    """Split-K factor so that a weight-gradient GEMM (few output tiles, long contraction) fills the 148 SMs."""
+    kb = (tokens + 63) // 64
+    want = max(1, (2 * 148) // max(1, n_out_tiles))
+    return max(1, min(kb, want))
+
+
+class _Linear(torch.autograd.Function):
+    """y = act(x @ W^T + b) on [tokens, c_in]; all three GEMMs on the tcgen05 kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, act):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w, bias=bias, act=act)
+        ctx.act = act
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(x2, w, y if act else None)
+        ctx.xshape = x.shape
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import fused_ops
+        x2, w, y = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(-1) != 1 or dy2.stride(0) != dy2.shape[1]:
+            dy2 = dy2.contiguous()
+        if ctx.act:
+            dy2 = fused_ops.act_backward(dy2, y, ctx.act)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            dw = weight_grad(dy2, x2, w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = fused_ops.colsum(dy2).to(w.dtype)
+        return dx, dw, db, None
+
+
+def weight_grad(dy2, x2, dtype=torch.bfloat16):
+    """dW[c_out, c_in] = dy^T @ x, contraction over tokens, fp32 split-K accumulation."""
+    n_out, n_in = dy2.shape[1], x2.shape[1]
+    if not dy2.is_cuda:
+        return (dy2.float().t() @ x2.float()).to(dtype)
+    if n_out < 64 or n_in < 64 or n_out % 8 or n_in % 8:
+        # narrow projections (pair-bias heads, 32-wide outer-product factors): the MN-major tile is 64 wide
+        return torch.matmul(dy2.t(), x2).to(dtype)
+    acc = torch.zeros(n_out, n_in, device=dy2.device, dtype=torch.float32)
+    tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
+    gemm(dy2, x2, a_mn=True, b_mn=True, out=acc, accumulate=True, splits=_wgrad_splits(dy2.shape[0], tiles))
+    return acc.to(dtype)
+
+
+def linear(x, w, bias=None, act=None):
+    """``act(x @ w.T + bias)`` over the last dimension of ``x``."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or x.shape[-1] % 8 or w.shape[0] % 8:
+        y = torch.nn.functional.linear(x, w, bias)
+        if _ACT[act] == ACT_RELU:
+            y = torch.relu(y)
+        elif _ACT[act] == ACT_SIGMOID:
+            y = torch.sigmoid(y)
+        return y
+    if torch.is_grad_enabled() and (x.requires_grad or w.requires_grad or (bias is not None and bias.requires_grad)):
+        return _Linear.apply(x, w, bias, act)
+    x2 = x.reshape(-1, x.shape[-1])
+    return gemm(x2, w, bias=bias, act=act).reshape(*x.shape[:-1], w.shape[0])
+
+
+class _BmmNT(torch.autograd.Function):
+    """out[b] = A[b] @ B[b]^T for [b, M, K] x [b, N, K]; gradients on the same kernel."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return gemm(a, b)
+
+    @staticmethod
+    def backward(ctx, dout):
+        a, b = ctx.saved_tensors
+        dout = dout.contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = gemm(dout, b, b_mn=True)          # [b, M, N] x [b, N, K] (contraction N, B stored [N, K])
+        if ctx.needs_input_grad[1]:
+            db = gemm(dout, a, a_mn=True, b_mn=True)  # dout^T [N, M] x a [M, K], contraction over M
+        return da, db
+
+
+def bmm_nt(a, b):
+    """Batched ``a @ b.transpose(-1, -2)`` (both operands contraction-contiguous)."""
+    ok = (a.is_cuda and a.dtype == torch.bfloat16 and a.shape[-1] % 8 == 0 and a.shape[-2] % 8 == 0
+          and b.shape[-2] % 8 == 0 and a.shape[-2] >= 64 and b.shape[-2] >= 64)
+    if not ok:
+        return torch.matmul(a, b.transpose(-1, -2))
+    a = a.contiguous()
+    b = b.contiguous()
+    if torch.is_grad_enabled() and (a.requires_grad or b.requires_grad):
+        return _BmmNT.apply(a, b)
+    return gemm(a, b)

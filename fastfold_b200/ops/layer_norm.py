@@ -1,0 +1,101 @@
+"""LayerNorm over the last dimension (csrc/layernorm.cu), forward and backward.
+
+``LayerNorm`` keeps the constructor and parameter names of the reference's
+``fastfold.model.fastnn.kernel.LayerNorm`` (kernel/layer_norm.py:19-60):
+``LayerNorm(normalized_shape, eps=1e-5)`` with ``weight`` / ``bias``.  The
+reference splits inputs whose third-last dimension exceeds 4000 into chunks
+(:37-50) to bound its workspace; this kernel needs no workspace proportional
+to the input, so no chunking is necessary.
+"""
+import numbers
+
+import torch
+from torch import nn
+
+from . import _lib
+
+
+def layer_norm_ref(x, weight, bias, eps):
+    return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), weight.float(), bias.float(), eps).to(x.dtype)
+
+
+def _native_ok(x, weight):
+    return x.is_cuda and x.dtype in _lib._DT and weight.dtype == x.dtype
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        lib = _lib.get()
+        xc = x.contiguous()
+        C = xc.shape[-1]
+        rows = xc.numel() // C
+        y = torch.empty_like(xc)
+        need_stats = torch.is_grad_enabled() or ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        mean = torch.empty(rows, device=x.device, dtype=torch.float32)
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        w = weight.contiguous()
+        b = bias.contiguous()
+        _lib.check(lib.ffb_layernorm_fwd(_lib.ptr(xc), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), _lib.ptr(mean), _lib.ptr(rstd),
+                                         rows, C, float(eps), _lib.dtype_code(x.dtype), _lib.stream_ptr()), "layernorm_fwd")
+        ctx.save_for_backward(xc, w, mean, rstd)
+        del need_stats
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.get()
+        xc, w, mean, rstd = ctx.saved_tensors
+        dyc = dy.contiguous()
+        C = xc.shape[-1]
+        rows = xc.numel() // C
+        dx = torch.empty_like(xc)
+        nblocks = int(min(296, max(1, (rows + 3) // 4)))
+        part = torch.empty(nblocks * 2 * C, device=xc.device, dtype=torch.float32)
+        dg = torch.empty_like(w)
+        db = torch.empty_like(w)
+        _lib.check(lib.ffb_layernorm_bwd(_lib.ptr(dyc), _lib.ptr(xc), _lib.ptr(w), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(dx),
+                                         _lib.ptr(part), nblocks, _lib.ptr(dg), _lib.ptr(db), rows, C,
+                                         _lib.dtype_code(xc.dtype), _lib.stream_ptr()), "layernorm_bwd")
+        return dx, dg, db, None
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    if not _native_ok(x, weight):
+        return torch.nn.functional.layer_norm(x, (x.shape[-1],), weight.to(x.dtype), bias.to(x.dtype), eps)
+    return _LayerNormFn.apply(x, weight, bias, eps)
+
+
+def layer_norm_transposed(x_cm, weight, bias, eps=1e-5):
+    """LayerNorm over dim 0 of ``x_cm [C, rows]`` returning ``[rows, C]`` (no-grad fast path)."""
+    C, rows = x_cm.shape
+    if not (x_cm.is_cuda and x_cm.dtype == torch.bfloat16 and C <= 256):
+        return layer_norm(x_cm.t().contiguous(), weight, bias, eps)
+    lib = _lib.get()
+    x_cm = x_cm.contiguous()
+    y = torch.empty(rows, C, device=x_cm.device, dtype=x_cm.dtype)
+    _lib.check(lib.ffb_layernorm_fwd_transposed(_lib.ptr(x_cm), _lib.ptr(weight.contiguous()), _lib.ptr(bias.contiguous()),
+                                                _lib.ptr(y), None, None, rows, C, float(eps), _lib.stream_ptr()),
+               "layernorm_fwd_transposed")
+    return y
+
+
+class LayerNorm(nn.Module):
+    def __init__(self, normalized_shape, eps=1e-5):
+        super().__init__()
+        if isinstance(normalized_shape, numbers.Integral):
+            normalized_shape = (normalized_shape,)
+        self.normalized_shape = torch.Size(normalized_shape)
+        assert len(self.normalized_shape) == 1, "LayerNorm normalises the last dimension"
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(*normalized_shape))
+        self.bias = nn.Parameter(torch.zeros(*normalized_shape))
+
+    def forward(self, x):
+        return layer_norm(x, self.weight, self.bias, self.eps)
+
+    def extra_repr(self):
+        return "%s, eps=%g" % (tuple(self.normalized_shape), self.eps)
+
+
+FusedLayerNorm = LayerNorm

@@ -1,0 +1,168 @@
+"""Training-step engine: flat parameter storage, fused Adam, gradient reduction, CUDA-graph replay.
+
+What the reference obtains from ColossalAI's engine (``engine.zero_grad /
+backward / step`` with ``HybridAdam`` and DDP, train.py:206-237) is provided
+here in one object:
+
+* all parameters live in one flat bf16 buffer (their ``.data`` are views), all
+  gradients in one flat bf16 buffer (``.grad`` are views), with fp32 master
+  weights and Adam moments beside them; one kernel (csrc/elementwise.cu
+  ``adam_k``) updates everything;
+* gradients are summed over the whole world (DAP x DP): parameters used on
+  DAP-sharded activations need the sum over the DAP group, parameters used in
+  replicated computation hold identical gradients on every DAP rank and are
+  averaged; the data-parallel mean is folded into the same scale;
+* the whole step - forward, loss, recomputation, backward, reduction and
+  update - can be captured into one CUDA graph and replayed, which removes the
+  host launch cost of the thousands of small kernels of an Evoformer step.
+"""
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..parallel import core
+
+
+class FlatAdamTrainer:
+    def __init__(self, model, loss_fn, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, use_graph=True,
+                 replicated_param_filter=None, grad_reducer=None):
+        """``loss_fn(model, *inputs) -> scalar loss``.  ``replicated_param_filter(name) -> bool`` marks parameters
+        whose computation is replicated (not sharded) over the DAP group."""
+        self.model = model
+        self.loss_fn = loss_fn
+        self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
+        self.step_count = 0
+        self.use_graph = use_graph and next(model.parameters()).is_cuda
+        self.graph = None
+        self.static_inputs = None
+        self.static_loss = None
+        self.grad_reducer = grad_reducer
+        self.launches_per_step = None
+        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        self.names = [n for n, _ in params]
+        self.params = [p for _, p in params]
+        dev = self.params[0].device
+        self.dtype = self.params[0].dtype
+        total = sum(p.numel() for p in self.params)
+        self.numel = total
+        self.flat_w = torch.empty(total, device=dev, dtype=self.dtype)
+        self.flat_g = torch.zeros(total, device=dev, dtype=self.dtype)
+        self.master = torch.empty(total, device=dev, dtype=torch.float32)
+        self.exp_avg = torch.zeros(total, device=dev, dtype=torch.float32)
+        self.exp_avg_sq = torch.zeros(total, device=dev, dtype=torch.float32)
+        self.hp = torch.zeros(4, device=dev, dtype=torch.float32)
+        self.hp_host = torch.zeros(4, dtype=torch.float32)
+        if dev.type == "cuda":
+            self.hp_host = self.hp_host.pin_memory()
+        # per-element gradient scale is uniform except for DAP-replicated parameters
+        P, D = core.get_dap_size(), core.get_dp_size()
+        self.rep_scale = None
+        off = 0
+        scales = []
+        for n, p in params:
+            k = p.numel()
+            self.flat_w[off:off + k].copy_(p.data.reshape(-1))
+            p.data = self.flat_w[off:off + k].view(p.shape)
+            p.grad = self.flat_g[off:off + k].view(p.shape)
+            rep = bool(replicated_param_filter(n)) if replicated_param_filter else False
+            scales.append((off, k, rep))
+            off += k
+        self.master.copy_(self.flat_w.float())
+        self.base_gscale = 1.0 / D
+        if P > 1 and any(r for _, _, r in scales):
+            self.rep_scale = torch.ones(total, device=dev, dtype=self.dtype)
+            for o, k, r in scales:
+                if r:
+                    self.rep_scale[o:o + k] = 1.0 / P
+
+    # ------------------------------------------------------------------
+    def _set_hp(self):
+        t = self.step_count + 1
+        self.hp_host[0] = self.lr
+        self.hp_host[1] = 1.0 - self.betas[0] ** t
+        self.hp_host[2] = 1.0 - self.betas[1] ** t
+        self.hp_host[3] = self.base_gscale
+        self.hp.copy_(self.hp_host, non_blocking=True)
+
+    def _reduce_grads(self):
+        if core.get_world_size() > 1:
+            if self.grad_reducer is not None:
+                self.grad_reducer(self.flat_g)
+            else:
+                dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM)
+        if self.rep_scale is not None:
+            self.flat_g.mul_(self.rep_scale)
+
+    def _adam(self):
+        if self.flat_w.is_cuda and self.dtype == torch.bfloat16:
+            lib = _lib.get()
+            _lib.check(lib.ffb_adam(_lib.ptr(self.master), _lib.ptr(self.exp_avg), _lib.ptr(self.exp_avg_sq), _lib.ptr(self.flat_g),
+                                    _lib.ptr(self.flat_w), self.numel, _lib.ptr(self.hp), self.betas[0], self.betas[1], self.eps,
+                                    self.wd, _lib.stream_ptr()), "adam")
+            return
+        lr, bc1, bc2, gs = [float(x) for x in self.hp.tolist()]
+        g = self.flat_g.float() * gs
+        if self.wd:
+            g = g + self.wd * self.master
+        self.exp_avg.mul_(self.betas[0]).add_(g, alpha=1 - self.betas[0])
+        self.exp_avg_sq.mul_(self.betas[1]).addcmul_(g, g, value=1 - self.betas[1])
+        self.master.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + self.eps, value=-lr)
+        self.flat_w.copy_(self.master.to(self.dtype))
+
+    def _body(self, inputs):
+        self.flat_g.zero_()
+        loss = self.loss_fn(self.model, *inputs)
+        loss.backward()
+        self._reduce_grads()
+        self._adam()
+        return loss.detach()
+
+    # ------------------------------------------------------------------
+    def step(self, *inputs):
+        """One optimisation step; returns the (device) loss tensor of this step."""
+        self._set_hp()
+        if not self.use_graph:
+            n0 = _lib.LAUNCHES[0]
+            loss = self._body(inputs)
+            self.launches_per_step = _lib.LAUNCHES[0] - n0
+            self.step_count += 1
+            return loss
+        if self.graph is None:
+            self.static_inputs = [x.clone() if isinstance(x, torch.Tensor) else x for x in inputs]
+            # warm-up on a side stream (allocator, cuBLAS handles, NCCL channels), then capture
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(2):
+                    self._body(self.static_inputs)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            # the two warm-up passes are real optimisation steps and are counted as such
+            self.graph = torch.cuda.CUDAGraph()
+            n0 = _lib.LAUNCHES[0]
+            with torch.cuda.graph(self.graph):
+                self.static_loss = self._body(self.static_inputs)
+            self.launches_per_step = _lib.LAUNCHES[0] - n0
+            self.step_count += 2
+            self._set_hp()
+        else:
+            for dst, src in zip(self.static_inputs, inputs):
+                if isinstance(dst, torch.Tensor) and dst.data_ptr() != src.data_ptr():
+                    dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        self.step_count += 1
+        return self.static_loss
+
+    def state_dict(self):
+        return {"step": self.step_count, "master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
+                "lr": self.lr, "names": self.names}
+
+    def load_state_dict(self, sd):
+        self.step_count = sd["step"]
+        self.master.copy_(sd["master"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.lr = sd.get("lr", self.lr)
+        self.flat_w.copy_(self.master.to(self.dtype))

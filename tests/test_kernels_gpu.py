@@ -1,0 +1,114 @@
+"""LayerNorm / softmax / fused elementwise kernels against fp32 PyTorch references.
+
+Shapes and tolerances follow the reference's kernel tests
+(tests/test_fastnn/test_layernorm.py:20, tests/test_fastnn/test_softmax.py:14).
+"""
+import pytest
+import torch
+
+from fastfold_b200 import ops
+from fastfold_b200.ops.layer_norm import layer_norm_transposed
+from fastfold_b200.ops.softmax import softmax_ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+LN_TOL = {torch.float32: 1e-4, torch.float16: 1e-1, torch.bfloat16: 1e-1}
+SM_TOL = {torch.float32: 1e-6, torch.float16: 2e-4, torch.bfloat16: 1e-3}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("cols", [64, 128, 129, 256, 384, 1024, 2048])
+def test_layernorm(dtype, cols, device_status):
+    torch.manual_seed(0)
+    x = torch.randn(3, 64, cols, device=DEV, dtype=dtype, requires_grad=True)
+    ln = ops.LayerNorm(cols).to(DEV, dtype)
+    with torch.no_grad():
+        ln.weight.copy_(torch.randn(cols) * 0.5 + 1)
+        ln.bias.copy_(torch.randn(cols) * 0.1)
+    y = ln(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    wr = ln.weight.detach().float().requires_grad_(True)
+    br = ln.bias.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.layer_norm(xr, (cols,), wr, br, ln.eps)
+    yr.backward(g.float())
+    tol = LN_TOL[dtype]
+    assert (y.float() - yr).abs().max() < tol
+    assert (x.grad.float() - xr.grad).abs().max() < tol
+    rel = lambda a, b: ((a.float() - b).abs().max() / (b.abs().max() + 1e-6)).item()
+    assert rel(ln.weight.grad, wr.grad) < (1e-4 if dtype == torch.float32 else 2e-2)
+    assert rel(ln.bias.grad, br.grad) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def test_layernorm_transposed(device_status):
+    x = torch.randn(128, 1000, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(128, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(128, device=DEV, dtype=torch.bfloat16)
+    y = layer_norm_transposed(x, w, b, 1e-5)
+    yr = torch.nn.functional.layer_norm(x.float().t(), (128,), w.float(), b.float(), 1e-5)
+    assert (y.float() - yr).abs().max() < 1e-1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("seq", [31, 32, 128, 129, 256, 259, 512, 700, 1024, 1500])
+def test_softmax(dtype, seq, device_status):
+    torch.manual_seed(1)
+    x = torch.randn(2, 3, 4, seq, seq, device=DEV, dtype=dtype, requires_grad=True)
+    mask = (torch.rand(2, 3, seq, device=DEV) > 0.2).to(dtype)
+    mask[..., 0] = 1
+    bias = torch.randn(2, 1, 4, seq, seq, device=DEV, dtype=dtype, requires_grad=True)
+    y = ops.fused_softmax(x, mask, bias)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    br = bias.detach().float().requires_grad_(True)
+    yr = softmax_ref(xr, mask.float(), br)
+    yr.backward(g.float())
+    tol = SM_TOL[dtype]
+    assert (y.float() - yr).abs().max() < tol
+    assert (x.grad.float() - xr.grad).abs().max() < tol * 10
+    assert (bias.grad.float() - br.grad).abs().max() < tol * 30
+
+
+def test_softmax_global_attention_shape(device_status):
+    # 4-D logits [b1, b2, H, S]: the mask row must follow b2, not row // (H * S)
+    x = torch.randn(1, 7, 8, 300, device=DEV, dtype=torch.bfloat16)
+    mask = (torch.rand(1, 7, 300, device=DEV) > 0.3).to(torch.bfloat16)
+    mask[..., 0] = 1
+    y = ops.fused_softmax(x, mask)
+    assert (y.float() - softmax_ref(x.float(), mask.float())).abs().max() < 1e-3
+
+
+def _check_grads(fn_fast, fn_ref, tensors, tol=3e-2):
+    fast = [t.detach().clone().requires_grad_(t.is_floating_point() and t.requires_grad) for t in tensors]
+    ref = [t.detach().float().requires_grad_(t.requires_grad) for t in tensors]
+    yf, yr = fn_fast(*fast), fn_ref(*ref)
+    g = torch.randn_like(yr)
+    yf.backward(g.to(yf.dtype))
+    yr.backward(g)
+    assert (yf.float() - yr).abs().max() < tol * (1 + yr.abs().max())
+    for a, b in zip(fast, ref):
+        if b.grad is not None:
+            assert a.grad is not None
+            assert (a.grad.float() - b.grad).abs().max() < tol * (1 + b.grad.abs().max()), (a.shape,)
+
+
+def test_fused_elementwise(device_status):
+    torch.manual_seed(2)
+    bf = torch.bfloat16
+    R = lambda *s: torch.randn(*s, device=DEV, dtype=bf).requires_grad_(True)
+    y, bias, z = R(1, 16, 24, 256), R(256), R(1, 16, 24, 256)
+    _check_grads(ops.bias_sigmod_ele, lambda y, b, z: torch.sigmoid(y + b) * z, [y, bias, z])
+    mask_row = ((torch.rand(1, 1, 24, 256, device=DEV) > 0.15).to(bf) / 0.85)
+    mask_col = ((torch.rand(1, 16, 1, 256, device=DEV) > 0.25).to(bf) / 0.75)
+    x, res = R(1, 16, 24, 256), R(1, 16, 24, 256)
+    for mk in (mask_row, mask_col, None):
+        _check_grads(lambda x, b, r: ops.bias_dropout_add(x, b, mk, r, 0.0, True),
+                     lambda x, b, r: r + (x + b) * (1 if mk is None else mk.float()), [x, bias, res])
+    ab, g = R(1, 16, 24, 256), R(1, 16, 24, 256)
+    _check_grads(lambda ab, b, g, r: ops.bias_ele_dropout_residual(ab, b, g, mask_row, r, 0.0, True),
+                 lambda ab, b, g, r: r + mask_row.float() * (g * (ab + b)), [ab, bias, g, res])
+    p, q = R(1, 16, 24, 256), R(1, 16, 24, 256)
+    rm = (torch.rand(1, 16, 24, device=DEV) > 0.2).to(bf)
+    _check_grads(lambda p, q: ops.glu_mask(p, q, rm), lambda p, q: rm.float().unsqueeze(-1) * p * torch.sigmoid(q), [p, q])
