@@ -281,6 +281,10 @@ def run_reference(args):
 
     def step(m, z, mm, pm, tm, tz, ts):
         opt.zero_grad(set_to_none=True)
+        # the reference's checkpoint_blocks uses reentrant torch.utils.checkpoint, which only back-propagates
+        # when an input requires grad (in its train.py the inputs come from the embedders and do)
+        m = m.detach().requires_grad_(True)
+        z = z.detach().requires_grad_(True)
         out = model(m, z, mm, pm, None)
         loss = mse_loss(out, tm, tz, ts)
         loss.backward()

@@ -11,18 +11,25 @@
 // the per-channel triangle-multiplication contraction and the outer-product-
 // mean contraction without a transposed copy of any operand.
 //
-// One CTA computes one 128 x BN output tile:
+// Persistent kernel, one CTA per SM, each CTA walks 128 x BN output tiles
+// (tile = blockIdx.x, + gridDim.x, ...; N-tiles fastest so that CTAs running at
+// the same time share A rows in L2):
 //   warp 0      : TMA producer (one elected lane) - fills a STAGES-deep ring of
-//                 128B-swizzled operand tiles, completion via mbarrier tx-count
+//                 128B-swizzled operand tiles, completion via mbarrier tx-count;
+//                 the ring keeps running across tile boundaries
 //   warp 1      : MMA issuer (one lane) - tcgen05.mma, 128 x BN x 16 per
-//                 instruction, tcgen05.commit releases ring slots and finally
-//                 signals "accumulator ready"
-//   warps 2..5  : epilogue - tcgen05.ld of their 32-lane TMEM quadrant, fused
-//                 bias / activation / gating / mask / dropout / residual, bf16
-//                 or fp32 stores (optionally transposed, optionally atomic for
-//                 split-K)
-// Several CTAs are resident per SM (smem permitting) so that one tile's
-// epilogue overlaps the next tile's loads and MMAs.
+//                 instruction, into one of TWO accumulator stages in TMEM;
+//                 tcgen05.commit releases ring slots and signals "stage full"
+//   warps 2..5  : epilogue - tcgen05.ld of their 32-lane TMEM quadrant, a
+//                 32 x 64 transpose through shared memory so that 8 lanes
+//                 cover 128 contiguous bytes of an output row, then fused
+//                 bias / activation / GLU / gate / mask / dropout / residual
+//                 and 16-byte stores (or vector fp32 reductions for split-K);
+//                 transposed (channel-major) stores use the thread-per-row
+//                 mapping directly.  The epilogue of tile t overlaps the MMAs
+//                 of tile t+1 through the second accumulator stage.
+// Every wait is bounded; a wait that runs out records a code in the status
+// word and the CTA unwinds (TMEM is always released).
 //
 // Covers what the reference leaves to cuBLAS through torch.matmul / einsum /
 // nn.Linear (fastfold/model/fastnn/ops.py:79-82,143-160,275-324,393-404) plus
@@ -38,15 +45,18 @@ __device__ int g_status[8];
 constexpr int BM = 128;
 constexpr int BK = 64;           // 64 bf16 = 128 B = one swizzle row
 constexpr int GEMM_THREADS = 192;
+constexpr int STG_LD = 65;       // staging row pitch in floats (odd -> conflict-free column access)
 
 template <int BN>
 struct GemmCfg {
-  static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 128) ? 3 : 4);
+  static constexpr int STAGES = (BN >= 256) ? 3 : 4;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int EPI_WARP_BYTES = 16384;              // per epilogue warp: 2 store tiles + mul tile + residual tile (4 KB each)
+  static constexpr int STG_BYTES = 4 * EPI_WARP_BYTES;      // (the fp32 transpose buffer of the generic path aliases it)
+  static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator stages
 };
 
 __device__ __forceinline__ void load8(const bf16* p, bool vec, int n, float* o) {
@@ -65,41 +75,129 @@ __device__ __forceinline__ void load8(const bf16* p, bool vec, int n, float* o) 
   }
 }
 
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+struct TileCoord {
+  int m0, n0, batch, split;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_n, int tiles_m, int splits) {
+  TileCoord t;
+  const int tn = tile % tiles_n;
+  int r = tile / tiles_n;
+  const int tm = r % tiles_m;
+  r /= tiles_m;
+  t.split = r % splits;
+  t.batch = r / splits;
+  t.m0 = tm * BM;
+  t.n0 = tn;   // scaled by BN by the caller
+  return t;
+}
+
+// Epilogue arithmetic on 8 consecutive output columns of one row (everything after bias/activation/glu).
+__device__ __forceinline__ void epi_tail8(float* v, const GemmArgs& g, int batch, int row, int oc, int nvalid, float rs) {
+  float t[8];
+  if (g.mul) {
+    const bf16* p = reinterpret_cast<const bf16*>(g.mul) + (long long)batch * g.mul_bstride + (long long)row * g.ldmul + oc;
+    load8(p, nvalid == 8 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0), nvalid, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= t[j];
+  }
+  if (g.rowscale) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= rs;
+  }
+  if (g.dmask) {
+    const bf16* p = reinterpret_cast<const bf16*>(g.dmask) + (long long)((row / g.dm_div) % g.dm_mod) * g.lddm + oc;
+    load8(p, nvalid == 8 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0), nvalid, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= t[j];
+  }
+  if (g.resid) {
+    const bf16* p = reinterpret_cast<const bf16*>(g.resid) + (long long)batch * g.res_bstride + (long long)row * g.ldres + oc;
+    load8(p, nvalid == 8 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0), nvalid, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] += t[j];
+  }
+}
+
+__device__ __forceinline__ void epi_store8(const float* v, const GemmArgs& g, int batch, int row, int oc, int nvalid) {
+  if (g.out_mode == OUT_BF16) {
+    bf16* dst = reinterpret_cast<bf16*>(g.C) + (long long)batch * g.c_bstride + (long long)row * g.ldc + oc;
+    if (nvalid == 8 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      uint4 u;
+      bf162* h = reinterpret_cast<bf162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      *reinterpret_cast<uint4*>(dst) = u;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nvalid) dst[j] = __float2bfloat16(v[j]);
+    }
+  } else {
+    float* dst = reinterpret_cast<float*>(g.C) + (long long)batch * g.c_bstride + (long long)row * g.ldc + oc;
+    const bool vec = nvalid == 8 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+    if (g.out_mode == OUT_F32_ATOMIC) {
+      if (vec) {
+        red_add_v4(dst, v[0], v[1], v[2], v[3]);
+        red_add_v4(dst + 4, v[4], v[5], v[6], v[7]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < nvalid) atomicAdd(dst + j, v[j]);
+      }
+    } else if (vec) {
+      *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nvalid) dst[j] = v[j];
+    }
+  }
+}
+
+// Persistent kernel: every CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                                 const __grid_constant__ CUtensorMap tmB,
-                                                                 const GemmArgs g) {
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                    const __grid_constant__ CUtensorMap tmB,
+                                                                    const __grid_constant__ CUtensorMap tmC,
+                                                                    const __grid_constant__ CUtensorMap tmMul,
+                                                                    const __grid_constant__ CUtensorMap tmRes,
+                                                                    const GemmArgs g, int num_tiles, int tiles_m, int tiles_n, int tma_epi) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024 B alignment for the 128B swizzle atoms
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * Cfg::STAGE_BYTES);
-  const uint32_t bar_full = smem_u32(bars);                 // STAGES barriers
-  const uint32_t bar_empty = bar_full + 8 * STAGES;         // STAGES barriers
-  const uint32_t bar_acc = bar_empty + 8 * STAGES;          // 1 barrier
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  float* staging = reinterpret_cast<float*>(smem_al + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * Cfg::STAGE_BYTES + Cfg::STG_BYTES);
+  const uint32_t bar_full = smem_u32(bars);                 // STAGES: operand tile landed
+  const uint32_t bar_empty = bar_full + 8 * STAGES;         // STAGES: operand tile consumed
+  const uint32_t bar_accf = bar_empty + 8 * STAGES;         // 2: accumulator stage complete
+  const uint32_t bar_acce = bar_accf + 16;                  // 2: accumulator stage drained
+  const uint32_t bar_epld = bar_acce + 16;                  // 4: per-epilogue-warp TMA loads of mul / residual tiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * BM;
-  const int batch = blockIdx.z / g.splits;
-  const int split = blockIdx.z - batch * g.splits;
   const int kb_total = (g.K + BK - 1) / BK;
-  const int kb_begin = split * g.kblocks_per_split;
-  int kb_end = kb_begin + g.kblocks_per_split;
-  if (kb_end > kb_total) kb_end = kb_total;
-  const int nkb = kb_end - kb_begin;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_acc, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_accf + 8 * s, 1);
+      mbar_init(bar_acce + 8 * s, 4);     // one arrival per epilogue warp
+    }
+    for (int s = 0; s < 4; ++s) mbar_init(bar_epld + 8 * s, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmA);
@@ -113,51 +211,70 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
-  if (nkb > 0) {
-    if (warp == 0) {
-      if (lane == 0) {
-        // ---------------- TMA producer ----------------
-        for (int i = 0; i < nkb; ++i) {
-          const int s = i % STAGES;
-          const int it = i / STAGES;
-          if (it > 0) {
-            if (!mbar_wait(bar_empty + 8 * s, (it - 1) & 1)) {
-              report(ST_TIMEOUT_MMA, i);
-              *abort_flag = 1;
-              break;
-            }
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      uint32_t it = 0;   // k-block counter over all tiles of this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, tiles_n, tiles_m, g.splits);
+        const int n0 = tc.n0 * BN;
+        const int kb_begin = tc.split * g.kblocks_per_split;
+        int kb_end = kb_begin + g.kblocks_per_split;
+        if (kb_end > kb_total) kb_end = kb_total;
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1)) {
+            report(ST_TIMEOUT_MMA, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
           }
-          const int k0 = (kb_begin + i) * BK;
+          const int k0 = kb * BK;
           const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
           mbar_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * (BK * 128), &tmA, bar_full + 8 * s, m0 + c * 64, k0, batch * g.a_zmul);
+            for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * (BK * 128), &tmA, bar_full + 8 * s, tc.m0 + c * 64, k0, tc.batch * g.a_zmul);
           } else {
-            tma_load_3d(sa, &tmA, bar_full + 8 * s, k0, m0, batch * g.a_zmul);
+            tma_load_3d(sa, &tmA, bar_full + 8 * s, k0, tc.m0, tc.batch * g.a_zmul);
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * (BK * 128), &tmB, bar_full + 8 * s, n0 + c * 64, k0, batch * g.b_zmul);
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * (BK * 128), &tmB, bar_full + 8 * s, n0 + c * 64, k0, tc.batch * g.b_zmul);
           } else {
-            tma_load_3d(sb, &tmB, bar_full + 8 * s, k0, n0, batch * g.b_zmul);
+            tma_load_3d(sb, &tmB, bar_full + 8 * s, k0, n0, tc.batch * g.b_zmul);
           }
         }
       }
-      __syncwarp();
-    } else if (warp == 1) {
-      if (lane == 0) {
-        // ---------------- MMA issuer ----------------
-        constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
-        bool ok = true;
-        for (int i = 0; i < nkb && ok; ++i) {
-          const int s = i % STAGES;
-          const int it = i / STAGES;
-          if (!mbar_wait(bar_full + 8 * s, it & 1)) {
-            report(ST_TIMEOUT_TMA, i);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0, lt = 0;   // k-block counter, local tile counter
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+        const TileCoord tc = tile_coord(tile, tiles_n, tiles_m, g.splits);
+        const int kb_begin = tc.split * g.kblocks_per_split;
+        int kb_end = kb_begin + g.kblocks_per_split;
+        if (kb_end > kb_total) kb_end = kb_total;
+        const uint32_t as = lt & 1;
+        if (!mbar_wait(bar_acce + 8 * as, ((lt >> 1) & 1) ^ 1)) {
+          report(ST_TIMEOUT_EPI, 1);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_acc = tmem_base + as * BN;
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(bar_full + 8 * s, (it / STAGES) & 1)) {
+            report(ST_TIMEOUT_TMA, kb);
             *abort_flag = 1;
             ok = false;
             break;
@@ -169,145 +286,296 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t ad = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t bd = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16(tmem_acc, ad, bd, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_acc, ad, bd, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
           }
           umma_commit(bar_empty + 8 * s);   // slot reusable once these MMAs retire
         }
-        if (ok) umma_commit(bar_acc);       // accumulator complete
+        if (ok) umma_commit(bar_accf + 8 * as);   // accumulator stage complete
       }
-      __syncwarp();
-    } else {
-      // ---------------- epilogue (warps 2..5) ----------------
-      const int quad = warp & 3;            // TMEM lane quadrant this warp may read
-      const int row = m0 + quad * 32 + lane;
-      bool ok = mbar_wait(bar_acc, 0);
-      if (!ok && lane == 0) {
-        if (*abort_flag == 0) report(ST_TIMEOUT_EPI, 0);
-      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    float* stg = staging + (warp - 2) * (Cfg::EPI_WARP_BYTES / 4);
+    const uint32_t epi_smem = smem_u32(stg);              // 16 KB, 1024-aligned: [out0][out1][mul][res]
+    const uint32_t my_ldbar = bar_epld + 8 * (warp - 2);
+    uint32_t ld_phase = 0, out_buf = 0;
+    const int Nout = g.glu ? (g.N >> 1) : g.N;
+    uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+      const TileCoord tc = tile_coord(tile, tiles_n, tiles_m, g.splits);
+      const int n0 = tc.n0 * BN;
+      const uint32_t as = lt & 1;
+      bool ok = mbar_wait(bar_accf + 8 * as, (lt >> 1) & 1);
+      if (!ok && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_EPI, 0);
       ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
-        tc_fence_after();
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + as * BN;
+      if (tma_epi) {
+        // TMA path (bf16 row-major output): thread = row; mul / residual tiles arrive by TMA, the result tile leaves
+        // by TMA, so every global access is a full-line bulk transfer and the warp only touches shared memory
+        const int row0 = tc.m0 + quad * 32;
+        const int row = row0 + lane;
+        const float rs = (g.rowscale && row < g.M) ? g.rowscale[(long long)tc.batch * g.rs_bstride + row] : 1.f;
+        const bf16* dm_row = (g.dmask && row < g.M) ? reinterpret_cast<const bf16*>(g.dmask) + (long long)((row / g.dm_div) % g.dm_mod) * g.lddm : nullptr;
+        const bool has_ld = (g.mul != nullptr) || (g.resid != nullptr);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = n0 + c * 64;
+          if (col0 >= g.N || row0 >= g.M) break;           // warp-uniform
+          if (has_ld && lane == 0) {
+            mbar_expect_tx(my_ldbar, (g.mul ? 4096u : 0u) + (g.resid ? 4096u : 0u));
+            if (g.mul) tma_load_3d(epi_smem + 8192, &tmMul, my_ldbar, col0, row0, tc.batch);
+            if (g.resid) tma_load_3d(epi_smem + 12288, &tmRes, my_ldbar, col0, row0, tc.batch);
+          }
+          float v[64];
+          tmem_ld_32x32(taddr + c * 64, v);
+          tmem_ld_32x32(taddr + c * 64 + 32, v + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            float bv[8];
+            if (g.bias) {
+              const bf16* bp = reinterpret_cast<const bf16*>(g.bias) + col0 + u * 8;
+              load8(bp, (g.N - col0 - u * 8) >= 8 && ((reinterpret_cast<uintptr_t>(bp) & 15) == 0), g.N - col0 - u * 8, bv);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) bv[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float t = v[u * 8 + j] * g.alpha + bv[j];
+              if (g.act == ACT_RELU) t = fmaxf(t, 0.f);
+              else if (g.act == ACT_SIGMOID) t = sigmoidf_(t);
+              v[u * 8 + j] = t;
+            }
+          }
+          if (has_ld) {
+            bool w = mbar_wait(my_ldbar, ld_phase);
+            ld_phase ^= 1;
+            if (!w && lane == 0) report(ST_TIMEOUT_TMA, 40);
+            // (on a timeout the tile is still written from whatever landed; the status word carries the failure)
+          }
+          const uint8_t* stg8 = reinterpret_cast<const uint8_t*>(stg);
+          if (g.mul) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              float t[8];
+              load8(reinterpret_cast<const bf16*>(stg8 + 8192 + lane * 128 + ((u ^ (lane & 7)) << 4)), true, 8, t);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[u * 8 + j] *= t[j];
+            }
+          }
+          if (g.rowscale) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] *= rs;
+          }
+          if (dm_row) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int oc = col0 + u * 8;
+              if (oc < g.N) {
+                float t[8];
+                const int nvalid = (g.N - oc) < 8 ? (g.N - oc) : 8;
+                load8(dm_row + oc, nvalid == 8 && ((reinterpret_cast<uintptr_t>(dm_row + oc) & 15) == 0), nvalid, t);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[u * 8 + j] *= t[j];
+              }
+            }
+          }
+          if (g.resid) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              float t[8];
+              load8(reinterpret_cast<const bf16*>(stg8 + 12288 + lane * 128 + ((u ^ (lane & 7)) << 4)), true, 8, t);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[u * 8 + j] += t[j];
+            }
+          }
+          // the store tile written two chunks ago must have been read out by its bulk store
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+          uint8_t* obuf = reinterpret_cast<uint8_t*>(stg) + out_buf * 4096;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            uint4 pk;
+            bf162* hp = reinterpret_cast<bf162*>(&pk);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) hp[j] = __floats2bfloat162_rn(v[u * 8 + 2 * j], v[u * 8 + 2 * j + 1]);
+            *reinterpret_cast<uint4*>(obuf + lane * 128 + ((u ^ (lane & 7)) << 4)) = pk;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&tmC),
+                         "r"(epi_smem + out_buf * 4096), "r"(col0), "r"(row0), "r"(tc.batch)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          out_buf ^= 1;
+        }
+      } else if (g.trans_out) {
+        // direct path: thread = row, so a warp writes 32 consecutive rows of one output column
+        const int row = tc.m0 + quad * 32 + lane;
         const bool row_ok = row < g.M;
-        const int Nout = g.glu ? (g.N >> 1) : g.N;
-        float rs = 1.f;
-        if (g.rowscale && row_ok) rs = g.rowscale[(long long)batch * g.rs_bstride + row];
-        const bf16* dm_row = nullptr;
-        if (g.dmask && row_ok) dm_row = reinterpret_cast<const bf16*>(g.dmask) + (long long)((row / g.dm_div) % g.dm_mod) * g.lddm;
-        const bf16* mul_row = (g.mul && row_ok) ? reinterpret_cast<const bf16*>(g.mul) + (long long)batch * g.mul_bstride + (long long)row * g.ldmul : nullptr;
-        const bf16* res_row = (g.resid && row_ok) ? reinterpret_cast<const bf16*>(g.resid) + (long long)batch * g.res_bstride + (long long)row * g.ldres : nullptr;
+        const float rs = (g.rowscale && row_ok) ? g.rowscale[(long long)tc.batch * g.rs_bstride + row] : 1.f;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           float v[32];
-          tmem_ld_32x32(tmem_acc + ((uint32_t)(quad * 32) << 16) + c * 32, v);
+          tmem_ld_32x32(taddr + c * 32, v);
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
           if (!row_ok || col0 >= g.N) continue;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] *= g.alpha;
-          if (g.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < g.N) v[j] += __bfloat162float(reinterpret_cast<const bf16*>(g.bias)[col0 + j]);
+          for (int j = 0; j < 32; ++j) {
+            v[j] *= g.alpha;
+            if (g.bias && col0 + j < g.N) v[j] += __bfloat162float(reinterpret_cast<const bf16*>(g.bias)[col0 + j]);
+            if (g.act == ACT_RELU) v[j] = fmaxf(v[j], 0.f);
+            else if (g.act == ACT_SIGMOID) v[j] = sigmoidf_(v[j]);
           }
-          if (g.act == ACT_RELU) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-          } else if (g.act == ACT_SIGMOID) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = sigmoidf_(v[j]);
-          }
-          int ncols = 32;
-          int ocol0 = col0;
+          int ncols = 32, ocol0 = col0;
           if (g.glu) {
-            // interleaved (value, gate) column pairs -> value * sigmoid(gate)
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = v[2 * j] * sigmoidf_(v[2 * j + 1]);
             ncols = 16;
             ocol0 = col0 >> 1;
           }
-          // elementwise tail: mul, row scale, dropout mask, residual
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             if (q * 8 >= ncols) break;
             const int oc = ocol0 + q * 8;
             if (oc >= Nout) break;
             const int nvalid = (Nout - oc) < 8 ? (Nout - oc) : 8;
-            float t[8];
-            if (mul_row) {
-              const bool vec = nvalid == 8 && ((reinterpret_cast<uintptr_t>(mul_row + oc) & 15) == 0);
-              load8(mul_row + oc, vec, nvalid, t);
+            epi_tail8(v + q * 8, g, tc.batch, row, oc, nvalid, rs);
+            if (g.out_mode == OUT_BF16) {
+              bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)tc.batch * g.c_bstride;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[q * 8 + j] *= t[j];
-            }
-            if (g.rowscale) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[q * 8 + j] *= rs;
-            }
-            if (dm_row) {
-              const bool vec = nvalid == 8 && ((reinterpret_cast<uintptr_t>(dm_row + oc) & 15) == 0);
-              load8(dm_row + oc, vec, nvalid, t);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[q * 8 + j] *= t[j];
-            }
-            if (res_row) {
-              const bool vec = nvalid == 8 && ((reinterpret_cast<uintptr_t>(res_row + oc) & 15) == 0);
-              load8(res_row + oc, vec, nvalid, t);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[q * 8 + j] += t[j];
-            }
-            // ---- store ----
-            if (g.trans_out) {
-              // C^T: element (row, col) goes to C[col * ldc + row]; a warp
-              // writes 32 consecutive rows of one column -> coalesced
-              if (g.out_mode == OUT_BF16) {
-                bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)batch * g.c_bstride;
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (j < nvalid) C[(long long)(oc + j) * g.ldc + row] = __float2bfloat16(v[q * 8 + j]);
-              } else {
-                float* C = reinterpret_cast<float*>(g.C) + (long long)batch * g.c_bstride;
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (j < nvalid) {
-                    if (g.out_mode == OUT_F32_ATOMIC) atomicAdd(&C[(long long)(oc + j) * g.ldc + row], v[q * 8 + j]);
-                    else C[(long long)(oc + j) * g.ldc + row] = v[q * 8 + j];
-                  }
-              }
-            } else if (g.out_mode == OUT_BF16) {
-              bf16* dst = reinterpret_cast<bf16*>(g.C) + (long long)batch * g.c_bstride + (long long)row * g.ldc + oc;
-              if (nvalid == 8 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                uint4 u;
-                bf162* h = reinterpret_cast<bf162*>(&u);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
-                *reinterpret_cast<uint4*>(dst) = u;
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (j < nvalid) dst[j] = __float2bfloat16(v[q * 8 + j]);
-              }
+              for (int j = 0; j < 8; ++j)
+                if (j < nvalid) C[(long long)(oc + j) * g.ldc + row] = __float2bfloat16(v[q * 8 + j]);
             } else {
-              float* dst = reinterpret_cast<float*>(g.C) + (long long)batch * g.c_bstride + (long long)row * g.ldc + oc;
-              if (g.out_mode == OUT_F32_ATOMIC) {
+              float* C = reinterpret_cast<float*>(g.C) + (long long)tc.batch * g.c_bstride;
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (j < nvalid) atomicAdd(dst + j, v[q * 8 + j]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (j < nvalid) dst[j] = v[q * 8 + j];
-              }
+              for (int j = 0; j < 8; ++j)
+                if (j < nvalid) {
+                  if (g.out_mode == OUT_F32_ATOMIC) atomicAdd(&C[(long long)(oc + j) * g.ldc + row], v[q * 8 + j]);
+                  else C[(long long)(oc + j) * g.ldc + row] = v[q * 8 + j];
+                }
             }
           }
         }
+      } else {
+        // staged path: transpose 32 rows x 64 columns through shared memory so that 8 lanes cover 128 B of a row
+        const int g8 = (lane & 7) * 8;
+        const int sub = lane >> 3;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          {
+            float v[32];
+            tmem_ld_32x32(taddr + c * 64, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) stg[lane * STG_LD + j] = v[j];
+            tmem_ld_32x32(taddr + c * 64 + 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) stg[lane * STG_LD + 32 + j] = v[j];
+          }
+          __syncwarp();
+          const int col = n0 + c * 64 + g8;       // raw accumulator column of this lane's group
+          if (col < g.N) {
+            float bv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) bv[j] = 0.f;
+            if (g.bias) {
+              const bf16* bp = reinterpret_cast<const bf16*>(g.bias) + col;
+              load8(bp, (g.N - col) >= 8 && ((reinterpret_cast<uintptr_t>(bp) & 15) == 0), g.N - col, bv);
+            }
+#pragma unroll 2
+            for (int i = 0; i < 8; ++i) {
+              const int rl = 4 * i + sub;
+              const int row = tc.m0 + quad * 32 + rl;
+              if (row >= g.M) continue;
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = stg[rl * STG_LD + g8 + j] * g.alpha + bv[j];
+              if (g.act == ACT_RELU) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.f);
+              } else if (g.act == ACT_SIGMOID) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = sigmoidf_(v[j]);
+              }
+              const float rs = g.rowscale ? g.rowscale[(long long)tc.batch * g.rs_bstride + row] : 1.f;
+              if (g.glu) {
+                float w[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = v[2 * j] * sigmoidf_(v[2 * j + 1]);
+#pragma unroll
+                for (int j = 4; j < 8; ++j) w[j] = 0.f;
+                const int oc = col >> 1;
+                int nvalid = Nout - oc;
+                if (nvalid > 4) nvalid = 4;
+                // 4 outputs per lane: tail and store work on a half-filled group of 8 (never vectorised)
+                float t[8];
+                if (g.mul) {
+                  const bf16* p = reinterpret_cast<const bf16*>(g.mul) + (long long)tc.batch * g.mul_bstride + (long long)row * g.ldmul + oc;
+                  load8(p, false, nvalid, t);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) w[j] *= t[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] *= rs;
+                if (g.dmask) {
+                  const bf16* p = reinterpret_cast<const bf16*>(g.dmask) + (long long)((row / g.dm_div) % g.dm_mod) * g.lddm + oc;
+                  load8(p, false, nvalid, t);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) w[j] *= t[j];
+                }
+                if (g.resid) {
+                  const bf16* p = reinterpret_cast<const bf16*>(g.resid) + (long long)tc.batch * g.res_bstride + (long long)row * g.ldres + oc;
+                  load8(p, false, nvalid, t);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) w[j] += t[j];
+                }
+                if (g.out_mode == OUT_BF16) {
+                  bf16* dst = reinterpret_cast<bf16*>(g.C) + (long long)tc.batch * g.c_bstride + (long long)row * g.ldc + oc;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j)
+                    if (j < nvalid) dst[j] = __float2bfloat16(w[j]);
+                } else {
+                  float* dst = reinterpret_cast<float*>(g.C) + (long long)tc.batch * g.c_bstride + (long long)row * g.ldc + oc;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j)
+                    if (j < nvalid) {
+                      if (g.out_mode == OUT_F32_ATOMIC) atomicAdd(dst + j, w[j]);
+                      else dst[j] = w[j];
+                    }
+                }
+              } else {
+                const int nvalid = (g.N - col) < 8 ? (g.N - col) : 8;
+                epi_tail8(v, g, tc.batch, row, col, nvalid, rs);
+                epi_store8(v, g, tc.batch, row, col, nvalid);
+              }
+            }
+          }
+          __syncwarp();
+        }
       }
+      // all TMEM reads of this accumulator stage are complete: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acce + 8 * as);
     }
+    if (tma_epi && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, Cfg::TMEM_COLS);
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -348,7 +616,8 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, long long rows, long long
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int batch, cudaStream_t st) {
+static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap* epi, int tma_epi, const GemmArgs& g, int batch,
+                      cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
@@ -356,17 +625,27 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmAr
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return -2;
     attr_set = true;
   }
-  dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, batch * g.splits);
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(ta, tb, g);
+  const int tiles_n = (g.N + BN - 1) / BN, tiles_m = (g.M + BM - 1) / BM;
+  const long long num_tiles = (long long)tiles_n * tiles_m * batch * g.splits;
+  if (num_tiles > 0x7fffffffLL) return -5;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  const int grid = (int)(num_tiles < sm_count ? num_tiles : sm_count);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(ta, tb, epi[0], epi[1], epi[2], g, (int)num_tiles, tiles_m, tiles_n, tma_epi);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int batch, cudaStream_t st) {
+static int launch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap* epi, int tma_epi, const GemmArgs& g,
+                     int batch, cudaStream_t st) {
   switch (bn) {
-    case 64: return launch_cfg<64, A_MN, B_MN>(ta, tb, g, batch, st);
-    case 128: return launch_cfg<128, A_MN, B_MN>(ta, tb, g, batch, st);
-    case 256: return launch_cfg<256, A_MN, B_MN>(ta, tb, g, batch, st);
+    case 64: return launch_cfg<64, A_MN, B_MN>(ta, tb, epi, tma_epi, g, batch, st);
+    case 128: return launch_cfg<128, A_MN, B_MN>(ta, tb, epi, tma_epi, g, batch, st);
+    case 256: return launch_cfg<256, A_MN, B_MN>(ta, tb, epi, tma_epi, g, batch, st);
     default: return -4;
   }
 }
@@ -387,7 +666,7 @@ int ffb_gemm_bf16(const void* A, const void* B, int a_mn, int b_mn, long long ld
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -11;
   if (g.glu && (g.N & 1)) return -12;
   if (bn == 0) {
-    if (g.N > 128 && !g.glu && (long long)((g.M + 127) / 128) * ((g.N + 255) / 256) * batch >= 148) bn = 256;
+    if (g.N > 128 && (long long)((g.M + 127) / 128) * ((g.N + 255) / 256) * batch * (g.splits > 0 ? g.splits : 1) >= 2 * 148) bn = 256;
     else if (g.N > 64) bn = 128;
     else bn = 64;
   }
@@ -410,13 +689,25 @@ int ffb_gemm_bf16(const void* A, const void* B, int a_mn, int b_mn, long long ld
   if (b_mn) r = make_tmap_bf16(&tb, B, g.K, g.N, ldb, bbatch, b_bstride, 64, BK);
   else r = make_tmap_bf16(&tb, B, g.N, g.K, ldb, bbatch, b_bstride, BK, bn);
   if (r) return 2000 + r;
+  // TMA epilogue: bf16 row-major output whose rows (and those of mul / residual) are 16-byte aligned
+  CUtensorMap epi[3];
+  epi[0] = ta; epi[1] = ta; epi[2] = ta;
+  auto al16 = [](const void* p, long long ld, long long bs) { return p && !(reinterpret_cast<uintptr_t>(p) & 15) && !(ld % 8) && !(bs % 8); };
+  int tma_epi = (g.out_mode == OUT_BF16 && !g.trans_out && !g.glu && g.N >= 64 && al16(g.C, g.ldc, g.c_bstride) && (batch == 1 || g.c_bstride != 0)) ? 1 : 0;
+  if (tma_epi && g.mul && !(al16(g.mul, g.ldmul, g.mul_bstride) && (batch == 1 || g.mul_bstride != 0))) tma_epi = 0;
+  if (tma_epi && g.resid && !(al16(g.resid, g.ldres, g.res_bstride) && (batch == 1 || g.res_bstride != 0))) tma_epi = 0;
+  if (tma_epi) {
+    if (make_tmap_bf16(&epi[0], g.C, g.M, g.N, g.ldc, batch, g.c_bstride, 64, 32)) tma_epi = 0;
+    if (tma_epi && g.mul && make_tmap_bf16(&epi[1], g.mul, g.M, g.N, g.ldmul, batch, g.mul_bstride, 64, 32)) tma_epi = 0;
+    if (tma_epi && g.resid && make_tmap_bf16(&epi[2], g.resid, g.M, g.N, g.ldres, batch, g.res_bstride, 64, 32)) tma_epi = 0;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (a_mn) {
-    if (b_mn) return launch_bn<true, true>(bn, ta, tb, g, batch, st);
-    return launch_bn<true, false>(bn, ta, tb, g, batch, st);
+    if (b_mn) return launch_bn<true, true>(bn, ta, tb, epi, tma_epi, g, batch, st);
+    return launch_bn<true, false>(bn, ta, tb, epi, tma_epi, g, batch, st);
   }
-  if (b_mn) return launch_bn<false, true>(bn, ta, tb, g, batch, st);
-  return launch_bn<false, false>(bn, ta, tb, g, batch, st);
+  if (b_mn) return launch_bn<false, true>(bn, ta, tb, epi, tma_epi, g, batch, st);
+  return launch_bn<false, false>(bn, ta, tb, epi, tma_epi, g, batch, st);
 }
 
 // Reads and clears the device status word; out[0] != 0 means a kernel gave up

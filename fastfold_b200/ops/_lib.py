@@ -48,6 +48,8 @@ def _declare(lib):
     sig = {
         "ffb_gemm_bf16": [P, P, I, I, L, L, L, L, I, I, ctypes.POINTER(GemmArgs), P],
         "ffb_read_status": [ctypes.POINTER(c_int), I],
+        "ffb_attention_fwd": [P, P, P, L, L, L, L, P, P, L, P, L, L, P, I, I, I, I, I, F, P],
+        "ffb_attention_bwd": [P, P, P, L, L, L, L, P, P, L, P, P, P, P, P, I, I, I, I, I, F, P],
         "ffb_layernorm_fwd": [P, P, P, P, P, P, L, I, F, I, P],
         "ffb_layernorm_bwd": [P, P, P, P, P, P, P, I, P, P, L, I, I, P],
         "ffb_layernorm_fwd_transposed": [P, P, P, P, P, P, L, I, F, P],

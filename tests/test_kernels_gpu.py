@@ -13,7 +13,8 @@ from fastfold_b200.ops.softmax import softmax_ref
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 LN_TOL = {torch.float32: 1e-4, torch.float16: 1e-1, torch.bfloat16: 1e-1}
-SM_TOL = {torch.float32: 1e-6, torch.float16: 2e-4, torch.bfloat16: 1e-3}
+# output rounding alone is half an ulp at values in [0.5, 1): 2.4e-4 (fp16), 2e-3 (bf16)
+SM_TOL = {torch.float32: 1e-6, torch.float16: 5e-4, torch.bfloat16: 4e-3}
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
