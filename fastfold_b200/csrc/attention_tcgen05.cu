@@ -27,6 +27,7 @@
 // (fastfold/model/fastnn/ops.py:304-319) and its unused Triton forward-only
 // attention core (kernel/triton/attention_core.py:12-121).
 #include "common.cuh"
+#include "tmap.h"
 
 namespace ffb {
 
@@ -404,36 +405,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
 }
 
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn2 get_encode2() {
-  static EncodeTiledFn2 fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess || !p) return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn2>(p);
-  }
-  return fn;
-}
-
-// bf16 tensor [d2][d1][d0] (d0 contiguous) with element strides s1, s2; box b0 x b1 x 1.
-int make_tmap3(CUtensorMap* map, const void* ptr, long long d0, long long d1, long long d2, long long s1, long long s2, int b0,
-               int b1, int swizzle_bytes) {
-  EncodeTiledFn2 enc = get_encode2();
-  if (!enc) return -1;
-  cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)(d2 > 0 ? d2 : 1)};
-  cuuint64_t strides[2] = {(cuuint64_t)s1 * 2, (cuuint64_t)(d2 > 1 ? s2 : d1 * s1) * 2};
-  cuuint32_t box[3] = {(cuuint32_t)b0, (cuuint32_t)b1, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                          : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
-                                                 : (swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)r;
+static int make_tmap3(CUtensorMap* map, const void* ptr, long long d0, long long d1, long long d2, long long s1, long long s2, int b0,
+                      int b1, int swizzle_bytes) {
+  return encode_tmap3_bf16(map, ptr, d0, d1, d2, s1, s2, b0, b1, swizzle_bytes);
 }
 
 }  // namespace ffb
@@ -494,6 +468,472 @@ int ffb_attention_fwd(const void* q, const void* k, const void* v, long long q_b
   int grid = items < sm_count ? (int)items : sm_count;
   attn_fwd_kernel<32><<<grid, AT_THREADS, AttnSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, tb, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -15;
+}
+
+}  // extern "C"
+
+// ===========================================================================
+// Backward.
+//
+// One CTA owns one (batch row, head) at a time and keeps every gradient of it
+// on chip: for each key block j (outer) and query tile i (inner)
+//     S  = Q_i K_j^T,  dP = dO_i V_j^T                  (tcgen05 -> TMEM)
+//     P  = exp2(S * scale*log2e + bias*log2e - L2_i),   dS = P o (dP - D_i)
+//     dV_j += P^T dO_i,  dK_j += scale dS^T Q_i,  dQ_i += scale dS K_j
+// with dK_j / dV_j (current j) and dQ_i (all i, n_q <= 512) accumulating in
+// TMEM.  P and dS are written once into 128B-swizzled shared tiles and are
+// read by the tensor core in both orientations (K-major for dQ, MN-major for
+// dK / dV), so nothing is transposed.  Q_i, K_j, V_j, dO_i tiles are loaded
+// once by TMA (64B swizzle) and serve as K-major operands of the S / dP
+// products and as MN-major operands of the gradient products.  The unscaled
+// dS is also stored (bf16) for the pair-bias gradient, which is its sum over
+// batch rows.  D_i = rowsum(dO o O) is computed at the start of each item.
+//
+// The reference has no attention backward of its own: autograd differentiates
+// its unfused matmul / softmax chain (fastfold/model/fastnn/ops.py:304-319,
+// kernel/softmax.py:39-59).
+// ===========================================================================
+namespace ffb {
+
+struct AttnBwdArgs {
+  int B, H, n_q, n_k, n_qt, n_kb, items;
+  float scale, scale_log2e;
+  const bf16* mask;
+  long long mask_bstride;
+  const bf16* o;      // [B][n_q][H*D] (forward output, contiguous)
+  const bf16* dout;   // [B][n_q][H*D]
+  const float* lse2;  // [B][H][n_q]
+  bf16 *dq, *dk, *dv; // [B][n][H*D] each (row stride H*D)
+  long long dq_bstride, dkv_bstride;
+  bf16* ds;           // [B][H][n_q][n_k] or null
+  int has_bias;
+};
+
+struct BwdSmem {
+  static constexpr int QDO = 0;                         // 2 x (Q 8 KB + dO 8 KB)
+  static constexpr int KV = QDO + 2 * 16384;            // 2 x (K 8 KB + V 8 KB)
+  static constexpr int BIAS = KV + 2 * 16384;           // 2 x 32 KB
+  static constexpr int P = BIAS + 2 * 32768;            // 32 KB
+  static constexpr int DS = P + 32768;                  // 32 KB
+  static constexpr int DROW = DS + 32768;               // float[512] D_i, float[512] L2_i
+  static constexpr int BARS = DROW + 4096;
+  static constexpr int TOTAL = BARS + 512 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                 const __grid_constant__ CUtensorMap tmK,
+                                                                 const __grid_constant__ CUtensorMap tmV,
+                                                                 const __grid_constant__ CUtensorMap tmDO,
+                                                                 const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
+  static_assert(D == 32, "head dim 32");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  float* drow = reinterpret_cast<float*>(sm + BwdSmem::DROW);
+  float* lrow = drow + 512;
+  const uint32_t b0 = smem_u32(sm + BwdSmem::BARS);
+  const uint32_t qdo_full = b0, qdo_empty = b0 + 16, kv_full = b0 + 32, kv_empty = b0 + 48;
+  const uint32_t bias_full = b0 + 64, bias_empty = b0 + 80;
+  const uint32_t sdp_full = b0 + 96, sdp_empty = b0 + 104, pds_full = b0 + 112, pds_empty = b0 + 120;
+  const uint32_t dkv_full = b0 + 128, dkv_empty = b0 + 136, dq_full = b0 + 144, dq_empty = b0 + 152;
+  const uint32_t drow_ready = b0 + 160;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + BwdSmem::BARS + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(qdo_full + 8 * s, 1);
+      mbar_init(qdo_empty + 8 * s, 1);
+      mbar_init(kv_full + 8 * s, 1);
+      mbar_init(kv_empty + 8 * s, 1);
+      mbar_init(bias_full + 8 * s, 1);
+      mbar_init(bias_empty + 8 * s, 4);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_empty, 4);
+    mbar_init(pds_full, 4);
+    mbar_init(pds_empty, 1);
+    mbar_init(dkv_full, 1);
+    mbar_init(dkv_empty, 4);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 4);
+    mbar_init(drow_ready, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 288, TM_DQ = 320;
+
+  const int steps_per_item = a.n_kb * a.n_qt;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      uint32_t t = 0, jc = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < a.items && ok; item += gridDim.x) {
+        const int b = item / a.H, h = item % a.H;
+        for (int j = 0; j < a.n_kb && ok; ++j, ++jc) {
+          const uint32_t ks = jc & 1;
+          if (!mbar_wait(kv_empty + 8 * ks, ((jc >> 1) & 1) ^ 1)) { report(ST_TIMEOUT_MMA, 50); ok = false; break; }
+          mbar_expect_tx(kv_full + 8 * ks, 16384);
+          tma_load_3d(base + BwdSmem::KV + ks * 16384, &tmK, kv_full + 8 * ks, h * D, j * AT_BK, b);
+          tma_load_3d(base + BwdSmem::KV + ks * 16384 + 8192, &tmV, kv_full + 8 * ks, h * D, j * AT_BK, b);
+          for (int i = 0; i < a.n_qt && ok; ++i, ++t) {
+            const uint32_t s = t & 1;
+            if (!mbar_wait(qdo_empty + 8 * s, ((t >> 1) & 1) ^ 1)) { report(ST_TIMEOUT_MMA, 51); ok = false; break; }
+            mbar_expect_tx(qdo_full + 8 * s, 16384);
+            tma_load_3d(base + BwdSmem::QDO + s * 16384, &tmQ, qdo_full + 8 * s, h * D, i * AT_BQ, b);
+            tma_load_3d(base + BwdSmem::QDO + s * 16384 + 8192, &tmDO, qdo_full + 8 * s, h * D, i * AT_BQ, b);
+            if (a.has_bias) {
+              if (!mbar_wait(bias_empty + 8 * s, ((t >> 1) & 1) ^ 1)) { report(ST_TIMEOUT_EPI, 52); ok = false; break; }
+              mbar_expect_tx(bias_full + 8 * s, 32768);
+              tma_load_3d(base + BwdSmem::BIAS + s * 32768, &tmBias, bias_full + 8 * s, j * AT_BK, i * AT_BQ, h);
+              tma_load_3d(base + BwdSmem::BIAS + s * 32768 + 16384, &tmBias, bias_full + 8 * s, j * AT_BK + 64, i * AT_BQ, h);
+            }
+          }
+        }
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t id_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t id_kv = make_idesc_bf16(128, D, 1, 1);      // (P^T | dS^T) MN-major x (dO | Q) MN-major
+      constexpr uint32_t id_q = make_idesc_bf16(128, D, 0, 1);       // dS K-major x K_j MN-major
+      uint32_t t = 0, jc = 0, ic = 0;
+      bool ok = true;
+      // first half of a step: S and dP
+      auto issue_a = [&](uint32_t tt, uint32_t jcc, bool first_i) -> bool {
+        const uint32_t s = tt & 1, ks = jcc & 1;
+        if (!mbar_wait(qdo_full + 8 * s, (tt >> 1) & 1)) { report(ST_TIMEOUT_TMA, 60); return false; }
+        if (first_i && !mbar_wait(kv_full + 8 * ks, (jcc >> 1) & 1)) { report(ST_TIMEOUT_TMA, 61); return false; }
+        if (!mbar_wait(sdp_empty, (tt & 1) ^ 1)) { report(ST_TIMEOUT_EPI, 62); return false; }
+        tc_fence_after();
+        const uint32_t qa = base + BwdSmem::QDO + s * 16384, da = qa + 8192;
+        const uint32_t ka = base + BwdSmem::KV + ks * 16384, va = ka + 8192;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem + TM_S, make_desc(qa + k * 32, 16, 512, 4), make_desc(ka + k * 32, 16, 512, 4), id_s, k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem + TM_DP, make_desc(da + k * 32, 16, 512, 4), make_desc(va + k * 32, 16, 512, 4), id_s, k > 0 ? 1u : 0u);
+        umma_commit(sdp_full);
+        return true;
+      };
+      for (int item = blockIdx.x; item < a.items && ok; item += gridDim.x, ++ic) {
+        for (int j = 0; j < a.n_kb && ok; ++j, ++jc) {
+          for (int i = 0; i < a.n_qt && ok; ++i, ++t) {
+            if (t == 0) ok = issue_a(0, 0, true);
+            if (!ok) break;
+            if (!mbar_wait(pds_full, t & 1)) { report(ST_TIMEOUT_EPI, 63); ok = false; break; }
+            if (i == 0 && !mbar_wait(dkv_empty, (jc & 1) ^ 1)) { report(ST_TIMEOUT_EPI, 64); ok = false; break; }
+            if (i == 0 && j == 0 && !mbar_wait(dq_empty, (ic & 1) ^ 1)) { report(ST_TIMEOUT_EPI, 65); ok = false; break; }
+            tc_fence_after();
+            const uint32_t s = t & 1, ks = jc & 1;
+            const uint32_t qa = base + BwdSmem::QDO + s * 16384, da = qa + 8192;
+            const uint32_t ka = base + BwdSmem::KV + ks * 16384;
+            const uint32_t pa = base + BwdSmem::P, dsa = base + BwdSmem::DS;
+#pragma unroll
+            for (int k = 0; k < AT_BQ / 16; ++k) {   // contraction over the 128 queries of tile i
+              umma_bf16(tmem + TM_DV, make_desc(pa + k * 2048, 16384, 1024, 2), make_desc(da + k * 1024, 16, 512, 4), id_kv, (i > 0 || k > 0) ? 1u : 0u);
+              umma_bf16(tmem + TM_DK, make_desc(dsa + k * 2048, 16384, 1024, 2), make_desc(qa + k * 1024, 16, 512, 4), id_kv, (i > 0 || k > 0) ? 1u : 0u);
+            }
+#pragma unroll
+            for (int k = 0; k < AT_BK / 16; ++k)     // contraction over the 128 keys of block j
+              umma_bf16(tmem + TM_DQ + i * 32, make_desc(dsa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, 2),
+                        make_desc(ka + k * 1024, 16, 512, 4), id_q, (j > 0 || k > 0) ? 1u : 0u);
+            umma_commit(pds_empty);
+            umma_commit(qdo_empty + 8 * s);
+            const bool last_i = (i + 1 == a.n_qt);
+            if (last_i) {
+              umma_commit(dkv_full);
+              umma_commit(kv_empty + 8 * ks);
+              if (j + 1 == a.n_kb) umma_commit(dq_full);
+            }
+            // next step's S / dP right away (its operands are usually already in shared memory)
+            const bool more = !(last_i && j + 1 == a.n_kb) || (item + (int)gridDim.x < a.items);
+            if (more) ok = issue_a(t + 1, last_i ? jc + 1 : jc, last_i);
+          }
+        }
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else {
+    // ---------------- softmax-gradient warps (thread = row) ----------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+    const int HD = a.H * D;
+    uint32_t t = 0, jc = 0, ic = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < a.items && ok; item += gridDim.x, ++ic) {
+      const int b = item / a.H, h = item % a.H;
+      // D_i = rowsum(dO o O) and L2_i for every query row of this (b, h): 4 warps x 32 rows per sweep
+      for (int row = r; row < a.n_qt * AT_BQ; row += 128) {
+        float dsum = 0.f, l2 = 0.f;
+        if (row < a.n_q) {
+          const bf16* op = a.o + ((long long)b * a.n_q + row) * HD + h * D;
+          const bf16* dp = a.dout + ((long long)b * a.n_q + row) * HD + h * D;
+#pragma unroll
+          for (int c = 0; c < D; c += 8) {
+            const uint4 uo = *reinterpret_cast<const uint4*>(op + c), ud = *reinterpret_cast<const uint4*>(dp + c);
+            const bf162 *ho = reinterpret_cast<const bf162*>(&uo), *hd = reinterpret_cast<const bf162*>(&ud);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 fo = __bfloat1622float2(ho[e]), fd = __bfloat1622float2(hd[e]);
+              dsum += fo.x * fd.x + fo.y * fd.y;
+            }
+          }
+          l2 = a.lse2[((long long)b * a.H + h) * a.n_q + row];
+        }
+        drow[row] = dsum;
+        lrow[row] = l2;
+      }
+      // the four warps read each other's rows later: make the writes visible to all of them
+      __syncwarp();
+      if (lane == 0) mbar_arrive(drow_ready);
+      if (!mbar_wait(drow_ready, ic & 1)) { if (lane == 0) report(ST_TIMEOUT_EPI, 70); ok = false; }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const bf16* mrow = a.mask ? a.mask + (long long)b * a.mask_bstride : nullptr;
+      for (int j = 0; j < a.n_kb && ok; ++j, ++jc) {
+        const int k0 = j * AT_BK;
+        for (int i = 0; i < a.n_qt; ++i, ++t) {
+          const uint32_t s = t & 1;
+          const int qrow = i * AT_BQ + r;
+          bool w = true;
+          if (a.has_bias) w = mbar_wait(bias_full + 8 * s, (t >> 1) & 1);
+          if (w) w = mbar_wait(sdp_full, t & 1);
+          if (w) w = mbar_wait(pds_empty, (t & 1) ^ 1);        // previous step's gradient MMAs have read P / dS
+          if (!w && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_MMA, 71);
+          w = __all_sync(0xffffffffu, w);
+          if (!w) { ok = false; break; }
+          tc_fence_after();
+          const float Di = drow[qrow], L2 = lrow[qrow];
+          const bool row_ok = qrow < a.n_q;
+          const uint8_t* btile = sm + BwdSmem::BIAS + s * 32768;
+          uint8_t* ptile = sm + BwdSmem::P;
+          uint8_t* dstile = sm + BwdSmem::DS;
+          bf16* ds_g = (a.ds && row_ok) ? a.ds + (((long long)b * a.H + h) * a.n_q + qrow) * a.n_k + k0 : nullptr;
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            float sv[64], dpv[64];
+            tmem_ld_32x32(lane_base + TM_S + half * 64, sv);
+            tmem_ld_32x32(lane_base + TM_S + half * 64 + 32, sv + 32);
+            tmem_ld_32x32(lane_base + TM_DP + half * 64, dpv);
+            tmem_ld_32x32(lane_base + TM_DP + half * 64 + 32, dpv + 32);
+            tmem_ld_wait();
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int cu = half * 8 + u;                   // 16-byte unit index within the 128-key row
+              float bv[8], mk[8];
+              if (a.has_bias) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(btile + half * 16384 + r * 128 + ((u ^ (r & 7)) << 4));
+                const bf162* hp = reinterpret_cast<const bf162*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __bfloat1622float2(hp[e]);
+                  bv[2 * e] = f.x;
+                  bv[2 * e + 1] = f.y;
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) bv[e] = 0.f;
+              }
+              const int kk = k0 + cu * 8;
+              if (mrow) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) mk[e] = (kk + e < a.n_k) ? __bfloat162float(mrow[kk + e]) : 0.f;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) mk[e] = 1.f;
+              }
+              uint4 pp, dd, dg;
+              bf162 *hpp = reinterpret_cast<bf162*>(&pp), *hdd = reinterpret_cast<bf162*>(&dd), *hdg = reinterpret_cast<bf162*>(&dg);
+#pragma unroll
+              for (int e = 0; e < 8; e += 2) {
+                float p[2], g[2];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  const int c = u * 8 + e + q;
+                  float v = sv[c] * a.scale_log2e + bv[e + q] * LOG2E;
+                  if (mk[e + q] == 0.f) v = -1e9f * LOG2E;
+                  float pe = ex2f(v - L2);
+                  if (!row_ok || kk + e + q >= a.n_k) pe = 0.f;
+                  p[q] = pe;
+                  g[q] = pe * (dpv[c] - Di);
+                }
+                hpp[e >> 1] = __floats2bfloat162_rn(p[0], p[1]);
+                hdg[e >> 1] = __floats2bfloat162_rn(g[0], g[1]);
+                hdd[e >> 1] = __floats2bfloat162_rn(g[0] * a.scale, g[1] * a.scale);
+              }
+              const uint32_t off = half * 16384 + r * 128 + ((u ^ (r & 7)) << 4);
+              *reinterpret_cast<uint4*>(ptile + off) = pp;
+              *reinterpret_cast<uint4*>(dstile + off) = dd;
+              if (ds_g) {
+                if (kk + 8 <= a.n_k) *reinterpret_cast<uint4*>(ds_g + cu * 8) = dg;
+                else {
+                  const bf16* src = reinterpret_cast<const bf16*>(&dg);
+                  for (int e = 0; e < 8; ++e)
+                    if (kk + e < a.n_k) ds_g[cu * 8 + e] = src[e];
+                }
+              }
+            }
+          }
+          tc_fence_before();
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(sdp_empty);
+            if (a.has_bias) mbar_arrive(bias_empty + 8 * s);
+            mbar_arrive(pds_full);
+          }
+        }
+        if (!ok) break;
+        // dK_j / dV_j complete: thread = key row
+        {
+          bool w = mbar_wait(dkv_full, jc & 1);
+          if (!w && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_MMA, 72);
+          w = __all_sync(0xffffffffu, w);
+          if (!w) { ok = false; break; }
+          tc_fence_after();
+          float gv[D], gk[D];
+          tmem_ld_32x32(lane_base + TM_DV, gv);
+          tmem_ld_32x32(lane_base + TM_DK, gk);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dkv_empty);
+          const int krow = k0 + r;
+          if (krow < a.n_k) {
+            bf16* pv = a.dv + (long long)b * a.dkv_bstride + (long long)krow * HD + h * D;
+            bf16* pk = a.dk + (long long)b * a.dkv_bstride + (long long)krow * HD + h * D;
+#pragma unroll
+            for (int c = 0; c < D; c += 8) {
+              uint4 x, y;
+              bf162 *hx = reinterpret_cast<bf162*>(&x), *hy = reinterpret_cast<bf162*>(&y);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                hx[e] = __floats2bfloat162_rn(gv[c + 2 * e], gv[c + 2 * e + 1]);
+                hy[e] = __floats2bfloat162_rn(gk[c + 2 * e], gk[c + 2 * e + 1]);
+              }
+              *reinterpret_cast<uint4*>(pv + c) = x;
+              *reinterpret_cast<uint4*>(pk + c) = y;
+            }
+          }
+        }
+      }
+      if (!ok) break;
+      // dQ_i complete for every query tile of this item
+      {
+        bool w = mbar_wait(dq_full, ic & 1);
+        if (!w && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_MMA, 73);
+        w = __all_sync(0xffffffffu, w);
+        if (!w) { ok = false; break; }
+        tc_fence_after();
+        for (int i = 0; i < a.n_qt; ++i) {
+          float gq[D];
+          tmem_ld_32x32(lane_base + TM_DQ + i * 32, gq);
+          tmem_ld_wait();
+          const int qrow = i * AT_BQ + r;
+          if (qrow < a.n_q) {
+            bf16* pq = a.dq + (long long)b * a.dq_bstride + (long long)qrow * HD + h * D;
+#pragma unroll
+            for (int c = 0; c < D; c += 8) {
+              uint4 x;
+              bf162* hx = reinterpret_cast<bf162*>(&x);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) hx[e] = __floats2bfloat162_rn(gq[c + 2 * e], gq[c + 2 * e + 1]);
+              *reinterpret_cast<uint4*>(pq + c) = x;
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_empty);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace ffb
+
+extern "C" {
+
+// Gradients of ffb_attention_fwd.  o / dout: [B][n_q][H*D] contiguous; dqkv: three [B][n_max][H*D] slabs
+// (dq, dk, dv; n_max = max(n_q, n_k)); ds: bf16 [B][H][n_q][n_k] (unscaled dS, for the bias gradient) or null.
+int ffb_attention_bwd(const void* q, const void* k, const void* v, long long q_bstride, long long q_rstride, long long kv_bstride,
+                      long long kv_rstride, const void* bias, const void* mask, long long mask_bstride, const void* o, const void* dout,
+                      const float* lse2, void* dqkv, void* ds, int B, int H, int n_q, int n_k, int D, float scale, void* stream) {
+  using namespace ffb;
+  if (D != 32) return -2;
+  if (n_q > 512) return -3;
+  if ((q_rstride % 8) || (kv_rstride % 8) || (q_bstride % 8) || (kv_bstride % 8) || (n_k % 8)) return -4;
+  AttnBwdArgs a;
+  a.B = B; a.H = H; a.n_q = n_q; a.n_k = n_k;
+  a.n_qt = (n_q + AT_BQ - 1) / AT_BQ;
+  a.n_kb = (n_k + AT_BK - 1) / AT_BK;
+  a.items = B * H;
+  a.scale = scale;
+  a.scale_log2e = scale * LOG2E;
+  a.mask = (const bf16*)mask;
+  a.mask_bstride = mask_bstride;
+  a.o = (const bf16*)o;
+  a.dout = (const bf16*)dout;
+  a.lse2 = lse2;
+  const long long HD = (long long)H * D;
+  const long long n_max = n_q > n_k ? n_q : n_k;
+  a.dq = (bf16*)dqkv;
+  a.dk = a.dq + (long long)B * n_max * HD;
+  a.dv = a.dk + (long long)B * n_max * HD;
+  a.dq_bstride = n_max * HD;
+  a.dkv_bstride = n_max * HD;
+  a.ds = (bf16*)ds;
+  a.has_bias = bias ? 1 : 0;
+  CUtensorMap tq, tk, tv, tdo, tb;
+  { int rc = make_tmap3(&tq, q, HD, n_q, B, q_rstride, q_bstride, D, AT_BQ, 64); if (rc) return -100000 - rc; }
+  if (make_tmap3(&tk, k, HD, n_k, B, kv_rstride, kv_bstride, D, AT_BK, 64)) return -11;
+  if (make_tmap3(&tv, v, HD, n_k, B, kv_rstride, kv_bstride, D, AT_BK, 64)) return -12;
+  { int rc = make_tmap3(&tdo, dout, HD, n_q, B, HD, (long long)n_q * HD, D, AT_BQ, 64); if (rc) return -130000 - rc; }
+  if (bias) {
+    if (make_tmap3(&tb, bias, n_k, n_q, H, n_k, (long long)n_q * n_k, 64, AT_BQ, 128)) return -14;
+  } else {
+    tb = tq;
+  }
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL) != cudaSuccess) return -15;
+    attr = true;
+  }
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  const int grid = a.items < sm_count ? a.items : sm_count;
+  attn_bwd_kernel<32><<<grid, AT_THREADS, BwdSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, tdo, tb, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -16;
 }
 
 }  // extern "C"

@@ -37,6 +37,7 @@
 // (fastfold/model/fastnn/kernel/jit/fused_ops.py:5-22).
 #include "common.cuh"
 #include "gemm_api.h"
+#include "tmap.h"
 
 namespace ffb {
 
@@ -583,36 +584,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
 // Host side: tensor-map encoding through the driver entry point (no link-time
 // dependency on libcuda) and the launcher.
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess || !p) return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// bf16 matrix [batch][rows][cols] (cols contiguous, row stride ld, batch stride
-// bstride, all in elements); box = box_cols x box_rows, 128B swizzle.
+// bf16 matrix [batch][rows][cols] (cols contiguous, row stride ld, batch stride bstride, all in elements);
+// box = box_cols x box_rows, 128B swizzle.
 int make_tmap_bf16(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, long long batch,
                    long long bstride, int box_cols, int box_rows) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return -1;
-  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? bstride : rows * ld) * 2};
-  if (strides[1] == 0) strides[1] = (cuuint64_t)ld * 2 * rows;
-  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)r;
+  return encode_tmap3_bf16(map, base, cols, rows, batch > 0 ? batch : 1, ld, bstride, box_cols, box_rows, 128);
 }
 
 template <int BN, bool A_MN, bool B_MN>

@@ -27,9 +27,16 @@ from .ops import Linear, OutProductMean
 from .triangle import PairCore, pad_amount
 
 
-def draw_block_dropout(n_res_padded, c_m, c_z, device, dtype, p_msa=0.15, p_pair=0.25, generator=None):
-    """All five axis-shared dropout masks of one block, from a single random draw."""
-    r = torch.rand(n_res_padded, c_m + 4 * c_z, device=device, generator=generator)
+def draw_block_dropout(n_res_padded, c_m, c_z, device, dtype, p_msa=0.15, p_pair=0.25, generator=None, n_res=None):
+    """All five axis-shared dropout masks of one block, from a single random draw.
+
+    The draw has the un-padded length ``n_res`` (rows added to make the length divisible by the DAP size get a
+    pass-through mask), so the random stream - and therefore the result - does not depend on the DAP size.
+    """
+    n_res = n_res_padded if n_res is None else n_res
+    r = torch.rand(n_res, c_m + 4 * c_z, device=device, generator=generator)
+    if n_res_padded > n_res:
+        r = torch.cat([r, r.new_ones(n_res_padded - n_res, r.shape[1])], dim=0)
     keep_m = (r[:, :c_m] >= p_msa).to(dtype) / (1.0 - p_msa)
     keep_z = (r[:, c_m:] >= p_pair).to(dtype) / (1.0 - p_pair)
     kz = keep_z.reshape(n_res_padded, 4, c_z)
@@ -64,7 +71,7 @@ class Evoformer(nn.Module):
         msa_mask = F.pad(msa_mask.unsqueeze(0), (0, pad))
         pair_mask = F.pad(pair_mask.unsqueeze(0), (0, pad, 0, pad))
         if _drop is None and self.training:
-            _drop = draw_block_dropout(seq_length + pad, self.c_m, self.c_z, m.device, m.dtype)
+            _drop = draw_block_dropout(seq_length + pad, self.c_m, self.c_z, m.device, m.dtype, n_res=seq_length)
         d_msa = None if _drop is None else _drop.get("msa_row")
         if not self.is_multimer:
             m = self.msa(m, z, msa_mask, d_msa)
@@ -100,7 +107,7 @@ def run_blocks(blocks, m, z, msa_mask, pair_mask, chunk_size, _mask_trans, train
     n_pad = pair_mask.size(-1) + pad_amount(pair_mask.size(-1), P)
     fns = []
     for b in blocks:
-        drop = draw_block_dropout(n_pad, c_m, c_z, m.device, m.dtype) if training else None
+        drop = draw_block_dropout(n_pad, c_m, c_z, m.device, m.dtype, n_res=pair_mask.size(-1)) if training else None
         fns.append(partial(b, msa_mask=msa_mask, pair_mask=pair_mask, chunk_size=chunk_size, _mask_trans=_mask_trans, _drop=drop))
     return checkpoint_blocks(fns, args=(m, z), blocks_per_ckpt=blocks_per_ckpt)
 

@@ -95,7 +95,8 @@ class _FlashFn(torch.autograd.Function):
         rc = lib.ffb_attention_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), qbs, qrs, kbs, krs, _lib.ptr(b3), _lib.ptr(m2), n_k,
                                    _lib.ptr(out), _lib.ptr(do_c), _lib.ptr(lse), _lib.ptr(dqkv), _lib.ptr(ds), B, H, n_q, n_k, d,
                                    float(ctx.scale), _lib.stream_ptr())
-        _lib.check(rc, "ffb_attention_bwd")
+        _lib.check(rc, "ffb_attention_bwd(q=%s strides=%s ptr=%x k strides=%s B=%d H=%d n=%d/%d)" % (
+            tuple(q.shape), q.stride(), q.data_ptr(), k.stride(), B, H, n_q, n_k))
         dq = dqkv[0, :, :n_q].view(1, B, n_q, H, d).permute(0, 1, 3, 2, 4)
         dk = dqkv[1, :, :n_k].view(1, B, n_k, H, d).permute(0, 1, 3, 2, 4)
         dv = dqkv[2, :, :n_k].view(1, B, n_k, H, d).permute(0, 1, 3, 2, 4)

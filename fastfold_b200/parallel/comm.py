@@ -54,7 +54,7 @@ def _gather(tensor, dim=-1):
     dim = dim % tensor.dim()
     t = tensor.contiguous()
     out = torch.empty((P,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-    dist.all_gather_into_tensor(out, t, group=core.get_dap_group())
+    dist.all_gather_into_tensor(out.view((-1,) + tuple(t.shape[1:])), t, group=core.get_dap_group())
     if dim == 0:
         return out.reshape((P * t.shape[0],) + tuple(t.shape[1:]))
     # [P, d0, .., dim, ..] -> [d0, .., P*dim, ..]

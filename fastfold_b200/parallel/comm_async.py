@@ -57,7 +57,7 @@ def _gather_async(tensor, dim):
         return tensor, None
     t = tensor.contiguous()
     out = torch.empty((P,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-    work = dist.all_gather_into_tensor(out, t, group=core.get_dap_group(), async_op=True)
+    work = dist.all_gather_into_tensor(out.view((-1,) + tuple(t.shape[1:])), t, group=core.get_dap_group(), async_op=True)
     return out, work
 
 

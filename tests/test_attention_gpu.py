@@ -34,3 +34,35 @@ def test_forward(B, n, H, use_bias, use_mask, device_status):
     ref = attention_core_ref(q.float(), k.float(), v.float(), None if mask is None else mask.float(), None if bias is None else bias.float())
     err = (out.float() - ref).abs().max().item()
     assert err < 2e-2, "max abs err %g" % err
+
+
+@pytest.mark.parametrize("B,n,H,use_bias,use_mask", [
+    (4, 128, 8, True, True), (16, 256, 8, True, True), (7, 256, 4, False, True), (5, 384, 4, True, False), (3, 200, 4, True, True),
+    (6, 512, 4, True, True),
+])
+def test_backward(B, n, H, use_bias, use_mask, device_status):
+    torch.manual_seed(B * 77 + n)
+    qkv = (torch.randn(1, B, n, 3, H, 32, device=DEV) * 0.7).to(torch.bfloat16).requires_grad_(True)
+    bias = torch.randn(1, 1, H, n, n, device=DEV).to(torch.bfloat16).requires_grad_(True) if use_bias else None
+    mask = None
+    if use_mask:
+        mask = (torch.rand(1, B, n, device=DEV) > 0.2).to(torch.bfloat16)
+        mask[..., 0] = 1
+    q, k, v = (qkv[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
+    assert flash.supported(q, k, v, mask, bias)
+    out = attention_core(q, k, v, mask, bias)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qkv_r = qkv.detach().float().requires_grad_(True)
+    bias_r = bias.detach().float().requires_grad_(True) if use_bias else None
+    qr, kr, vr = (qkv_r[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
+    ref = attention_core_ref(qr, kr, vr, None if mask is None else mask.float(), bias_r)
+    ref.backward(g.float())
+    assert (out.float() - ref).abs().max() < 2e-2
+    gerr = (qkv.grad.float() - qkv_r.grad).abs().max().item()
+    gmax = qkv_r.grad.abs().max().item()
+    assert gerr < 3e-2 * max(1.0, gmax), "dqkv err %g (max %g)" % (gerr, gmax)
+    if use_bias:
+        berr = (bias.grad.float() - bias_r.grad).abs().max().item()
+        bmax = bias_r.grad.abs().max().item()
+        assert berr < 3e-2 * max(1.0, bmax), "dbias err %g (max %g)" % (berr, bmax)
