@@ -45,7 +45,8 @@ __device__ int g_status[8];
 
 constexpr int BM = 128;
 constexpr int BK = 64;           // 64 bf16 = 128 B = one swizzle row
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;
 constexpr int STG_LD = 65;       // staging row pitch in floats (odd -> conflict-free column access)
 
 template <int BN>
@@ -54,8 +55,8 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int EPI_WARP_BYTES = 16384;              // per epilogue warp: 2 store tiles + mul tile + residual tile (4 KB each)
-  static constexpr int STG_BYTES = 4 * EPI_WARP_BYTES;      // (the fp32 transpose buffer of the generic path aliases it)
+  static constexpr int EPI_WARP_BYTES = 9216;               // per epilogue warp: 2 x 4 KB TMA tiles (the 32 x 65 fp32 transpose
+  static constexpr int STG_BYTES = EPI_WARPS * EPI_WARP_BYTES;  // buffer of the generic path aliases them)
   static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator stages
 };
@@ -181,8 +182,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
   const uint32_t bar_empty = bar_full + 8 * STAGES;         // STAGES: operand tile consumed
   const uint32_t bar_accf = bar_empty + 8 * STAGES;         // 2: accumulator stage complete
   const uint32_t bar_acce = bar_accf + 16;                  // 2: accumulator stage drained
-  const uint32_t bar_epld = bar_acce + 16;                  // 4: per-epilogue-warp TMA loads of mul / residual tiles
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 8);
+  const uint32_t bar_epld = bar_acce + 16;                  // 8: per-epilogue-warp TMA loads of mul / residual tiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + EPI_WARPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -196,9 +197,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_accf + 8 * s, 1);
-      mbar_init(bar_acce + 8 * s, 4);     // one arrival per epilogue warp
+      mbar_init(bar_acce + 8 * s, EPI_WARPS);     // one arrival per epilogue warp
     }
-    for (int s = 0; s < 4; ++s) mbar_init(bar_epld + 8 * s, 1);
+    for (int s = 0; s < EPI_WARPS; ++s) mbar_init(bar_epld + 8 * s, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmA);
@@ -296,10 +297,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
     }
     __syncwarp();
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
+    // ---------------- epilogue (warps 2..9): two warps per TMEM lane quadrant, alternating column chunks ----------------
+    const int half = (warp - 2) >> 2;
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
     float* stg = staging + (warp - 2) * (Cfg::EPI_WARP_BYTES / 4);
-    const uint32_t epi_smem = smem_u32(stg);              // 16 KB, 1024-aligned: [out0][out1][mul][res]
+    const uint32_t epi_smem = smem_u32(stg);              // 1024-aligned: [tile0 4 KB][tile1 4 KB]
     const uint32_t my_ldbar = bar_epld + 8 * (warp - 2);
     uint32_t ld_phase = 0, out_buf = 0;
     const int Nout = g.glu ? (g.N >> 1) : g.N;
@@ -323,14 +325,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
         const bf16* dm_row = (g.dmask && row < g.M) ? reinterpret_cast<const bf16*>(g.dmask) + (long long)((row / g.dm_div) % g.dm_mod) * g.lddm : nullptr;
         const bool has_ld = (g.mul != nullptr) || (g.resid != nullptr);
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = half; c < BN / 64; c += 2) {
           const int col0 = n0 + c * 64;
           if (col0 >= g.N || row0 >= g.M) break;           // warp-uniform
-          if (has_ld && lane == 0) {
-            mbar_expect_tx(my_ldbar, (g.mul ? 4096u : 0u) + (g.resid ? 4096u : 0u));
-            if (g.mul) tma_load_3d(epi_smem + 8192, &tmMul, my_ldbar, col0, row0, tc.batch);
-            if (g.resid) tma_load_3d(epi_smem + 12288, &tmRes, my_ldbar, col0, row0, tc.batch);
+          // tile[out_buf] receives the residual (if any) and then the result; tile[out_buf ^ 1] receives mul (if any).
+          // A tile may be refilled only after the bulk store that last read it has finished reading.
+          if (lane == 0) {
+            if (g.mul) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            if (has_ld) {
+              mbar_expect_tx(my_ldbar, (g.mul ? 4096u : 0u) + (g.resid ? 4096u : 0u));
+              if (g.resid) tma_load_3d(epi_smem + out_buf * 4096, &tmRes, my_ldbar, col0, row0, tc.batch);
+              if (g.mul) tma_load_3d(epi_smem + (out_buf ^ 1) * 4096, &tmMul, my_ldbar, col0, row0, tc.batch);
+            }
           }
+          __syncwarp();
           float v[64];
           tmem_ld_32x32(taddr + c * 64, v);
           tmem_ld_32x32(taddr + c * 64 + 32, v + 32);
@@ -354,17 +363,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
             }
           }
           if (has_ld) {
-            bool w = mbar_wait(my_ldbar, ld_phase);
+            const bool w = mbar_wait(my_ldbar, ld_phase);
             ld_phase ^= 1;
-            if (!w && lane == 0) report(ST_TIMEOUT_TMA, 40);
-            // (on a timeout the tile is still written from whatever landed; the status word carries the failure)
+            if (!w && lane == 0) report(ST_TIMEOUT_TMA, 40);   // the status word carries the failure; the tile is still written
           }
-          const uint8_t* stg8 = reinterpret_cast<const uint8_t*>(stg);
+          uint8_t* stg8 = reinterpret_cast<uint8_t*>(stg);
+          uint8_t* obuf = stg8 + out_buf * 4096;
           if (g.mul) {
+            const uint8_t* mbuf = stg8 + (out_buf ^ 1) * 4096;
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
               float t[8];
-              load8(reinterpret_cast<const bf16*>(stg8 + 8192 + lane * 128 + ((u ^ (lane & 7)) << 4)), true, 8, t);
+              load8(reinterpret_cast<const bf16*>(mbuf + lane * 128 + ((u ^ (lane & 7)) << 4)), true, 8, t);
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[u * 8 + j] *= t[j];
             }
@@ -386,26 +396,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
               }
             }
           }
-          if (g.resid) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+          for (int u = 0; u < 8; ++u) {
+            uint8_t* slot = obuf + lane * 128 + ((u ^ (lane & 7)) << 4);   // this thread's own row: read residual, write result
+            if (g.resid) {
               float t[8];
-              load8(reinterpret_cast<const bf16*>(stg8 + 12288 + lane * 128 + ((u ^ (lane & 7)) << 4)), true, 8, t);
+              load8(reinterpret_cast<const bf16*>(slot), true, 8, t);
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[u * 8 + j] += t[j];
             }
-          }
-          // the store tile written two chunks ago must have been read out by its bulk store
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-          uint8_t* obuf = reinterpret_cast<uint8_t*>(stg) + out_buf * 4096;
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
             uint4 pk;
             bf162* hp = reinterpret_cast<bf162*>(&pk);
 #pragma unroll
             for (int j = 0; j < 4; ++j) hp[j] = __floats2bfloat162_rn(v[u * 8 + 2 * j], v[u * 8 + 2 * j + 1]);
-            *reinterpret_cast<uint4*>(obuf + lane * 128 + ((u ^ (lane & 7)) << 4)) = pk;
+            *reinterpret_cast<uint4*>(slot) = pk;
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -423,7 +427,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
         const bool row_ok = row < g.M;
         const float rs = (g.rowscale && row_ok) ? g.rowscale[(long long)tc.batch * g.rs_bstride + row] : 1.f;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = half; c < BN / 32; c += 2) {
           float v[32];
           tmem_ld_32x32(taddr + c * 32, v);
           tmem_ld_wait();
@@ -471,7 +475,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
         const int g8 = (lane & 7) * 8;
         const int sub = lane >> 3;
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = half; c < BN / 64; c += 2) {
           {
             float v[32];
             tmem_ld_32x32(taddr + c * 64, v);
