@@ -1,0 +1,395 @@
+// Collectives of Dynamic Axial Parallelism as kernels over NVLink / NVSwitch peer memory.
+//
+// Every rank owns a slab of a *symmetric heap* (same size and layout on every GPU of the DAP group, all peers
+// mapped into this GPU's address space) plus a symmetric pad of 32-bit flags.  A collective is two kernels:
+//
+//   publish   the rank's contribution is copied into its own slot of the heap (or a producer kernel wrote it
+//             there directly) and the rank raises ready[slot][rank] = epoch in every peer's flag pad;
+//   consume   a kernel that needs peer data polls ready[slot][peer] in its OWN pad (local memory), then reads
+//             the peer's slot with plain loads over NVLink - as a copy (all-gather, all-to-all), fused with the
+//             transpose + LayerNorm that follows an all-to-all, or as TMA tiles of a GEMM operand
+//             (gemm_tcgen05.cu) - and finally raises done[slot][rank] = epoch in every peer's pad, which is what a
+//             later publish into the same slot waits for.
+//
+// Epochs are device-side counters (one per slot, advanced by the consumer), never kernel arguments, so a CUDA
+// graph that contains these kernels can be replayed.  Every wait has a time limit; when it runs out the kernel
+// records ST_TIMEOUT_PEER in the status word, skips the data it could not get and returns - it never spins
+// forever and never traps.  Only plain peer loads / stores are used (no multimem, no multicast loads).
+//
+// The reference performs the same exchanges with NCCL calls through torch.distributed
+// (fastfold/distributed/comm.py:42-65,146-173, comm_async.py:66-147) followed by separate rearrange / cat copies.
+#include "common.cuh"
+#include "comm_api.h"
+
+namespace ffb {
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// flag pad layout (uint32 words)
+__device__ __forceinline__ int w_ready(int slot, int r) { return slot * 16 + r; }
+__device__ __forceinline__ int w_done(int slot, int r) { return slot * 16 + 8 + r; }
+__device__ __forceinline__ int w_epoch(int slot) { return SYMM_MAX_SLOTS * 16 + slot; }             // local only
+__device__ __forceinline__ int w_blocks(int slot) { return SYMM_MAX_SLOTS * 17 + slot; }            // local only
+
+// Bounded poll of a flag in local memory; returns false on timeout.
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, uint64_t limit_ns) {
+  if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+      __nanosleep(64);
+    }
+    if (globaltimer_ns() - t0 > limit_ns) return false;
+  }
+}
+
+// One thread: wait until flag word `base(slot, r)` reached `want` for every peer r != rank.
+__device__ __forceinline__ bool wait_peers(const SymmCtx& c, bool ready_not_done, int slot, uint32_t want) {
+  bool ok = true;
+  for (int r = 0; r < c.world; ++r) {
+    if (r == c.rank) continue;
+    const uint32_t* p = c.flags[c.rank] + (ready_not_done ? w_ready(slot, r) : w_done(slot, r));
+    if (!wait_flag(p, want, c.wait_ns)) {
+      report(ST_TIMEOUT_PEER, (slot << 8) | r);
+      ok = false;
+    }
+  }
+  return ok;
+}
+
+// The block that finishes last raises this rank's flag in every peer's pad (and, for `done`, advances the epoch).
+__device__ __forceinline__ void last_block_signal(const SymmCtx& c, int slot, uint32_t epoch, bool ready_not_done) {
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* blk = c.flags[c.rank] + w_blocks(slot);
+    const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+    s_last = (atomicAdd(blk, 1u) == total - 1) ? 1 : 0;
+    if (s_last) {
+      *blk = 0;
+      __threadfence_system();
+      for (int r = 0; r < c.world; ++r)
+        st_release_sys(c.flags[r] + (ready_not_done ? w_ready(slot, c.rank) : w_done(slot, c.rank)), epoch);
+      if (!ready_not_done) c.flags[c.rank][w_epoch(slot)] = epoch;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t next_epoch(const SymmCtx& c, int slot) {
+  return reinterpret_cast<volatile uint32_t*>(c.flags[c.rank])[w_epoch(slot)] + 1u;
+}
+
+// ---------------------------------------------------------------------------
+// publish: src -> own heap slot, then ready[slot][rank] = epoch on every peer
+// ---------------------------------------------------------------------------
+__global__ void symm_publish_k(SymmCtx c, int slot, long long heap_off, const uint4* __restrict__ src, long long n16) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = next_epoch(c, slot);
+    // the previous use of this slot must have been read by every peer before it is overwritten
+    wait_peers(c, false, slot, s_epoch - 1u);
+  }
+  __syncthreads();
+  uint4* dst = reinterpret_cast<uint4*>(c.heap[c.rank] + heap_off);
+  if (src != nullptr) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+  }
+  last_block_signal(c, slot, s_epoch, true);
+}
+
+// ---------------------------------------------------------------------------
+// all-gather: dst[r] = slot of peer r (each of n16 16-byte units)
+// all-to-all: every rank published P chunks; dst[r] = chunk `rank` of peer r
+// ---------------------------------------------------------------------------
+__global__ void symm_pull_k(SymmCtx c, int slot, long long heap_off, uint4* __restrict__ dst, long long n16, int all_to_all) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_epoch = next_epoch(c, slot);
+    s_ok = wait_peers(c, true, slot, s_epoch) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const long long total = n16 * c.world;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      const int r = (int)(i / n16);
+      const long long k = i - (long long)r * n16;
+      const uint4* src = reinterpret_cast<const uint4*>(c.heap[r] + heap_off) + (all_to_all ? (long long)c.rank * n16 : 0) + k;
+      dst[i] = *src;
+    }
+  }
+  last_block_signal(c, slot, s_epoch, false);
+}
+
+// ---------------------------------------------------------------------------
+// all-to-all fused with (optional transpose and) LayerNorm.
+//
+// Every rank published its shard X_r in its natural layout.  mode 0 ("row -> column"): X_r is [A/P][B][C] and the
+// result on this rank is Y [A][B/P][C] with Y[a][bl] = X_{a / (A/P)}[a % (A/P)][rank * B/P + bl].  mode 1
+// ("column -> row"): X_r is [A][B/P][C], Y [A/P][B][C] with Y[al][b] = X_{b / (B/P)}[rank * A/P + al][b % (B/P)].
+// One warp per output row of C channels: the row is read once over NVLink, written raw (the residual stream) and,
+// when gamma is given, written normalised - optionally at the transposed position [b][a] (column attention and
+// the "ending node" triangle attention normalise the transposed tensor).
+// ---------------------------------------------------------------------------
+template <int VPL>
+__global__ void __launch_bounds__(128) symm_a2a_ln_k(SymmCtx c, int slot, long long heap_off, int mode, int A, int B, int C,
+                                                     bf16* __restrict__ y_raw, bf16* __restrict__ y_norm, const bf16* __restrict__ gamma,
+                                                     const bf16* __restrict__ beta, float eps, int transpose_norm) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_epoch = next_epoch(c, slot);
+    s_ok = wait_peers(c, true, slot, s_epoch) ? 1 : 0;
+  }
+  __syncthreads();
+  const int P = c.world;
+  const int Ad = mode == 0 ? A : A / P, Bd = mode == 0 ? B / P : B;       // output extents
+  const long long rows = (long long)Ad * Bd;
+  const int lane = threadIdx.x & 31;
+  constexpr int NV = VPL / 8;
+  if (s_ok) {
+    for (long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5); row < rows; row += (long long)gridDim.x * 4) {
+      const int a = (int)(row / Bd), b = (int)(row - (long long)a * Bd);
+      int r;
+      long long src_row;
+      if (mode == 0) {
+        const int ap = A / P;
+        r = a / ap;
+        src_row = (long long)(a - r * ap) * B + (long long)c.rank * Bd + b;
+      } else {
+        const int bp = B / P;
+        r = b / bp;
+        src_row = (long long)(c.rank * Ad + a) * bp + (b - r * bp);
+      }
+      const bf16* src = reinterpret_cast<const bf16*>(c.heap[r] + heap_off) + src_row * C;
+      float v[VPL];
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c0 = (i * 32 + lane) * 8;
+        if (c0 < C) {
+          const uint4 u = *reinterpret_cast<const uint4*>(src + c0);
+          if (y_raw) *reinterpret_cast<uint4*>(y_raw + row * C + c0) = u;
+          const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            v[i * 8 + 2 * j] = f.x;
+            v[i * 8 + 2 * j + 1] = f.y;
+            s += f.x + f.y;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i * 8 + j] = 0.f;
+        }
+      }
+      if (y_norm) {
+        const float mean = warp_sum(s) / C;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c0 = (i * 32 + lane) * 8;
+          if (c0 < C) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float d = v[i * 8 + j] - mean;
+              q += d * d;
+            }
+          }
+        }
+        const float rstd = rsqrtf(warp_sum(q) / C + eps);
+        const long long orow = transpose_norm ? ((long long)b * Ad + a) : row;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c0 = (i * 32 + lane) * 8;
+          if (c0 < C) {
+            const uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0), ub = *reinterpret_cast<const uint4*>(beta + c0);
+            const bf162 *hg = reinterpret_cast<const bf162*>(&ug), *hb = reinterpret_cast<const bf162*>(&ub);
+            uint4 uo;
+            bf162* ho = reinterpret_cast<bf162*>(&uo);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 g2 = __bfloat1622float2(hg[j]), b2 = __bfloat1622float2(hb[j]);
+              ho[j] = __floats2bfloat162_rn((v[i * 8 + 2 * j] - mean) * rstd * g2.x + b2.x, (v[i * 8 + 2 * j + 1] - mean) * rstd * g2.y + b2.y);
+            }
+            *reinterpret_cast<uint4*>(y_norm + orow * C + c0) = uo;
+          }
+        }
+      }
+    }
+  }
+  last_block_signal(c, slot, s_epoch, false);
+}
+
+// ---------------------------------------------------------------------------
+// Two-shot all-reduce (sum) of a bf16 vector that lives at the same heap offset on every rank (the flat gradient
+// buffer): rank q sums element range q over all peers in fp32 and stores the result back into every peer's copy.
+// Ranges are disjoint, so no rank reads what another one is writing.  `scale` is applied to the sum.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) symm_allreduce_bf16_k(SymmCtx c, int slot, long long heap_off, long long n8, float scale) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_epoch = next_epoch(c, slot);
+    // entry: every rank announces that its gradients are complete (this kernel runs after backward on the stream)
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_ready(slot, c.rank), s_epoch);
+    }
+    s_ok = wait_peers(c, true, slot, s_epoch) ? 1 : 0;
+  }
+  __syncthreads();
+  const int P = c.world;
+  const long long per = (n8 + P - 1) / P;
+  const long long lo = per * c.rank;
+  long long hi = lo + per;
+  if (hi > n8) hi = n8;
+  if (s_ok) {
+    for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (long long)gridDim.x * blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int r = 0; r < P; ++r) {
+        const uint4 u = *(reinterpret_cast<const uint4*>(c.heap[r] + heap_off) + i);
+        const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      bf162* ho = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ho[j] = __floats2bfloat162_rn(acc[2 * j] * scale, acc[2 * j + 1] * scale);
+      for (int r = 0; r < P; ++r) *(reinterpret_cast<uint4*>(c.heap[r] + heap_off) + i) = o;
+    }
+  }
+  // exit: every rank's range has been written everywhere before anyone reads the result
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* blk = c.flags[c.rank] + w_blocks(slot);
+    s_last = (atomicAdd(blk, 1u) == gridDim.x - 1) ? 1 : 0;
+    if (s_last) {
+      *blk = 0;
+      __threadfence_system();
+      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_done(slot, c.rank), s_epoch);
+      wait_peers(c, false, slot, s_epoch);
+      c.flags[c.rank][w_epoch(slot)] = s_epoch;
+    }
+  }
+}
+
+// Raises ready[slot][rank] after a producer kernel wrote the slot directly (stream-ordered behind it), waiting first
+// (pre = 1, run BEFORE the producer) for the peers to have finished with the slot's previous contents.
+__global__ void symm_slot_fence_k(SymmCtx c, int slot, int pre) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const uint32_t e = next_epoch(c, slot);
+  if (pre) {
+    wait_peers(c, false, slot, e - 1u);
+  } else {
+    __threadfence_system();
+    for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_ready(slot, c.rank), e);
+  }
+}
+
+// Consumer-side bookkeeping for a kernel that read peer slots itself (e.g. the GEMM reading operand tiles through
+// peer tensor maps): pre = 1 waits for every peer's ready flag (run before the consumer), pre = 0 raises done and
+// advances the epoch (run after it).
+__global__ void symm_consume_fence_k(SymmCtx c, int slot, int pre) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const uint32_t e = next_epoch(c, slot);
+  if (pre) {
+    wait_peers(c, true, slot, e);
+  } else {
+    __threadfence_system();
+    for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_done(slot, c.rank), e);
+    c.flags[c.rank][w_epoch(slot)] = e;
+  }
+}
+
+// Test hook: waits on a ready flag that nothing raises, with a short limit; must time out and report, not hang.
+__global__ void symm_wait_never_k(SymmCtx c, int slot) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const uint32_t* p = c.flags[c.rank] + w_ready(slot, (c.rank + 1) % (c.world > 1 ? c.world : 2));
+    if (!wait_flag(p, 0x7fffffffu, c.wait_ns)) report(ST_TIMEOUT_PEER, slot << 8);
+  }
+}
+
+}  // namespace ffb
+
+using namespace ffb;
+
+extern "C" {
+
+static int grid_for(long long n, int threads, int cap) {
+  long long g = (n + threads - 1) / threads;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return (int)g;
+}
+
+int ffb_symm_publish(const SymmCtx* c, int slot, long long heap_off, const void* src, long long bytes, void* stream) {
+  if (bytes % 16 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
+  const long long n16 = bytes / 16;
+  symm_publish_k<<<grid_for(n16, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, (const uint4*)src, n16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int ffb_symm_pull(const SymmCtx* c, int slot, long long heap_off, void* dst, long long bytes_per_rank, int all_to_all, void* stream) {
+  if (bytes_per_rank % 16 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
+  const long long n16 = bytes_per_rank / 16;
+  symm_pull_k<<<grid_for(n16 * c->world, 256, 592), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, (uint4*)dst, n16, all_to_all);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int ffb_symm_a2a_layernorm(const SymmCtx* c, int slot, long long heap_off, int mode, int A, int B, int C, void* y_raw, void* y_norm,
+                           const void* gamma, const void* beta, float eps, int transpose_norm, void* stream) {
+  if (C % 8 || C > 1024 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
+  if ((mode == 0 && (A % c->world || B % c->world)) || (mode == 1 && (A % c->world || B % c->world))) return -3;
+  const long long rows = (long long)(mode == 0 ? A : A / c->world) * (mode == 0 ? B / c->world : B);
+  const int grid = grid_for(rows, 4, 1184);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (C <= 256) symm_a2a_ln_k<8><<<grid, 128, 0, st>>>(*c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else if (C <= 512) symm_a2a_ln_k<16><<<grid, 128, 0, st>>>(*c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else symm_a2a_ln_k<32><<<grid, 128, 0, st>>>(*c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int ffb_symm_allreduce_bf16(const SymmCtx* c, int slot, long long heap_off, long long n_elems, float scale, void* stream) {
+  if (n_elems % 8 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
+  const long long n8 = n_elems / 8;
+  const long long per = (n8 + c->world - 1) / c->world;
+  symm_allreduce_bf16_k<<<grid_for(per, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, n8, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int ffb_symm_slot_fence(const SymmCtx* c, int slot, int pre, void* stream) {
+  symm_slot_fence_k<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, pre);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int ffb_symm_consume_fence(const SymmCtx* c, int slot, int pre, void* stream) {
+  symm_consume_fence_k<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, pre);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int ffb_symm_wait_never(const SymmCtx* c, int slot, void* stream) {
+  symm_wait_never_k<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // extern "C"

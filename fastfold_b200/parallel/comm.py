@@ -33,6 +33,18 @@ def _P():
     return core.get_dap_size()
 
 
+def _heap_for(t):
+    """Symmetric heap to use for this tensor, or None (CPU tensors, odd sizes, NCCL baseline selected)."""
+    if not t.is_cuda:
+        return None
+    from . import symm
+    h = symm.get_heap("dap")
+    if h is None:
+        return None
+    nb = t.numel() * t.element_size()
+    return h if (nb % (16 * h.world) == 0 and nb > 0) else None
+
+
 def _reduce(tensor):
     if _P() == 1:
         return tensor
@@ -53,8 +65,12 @@ def _gather(tensor, dim=-1):
         return tensor
     dim = dim % tensor.dim()
     t = tensor.contiguous()
-    out = torch.empty((P,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-    dist.all_gather_into_tensor(out.view((-1,) + tuple(t.shape[1:])), t, group=core.get_dap_group())
+    h = _heap_for(t)
+    if h is not None:
+        out = h.all_gather(None, t)
+    else:
+        out = torch.empty((P,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out.view((-1,) + tuple(t.shape[1:])), t, group=core.get_dap_group())
     if dim == 0:
         return out.reshape((P * t.shape[0],) + tuple(t.shape[1:]))
     # [P, d0, .., dim, ..] -> [d0, .., P*dim, ..]
@@ -75,6 +91,10 @@ def _reduce_scatter(tensor, dim):
     shape[dim] = size
     # bring the P chunks to the front so that the collective works on one contiguous buffer
     t = tensor.reshape(shape[:dim] + [P, size] + shape[dim + 1:]).movedim(dim, 0).contiguous()
+    h = _heap_for(t)
+    if h is not None:
+        # chunk q of every rank travels to rank q (NVLink traffic of a reduce-scatter), summed locally in fp32
+        return h.all_to_all(None, t).float().sum(dim=0).to(tensor.dtype)
     out = torch.empty(shape, dtype=tensor.dtype, device=tensor.device)
     if dist.get_backend(core.get_dap_group()) == "gloo":
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=core.get_dap_group())
@@ -93,8 +113,12 @@ def _all_to_all(tensor, in_dim, out_dim):
     size = divide(tensor.shape[in_dim], P)
     shape = list(tensor.shape)
     send = tensor.reshape(shape[:in_dim] + [P, size] + shape[in_dim + 1:]).movedim(in_dim, 0).contiguous()
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=core.get_dap_group())
+    h = _heap_for(send)
+    if h is not None:
+        recv = h.all_to_all(None, send)
+    else:
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=core.get_dap_group())
     # recv[p] = chunk from rank p, shaped like tensor with in_dim -> size
     recv = recv.movedim(0, out_dim)   # [.., P, out, ..] with P placed before out_dim's extent
     oshape = list(shape)

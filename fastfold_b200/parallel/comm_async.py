@@ -56,6 +56,10 @@ def _gather_async(tensor, dim):
     if P == 1:
         return tensor, None
     t = tensor.contiguous()
+    from .comm import _heap_for
+    h = _heap_for(t)
+    if h is not None:
+        return h.all_gather(None, t), None     # the kernels are asynchronous on the stream already
     out = torch.empty((P,) + tuple(t.shape), dtype=t.dtype, device=t.device)
     work = dist.all_gather_into_tensor(out.view((-1,) + tuple(t.shape[1:])), t, group=core.get_dap_group(), async_op=True)
     return out, work
@@ -151,6 +155,10 @@ def all_to_all_async(x, in_dim, out_dim):
     size = divide(x.shape[in_d], P)
     shape = list(x.shape)
     send = x.reshape(shape[:in_d] + [P, size] + shape[in_d + 1:]).movedim(in_d, 0).contiguous()
+    from .comm import _heap_for
+    h = _heap_for(send)
+    if h is not None:
+        return h.all_to_all(None, send), _A2AWork(None, shape, in_d, out_dim % x.dim(), None)
     recv = torch.empty_like(send)
     work = dist.all_to_all_single(recv, send, group=core.get_dap_group(), async_op=True)
     return recv, _A2AWork(work, shape, in_d, out_dim % x.dim(), send)
@@ -161,7 +169,8 @@ def all_to_all_async_opp(buf, work, in_dim, out_dim):
         return buf
     if isinstance(work, _AsyncHandle):
         return _A2ASync.apply(work.src, work.in_dim, work.out_dim)
-    work.work.wait()
+    if work.work is not None:
+        work.work.wait()
     P = core.get_dap_size()
     size = work.shape[work.in_dim] // P
     recv = buf.movedim(0, work.out_dim)

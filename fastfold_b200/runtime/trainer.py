@@ -48,7 +48,19 @@ class FlatAdamTrainer:
         total = sum(p.numel() for p in self.params)
         self.numel = total
         self.flat_w = torch.empty(total, device=dev, dtype=self.dtype)
-        self.flat_g = torch.zeros(total, device=dev, dtype=self.dtype)
+        # gradients live in the symmetric heap when there is one: the reduction kernel reads and writes peers' copies
+        self.grad_heap, self.grad_slot = None, None
+        padded = (total + 7) // 8 * 8
+        if dev.type == "cuda" and self.dtype == torch.bfloat16 and core.get_world_size() > 1 and grad_reducer is None:
+            from ..parallel import symm
+            self.grad_heap = symm.get_heap("world")
+        if self.grad_heap is not None:
+            self.grad_slot = self.grad_heap.slot("flat_grads", padded * 2)
+            self.flat_g_padded = self.grad_heap.view(self.grad_slot, (padded,), self.dtype)
+            self.flat_g_padded.zero_()
+            self.flat_g = self.flat_g_padded[:total]
+        else:
+            self.flat_g = torch.zeros(total, device=dev, dtype=self.dtype)
         self.master = torch.empty(total, device=dev, dtype=torch.float32)
         self.exp_avg = torch.zeros(total, device=dev, dtype=torch.float32)
         self.exp_avg_sq = torch.zeros(total, device=dev, dtype=torch.float32)
@@ -90,6 +102,8 @@ class FlatAdamTrainer:
         if core.get_world_size() > 1:
             if self.grad_reducer is not None:
                 self.grad_reducer(self.flat_g)
+            elif self.grad_heap is not None:
+                self.grad_heap.all_reduce_(self.grad_slot, self.flat_g_padded.numel())
             else:
                 dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM)
         if self.rep_scale is not None:

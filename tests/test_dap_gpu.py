@@ -1,0 +1,89 @@
+"""DAP on real GPUs (NCCL / fused P2P kernels): a 2-rank Evoformer stack must reproduce the 1-rank result."""
+import os
+import socket
+import sys
+import tempfile
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _model():
+    from fastfold_b200.models.fastnn import EvoformerStack
+    torch.manual_seed(3)
+    model = EvoformerStack(256, 128, 384, 2, blocks_per_ckpt=1)
+    g = torch.Generator().manual_seed(4)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2 and float(p.abs().sum()) == 0.0:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+    return model
+
+
+def _inputs(S, N):
+    g = torch.Generator().manual_seed(5)
+    m = torch.randn(S, N, 256, generator=g)
+    z = torch.randn(N, N, 128, generator=g)
+    mm = (torch.rand(S, N, generator=g) > 0.1).float()
+    pm = (torch.rand(N, N, generator=g) > 0.1).float()
+    return m, z, mm, pm
+
+
+def _run(dev, S, N, train):
+    model = _model().to(dev, torch.bfloat16).train(train)
+    m, z, mm, pm = (t.to(dev, torch.bfloat16) for t in _inputs(S, N))
+    torch.manual_seed(11)
+    if train:
+        m.requires_grad_(True)
+        z.requires_grad_(True)
+        om, oz, s = model(m, z, mm, pm, None)
+        (om.float().pow(2).mean() + oz.float().pow(2).mean() + s.float().pow(2).mean()).backward()
+        return om.detach().float().cpu(), oz.detach().float().cpu(), m.grad.float().cpu(), z.grad.float().cpu()
+    with torch.no_grad():
+        om, oz, s = model(m, z, mm, pm, None)
+    return om.float().cpu(), oz.float().cpu(), s.float().cpu(), None
+
+
+def _worker(rank, world, port, S, N, train, out_path):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, ROOT)
+    from fastfold_b200.parallel import init_dap, shutdown
+    from fastfold_b200.ops import _lib
+    init_dap(world, timeout_s=120)
+    out = _run(torch.device("cuda", rank), S, N, train)
+    torch.cuda.synchronize()
+    st = _lib.read_status()
+    if rank == 0:
+        torch.save({"out": out, "status": st}, out_path)
+    shutdown()
+
+
+@pytest.mark.parametrize("S,N,train", [(32, 64, False), (32, 72, False), (32, 64, True)])
+def test_two_ranks_match_one(S, N, train):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ref = _run(torch.device("cuda", 0), S, N, train)
+    with tempfile.TemporaryDirectory() as d:
+        out_path = os.path.join(d, "o.pt")
+        mp.spawn(_worker, args=(2, _free_port(), S, N, train, out_path), nprocs=2, join=True)
+        got = torch.load(out_path)
+    assert got["status"][0] == 0, got["status"]
+    for a, b in zip(got["out"], ref):
+        if b is None:
+            continue
+        err = (a - b).abs().mean().item()
+        scale = b.abs().mean().item() + 1e-6
+        assert err < 3e-2 * max(1.0, scale), "mean abs err %g (scale %g)" % (err, scale)
