@@ -1,6 +1,7 @@
 // Argument block of the tcgen05 GEMM launcher (mirrored field-for-field by the
 // ctypes structure in fastfold_b200/ops/_lib.py).
 #pragma once
+#include <cuda.h>
 
 enum GemmAct { ACT_NONE = 0, ACT_RELU = 1, ACT_SIGMOID = 2 };
 enum GemmOut { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2 };
@@ -27,4 +28,10 @@ struct GemmArgs {
   long long lddm;
   const void* resid;        // bf16 residual added last
   long long ldres, res_bstride;
+  int peer_slab;            // gathered-operand GEMMs: extent of one rank's slab along the gathered (M or N) dimension
+};
+
+// Tensor maps of the slabs of a gathered operand, one per rank of the DAP group (peer memory, plain TMA loads).
+struct PeerMaps {
+  CUtensorMap m[8];
 };

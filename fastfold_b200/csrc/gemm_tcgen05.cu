@@ -163,12 +163,16 @@ __device__ __forceinline__ void epi_store8(const float* v, const GemmArgs& g, in
 }
 
 // Persistent kernel: every CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
-template <int BN, bool A_MN, bool B_MN>
+// PEER: 0 = both operands local; 1 = the A operand is gathered along M, 2 = the B operand is gathered along N: the
+// slab of rank r lives in r's memory and its tiles are fetched with TMA straight over NVLink (all-gather fused into
+// the GEMM's load stage; the gathered operand is never materialised).
+template <int BN, bool A_MN, bool B_MN, int PEER>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                     const __grid_constant__ CUtensorMap tmB,
                                                                     const __grid_constant__ CUtensorMap tmC,
                                                                     const __grid_constant__ CUtensorMap tmMul,
                                                                     const __grid_constant__ CUtensorMap tmRes,
+                                                                    const __grid_constant__ PeerMaps pm,
                                                                     const GemmArgs g, int num_tiles, int tiles_m, int tiles_n, int tma_epi) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -237,18 +241,30 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
           const int k0 = kb * BK;
           const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
+          const CUtensorMap* mapA = &tmA;
+          const CUtensorMap* mapB = &tmB;
+          int am0 = tc.m0, bn0 = n0;
+          if (PEER == 1) {
+            const int r = tc.m0 / g.peer_slab;
+            mapA = &pm.m[r];
+            am0 = tc.m0 - r * g.peer_slab;
+          } else if (PEER == 2) {
+            const int r = n0 / g.peer_slab;
+            mapB = &pm.m[r];
+            bn0 = n0 - r * g.peer_slab;
+          }
           mbar_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * (BK * 128), &tmA, bar_full + 8 * s, tc.m0 + c * 64, k0, tc.batch * g.a_zmul);
+            for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * (BK * 128), mapA, bar_full + 8 * s, am0 + c * 64, k0, tc.batch * g.a_zmul);
           } else {
-            tma_load_3d(sa, &tmA, bar_full + 8 * s, k0, tc.m0, tc.batch * g.a_zmul);
+            tma_load_3d(sa, mapA, bar_full + 8 * s, k0, am0, tc.batch * g.a_zmul);
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * (BK * 128), &tmB, bar_full + 8 * s, n0 + c * 64, k0, tc.batch * g.b_zmul);
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * (BK * 128), mapB, bar_full + 8 * s, bn0 + c * 64, k0, tc.batch * g.b_zmul);
           } else {
-            tma_load_3d(sb, &tmB, bar_full + 8 * s, k0, n0, tc.batch * g.b_zmul);
+            tma_load_3d(sb, mapB, bar_full + 8 * s, k0, bn0, tc.batch * g.b_zmul);
           }
         }
       }
@@ -595,12 +611,14 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, long long rows, long long
   return encode_tmap3_bf16(map, base, cols, rows, batch > 0 ? batch : 1, ld, bstride, box_cols, box_rows, 128);
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int PEER = 0>
 static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap* epi, int tma_epi, const GemmArgs& g, int batch,
-                      cudaStream_t st) {
+                      cudaStream_t st, const PeerMaps* pm = nullptr) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set = false;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static PeerMaps no_peers;
+  if (!pm) pm = &no_peers;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, PEER>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return -2;
     attr_set = true;
@@ -615,7 +633,7 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   const int grid = (int)(num_tiles < sm_count ? num_tiles : sm_count);
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(ta, tb, epi[0], epi[1], epi[2], g, (int)num_tiles, tiles_m, tiles_n, tma_epi);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(ta, tb, epi[0], epi[1], epi[2], *pm, g, (int)num_tiles, tiles_m, tiles_n, tma_epi);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -634,17 +652,17 @@ static int launch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const
 
 using namespace ffb;
 
-extern "C" {
-
-// A: a_mn == 0 -> [batch][M][K] (ld = lda); a_mn == 1 -> [batch][K][M].
-// B: b_mn == 0 -> [batch][N][K] (ld = ldb); b_mn == 1 -> [batch][K][N].
-// A batch stride of 0 broadcasts the operand over the batch.
-int ffb_gemm_bf16(const void* A, const void* B, int a_mn, int b_mn, long long lda, long long ldb, long long a_bstride,
-                  long long b_bstride, int batch, int bn, GemmArgs* args, void* stream) {
+// Common front end of the two entry points.  peer_which: 0 none, 1 = A gathered (peer_ptrs = base of every rank's
+// A slab), 2 = B gathered.  For a gathered operand the pointer / strides describe ONE slab and M (or N) is the full
+// gathered extent.
+static int gemm_launch(const void* A, const void* B, int a_mn, int b_mn, long long lda, long long ldb, long long a_bstride,
+                       long long b_bstride, int batch, int bn, GemmArgs* args, void* stream, int peer_which, const void* const* peer_ptrs,
+                       int n_peers) {
   GemmArgs g = *args;
   if (g.M <= 0 || g.N <= 0 || g.K <= 0 || batch <= 0) return -10;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -11;
   if (g.glu && (g.N & 1)) return -12;
+  if (peer_which) bn = 128;
   if (bn == 0) {
     if (g.N > 128 && (long long)((g.M + 127) / 128) * ((g.N + 255) / 256) * batch * (g.splits > 0 ? g.splits : 1) >= 2 * 148) bn = 256;
     else if (g.N > 64) bn = 128;
@@ -663,12 +681,40 @@ int ffb_gemm_bf16(const void* A, const void* B, int a_mn, int b_mn, long long ld
   if ((a_bstride % 8) || (b_bstride % 8)) return -14;
   if ((a_mn || b_mn) && bn < 64) return -15;
   const int abatch = g.a_zmul ? batch : 1, bbatch = g.b_zmul ? batch : 1;
-  if (a_mn) r = make_tmap_bf16(&ta, A, g.K, g.M, lda, abatch, a_bstride, 64, BK);
-  else r = make_tmap_bf16(&ta, A, g.M, g.K, lda, abatch, a_bstride, BK, BM);
+  // extents of one slab of the gathered operand
+  int a_rows = g.M, b_rows = g.N;
+  if (peer_which) {
+    if (n_peers < 1 || n_peers > 8 || g.peer_slab <= 0) return -16;
+    if (peer_which == 1) {
+      if (g.peer_slab % BM || g.peer_slab * n_peers != g.M) return -17;
+      a_rows = g.peer_slab;
+    } else {
+      if (g.peer_slab % bn || g.peer_slab * n_peers != g.N) return -17;
+      b_rows = g.peer_slab;
+    }
+  }
+  if (a_mn) r = make_tmap_bf16(&ta, A, g.K, a_rows, lda, abatch, a_bstride, 64, BK);
+  else r = make_tmap_bf16(&ta, A, a_rows, g.K, lda, abatch, a_bstride, BK, BM);
   if (r) return 1000 + r;
-  if (b_mn) r = make_tmap_bf16(&tb, B, g.K, g.N, ldb, bbatch, b_bstride, 64, BK);
-  else r = make_tmap_bf16(&tb, B, g.N, g.K, ldb, bbatch, b_bstride, BK, bn);
+  if (b_mn) r = make_tmap_bf16(&tb, B, g.K, b_rows, ldb, bbatch, b_bstride, 64, BK);
+  else r = make_tmap_bf16(&tb, B, b_rows, g.K, ldb, bbatch, b_bstride, BK, bn);
   if (r) return 2000 + r;
+  PeerMaps pm;
+  if (peer_which) {
+    for (int p = 0; p < n_peers; ++p) {
+      const void* base = peer_ptrs[p];
+      if (reinterpret_cast<uintptr_t>(base) & 15) return -18;
+      if (peer_which == 1) {
+        if (a_mn) r = make_tmap_bf16(&pm.m[p], base, g.K, a_rows, lda, abatch, a_bstride, 64, BK);
+        else r = make_tmap_bf16(&pm.m[p], base, a_rows, g.K, lda, abatch, a_bstride, BK, BM);
+      } else {
+        if (b_mn) r = make_tmap_bf16(&pm.m[p], base, g.K, b_rows, ldb, bbatch, b_bstride, 64, BK);
+        else r = make_tmap_bf16(&pm.m[p], base, b_rows, g.K, ldb, bbatch, b_bstride, BK, bn);
+      }
+      if (r) return 3000 + r;
+    }
+    for (int p = n_peers; p < 8; ++p) pm.m[p] = pm.m[0];
+  }
   // TMA epilogue: bf16 row-major output whose rows (and those of mul / residual) are 16-byte aligned
   CUtensorMap epi[3];
   epi[0] = ta; epi[1] = ta; epi[2] = ta;
@@ -682,12 +728,41 @@ int ffb_gemm_bf16(const void* A, const void* B, int a_mn, int b_mn, long long ld
     if (tma_epi && g.resid && make_tmap_bf16(&epi[2], g.resid, g.M, g.N, g.ldres, batch, g.res_bstride, 64, 32)) tma_epi = 0;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (peer_which == 1) {
+    if (a_mn && b_mn) return launch_cfg<128, true, true, 1>(ta, tb, epi, tma_epi, g, batch, st, &pm);
+    return -19;
+  }
+  if (peer_which == 2) {
+    if (!a_mn && !b_mn) return launch_cfg<128, false, false, 2>(ta, tb, epi, tma_epi, g, batch, st, &pm);
+    if (a_mn && b_mn) return launch_cfg<128, true, true, 2>(ta, tb, epi, tma_epi, g, batch, st, &pm);
+    return -19;
+  }
   if (a_mn) {
     if (b_mn) return launch_bn<true, true>(bn, ta, tb, epi, tma_epi, g, batch, st);
     return launch_bn<true, false>(bn, ta, tb, epi, tma_epi, g, batch, st);
   }
   if (b_mn) return launch_bn<false, true>(bn, ta, tb, epi, tma_epi, g, batch, st);
   return launch_bn<false, false>(bn, ta, tb, epi, tma_epi, g, batch, st);
+}
+
+extern "C" {
+
+// A: a_mn == 0 -> [batch][M][K] (ld = lda); a_mn == 1 -> [batch][K][M].
+// B: b_mn == 0 -> [batch][N][K] (ld = ldb); b_mn == 1 -> [batch][K][N].
+// A batch stride of 0 broadcasts the operand over the batch.
+int ffb_gemm_bf16(const void* A, const void* B, int a_mn, int b_mn, long long lda, long long ldb, long long a_bstride,
+                  long long b_bstride, int batch, int bn, GemmArgs* args, void* stream) {
+  return gemm_launch(A, B, a_mn, b_mn, lda, ldb, a_bstride, b_bstride, batch, bn, args, stream, 0, nullptr, 0);
+}
+
+// All-gather fused into the GEMM: operand `peer_which` (1 = A along M, 2 = B along N) is the concatenation of
+// n_peers slabs of args->peer_slab rows each, slab p starting at peer_ptrs[p] (addresses of peer GPUs' memory as
+// mapped on this GPU; same strides for every slab).  The caller orders this launch behind the peers' writes.
+int ffb_gemm_bf16_peer(const void* A, const void* B, int a_mn, int b_mn, long long lda, long long ldb, long long a_bstride,
+                       long long b_bstride, int batch, GemmArgs* args, int peer_which, const void* const* peer_ptrs, int n_peers,
+                       void* stream) {
+  if (peer_which != 1 && peer_which != 2) return -20;
+  return gemm_launch(A, B, a_mn, b_mn, lda, ldb, a_bstride, b_bstride, batch, 128, args, stream, peer_which, peer_ptrs, n_peers);
 }
 
 // Reads and clears the device status word; out[0] != 0 means a kernel gave up

@@ -7,6 +7,7 @@ from ... import ops as K
 from ...parallel import core
 from ...parallel.comm import gather, scatter, row_to_col, col_to_row
 from ...parallel.comm_async import all_to_all_async, all_to_all_async_opp
+from ...parallel.fused import a2a_layer_norm
 from ...utils.checkpointing import checkpoint_blocks
 from .ops import (ChunkMSARowAttentionWithPairBias, ChunkMSAColumnGlobalAttention, ChunkTransition, GlobalAttention,
                   OutProductMean, SelfAttention, Transition, _fusable)
@@ -29,8 +30,9 @@ class MSAColumnAttention(nn.Module):
         self.layernormM = K.LayerNorm(d_node)
         self.attention = SelfAttention(qkv_dim=d_node, c=c, n_head=n_head, out_dim=d_node, gating=True)
 
-    def forward(self, M_raw, M_mask):
-        M = self.layernormM(M_raw.transpose(-2, -3).contiguous())
+    def forward(self, M_raw, M_mask, M_norm_t=None):
+        """``M_norm_t``: ``layernormM`` of the transposed input ``[1, N/P, S, c]`` when the caller already has it."""
+        M = self.layernormM(M_raw.transpose(-2, -3).contiguous()) if M_norm_t is None else M_norm_t
         out, _ = self.attention(M, M_mask.transpose(-1, -2).contiguous())
         return M_raw + out.transpose(-2, -3)
 
@@ -49,9 +51,10 @@ class MSACore(nn.Module):
     def forward(self, node, pair, node_mask, dropmask=None):
         node_mask_row = scatter(node_mask, dim=1)
         node = self.MSARowAttentionWithPairBias(node, pair, node_mask_row, dropmask)
-        node = row_to_col(node)
+        # row -> column switch fused with the transpose + LayerNorm of the column attention
+        node, node_nt = a2a_layer_norm(node, self.MSAColumnAttention.layernormM, 0, transpose_norm=True)
         node_mask_col = scatter(node_mask, dim=2)
-        node = self.MSAColumnAttention(node, node_mask_col)
+        node = self.MSAColumnAttention(node, node_mask_col, M_norm_t=node_nt)
         node = self.MSATransition(node)
         return node
 

@@ -366,19 +366,42 @@ class _TriangleMultiplication(nn.Module):
             p = _bmm_tn(lt, rt)                              # [c, i, j]
         return p.permute(1, 2, 0).unsqueeze(0)
 
-    def _fused_nograd(self, Z_raw, Z_mask, dropmask):
+    def _fused_nograd(self, Z_raw, Z_mask, dropmask, Z_norm=None):
         """Inference / checkpoint first pass: 7 kernels, no transposed copies."""
         c = self.c
         A, B = Z_raw.shape[1], Z_raw.shape[2]
-        Z = self.layernorm1(Z_raw)
+        Z = self.layernorm1(Z_raw) if Z_norm is None else Z_norm
         z2 = Z.reshape(A * B, -1)
         w, b = self._glu_weights()
-        lr_t = K.gemm(z2, w, bias=b, glu=True, rowscale=Z_mask.reshape(-1), trans_out=True)      # [2c, A*B]
+        P = core.get_dap_size()
+        heap = None
+        if P > 1:
+            from ...parallel import symm
+            heap = symm.get_heap("dap")
+            # the gathered operand's slab extent must be a whole number of 128-wide tiles
+            if heap is not None and ((A if self.outgoing else B) % 128 or (2 * c * A * B * 2) % 16):
+                heap = None
+        if heap is not None:
+            # All-gather fused into the contraction GEMM: the projection GEMM writes its (channel-major) result
+            # straight into a symmetric-heap slot; the contraction then reads every rank's slab of the gathered
+            # operand tile by tile through TMA over NVLink - no gathered copy exists anywhere.
+            slot = heap.next_ring_slot(2 * c * A * B * 2)
+            heap.slot_fence(slot, pre=True)
+            lr_t = K.gemm(z2, w, bias=b, glu=True, rowscale=Z_mask.reshape(-1), trans_out=True, out=heap.view(slot, (2 * c, A * B), Z.dtype))
+            heap.slot_fence(slot, pre=False)
+        else:
+            lr_t = K.gemm(z2, w, bias=b, glu=True, rowscale=Z_mask.reshape(-1), trans_out=True)      # [2c, A*B]
         left_t = lr_t[:c].reshape(c, A, B)
         right_t = lr_t[c:].reshape(c, A, B)
         g = K.gemm(z2, self.output_gate.weight, bias=self.output_gate.bias, act="sigmoid")
-        P = core.get_dap_size()
-        if self.outgoing:
+        if heap is not None:
+            heap.consume_fence(slot, pre=True)
+            if self.outgoing:      # right operand [c, j, k] gathered along j (the GEMM's N extent)
+                p = K.gemm(left_t, right_t, peer=("b", heap.peer_addresses(slot, c * A * B * 2)))
+            else:                  # left operand [c, k, i] gathered along i (the GEMM's M extent)
+                p = K.gemm(left_t, right_t, a_mn=True, b_mn=True, peer=("a", heap.peer_addresses(slot, 0)))
+            heap.consume_fence(slot, pre=False)
+        elif self.outgoing:
             if P > 1:
                 right_t = comm._gather(right_t.contiguous(), dim=1)                             # [c, N, k]
             p = K.gemm(left_t, right_t)                                                        # [c, i, j]
@@ -435,7 +458,8 @@ class _TriangleMultiplication(nn.Module):
             pending = nxt
         return out
 
-    def forward(self, Z_raw, Z_mask, dropmask=None):
+    def forward(self, Z_raw, Z_mask, dropmask=None, Z_norm=None):
+        """``Z_norm``: ``layernorm1(Z_raw)`` when the caller already has it (fused all-to-all + LayerNorm)."""
         training = self.training
         if dropmask is None and training and self.p_drop > 0:
             dropmask = F.dropout(torch.ones_like(Z_raw[:, 0:1, :, :]), p=self.p_drop, training=True)
@@ -445,9 +469,9 @@ class _TriangleMultiplication(nn.Module):
             return self._chunked(Z_raw, Z_mask)
         can_fuse = _fusable(Z_raw) and (Z_raw.shape[1] * Z_raw.shape[2]) % 8 == 0 and Z_raw.shape[1] % 8 == 0 and Z_raw.shape[2] % 8 == 0
         if can_fuse:
-            return self._fused_nograd(Z_raw, Z_mask, dropmask)
+            return self._fused_nograd(Z_raw, Z_mask, dropmask, Z_norm)
         c = self.c
-        Z = self.layernorm1(Z_raw)
+        Z = self.layernorm1(Z_raw) if Z_norm is None else Z_norm
         proj = K.glu_mask(self.left_right_projection(Z), self.left_right_gate(Z), Z_mask)
         left, right = proj[..., :c], proj[..., c:]
         if self.outgoing:
@@ -519,19 +543,24 @@ class _TriangleAttention(nn.Module):
         self.attention = SelfAttention(qkv_dim=d_pair, c=c, n_head=n_head, out_dim=d_pair, gating=True, last_bias_fuse=True)
         self.out_bias = nn.Parameter(torch.zeros((d_pair,)))
 
-    def forward(self, Z_raw, Z_mask, dropmask=None):
+    def forward(self, Z_raw, Z_mask, dropmask=None, Z_norm=None):
+        """``Z_norm``: the normalised input in the layout the attention runs in (for the ending node: transposed),
+        when the caller already has it from the fused all-to-all + LayerNorm."""
         training = self.training
         if self.starting:
-            Zin, mask = Z_raw, Z_mask
+            mask = Z_mask
             if dropmask is None and training and self.p_drop > 0:
                 dropmask = F.dropout(torch.ones_like(Z_raw[:, 0:1, :, :]), p=self.p_drop, training=True)
         else:
-            Zin, mask = Z_raw.transpose(-2, -3).contiguous(), Z_mask.transpose(-1, -2).contiguous()
+            mask = Z_mask.transpose(-1, -2).contiguous()
             if dropmask is None and training and self.p_drop > 0:
                 dropmask = F.dropout(torch.ones_like(Z_raw[:, :, 0:1, :]), p=self.p_drop, training=True)
         if not training:
             dropmask = None
-        Z = self.layernorm1(Zin)
+        if Z_norm is not None:
+            Z = Z_norm
+        else:
+            Z = self.layernorm1(Z_raw if self.starting else Z_raw.transpose(-2, -3).contiguous())
         b = self.linear_b(Z)
         b, work = gather_async(b, dim=1)
         tail = None

@@ -2,6 +2,7 @@
 import torch.nn as nn
 
 from ...parallel.comm import scatter, row_to_col, col_to_row
+from ...parallel.fused import a2a_layer_norm
 from .ops import (AsyncChunkTriangleMultiplicationOutgoing, AsyncChunkTriangleMultiplicationIncoming,
                   ChunkTriangleAttentionStartingNode, ChunkTriangleAttentionEndingNode, ChunkTransition)
 
@@ -49,16 +50,17 @@ class PairCore(nn.Module):
         d = _drop or {}
         pair_mask_row = scatter(pair_mask, dim=1)
         pair_mask_col = scatter(pair_mask, dim=2)
+        # each axis switch is fused with the LayerNorm (and transpose) of the module that consumes its result
         pair = self.TriangleMultiplicationOutgoing(pair, pair_mask_row, d.get("tri_mul_out"))
-        pair = row_to_col(pair)
+        pair, pn = a2a_layer_norm(pair, self.TriangleMultiplicationIncoming.layernorm1, 0)
         dm = d.get("tri_mul_in")
         if dm is not None:
             dm = scatter(dm, dim=2)
-        pair = self.TriangleMultiplicationIncoming(pair, pair_mask_col, dm)
-        pair = col_to_row(pair)
-        pair = self.TriangleAttentionStartingNode(pair, pair_mask_row, d.get("tri_att_start"))
-        pair = row_to_col(pair)
-        pair = self.TriangleAttentionEndingNode(pair, pair_mask_col, d.get("tri_att_end"))
+        pair = self.TriangleMultiplicationIncoming(pair, pair_mask_col, dm, Z_norm=pn)
+        pair, pn = a2a_layer_norm(pair, self.TriangleAttentionStartingNode.layernorm1, 1)
+        pair = self.TriangleAttentionStartingNode(pair, pair_mask_row, d.get("tri_att_start"), Z_norm=pn)
+        pair, pn = a2a_layer_norm(pair, self.TriangleAttentionEndingNode.layernorm1, 0, transpose_norm=True)
+        pair = self.TriangleAttentionEndingNode(pair, pair_mask_col, d.get("tri_att_end"), Z_norm=pn)
         pair = self.PairTransition(pair)
         pair = col_to_row(pair)
         return pair

@@ -40,6 +40,7 @@ class GemmArgs(ctypes.Structure):
         ("mul", c_void_p), ("ldmul", c_ll), ("mul_bstride", c_ll),
         ("dmask", c_void_p), ("lddm", c_ll),
         ("resid", c_void_p), ("ldres", c_ll), ("res_bstride", c_ll),
+        ("peer_slab", c_int),
     ]
 
 
@@ -47,6 +48,7 @@ def _declare(lib):
     P, I, L, F = c_void_p, c_int, c_ll, c_float
     sig = {
         "ffb_gemm_bf16": [P, P, I, I, L, L, L, L, I, I, ctypes.POINTER(GemmArgs), P],
+        "ffb_gemm_bf16_peer": [P, P, I, I, L, L, L, L, I, ctypes.POINTER(GemmArgs), I, ctypes.POINTER(c_void_p), I, P],
         "ffb_read_status": [ctypes.POINTER(c_int), I],
         "ffb_attention_fwd": [P, P, P, L, L, L, L, P, P, L, P, L, L, P, I, I, I, I, I, F, P],
         "ffb_attention_bwd": [P, P, P, L, L, L, L, P, P, L, P, P, P, P, P, I, I, I, I, I, F, P],

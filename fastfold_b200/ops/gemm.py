@@ -53,7 +53,7 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, gl
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=False, rowscale=None, mul=None,
-         dmask=None, resid=None, trans_out=False, out=None, out_dtype=None, splits=1, accumulate=False, bn=0):
+         dmask=None, resid=None, trans_out=False, out=None, out_dtype=None, splits=1, accumulate=False, bn=0, peer=None):
     """``C = epilogue(alpha * A @ B^T)`` with A ``[.., M, K]`` and B ``[.., N, K]``.
 
     ``a_mn`` / ``b_mn``: the operand is stored with the contraction index
@@ -63,6 +63,9 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
     ``accumulate=True`` adds into an fp32 ``out`` with atomics (allows ``splits > 1``).
     A leading batch dimension may be present on either operand (a 2-D operand is
     shared by all batches).
+    ``peer=("a" | "b", [address of every rank's slab])``: that operand is the concatenation, along its M / N extent,
+    of one equally shaped slab per rank; the tensor passed in is this rank's slab (it supplies shape and strides)
+    and the kernel fetches every slab's tiles from the given addresses - peer GPUs' memory - with TMA.
     """
     if not a.is_cuda:
         r = gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, alpha=alpha, bias=bias, act=act, glu=glu, rowscale=rowscale, mul=mul,
@@ -95,6 +98,13 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
     else:
         N, Kb = b3.shape[1], b3.shape[2]
     assert K == Kb, "contraction extents differ: %d vs %d" % (K, Kb)
+    peer_slab = 0
+    if peer is not None:
+        which, addrs = peer
+        if which == "a":
+            peer_slab, M = M, M * len(addrs)
+        else:
+            peer_slab, N = N, N * len(addrs)
     n_out = N // 2 if glu else N
     batched = a.dim() == 3 or b.dim() == 3
     oshape = (n_out, M) if trans_out else (M, n_out)
@@ -152,6 +162,16 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
         g.resid = resid.data_ptr()
         g.ldres = resid.stride(-2)
         g.res_bstride = resid.stride(0) if (batched and resid.dim() == 3) else 0
+    if peer is not None:
+        import ctypes
+        which, addrs = peer
+        g.peer_slab = peer_slab
+        arr = (ctypes.c_void_p * len(addrs))(*[int(x) for x in addrs])
+        rc = lib.ffb_gemm_bf16_peer(_lib.ptr(a3), _lib.ptr(b3), 1 if a_mn else 0, 1 if b_mn else 0, a3.stride(1), b3.stride(1),
+                                    a3.stride(0) if a.dim() == 3 else 0, b3.stride(0) if b.dim() == 3 else 0, batch, g,
+                                    1 if which == "a" else 2, arr, len(addrs), _lib.stream_ptr())
+        _lib.check(rc, "ffb_gemm_bf16_peer(M=%d,N=%d,K=%d,batch=%d,slab=%d)" % (M, N, K, batch, peer_slab))
+        return out
     rc = lib.ffb_gemm_bf16(_lib.ptr(a3), _lib.ptr(b3), 1 if a_mn else 0, 1 if b_mn else 0, a3.stride(1), b3.stride(1),
                            a3.stride(0) if a.dim() == 3 else 0, b3.stride(0) if b.dim() == 3 else 0, batch, bn, g,
                            _lib.stream_ptr())

@@ -190,6 +190,21 @@ class SymmHeap:
         _lib.check(_libc().ffb_symm_allreduce_bf16(ctypes.byref(self.ctx), s.index, s.offset, n_elems, float(scale), _lib.stream_ptr()),
                    "symm_allreduce_bf16")
 
+    # -- producer / consumer fences for kernels that write or read a slot themselves ----------------------
+    def slot_fence(self, slot, pre):
+        """``pre=True`` (before the producer kernel): wait until every peer has finished with the slot's previous
+        contents.  ``pre=False`` (after it): raise this rank's ready flag on every peer."""
+        _lib.check(_libc().ffb_symm_slot_fence(ctypes.byref(self.ctx), slot.index, 1 if pre else 0, _lib.stream_ptr()), "symm_slot_fence")
+
+    def consume_fence(self, slot, pre):
+        """``pre=True`` (before a kernel that reads peers' slots): wait for every peer's ready flag.  ``pre=False``
+        (after it): raise this rank's done flag on every peer and advance the slot's epoch."""
+        _lib.check(_libc().ffb_symm_consume_fence(ctypes.byref(self.ctx), slot.index, 1 if pre else 0, _lib.stream_ptr()), "symm_consume_fence")
+
+    def peer_addresses(self, slot, byte_offset=0):
+        """Address of ``slot`` (+ offset) in every rank's slab, as mapped on this GPU."""
+        return [int(self.ctx.heap[r]) + slot.offset + byte_offset for r in range(self.world)]
+
     def wait_never(self, slot):
         """Test hook: a kernel waits for a flag nobody raises; returns after the heap's wait limit with status 4."""
         _lib.check(_libc().ffb_symm_wait_never(ctypes.byref(self.ctx), slot.index, _lib.stream_ptr()), "symm_wait_never")

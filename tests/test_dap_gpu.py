@@ -71,7 +71,7 @@ def _worker(rank, world, port, S, N, train, out_path):
     shutdown()
 
 
-@pytest.mark.parametrize("S,N,train", [(32, 64, False), (32, 72, False), (32, 64, True)])
+@pytest.mark.parametrize("S,N,train", [(32, 64, False), (32, 72, False), (32, 64, True), (16, 256, False), (16, 256, True)])
 def test_two_ranks_match_one(S, N, train):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
