@@ -40,6 +40,15 @@ with open(_DATA) as _fh:
             globals()[_name] = _decode(_val)
 del _fh, _name, _val
 
+# lower-case aliases of the index tables
+restype_atom14_to_atom37 = RESTYPE_ATOM14_TO_ATOM37
+restype_atom37_to_atom14 = RESTYPE_ATOM37_TO_ATOM14
+restype_atom14_is_ambiguous = RESTYPE_ATOM14_IS_AMBIGUOUS
+restype_rigidgroup_base_atom37_idx = RESTYPE_RIGIDGROUP_BASE_ATOM37_IDX
+restype_rigidgroup_mask = RESTYPE_RIGIDGROUP_MASK
+renaming_matrices = RENAMING_MATRICES
+chi_atom_indices = CHI_ATOM_INDICES
+
 # Distance from one CA to next CA [trans configuration: omega = 180].
 ca_ca = 3.80209737096
 

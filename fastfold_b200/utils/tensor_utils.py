@@ -96,12 +96,10 @@ def chunk_layer(layer, inputs, chunk_size, no_batch_dims):
     orig_batch_dims = tuple(max(s) for s in zip(*initial_dims))
 
     def prep(t):
+        # inputs whose batch dims are all 1 (e.g. a bias shared by every row) stay un-expanded and are not sliced
         if not sum(t.shape[:no_batch_dims]) == no_batch_dims:
             t = t.expand(orig_batch_dims + t.shape[no_batch_dims:])
-            t = t.reshape(-1, *t.shape[no_batch_dims:])
-        else:
-            t = t.expand(orig_batch_dims + t.shape[no_batch_dims:])
-        return t
+        return t.reshape(-1, *t.shape[no_batch_dims:])
 
     prepped = tensor_tree_map(prep, inputs)
     flat_batch_dim = 1
