@@ -1,0 +1,84 @@
+"""``fastfold`` import names on top of ``fastfold_b200``.
+
+Programs written against the reference package keep working unchanged::
+
+    from fastfold.distributed import init_dap
+    from fastfold.model.fastnn import Evoformer, set_chunk_size
+    from fastfold.model.hub import AlphaFold
+    from fastfold.utils.inject_fastnn import inject_fastnn      # or: from fastfold.utils import inject_fastnn
+    from fastfold.utils.import_weights import import_jax_weights_
+    from fastfold.config import model_config
+
+Every name resolves to the module of ``fastfold_b200`` that implements it (no code lives here).
+"""
+import importlib
+import sys
+
+VERSION = "0.2.0-b200"
+
+_ALIASES = {
+    "fastfold.config": "fastfold_b200.config",
+    "fastfold.common": "fastfold_b200.common",
+    "fastfold.common.residue_constants": "fastfold_b200.common.residue_constants",
+    "fastfold.common.protein": "fastfold_b200.common.protein",
+    "fastfold.distributed": "fastfold_b200.parallel",
+    "fastfold.distributed.core": "fastfold_b200.parallel.core",
+    "fastfold.distributed.comm": "fastfold_b200.parallel.comm",
+    "fastfold.distributed.comm_async": "fastfold_b200.parallel.comm_async",
+    "fastfold.model": "fastfold_b200.models",
+    "fastfold.model.fastnn": "fastfold_b200.models.fastnn",
+    "fastfold.model.fastnn.ops": "fastfold_b200.models.fastnn.ops",
+    "fastfold.model.fastnn.msa": "fastfold_b200.models.fastnn.msa",
+    "fastfold.model.fastnn.triangle": "fastfold_b200.models.fastnn.triangle",
+    "fastfold.model.fastnn.evoformer": "fastfold_b200.models.fastnn.evoformer",
+    "fastfold.model.fastnn.kernel": "fastfold_b200.ops.compat",
+    "fastfold.model.nn": "fastfold_b200.models.nn",
+    "fastfold.model.nn.primitives": "fastfold_b200.models.nn.primitives",
+    "fastfold.model.nn.evoformer": "fastfold_b200.models.nn.evoformer",
+    "fastfold.model.nn.structure_module": "fastfold_b200.models.nn.structure_module",
+    "fastfold.model.nn.heads": "fastfold_b200.models.nn.heads",
+    "fastfold.model.nn.embedders": "fastfold_b200.models.nn.embedders",
+    "fastfold.model.nn.template": "fastfold_b200.models.nn.template",
+    "fastfold.model.hub": "fastfold_b200.models.hub",
+    "fastfold.model.hub.alphafold": "fastfold_b200.models.hub.alphafold",
+    "fastfold.model.hub.loss": "fastfold_b200.models.hub.loss",
+    "fastfold.model.hub.lr_scheduler": "fastfold_b200.models.hub.lr_scheduler",
+    "fastfold.utils": "fastfold_b200.utils",
+    "fastfold.utils.inject_fastnn": "fastfold_b200.utils.inject_fastnn",
+    "fastfold.utils.import_weights": "fastfold_b200.utils.import_weights",
+    "fastfold.utils.rigid_utils": "fastfold_b200.utils.rigid_utils",
+    "fastfold.utils.feats": "fastfold_b200.utils.feats",
+    "fastfold.utils.tensor_utils": "fastfold_b200.utils.tensor_utils",
+    "fastfold.utils.checkpointing": "fastfold_b200.utils.checkpointing",
+    "fastfold.utils.validation_utils": "fastfold_b200.utils.validation_utils",
+    "fastfold.data": "fastfold_b200.data",
+    "fastfold.data.data_pipeline": "fastfold_b200.data.data_pipeline",
+    "fastfold.data.data_transforms": "fastfold_b200.data.data_transforms",
+    "fastfold.data.parsers": "fastfold_b200.data.parsers",
+}
+
+
+class _AliasFinder:
+    """Import hook: ``fastfold.x.y`` -> the aliased ``fastfold_b200`` module object."""
+
+    @staticmethod
+    def find_spec(name, path=None, target=None):
+        if name in _ALIASES:
+            from importlib.machinery import ModuleSpec
+            return ModuleSpec(name, _AliasLoader(), is_package=True)
+        return None
+
+
+class _AliasLoader:
+    @staticmethod
+    def create_module(spec):
+        mod = importlib.import_module(_ALIASES[spec.name])
+        return mod
+
+    @staticmethod
+    def exec_module(module):
+        pass
+
+
+if not any(isinstance(f, type) and f.__name__ == "_AliasFinder" for f in sys.meta_path):
+    sys.meta_path.insert(0, _AliasFinder)

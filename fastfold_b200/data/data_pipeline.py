@@ -1,0 +1,164 @@
+"""From a FASTA file (+ a directory of alignments) to the raw numpy feature dict, and on to model tensors.
+
+``DataPipeline.process_fasta(fasta_path, alignment_dir)`` reads whatever alignments exist in ``alignment_dir``
+(``*.a3m`` / ``*.sto`` as written by jackhmmer / hhblits; none -> single-sequence mode) and produces sequence + MSA
+features; ``FeaturePipeline.process_features(raw, mode)`` applies the tensor transforms (MSA sampling, clustering,
+masking, ``msa_feat``) once per recycling iteration and stacks the iterations on the LAST axis.  Alignment tools
+are run by ``AlignmentRunner`` (subprocess wrappers in ``data/tools.py``) when their binaries exist.  Templates from
+HHR hits need mmCIF files and are produced by ``data/templates.py`` when available; otherwise template features
+are empty.  Same roles as fastfold/data/data_pipeline.py, feature_pipeline.py and input_pipeline.py.
+"""
+import copy
+import os
+from typing import Mapping, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..common import residue_constants as rc
+from . import data_transforms as dt
+from . import parsers
+
+FeatureDict = Mapping[str, np.ndarray]
+
+
+def make_sequence_features(sequence: str, description: str, num_res: int) -> FeatureDict:
+    return {
+        "aatype": rc.sequence_to_onehot(sequence, rc.restype_order_with_x, map_unknown_to_x=True),
+        "between_segment_residues": np.zeros((num_res,), dtype=np.int32),
+        "domain_name": np.array([description.encode("utf-8")], dtype=object),
+        "residue_index": np.array(range(num_res), dtype=np.int32),
+        "seq_length": np.array([num_res] * num_res, dtype=np.int32),
+        "sequence": np.array([sequence.encode("utf-8")], dtype=object),
+    }
+
+
+def make_msa_features(msas: Sequence[Sequence[str]], deletion_matrices: Sequence[parsers.DeletionMatrix]) -> FeatureDict:
+    if not msas:
+        raise ValueError("At least one MSA must be provided.")
+    int_msa, deletion_matrix, seen = [], [], set()
+    for msa, dels in zip(msas, deletion_matrices):
+        for seq, d in zip(msa, dels):
+            if seq in seen:
+                continue
+            seen.add(seq)
+            int_msa.append([rc.HHBLITS_AA_TO_ID[r] for r in seq])
+            deletion_matrix.append(d)
+    num_res = len(msas[0][0])
+    return {"deletion_matrix_int": np.array(deletion_matrix, dtype=np.int32), "msa": np.array(int_msa, dtype=np.int32),
+            "num_alignments": np.array([len(int_msa)] * num_res, dtype=np.int32)}
+
+
+def empty_template_features(num_res: int) -> FeatureDict:
+    return {"template_aatype": np.zeros((0, num_res, 22), np.float32), "template_all_atom_masks": np.zeros((0, num_res, 37), np.float32),
+            "template_all_atom_positions": np.zeros((0, num_res, 37, 3), np.float32), "template_domain_names": np.zeros((0,), object),
+            "template_sequence": np.zeros((0,), object), "template_sum_probs": np.zeros((0, 1), np.float32)}
+
+
+class DataPipeline:
+    def __init__(self, template_featurizer=None):
+        self.template_featurizer = template_featurizer
+
+    @staticmethod
+    def _read_alignments(alignment_dir, query):
+        msas, dels = [], []
+        if alignment_dir and os.path.isdir(alignment_dir):
+            for f in sorted(os.listdir(alignment_dir)):
+                path = os.path.join(alignment_dir, f)
+                if f.endswith(".a3m"):
+                    m, d, _ = parsers.parse_a3m(open(path).read())
+                elif f.endswith(".sto"):
+                    m, d, _ = parsers.parse_stockholm(open(path).read())
+                else:
+                    continue
+                if m and len(m[0]) == len(query):
+                    msas.append(m)
+                    dels.append(d)
+        if not msas:      # single-sequence mode
+            msas, dels = [[query]], [[[0] * len(query)]]
+        return msas, dels
+
+    def process_fasta(self, fasta_path: str, alignment_dir: Optional[str] = None) -> FeatureDict:
+        seqs, descs = parsers.parse_fasta(open(fasta_path).read())
+        if len(seqs) != 1:
+            raise ValueError("More than one input sequence found in %s." % fasta_path)
+        return self.process_sequence(seqs[0], descs[0], alignment_dir)
+
+    def process_sequence(self, sequence, description="query", alignment_dir=None) -> FeatureDict:
+        n = len(sequence)
+        feats = dict(make_sequence_features(sequence, description, n))
+        msas, dels = self._read_alignments(alignment_dir, sequence)
+        feats.update(make_msa_features(msas, dels))
+        templ = None
+        if self.template_featurizer is not None and alignment_dir:
+            hhr = os.path.join(alignment_dir, "pdb70_hits.hhr")
+            if os.path.exists(hhr):
+                templ = self.template_featurizer.get_templates(sequence, parsers.parse_hhr(open(hhr).read())).features
+        feats.update(templ if templ is not None else empty_template_features(n))
+        return feats
+
+
+def np_to_tensor_dict(np_example, features):
+    return {k: torch.tensor(np.asarray(v)) for k, v in np_example.items() if k in features and np.asarray(v).dtype != object}
+
+
+def _nonensembled(cfg_common, cfg_mode):
+    t = [dt.cast_to_64bit_ints, dt.correct_msa_restypes, dt.squeeze_features, dt.randomly_replace_msa_with_unknown(0.0), dt.make_seq_mask,
+         dt.make_msa_mask, dt.make_hhblits_profile]
+    t.append(dt.make_atom14_masks)
+    if cfg_mode.supervised:
+        t += [dt.make_atom14_positions, dt.atom37_to_frames, dt.atom37_to_torsion_angles(""), dt.make_pseudo_beta(""), dt.get_backbone_frames,
+              dt.get_chi_angles]
+    return t
+
+
+def _ensembled(cfg_common, cfg_mode, seed):
+    max_msa = cfg_mode.max_msa_clusters
+    t = [dt.sample_msa(max_msa, keep_extra=True, seed=seed)]
+    if "masked_msa" in cfg_common:
+        t.append(dt.make_masked_msa(cfg_common.masked_msa, cfg_mode.masked_msa_replace_fraction))
+    if cfg_common.msa_cluster_features:
+        t += [dt.nearest_neighbor_clusters(), dt.summarize_clusters]
+    t.append(dt.crop_extra_msa(cfg_mode.max_extra_msa) if cfg_mode.max_extra_msa else dt.delete_extra_msa)
+    t.append(dt.make_msa_feat)
+    return t
+
+
+class FeaturePipeline:
+    def __init__(self, config):
+        self.config = config      # the ``data`` sub-tree of ``model_config``
+
+    def process_features(self, raw_features: FeatureDict, mode: str = "predict", seed: int = 0):
+        cfg = copy.deepcopy(self.config)
+        mode_cfg = cfg[mode]
+        raw = dict(raw_features)
+        num_res = int(np.asarray(raw["seq_length"]).reshape(-1)[0])
+        if "deletion_matrix_int" in raw:
+            raw["deletion_matrix"] = np.asarray(raw.pop("deletion_matrix_int")).astype(np.float32)
+        names = list(cfg.common.unsupervised_features) + ["deletion_matrix"]
+        if mode_cfg.supervised:
+            names += list(cfg.supervised.supervised_features)
+        tensors = np_to_tensor_dict(raw, names)
+        for fn in _nonensembled(cfg.common, mode_cfg):
+            tensors = fn(tensors)
+        n_iter = cfg.common.max_recycling_iters + 1
+        keep = [k for k in cfg.common.feat.keys() if not k.startswith("template_")]
+        per_iter = []
+        for it in range(n_iter):
+            d = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in tensors.items()}
+            s = seed + it if cfg.common.resample_msa_in_recycling else seed
+            torch.manual_seed(s)
+            for fn in _ensembled(cfg.common, mode_cfg, s):
+                d = fn(d)
+            d["seq_length"] = torch.tensor(num_res)
+            if mode_cfg.crop and mode_cfg.crop_size:
+                schema = {k: v for k, v in cfg.common.feat.items()}
+                d = dt.random_crop_to_size(mode_cfg.crop_size, mode_cfg.max_templates, schema, mode_cfg.subsample_templates, seed=seed)(d)
+            d = {k: v for k, v in d.items() if k in keep}
+            if mode_cfg.fixed_size:
+                nres = mode_cfg.crop_size if (mode_cfg.crop and mode_cfg.crop_size) else num_res
+                schema = {k: cfg.common.feat[k] for k in d}
+                d = dt.make_fixed_size(schema, mode_cfg.max_msa_clusters, mode_cfg.max_extra_msa, nres, 0)(d)
+            per_iter.append(d)
+        out = {k: torch.stack([d[k] for d in per_iter], dim=-1) for k in per_iter[0]}
+        return out

@@ -171,3 +171,261 @@ def get_chi_angles(protein):
     protein["chi_angles_sin_cos"] = protein["torsion_angles_sin_cos"][..., 3:, :].to(dtype)
     protein["chi_mask"] = protein["torsion_angles_mask"][..., 3:].to(dtype)
     return protein
+
+
+# ---------------------------------------------------------------------------
+# Part 2: sequence / MSA features
+# ---------------------------------------------------------------------------
+def cast_to_64bit_ints(protein):
+    for k, v in protein.items():
+        if v.dtype == torch.int32:
+            protein[k] = v.type(torch.int64)
+    return protein
+
+
+def make_one_hot(x, num_classes):
+    return torch.nn.functional.one_hot(x.long(), num_classes).float()
+
+
+def make_seq_mask(protein):
+    protein["seq_mask"] = torch.ones(protein["aatype"].shape, dtype=torch.float32)
+    return protein
+
+
+def make_template_mask(protein):
+    protein["template_mask"] = torch.ones(protein["template_aatype"].shape[0], dtype=torch.float32)
+    return protein
+
+
+def correct_msa_restypes(protein):
+    """HHblits residue ids (alphabetical with gap) -> this package's residue order."""
+    perm = torch.tensor(list(rc.MAP_HHBLITS_AATYPE_TO_OUR_AATYPE), dtype=torch.long)
+    protein["msa"] = perm[protein["msa"].long()]
+    return protein
+
+
+def squeeze_features(protein):
+    """One-hot aatype -> indices; drops the singleton dims the raw numpy features carry."""
+    if protein["aatype"].dim() == 2:
+        protein["aatype"] = torch.argmax(protein["aatype"], dim=-1)
+    for k in ["domain_name", "msa", "num_alignments", "seq_length", "sequence", "superfamily", "deletion_matrix", "resolution",
+              "between_segment_residues", "residue_index", "template_all_atom_mask"]:
+        if k in protein and isinstance(protein[k], torch.Tensor) and protein[k].dim() > 0 and protein[k].shape[-1] == 1 and k not in ("msa", "deletion_matrix"):
+            protein[k] = protein[k].squeeze(-1)
+    for k in ["seq_length", "num_alignments"]:
+        if k in protein and protein[k].dim() > 0:
+            protein[k] = protein[k][0]
+    return protein
+
+
+@curry1
+def randomly_replace_msa_with_unknown(protein, replace_proportion):
+    msa_mask = torch.rand(protein["msa"].shape) < replace_proportion
+    x_idx, gap_idx = 20, 21
+    msa_mask = torch.logical_and(msa_mask, protein["msa"] != gap_idx)
+    protein["msa"] = torch.where(msa_mask, torch.ones_like(protein["msa"]) * x_idx, protein["msa"])
+    aatype_mask = torch.rand(protein["aatype"].shape) < replace_proportion
+    protein["aatype"] = torch.where(aatype_mask, torch.ones_like(protein["aatype"]) * x_idx, protein["aatype"])
+    return protein
+
+
+@curry1
+def sample_msa(protein, max_seq, keep_extra, seed=None):
+    """Keeps the query plus a random subset of ``max_seq - 1`` other rows; the rest becomes the extra MSA."""
+    num_seq = protein["msa"].shape[0]
+    g = torch.Generator()
+    if seed is not None:
+        g.manual_seed(seed)
+    else:
+        g.seed()
+    shuffled = torch.randperm(num_seq - 1, generator=g) + 1
+    index_order = torch.cat((torch.tensor([0]), shuffled), dim=0)
+    num_sel = min(max_seq, num_seq)
+    sel_seq, not_sel_seq = torch.split(index_order, [num_sel, num_seq - num_sel])
+    for k in MSA_FEATURE_NAMES:
+        if k in protein:
+            if keep_extra:
+                protein["extra_" + k] = torch.index_select(protein[k], 0, not_sel_seq)
+            protein[k] = torch.index_select(protein[k], 0, sel_seq)
+    return protein
+
+
+@curry1
+def crop_extra_msa(protein, max_extra_msa):
+    num_seq = protein["extra_msa"].shape[0]
+    num_sel = min(max_extra_msa, num_seq)
+    select_indices = torch.randperm(num_seq)[:num_sel]
+    for k in MSA_FEATURE_NAMES:
+        if "extra_" + k in protein:
+            protein["extra_" + k] = torch.index_select(protein["extra_" + k], 0, select_indices)
+    return protein
+
+
+def delete_extra_msa(protein):
+    for k in MSA_FEATURE_NAMES:
+        protein.pop("extra_" + k, None)
+    return protein
+
+
+def make_msa_mask(protein):
+    protein["msa_mask"] = torch.ones(protein["msa"].shape, dtype=torch.float32)
+    protein["msa_row_mask"] = torch.ones(protein["msa"].shape[0], dtype=torch.float32)
+    return protein
+
+
+def make_hhblits_profile(protein):
+    if "hhblits_profile" not in protein:
+        protein["hhblits_profile"] = torch.mean(make_one_hot(protein["msa"], 22), dim=0)
+    return protein
+
+
+@curry1
+def make_masked_msa(protein, config, replace_fraction):
+    """BERT-style corruption: a fraction of positions is replaced by a draw from uniform / profile / same / mask token."""
+    random_aa = torch.tensor([0.05] * 20 + [0.0, 0.0], dtype=torch.float32)
+    categorical_probs = (config.uniform_prob * random_aa + config.profile_prob * protein["hhblits_profile"] +
+                         config.same_prob * make_one_hot(protein["msa"], 22))
+    pad_shapes = list(reduce(add, [(0, 0) for _ in range(len(categorical_probs.shape))]))
+    pad_shapes[1] = 1
+    mask_prob = 1.0 - config.profile_prob - config.same_prob - config.uniform_prob
+    assert mask_prob >= 0.0
+    categorical_probs = torch.nn.functional.pad(categorical_probs, pad_shapes, value=mask_prob)
+    sh = protein["msa"].shape
+    mask_position = torch.rand(sh) < replace_fraction
+    counts = categorical_probs.reshape(-1, categorical_probs.shape[-1])
+    bert_msa = torch.multinomial(counts + 1e-9, 1).reshape(sh)
+    bert_msa = torch.where(mask_position, bert_msa, protein["msa"])
+    protein["bert_mask"] = mask_position.to(torch.float32)
+    protein["true_msa"] = protein["msa"]
+    protein["msa"] = bert_msa
+    return protein
+
+
+@curry1
+def nearest_neighbor_clusters(protein, gap_agreement_weight=0.0):
+    """Assigns every extra sequence to the closest kept (cluster-centre) sequence by residue agreement."""
+    weights = torch.cat([torch.ones(21), gap_agreement_weight * torch.ones(1), torch.zeros(1)], 0)
+    msa_one_hot = make_one_hot(protein["msa"], 23)
+    sample_one_hot = protein["msa_mask"][:, :, None] * msa_one_hot
+    extra_msa_one_hot = make_one_hot(protein["extra_msa"], 23)
+    extra_one_hot = protein["extra_msa_mask"][:, :, None] * extra_msa_one_hot
+    num_seq, num_res, _ = sample_one_hot.shape
+    extra_num_seq = extra_one_hot.shape[0]
+    agreement = torch.matmul(torch.reshape(extra_one_hot, [extra_num_seq, num_res * 23]),
+                             torch.reshape(sample_one_hot * weights, [num_seq, num_res * 23]).transpose(0, 1))
+    protein["extra_cluster_assignment"] = torch.argmax(agreement, dim=1).to(torch.int64)
+    return protein
+
+
+def unsorted_segment_sum(data, segment_ids, num_segments):
+    assert len(segment_ids.shape) == 1 and segment_ids.shape[0] == data.shape[0]
+    segment_ids = segment_ids.view(segment_ids.shape[0], *((1,) * len(data.shape[1:]))).expand(data.shape)
+    out = torch.zeros(num_segments, *data.shape[1:], dtype=data.dtype).scatter_add_(0, segment_ids, data.float() if data.dtype != torch.float32 else data)
+    return out.type(data.dtype)
+
+
+def summarize_clusters(protein):
+    num_seq = protein["msa"].shape[0]
+
+    def csum(x):
+        return unsorted_segment_sum(x, protein["extra_cluster_assignment"], num_seq)
+
+    mask = protein["extra_msa_mask"]
+    mask_counts = 1e-6 + protein["msa_mask"] + csum(mask)
+    msa_sum = csum(mask[:, :, None] * make_one_hot(protein["extra_msa"], 23)) + make_one_hot(protein["msa"], 23)
+    protein["cluster_profile"] = msa_sum / mask_counts[:, :, None]
+    del_sum = csum(mask * protein["extra_deletion_matrix"]) + protein["deletion_matrix"]
+    protein["cluster_deletion_mean"] = del_sum / mask_counts
+    return protein
+
+
+def make_msa_feat(protein):
+    """``msa_feat`` (49), ``target_feat`` (22) and the extra-MSA deletion features."""
+    has_break = torch.clip(protein["between_segment_residues"].to(torch.float32), 0, 1)
+    aatype_1hot = make_one_hot(protein["aatype"], 21)
+    protein["target_feat"] = torch.cat([has_break.unsqueeze(-1), aatype_1hot], dim=-1)
+    msa_1hot = make_one_hot(protein["msa"], 23)
+    has_deletion = torch.clip(protein["deletion_matrix"], 0.0, 1.0)
+    deletion_value = torch.atan(protein["deletion_matrix"] / 3.0) * (2.0 / np.pi)
+    msa_feat = [msa_1hot, has_deletion.unsqueeze(-1), deletion_value.unsqueeze(-1)]
+    if "cluster_profile" in protein:
+        deletion_mean_value = torch.atan(protein["cluster_deletion_mean"] / 3.0) * (2.0 / np.pi)
+        msa_feat.extend([protein["cluster_profile"], deletion_mean_value.unsqueeze(-1)])
+    if "extra_deletion_matrix" in protein:
+        protein["extra_has_deletion"] = torch.clip(protein["extra_deletion_matrix"], 0.0, 1.0)
+        protein["extra_deletion_value"] = torch.atan(protein["extra_deletion_matrix"] / 3.0) * (2.0 / np.pi)
+    protein["msa_feat"] = torch.cat(msa_feat, dim=-1)
+    return protein
+
+
+@curry1
+def select_feat(protein, feature_list):
+    return {k: v for k, v in protein.items() if k in feature_list}
+
+
+@curry1
+def crop_templates(protein, max_templates):
+    for k, v in protein.items():
+        if k.startswith("template_"):
+            protein[k] = v[:max_templates]
+    return protein
+
+
+@curry1
+def make_fixed_size(protein, shape_schema, msa_cluster_size, extra_msa_size, num_res=0, num_templates=0):
+    """Pads every feature to the static shape given by the schema (placeholders replaced by the sizes passed in)."""
+    from ..config import NUM_EXTRA_SEQ, NUM_MSA_SEQ, NUM_RES, NUM_TEMPLATES
+    pad_size_map = {NUM_RES: num_res, NUM_MSA_SEQ: msa_cluster_size, NUM_EXTRA_SEQ: extra_msa_size, NUM_TEMPLATES: num_templates}
+    for k, v in protein.items():
+        if k == "extra_cluster_assignment":
+            continue
+        shape = list(v.shape)
+        schema = shape_schema[k]
+        assert len(shape) == len(schema), "Rank mismatch between shape and shape schema for %s: %s vs %s" % (k, shape, schema)
+        pad_size = [pad_size_map.get(s2, None) or s1 for (s1, s2) in zip(shape, schema)]
+        padding = [(0, p - v.shape[i]) for i, p in enumerate(pad_size)]
+        padding.reverse()
+        padding = list(itertools.chain(*padding))
+        if padding:
+            protein[k] = torch.nn.functional.pad(v, padding)
+            protein[k] = torch.reshape(protein[k], pad_size)
+    return protein
+
+
+@curry1
+def random_crop_to_size(protein, crop_size, max_templates, shape_schema, subsample_templates=False, seed=None):
+    """Crops the residue axis (and the template axis) of every feature to ``crop_size`` at a random offset."""
+    from ..config import NUM_RES, NUM_TEMPLATES
+    g = torch.Generator()
+    if seed is not None:
+        g.manual_seed(seed)
+    else:
+        g.seed()
+    seq_length = int(protein["seq_length"])
+    num_templates = protein["template_mask"].shape[-1] if "template_mask" in protein else 0
+    num_res_crop_size = min(seq_length, crop_size)
+    n = seq_length - num_res_crop_size
+    right_anchor = n
+    if "use_clamped_fape" in protein and float(protein["use_clamped_fape"]) == 1.0:
+        right_anchor = n
+    num_res_crop_start = int(torch.randint(0, right_anchor + 1, (1,), generator=g)[0])
+    templ_start = int(torch.randint(0, num_templates + 1, (1,), generator=g)[0]) if (subsample_templates and num_templates) else 0
+    templates_select = torch.randperm(num_templates, generator=g) if num_templates else None
+    num_templates_crop = min(num_templates - templ_start, max_templates)
+    for k, v in protein.items():
+        if k not in shape_schema or ("template" not in k and NUM_RES not in shape_schema[k]):
+            continue
+        if k.startswith("template") and subsample_templates and templates_select is not None:
+            v = v[templates_select]
+        slices = []
+        for dim_size, dim in zip(shape_schema[k], v.shape):
+            is_res = dim_size == NUM_RES
+            if dim_size == NUM_TEMPLATES and k.startswith("template"):
+                start, size = templ_start, num_templates_crop
+            else:
+                start = num_res_crop_start if is_res else 0
+                size = num_res_crop_size if is_res else dim
+            slices.append(slice(start, start + size))
+        protein[k] = v[tuple(slices)]
+    protein["seq_length"] = protein["seq_length"].new_tensor(num_res_crop_size)
+    return protein

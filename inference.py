@@ -1,0 +1,124 @@
+#!/usr/bin/env python
+"""Structure prediction from a FASTA file.
+
+    python inference.py target.fasta data/pdb_mmcif/mmcif_files --output_dir ./out --gpus 2 \
+        --use_precomputed_alignments ./alignments --model_name model_1 --param_path data/params/params_model_1.npz \
+        --chunk_size 64 --inplace
+
+Flags follow the reference's inference.py:68-119,491-551.  Alignments are read from
+``--use_precomputed_alignments`` (one sub-directory per FASTA tag) or produced by the alignment tools when their
+binaries and databases are given (``--enable_workflow`` runs the searches concurrently); without either the query
+is folded in single-sequence mode.  Without ``--param_path`` the model keeps its random initialisation (useful for
+timing only).  Outputs: ``<tag>_<model>.pdb`` (+ ``.pkl`` with ``--save_prediction_result``), optionally relaxed.
+"""
+import argparse
+import os
+import pickle
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def add_data_args(parser):
+    for name in ("uniref90_database_path", "mgnify_database_path", "pdb70_database_path", "uniclust30_database_path", "bfd_database_path",
+                 "uniprot_database_path", "pdb_seqres_database_path"):
+        parser.add_argument("--" + name, type=str, default=None)
+    parser.add_argument("--jackhmmer_binary_path", type=str, default="/usr/bin/jackhmmer")
+    parser.add_argument("--hhblits_binary_path", type=str, default="/usr/bin/hhblits")
+    parser.add_argument("--hhsearch_binary_path", type=str, default="/usr/bin/hhsearch")
+    parser.add_argument("--hmmsearch_binary_path", type=str, default="/usr/bin/hmmsearch")
+    parser.add_argument("--hmmbuild_binary_path", type=str, default="/usr/bin/hmmbuild")
+    parser.add_argument("--kalign_binary_path", type=str, default="/usr/bin/kalign")
+    parser.add_argument("--max_template_date", type=str, default="2100-01-01")
+    parser.add_argument("--obsolete_pdbs_path", type=str, default=None)
+    parser.add_argument("--release_dates_path", type=str, default=None)
+    parser.add_argument("--chunk_size", type=int, default=None)
+    parser.add_argument("--enable_workflow", default=False, action="store_true")
+    parser.add_argument("--inplace", default=False, action="store_true")
+
+
+def main(args):
+    import numpy as np
+    from fastfold_b200.common import protein
+    from fastfold_b200.config import model_config
+    from fastfold_b200.data.data_pipeline import DataPipeline, FeaturePipeline
+    from fastfold_b200.data import parsers
+    from fastfold_b200.runtime.inference import run_inference
+    os.makedirs(args.output_dir, exist_ok=True)
+    seqs, tags = parsers.parse_fasta(open(args.fasta_path).read())
+    if args.model_preset == "multimer" and "multimer" not in args.model_name:
+        args.model_name = "multimer"
+    if args.model_preset == "monomer" and len(seqs) != 1:
+        raise ValueError("monomer preset expects one sequence in the FASTA file; use --model_preset multimer")
+    config = model_config(args.model_name)
+    tag = tags[0].split()[0] if tags else "query"
+    alignment_dir = None
+    if args.use_precomputed_alignments:
+        cand = os.path.join(args.use_precomputed_alignments, tag)
+        alignment_dir = cand if os.path.isdir(cand) else args.use_precomputed_alignments
+    elif args.uniref90_database_path:
+        from fastfold_b200.data.tools import AlignmentRunner
+        from fastfold_b200.workflow import FastFoldDataWorkFlow
+        alignment_dir = os.path.join(args.output_dir, "alignments", tag)
+        os.makedirs(alignment_dir, exist_ok=True)
+        t0 = time.perf_counter()
+        cls = FastFoldDataWorkFlow if args.enable_workflow else AlignmentRunner
+        cls(jackhmmer_binary_path=args.jackhmmer_binary_path, hhblits_binary_path=args.hhblits_binary_path,
+            hhsearch_binary_path=args.hhsearch_binary_path, uniref90_database_path=args.uniref90_database_path,
+            mgnify_database_path=args.mgnify_database_path, bfd_database_path=args.bfd_database_path,
+            uniclust30_database_path=args.uniclust30_database_path, pdb70_database_path=args.pdb70_database_path,
+            use_small_bfd=(args.preset == "reduced_dbs"), no_cpus=args.cpus).run(args.fasta_path, alignment_dir)
+        print("Alignment data workflow time: %.1f s" % (time.perf_counter() - t0))
+    featurizer = None
+    if args.template_mmcif_dir and os.path.isdir(args.template_mmcif_dir) and config.model.template.enabled:
+        from fastfold_b200.data.templates import TemplateHitFeaturizer
+        featurizer = TemplateHitFeaturizer(mmcif_dir=args.template_mmcif_dir, max_template_date=args.max_template_date, max_hits=4,
+                                           kalign_binary_path=args.kalign_binary_path)
+    raw = DataPipeline(template_featurizer=featurizer).process_sequence(seqs[0], tag, alignment_dir)
+    feats = FeaturePipeline(config.data).process_features(raw, mode="predict", seed=args.data_random_seed or 0)
+    overrides = {}
+    if "template_aatype" not in feats:
+        overrides["model.template.enabled"] = False
+    out = run_inference(feats, gpus=args.gpus, model_name=args.model_name, param_path=args.param_path, chunk_size=args.chunk_size,
+                        inplace=args.inplace, overrides=overrides)
+    print("Inference time: %.3f s (device-timed), peak memory %.2f GiB" % (out["_seconds"], out["_peak_gib"]))
+    plddt_b = np.repeat(out["plddt"][..., None], 37, axis=-1)
+    f = {"aatype": feats["aatype"][..., 0].numpy(), "residue_index": feats["residue_index"][..., 0].numpy()}
+    prot = protein.from_prediction(f, out, b_factors=plddt_b)
+    path = os.path.join(args.output_dir, "%s_%s_unrelaxed.pdb" % (tag, args.model_name))
+    with open(path, "w") as fh:
+        fh.write(protein.to_pdb(prot))
+    print("wrote", path)
+    if args.relaxation:
+        from fastfold_b200.relax import AmberRelaxation
+        t0 = time.perf_counter()
+        relaxed, _, _ = AmberRelaxation(use_gpu=True, **config.relax).process(prot=prot)
+        print("Relaxation time: %.1f s" % (time.perf_counter() - t0))
+        with open(os.path.join(args.output_dir, "%s_%s_relaxed.pdb" % (tag, args.model_name)), "w") as fh:
+            fh.write(relaxed)
+    if args.save_prediction_result:
+        with open(os.path.join(args.output_dir, "%s_%s_output_dict.pkl" % (tag, args.model_name)), "wb") as fh:
+            pickle.dump(out, fh, protocol=pickle.HIGHEST_PROTOCOL)
+
+
+if __name__ == "__main__":
+    p = argparse.ArgumentParser()
+    p.add_argument("fasta_path", type=str)
+    p.add_argument("template_mmcif_dir", type=str, nargs="?", default=None)
+    p.add_argument("--use_precomputed_alignments", type=str, default=None)
+    p.add_argument("--output_dir", type=str, default=os.getcwd())
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--model_name", type=str, default="model_1")
+    p.add_argument("--param_path", type=str, default=None)
+    p.add_argument("--model_preset", type=str, default="monomer", choices=["monomer", "multimer"])
+    p.add_argument("--preset", type=str, default="full_dbs", choices=("reduced_dbs", "full_dbs"))
+    p.add_argument("--cpus", type=int, default=12)
+    p.add_argument("--relaxation", action="store_true", default=False)
+    p.add_argument("--save_prediction_result", action="store_true", default=False)
+    p.add_argument("--data_random_seed", type=int, default=None)
+    add_data_args(p)
+    a = p.parse_args()
+    if a.param_path is None:
+        a.param_path = os.path.join("data", "params", "params_" + a.model_name + ".npz")
+    main(a)

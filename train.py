@@ -1,0 +1,145 @@
+#!/usr/bin/env python
+"""Training entry point.
+
+    torchrun --nproc_per_node=8 train.py --dap_size 2 --config_preset initial_training --synthetic --max_steps 100 \
+        --save_ckpt_path ./ckpt --save_ckpt_interval 50
+
+Flags follow the reference's train.py:37-159 (``--from_torch --dap_size --config_preset --seed --max_epochs
+--log_interval --log_path --save_ckpt_path --save_ckpt_interval`` + data paths).  World = DAP x DP: ranks of one DAP
+group share a sample, different groups get different samples.  Differences on purpose: the optimizer, gradient
+reduction and (optionally) CUDA-graph replay come from ``FlatAdamTrainer`` instead of ColossalAI's engine; a
+checkpoint holds model, optimizer moments, scheduler, step and RNG state and ``--resume`` continues from it (the
+reference pickles the bare module and cannot resume, train.py:253-254); the schedule advances per step.
+``--synthetic`` trains on generated features (no databases); otherwise ``--train_data_dir`` must hold ``<tag>.pdb``
+structures with optional alignments under ``--train_alignment_dir/<tag>``.
+"""
+import argparse
+import logging
+import os
+import random
+import sys
+import time
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--from_torch", default=False, action="store_true")
+    p.add_argument("--dap_size", type=int, default=1)
+    p.add_argument("--config_preset", type=str, default="initial_training")
+    p.add_argument("--seed", type=int, default=42)
+    p.add_argument("--max_epochs", type=int, default=10000)
+    p.add_argument("--max_steps", type=int, default=None)
+    p.add_argument("--train_epoch_len", type=int, default=64)
+    p.add_argument("--log_interval", type=int, default=1)
+    p.add_argument("--log_path", type=str, default="train_log")
+    p.add_argument("--save_ckpt_path", type=str, default=None)
+    p.add_argument("--save_ckpt_interval", type=int, default=1)
+    p.add_argument("--resume", type=str, default=None)
+    p.add_argument("--synthetic", default=False, action="store_true")
+    p.add_argument("--train_data_dir", type=str, default=None)
+    p.add_argument("--train_alignment_dir", type=str, default=None)
+    p.add_argument("--val_data_dir", type=str, default=None)
+    p.add_argument("--val_alignment_dir", type=str, default=None)
+    p.add_argument("--template_mmcif_dir", type=str, default=None)
+    p.add_argument("--max_template_date", type=str, default="2021-10-10")
+    p.add_argument("--n_res", type=int, default=None, help="(synthetic) crop size; default from the preset")
+    p.add_argument("--n_seq", type=int, default=None)
+    p.add_argument("--n_extra", type=int, default=None)
+    p.add_argument("--blocks", type=int, default=None, help="override the number of Evoformer blocks (debugging)")
+    p.add_argument("--lr", type=float, default=1e-3)
+    p.add_argument("--no_graph", default=False, action="store_true")
+    return p.parse_args()
+
+
+def main():
+    args = parse()
+    from fastfold_b200.config import model_config
+    from fastfold_b200.models.hub import AlphaFold, AlphaFoldLoss, AlphaFoldLRScheduler
+    from fastfold_b200.parallel import core, init_dap
+    from fastfold_b200.runtime import FlatAdamTrainer
+    from fastfold_b200.runtime.checkpoint import load_checkpoint, save_checkpoint
+    from fastfold_b200.utils.inject_fastnn import inject_fastnn
+    from fastfold_b200.utils.tensor_utils import tensor_tree_map
+    from fastfold_b200.utils.validation_utils import validation_metrics
+    init_dap(args.dap_size)
+    rank = core.get_rank()
+    cuda = torch.cuda.is_available()
+    device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+    # every rank seeds alike: DAP ranks must draw identical dropout masks
+    random.seed(args.seed)
+    np.random.seed(args.seed)
+    torch.manual_seed(args.seed)
+    logging.basicConfig(level=logging.INFO if rank == 0 else logging.WARNING, format="%(asctime)s %(message)s",
+                        handlers=[logging.StreamHandler()] + ([logging.FileHandler(args.log_path + ".log")] if rank == 0 else []))
+    log = logging.getLogger("train")
+    config = model_config(args.config_preset, train=True)
+    if args.blocks:
+        config.model.evoformer_stack.no_blocks = args.blocks
+    model = inject_fastnn(AlphaFold(config))
+    model = model.to(device=device, dtype=torch.bfloat16 if cuda else torch.float32).train()
+    criterion = AlphaFoldLoss(config.loss)
+
+    tc = config.data.train
+    n_res, n_seq, n_extra = args.n_res or tc.crop_size, args.n_seq or tc.max_msa_clusters, args.n_extra or tc.max_extra_msa
+    if args.synthetic or not args.train_data_dir:
+        from fastfold_b200.data.data_modules import SyntheticDataset
+        dataset = SyntheticDataset(n_res, n_seq, n_extra, n_recycle=config.data.common.max_recycling_iters, length=args.train_epoch_len,
+                                   seed=args.seed, dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size(),
+                                   n_templ=tc.max_templates if config.model.template.enabled else 0)
+    else:
+        from fastfold_b200.data.data_modules import StructureDataset
+        dataset = StructureDataset(args.train_data_dir, args.train_alignment_dir, config.data, mode="train", seed=args.seed,
+                                   dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size())
+
+    def loss_fn(mod, batch):
+        out = mod(batch)
+        last = tensor_tree_map(lambda t: t[..., -1], batch)
+        loss, parts = criterion(out, last, _return_breakdown=True)
+        loss_fn.last = (out, last, parts)
+        return loss
+
+    # the full model's feature dict is not a flat tensor list and the number of recycling iterations varies per
+    # step, so the step runs eagerly here; the Evoformer benchmark (bench.py) shows the captured-graph path
+    trainer = FlatAdamTrainer(model, loss_fn, lr=args.lr, eps=1e-8, use_graph=False,
+                              replicated_param_filter=lambda n: not (n.startswith("evoformer.blocks") or n.startswith("extra_msa_stack.blocks")))
+    sched = AlphaFoldLRScheduler(trainer, max_lr=args.lr)
+    start_epoch = 0
+    if args.resume:
+        start_epoch = load_checkpoint(args.resume, model, trainer, sched, device)
+        log.info("resumed from %s at step %d (epoch %d)", args.resume, trainer.step_count, start_epoch)
+    steps_done = 0
+    for epoch in range(start_epoch, args.max_epochs):
+        t_epoch = time.time()
+        for i in range(len(dataset)):
+            batch = dataset.get(epoch, i)
+            n_iter = int(batch.pop("no_recycling_iters", torch.tensor(batch["aatype"].shape[-1] - 1)).reshape(-1)[0]) + 1
+            batch = {k: v[..., :n_iter].to(device, non_blocking=True) for k, v in batch.items()}
+            loss = trainer.step(batch)
+            sched.step()
+            steps_done += 1
+            if rank == 0 and (i + 1) % args.log_interval == 0:
+                out, last, parts = loss_fn.last
+                with torch.no_grad():
+                    metrics = validation_metrics(out, last)
+                log.info("epoch %d step %d lr %.2e loss %.4f | %s | %s", epoch, trainer.step_count, trainer.lr, float(loss),
+                         " ".join("%s %.3f" % (k, float(v)) for k, v in parts.items() if k not in ("loss", "unscaled_loss")),
+                         " ".join("%s %.3f" % (k, float(v)) for k, v in metrics.items()))
+            if args.max_steps and steps_done >= args.max_steps:
+                break
+        log.info("epoch %d done in %.1f s", epoch, time.time() - t_epoch)
+        if args.save_ckpt_path and (epoch + 1) % args.save_ckpt_interval == 0:
+            save_checkpoint(os.path.join(args.save_ckpt_path, "checkpoint.pt"), model, trainer, sched, epoch + 1)
+            if rank == 0:
+                log.info("checkpoint written to %s", args.save_ckpt_path)
+        if args.max_steps and steps_done >= args.max_steps:
+            break
+    core.shutdown()
+
+
+if __name__ == "__main__":
+    main()
