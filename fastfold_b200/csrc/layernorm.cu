@@ -365,3 +365,48 @@ int ffb_layernorm_fwd_transposed(const void* x, const void* gamma, const void* b
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the backward (see layernorm_noalloc.h).
+// ---------------------------------------------------------------------------
+#include <stdio.h>
+
+#include "layernorm_noalloc.h"
+
+// Partial dgamma / dbeta sums of FFB_LN_NOALLOC_BLOCKS blocks.  In host code this name is only a handle for
+// cudaGetSymbolAddress - never a pointer to hand to a kernel.
+static __device__ __align__(256) float g_ln_noalloc_scratch[FFB_LN_NOALLOC_BLOCKS * 2 * FFB_LN_NOALLOC_MAX_C];
+
+// Device address of the array on each device of the process, resolved on first use with that device current.
+static float* ln_noalloc_scratch_ptr() {
+  static float* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_ln_noalloc_scratch) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  return ptrs[dev];
+}
+
+extern "C" int ffb_layernorm_bwd_noalloc(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                                         void* dgamma, void* dbeta, long long rows, int C, int dtype, void* stream) {
+  if (C > FFB_LN_NOALLOC_MAX_C || C <= 0) {
+    fprintf(stderr, "ffb_layernorm_bwd_noalloc: C = %d exceeds the built-in scratch capacity (C <= %d)\n", C, FFB_LN_NOALLOC_MAX_C);
+    return FFB_LN_NOALLOC_TOO_WIDE;
+  }
+  if (rows <= 0) return 0;
+  float* part = ln_noalloc_scratch_ptr();
+  if (!part) return -1;
+  long long want = (rows + LN_WARPS - 1) / LN_WARPS;
+  const int nblocks = (int)(want < FFB_LN_NOALLOC_BLOCKS ? want : FFB_LN_NOALLOC_BLOCKS);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // ln_bwd_dispatch clears the 2 * C * nblocks floats it is about to accumulate into, on the same stream
+  switch (dtype) {
+    case 0: return ln_bwd_dispatch<float>((const float*)dy, (const float*)x, (const float*)gamma, mean, rstd, (float*)dx, part, nblocks, (float*)dgamma, (float*)dbeta, rows, C, st);
+    case 1: return ln_bwd_dispatch<__half>((const __half*)dy, (const __half*)x, (const __half*)gamma, mean, rstd, (__half*)dx, part, nblocks, (__half*)dgamma, (__half*)dbeta, rows, C, st);
+    case 2: return ln_bwd_dispatch<bf16>((const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part, nblocks, (bf16*)dgamma, (bf16*)dbeta, rows, C, st);
+  }
+  return -2;
+}
