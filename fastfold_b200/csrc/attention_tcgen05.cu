@@ -8,20 +8,25 @@
 // walks over batch rows; for sequences of up to 256 keys the bias tiles are
 // loaded once and stay resident in shared memory for the whole walk.
 //
-// Per CTA (192 threads):
+// Per CTA (320 threads):
 //   warp 0     TMA producer: Q tile, K/V key blocks (64B-swizzled, straight out of
 //              the fused QKV projection output, no head transposes), bias tiles
 //   warp 1     MMA issuer: S = Q K^T (tcgen05, 128 x 128 x 32) into one of two TMEM
-//              stages; PV = P V (128 x 32 x 128) into one of two TMEM stages
-//   warps 2-5  softmax: thread = query row.  tcgen05.ld of S, scale + bias + mask,
-//              online max / sum, P written as bf16 into the 128B-swizzled shared
-//              tile that the PV MMA reads; the running output row lives in
-//              registers and is rescaled there (no TMEM read-modify-write)
-// S MMA of block j+1 and the PV MMA of block j overlap the softmax of block j.
+//              stages; per key half, PV = P V (128 x 32 x 64) into its own TMEM stage
+//   warps 2-9  softmax: two threads per query row, each owning one 64-key half of
+//              every 128-key block (warps 2-5: keys 0-63, warps 6-9: keys 64-127).
+//              A thread runs its own online softmax over its keys: tcgen05.ld of S,
+//              scale + bias (+ mask), running max / sum, P written as bf16 into the
+//              128B-swizzled shared tile that its half's PV MMA reads; its partial
+//              output row lives in registers.  The two halves of a row are merged
+//              once per item through shared memory (flash-decoding style), each
+//              thread finishing 16 of the 32 output channels.
+// The issuer runs one block ahead across item boundaries, so S of block g+1 and
+// the PV products of block g overlap the softmax of block g.
 // Masked keys get the logit -1e9 (replaced, not added), as in the reference's
 // softmax kernels (softmax_cuda_kernel.cu:338-423,618-706); keys beyond the
 // sequence end get -inf.  The kernel also stores log2-domain row statistics
-// L2 = m2 + log2(l) for the backward kernel.
+// L2 = m * log2(e) + log2(l) for the backward kernel.
 //
 // Replaces logits matmul + fused_softmax + weights*v of the reference
 // (fastfold/model/fastnn/ops.py:304-319) and its unused Triton forward-only
@@ -33,7 +38,7 @@ namespace ffb {
 
 constexpr int AT_BQ = 128;      // queries per tile
 constexpr int AT_BK = 128;      // keys per block
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 320; // producer warp, MMA warp, 8 softmax / gradient warps
 constexpr int AT_KV_STAGES = 3;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -42,7 +47,7 @@ struct AttnArgs {
   int n_qt, n_kb;                // query tiles, key blocks
   int items;                     // H * n_qt * B work items
   int bias_resident;             // 1: n_kb <= 2, bias tiles stay in shared memory across batch rows
-  float scale_log2e;             // scale * log2(e)
+  float scale;                   // logit scale
   const bf16* mask;              // [B][n_k] or null
   long long mask_bstride;
   bf16* out;                     // [B][n_q][H*D]
@@ -68,13 +73,35 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+// two bf16 packed in a word -> two floats (low half first)
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// Keep-bits of 64 consecutive keys starting at kbase: bit c of (lo | hi << 32) is set when key kbase + c is inside the
+// sequence and its mask entry is non-zero.  `valid` gets the in-sequence bits alone.  One warp-wide call.
+__device__ __forceinline__ void key_bits(const bf16* mrow, int kbase, int n_k, int lane, uint32_t& keep_lo, uint32_t& keep_hi,
+                                         uint32_t& valid_lo, uint32_t& valid_hi) {
+  const int k_a = kbase + lane, k_b = kbase + 32 + lane;
+  const bool in_a = k_a < n_k, in_b = k_b < n_k;
+  bool on_a = in_a, on_b = in_b;
+  if (mrow) {
+    if (in_a) on_a = __bfloat162float(mrow[k_a]) != 0.f;
+    if (in_b) on_b = __bfloat162float(mrow[k_b]) != 0.f;
+  }
+  valid_lo = __ballot_sync(0xffffffffu, in_a);
+  valid_hi = __ballot_sync(0xffffffffu, in_b);
+  keep_lo = __ballot_sync(0xffffffffu, on_a);
+  keep_hi = __ballot_sync(0xffffffffu, on_b);
+}
+
 struct AttnSmem {
   // offsets (bytes) from the 1024-aligned base
   static constexpr int Q = 0;                                  // 2 x [128][64 B]            16 KB
   static constexpr int KV = Q + 2 * 8192;                      // STAGES x (K 8 KB + V 8 KB) 48 KB
   static constexpr int BIAS = KV + AT_KV_STAGES * 16384;       // 2 x [2 boxes][128][128 B]  64 KB
   static constexpr int P = BIAS + 2 * 32768;                   // 2 x [2 chunks][128][128 B] 64 KB
-  static constexpr int BARS = P + 2 * 32768;
+  static constexpr int XCH = P + 2 * 32768;                    // [2 halves][18][128] floats 18 KB
+  static constexpr int BARS = XCH + 2 * 18 * 128 * 4;
   static constexpr int TOTAL = BARS + 512 + 1024;
 };
 
@@ -88,13 +115,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + AttnSmem::BARS);
-  // barrier map
+  // barrier map (8 bytes each)
   const uint32_t b0 = smem_u32(bars);
   const uint32_t q_full = b0, q_empty = b0 + 16;                       // 2 + 2
   const uint32_t kv_full = b0 + 32, kv_empty = kv_full + 8 * AT_KV_STAGES;
   const uint32_t bias_full = kv_empty + 8 * AT_KV_STAGES, bias_empty = bias_full + 16;
   const uint32_t s_full = bias_empty + 16, s_empty = s_full + 16;
-  const uint32_t p_full = s_empty + 16, o_full = p_full + 16;
+  const uint32_t p_full = s_empty + 16;                                // [stage][half]
+  const uint32_t o_full = p_full + 32;                                 // [stage][half]
+  const uint32_t x_ready = o_full + 32, x_done = x_ready + 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + AttnSmem::BARS + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -106,9 +135,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
       mbar_init(q_full + 8 * s, 1);
       mbar_init(q_empty + 8 * s, 1);
       mbar_init(bias_full + 8 * s, 1);
-      mbar_init(bias_empty + 8 * s, 4);
+      mbar_init(bias_empty + 8 * s, 8);
       mbar_init(s_full + 8 * s, 1);
-      mbar_init(s_empty + 8 * s, 4);
+      mbar_init(s_empty + 8 * s, 8);
+    }
+    for (int s = 0; s < 4; ++s) {
       mbar_init(p_full + 8 * s, 4);
       mbar_init(o_full + 8 * s, 1);
     }
@@ -116,6 +147,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
       mbar_init(kv_full + 8 * s, 1);
       mbar_init(kv_empty + 8 * s, 1);
     }
+    mbar_init(x_ready, 8);
+    mbar_init(x_done, 8);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -132,7 +165,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t TM_S = 0, TM_O = 256;
+  const uint32_t TM_S = 0, TM_O = 256;       // S: 2 stages x 128 columns; O: [stage][half] x 32 columns
 
   // contiguous range of work items for this CTA; item = (h * n_qt + qt) * B + b
   const int per = (a.items + gridDim.x - 1) / gridDim.x;
@@ -188,12 +221,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
       // ---------------- MMA issuer ----------------
       constexpr uint32_t idesc_s = make_idesc_bf16(128, AT_BK, 0, 0);     // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);         // P (K-major) x V (MN-major)
-      uint32_t jt = 0, qi = 0;
+      const uint32_t total = (uint32_t)(it_end > it_begin ? it_end - it_begin : 0) * (uint32_t)a.n_kb;
       bool ok = true;
-      auto issue_s = [&](uint32_t jglob, uint32_t qs) -> bool {
-        const uint32_t s = jglob % AT_KV_STAGES, sb = jglob & 1;
-        if (!mbar_wait(kv_full + 8 * s, (jglob / AT_KV_STAGES) & 1)) { report(ST_TIMEOUT_TMA, 20); return false; }
-        if (!mbar_wait(s_empty + 8 * sb, ((jglob >> 1) & 1) ^ 1)) { report(ST_TIMEOUT_EPI, 21); return false; }
+      uint32_t s_g = 0, s_qi = 0, s_j = 0;     // next S product: global block, item and block-in-item counters
+      auto issue_s = [&]() -> bool {
+        const uint32_t s = s_g % AT_KV_STAGES, sb = s_g & 1, qs = s_qi & 1;
+        if (s_j == 0 && !mbar_wait(q_full + 8 * qs, (s_qi >> 1) & 1)) { report(ST_TIMEOUT_TMA, 22); return false; }
+        if (!mbar_wait(kv_full + 8 * s, (s_g / AT_KV_STAGES) & 1)) { report(ST_TIMEOUT_TMA, 20); return false; }
+        if (!mbar_wait(s_empty + 8 * sb, ((s_g >> 1) & 1) ^ 1)) { report(ST_TIMEOUT_EPI, 21); return false; }
         tc_fence_after();
         const uint32_t qa = base + AttnSmem::Q + qs * 8192;
         const uint32_t ka = base + AttnSmem::KV + s * 16384;
@@ -201,42 +236,49 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
         for (int k = 0; k < D / 16; ++k)
           umma_bf16(tmem + TM_S + sb * 128, make_desc(qa + k * 32, 16, 512, 4), make_desc(ka + k * 32, 16, 512, 4), idesc_s, k > 0 ? 1u : 0u);
         umma_commit(s_full + 8 * sb);
+        ++s_g;
+        if (++s_j == (uint32_t)a.n_kb) {
+          umma_commit(q_empty + 8 * qs);      // all S products of this item issued: the Q slot drains with them
+          s_j = 0;
+          ++s_qi;
+        }
         return true;
       };
-      for (int item = it_begin; item < it_end && ok; ++item, ++qi) {
-        const uint32_t qs = qi & 1;
-        if (!mbar_wait(q_full + 8 * qs, (qi >> 1) & 1)) { report(ST_TIMEOUT_TMA, 22); *abort_flag = 1; break; }
-        ok = issue_s(jt, qs);
-        for (int j = 0; j < a.n_kb && ok; ++j, ++jt) {
-          if (j + 1 < a.n_kb) ok = issue_s(jt + 1, qs);
-          if (!ok) break;
-          if (j + 1 == a.n_kb) umma_commit(q_empty + 8 * qs);    // all S MMAs of this item issued: Q slot drains with them
-          const uint32_t pb = jt & 1;
-          if (!mbar_wait(p_full + 8 * pb, (jt >> 1) & 1)) { report(ST_TIMEOUT_EPI, 23); ok = false; break; }
-          tc_fence_after();
-          const uint32_t s = jt % AT_KV_STAGES;
-          const uint32_t pa = base + AttnSmem::P + pb * 32768;
-          const uint32_t va = base + AttnSmem::KV + s * 16384 + 8192;
+      if (total > 0) ok = issue_s();
+      for (uint32_t g = 0; g < total && ok; ++g) {
+        if (g + 1 < total) ok = issue_s();
+        if (!ok) break;
+        const uint32_t pb = g & 1, s = g % AT_KV_STAGES;
+        const uint32_t pa = base + AttnSmem::P + pb * 32768;
+        const uint32_t va = base + AttnSmem::KV + s * 16384 + 8192;
 #pragma unroll
-          for (int k = 0; k < AT_BK / 16; ++k)
-            umma_bf16(tmem + TM_O + pb * 32, make_desc(pa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, 2),
-                      make_desc(va + k * 1024, 16, 512, 4), idesc_o, k > 0 ? 1u : 0u);
-          umma_commit(o_full + 8 * pb);
-          umma_commit(kv_empty + 8 * s);
+        for (int half = 0; half < 2; ++half) {
+          if (!mbar_wait(p_full + 8 * (pb * 2 + half), (g >> 1) & 1)) { report(ST_TIMEOUT_EPI, 23); ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem + TM_O + (pb * 2 + half) * 32, make_desc(pa + half * 16384 + k * 32, 16, 1024, 2),
+                      make_desc(va + (half * 4 + k) * 1024, 16, 512, 4), idesc_o, k > 0 ? 1u : 0u);
+          umma_commit(o_full + 8 * (pb * 2 + half));
         }
+        if (!ok) break;
+        umma_commit(kv_empty + 8 * s);
       }
       if (!ok) *abort_flag = 1;
     }
     __syncwarp();
   } else {
-    // ---------------- softmax / output (warps 2..5): thread = query row ----------------
-    const int quad = warp & 3;
+    // ---------------- softmax / output (warps 2..9): thread = (query row, key half) ----------------
+    const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;               // which 64 keys of every block
     const int r = quad * 32 + lane;                 // row within the query tile
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
-    uint32_t jt = 0, bt = 0;
+    float* xch_mine = reinterpret_cast<float*>(sm + AttnSmem::XCH) + half * (18 * 128) + r;
+    const float* xch_other = reinterpret_cast<const float*>(sm + AttnSmem::XCH) + (half ^ 1) * (18 * 128) + r;
+    uint32_t jt = 0, bt = 0, ic = 0;
     int prev_group = -1;
     bool ok = true;
-    for (int item = it_begin; item < it_end && ok; ++item) {
+    for (int item = it_begin; item < it_end && ok; ++item, ++ic) {
       const int b = item % a.B;
       const int grp = item / a.B;
       const int qt = grp % a.n_qt, h = grp / a.n_qt;
@@ -247,11 +289,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
       float o[D];
 #pragma unroll
       for (int c = 0; c < D; ++c) o[c] = 0.f;
-      float m2 = -INFINITY, l = 0.f, alpha_prev = 1.f;
+      float m = -INFINITY, l = 0.f, alpha_prev = 1.f;       // m in natural-log units
       const bf16* mrow = a.mask ? a.mask + (long long)b * a.mask_bstride : nullptr;
       for (int j = 0; j < a.n_kb; ++j, ++jt) {
-        const int k0 = j * AT_BK;
+        const int kbase = j * AT_BK + half * 64;
         const uint32_t sb = jt & 1;
+        // key bits first: their global loads overlap the wait for S
+        uint32_t keep_lo, keep_hi, valid_lo, valid_hi;
+        key_bits(mrow, kbase, a.n_k, lane, keep_lo, keep_hi, valid_lo, valid_hi);
+        const bool plain = (keep_lo & keep_hi) == 0xffffffffu;         // every key of this half in range and unmasked
         uint32_t bs = 0;
         if (a.has_bias) {
           bs = a.bias_resident ? (uint32_t)j : (bt & 1);
@@ -266,133 +312,177 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        // ---- logits of this row: 128 keys in registers ----
-        float s[AT_BK];
-#pragma unroll
-        for (int c = 0; c < AT_BK / 32; ++c) tmem_ld_32x32(lane_base + TM_S + sb * 128 + c * 32, s + c * 32);
+        // ---- logits of this row's 64 keys in registers ----
+        float s[64];
+        tmem_ld_32x32(lane_base + TM_S + sb * 128 + half * 64, s);
+        tmem_ld_32x32(lane_base + TM_S + sb * 128 + half * 64 + 32, s + 32);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_empty + 8 * sb);          // S stage may be overwritten by the next-but-one block
-        const uint8_t* btile = sm + AttnSmem::BIAS + bs * 32768;
-        float mx = m2;
+        if (a.has_bias) {
+          const uint8_t* brow = sm + AttnSmem::BIAS + bs * 32768 + half * 16384 + r * 128;
 #pragma unroll
-        for (int u = 0; u < AT_BK / 8; ++u) {
-          float bv[8];
-          if (a.has_bias) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(btile + (u >> 3) * 16384 + r * 128 + (((u & 7) ^ (r & 7)) << 4));
-            const bf162* hp = reinterpret_cast<const bf162*>(&raw);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __bfloat1622float2(hp[e]);
-              bv[2 * e] = f.x;
-              bv[2 * e + 1] = f.y;
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) bv[e] = 0.f;
+          for (int u = 0; u < 8; ++u) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(brow + ((u ^ (r & 7)) << 4));
+            s[u * 8 + 0] = fmaf(s[u * 8 + 0], a.scale, bf_lo(raw.x));
+            s[u * 8 + 1] = fmaf(s[u * 8 + 1], a.scale, bf_hi(raw.x));
+            s[u * 8 + 2] = fmaf(s[u * 8 + 2], a.scale, bf_lo(raw.y));
+            s[u * 8 + 3] = fmaf(s[u * 8 + 3], a.scale, bf_hi(raw.y));
+            s[u * 8 + 4] = fmaf(s[u * 8 + 4], a.scale, bf_lo(raw.z));
+            s[u * 8 + 5] = fmaf(s[u * 8 + 5], a.scale, bf_hi(raw.z));
+            s[u * 8 + 6] = fmaf(s[u * 8 + 6], a.scale, bf_lo(raw.w));
+            s[u * 8 + 7] = fmaf(s[u * 8 + 7], a.scale, bf_hi(raw.w));
           }
-          float mk[8];
-          if (mrow) {
-            const int kk = k0 + u * 8;
-            if (kk + 8 <= a.n_k) {
-              const uint4 raw = *reinterpret_cast<const uint4*>(mrow + kk);
-              const bf162* hp = reinterpret_cast<const bf162*>(&raw);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(hp[e]);
-                mk[2 * e] = f.x;
-                mk[2 * e + 1] = f.y;
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) mk[e] = (kk + e < a.n_k) ? __bfloat162float(mrow[kk + e]) : 0.f;
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) mk[e] = 1.f;
+          if (!a.bias_resident || last_of_group) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bias_empty + 8 * bs);
           }
+        } else {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int c = u * 8 + e;
-            float v = s[c] * a.scale_log2e + bv[e] * LOG2E;
-            if (mk[e] == 0.f) v = -1e9f * LOG2E;
-            if (k0 + c >= a.n_k) v = -INFINITY;
-            s[c] = v;
-            mx = fmaxf(mx, v);
+          for (int c = 0; c < 64; ++c) s[c] *= a.scale;
+        }
+        if (!plain) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            const uint32_t keep = c < 32 ? keep_lo : keep_hi, valid = c < 32 ? valid_lo : valid_hi;
+            if (!((keep >> (c & 31)) & 1u)) s[c] = -1e9f;
+            if (!((valid >> (c & 31)) & 1u)) s[c] = -INFINITY;
           }
         }
-        if (a.has_bias && (!a.bias_resident || last_of_group)) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bias_empty + 8 * bs);
+        float mx0 = m, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 64; c += 4) {
+          mx0 = fmaxf(mx0, s[c]);
+          mx1 = fmaxf(mx1, s[c + 1]);
+          mx2 = fmaxf(mx2, s[c + 2]);
+          mx3 = fmaxf(mx3, s[c + 3]);
         }
-        const float alpha = ex2f(m2 - mx);                      // m2 = -inf on the first block -> 0
-        m2 = mx;
-        float rowsum = 0.f;
-        // ---- P = exp2(s - m) as bf16 into the swizzled A-operand tile ----
-        uint8_t* ptile = sm + AttnSmem::P + sb * 32768;
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        const float mxs = (mx == -INFINITY) ? 0.f : mx;        // a half with no key in range yet: all p = 0
+        const float alpha = ex2f((m - mxs) * LOG2E);            // m = -inf on the first block -> 0
+        m = mx;
+        // ---- P = exp(s - m) as bf16 into the swizzled A-operand tile ----
+        uint8_t* prow = sm + AttnSmem::P + sb * 32768 + half * 16384 + r * 128;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        if (plain) {
+          const float nm = -mxs * LOG2E;
 #pragma unroll
-        for (int u = 0; u < AT_BK / 8; ++u) {
-          uint4 pk;
-          bf162* hp = reinterpret_cast<bf162*>(&pk);
+          for (int u = 0; u < 8; ++u) {
+            float p[8];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float p0 = ex2f(s[u * 8 + 2 * e] - mx), p1 = ex2f(s[u * 8 + 2 * e + 1] - mx);
-            hp[e] = __floats2bfloat162_rn(p0, p1);
-            const float2 back = __bfloat1622float2(hp[e]);     // sum what the MMA will actually see
-            rowsum += back.x + back.y;
+            for (int e = 0; e < 8; ++e) p[e] = ex2f(fmaf(s[u * 8 + e], LOG2E, nm));
+            sum0 += p[0] + p[4];
+            sum1 += p[1] + p[5];
+            sum2 += p[2] + p[6];
+            sum3 += p[3] + p[7];
+            uint4 pk;
+            bf162* hp = reinterpret_cast<bf162*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) hp[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+            *reinterpret_cast<uint4*>(prow + ((u ^ (r & 7)) << 4)) = pk;
           }
-          *reinterpret_cast<uint4*>(ptile + (u >> 3) * 16384 + r * 128 + (((u & 7) ^ (r & 7)) << 4)) = pk;
+        } else {
+          // masked logits are huge: subtract first, so that equal logits give exactly 1
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            float p[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) p[e] = ex2f((s[u * 8 + e] - mxs) * LOG2E);
+            sum0 += p[0] + p[4];
+            sum1 += p[1] + p[5];
+            sum2 += p[2] + p[6];
+            sum3 += p[3] + p[7];
+            uint4 pk;
+            bf162* hp = reinterpret_cast<bf162*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) hp[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+            *reinterpret_cast<uint4*>(prow + ((u ^ (r & 7)) << 4)) = pk;
+          }
         }
-        l = l * alpha + rowsum;
-        // previous block's PV (if any) joins the register accumulator before this block's scaling is applied
+        l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+        fence_proxy_async_smem();                              // generic-proxy P stores -> visible to the MMA (async proxy)
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full + 8 * (sb * 2 + half));
+        // previous block's PV (if any) joins the register accumulator with the scaling that preceded this block
         if (j > 0) {
           const uint32_t ob = (jt - 1) & 1;
-          bool w = mbar_wait(o_full + 8 * ob, ((jt - 1) >> 1) & 1);
+          bool w = mbar_wait(o_full + 8 * (ob * 2 + half), ((jt - 1) >> 1) & 1);
           if (!w && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_MMA, 32);
           w = __all_sync(0xffffffffu, w);
           if (!w) { ok = false; break; }
           tc_fence_after();
           float pv[D];
-          tmem_ld_32x32(lane_base + TM_O + ob * 32, pv);
+          tmem_ld_32x32(lane_base + TM_O + (ob * 2 + half) * 32, pv);
           tmem_ld_wait();
 #pragma unroll
           for (int c = 0; c < D; ++c) o[c] = o[c] * alpha_prev + pv[c];
         }
         alpha_prev = alpha;
-        fence_proxy_async_smem();                              // generic-proxy P stores -> visible to the MMA (async proxy)
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(p_full + 8 * sb);
       }
       if (!ok) break;
       // last block's PV
       {
         const uint32_t ob = (jt - 1) & 1;
-        bool w = mbar_wait(o_full + 8 * ob, ((jt - 1) >> 1) & 1);
+        bool w = mbar_wait(o_full + 8 * (ob * 2 + half), ((jt - 1) >> 1) & 1);
         if (!w && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_MMA, 33);
         w = __all_sync(0xffffffffu, w);
         if (!w) { ok = false; break; }
         tc_fence_after();
         float pv[D];
-        tmem_ld_32x32(lane_base + TM_O + ob * 32, pv);
+        tmem_ld_32x32(lane_base + TM_O + (ob * 2 + half) * 32, pv);
         tmem_ld_wait();
+        tc_fence_before();
 #pragma unroll
         for (int c = 0; c < D; ++c) o[c] = o[c] * alpha_prev + pv[c];
       }
+      // ---- merge the two key halves of the row: this thread finishes channels [half * 16, half * 16 + 16) ----
+      if (ic > 0) {
+        bool w = mbar_wait(x_done, (ic - 1) & 1);              // the previous item's exchange has been read
+        if (!w && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_EPI, 34);
+        w = __all_sync(0xffffffffu, w);
+        if (!w) { ok = false; break; }
+      }
+      xch_mine[0] = m;
+      xch_mine[128] = l;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) xch_mine[(2 + c) * 128] = half ? o[c] : o[16 + c];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x_ready);
+      {
+        bool w = mbar_wait(x_ready, ic & 1);
+        if (!w && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_EPI, 35);
+        w = __all_sync(0xffffffffu, w);
+        if (!w) { ok = false; break; }
+      }
+      const float pm = xch_other[0], pl = xch_other[128];
+      float po[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) po[c] = xch_other[(2 + c) * 128];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x_done);
+      const float mt = fmaxf(m, pm);                           // finite: block 0 of half 0 always holds a key in range
+      const float w_me = ex2f((m - mt) * LOG2E), w_ot = ex2f((pm - mt) * LOG2E);
+      const float lt = l * w_me + pl * w_ot;
       const int qrow = q0 + r;
       if (qrow < a.n_q) {
-        const float inv = 1.f / l;
-        bf16* dst = a.out + (long long)b * a.out_bstride + (long long)qrow * a.out_rstride + h * D;
+        const float inv = 1.f / lt;
+        const float f_me = w_me * inv, f_ot = w_ot * inv;
+        bf16* dst = a.out + (long long)b * a.out_bstride + (long long)qrow * a.out_rstride + h * D + half * 16;
 #pragma unroll
-        for (int c = 0; c < D; c += 8) {
+        for (int c = 0; c < 16; c += 8) {
           uint4 pk;
           bf162* hp = reinterpret_cast<bf162*>(&pk);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) hp[e] = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
+          for (int e = 0; e < 4; ++e) {
+            const int cc = c + 2 * e;
+            const float mine0 = half ? o[16 + cc] : o[cc], mine1 = half ? o[16 + cc + 1] : o[cc + 1];
+            hp[e] = __floats2bfloat162_rn(mine0 * f_me + po[cc] * f_ot, mine1 * f_me + po[cc + 1] * f_ot);
+          }
           *reinterpret_cast<uint4*>(dst + c) = pk;
         }
-        if (a.lse2) a.lse2[((long long)b * a.H + h) * a.n_q + qrow] = m2 + log2f(l);
+        if (a.lse2 && half == 0) a.lse2[((long long)b * a.H + h) * a.n_q + qrow] = mt * LOG2E + log2f(lt);
       }
     }
   }
@@ -435,7 +525,7 @@ int ffb_attention_fwd(const void* q, const void* k, const void* v, long long q_b
   if (items <= 0 || items > 0x7fffffffLL) return -6;
   a.items = (int)items;
   a.bias_resident = (bias && a.n_kb <= 2) ? 1 : 0;
-  a.scale_log2e = scale * LOG2E;
+  a.scale = scale;
   a.mask = (const bf16*)mask;
   a.mask_bstride = mask_bstride;
   a.out = (bf16*)out;
@@ -549,17 +639,17 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
       mbar_init(kv_full + 8 * s, 1);
       mbar_init(kv_empty + 8 * s, 1);
       mbar_init(bias_full + 8 * s, 1);
-      mbar_init(bias_empty + 8 * s, 4);
+      mbar_init(bias_empty + 8 * s, 8);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 4);
-    mbar_init(pds_full, 4);
+    mbar_init(sdp_empty, 8);
+    mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     mbar_init(dkv_full, 1);
-    mbar_init(dkv_empty, 4);
+    mbar_init(dkv_empty, 8);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 4);
-    mbar_init(drow_ready, 4);
+    mbar_init(dq_empty, 8);
+    mbar_init(drow_ready, 8);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -673,8 +763,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
     }
     __syncwarp();
   } else {
-    // ---------------- softmax-gradient warps (thread = row) ----------------
-    const int quad = warp & 3;
+    // ---------------- softmax-gradient warps: thread = (row, 64-key half of the block) ----------------
+    const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
     const int HD = a.H * D;
@@ -682,8 +773,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
     bool ok = true;
     for (int item = blockIdx.x; item < a.items && ok; item += gridDim.x, ++ic) {
       const int b = item / a.H, h = item % a.H;
-      // D_i = rowsum(dO o O) and L2_i for every query row of this (b, h): 4 warps x 32 rows per sweep
-      for (int row = r; row < a.n_qt * AT_BQ; row += 128) {
+      // D_i = rowsum(dO o O) and L2_i for every query row of this (b, h): 8 warps x 32 rows per sweep
+      for (int row = half * 128 + r; row < a.n_qt * AT_BQ; row += 256) {
         float dsum = 0.f, l2 = 0.f;
         if (row < a.n_q) {
           const bf16* op = a.o + ((long long)b * a.n_q + row) * HD + h * D;
@@ -703,7 +794,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
         drow[row] = dsum;
         lrow[row] = l2;
       }
-      // the four warps read each other's rows later: make the writes visible to all of them
+      // the warps read each other's rows later: make the writes visible to all of them
       __syncwarp();
       if (lane == 0) mbar_arrive(drow_ready);
       if (!mbar_wait(drow_ready, ic & 1)) { if (lane == 0) report(ST_TIMEOUT_EPI, 70); ok = false; }
@@ -723,74 +814,77 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
           w = __all_sync(0xffffffffu, w);
           if (!w) { ok = false; break; }
           tc_fence_after();
-          const float Di = drow[qrow], L2 = lrow[qrow];
           const bool row_ok = qrow < a.n_q;
-          const uint8_t* btile = sm + BwdSmem::BIAS + s * 32768;
-          uint8_t* ptile = sm + BwdSmem::P;
-          uint8_t* dstile = sm + BwdSmem::DS;
-          bf16* ds_g = (a.ds && row_ok) ? a.ds + (((long long)b * a.H + h) * a.n_q + qrow) * a.n_k + k0 : nullptr;
-#pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
-            float sv[64], dpv[64];
-            tmem_ld_32x32(lane_base + TM_S + half * 64, sv);
-            tmem_ld_32x32(lane_base + TM_S + half * 64 + 32, sv + 32);
-            tmem_ld_32x32(lane_base + TM_DP + half * 64, dpv);
-            tmem_ld_32x32(lane_base + TM_DP + half * 64 + 32, dpv + 32);
-            tmem_ld_wait();
+          const float Di = drow[qrow];
+          const float nL2 = row_ok ? -lrow[qrow] : -INFINITY;     // rows past the end: p = exp2(-inf) = 0
+          const int kbase = k0 + half * 64;
+          uint32_t keep_lo, keep_hi, valid_lo, valid_hi;
+          key_bits(mrow, kbase, a.n_k, lane, keep_lo, keep_hi, valid_lo, valid_hi);
+          const bool plain = (keep_lo & keep_hi) == 0xffffffffu;
+          const uint8_t* brow = sm + BwdSmem::BIAS + s * 32768 + half * 16384 + r * 128;
+          uint8_t* prow = sm + BwdSmem::P + half * 16384 + r * 128;
+          uint8_t* dsrow = sm + BwdSmem::DS + half * 16384 + r * 128;
+          bf16* ds_g = (a.ds && row_ok) ? a.ds + (((long long)b * a.H + h) * a.n_q + qrow) * a.n_k + kbase : nullptr;
+          float sv[64], dpv[64];
+          tmem_ld_32x32(lane_base + TM_S + half * 64, sv);
+          tmem_ld_32x32(lane_base + TM_S + half * 64 + 32, sv + 32);
+          tmem_ld_32x32(lane_base + TM_DP + half * 64, dpv);
+          tmem_ld_32x32(lane_base + TM_DP + half * 64 + 32, dpv + 32);
+          tmem_ld_wait();
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int cu = half * 8 + u;                   // 16-byte unit index within the 128-key row
-              float bv[8], mk[8];
-              if (a.has_bias) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(btile + half * 16384 + r * 128 + ((u ^ (r & 7)) << 4));
-                const bf162* hp = reinterpret_cast<const bf162*>(&raw);
+          for (int u = 0; u < 8; ++u) {
+            float v[8];
+            if (a.has_bias) {
+              const uint4 raw = *reinterpret_cast<const uint4*>(brow + ((u ^ (r & 7)) << 4));
+              v[0] = fmaf(sv[u * 8 + 0], a.scale, bf_lo(raw.x));
+              v[1] = fmaf(sv[u * 8 + 1], a.scale, bf_hi(raw.x));
+              v[2] = fmaf(sv[u * 8 + 2], a.scale, bf_lo(raw.y));
+              v[3] = fmaf(sv[u * 8 + 3], a.scale, bf_hi(raw.y));
+              v[4] = fmaf(sv[u * 8 + 4], a.scale, bf_lo(raw.z));
+              v[5] = fmaf(sv[u * 8 + 5], a.scale, bf_hi(raw.z));
+              v[6] = fmaf(sv[u * 8 + 6], a.scale, bf_lo(raw.w));
+              v[7] = fmaf(sv[u * 8 + 7], a.scale, bf_hi(raw.w));
+            } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 f = __bfloat1622float2(hp[e]);
-                  bv[2 * e] = f.x;
-                  bv[2 * e + 1] = f.y;
-                }
-              } else {
+              for (int e = 0; e < 8; ++e) v[e] = sv[u * 8 + e] * a.scale;
+            }
+            float pe[8], g[8];
+            if (plain) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) bv[e] = 0.f;
+              for (int e = 0; e < 8; ++e) pe[e] = ex2f(fmaf(v[e], LOG2E, nL2));
+            } else {
+              // masked logits are -1e9: the exponent of a fully masked row is only known to a few hundred units, so it is
+              // clamped to 0 (p <= 1 always); keys past the end get p = 0
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const int c = u * 8 + e;
+                const uint32_t keep = c < 32 ? keep_lo : keep_hi, valid = c < 32 ? valid_lo : valid_hi;
+                const float vv = ((keep >> (c & 31)) & 1u) ? v[e] : -1e9f;
+                float pp = ex2f(fminf(fmaf(vv, LOG2E, nL2), 0.f));
+                if (!((valid >> (c & 31)) & 1u)) pp = 0.f;
+                pe[e] = pp;
               }
-              const int kk = k0 + cu * 8;
-              if (mrow) {
+            }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) mk[e] = (kk + e < a.n_k) ? __bfloat162float(mrow[kk + e]) : 0.f;
-              } else {
+            for (int e = 0; e < 8; ++e) g[e] = pe[e] * (dpv[u * 8 + e] - Di);
+            uint4 pp, dd, dg;
+            bf162 *hpp = reinterpret_cast<bf162*>(&pp), *hdd = reinterpret_cast<bf162*>(&dd), *hdg = reinterpret_cast<bf162*>(&dg);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) mk[e] = 1.f;
-              }
-              uint4 pp, dd, dg;
-              bf162 *hpp = reinterpret_cast<bf162*>(&pp), *hdd = reinterpret_cast<bf162*>(&dd), *hdg = reinterpret_cast<bf162*>(&dg);
-#pragma unroll
-              for (int e = 0; e < 8; e += 2) {
-                float p[2], g[2];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                  const int c = u * 8 + e + q;
-                  float v = sv[c] * a.scale_log2e + bv[e + q] * LOG2E;
-                  if (mk[e + q] == 0.f) v = -1e9f * LOG2E;
-                  float pe = ex2f(v - L2);
-                  if (!row_ok || kk + e + q >= a.n_k) pe = 0.f;
-                  p[q] = pe;
-                  g[q] = pe * (dpv[c] - Di);
-                }
-                hpp[e >> 1] = __floats2bfloat162_rn(p[0], p[1]);
-                hdg[e >> 1] = __floats2bfloat162_rn(g[0], g[1]);
-                hdd[e >> 1] = __floats2bfloat162_rn(g[0] * a.scale, g[1] * a.scale);
-              }
-              const uint32_t off = half * 16384 + r * 128 + ((u ^ (r & 7)) << 4);
-              *reinterpret_cast<uint4*>(ptile + off) = pp;
-              *reinterpret_cast<uint4*>(dstile + off) = dd;
-              if (ds_g) {
-                if (kk + 8 <= a.n_k) *reinterpret_cast<uint4*>(ds_g + cu * 8) = dg;
-                else {
-                  const bf16* src = reinterpret_cast<const bf16*>(&dg);
-                  for (int e = 0; e < 8; ++e)
-                    if (kk + e < a.n_k) ds_g[cu * 8 + e] = src[e];
-                }
+            for (int e = 0; e < 4; ++e) {
+              hpp[e] = __floats2bfloat162_rn(pe[2 * e], pe[2 * e + 1]);
+              hdg[e] = __floats2bfloat162_rn(g[2 * e], g[2 * e + 1]);
+              hdd[e] = __floats2bfloat162_rn(g[2 * e] * a.scale, g[2 * e + 1] * a.scale);
+            }
+            const uint32_t off = (u ^ (r & 7)) << 4;
+            *reinterpret_cast<uint4*>(prow + off) = pp;
+            *reinterpret_cast<uint4*>(dsrow + off) = dd;
+            if (ds_g) {
+              const int kk = kbase + u * 8;
+              if (kk + 8 <= a.n_k) *reinterpret_cast<uint4*>(ds_g + u * 8) = dg;
+              else {
+                const bf16* src = reinterpret_cast<const bf16*>(&dg);
+                for (int e = 0; e < 8; ++e)
+                  if (kk + e < a.n_k) ds_g[u * 8 + e] = src[e];
               }
             }
           }
@@ -811,28 +905,22 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
           w = __all_sync(0xffffffffu, w);
           if (!w) { ok = false; break; }
           tc_fence_after();
-          float gv[D], gk[D];
-          tmem_ld_32x32(lane_base + TM_DV, gv);
-          tmem_ld_32x32(lane_base + TM_DK, gk);
+          float gg[D];
+          tmem_ld_32x32(lane_base + (half ? TM_DK : TM_DV), gg);     // keys 0-63 group stores dV, the other dK
           tmem_ld_wait();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(dkv_empty);
           const int krow = k0 + r;
           if (krow < a.n_k) {
-            bf16* pv = a.dv + (long long)b * a.dkv_bstride + (long long)krow * HD + h * D;
-            bf16* pk = a.dk + (long long)b * a.dkv_bstride + (long long)krow * HD + h * D;
+            bf16* pg = (half ? a.dk : a.dv) + (long long)b * a.dkv_bstride + (long long)krow * HD + h * D;
 #pragma unroll
             for (int c = 0; c < D; c += 8) {
-              uint4 x, y;
-              bf162 *hx = reinterpret_cast<bf162*>(&x), *hy = reinterpret_cast<bf162*>(&y);
+              uint4 x;
+              bf162* hx = reinterpret_cast<bf162*>(&x);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                hx[e] = __floats2bfloat162_rn(gv[c + 2 * e], gv[c + 2 * e + 1]);
-                hy[e] = __floats2bfloat162_rn(gk[c + 2 * e], gk[c + 2 * e + 1]);
-              }
-              *reinterpret_cast<uint4*>(pv + c) = x;
-              *reinterpret_cast<uint4*>(pk + c) = y;
+              for (int e = 0; e < 4; ++e) hx[e] = __floats2bfloat162_rn(gg[c + 2 * e], gg[c + 2 * e + 1]);
+              *reinterpret_cast<uint4*>(pg + c) = x;
             }
           }
         }
@@ -845,7 +933,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
         w = __all_sync(0xffffffffu, w);
         if (!w) { ok = false; break; }
         tc_fence_after();
-        for (int i = 0; i < a.n_qt; ++i) {
+        for (int i = half; i < a.n_qt; i += 2) {
           float gq[D];
           tmem_ld_32x32(lane_base + TM_DQ + i * 32, gq);
           tmem_ld_wait();

@@ -162,3 +162,130 @@ class FeaturePipeline:
             per_iter.append(d)
         out = {k: torch.stack([d[k] for d in per_iter], dim=-1) for k in per_iter[0]}
         return out
+
+
+# ---------------------------------------------------------------------------
+# Running the alignment tools (fastfold/data/data_pipeline.py:262-560)
+# ---------------------------------------------------------------------------
+class AlignmentRunner:
+    """Runs whichever searches have both a binary and a database, and writes their results into ``output_dir``:
+
+    ``uniref90_hits.a3m`` (jackhmmer), ``pdb70_hits.hhr`` (hhsearch on the uniref90 profile), ``mgnify_hits.a3m``
+    (jackhmmer) and ``bfd_uniref_hits.a3m`` (hhblits on BFD + UniRef30) or ``small_bfd_hits.sto`` (jackhmmer on small
+    BFD).  The three independent searches run concurrently (they are subprocess-bound).
+    """
+
+    def __init__(self, jackhmmer_binary_path=None, hhblits_binary_path=None, hhsearch_binary_path=None, uniref90_database_path=None,
+                 mgnify_database_path=None, bfd_database_path=None, uniref30_database_path=None, pdb70_database_path=None,
+                 use_small_bfd=None, no_cpus=None, uniref_max_hits: int = 10000, mgnify_max_hits: int = 5000):
+        from . import tools
+        groups = {"jackhmmer": (jackhmmer_binary_path, [uniref90_database_path, mgnify_database_path, bfd_database_path if use_small_bfd else None]),
+                  "hhblits": (hhblits_binary_path, [bfd_database_path if not use_small_bfd else None]),
+                  "hhsearch": (hhsearch_binary_path, [pdb70_database_path])}
+        for name, (binary, dbs) in groups.items():
+            if binary is None and any(d is not None for d in dbs):
+                raise ValueError("%s DBs provided but %s binary is None" % (name, name))
+        if pdb70_database_path is not None and uniref90_database_path is None:
+            raise ValueError("uniref90_database_path must be specified in order to perform template search")
+        self.uniref_max_hits, self.mgnify_max_hits, self.use_small_bfd = uniref_max_hits, mgnify_max_hits, use_small_bfd
+        n_cpu = no_cpus or os.cpu_count() or 1
+        mk_jack = lambda db: tools.Jackhmmer(binary_path=jackhmmer_binary_path, database_path=db, n_cpu=n_cpu) if db else None
+        self.jackhmmer_uniref90_runner = mk_jack(uniref90_database_path) if jackhmmer_binary_path else None
+        self.jackhmmer_mgnify_runner = mk_jack(mgnify_database_path) if jackhmmer_binary_path else None
+        self.jackhmmer_small_bfd_runner = mk_jack(bfd_database_path) if (jackhmmer_binary_path and use_small_bfd) else None
+        self.hhblits_bfd_uniref_runner = None
+        if bfd_database_path is not None and not use_small_bfd:
+            dbs = [bfd_database_path] + ([uniref30_database_path] if uniref30_database_path else [])
+            self.hhblits_bfd_uniref_runner = tools.HHBlits(binary_path=hhblits_binary_path, databases=dbs, n_cpu=n_cpu)
+        self.hhsearch_pdb70_runner = None
+        if pdb70_database_path is not None:
+            self.hhsearch_pdb70_runner = tools.HHSearch(binary_path=hhsearch_binary_path, databases=[pdb70_database_path], n_cpu=n_cpu)
+
+    def _uniref_and_templates(self, fasta_path, output_dir):
+        if self.jackhmmer_uniref90_runner is None:
+            return
+        sto = self.jackhmmer_uniref90_runner.query(fasta_path)[0]["sto"]
+        a3m = parsers.convert_stockholm_to_a3m(sto, max_sequences=self.uniref_max_hits)
+        with open(os.path.join(output_dir, "uniref90_hits.a3m"), "w") as f:
+            f.write(a3m)
+        if self.hhsearch_pdb70_runner is not None:
+            with open(os.path.join(output_dir, "pdb70_hits.hhr"), "w") as f:
+                f.write(self.hhsearch_pdb70_runner.query(a3m))
+
+    def _mgnify(self, fasta_path, output_dir):
+        if self.jackhmmer_mgnify_runner is None:
+            return
+        sto = self.jackhmmer_mgnify_runner.query(fasta_path)[0]["sto"]
+        with open(os.path.join(output_dir, "mgnify_hits.a3m"), "w") as f:
+            f.write(parsers.convert_stockholm_to_a3m(sto, max_sequences=self.mgnify_max_hits))
+
+    def _bfd(self, fasta_path, output_dir):
+        if self.use_small_bfd and self.jackhmmer_small_bfd_runner is not None:
+            with open(os.path.join(output_dir, "small_bfd_hits.sto"), "w") as f:
+                f.write(self.jackhmmer_small_bfd_runner.query(fasta_path)[0]["sto"])
+        elif self.hhblits_bfd_uniref_runner is not None:
+            with open(os.path.join(output_dir, "bfd_uniref_hits.a3m"), "w") as f:
+                f.write(self.hhblits_bfd_uniref_runner.query(fasta_path)["a3m"])
+
+    def run(self, fasta_path: str, output_dir: str):
+        from concurrent.futures import ThreadPoolExecutor
+        os.makedirs(output_dir, exist_ok=True)
+        with ThreadPoolExecutor(max_workers=3) as pool:
+            jobs = [pool.submit(fn, fasta_path, output_dir) for fn in (self._uniref_and_templates, self._mgnify, self._bfd)]
+            for j in jobs:
+                j.result()
+
+
+class AlignmentRunnerMultimer(AlignmentRunner):
+    """Per-chain searches of the multimer pipeline: Stockholm outputs (kept for species pairing), a UniProt search and
+    an hmmsearch template search on PDB seqres (fastfold/data/data_pipeline.py:458-560)."""
+
+    def __init__(self, jackhmmer_binary_path=None, hhblits_binary_path=None, hmmsearch_binary_path=None, hmmbuild_binary_path=None,
+                 uniref90_database_path=None, mgnify_database_path=None, bfd_database_path=None, uniref30_database_path=None,
+                 uniprot_database_path=None, pdb_seqres_database_path=None, use_small_bfd=None, no_cpus=None, uniref_max_hits: int = 10000,
+                 mgnify_max_hits: int = 5000, uniprot_max_hits: int = 50000):
+        from . import tools
+        super().__init__(jackhmmer_binary_path=jackhmmer_binary_path, hhblits_binary_path=hhblits_binary_path,
+                         uniref90_database_path=uniref90_database_path, mgnify_database_path=mgnify_database_path,
+                         bfd_database_path=bfd_database_path, uniref30_database_path=uniref30_database_path, use_small_bfd=use_small_bfd,
+                         no_cpus=no_cpus, uniref_max_hits=uniref_max_hits, mgnify_max_hits=mgnify_max_hits)
+        self.uniprot_max_hits = uniprot_max_hits
+        n_cpu = no_cpus or os.cpu_count() or 1
+        self.jackhmmer_uniprot_runner = None
+        if uniprot_database_path is not None:
+            self.jackhmmer_uniprot_runner = tools.Jackhmmer(binary_path=jackhmmer_binary_path, database_path=uniprot_database_path, n_cpu=n_cpu)
+        self.hmmsearch_pdb_runner = None
+        if pdb_seqres_database_path is not None:
+            self.hmmsearch_pdb_runner = tools.Hmmsearch(binary_path=hmmsearch_binary_path, hmmbuild_binary_path=hmmbuild_binary_path,
+                                                        database_path=pdb_seqres_database_path)
+
+    def _uniref_and_templates(self, fasta_path, output_dir):
+        if self.jackhmmer_uniref90_runner is None:
+            return
+        sto = self.jackhmmer_uniref90_runner.query(fasta_path, max_sequences=self.uniref_max_hits)[0]["sto"]
+        with open(os.path.join(output_dir, "uniref90_hits.sto"), "w") as f:
+            f.write(sto)
+        if self.hmmsearch_pdb_runner is not None:
+            clean = parsers.remove_empty_columns_from_stockholm_msa(parsers.deduplicate_stockholm_msa(sto))
+            with open(os.path.join(output_dir, "pdb_hits.sto"), "w") as f:
+                f.write(self.hmmsearch_pdb_runner.query(clean))
+
+    def _mgnify(self, fasta_path, output_dir):
+        if self.jackhmmer_mgnify_runner is None:
+            return
+        with open(os.path.join(output_dir, "mgnify_hits.sto"), "w") as f:
+            f.write(self.jackhmmer_mgnify_runner.query(fasta_path, max_sequences=self.mgnify_max_hits)[0]["sto"])
+
+    def _uniprot(self, fasta_path, output_dir):
+        if self.jackhmmer_uniprot_runner is None:
+            return
+        with open(os.path.join(output_dir, "uniprot_hits.sto"), "w") as f:
+            f.write(self.jackhmmer_uniprot_runner.query(fasta_path, max_sequences=self.uniprot_max_hits)[0]["sto"])
+
+    def run(self, fasta_path: str, output_dir: str):
+        from concurrent.futures import ThreadPoolExecutor
+        os.makedirs(output_dir, exist_ok=True)
+        with ThreadPoolExecutor(max_workers=4) as pool:
+            jobs = [pool.submit(fn, fasta_path, output_dir) for fn in (self._uniref_and_templates, self._mgnify, self._bfd, self._uniprot)]
+            for j in jobs:
+                j.result()

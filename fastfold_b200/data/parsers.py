@@ -78,13 +78,6 @@ def parse_stockholm(stockholm_string: str) -> Tuple[List[str], DeletionMatrix, L
     return msa, deletion_matrix, list(name_to_seq.keys())
 
 
-def convert_stockholm_to_a3m(stockholm_format: str, max_sequences: Optional[int] = None) -> str:
-    msa, _, names = parse_stockholm(stockholm_format)
-    if max_sequences:
-        msa, names = msa[:max_sequences], names[:max_sequences]
-    return "\n".join(">%s\n%s" % (n, s) for n, s in zip(names, msa)) + "\n"
-
-
 def deduplicate_stockholm_msa(stockholm_msa: str) -> str:
     seen, keep = set(), set()
     for line in stockholm_msa.splitlines():
@@ -139,4 +132,153 @@ def parse_hhr(hhr_string: str) -> Sequence[TemplateHit]:
                     ih.append(-1 if ch == "-" else pos)
                     pos += ch != "-"
         hits.append(TemplateHit(number, name, aligned_cols, sum_probs, query, hit, iq, ih))
+    return hits
+
+
+# ---------------------------------------------------------------------------
+# Stockholm utilities used by the alignment runner (fastfold/data/parsers.py:186-330)
+# ---------------------------------------------------------------------------
+def _keep_stockholm_lines(lines: Iterable[str], names: set) -> str:
+    """Header, per-file annotations and every line that belongs to one of ``names``."""
+    out = []
+    for line in lines:
+        s = line.strip()
+        if not s or s.startswith("//") or s.startswith("# STOCKHOLM"):
+            continue
+        if s.startswith("#=GS") or s.startswith("#=GR"):
+            if s.split()[1] in names:
+                out.append(line.rstrip("\n"))
+        elif s.startswith("#"):
+            out.append(line.rstrip("\n"))          # #=GF / #=GC apply to the whole alignment
+        elif s.split()[0] in names:
+            out.append(line.rstrip("\n"))
+    return "# STOCKHOLM 1.0\n" + "\n".join(out) + "\n//\n"
+
+
+def truncate_stockholm_msa(stockholm_msa_path: str, max_sequences: int) -> str:
+    """The first ``max_sequences`` sequences of a (possibly huge) Stockholm file, read in two streaming passes."""
+    names = set()
+    with open(stockholm_msa_path) as f:
+        for line in f:
+            s = line.strip()
+            if s and not s.startswith(("#", "//")):
+                names.add(s.split()[0])
+                if len(names) >= max_sequences:
+                    break
+    with open(stockholm_msa_path) as f:
+        return _keep_stockholm_lines(f, names)
+
+
+def remove_empty_columns_from_stockholm_msa(stockholm_msa: str) -> str:
+    """Drop the columns that are gaps in the query (first sequence) of every block."""
+    out, block = [], []
+
+    def flush():
+        rows = [ln for ln in block if ln.strip() and not ln.startswith("#")]
+        if not rows:
+            out.extend(block)
+            return
+        first = rows[0].split()[1]
+        keep = [i for i, ch in enumerate(first) if ch != "-"]
+        for ln in block:
+            if not ln.strip():
+                out.append(ln)
+                continue
+            if ln.startswith("#=GC") or ln.startswith("#=GR") or not ln.startswith("#"):
+                head, _, data = ln.rpartition(" ")
+                if len(data) == len(first):
+                    data = "".join(data[i] for i in keep)
+                    out.append(head + " " + data)
+                    continue
+            out.append(ln)
+
+    for line in stockholm_msa.splitlines():
+        if not line.strip() or line.startswith("//"):
+            flush()
+            block = []
+            out.append(line)
+        else:
+            block.append(line)
+    flush()
+    return "\n".join(out) + "\n"
+
+
+def convert_stockholm_to_a3m(stockholm_format: str, max_sequences: Optional[int] = None, remove_first_row_gaps: bool = True) -> str:
+    """Stockholm -> A3M: columns that are gaps in the query become lower-case insertions in the other rows."""
+    descriptions, sequences = {}, collections.OrderedDict()
+    for line in stockholm_format.splitlines():
+        s = line.strip()
+        if not s or s.startswith("//"):
+            continue
+        if s.startswith("#=GS"):
+            parts = s.split(maxsplit=3)
+            if len(parts) == 4 and parts[2] == "DE":
+                descriptions[parts[1]] = parts[3]
+            continue
+        if s.startswith("#"):
+            continue
+        name, seq = s.split()
+        if name not in sequences:
+            if max_sequences and len(sequences) >= max_sequences:
+                continue
+            sequences[name] = ""
+        sequences[name] += seq
+    if not sequences:
+        return ""
+    query = next(iter(sequences.values()))
+    out = []
+    for name, seq in sequences.items():
+        if remove_first_row_gaps:
+            chars = []
+            for q, c in zip(query, seq):
+                if q != "-":
+                    chars.append(c)
+                elif c != "-":
+                    chars.append(c.lower())
+            seq = "".join(chars)
+        else:
+            seq = seq.replace(".", "")
+        out.append(">%s %s\n%s" % (name, descriptions.get(name, ""), seq))
+    return "\n".join(out) + "\n"
+
+
+def parse_e_values_from_tblout(tblout: str) -> Dict[str, float]:
+    e_values = {"query": 0.0}
+    for line in tblout.splitlines():
+        if line and not line.startswith("#"):
+            f = line.split()
+            e_values[f[0]] = float(f[4])
+    return e_values
+
+
+def _hmmsearch_description(desc: str):
+    """``<pdb>_<chain>/<start>-<end> mol:protein length:<n>  <text>`` -> (name, start, end, length)."""
+    m = re.match(r"^([a-zA-Z\d]{4}_[a-zA-Z0-9.]+)/(\d+)-(\d+).*?length:(\d+)", desc.strip())
+    if not m:
+        raise ValueError("Could not parse hmmsearch description %r" % desc)
+    return m.group(1), int(m.group(2)), int(m.group(3)), int(m.group(4))
+
+
+def parse_hmmsearch_a3m(query_sequence: str, a3m_string: str, skip_first: bool = True) -> Sequence[TemplateHit]:
+    """Template hits from an hmmsearch alignment converted to A3M (multimer template search)."""
+    seqs, descs = parse_fasta(a3m_string)
+    pairs = list(zip(seqs, descs))[1 if skip_first else 0:]
+    iq = [-1 if ch == "-" else i for i, ch in enumerate(query_sequence)]
+    hits = []
+    for i, (seq, desc) in enumerate(pairs, 1):
+        if "mol:protein" not in desc:
+            continue
+        name, start, _, _ = _hmmsearch_description(desc)
+        aligned = sum(1 for ch in seq if ch.isupper())
+        ih, pos = [], start - 1
+        for ch in seq:
+            if ch == "-":
+                ih.append(-1)
+            else:
+                ih.append(pos)
+                pos += 1
+        upper = seq.upper()
+        # insertions relative to the query (lower case) have no query column: drop them from the pairing
+        cols = [k for k, ch in enumerate(seq) if not ch.islower()]
+        hits.append(TemplateHit(i, name, aligned, None, query_sequence, "".join(upper[k] for k in cols), iq, [ih[k] for k in cols]))
     return hits

@@ -17,6 +17,7 @@ def _qkv(B, n, H, d=32):
 @pytest.mark.parametrize("B,n,H,use_bias,use_mask", [
     (4, 128, 8, True, True), (128, 256, 8, True, True), (37, 256, 4, True, False), (256, 128, 8, False, True),
     (3, 384, 4, True, True), (2, 200, 4, True, True), (5, 1024, 4, True, True), (9, 72, 8, False, False),
+    (3, 40, 4, True, True), (300, 256, 4, True, False),
 ])
 def test_forward(B, n, H, use_bias, use_mask, device_status):
     torch.manual_seed(B * 1000 + n)
@@ -66,3 +67,30 @@ def test_backward(B, n, H, use_bias, use_mask, device_status):
         berr = (bias.grad.float() - bias_r.grad).abs().max().item()
         bmax = bias_r.grad.abs().max().item()
         assert berr < 3e-2 * max(1.0, bmax), "dbias err %g (max %g)" % (berr, bmax)
+
+
+def test_backward_fully_masked_row_stays_finite(device_status):
+    """A batch row whose keys are all masked (a padded MSA row) must not poison the other rows' gradients."""
+    torch.manual_seed(5)
+    B, n, H = 6, 256, 4
+    qkv = (torch.randn(1, B, n, 3, H, 32, device=DEV) * 0.7).to(torch.bfloat16).requires_grad_(True)
+    bias = torch.randn(1, 1, H, n, n, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    mask = torch.ones(1, B, n, device=DEV, dtype=torch.bfloat16)
+    mask[0, 2] = 0
+    q, k, v = (qkv[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
+    out = attention_core(q, k, v, mask, bias)
+    g = torch.randn_like(out)
+    g[:, 2] = 0                      # the model multiplies masked rows away downstream
+    out.backward(g)
+    assert torch.isfinite(out.float()).all()
+    assert torch.isfinite(qkv.grad.float()).all() and torch.isfinite(bias.grad.float()).all()
+    qkv_r = qkv.detach().float().requires_grad_(True)
+    bias_r = bias.detach().float().requires_grad_(True)
+    qr, kr, vr = (qkv_r[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
+    ref = attention_core_ref(qr, kr, vr, mask.float(), bias_r)
+    ref.backward(g.float())
+    keep = [0, 1, 3, 4, 5]
+    gerr = (qkv.grad.float()[:, keep] - qkv_r.grad[:, keep]).abs().max().item()
+    assert gerr < 3e-2 * max(1.0, qkv_r.grad.abs().max().item())
+    berr = (bias.grad.float() - bias_r.grad).abs().max().item()
+    assert berr < 3e-2 * max(1.0, bias_r.grad.abs().max().item())
