@@ -590,11 +590,12 @@ struct AttnBwdArgs {
   float scale, scale_log2e;
   const bf16* mask;
   long long mask_bstride;
-  const bf16* o;      // [B][n_q][H*D] (forward output, contiguous)
-  const bf16* dout;   // [B][n_q][H*D]
+  const bf16* o;      // forward output and its gradient: element (b, row, h, c) at ptr[b * o_bstride + row * o_rstride + h * D + c]
+  const bf16* dout;
+  long long o_bstride, o_rstride;
   const float* lse2;  // [B][H][n_q]
-  bf16 *dq, *dk, *dv; // [B][n][H*D] each (row stride H*D)
-  long long dq_bstride, dkv_bstride;
+  bf16 *dq, *dk, *dv; // element (b, row, h, c) at ptr[b * bstride + row * rstride + h * D + c]
+  long long dq_bstride, dkv_bstride, dq_rstride, dkv_rstride;
   bf16* ds;           // [B][H][n_q][n_k] or null
   int has_bias;
 };
@@ -777,8 +778,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
       for (int row = half * 128 + r; row < a.n_qt * AT_BQ; row += 256) {
         float dsum = 0.f, l2 = 0.f;
         if (row < a.n_q) {
-          const bf16* op = a.o + ((long long)b * a.n_q + row) * HD + h * D;
-          const bf16* dp = a.dout + ((long long)b * a.n_q + row) * HD + h * D;
+          const bf16* op = a.o + (long long)b * a.o_bstride + (long long)row * a.o_rstride + h * D;
+          const bf16* dp = a.dout + (long long)b * a.o_bstride + (long long)row * a.o_rstride + h * D;
 #pragma unroll
           for (int c = 0; c < D; c += 8) {
             const uint4 uo = *reinterpret_cast<const uint4*>(op + c), ud = *reinterpret_cast<const uint4*>(dp + c);
@@ -913,7 +914,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
           if (lane == 0) mbar_arrive(dkv_empty);
           const int krow = k0 + r;
           if (krow < a.n_k) {
-            bf16* pg = (half ? a.dk : a.dv) + (long long)b * a.dkv_bstride + (long long)krow * HD + h * D;
+            bf16* pg = (half ? a.dk : a.dv) + (long long)b * a.dkv_bstride + (long long)krow * a.dkv_rstride + h * D;
 #pragma unroll
             for (int c = 0; c < D; c += 8) {
               uint4 x;
@@ -939,7 +940,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
           tmem_ld_wait();
           const int qrow = i * AT_BQ + r;
           if (qrow < a.n_q) {
-            bf16* pq = a.dq + (long long)b * a.dq_bstride + (long long)qrow * HD + h * D;
+            bf16* pq = a.dq + (long long)b * a.dq_bstride + (long long)qrow * a.dq_rstride + h * D;
 #pragma unroll
             for (int c = 0; c < D; c += 8) {
               uint4 x;
@@ -968,15 +969,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
 
 extern "C" {
 
-// Gradients of ffb_attention_fwd.  o / dout: [B][n_q][H*D] contiguous; dqkv: three [B][n_max][H*D] slabs
-// (dq, dk, dv; n_max = max(n_q, n_k)); ds: bf16 [B][H][n_q][n_k] (unscaled dS, for the bias gradient) or null.
-int ffb_attention_bwd(const void* q, const void* k, const void* v, long long q_bstride, long long q_rstride, long long kv_bstride,
-                      long long kv_rstride, const void* bias, const void* mask, long long mask_bstride, const void* o, const void* dout,
-                      const float* lse2, void* dqkv, void* ds, int B, int H, int n_q, int n_k, int D, float scale, void* stream) {
+// Gradients of ffb_attention_fwd.  o / dout: element (b, row, h, c) at ptr[b * o_bstride + row * o_rstride + h * D + c]
+// (the forward's out_bstride / out_rstride); dq / dk / dv: element (b, row, h, c) at
+// ptr[b * bstride + row * rstride + h * D + c], so the three gradients can be written straight into a packed
+// [B][n][3][H*D] tensor; ds: bf16 [B][H][n_q][n_k] (unscaled dS, for the bias gradient) or null.
+int ffb_attention_bwd_strided(const void* q, const void* k, const void* v, long long q_bstride, long long q_rstride,
+                              long long kv_bstride, long long kv_rstride, const void* bias, const void* mask, long long mask_bstride,
+                              const void* o, const void* dout, long long o_bstride, long long o_rstride, const float* lse2, void* dq,
+                              void* dk, void* dv, long long dq_bstride,
+                              long long dq_rstride, long long dkv_bstride, long long dkv_rstride, void* ds, int B, int H, int n_q,
+                              int n_k, int D, float scale, void* stream) {
   using namespace ffb;
   if (D != 32) return -2;
   if (n_q > 512) return -3;
   if ((q_rstride % 8) || (kv_rstride % 8) || (q_bstride % 8) || (kv_bstride % 8) || (n_k % 8)) return -4;
+  if ((dq_rstride % 8) || (dkv_rstride % 8) || (dq_bstride % 8) || (dkv_bstride % 8) || (o_bstride % 8) || (o_rstride % 8)) return -5;
   AttnBwdArgs a;
   a.B = B; a.H = H; a.n_q = n_q; a.n_k = n_k;
   a.n_qt = (n_q + AT_BQ - 1) / AT_BQ;
@@ -988,21 +995,24 @@ int ffb_attention_bwd(const void* q, const void* k, const void* v, long long q_b
   a.mask_bstride = mask_bstride;
   a.o = (const bf16*)o;
   a.dout = (const bf16*)dout;
+  a.o_bstride = o_bstride;
+  a.o_rstride = o_rstride;
   a.lse2 = lse2;
   const long long HD = (long long)H * D;
-  const long long n_max = n_q > n_k ? n_q : n_k;
-  a.dq = (bf16*)dqkv;
-  a.dk = a.dq + (long long)B * n_max * HD;
-  a.dv = a.dk + (long long)B * n_max * HD;
-  a.dq_bstride = n_max * HD;
-  a.dkv_bstride = n_max * HD;
+  a.dq = (bf16*)dq;
+  a.dk = (bf16*)dk;
+  a.dv = (bf16*)dv;
+  a.dq_bstride = dq_bstride;
+  a.dkv_bstride = dkv_bstride;
+  a.dq_rstride = dq_rstride;
+  a.dkv_rstride = dkv_rstride;
   a.ds = (bf16*)ds;
   a.has_bias = bias ? 1 : 0;
   CUtensorMap tq, tk, tv, tdo, tb;
   { int rc = make_tmap3(&tq, q, HD, n_q, B, q_rstride, q_bstride, D, AT_BQ, 64); if (rc) return -100000 - rc; }
   if (make_tmap3(&tk, k, HD, n_k, B, kv_rstride, kv_bstride, D, AT_BK, 64)) return -11;
   if (make_tmap3(&tv, v, HD, n_k, B, kv_rstride, kv_bstride, D, AT_BK, 64)) return -12;
-  { int rc = make_tmap3(&tdo, dout, HD, n_q, B, HD, (long long)n_q * HD, D, AT_BQ, 64); if (rc) return -130000 - rc; }
+  { int rc = make_tmap3(&tdo, dout, HD, n_q, B, o_rstride, o_bstride, D, AT_BQ, 64); if (rc) return -130000 - rc; }
   if (bias) {
     if (make_tmap3(&tb, bias, n_k, n_q, H, n_k, (long long)n_q * n_k, 64, AT_BQ, 128)) return -14;
   } else {
@@ -1022,6 +1032,20 @@ int ffb_attention_bwd(const void* q, const void* k, const void* v, long long q_b
   const int grid = a.items < sm_count ? a.items : sm_count;
   attn_bwd_kernel<32><<<grid, AT_THREADS, BwdSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, tdo, tb, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -16;
+}
+
+
+// Same, with the gradients in three [B][n_max][H*D] slabs (dq, dk, dv; n_max = max(n_q, n_k)) of one buffer.
+int ffb_attention_bwd(const void* q, const void* k, const void* v, long long q_bstride, long long q_rstride, long long kv_bstride,
+                      long long kv_rstride, const void* bias, const void* mask, long long mask_bstride, const void* o, const void* dout,
+                      const float* lse2, void* dqkv, void* ds, int B, int H, int n_q, int n_k, int D, float scale, void* stream) {
+  const long long HD = (long long)H * D;
+  const long long n_max = n_q > n_k ? n_q : n_k;
+  ffb::bf16* g = (ffb::bf16*)dqkv;
+  return ffb_attention_bwd_strided(q, k, v, q_bstride, q_rstride, kv_bstride, kv_rstride, bias, mask, mask_bstride, o, dout,
+                                   (long long)n_q * HD, HD, lse2, g,
+                                   g + (long long)B * n_max * HD, g + 2 * (long long)B * n_max * HD, n_max * HD, HD, n_max * HD, HD, ds,
+                                   B, H, n_q, n_k, D, scale, stream);
 }
 
 }  // extern "C"

@@ -29,6 +29,13 @@ struct GemmArgs {
   const void* resid;        // bf16 residual added last
   long long ldres, res_bstride;
   int peer_slab;            // gathered-operand GEMMs: extent of one rank's slab along the gathered (M or N) dimension
+  // Block-permuted bf16 output: with m = 32 * m1 + m0 and n = 32 * n1 + n0, element (m, n) goes to
+  // C[(m1 / cq_mdiv) * cq_sr2 + (m1 % cq_mdiv) * cq_sr1 + n1 * cq_sc1 + m0 * 32 + n0], i.e. every 32 x 32 block is
+  // contiguous (2 KB) and the blocks are placed by three free strides (d = e = 32 below):
+  //   [(i d), (j e)] -> [i][j][d][e]:      cq_mdiv = 1, cq_sr2 = J * 1024, cq_sr1 = 0, cq_sc1 = 1024
+  //   [(i j), (d e)] -> [(i d)][(j e)]:    cq_mdiv = J / 32, cq_sr2 = J * 1024, cq_sr1 = 1024, cq_sc1 = 32 * J
+  int cq, cq_mdiv;
+  long long cq_sr2, cq_sr1, cq_sc1;
 };
 
 // Tensor maps of the slabs of a gathered operand, one per rank of the DAP group (peer memory, plain TMA loads).

@@ -414,7 +414,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
           }
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            uint8_t* slot = obuf + lane * 128 + ((u ^ (lane & 7)) << 4);   // this thread's own row: read residual, write result
+            // this thread's own row: read residual, write result.  Block-permuted output: two linear [32][32] blocks
+            uint8_t* slot = g.cq ? obuf + (u >> 2) * 2048 + lane * 64 + ((u & 3) << 4) : obuf + lane * 128 + ((u ^ (lane & 7)) << 4);
             if (g.resid) {
               float t[8];
               load8(reinterpret_cast<const bf16*>(slot), true, 8, t);
@@ -430,9 +431,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&tmC),
-                         "r"(epi_smem + out_buf * 4096), "r"(col0), "r"(row0), "r"(tc.batch)
-                         : "memory");
+            if (g.cq) {
+              // each 32 x 32 block of the tile is one contiguous 2 KB run of the destination: plain bulk copies
+              const int m1 = row0 >> 5;
+              bf16* dst = reinterpret_cast<bf16*>(g.C) + (long long)tc.batch * g.c_bstride + (long long)(m1 / g.cq_mdiv) * g.cq_sr2 +
+                          (long long)(m1 % g.cq_mdiv) * g.cq_sr1 + (long long)(col0 >> 5) * g.cq_sc1;
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 2048;" ::"l"(dst), "r"(epi_smem + out_buf * 4096)
+                           : "memory");
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 2048;" ::"l"(dst + g.cq_sc1),
+                           "r"(epi_smem + out_buf * 4096 + 2048)
+                           : "memory");
+            } else {
+              asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&tmC),
+                           "r"(epi_smem + out_buf * 4096), "r"(col0), "r"(row0), "r"(tc.batch)
+                           : "memory");
+            }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
           out_buf ^= 1;
@@ -722,7 +735,12 @@ static int gemm_launch(const void* A, const void* B, int a_mn, int b_mn, long lo
   int tma_epi = (g.out_mode == OUT_BF16 && !g.trans_out && !g.glu && g.N >= 64 && al16(g.C, g.ldc, g.c_bstride) && (batch == 1 || g.c_bstride != 0)) ? 1 : 0;
   if (tma_epi && g.mul && !(al16(g.mul, g.ldmul, g.mul_bstride) && (batch == 1 || g.mul_bstride != 0))) tma_epi = 0;
   if (tma_epi && g.resid && !(al16(g.resid, g.ldres, g.res_bstride) && (batch == 1 || g.res_bstride != 0))) tma_epi = 0;
-  if (tma_epi) {
+  if (g.cq) {
+    // block-permuted store: bf16, whole 32 x 64 warp tiles only, no mul / residual tiles (they would be fetched in matrix layout)
+    if (g.out_mode != OUT_BF16 || g.trans_out || g.glu || g.mul || g.resid || (g.M % 32) || (g.N % 64)) return -23;
+    if ((reinterpret_cast<uintptr_t>(g.C) & 15) || (g.cq_sr1 % 8) || (g.cq_sr2 % 8) || (g.cq_sc1 % 8) || (g.c_bstride % 8) || g.cq_mdiv < 1) return -23;
+    tma_epi = 1;
+  } else if (tma_epi) {
     if (make_tmap_bf16(&epi[0], g.C, g.M, g.N, g.ldc, batch, g.c_bstride, 64, 32)) tma_epi = 0;
     if (tma_epi && g.mul && make_tmap_bf16(&epi[1], g.mul, g.M, g.N, g.ldmul, batch, g.mul_bstride, 64, 32)) tma_epi = 0;
     if (tma_epi && g.resid && make_tmap_bf16(&epi[2], g.resid, g.M, g.N, g.ldres, batch, g.res_bstride, 64, 32)) tma_epi = 0;

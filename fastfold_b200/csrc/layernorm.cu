@@ -236,14 +236,24 @@ __global__ void ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restr
 
 // dgamma[c] = sum_b part[b][0][c], dbeta[c] = sum_b part[b][1][c]
 template <typename T>
-__global__ void ln_bwd_reduce_kernel(const float* __restrict__ part, int nblocks, int C, T* __restrict__ dgamma,
-                                     T* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * C) return;
+__global__ void __launch_bounds__(1024) ln_bwd_reduce_kernel(const float* __restrict__ part, int nblocks, int C,
+                                                             T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  // block = 32 columns x 32 row slices: coalesced 128-byte reads, 32 partial sums per column folded through shared memory
+  __shared__ float acc[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += part[(long long)b * 2 * C + c];
-  if (c < C) dgamma[c] = from_f<T>(s);
-  else dbeta[c - C] = from_f<T>(s);
+  if (c < 2 * C)
+    for (int b = ty; b < nblocks; b += 32) s += part[(long long)b * 2 * C + c];
+  acc[ty][tx] = s;
+  __syncthreads();
+  // warp ty now owns column ty of the tile: lanes hold its 32 slices
+  float v = warp_sum(acc[tx][ty]);
+  const int co = blockIdx.x * 32 + ty;
+  if (tx == 0 && co < 2 * C) {
+    if (co < C) dgamma[co] = from_f<T>(v);
+    else dbeta[co - C] = from_f<T>(v);
+  }
 }
 
 // LayerNorm over the leading dimension of x[C][rows] (row index contiguous),
@@ -317,7 +327,7 @@ static int ln_bwd_dispatch(const T* dy, const T* x, const T* g, const float* mea
   else if (aligned && C <= 64 * VEC) ln_bwd_kernel<T, 2 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
   else if (aligned && C <= 128 * VEC) ln_bwd_kernel<T, 4 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
   else ln_bwd_generic_kernel<T><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
-  ln_bwd_reduce_kernel<T><<<(2 * C + 127) / 128, 128, 0, st>>>(part, nblocks, C, dgamma, dbeta);
+  ln_bwd_reduce_kernel<T><<<(2 * C + 31) / 32, 1024, 0, st>>>(part, nblocks, C, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

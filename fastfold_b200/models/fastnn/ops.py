@@ -23,6 +23,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ... import ops as K
+from ...ops import flash
 from ...ops.attention import attention_core
 from ...parallel import comm, core
 from ...parallel.comm import gather, scatter
@@ -160,18 +161,19 @@ class OutProductMean(nn.Module):
         N, e = right_all.shape[2], right_all.shape[3]
         l2 = left.reshape(S, ni * d)
         r2 = right_all.reshape(S, N * e)
-        if left.is_cuda and left.dtype == torch.bfloat16 and (ni * d) % 8 == 0 and (N * e) % 64 == 0 and ni * d >= 64:
-            if torch.is_grad_enabled() and (l2.requires_grad or r2.requires_grad):
-                o = _OuterProduct.apply(l2, r2)
+        if _fusable(Z_raw) and d == 32 and e == 32 and N % 32 == 0 and ni * d >= 64 and self.o_linear.bias is not None:
+            # the product [(i d), (j e)] leaves the GEMM epilogue already laid out as [i, j, d, e], the operand layout of
+            # the output projection; its gradient comes back the other way through the same block-permuting store
+            if torch.is_grad_enabled() and any(t.requires_grad for t in (l2, r2, Z_raw, self.o_linear.weight)):
+                out = _OpmCore.apply(l2, r2, self.o_linear.weight, self.o_linear.bias, inv_norm.reshape(-1), Z_raw.reshape(ni * N, -1))
             else:
-                o = K.gemm(l2, r2, a_mn=True, b_mn=True)          # [(i d), (j e)], contraction over S
+                out = _opm_forward(l2, r2, self.o_linear.weight, self.o_linear.bias, inv_norm.reshape(-1), Z_raw.reshape(ni * N, -1))[0]
+            return out.reshape(Z_raw.shape)
+        if left.is_cuda and left.dtype == torch.bfloat16 and (ni * d) % 8 == 0 and (N * e) % 64 == 0 and ni * d >= 64:
+            o = K.gemm(l2, r2, a_mn=True, b_mn=True) if not torch.is_grad_enabled() else _bmm_tn(l2, r2)
         else:
             o = torch.matmul(l2.t(), r2)
         o = o.reshape(ni, d, N, e).permute(0, 2, 1, 3).reshape(1, ni, N, d * e)
-        if _fusable(o):
-            out = K.gemm(o.reshape(ni * N, d * e), self.o_linear.weight, bias=self.o_linear.bias,
-                         rowscale=inv_norm.reshape(-1), resid=Z_raw.reshape(ni * N, -1))
-            return out.reshape(Z_raw.shape)
         return Z_raw + self.o_linear(o) * inv_norm.to(o.dtype)
 
     def forward(self, M, M_mask, Z_raw):
@@ -199,24 +201,44 @@ class OutProductMean(nn.Module):
         return Z_raw
 
 
-class _OuterProduct(torch.autograd.Function):
-    """o[(i d), (j e)] = sum_s l[s, (i d)] r[s, (j e)] with both gradients on the tcgen05 kernel."""
+def _opm_forward(l2, r2, w, bias, inv_norm, z2):
+    """o4 [i, j, d, e] = sum_s l2[s, (i d)] r2[s, (j e)];  out = z2 + inv_norm * (o4 W^T + bias)."""
+    S = l2.shape[0]
+    ni, N = l2.shape[1] // 32, r2.shape[1] // 32
+    o4 = K.gemm(l2, r2, a_mn=True, b_mn=True, block_out=((ni * N, 1024), 1, N * 1024, 0, 1024))
+    out = K.gemm(o4, w, bias=bias, rowscale=inv_norm, resid=z2)
+    return out, o4
+
+
+class _OpmCore(torch.autograd.Function):
+    """Outer product + output projection + normalisation + residual of the outer-product-mean module, with a hand-written
+    backward: five tcgen05 GEMMs and no permuted copy in either direction."""
 
     @staticmethod
-    def forward(ctx, l2, r2):
-        ctx.save_for_backward(l2, r2)
-        return K.gemm(l2, r2, a_mn=True, b_mn=True)
+    def forward(ctx, l2, r2, w, bias, inv_norm, z2):
+        out, o4 = _opm_forward(l2, r2, w, bias, inv_norm, z2)
+        ctx.save_for_backward(l2, r2, w, inv_norm, o4)
+        return out
 
     @staticmethod
-    def backward(ctx, do):
-        l2, r2 = ctx.saved_tensors
-        do = do.contiguous()
-        dl = dr = None
-        if ctx.needs_input_grad[0]:
-            dl = K.gemm(r2, do)                      # [S, (i d)] = r2 [S, (j e)] x do [(i d), (j e)]^T
-        if ctx.needs_input_grad[1]:
-            dr = K.gemm(l2, do, b_mn=True)           # [S, (j e)] = l2 [S, (i d)] x do [(i d), (j e)]
-        return dl, dr
+    def backward(ctx, dout):
+        l2, r2, w, inv_norm, o4 = ctx.saved_tensors
+        ni, N = l2.shape[1] // 32, r2.shape[1] // 32
+        dout = dout.contiguous()
+        dys = dout * inv_norm.to(dout.dtype).unsqueeze(-1)                 # gradient of (o4 W^T + bias)
+        dw = db = dl = dr = None
+        if ctx.needs_input_grad[2]:
+            dw = K.weight_grad(dys, o4).to(w.dtype)
+        if ctx.needs_input_grad[3]:
+            db = K.colsum(dys).to(w.dtype)
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            # d o4 = dys W, stored as the matrix [(i d), (j e)] that the two operand gradients contract with
+            do = K.gemm(dys, w, b_mn=True, block_out=((ni * 32, N * 32), N // 32, N * 1024, 1024, 32 * N))
+            if ctx.needs_input_grad[0]:
+                dl = K.gemm(r2, do)                      # [S, (i d)] = r2 [S, (j e)] x do^T
+            if ctx.needs_input_grad[1]:
+                dr = K.gemm(l2, do, b_mn=True)           # [S, (j e)] = l2 [S, (i d)] x do
+        return dl, dr, dw, db, None, dout if ctx.needs_input_grad[5] else None
 
 
 # ---------------------------------------------------------------------------
@@ -237,21 +259,40 @@ class SelfAttention(nn.Module):
             self.gating_linear = Linear(qkv_dim, n_head * c, initializer="zero", use_bias=False)
         self.o_linear = Linear(n_head * c, out_dim, initializer="zero", use_bias=(not last_bias_fuse))
 
-    def _bias(self, nonbatched_bias):
+    def _bias(self, nonbatched_bias, transposed=False):
         if nonbatched_bias is None:
             return None
         if nonbatched_bias[-1] == -1:
             return nonbatched_bias[0]
+        if transposed:      # projected from the un-transposed pair tensor [k, q_local, h]: gather the query axis
+            b = gather_async_opp(*nonbatched_bias, dim=2)
+            return b.permute(0, 3, 2, 1).contiguous()      # 'b k q h -> b h q k'
         b = gather_async_opp(*nonbatched_bias, dim=1)
         return b.permute(0, 3, 1, 2).contiguous()          # 'b q k h -> b h q k'
 
-    def _one(self, x, mask, bias, tail):
-        b1, b2, n, _ = x.shape
+    def _one(self, x, mask, bias, tail, transposed=False):
+        """``transposed``: ``x [b1, n, b2, c]`` and the attention runs along dim 1 (``mask [b1, b2, n]``)."""
         H, d = self.n_head, self.c
-        qkv = self.to_qkv(x).reshape(b1, b2, n, 3, H, d)
-        q, k, v = (qkv[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
-        o = attention_core(q, k, v, mask, None if bias is None else bias.unsqueeze(1), self.scaling)
-        o = o.permute(0, 1, 3, 2, 4).reshape(b1, b2, n, H * d)
+        bias5 = None if bias is None else bias.unsqueeze(1)
+        if transposed:
+            b1, n, b2, _ = x.shape
+            qkv = self.to_qkv(x).reshape(b1, n, b2, 3, H, d)
+            if not flash.packed_supported(qkv, mask, bias5, transposed=True):
+                out, _ = self._one(x.transpose(1, 2).contiguous(), mask, bias, None)
+                return out.transpose(1, 2).contiguous(), False
+            o = flash.flash_attention_packed(qkv, mask, bias5, self.scaling, transposed=True)      # [b1, n, b2, H*d]
+            b2, n = n, b2        # below only the flattened row count b2 * n matters
+        else:
+            b1, b2, n, _ = x.shape
+            qkv = self.to_qkv(x).reshape(b1, b2, n, 3, H, d)
+        if transposed:
+            pass
+        elif flash.packed_supported(qkv, mask, bias5):
+            o = flash.flash_attention_packed(qkv, mask, bias5, self.scaling)           # [b1, b2, n, H*d]
+        else:
+            q, k, v = (qkv[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
+            o = attention_core(q, k, v, mask, bias5, self.scaling)
+            o = o.permute(0, 1, 3, 2, 4).reshape(b1, b2, n, H * d)
         fused = _fusable(x)
         if self.gating:
             if fused:
@@ -266,12 +307,13 @@ class SelfAttention(nn.Module):
             return out.reshape(resid.shape), True
         return self.o_linear(o), False
 
-    def forward(self, in_data, mask, nonbatched_bias=None, tail=None):
+    def forward(self, in_data, mask, nonbatched_bias=None, tail=None, transposed=False):
         """``tail=(out_bias, (mask2d, div, mod) or None, residual)`` lets the output projection absorb the
-        bias / dropout / residual that follow it; the second return value says whether it did."""
-        bias = self._bias(nonbatched_bias)
-        if CHUNK_SIZE is None or CHUNK_SIZE >= in_data.shape[1]:
-            return self._one(in_data, mask, bias, tail)
+        bias / dropout / residual that follow it; the second return value says whether it did.
+        ``transposed``: attend along dim 1 of ``in_data`` instead of dim 2 (no chunking in that mode)."""
+        bias = self._bias(nonbatched_bias, transposed)
+        if transposed or CHUNK_SIZE is None or CHUNK_SIZE >= in_data.shape[1]:
+            return self._one(in_data, mask, bias, tail, transposed)
         outs = []
         for ax in range(0, in_data.shape[1], CHUNK_SIZE):
             o, _ = self._one(in_data[:, ax:ax + CHUNK_SIZE], mask[:, ax:ax + CHUNK_SIZE], bias, None)
@@ -557,21 +599,33 @@ class _TriangleAttention(nn.Module):
                 dropmask = F.dropout(torch.ones_like(Z_raw[:, :, 0:1, :]), p=self.p_drop, training=True)
         if not training:
             dropmask = None
+        strided = self.strided(Z_raw)
         if Z_norm is not None:
             Z = Z_norm
         else:
-            Z = self.layernorm1(Z_raw if self.starting else Z_raw.transpose(-2, -3).contiguous())
+            Z = self.layernorm1(Z_raw if (self.starting or strided) else Z_raw.transpose(-2, -3).contiguous())
         b = self.linear_b(Z)
-        b, work = gather_async(b, dim=1)
+        b, work = gather_async(b, dim=2 if strided else 1)
         tail = None
-        if self.starting and _fusable(Z_raw):
+        if (self.starting or strided) and _fusable(Z_raw):
             tail = (self.out_bias, None if dropmask is None else _mask_idx(Z_raw, dropmask), Z_raw)
-        out, done = self.attention(Z, mask, (b, work), tail=tail)
+        out, done = self.attention(Z, mask, (b, work), tail=tail, transposed=strided)
         if done:
             return out
+        if strided:
+            return K.bias_dropout_add(out, self.out_bias, dropmask, Z_raw, prob=0.0, training=training)
         if not self.starting:
             out = out.transpose(-2, -3)
         return K.bias_dropout_add(out.contiguous(), self.out_bias, dropmask, Z_raw, prob=0.0, training=training)
+
+    def strided(self, Z_raw):
+        """Ending node on the GPU: the attention kernels walk the first pair axis through their row / batch strides, so
+        neither the input nor the output is transposed (``Z_norm``, when given, is then in the un-transposed layout)."""
+        if self.starting or CHUNK_SIZE is not None:
+            return False
+        if not (Z_raw.is_cuda and Z_raw.dtype == torch.bfloat16 and self.c == flash.HEAD_DIM and Z_raw.shape[1] % 8 == 0):
+            return False
+        return not (torch.is_grad_enabled() and Z_raw.shape[1] > 512)
 
     def inplace(self, Z_raw, Z_mask, dropmask=None):
         Z_raw[0] = self.forward(Z_raw[0], Z_mask, dropmask)

@@ -41,6 +41,7 @@ class GemmArgs(ctypes.Structure):
         ("dmask", c_void_p), ("lddm", c_ll),
         ("resid", c_void_p), ("ldres", c_ll), ("res_bstride", c_ll),
         ("peer_slab", c_int),
+        ("cq", c_int), ("cq_mdiv", c_int), ("cq_sr2", c_ll), ("cq_sr1", c_ll), ("cq_sc1", c_ll),
     ]
 
 
@@ -52,6 +53,7 @@ def _declare(lib):
         "ffb_read_status": [ctypes.POINTER(c_int), I],
         "ffb_attention_fwd": [P, P, P, L, L, L, L, P, P, L, P, L, L, P, I, I, I, I, I, F, P],
         "ffb_attention_bwd": [P, P, P, L, L, L, L, P, P, L, P, P, P, P, P, I, I, I, I, I, F, P],
+        "ffb_attention_bwd_strided": [P, P, P, L, L, L, L, P, P, L, P, P, L, L, P, P, P, P, L, L, L, L, P, I, I, I, I, I, F, P],
         "ffb_layernorm_fwd": [P, P, P, P, P, P, L, I, F, I, P],
         "ffb_layernorm_bwd": [P, P, P, P, P, P, P, I, P, P, L, I, I, P],
         "ffb_layernorm_fwd_transposed": [P, P, P, P, P, P, L, I, F, P],

@@ -115,3 +115,90 @@ def flash_attention(q, k, v, mask, bias, scale):
     _, B, n_q, HD = out.shape
     H = q.shape[2]
     return out.view(1, B, n_q, H, HD // H).permute(0, 1, 3, 2, 4)
+
+
+# ---------------------------------------------------------------------------
+# Packed path: the fused QKV projection output goes in as one tensor and its gradient comes back as one tensor,
+# written in place by the backward kernel (no per-slice zero-fill / copy / accumulate in autograd).  With
+# ``transposed=True`` the attention runs along dim 1 of ``qkv [1, n, B, 3, H, d]`` (batch = dim 2): the kernels take
+# row / batch strides, so the triangle attention around the ending node needs no transposed copy of the pair tensor.
+# ---------------------------------------------------------------------------
+def packed_supported(qkv, mask, bias, transposed=False):
+    """``qkv [1, B, n, 3, H, d]`` (or ``[1, n, B, 3, H, d]``) contiguous bf16 on a GPU, self attention."""
+    if not (qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 6 and qkv.shape[0] == 1 and qkv.shape[3] == 3
+            and qkv.shape[-1] == HEAD_DIM and qkv.is_contiguous() and qkv.data_ptr() % 16 == 0):
+        return False
+    if not (_lib.has("ffb_attention_fwd") and _lib.has("ffb_attention_bwd_strided")):
+        return False
+    n = qkv.shape[1] if transposed else qkv.shape[2]
+    if n % 8:
+        return False
+    if torch.is_grad_enabled() and (qkv.requires_grad or (bias is not None and bias.requires_grad)) and n > 512:
+        return False
+    if bias is not None and (bias.dim() != 5 or bias.shape[0] != 1 or bias.shape[1] != 1):
+        return False
+    return True
+
+
+def _packed_geometry(qkv, transposed):
+    """B, n, H, d and the (batch, row) strides of the q/k/v slabs and of the output."""
+    if transposed:
+        _, n, B, _, H, d = qkv.shape
+        HD = H * d
+        return B, n, H, d, (3 * HD, B * 3 * HD), (HD, B * HD)
+    _, B, n, _, H, d = qkv.shape
+    HD = H * d
+    return B, n, H, d, (n * 3 * HD, 3 * HD), (n * HD, HD)
+
+
+def _packed_fwd(qkv, mask, bias, scale, want_lse, transposed):
+    lib = _lib.get()
+    B, n, H, d, (bs, rs), (obs, ors) = _packed_geometry(qkv, transposed)
+    HD = H * d
+    out = torch.empty((1, n, B, HD) if transposed else (1, B, n, HD), device=qkv.device, dtype=qkv.dtype)
+    lse = torch.empty(B, H, n, device=qkv.device, dtype=torch.float32) if want_lse else None
+    b3 = bias.reshape(H, n, n).contiguous() if bias is not None else None
+    m2 = mask.reshape(B, n).to(torch.bfloat16).contiguous() if mask is not None else None
+    base = qkv.data_ptr()
+    rc = lib.ffb_attention_fwd(base, base + 2 * HD, base + 4 * HD, bs, rs, bs, rs, _lib.ptr(b3), _lib.ptr(m2), n,
+                               _lib.ptr(out), obs, ors, _lib.ptr(lse), B, H, n, n, d, float(scale), _lib.stream_ptr())
+    _lib.check(rc, "ffb_attention_fwd packed (B=%d,H=%d,n=%d)" % (B, H, n))
+    return out, lse, b3, m2
+
+
+class _FlashPackedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, mask, bias, scale, transposed):
+        out, lse, b3, m2 = _packed_fwd(qkv, mask, bias, scale, True, transposed)
+        ctx.save_for_backward(qkv, b3, m2, out, lse)
+        ctx.scale, ctx.transposed = scale, transposed
+        ctx.bias_shape = None if bias is None else tuple(bias.shape)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        lib = _lib.get()
+        qkv, b3, m2, out, lse = ctx.saved_tensors
+        B, n, H, d, (bs, rs), (obs, ors) = _packed_geometry(qkv, ctx.transposed)
+        HD = H * d
+        do = do.contiguous()
+        dqkv = torch.empty_like(qkv)
+        ds = torch.empty(B, H, n, n, device=qkv.device, dtype=qkv.dtype) if b3 is not None else None
+        base, gbase = qkv.data_ptr(), dqkv.data_ptr()
+        rc = lib.ffb_attention_bwd_strided(base, base + 2 * HD, base + 4 * HD, bs, rs, bs, rs, _lib.ptr(b3), _lib.ptr(m2), n, _lib.ptr(out),
+                                           _lib.ptr(do), obs, ors, _lib.ptr(lse), gbase, gbase + 2 * HD, gbase + 4 * HD, bs, rs, bs, rs,
+                                           _lib.ptr(ds), B, H, n, n, d, float(ctx.scale), _lib.stream_ptr())
+        _lib.check(rc, "ffb_attention_bwd_strided (B=%d,H=%d,n=%d)" % (B, H, n))
+        dbias = None
+        if ds is not None and ctx.needs_input_grad[2]:
+            dbias = ds.sum(dim=0).reshape(ctx.bias_shape)
+        return dqkv, None, dbias, None, None
+
+
+def flash_attention_packed(qkv, mask, bias, scale, transposed=False):
+    """``qkv [1, B, n, 3, H, d]`` -> ``[1, B, n, H*d]`` (heads side by side, ready for gating / output projection);
+    ``transposed``: ``qkv [1, n, B, 3, H, d]`` -> ``[1, n, B, H*d]``, ``mask [.., B, n]``."""
+    need_grad = torch.is_grad_enabled() and (qkv.requires_grad or (bias is not None and bias.requires_grad))
+    if need_grad:
+        return _FlashPackedFn.apply(qkv, mask, bias, scale, transposed)
+    return _packed_fwd(qkv, mask, bias, scale, False, transposed)[0]

@@ -53,7 +53,7 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, gl
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=False, rowscale=None, mul=None,
-         dmask=None, resid=None, trans_out=False, out=None, out_dtype=None, splits=1, accumulate=False, bn=0, peer=None):
+         dmask=None, resid=None, trans_out=False, out=None, out_dtype=None, splits=1, accumulate=False, bn=0, peer=None, block_out=None):
     """``C = epilogue(alpha * A @ B^T)`` with A ``[.., M, K]`` and B ``[.., N, K]``.
 
     ``a_mn`` / ``b_mn``: the operand is stored with the contraction index
@@ -66,8 +66,24 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
     ``peer=("a" | "b", [address of every rank's slab])``: that operand is the concatenation, along its M / N extent,
     of one equally shaped slab per rank; the tensor passed in is this rank's slab (it supplies shape and strides)
     and the kernel fetches every slab's tiles from the given addresses - peer GPUs' memory - with TMA.
+    ``block_out=(shape, mdiv, sr2, sr1, sc1)``: the bf16 result is stored block-permuted into a new tensor of ``shape``:
+    with ``m = 32 m1 + m0`` and ``n = 32 n1 + n0``, element ``(m, n)`` lands at flat index
+    ``(m1 // mdiv) sr2 + (m1 % mdiv) sr1 + n1 sc1 + 32 m0 + n0`` (every 32 x 32 block contiguous).  With ``d = e = 32``:
+    ``[(i d), (j e)] -> [i, j, d, e]`` is ``(1, 1024 J, 0, 1024)`` and ``[(i j), (d e)] -> [(i d), (j e)]`` is
+    ``(J // 32, 1024 J, 1024, 32 J)``.  Needs ``M % 32 == 0``, ``N % 64 == 0``.
     """
+    if block_out is not None:
+        assert out is None and not trans_out and not glu and mul is None and resid is None and a.dim() == 2 and b.dim() == 2
     if not a.is_cuda:
+        if block_out is not None:
+            shape, mdiv, sr2, sr1, sc1 = block_out
+            r = gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, alpha=alpha, bias=bias, act=act, rowscale=rowscale, dmask=dmask, out_dtype=out_dtype)
+            Mr, Nr = r.shape
+            res = torch.empty(shape, dtype=r.dtype)
+            m1 = Mr // 32
+            dst = torch.as_strided(res, (m1 // mdiv, mdiv, Nr // 32, 32, 32), (sr2, sr1, sc1, 32, 1))
+            dst.copy_(r.reshape(m1 // mdiv, mdiv, 32, Nr // 32, 32).permute(0, 1, 3, 2, 4))
+            return res
         r = gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, alpha=alpha, bias=bias, act=act, glu=glu, rowscale=rowscale, mul=mul,
                      dmask=dmask, resid=resid, trans_out=trans_out, out_dtype=out_dtype)
         if out is not None:
@@ -110,6 +126,13 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
     oshape = (n_out, M) if trans_out else (M, n_out)
     if batched:
         oshape = (batch,) + oshape
+    blocked = None
+    if block_out is not None:
+        shape, mdiv, sr2, sr1, sc1 = block_out
+        assert M % 32 == 0 and n_out % 64 == 0 and (M // 32) % mdiv == 0 and out_dtype in (None, torch.bfloat16)
+        blocked = torch.empty(shape, device=a.device, dtype=torch.bfloat16)
+        assert blocked.numel() == M * n_out
+        out = blocked.view(-1).as_strided((M, n_out), (8, 1))          # carries shape and dtype through the checks; the kernel ignores ldc
     if out is None:
         odt = out_dtype or torch.bfloat16
         out = torch.empty(oshape, device=a.device, dtype=odt)
@@ -133,6 +156,8 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
     g.C = out.data_ptr()
     g.ldc = out.stride(-2)
     g.c_bstride = out.stride(0) if batched else 0
+    if blocked is not None:
+        g.cq, g.cq_mdiv, g.cq_sr2, g.cq_sr1, g.cq_sc1 = 1, int(block_out[1]), int(block_out[2]), int(block_out[3]), int(block_out[4])
     keep = [a, b, out]
     if bias is not None:
         bias = bias.to(torch.bfloat16).contiguous()
@@ -176,7 +201,7 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
                            a3.stride(0) if a.dim() == 3 else 0, b3.stride(0) if b.dim() == 3 else 0, batch, bn, g,
                            _lib.stream_ptr())
     _lib.check(rc, "ffb_gemm_bf16(M=%d,N=%d,K=%d,batch=%d)" % (M, N, K, batch))
-    return out
+    return blocked if blocked is not None else out
 
 
 def _wgrad_splits(tokens, n_out_tiles):

@@ -94,3 +94,68 @@ def test_backward_fully_masked_row_stays_finite(device_status):
     assert gerr < 3e-2 * max(1.0, qkv_r.grad.abs().max().item())
     berr = (bias.grad.float() - bias_r.grad).abs().max().item()
     assert berr < 3e-2 * max(1.0, bias_r.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("B,n,H,use_bias", [(6, 256, 4, True), (5, 128, 8, False), (3, 200, 4, True)])
+def test_packed_qkv_path(B, n, H, use_bias, device_status):
+    """The packed entry (one QKV tensor in, one gradient tensor out) against the fp32 reference."""
+    torch.manual_seed(B + n)
+    qkv = (torch.randn(1, B, n, 3, H, 32, device=DEV) * 0.7).to(torch.bfloat16).requires_grad_(True)
+    bias = torch.randn(1, 1, H, n, n, device=DEV).to(torch.bfloat16).requires_grad_(True) if use_bias else None
+    mask = (torch.rand(1, B, n, device=DEV) > 0.2).to(torch.bfloat16)
+    mask[..., 0] = 1
+    assert flash.packed_supported(qkv, mask, bias)
+    out = flash.flash_attention_packed(qkv, mask, bias, 32 ** -0.5)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qkv_r = qkv.detach().float().requires_grad_(True)
+    bias_r = bias.detach().float().requires_grad_(True) if use_bias else None
+    qr, kr, vr = (qkv_r[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
+    ref = attention_core_ref(qr, kr, vr, mask.float(), bias_r).permute(0, 1, 3, 2, 4).reshape(out.shape)
+    ref.backward(g.float())
+    assert (out.float() - ref).abs().max() < 2e-2
+    gerr = (qkv.grad.float() - qkv_r.grad).abs().max().item()
+    assert gerr < 3e-2 * max(1.0, qkv_r.grad.abs().max().item())
+    if use_bias:
+        berr = (bias.grad.float() - bias_r.grad).abs().max().item()
+        assert berr < 3e-2 * max(1.0, bias_r.grad.abs().max().item())
+
+
+def test_ending_node_strided_matches_transposed_reference(device_status):
+    """Triangle attention around the ending node: GPU path (row / batch strides, no transposes; fused tail under
+    no_grad, autograd under grad) against the same module in fp32 on the CPU (explicit transposes)."""
+    from fastfold_b200.models.fastnn.ops import ChunkTriangleAttentionEndingNode
+    torch.manual_seed(11)
+    N, c = 64, 128
+    ref = ChunkTriangleAttentionEndingNode(c, p_drop=0.25, c=32, n_head=4)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(torch.randn_like(p) * 0.1)
+    gpu = ChunkTriangleAttentionEndingNode(c, p_drop=0.25, c=32, n_head=4)
+    gpu.load_state_dict(ref.state_dict())
+    gpu = gpu.to(DEV, torch.bfloat16)
+    ref.eval(); gpu.eval()
+    z = torch.randn(1, N, N, c)
+    mask = (torch.rand(1, N, N) > 0.1).float()
+    mask[:, 0, :] = 1
+    zg = z.to(DEV, torch.bfloat16)
+    zr = zg.float().cpu().requires_grad_(True)
+    with torch.no_grad():
+        for p, q in zip(ref.parameters(), gpu.parameters()):
+            p.copy_(q.float().cpu())
+    out_ref = ref(zr, mask)
+    assert gpu.strided(zg)
+    with torch.no_grad():
+        out_nograd = gpu(zg, mask.to(DEV, torch.bfloat16))
+    assert (out_nograd.float().cpu() - out_ref.detach()).abs().max() < 0.06
+    zg2 = zg.clone().requires_grad_(True)
+    out_grad = gpu(zg2, mask.to(DEV, torch.bfloat16))
+    assert (out_grad.float().cpu() - out_ref.detach()).abs().max() < 0.06
+    g = torch.randn_like(out_ref)
+    out_ref.backward(g)
+    out_grad.backward(g.to(DEV, torch.bfloat16))
+    err = (zg2.grad.float().cpu() - zr.grad).abs().max().item()
+    assert err < 0.05 * max(1.0, zr.grad.abs().max().item()), err
+    for (n_, p), q in zip(ref.named_parameters(), gpu.parameters()):
+        e = (q.grad.float().cpu() - p.grad).abs().max().item()
+        assert e < 0.06 * max(1.0, p.grad.abs().max().item()), (n_, e)

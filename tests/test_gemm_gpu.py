@@ -117,3 +117,41 @@ def test_bmm_autograd(device_status):
     _close(out, of, 64)
     _close(a.grad, af.grad, 192)
     _close(b.grad, bf.grad, 128)
+
+
+def test_block_permuted_output(device_status):
+    """Outer-product layouts: [(i d), (j e)] stored as [i, j, d, e], and [(i j), (d e)] stored as [(i d), (j e)]."""
+    torch.manual_seed(3)
+    S, ni, N = 128, 64, 96
+    l2 = torch.randn(S, ni * 32, device="cuda").to(torch.bfloat16)
+    r2 = torch.randn(S, N * 32, device="cuda").to(torch.bfloat16)
+    o4 = gemm(l2, r2, a_mn=True, b_mn=True, block_out=((ni, N, 32, 32), 1, N * 1024, 0, 1024))
+    ref = (l2.float().t() @ r2.float()).reshape(ni, 32, N, 32).permute(0, 2, 1, 3)
+    assert (o4.float() - ref).abs().max() < 0.25 and (o4.float() - ref).abs().mean() < 0.03
+    dy = (torch.randn(ni * N, 128, device="cuda") * 0.1).to(torch.bfloat16)
+    w = torch.randn(128, 1024, device="cuda").to(torch.bfloat16)
+    do = gemm(dy, w, b_mn=True, block_out=((ni * 32, N * 32), N // 32, N * 1024, 1024, 32 * N))
+    ref = (dy.float() @ w.float()).reshape(ni, N, 32, 32).permute(0, 2, 1, 3).reshape(ni * 32, N * 32)
+    err = (do.float() - ref).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
+
+
+def test_outer_product_mean_core_gradients(device_status):
+    """The hand-written backward of the fused outer-product-mean tail against autograd on the fp32 composite."""
+    from fastfold_b200.models.fastnn.ops import _OpmCore
+    torch.manual_seed(4)
+    S, ni, N, cz = 64, 32, 64, 128
+    mk = lambda *shape, s=1.0: (torch.randn(*shape, device="cuda") * s).to(torch.bfloat16).requires_grad_(True)
+    l2, r2, w, b, z2 = mk(S, ni * 32, s=0.5), mk(S, N * 32, s=0.5), mk(cz, 1024, s=0.05), mk(cz, s=0.1), mk(ni * N, cz)
+    inv = (torch.rand(ni * N, device="cuda") + 0.5).float()
+    out = _OpmCore.apply(l2, r2, w, b, inv, z2)
+    g = torch.randn_like(out)
+    out.backward(g)
+    fl = [t.detach().float().requires_grad_(True) for t in (l2, r2, w, b, z2)]
+    o = (fl[0].t() @ fl[1]).reshape(ni, 32, N, 32).permute(0, 2, 1, 3).reshape(ni * N, 1024)
+    ref = fl[4] + (o @ fl[2].t() + fl[3]) * inv.unsqueeze(-1)
+    ref.backward(g.float())
+    assert (out.float() - ref).abs().max() < 0.05 * max(1.0, ref.abs().max().item())
+    for got, want, name in zip((l2, r2, w, b, z2), fl, "l r w b z".split()):
+        err = (got.grad.float() - want.grad).abs().max().item()
+        assert err < 3e-2 * max(1.0, want.grad.abs().max().item()), (name, err)

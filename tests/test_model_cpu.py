@@ -72,3 +72,19 @@ def test_single_block_forward_backward_matches_reference_layout():
         outs.append((om.detach(), oz.detach(), m_.grad, z_.grad))
     for a, b in zip(*outs):
         assert (a - b).abs().max() < 1e-4 * max(1.0, b.abs().max().item())
+
+
+def test_block_permuted_gemm_reference_layouts():
+    """CPU oracle of the block-permuted GEMM output: both layouts used by the outer-product-mean module."""
+    import torch
+    from fastfold_b200.ops import gemm
+    torch.manual_seed(0)
+    S, ni, N = 16, 2, 64
+    l2, r2 = torch.randn(S, ni * 32), torch.randn(S, N * 32)
+    o4 = gemm(l2, r2, a_mn=True, b_mn=True, block_out=((ni, N, 32, 32), 1, N * 1024, 0, 1024))
+    ref = (l2.t() @ r2).reshape(ni, 32, N, 32).permute(0, 2, 1, 3)
+    assert torch.allclose(o4, ref, atol=1e-4)
+    dy, w = torch.randn(ni * N, 8), torch.randn(8, 1024)
+    do = gemm(dy, w, b_mn=True, block_out=((ni * 32, N * 32), N // 32, N * 1024, 1024, 32 * N))
+    ref = (dy @ w).reshape(ni, N, 32, 32).permute(0, 2, 1, 3).reshape(ni * 32, N * 32)
+    assert torch.allclose(do, ref, atol=1e-4)
