@@ -48,6 +48,8 @@ constexpr int BK = 64;           // 64 bf16 = 128 B = one swizzle row
 constexpr int GEMM_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
 constexpr int EPI_WARPS = 8;
 constexpr int STG_LD = 65;       // staging row pitch in floats (odd -> conflict-free column access)
+constexpr int FAST_BIAS_MAX_N = 1024;                          // widest output whose bias the fast epilogue keeps in shared memory
+constexpr int BIAS_SMEM_BYTES = (FAST_BIAS_MAX_N + 64) * 4;    // fp32, zero-padded by one column chunk
 
 template <int BN>
 struct GemmCfg {
@@ -57,7 +59,7 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_WARP_BYTES = 9216;               // per epilogue warp: 2 x 4 KB TMA tiles (the 32 x 65 fp32 transpose
   static constexpr int STG_BYTES = EPI_WARPS * EPI_WARP_BYTES;  // buffer of the generic path aliases them)
-  static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + BIAS_SMEM_BYTES;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator stages
 };
 
@@ -189,10 +191,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
   const uint32_t bar_epld = bar_acce + 16;                  // 8: per-epilogue-warp TMA loads of mul / residual tiles
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + EPI_WARPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_bias = reinterpret_cast<float*>(smem_al + STAGES * Cfg::STAGE_BYTES + Cfg::STG_BYTES + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kb_total = (g.K + BK - 1) / BK;
+  if (tma_epi == 2 && g.bias) {
+    // fast epilogue: the whole bias vector as fp32 in shared memory, read back as broadcast 16-byte loads
+    const bf16* bp = reinterpret_cast<const bf16*>(g.bias);
+    for (int i = threadIdx.x; i < FAST_BIAS_MAX_N + 64; i += GEMM_THREADS) s_bias[i] = (i < g.N) ? __bfloat162float(bp[i]) : 0.f;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -332,7 +340,103 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + as * BN;
-      if (tma_epi) {
+      if (tma_epi == 2) {
+        // Fast path (bf16 row-major output, at most bias + activation): TMEM -> registers -> swizzled shared tile -> TMA
+        // store, with no per-element branches.  The common projection / gradient GEMMs of the model all land here.
+        const int row0 = tc.m0 + quad * 32;
+#pragma unroll 1
+        for (int c = half; c < BN / 64; c += 2) {
+          const int col0 = n0 + c * 64;
+          if (col0 >= g.N || row0 >= g.M) break;           // warp-uniform
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the store that last read this tile is done
+          __syncwarp();
+          float v[64];
+          tmem_ld_32x32(taddr + c * 64, v);
+          tmem_ld_32x32(taddr + c * 64 + 32, v + 32);
+          tmem_ld_wait();
+          if (g.bias) {
+            const float4* bp = reinterpret_cast<const float4*>(s_bias + col0);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              const float4 b4 = bp[q];
+              v[4 * q] += b4.x;
+              v[4 * q + 1] += b4.y;
+              v[4 * q + 2] += b4.z;
+              v[4 * q + 3] += b4.w;
+            }
+          }
+          if (g.act == ACT_RELU) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = fmaxf(v[j], 0.f);
+          } else if (g.act == ACT_SIGMOID) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = sigmoidf_(v[j]);
+          }
+          uint8_t* obuf = reinterpret_cast<uint8_t*>(stg) + out_buf * 4096 + lane * 128;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            uint4 pk;
+            bf162* hp = reinterpret_cast<bf162*>(&pk);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) hp[j] = __floats2bfloat162_rn(v[u * 8 + 2 * j], v[u * 8 + 2 * j + 1]);
+            *reinterpret_cast<uint4*>(obuf + ((u ^ (lane & 7)) << 4)) = pk;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&tmC),
+                         "r"(epi_smem + out_buf * 4096), "r"(col0), "r"(row0), "r"(tc.batch)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          out_buf ^= 1;
+        }
+      } else if (tma_epi == 3) {
+        // Fast transposed path (bf16 C^T, at most bias + activation): the 32 x 64 warp tile is transposed on its way into
+        // shared memory ([64 columns][32 rows], 64-byte lines written by whole warps) and leaves as one TMA store.
+        const int row0 = tc.m0 + quad * 32;
+#pragma unroll 1
+        for (int c = half; c < BN / 64; c += 2) {
+          const int col0 = n0 + c * 64;
+          if (col0 >= g.N || row0 >= g.M) break;           // warp-uniform
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+          float v[64];
+          tmem_ld_32x32(taddr + c * 64, v);
+          tmem_ld_32x32(taddr + c * 64 + 32, v + 32);
+          tmem_ld_wait();
+          if (g.bias) {
+            const float4* bp = reinterpret_cast<const float4*>(s_bias + col0);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              const float4 b4 = bp[q];
+              v[4 * q] += b4.x;
+              v[4 * q + 1] += b4.y;
+              v[4 * q + 2] += b4.z;
+              v[4 * q + 3] += b4.w;
+            }
+          }
+          if (g.act == ACT_RELU) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = fmaxf(v[j], 0.f);
+          } else if (g.act == ACT_SIGMOID) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = sigmoidf_(v[j]);
+          }
+          bf16* obuf = reinterpret_cast<bf16*>(reinterpret_cast<uint8_t*>(stg) + out_buf * 4096) + lane;
+#pragma unroll
+          for (int j = 0; j < 64; ++j) obuf[j * 32] = __float2bfloat16(v[j]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&tmC),
+                         "r"(epi_smem + out_buf * 4096), "r"(row0), "r"(col0), "r"(tc.batch)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          out_buf ^= 1;
+        }
+      } else if (tma_epi) {
         // TMA path (bf16 row-major output): thread = row; mul / residual tiles arrive by TMA, the result tile leaves
         // by TMA, so every global access is a full-line bulk transfer and the warp only touches shared memory
         const int row0 = tc.m0 + quad * 32;
@@ -744,6 +848,13 @@ static int gemm_launch(const void* A, const void* B, int a_mn, int b_mn, long lo
     if (make_tmap_bf16(&epi[0], g.C, g.M, g.N, g.ldc, batch, g.c_bstride, 64, 32)) tma_epi = 0;
     if (tma_epi && g.mul && make_tmap_bf16(&epi[1], g.mul, g.M, g.N, g.ldmul, batch, g.mul_bstride, 64, 32)) tma_epi = 0;
     if (tma_epi && g.resid && make_tmap_bf16(&epi[2], g.resid, g.M, g.N, g.ldres, batch, g.res_bstride, 64, 32)) tma_epi = 0;
+  }
+  if (tma_epi && !g.cq && !g.mul && !g.resid && !g.rowscale && !g.dmask && g.alpha == 1.0f && (!g.bias || g.N <= FAST_BIAS_MAX_N))
+    tma_epi = 2;   // fast epilogue
+  if (!tma_epi && g.trans_out && g.out_mode == OUT_BF16 && !g.glu && !g.mul && !g.resid && !g.rowscale && !g.dmask && g.alpha == 1.0f &&
+      (!g.bias || g.N <= FAST_BIAS_MAX_N) && al16(g.C, g.ldc, g.c_bstride) && (batch == 1 || g.c_bstride != 0) && g.M >= 32) {
+    // fast transposed epilogue: C^T is a [N][M] matrix with row stride ldc; tiles of 64 rows x 32 contiguous elements
+    if (encode_tmap3_bf16(&epi[0], g.C, g.M, g.N, batch, g.ldc, g.c_bstride, 32, 64, 0) == 0) tma_epi = 3;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (peer_which == 1) {

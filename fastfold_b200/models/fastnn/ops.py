@@ -161,7 +161,8 @@ class OutProductMean(nn.Module):
         N, e = right_all.shape[2], right_all.shape[3]
         l2 = left.reshape(S, ni * d)
         r2 = right_all.reshape(S, N * e)
-        if _fusable(Z_raw) and d == 32 and e == 32 and N % 32 == 0 and ni * d >= 64 and self.o_linear.bias is not None:
+        if (Z_raw.is_cuda and Z_raw.dtype == torch.bfloat16 and d == 32 and e == 32 and N % 32 == 0 and ni * d >= 64
+                and self.o_linear.bias is not None):
             # the product [(i d), (j e)] leaves the GEMM epilogue already laid out as [i, j, d, e], the operand layout of
             # the output projection; its gradient comes back the other way through the same block-permuting store
             if torch.is_grad_enabled() and any(t.requires_grad for t in (l2, r2, Z_raw, self.o_linear.weight)):
@@ -514,6 +515,9 @@ class _TriangleMultiplication(nn.Module):
             return self._fused_nograd(Z_raw, Z_mask, dropmask, Z_norm)
         c = self.c
         Z = self.layernorm1(Z_raw) if Z_norm is None else Z_norm
+        if (Z_raw.is_cuda and Z_raw.dtype == torch.bfloat16 and (Z_raw.shape[1] * Z_raw.shape[2]) % 8 == 0 and Z_raw.shape[1] % 8 == 0
+                and Z_raw.shape[2] % 8 == 0 and c <= 256 and c % 8 == 0):
+            return self._channel_major_train(Z_raw, Z, Z_mask, dropmask, training)
         proj = K.glu_mask(self.left_right_projection(Z), self.left_right_gate(Z), Z_mask)
         left, right = proj[..., :c], proj[..., c:]
         if self.outgoing:
@@ -526,6 +530,30 @@ class _TriangleMultiplication(nn.Module):
             left = gather_async_opp(left, work, dim=2)
         ab = self._contract(left, right)
         ab = self.output_projection(self.layernorm2(ab.contiguous()))
+        return K.bias_ele_dropout_residual(ab, self.output_bias, g, dropmask, Z_raw, prob=0.0, training=training)
+
+    def _channel_major_train(self, Z_raw, Z, Z_mask, dropmask, training):
+        """Differentiable GPU path: the projections leave their GEMM channel-major, the gate, the contraction and the
+        second LayerNorm's input stay channel-major, and every backward kernel reads / writes that layout too, so the
+        step has no permuted copy in either direction."""
+        c = self.c
+        A, B = Z_raw.shape[1], Z_raw.shape[2]
+        z2 = Z.reshape(A * B, -1)
+        w = torch.cat([self.left_right_projection.weight, self.left_right_gate.weight], dim=0)          # [4c, d]: values, then gates
+        b = torch.cat([self.left_right_projection.bias, self.left_right_gate.bias], dim=0)
+        left_t, right_t = K.glu_mask_t(K.linear_t(z2, w, b), Z_mask.reshape(-1), split=c)              # 2 x [c, A*B]
+        left_t = left_t.reshape(c, A, B)
+        right_t = right_t.reshape(c, A, B)
+        g = self.output_gate(Z, act="sigmoid")
+        if self.outgoing:
+            right_t = gather(right_t, dim=1, reduce_grad=True)          # [c, j (all), k]
+            p = K.bmm_nt(left_t, right_t)                               # [c, i, j]
+        else:
+            left_t = gather(left_t, dim=2, reduce_grad=True)            # [c, k, i (all)]
+            p = _bmm_tn(left_t, right_t)                                # [c, i, j]
+        n_i, n_j = p.shape[1], p.shape[2]
+        ab = K.layer_norm_transposed(p.reshape(c, n_i * n_j), self.layernorm2.weight, self.layernorm2.bias, self.layernorm2.eps)
+        ab = self.output_projection(ab).reshape(Z_raw.shape)
         return K.bias_ele_dropout_residual(ab, self.output_bias, g, dropmask, Z_raw, prob=0.0, training=training)
 
     def inplace(self, Z_raw, Z_mask, dropmask=None):

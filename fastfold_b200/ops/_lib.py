@@ -57,6 +57,9 @@ def _declare(lib):
         "ffb_layernorm_fwd": [P, P, P, P, P, P, L, I, F, I, P],
         "ffb_layernorm_bwd": [P, P, P, P, P, P, P, I, P, P, L, I, I, P],
         "ffb_layernorm_fwd_transposed": [P, P, P, P, P, P, L, I, F, P],
+        "ffb_layernorm_bwd_transposed": [P, P, P, P, P, P, P, P, P, L, I, P],
+        "ffb_glu_mask_t_fwd": [P, P, P, I, L, P],
+        "ffb_glu_mask_t_bwd": [P, P, P, P, I, L, P],
         "ffb_softmax_fwd": [P, P, P, P, L, L, L, L, I, I, P],
         "ffb_softmax_bwd": [P, P, P, L, I, I, P],
         "ffb_bias_sigmoid_mul_fwd": [P, P, P, P, L, I, P],

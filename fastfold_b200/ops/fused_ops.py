@@ -214,6 +214,48 @@ def glu_mask(p, q, rowmask=None):
 
 
 # ---------------------------------------------------------------------------
+class _GluMaskT(torch.autograd.Function):
+    """Channel-major gated projection: ``pre [2 C2, R]`` (values, then gates) -> ``pre[:C2] * sigmoid(pre[C2:]) * mask[R]``,
+    returned as its first ``split`` channels and the rest (two views of one buffer, so that autograd does not
+    zero-fill and accumulate per slice)."""
+
+    @staticmethod
+    def forward(ctx, pre, mask, split):
+        lib = _lib.get()
+        C2, R = pre.shape[0] // 2, pre.shape[1]
+        out = torch.empty(C2, R, device=pre.device, dtype=pre.dtype)
+        _lib.check(lib.ffb_glu_mask_t_fwd(_lib.ptr(pre), _lib.ptr(mask), _lib.ptr(out), C2, R, _lib.stream_ptr()), "glu_mask_t_fwd")
+        ctx.save_for_backward(pre, mask)
+        ctx.split = split
+        return out[:split], out[split:]
+
+    @staticmethod
+    def backward(ctx, d_lo, d_hi):
+        lib = _lib.get()
+        pre, mask = ctx.saved_tensors
+        C2, R = pre.shape[0] // 2, pre.shape[1]
+        if d_lo is None:
+            d_lo = pre.new_zeros(ctx.split, R)
+        if d_hi is None:
+            d_hi = pre.new_zeros(C2 - ctx.split, R)
+        dout = torch.cat([d_lo.reshape(ctx.split, R), d_hi.reshape(C2 - ctx.split, R)], dim=0)
+        dpre = torch.empty_like(pre)
+        _lib.check(lib.ffb_glu_mask_t_bwd(_lib.ptr(dout), _lib.ptr(pre), _lib.ptr(mask), _lib.ptr(dpre), C2, R, _lib.stream_ptr()), "glu_mask_t_bwd")
+        return dpre, None, None
+
+
+def glu_mask_t(pre, mask, split=None):
+    """``pre [2 C2, R]`` channel-major (rows ``[0, C2)`` values, ``[C2, 2 C2)`` gates), ``mask [R]`` -> the gated product
+    ``[C2, R]`` as the pair ``(first split channels, remaining channels)``; ``split`` defaults to ``C2 // 2``."""
+    C2 = pre.shape[0] // 2
+    split = C2 // 2 if split is None else split
+    if _bf16_cuda(pre) and pre.is_contiguous() and pre.shape[1] % 8 == 0 and _lib.has("ffb_glu_mask_t_fwd"):
+        return _GluMaskT.apply(pre, mask.reshape(-1).to(pre.dtype).contiguous(), split)
+    out = pre[:C2] * torch.sigmoid(pre[C2:]) * mask.reshape(1, -1).to(pre.dtype)
+    return out[:split], out[split:]
+
+
+# ---------------------------------------------------------------------------
 def act_backward(dy2, y2, act):
     """dy * act'(pre-activation), expressed through the saved activation output."""
     mode = 1 if act == "relu" else 2

@@ -243,6 +243,45 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db, None
 
 
+class _LinearT(torch.autograd.Function):
+    """y_t [c_out, tokens] = (x @ W^T + b)^T: the GEMM epilogue stores the transpose, and both gradient GEMMs read the
+    channel-major output gradient in place (as an MN-major / K-major operand), so nothing is ever transposed."""
+
+    @staticmethod
+    def forward(ctx, x2, w, bias):
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        return gemm(x2, w, bias=bias, trans_out=True)
+
+    @staticmethod
+    def backward(ctx, dy_t):
+        x2, w = ctx.saved_tensors
+        dy_t = dy_t.contiguous()                                  # [c_out, tokens]
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy_t, w, a_mn=True, b_mn=True)              # [tokens, c_in]: contraction over c_out, both operands stored [c_out, .]
+        if ctx.needs_input_grad[1]:
+            n_out, n_in = w.shape
+            acc = torch.zeros(n_out, n_in, device=w.device, dtype=torch.float32)
+            tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
+            gemm(dy_t, x2, b_mn=True, out=acc, accumulate=True, splits=_wgrad_splits(x2.shape[0], tiles))   # contraction over tokens
+            dw = acc.to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy_t.float().sum(dim=1).to(w.dtype)
+        return dx, dw, db
+
+
+def linear_t(x2, w, bias=None):
+    """``(x2 @ w.T + bias).T`` as a contiguous ``[c_out, tokens]`` tensor."""
+    ok = (x2.is_cuda and x2.dtype == torch.bfloat16 and x2.dim() == 2 and x2.shape[1] % 8 == 0 and x2.shape[0] % 8 == 0
+          and w.shape[0] >= 64 and w.shape[1] >= 64 and x2.shape[0] >= 64)
+    if not ok:
+        return torch.nn.functional.linear(x2, w, bias).t().contiguous()
+    if torch.is_grad_enabled() and (x2.requires_grad or w.requires_grad or (bias is not None and bias.requires_grad)):
+        return _LinearT.apply(x2, w, bias)
+    return gemm(x2, w, bias=bias, trans_out=True)
+
+
 def weight_grad(dy2, x2, dtype=torch.bfloat16):
     """dW[c_out, c_in] = dy^T @ x, contraction over tokens, fp32 split-K accumulation."""
     n_out, n_in = dy2.shape[1], x2.shape[1]

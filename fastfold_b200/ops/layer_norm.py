@@ -66,18 +66,58 @@ def layer_norm(x, weight, bias, eps=1e-5):
     return _LayerNormFn.apply(x, weight, bias, eps)
 
 
-def layer_norm_transposed(x_cm, weight, bias, eps=1e-5):
-    """LayerNorm over dim 0 of ``x_cm [C, rows]`` returning ``[rows, C]`` (no-grad fast path)."""
-    C, rows = x_cm.shape
-    if not (x_cm.is_cuda and x_cm.dtype == torch.bfloat16 and C <= 256):
-        return layer_norm(x_cm.t().contiguous(), weight, bias, eps)
+def _ln_t_supported(x_cm):
+    return x_cm.is_cuda and x_cm.dtype == torch.bfloat16 and x_cm.shape[0] <= 256
+
+
+def _ln_t_forward(x_cm, weight, bias, eps, want_stats):
     lib = _lib.get()
+    C, rows = x_cm.shape
     x_cm = x_cm.contiguous()
     y = torch.empty(rows, C, device=x_cm.device, dtype=x_cm.dtype)
+    mean = torch.empty(rows, device=x_cm.device, dtype=torch.float32) if want_stats else None
+    rstd = torch.empty(rows, device=x_cm.device, dtype=torch.float32) if want_stats else None
     _lib.check(lib.ffb_layernorm_fwd_transposed(_lib.ptr(x_cm), _lib.ptr(weight.contiguous()), _lib.ptr(bias.contiguous()),
-                                                _lib.ptr(y), None, None, rows, C, float(eps), _lib.stream_ptr()),
+                                                _lib.ptr(y), _lib.ptr(mean), _lib.ptr(rstd), rows, C, float(eps), _lib.stream_ptr()),
                "layernorm_fwd_transposed")
-    return y
+    return y, x_cm, mean, rstd
+
+
+class _LayerNormTFn(torch.autograd.Function):
+    """LayerNorm over dim 0 of a channel-major tensor; the input gradient comes back channel-major as well."""
+
+    @staticmethod
+    def forward(ctx, x_cm, weight, bias, eps):
+        y, x_c, mean, rstd = _ln_t_forward(x_cm, weight, bias, eps, True)
+        ctx.save_for_backward(x_c, weight, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.get()
+        x_cm, weight, mean, rstd = ctx.saved_tensors
+        C, rows = x_cm.shape
+        dy = dy.contiguous()
+        dx = torch.empty_like(x_cm)
+        part = torch.empty(((rows + 31) // 32) * 2 * C, device=dy.device, dtype=torch.float32)
+        dg = torch.empty(C, device=dy.device, dtype=torch.float32)
+        db = torch.empty(C, device=dy.device, dtype=torch.float32)
+        _lib.check(lib.ffb_layernorm_bwd_transposed(_lib.ptr(dy), _lib.ptr(x_cm), _lib.ptr(weight.contiguous()), _lib.ptr(mean), _lib.ptr(rstd),
+                                                    _lib.ptr(dx), _lib.ptr(part), _lib.ptr(dg), _lib.ptr(db), rows, C, _lib.stream_ptr()),
+                   "layernorm_bwd_transposed")
+        return dx, dg.to(weight.dtype), db.to(weight.dtype), None
+
+
+def layer_norm_transposed(x_cm, weight, bias, eps=1e-5):
+    """LayerNorm over dim 0 of ``x_cm [C, rows]`` returning ``[rows, C]``; differentiable (the gradient of ``x_cm`` is
+    produced channel-major by its own kernel)."""
+    if not _ln_t_supported(x_cm):
+        return layer_norm(x_cm.t().contiguous(), weight, bias, eps)
+    if torch.is_grad_enabled() and (x_cm.requires_grad or weight.requires_grad or bias.requires_grad):
+        if _lib.has("ffb_layernorm_bwd_transposed"):
+            return _LayerNormTFn.apply(x_cm, weight, bias, eps)
+        return layer_norm(x_cm.t().contiguous(), weight, bias, eps)
+    return _ln_t_forward(x_cm, weight, bias, eps, False)[0]
 
 
 class LayerNorm(nn.Module):

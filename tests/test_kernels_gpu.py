@@ -113,3 +113,30 @@ def test_fused_elementwise(device_status):
     p, q = R(1, 16, 24, 256), R(1, 16, 24, 256)
     rm = (torch.rand(1, 16, 24, device=DEV) > 0.2).to(bf)
     _check_grads(lambda p, q: ops.glu_mask(p, q, rm), lambda p, q: rm.float().unsqueeze(-1) * p * torch.sigmoid(q), [p, q])
+
+
+def test_channel_major_ops_match_references(device_status):
+    """linear_t, glu_mask_t and layer_norm_transposed (forward + backward) against fp32 PyTorch."""
+    from fastfold_b200 import ops as K
+    torch.manual_seed(21)
+    R, d, c = 4096 + 64, 128, 128
+    x = (torch.randn(R, d, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(4 * c, d, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    b = (torch.randn(4 * c, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    mask = (torch.rand(R, device="cuda") > 0.2).to(torch.bfloat16)
+    gam = (1 + 0.1 * torch.randn(c, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    bet = (0.1 * torch.randn(c, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    lo, hi = K.glu_mask_t(K.linear_t(x, w, b), mask, split=c)
+    y = K.layer_norm_transposed(lo * hi, gam, bet, 1e-5)                  # [R, c]
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf, bf, gf, btf = (t.detach().float().requires_grad_(True) for t in (x, w, b, gam, bet))
+    pre = (xf @ wf.t() + bf).t()
+    glu = pre[:2 * c] * torch.sigmoid(pre[2 * c:]) * mask.float().unsqueeze(0)
+    prod = (glu[:c].bfloat16().float() * glu[c:].bfloat16().float())     # the kernel path rounds the gated values to bf16
+    ref = torch.nn.functional.layer_norm(prod.t(), (c,), gf, btf, 1e-5)
+    ref.backward(g.float())
+    assert (y.float() - ref).abs().max() < 0.08
+    for got, want, name in ((x, xf, "x"), (w, wf, "w"), (b, bf, "b"), (gam, gf, "gamma"), (bet, btf, "beta")):
+        err = (got.grad.float() - want.grad).abs().max().item()
+        assert err < 0.05 * max(1.0, want.grad.abs().max().item()), (name, err, want.grad.abs().max().item())
