@@ -43,6 +43,22 @@ namespace ffb {
 
 __device__ int g_status[8];
 
+// Optional phase timeline of CTA 0 (compiled in only for profiling builds: -DFFB_GEMM_TRACE).
+#ifdef FFB_GEMM_TRACE
+__device__ unsigned long long g_gemm_trace[256 + 4 * 160];     // [15 tiles][16 slots] of CTA 0, then [CTA][4] phase stamps
+#define GEMM_TRACE(tile_local, slot)                                                        \
+  do {                                                                                      \
+    if (blockIdx.x == 0 && (tile_local) < 15) g_gemm_trace[(tile_local) * 16 + (slot)] = globaltimer_ns(); \
+  } while (0)
+#define GEMM_TRACE_CTA(slot)                                                                \
+  do {                                                                                      \
+    if (threadIdx.x == 0 && blockIdx.x < 160) g_gemm_trace[256 + blockIdx.x * 4 + (slot)] = globaltimer_ns(); \
+  } while (0)
+#else
+#define GEMM_TRACE(tile_local, slot) do {} while (0)
+#define GEMM_TRACE_CTA(slot) do {} while (0)
+#endif
+
 constexpr int BM = 128;
 constexpr int BK = 64;           // 64 bf16 = 128 B = one swizzle row
 constexpr int GEMM_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
@@ -179,6 +195,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
+  GEMM_TRACE_CTA(0);
   // operand tiles need 1024 B alignment for the 128B swizzle atoms
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -226,13 +243,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  GEMM_TRACE_CTA(1);   // start of the main phase
 
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer ----------------
       uint32_t it = 0;   // k-block counter over all tiles of this CTA
+      uint32_t plt = 0;  // local tile counter
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++plt) {
         const TileCoord tc = tile_coord(tile, tiles_n, tiles_m, g.splits);
         const int n0 = tc.n0 * BN;
         const int kb_begin = tc.split * g.kblocks_per_split;
@@ -261,6 +280,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
             mapB = &pm.m[r];
             bn0 = n0 - r * g.peer_slab;
           }
+          if (kb == kb_begin) GEMM_TRACE(plt, 0);      // producer: slot free, first loads of the tile go out
           mbar_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
@@ -306,6 +326,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
             break;
           }
           tc_fence_after();
+          if (kb == kb_begin) GEMM_TRACE(lt, 1);       // issuer: first operand tile landed
           const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
 #pragma unroll
@@ -317,6 +338,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
           umma_commit(bar_empty + 8 * s);   // slot reusable once these MMAs retire
         }
         if (ok) umma_commit(bar_accf + 8 * as);   // accumulator stage complete
+        GEMM_TRACE(lt, 2);                         // issuer: all MMAs of the tile issued
       }
     }
     __syncwarp();
@@ -339,6 +361,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (warp == 2 && lane == 0) GEMM_TRACE(lt, 3);   // epilogue: accumulator complete
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + as * BN;
       if (tma_epi == 2) {
         // Fast path (bf16 row-major output, at most bias + activation): TMEM -> registers -> swizzled shared tile -> TMA
@@ -705,16 +728,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acce + 8 * as);
+      if (warp == 2 && lane == 0) GEMM_TRACE(lt, 4);   // epilogue: tile handed to the store engine, accumulator released
     }
     if (tma_epi && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     __syncwarp();
   }
   tc_fence_before();
   __syncthreads();
+  GEMM_TRACE_CTA(2);   // end of the main phase
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+  GEMM_TRACE_CTA(3);
 }
 
 // ---------------------------------------------------------------------------
@@ -893,6 +919,12 @@ int ffb_gemm_bf16_peer(const void* A, const void* B, int a_mn, int b_mn, long lo
   if (peer_which != 1 && peer_which != 2) return -20;
   return gemm_launch(A, B, a_mn, b_mn, lda, ldb, a_bstride, b_bstride, batch, 128, args, stream, peer_which, peer_ptrs, n_peers);
 }
+
+#ifdef FFB_GEMM_TRACE
+int ffb_gemm_trace_read(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * (256 + 4 * 160)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // Reads and clears the device status word; out[0] != 0 means a kernel gave up
 // on a wait (out[1..3] = block index, out[4] = detail).

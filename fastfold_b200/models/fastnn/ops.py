@@ -613,9 +613,10 @@ class _TriangleAttention(nn.Module):
         self.attention = SelfAttention(qkv_dim=d_pair, c=c, n_head=n_head, out_dim=d_pair, gating=True, last_bias_fuse=True)
         self.out_bias = nn.Parameter(torch.zeros((d_pair,)))
 
-    def forward(self, Z_raw, Z_mask, dropmask=None, Z_norm=None):
-        """``Z_norm``: the normalised input in the layout the attention runs in (for the ending node: transposed),
-        when the caller already has it from the fused all-to-all + LayerNorm."""
+    def forward(self, Z_raw, Z_mask, dropmask=None, Z_norm=None, strided=None):
+        """``Z_norm``: the normalised input when the caller already has it from the fused all-to-all + LayerNorm; for the
+        ending node the caller also says through ``strided`` which layout that is (``self.strided_for`` decides:
+        True = same layout as ``Z_raw``, False = transposed)."""
         training = self.training
         if self.starting:
             mask = Z_mask
@@ -627,7 +628,8 @@ class _TriangleAttention(nn.Module):
                 dropmask = F.dropout(torch.ones_like(Z_raw[:, :, 0:1, :]), p=self.p_drop, training=True)
         if not training:
             dropmask = None
-        strided = self.strided(Z_raw)
+        if strided is None:
+            strided = self.strided(Z_raw)
         if Z_norm is not None:
             Z = Z_norm
         else:
@@ -649,11 +651,15 @@ class _TriangleAttention(nn.Module):
     def strided(self, Z_raw):
         """Ending node on the GPU: the attention kernels walk the first pair axis through their row / batch strides, so
         neither the input nor the output is transposed (``Z_norm``, when given, is then in the un-transposed layout)."""
+        return self.strided_for(Z_raw.shape[1], Z_raw)
+
+    def strided_for(self, n_attn, like):
+        """``n_attn``: length of the axis the ending node attends along (the full first pair axis)."""
         if self.starting or CHUNK_SIZE is not None:
             return False
-        if not (Z_raw.is_cuda and Z_raw.dtype == torch.bfloat16 and self.c == flash.HEAD_DIM and Z_raw.shape[1] % 8 == 0):
+        if not (like.is_cuda and like.dtype == torch.bfloat16 and self.c == flash.HEAD_DIM and n_attn % 8 == 0):
             return False
-        return not (torch.is_grad_enabled() and Z_raw.shape[1] > 512)
+        return not (torch.is_grad_enabled() and n_attn > 512)
 
     def inplace(self, Z_raw, Z_mask, dropmask=None):
         Z_raw[0] = self.forward(Z_raw[0], Z_mask, dropmask)

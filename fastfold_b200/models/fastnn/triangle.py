@@ -59,9 +59,10 @@ class PairCore(nn.Module):
         pair = self.TriangleMultiplicationIncoming(pair, pair_mask_col, dm, Z_norm=pn)
         pair, pn = a2a_layer_norm(pair, self.TriangleAttentionStartingNode.layernorm1, 1)
         pair = self.TriangleAttentionStartingNode(pair, pair_mask_row, d.get("tri_att_start"), Z_norm=pn)
-        pair, pn = a2a_layer_norm(pair, self.TriangleAttentionEndingNode.layernorm1, 0,
-                                  transpose_norm=not self.TriangleAttentionEndingNode.strided(pair))
-        pair = self.TriangleAttentionEndingNode(pair, pair_mask_col, d.get("tri_att_end"), Z_norm=pn)
+        # the ending node attends along the first pair axis, which is complete after the switch to column shards
+        strided = self.TriangleAttentionEndingNode.strided_for(pair.shape[2], pair)
+        pair, pn = a2a_layer_norm(pair, self.TriangleAttentionEndingNode.layernorm1, 0, transpose_norm=not strided)
+        pair = self.TriangleAttentionEndingNode(pair, pair_mask_col, d.get("tri_att_end"), Z_norm=pn, strided=strided)
         pair = self.PairTransition(pair)
         pair = col_to_row(pair)
         return pair
