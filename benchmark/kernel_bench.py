@@ -1,0 +1,198 @@
+"""Micro-benchmarks of the hand-written kernels on the shapes of the headline configuration.
+
+    python benchmark/kernel_bench.py gemm      [--m 65536 --n 512 --k 128] [--bias] [--ref]
+    python benchmark/kernel_bench.py attention [--b 128 --h 8 --len 256] [--backward]
+    python benchmark/kernel_bench.py layernorm [--rows 65536 --c 128] [--backward]
+    python benchmark/kernel_bench.py all
+
+Every timing is taken on the device: the op is captured ``--iters`` times in a CUDA graph, each instance preceded
+by a write of a buffer larger than the L2 cache, and the time of the flush-only graph is subtracted, so the figure
+is a cold-cache kernel time without host launch overhead.  ``--plain`` skips graphs and flushes and just launches
+the op a few times (the form to put under a profiler).  Roofline fractions are printed against the measured peaks in
+``MEASURED_PEAKS.json`` at the repository root when that file exists.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from fastfold_b200 import ops as K  # noqa: E402
+from fastfold_b200.ops import flash  # noqa: E402
+
+DEV = "cuda"
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return d.get("hbm_gbs", 6650.0) * 1e9, d.get("bf16_tflops", 1590.0) * 1e12, "of measured"
+    return 6650e9, 1590e12, "of fallback"
+
+
+def _graph_time(fn, iters, reps=3):
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        fn()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(iters):
+                fn()
+    torch.cuda.synchronize()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (iters * reps)          # us
+
+
+class Timer:
+    def __init__(self, iters, plain):
+        self.iters, self.plain = iters, plain
+        self.flush = None if plain else torch.empty(192 << 20, device=DEV, dtype=torch.uint8)
+
+    def __call__(self, fn):
+        if self.plain:
+            for _ in range(4):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(self.iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / self.iters
+
+        def both():
+            self.flush.zero_()
+            fn()
+        return _graph_time(both, self.iters) - _graph_time(lambda: self.flush.zero_(), self.iters)
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def bench_gemm(t, M, N, Kd, bias, ref):
+    hbm, flops_peak, tag = _peaks()
+    a, b = _rand(M, Kd), _rand(N, Kd)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    bv = _rand(N) if bias else None
+    us = t(lambda: K.gemm(a, b, out=out, bias=bv))
+    byt = (M * Kd + N * Kd + M * N) * 2
+    fl = 2.0 * M * N * Kd
+    floor = max(byt / hbm, fl / flops_peak) * 1e6
+    line = "gemm M=%d N=%d K=%d%s: %.1f us  (%.0f GB/s, %.0f TFLOP/s; roofline floor %.1f us -> %.2f %s)" % (
+        M, N, Kd, " +bias" if bias else "", us, byt / us / 1e3, fl / us / 1e6, floor, floor / us, tag)
+    if ref:
+        line += "  | torch.matmul %.1f us" % t(lambda: torch.matmul(a, b.t(), out=out))
+    print(line)
+
+
+def bench_attention(t, B, H, n, backward):
+    hbm, _, tag = _peaks()
+    qkv = _rand(1, B, n, 3, H, 32, scale=0.7)
+    bias = _rand(1, 1, H, n, n)
+    mask = (torch.rand(1, B, n, device=DEV) > 0.1).to(torch.bfloat16)
+    byt = (4 * B * n * H * 32 + H * n * n) * 2
+    if not backward:
+        with torch.no_grad():
+            us = t(lambda: flash.flash_attention_packed(qkv, mask, bias, 32 ** -0.5))
+        mufu = B * H * n * n / (148 * 16 * 1.9e9) * 1e6
+        print("attention fwd B=%d H=%d n=%d d=32: %.1f us  (HBM floor %.1f us, exp-unit floor %.1f us -> %.2f %s)" % (
+            B, H, n, us, byt / hbm * 1e6, mufu, max(byt / hbm * 1e6, mufu) / us, tag))
+        return
+    qkv.requires_grad_(True)
+    bias.requires_grad_(True)
+
+    def both():      # forward and backward in one go (autograd runs the backward on the stream of its forward)
+        out = flash.flash_attention_packed(qkv, mask, bias, 32 ** -0.5)
+        out.backward(g)
+        qkv.grad = None
+        bias.grad = None
+    g = torch.randn(1, B, n, H * 32, device=DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        fwd = t(lambda: flash.flash_attention_packed(qkv, mask, bias, 32 ** -0.5))
+    us = t(both)
+    print("attention fwd+bwd (+ bias-gradient reduction) B=%d H=%d n=%d d=32: %.1f us  (backward alone ~ %.1f us)" % (B, H, n, us, us - fwd))
+
+
+def bench_layernorm(t, rows, C, backward):
+    hbm, _, tag = _peaks()
+    x = _rand(rows, C)
+    ln = K.LayerNorm(C).to(DEV, torch.bfloat16)
+    if not backward:
+        with torch.no_grad():
+            us = t(lambda: ln(x))
+        byt = 2 * rows * C * 2
+        print("layernorm fwd rows=%d C=%d: %.1f us  (%.0f GB/s -> %.2f %s)" % (rows, C, us, byt / us / 1e3, byt / hbm * 1e6 / us, tag))
+        return
+    x.requires_grad_(True)
+    g = torch.randn(rows, C, device=DEV).to(torch.bfloat16)
+
+    def both():
+        y = ln(x)
+        y.backward(g)
+        x.grad = None
+        ln.weight.grad = None
+        ln.bias.grad = None
+    with torch.no_grad():
+        fwd = t(lambda: ln(x))
+    us = t(both) - fwd
+    byt = 3 * rows * C * 2
+    print("layernorm bwd rows=%d C=%d: %.1f us  (%.0f GB/s -> %.2f %s)" % (rows, C, us, byt / us / 1e3, byt / hbm * 1e6 / us, tag))
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "all"])
+    ap.add_argument("--m", type=int, default=65536)
+    ap.add_argument("--n", type=int, default=512)
+    ap.add_argument("--k", type=int, default=128)
+    ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--ref", action="store_true", help="also time torch.matmul (cuBLAS) on the same shape")
+    ap.add_argument("--b", type=int, default=128)
+    ap.add_argument("--h", type=int, default=8)
+    ap.add_argument("--len", type=int, default=256)
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--c", type=int, default=128)
+    ap.add_argument("--backward", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--plain", action="store_true", help="no graphs, no cache flush: a few plain launches (for profilers)")
+    args = ap.parse_args()
+    t = Timer(args.iters, args.plain)
+    if args.op == "gemm":
+        bench_gemm(t, args.m, args.n, args.k, args.bias, args.ref)
+    elif args.op == "attention":
+        bench_attention(t, args.b, args.h, args.len, args.backward)
+    elif args.op == "layernorm":
+        bench_layernorm(t, args.rows, args.c, args.backward)
+    else:
+        for (M, N, Kd) in [(65536, 128, 128), (65536, 512, 128), (65536, 384, 128), (65536, 128, 512), (32768, 768, 256), (32768, 1024, 256),
+                           (32768, 256, 1024), (32768, 256, 256), (8192, 8192, 128), (8192, 8192, 8192)]:
+            bench_gemm(t, M, N, Kd, True, True)
+        for (B, H, n) in [(128, 8, 256), (256, 8, 128), (256, 4, 256)]:
+            bench_attention(t, B, H, n, False)
+            bench_attention(t, B, H, n, True)
+        for (rows, C) in [(65536, 128), (32768, 256)]:
+            bench_layernorm(t, rows, C, False)
+            bench_layernorm(t, rows, C, True)
+    from fastfold_b200.ops import _lib
+    st = _lib.read_status()
+    if st[0]:
+        print("device status:", st)
+
+
+if __name__ == "__main__":
+    main()

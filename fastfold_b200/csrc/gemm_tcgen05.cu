@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kb_total = (g.K + BK - 1) / BK;
-  if (tma_epi == 2 && g.bias) {
+  if ((tma_epi == 2 || tma_epi == 3) && g.bias && g.N <= FAST_BIAS_MAX_N) {
     // fast epilogue: the whole bias vector as fp32 in shared memory, read back as broadcast 16-byte loads
     const bf16* bp = reinterpret_cast<const bf16*>(g.bias);
     for (int i = threadIdx.x; i < FAST_BIAS_MAX_N + 64; i += GEMM_THREADS) s_bias[i] = (i < g.N) ? __bfloat162float(bp[i]) : 0.f;
@@ -364,8 +364,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
       if (warp == 2 && lane == 0) GEMM_TRACE(lt, 3);   // epilogue: accumulator complete
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + as * BN;
       if (tma_epi == 2) {
-        // Fast path (bf16 row-major output, at most bias + activation): TMEM -> registers -> swizzled shared tile -> TMA
-        // store, with no per-element branches.  The common projection / gradient GEMMs of the model all land here.
+        // Fast path (bf16 output, row-major or block-permuted, at most bias + activation): TMEM -> registers -> shared
+        // tile -> bulk store, with no per-element branches.  The common projection / gradient GEMMs of the model land here.
         const int row0 = tc.m0 + quad * 32;
 #pragma unroll 1
         for (int c = half; c < BN / 64; c += 2) {
@@ -378,14 +378,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
           tmem_ld_32x32(taddr + c * 64 + 32, v + 32);
           tmem_ld_wait();
           if (g.bias) {
-            const float4* bp = reinterpret_cast<const float4*>(s_bias + col0);
+            if (g.N <= FAST_BIAS_MAX_N) {
+              const float4* bp = reinterpret_cast<const float4*>(s_bias + col0);
 #pragma unroll
-            for (int q = 0; q < 16; ++q) {
-              const float4 b4 = bp[q];
-              v[4 * q] += b4.x;
-              v[4 * q + 1] += b4.y;
-              v[4 * q + 2] += b4.z;
-              v[4 * q + 3] += b4.w;
+              for (int q = 0; q < 16; ++q) {
+                const float4 b4 = bp[q];
+                v[4 * q] += b4.x;
+                v[4 * q + 1] += b4.y;
+                v[4 * q + 2] += b4.z;
+                v[4 * q + 3] += b4.w;
+              }
+            } else {
+              // wide outputs: the chunk's 64 bias values straight from global memory (same address in every lane)
+              const bf16* bp = reinterpret_cast<const bf16*>(g.bias) + col0;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float t[8];
+                load8(bp + q * 8, (g.N - col0 - q * 8) >= 8 && ((reinterpret_cast<uintptr_t>(bp + q * 8) & 15) == 0), g.N - col0 - q * 8, t);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] += t[j];
+              }
             }
           }
           if (g.act == ACT_RELU) {
@@ -395,21 +407,34 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
 #pragma unroll
             for (int j = 0; j < 64; ++j) v[j] = sigmoidf_(v[j]);
           }
-          uint8_t* obuf = reinterpret_cast<uint8_t*>(stg) + out_buf * 4096 + lane * 128;
+          uint8_t* obuf = reinterpret_cast<uint8_t*>(stg) + out_buf * 4096;
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             uint4 pk;
             bf162* hp = reinterpret_cast<bf162*>(&pk);
 #pragma unroll
             for (int j = 0; j < 4; ++j) hp[j] = __floats2bfloat162_rn(v[u * 8 + 2 * j], v[u * 8 + 2 * j + 1]);
-            *reinterpret_cast<uint4*>(obuf + ((u ^ (lane & 7)) << 4)) = pk;
+            // row-major: 128-byte swizzled rows; block-permuted: two linear [32][32] blocks
+            uint8_t* slot = g.cq ? obuf + (u >> 2) * 2048 + lane * 64 + ((u & 3) << 4) : obuf + lane * 128 + ((u ^ (lane & 7)) << 4);
+            *reinterpret_cast<uint4*>(slot) = pk;
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&tmC),
-                         "r"(epi_smem + out_buf * 4096), "r"(col0), "r"(row0), "r"(tc.batch)
-                         : "memory");
+            if (g.cq) {
+              const int m1 = row0 >> 5;
+              bf16* dst = reinterpret_cast<bf16*>(g.C) + (long long)tc.batch * g.c_bstride + (long long)(m1 / g.cq_mdiv) * g.cq_sr2 +
+                          (long long)(m1 % g.cq_mdiv) * g.cq_sr1 + (long long)(col0 >> 5) * g.cq_sc1;
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 2048;" ::"l"(dst), "r"(epi_smem + out_buf * 4096)
+                           : "memory");
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 2048;" ::"l"(dst + g.cq_sc1),
+                           "r"(epi_smem + out_buf * 4096 + 2048)
+                           : "memory");
+            } else {
+              asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&tmC),
+                           "r"(epi_smem + out_buf * 4096), "r"(col0), "r"(row0), "r"(tc.batch)
+                           : "memory");
+            }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
           out_buf ^= 1;
@@ -875,8 +900,7 @@ static int gemm_launch(const void* A, const void* B, int a_mn, int b_mn, long lo
     if (tma_epi && g.mul && make_tmap_bf16(&epi[1], g.mul, g.M, g.N, g.ldmul, batch, g.mul_bstride, 64, 32)) tma_epi = 0;
     if (tma_epi && g.resid && make_tmap_bf16(&epi[2], g.resid, g.M, g.N, g.ldres, batch, g.res_bstride, 64, 32)) tma_epi = 0;
   }
-  if (tma_epi && !g.cq && !g.mul && !g.resid && !g.rowscale && !g.dmask && g.alpha == 1.0f && (!g.bias || g.N <= FAST_BIAS_MAX_N))
-    tma_epi = 2;   // fast epilogue
+  if (tma_epi && !g.mul && !g.resid && !g.rowscale && !g.dmask && g.alpha == 1.0f) tma_epi = 2;   // fast epilogue
   if (!tma_epi && g.trans_out && g.out_mode == OUT_BF16 && !g.glu && !g.mul && !g.resid && !g.rowscale && !g.dmask && g.alpha == 1.0f &&
       (!g.bias || g.N <= FAST_BIAS_MAX_N) && al16(g.C, g.ldc, g.c_bstride) && (batch == 1 || g.c_bstride != 0) && g.M >= 32) {
     // fast transposed epilogue: C^T is a [N][M] matrix with row stride ldc; tiles of 64 rows x 32 contiguous elements
