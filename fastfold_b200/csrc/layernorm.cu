@@ -302,6 +302,165 @@ __global__ void __launch_bounds__(256) ln_fwd_transposed_kernel(const bf16* __re
   }
 }
 
+// ---------------------------------------------------------------------------
+// bf16 rows of C = 8 * L elements, L in {8, 16, 32} lanes per row (C = 64, 128, 256 - every LayerNorm of the
+// Evoformer): a warp works on 32 / L rows side by side and on MR_U such groups per step, so that every lane has
+// MR_U independent 16-byte loads in flight (the one-row-per-warp kernels above leave half the lanes idle at C = 128
+// and have a single load in flight per lane).
+// ---------------------------------------------------------------------------
+constexpr int MR_U = 4;
+
+template <int L>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = L / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  bf162* h = reinterpret_cast<bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+template <int L>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_mr_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma,
+                                                                 const bf16* __restrict__ beta, bf16* __restrict__ y,
+                                                                 float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                 long long rows, float eps) {
+  constexpr int C = 8 * L, G = 32 / L;
+  const int lane = threadIdx.x & 31, li = lane % L, grp = lane / L;
+  const long long base = ((long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5)) * (G * MR_U) + grp;
+  float g[8], b[8];
+  unpack8(*reinterpret_cast<const uint4*>(gamma + li * 8), g);
+  unpack8(*reinterpret_cast<const uint4*>(beta + li * 8), b);
+  uint4 raw[MR_U];
+#pragma unroll
+  for (int u = 0; u < MR_U; ++u) {
+    const long long row = base + u * G;
+    raw[u] = row < rows ? *reinterpret_cast<const uint4*>(x + row * C + li * 8) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int u = 0; u < MR_U; ++u) {
+    const long long row = base + u * G;
+    float v[8];
+    unpack8(raw[u], v);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[j];
+    const float mean = group_sum<L>(s) * (1.f / C);
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] -= mean;
+      q += v[j] * v[j];
+    }
+    const float rstd = rsqrtf(group_sum<L>(q) * (1.f / C) + eps);
+    if (row < rows) {
+      if (li == 0) {
+        if (mean_out) mean_out[row] = mean;
+        if (rstd_out) rstd_out[row] = rstd;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = v[j] * rstd * g[j] + b[j];
+      *reinterpret_cast<uint4*>(y + row * C + li * 8) = pack8(v);
+    }
+  }
+}
+
+// part: [gridDim.x][2][C], written with plain stores (every block writes its whole row of partials)
+template <int L>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_mr_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                                 const bf16* __restrict__ gamma, const float* __restrict__ mean,
+                                                                 const float* __restrict__ rstd, bf16* __restrict__ dx,
+                                                                 float* __restrict__ part, long long rows) {
+  constexpr int C = 8 * L, G = 32 / L;
+  __shared__ float red[LN_WARPS][2][C];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, li = lane % L, grp = lane / L;
+  float g[8], dg[8], db[8];
+  unpack8(*reinterpret_cast<const uint4*>(gamma + li * 8), g);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) dg[j] = db[j] = 0.f;
+  const long long step = (long long)gridDim.x * LN_WARPS * (G * MR_U);
+  for (long long base = ((long long)blockIdx.x * LN_WARPS + warp) * (G * MR_U) + grp; base - grp < rows; base += step) {
+    uint4 rx[MR_U], rd[MR_U];
+    float mu[MR_U], rs[MR_U];
+#pragma unroll
+    for (int u = 0; u < MR_U; ++u) {
+      const long long row = base + u * G;
+      const bool ok = row < rows;
+      rx[u] = ok ? *reinterpret_cast<const uint4*>(x + row * C + li * 8) : make_uint4(0, 0, 0, 0);
+      rd[u] = ok ? *reinterpret_cast<const uint4*>(dy + row * C + li * 8) : make_uint4(0, 0, 0, 0);
+      mu[u] = ok ? mean[row] : 0.f;
+      rs[u] = ok ? rstd[row] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < MR_U; ++u) {
+      const long long row = base + u * G;
+      float xh[8], d[8];
+      unpack8(rx[u], xh);
+      unpack8(rd[u], d);
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[j] = (xh[j] - mu[u]) * rs[u];
+        dg[j] += d[j] * xh[j];
+        db[j] += d[j];
+        d[j] *= g[j];
+        s1 += d[j];
+        s2 += d[j] * xh[j];
+      }
+      s1 = group_sum<L>(s1) * (1.f / C);
+      s2 = group_sum<L>(s2) * (1.f / C);
+      if (row < rows) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d[j] = rs[u] * (d[j] - s1 - xh[j] * s2);
+        *reinterpret_cast<uint4*>(dx + row * C + li * 8) = pack8(d);
+      }
+    }
+  }
+  // fold the row groups of the warp (lanes li, li + L, ...), then the warps of the block
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+#pragma unroll
+    for (int o = L; o < 32; o <<= 1) {
+      dg[j] += __shfl_xor_sync(0xffffffffu, dg[j], o);
+      db[j] += __shfl_xor_sync(0xffffffffu, db[j], o);
+    }
+  }
+  if (grp == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      red[warp][0][li * 8 + j] = dg[j];
+      red[warp][1][li * 8 + j] = db[j];
+    }
+  }
+  __syncthreads();
+  float* p0 = part + (long long)blockIdx.x * 2 * C;
+  for (int i = threadIdx.x; i < 2 * C; i += LN_WARPS * 32) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < LN_WARPS; ++w) t += (&red[w][0][0])[i];
+    p0[i] = t;
+  }
+}
+
+template <typename T>
+struct IsBf16 { static constexpr bool value = false; };
+template <>
+struct IsBf16<bf16> { static constexpr bool value = true; };
+
 template <typename T>
 static int ln_fwd_dispatch(const T* x, const T* g, const T* b, T* y, float* mean, float* rstd, long long rows, int C, float eps,
                            cudaStream_t st) {
@@ -309,6 +468,16 @@ static int ln_fwd_dispatch(const T* x, const T* g, const T* b, T* y, float* mean
   const dim3 grid((unsigned)((rows + LN_WARPS - 1) / LN_WARPS));
   const bool aligned = (C % VEC == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
                                            reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(b)) % 16 == 0);
+  if (IsBf16<T>::value && aligned && (C == 64 || C == 128 || C == 256)) {
+    const bf16 *xb = reinterpret_cast<const bf16*>(x), *gb = reinterpret_cast<const bf16*>(g), *bb = reinterpret_cast<const bf16*>(b);
+    bf16* yb = reinterpret_cast<bf16*>(y);
+    const int rows_per_block = LN_WARPS * MR_U * (256 / C);
+    const dim3 gmr((unsigned)((rows + rows_per_block - 1) / rows_per_block));
+    if (C == 64) ln_fwd_mr_kernel<8><<<gmr, LN_WARPS * 32, 0, st>>>(xb, gb, bb, yb, mean, rstd, rows, eps);
+    else if (C == 128) ln_fwd_mr_kernel<16><<<gmr, LN_WARPS * 32, 0, st>>>(xb, gb, bb, yb, mean, rstd, rows, eps);
+    else ln_fwd_mr_kernel<32><<<gmr, LN_WARPS * 32, 0, st>>>(xb, gb, bb, yb, mean, rstd, rows, eps);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  }
   if (aligned && C <= 32 * VEC) ln_fwd_kernel<T, VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
   else if (aligned && C <= 64 * VEC) ln_fwd_kernel<T, 2 * VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
   else if (aligned && C <= 128 * VEC) ln_fwd_kernel<T, 4 * VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
@@ -323,7 +492,13 @@ static int ln_bwd_dispatch(const T* dy, const T* x, const T* g, const float* mea
   if (cudaMemsetAsync(part, 0, sizeof(float) * 2 * C * nblocks, st) != cudaSuccess) return -1;
   const bool aligned = (C % VEC == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
                                            reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(g)) % 16 == 0);
-  if (aligned && C <= 32 * VEC) ln_bwd_kernel<T, VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
+  if (IsBf16<T>::value && aligned && (C == 64 || C == 128 || C == 256)) {
+    const bf16 *db_ = reinterpret_cast<const bf16*>(dy), *xb = reinterpret_cast<const bf16*>(x), *gb = reinterpret_cast<const bf16*>(g);
+    bf16* dxb = reinterpret_cast<bf16*>(dx);
+    if (C == 64) ln_bwd_mr_kernel<8><<<nblocks, LN_WARPS * 32, 0, st>>>(db_, xb, gb, mean, rstd, dxb, part, rows);
+    else if (C == 128) ln_bwd_mr_kernel<16><<<nblocks, LN_WARPS * 32, 0, st>>>(db_, xb, gb, mean, rstd, dxb, part, rows);
+    else ln_bwd_mr_kernel<32><<<nblocks, LN_WARPS * 32, 0, st>>>(db_, xb, gb, mean, rstd, dxb, part, rows);
+  } else if (aligned && C <= 32 * VEC) ln_bwd_kernel<T, VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
   else if (aligned && C <= 64 * VEC) ln_bwd_kernel<T, 2 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
   else if (aligned && C <= 128 * VEC) ln_bwd_kernel<T, 4 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
   else ln_bwd_generic_kernel<T><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
