@@ -248,7 +248,8 @@ def _multimer_overrides(c):
     c.data.common.max_recycling_iters = 20
     c.model.input_embedder.update_from({"tf_dim": 21, "max_relative_idx": 32, "use_chain_relative": True, "max_relative_chain": 2})
     c.model.template.update_from({"template_single_embedder": {"c_in": 34, "c_m": c.globals.c_m},
-                                  "template_pair_embedder": {"c_z": c.globals.c_z, "c_out": 64, "c_dgram": 39, "c_aatype": 22}})
+                                  "template_pair_embedder": {"c_z": c.globals.c_z, "c_out": 64, "c_dgram": 39, "c_aatype": 22},
+                                  "c_t": c.globals.c_t, "c_z": c.globals.c_z})
     c.model.template.template_pair_stack.tri_mul_first = True
     c.model.heads.masked_msa.c_out = 22
     c.model.structure_module.trans_scale_factor = 20

@@ -38,7 +38,7 @@ class AlphaFold(nn.Module):
         self.extra_msa_embedder = ExtraMSAEmbedder(**c.extra_msa["extra_msa_embedder"])
         self.extra_msa_stack = ExtraMSAStack(is_multimer=self.globals.get("is_multimer", False), **c.extra_msa["extra_msa_stack"])
         self.evoformer = EvoformerStack(is_multimer=self.globals.get("is_multimer", False), **c["evoformer_stack"])
-        self.structure_module = StructureModule(**c["structure_module"])
+        self.structure_module = StructureModule(is_multimer=self.globals.get("is_multimer", False), **c["structure_module"])
         self.aux_heads = AuxiliaryHeads(c["heads"])
 
     # ------------------------------------------------------------------
@@ -57,7 +57,11 @@ class AlphaFold(nn.Module):
         msa_mask = feats["msa_mask"]
         inplace = bool(self.globals.get("inplace", False)) and not (self.training or torch.is_grad_enabled())
 
-        m, z = self.input_embedder(feats["target_feat"], feats["residue_index"], feats["msa_feat"])
+        is_multimer = bool(self.globals.get("is_multimer", False))
+        if is_multimer:
+            m, z = self.input_embedder(feats)
+        else:
+            m, z = self.input_embedder(feats["target_feat"], feats["residue_index"], feats["msa_feat"])
         if None in [m_1_prev, z_prev, x_prev]:
             m_1_prev = m.new_zeros((*batch_dims, n, self.config.input_embedder.c_m), requires_grad=False)
             z_prev = z.new_zeros((*batch_dims, n, n, self.config.input_embedder.c_z), requires_grad=False)
@@ -71,7 +75,18 @@ class AlphaFold(nn.Module):
         z = z + z_prev_emb
         del m_1_prev, z_prev, x_prev, m_1_prev_emb, z_prev_emb
 
-        if self.config.template.enabled:
+        if self.config.template.enabled and is_multimer:
+            template_feats = {k: v for k, v in feats.items() if k.startswith("template_")}
+            asym = feats["asym_id"]
+            multichain_mask_2d = asym[..., None] == asym[..., None, :]
+            template_embeds = self.template_embedder(template_feats, z, pair_mask.to(dtype=z.dtype), len(batch_dims), self.globals.chunk_size,
+                                                     multichain_mask_2d=multichain_mask_2d)
+            z = z + template_embeds["template_pair_embedding"]
+            if "template_single_embedding" in template_embeds:
+                m = torch.cat([m, template_embeds["template_single_embedding"].to(m.dtype)], dim=-3)
+                msa_mask = torch.cat([feats["msa_mask"], template_embeds["template_mask"].to(feats["msa_mask"].dtype)], dim=-2)
+            del template_feats, template_embeds
+        elif self.config.template.enabled:
             template_feats = {k: v for k, v in feats.items() if k.startswith("template_")}
             template_embeds = self.template_embedder(template_feats, z, pair_mask.to(dtype=z.dtype), len(batch_dims),
                                                      self.globals.chunk_size)

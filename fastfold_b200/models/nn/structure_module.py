@@ -51,20 +51,46 @@ class AngleResnet(nn.Module):
         return unnormalized, s / norm
 
 
+class PointProjection(nn.Module):
+    """Multimer parameterisation of the point projections: one linear layer whose output is laid out
+    ``[head][x | y | z][point]`` (fastfold/model/nn/structure_module.py:160-193); returns global-frame points
+    ``[*, N, H, P, 3]``."""
+
+    def __init__(self, c_hidden, num_points, no_heads):
+        super().__init__()
+        self.no_heads, self.num_points = no_heads, num_points
+        self.linear = Linear(c_hidden, no_heads * 3 * num_points)
+
+    def forward(self, activations, rigids):
+        p = self.linear(activations)
+        p = p.reshape(*p.shape[:-1], self.no_heads, 3, self.num_points).transpose(-1, -2)       # [*, N, H, P, 3]
+        return rigids[..., None, None].apply(p)
+
+
 class InvariantPointAttention(nn.Module):
     """Algorithm 22.  Attention logits = scalar q.k + pair bias - weighted squared distances between query / key points
     expressed in the global frame; outputs = attended scalars, attended points (back in the local frame, plus their
     norms) and attended pair rows."""
 
-    def __init__(self, c_s, c_z, c_hidden, no_heads, no_qk_points, no_v_points, inf=1e5, eps=1e-8):
+    def __init__(self, c_s, c_z, c_hidden, no_heads, no_qk_points, no_v_points, inf=1e5, eps=1e-8, is_multimer=False):
         super().__init__()
         self.c_s, self.c_z, self.c_hidden, self.no_heads = c_s, c_z, c_hidden, no_heads
         self.no_qk_points, self.no_v_points, self.inf, self.eps = no_qk_points, no_v_points, inf, eps
+        self.is_multimer = is_multimer
         hc = c_hidden * no_heads
-        self.linear_q = Linear(c_s, hc)
-        self.linear_kv = Linear(c_s, 2 * hc)
-        self.linear_q_points = Linear(c_s, no_heads * no_qk_points * 3)
-        self.linear_kv_points = Linear(c_s, no_heads * (no_qk_points + no_v_points) * 3)
+        if is_multimer:
+            # separate, bias-free q / k / v projections and one point projection per role (multimer checkpoint layout)
+            self.linear_q = Linear(c_s, hc, bias=False)
+            self.linear_k = Linear(c_s, hc, bias=False)
+            self.linear_v = Linear(c_s, hc, bias=False)
+            self.linear_q_points = PointProjection(c_s, no_qk_points, no_heads)
+            self.linear_k_points = PointProjection(c_s, no_qk_points, no_heads)
+            self.linear_v_points = PointProjection(c_s, no_v_points, no_heads)
+        else:
+            self.linear_q = Linear(c_s, hc)
+            self.linear_kv = Linear(c_s, 2 * hc)
+            self.linear_q_points = Linear(c_s, no_heads * no_qk_points * 3)
+            self.linear_kv_points = Linear(c_s, no_heads * (no_qk_points + no_v_points) * 3)
         self.linear_b = Linear(c_z, no_heads)
         self.head_weights = nn.Parameter(torch.zeros((no_heads)))
         ipa_point_weights_init_(self.head_weights)
@@ -76,19 +102,28 @@ class InvariantPointAttention(nn.Module):
     def forward(self, s, z, r, mask):
         H = self.no_heads
         q = self.linear_q(s)
-        kv = self.linear_kv(s)
         q = q.view(q.shape[:-1] + (H, -1))
-        kv = kv.view(kv.shape[:-1] + (H, -1))
-        k, v = torch.split(kv, self.c_hidden, dim=-1)
-        q_pts = self.linear_q_points(s)
-        q_pts = torch.stack(torch.split(q_pts, q_pts.shape[-1] // 3, dim=-1), dim=-1)
-        q_pts = r[..., None].apply(q_pts)
-        q_pts = q_pts.view(q_pts.shape[:-2] + (H, self.no_qk_points, 3))
-        kv_pts = self.linear_kv_points(s)
-        kv_pts = torch.stack(torch.split(kv_pts, kv_pts.shape[-1] // 3, dim=-1), dim=-1)
-        kv_pts = r[..., None].apply(kv_pts)
-        kv_pts = kv_pts.view(kv_pts.shape[:-2] + (H, -1, 3))
-        k_pts, v_pts = torch.split(kv_pts, [self.no_qk_points, self.no_v_points], dim=-2)
+        if self.is_multimer:
+            k = self.linear_k(s)
+            v = self.linear_v(s)
+            k = k.view(k.shape[:-1] + (H, -1))
+            v = v.view(v.shape[:-1] + (H, -1))
+            q_pts = self.linear_q_points(s, r)
+            k_pts = self.linear_k_points(s, r)
+            v_pts = self.linear_v_points(s, r)
+        else:
+            kv = self.linear_kv(s)
+            kv = kv.view(kv.shape[:-1] + (H, -1))
+            k, v = torch.split(kv, self.c_hidden, dim=-1)
+            q_pts = self.linear_q_points(s)
+            q_pts = torch.stack(torch.split(q_pts, q_pts.shape[-1] // 3, dim=-1), dim=-1)
+            q_pts = r[..., None].apply(q_pts)
+            q_pts = q_pts.view(q_pts.shape[:-2] + (H, self.no_qk_points, 3))
+            kv_pts = self.linear_kv_points(s)
+            kv_pts = torch.stack(torch.split(kv_pts, kv_pts.shape[-1] // 3, dim=-1), dim=-1)
+            kv_pts = r[..., None].apply(kv_pts)
+            kv_pts = kv_pts.view(kv_pts.shape[:-2] + (H, -1, 3))
+            k_pts, v_pts = torch.split(kv_pts, [self.no_qk_points, self.no_v_points], dim=-2)
         b = self.linear_b(z)
         a = torch.matmul(permute_final_dims(q.float(), (1, 0, 2)), permute_final_dims(k.float(), (1, 2, 0)))
         a = a * math.sqrt(1.0 / (3 * self.c_hidden))
@@ -152,8 +187,9 @@ class StructureModuleTransition(nn.Module):
 
 class StructureModule(nn.Module):
     def __init__(self, c_s, c_z, c_ipa, c_resnet, no_heads_ipa, no_qk_points, no_v_points, dropout_rate, no_blocks, no_transition_layers,
-                 no_resnet_blocks, no_angles, trans_scale_factor, epsilon, inf, **kwargs):
+                 no_resnet_blocks, no_angles, trans_scale_factor, epsilon, inf, is_multimer=False, **kwargs):
         super().__init__()
+        self.is_multimer = is_multimer
         self.c_s, self.c_z, self.no_blocks, self.trans_scale_factor, self.epsilon, self.inf = c_s, c_z, no_blocks, trans_scale_factor, epsilon, inf
         self.default_frames = None
         self.group_idx = None
@@ -162,7 +198,7 @@ class StructureModule(nn.Module):
         self.layer_norm_s = LayerNorm(c_s)
         self.layer_norm_z = LayerNorm(c_z)
         self.linear_in = Linear(c_s, c_s)
-        self.ipa = InvariantPointAttention(c_s, c_z, c_ipa, no_heads_ipa, no_qk_points, no_v_points, inf=inf, eps=epsilon)
+        self.ipa = InvariantPointAttention(c_s, c_z, c_ipa, no_heads_ipa, no_qk_points, no_v_points, inf=inf, eps=epsilon, is_multimer=is_multimer)
         self.ipa_dropout = nn.Dropout(dropout_rate)
         self.layer_norm_ipa = LayerNorm(c_s)
         self.transition = StructureModuleTransition(c_s, no_transition_layers, dropout_rate)

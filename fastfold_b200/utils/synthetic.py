@@ -12,7 +12,9 @@ import torch
 from ..common import residue_constants as rc
 
 
-def random_features(n_res, n_seq, n_extra, n_templ=0, n_recycle=3, seed=0, device="cpu", supervised=False):
+def random_features(n_res, n_seq, n_extra, n_templ=0, n_recycle=3, seed=0, device="cpu", supervised=False, chains=None):
+    """``chains``: list of chain lengths summing to ``n_res`` -> multimer features (``asym_id`` / ``entity_id`` / ``sym_id``,
+    per-chain ``residue_index``, 21-class ``target_feat``); chains of equal length count as copies of one entity."""
     g = torch.Generator().manual_seed(seed)
     R = n_recycle + 1
     aatype = torch.randint(0, 20, (n_res,), generator=g)
@@ -50,6 +52,19 @@ def random_features(n_res, n_seq, n_extra, n_templ=0, n_recycle=3, seed=0, devic
             "template_torsion_angles_mask": torch.ones(n_templ, n_res, 7),
             "template_sum_probs": torch.rand(n_templ, 1, generator=g),
         })
+    if chains is not None:
+        assert sum(chains) == n_res
+        asym, entity, sym, ridx = [], [], [], []
+        seen = {}
+        for c, L in enumerate(chains):
+            e = seen.setdefault(L, len(seen) + 1)
+            copies = sum(1 for x in chains[:c] if x == L)
+            asym += [c + 1] * L
+            entity += [e] * L
+            sym += [copies + 1] * L
+            ridx += list(range(L))
+        feats.update({"asym_id": torch.tensor(asym), "entity_id": torch.tensor(entity), "sym_id": torch.tensor(sym),
+                      "residue_index": torch.tensor(ridx), "target_feat": torch.nn.functional.one_hot(aatype, 21).float()})
     if supervised:
         feats.update(random_ground_truth(aatype, g))
     out = {}

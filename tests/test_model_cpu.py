@@ -88,3 +88,26 @@ def test_block_permuted_gemm_reference_layouts():
     do = gemm(dy, w, b_mn=True, block_out=((ni * 32, N * 32), N // 32, N * 1024, 1024, 32 * N))
     ref = (dy @ w).reshape(ni, N, 32, 32).permute(0, 2, 1, 3).reshape(ni * 32, N * 32)
     assert torch.allclose(do, ref, atol=1e-4)
+
+
+def test_multimer_preset_forward():
+    """The multimer preset builds (chain-aware input embedder, multimer template embedder, split IPA projections)
+    and runs on synthetic two-chain features."""
+    import torch
+    from fastfold_b200.config import model_config
+    from fastfold_b200.models.hub import AlphaFold
+    from fastfold_b200.utils.synthetic import random_features
+    cfg = model_config("multimer")
+    cfg.model.evoformer_stack.no_blocks = 1
+    cfg.model.extra_msa.extra_msa_stack.no_blocks = 1
+    cfg.model.template.template_pair_stack.no_blocks = 1
+    cfg.model.structure_module.no_blocks = 2
+    torch.manual_seed(0)
+    model = AlphaFold(cfg).eval()
+    assert hasattr(model.structure_module.ipa, "linear_k_points") and not hasattr(model.structure_module.ipa, "linear_kv")
+    batch = random_features(n_res=20, n_seq=6, n_extra=8, n_templ=2, n_recycle=1, chains=[12, 8])
+    with torch.no_grad():
+        out = model(batch)
+    assert out["final_atom_positions"].shape == (20, 37, 3)
+    assert torch.isfinite(out["final_atom_positions"]).all() and torch.isfinite(out["pair"]).all()
+    assert out["masked_msa_logits"].shape[-1] == 22
