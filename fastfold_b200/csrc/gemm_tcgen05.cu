@@ -766,6 +766,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
   GEMM_TRACE_CTA(3);
+#ifdef FFB_GEMM_TRACE_EXTRA
+  if (threadIdx.x == 0 && blockIdx.x < 160) {
+    // how long do the bulk stores still in flight take to complete (they hold the CTA's shared memory until then)?
+    g_gemm_trace[256 + blockIdx.x * 4 + 0] = g_gemm_trace[256 + blockIdx.x * 4 + 3];
+  }
+  if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  __syncthreads();
+  GEMM_TRACE_CTA(3);
+#endif
 }
 
 // ---------------------------------------------------------------------------

@@ -275,15 +275,32 @@ __global__ void __launch_bounds__(256) ln_fwd_transposed_kernel(const bf16* __re
     tile[c * (LNT_ROWS + 1) + tx] = (r < rows) ? __bfloat162float(x[(long long)c * rows + r]) : 0.f;
   }
   __syncthreads();
-  if (ty == 0) {
+  // statistics: every warp sums its share of the channels for row tx, shares are folded through shared memory
+  __shared__ float s_part[8][LNT_ROWS];
+  {
     float s = 0.f;
-    for (int c = 0; c < C; ++c) s += tile[c * (LNT_ROWS + 1) + tx];
-    const float mu = s / C;
+    for (int c = ty; c < C; c += 8) s += tile[c * (LNT_ROWS + 1) + tx];
+    s_part[ty][tx] = s;
+  }
+  __syncthreads();
+  float mu = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) mu += s_part[w][tx];
+  mu /= C;
+  __syncthreads();
+  {
     float q = 0.f;
-    for (int c = 0; c < C; ++c) {
+    for (int c = ty; c < C; c += 8) {
       const float d = tile[c * (LNT_ROWS + 1) + tx] - mu;
       q += d * d;
     }
+    s_part[ty][tx] = q;
+  }
+  __syncthreads();
+  if (ty == 0) {
+    float q = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) q += s_part[w][tx];
     const float rs = rsqrtf(q / C + eps);
     s_mean[tx] = mu;
     s_rstd[tx] = rs;

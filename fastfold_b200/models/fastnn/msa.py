@@ -30,8 +30,26 @@ class MSAColumnAttention(nn.Module):
         self.layernormM = K.LayerNorm(d_node)
         self.attention = SelfAttention(qkv_dim=d_node, c=c, n_head=n_head, out_dim=d_node, gating=True)
 
-    def forward(self, M_raw, M_mask, M_norm_t=None):
-        """``M_norm_t``: ``layernormM`` of the transposed input ``[1, N/P, S, c]`` when the caller already has it."""
+    def strided_for(self, n_seq, like):
+        """GPU path without transposed copies: the attention kernels walk the sequence axis (dim 1) through their row /
+        batch strides.  ``n_seq``: length of that axis."""
+        from ...ops import flash
+        from . import ops as fops
+        if fops.CHUNK_SIZE is not None:
+            return False
+        if not (like.is_cuda and like.dtype == torch.bfloat16 and self.c == flash.HEAD_DIM and n_seq % 8 == 0):
+            return False
+        return not (torch.is_grad_enabled() and n_seq > 512)
+
+    def forward(self, M_raw, M_mask, M_norm_t=None, strided=None):
+        """``M_norm_t``: ``layernormM`` of the input when the caller already has it - transposed ``[1, N/P, S, c]`` unless
+        ``strided`` (then in the layout of ``M_raw``); ``strided=None`` decides here."""
+        if strided is None:
+            strided = M_norm_t is None and self.strided_for(M_raw.shape[1], M_raw)
+        if strided:
+            M = self.layernormM(M_raw) if M_norm_t is None else M_norm_t
+            out, _ = self.attention(M, M_mask.transpose(-1, -2).contiguous(), transposed=True)
+            return M_raw + out
         M = self.layernormM(M_raw.transpose(-2, -3).contiguous()) if M_norm_t is None else M_norm_t
         out, _ = self.attention(M, M_mask.transpose(-1, -2).contiguous())
         return M_raw + out.transpose(-2, -3)
@@ -52,9 +70,10 @@ class MSACore(nn.Module):
         node_mask_row = scatter(node_mask, dim=1)
         node = self.MSARowAttentionWithPairBias(node, pair, node_mask_row, dropmask)
         # row -> column switch fused with the transpose + LayerNorm of the column attention
-        node, node_nt = a2a_layer_norm(node, self.MSAColumnAttention.layernormM, 0, transpose_norm=True)
+        strided = self.MSAColumnAttention.strided_for(node.shape[1] * core.get_dap_size(), node)     # full sequence count after the switch
+        node, node_nt = a2a_layer_norm(node, self.MSAColumnAttention.layernormM, 0, transpose_norm=not strided)
         node_mask_col = scatter(node_mask, dim=2)
-        node = self.MSAColumnAttention(node, node_mask_col, M_norm_t=node_nt)
+        node = self.MSAColumnAttention(node, node_mask_col, M_norm_t=node_nt, strided=strided)
         node = self.MSATransition(node)
         return node
 

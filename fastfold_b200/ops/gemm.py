@@ -267,7 +267,7 @@ class _LinearT(torch.autograd.Function):
             gemm(dy_t, x2, b_mn=True, out=acc, accumulate=True, splits=_wgrad_splits(x2.shape[0], tiles))   # contraction over tokens
             dw = acc.to(w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy_t.float().sum(dim=1).to(w.dtype)
+            db = torch.sum(dy_t, dim=1, dtype=torch.float32).to(w.dtype)      # converts inside the reduction, no fp32 copy
         return dx, dw, db
 
 
