@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kb_total = (g.K + BK - 1) / BK;
-  if ((tma_epi == 2 || tma_epi == 3) && g.bias && g.N <= FAST_BIAS_MAX_N) {
+  if (tma_epi && g.bias && g.N <= FAST_BIAS_MAX_N) {
     // fast epilogue: the whole bias vector as fp32 in shared memory, read back as broadcast 16-byte loads
     const bf16* bp = reinterpret_cast<const bf16*>(g.bias);
     for (int i = threadIdx.x; i < FAST_BIAS_MAX_N + 64; i += GEMM_THREADS) s_bias[i] = (i < g.N) ? __bfloat162float(bp[i]) : 0.f;
@@ -512,23 +512,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
           tmem_ld_32x32(taddr + c * 64, v);
           tmem_ld_32x32(taddr + c * 64 + 32, v + 32);
           tmem_ld_wait();
+          if (g.alpha != 1.0f) {
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            float bv[8];
-            if (g.bias) {
-              const bf16* bp = reinterpret_cast<const bf16*>(g.bias) + col0 + u * 8;
-              load8(bp, (g.N - col0 - u * 8) >= 8 && ((reinterpret_cast<uintptr_t>(bp) & 15) == 0), g.N - col0 - u * 8, bv);
+            for (int j = 0; j < 64; ++j) v[j] *= g.alpha;
+          }
+          if (g.bias) {
+            if (g.N <= FAST_BIAS_MAX_N) {
+              const float4* bp = reinterpret_cast<const float4*>(s_bias + col0);
+#pragma unroll
+              for (int q = 0; q < 16; ++q) {
+                const float4 b4 = bp[q];
+                v[4 * q] += b4.x;
+                v[4 * q + 1] += b4.y;
+                v[4 * q + 2] += b4.z;
+                v[4 * q + 3] += b4.w;
+              }
             } else {
+              const bf16* bp = reinterpret_cast<const bf16*>(g.bias) + col0;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) bv[j] = 0.f;
-            }
+              for (int q = 0; q < 8; ++q) {
+                float t[8];
+                load8(bp + q * 8, (g.N - col0 - q * 8) >= 8 && ((reinterpret_cast<uintptr_t>(bp + q * 8) & 15) == 0), g.N - col0 - q * 8, t);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float t = v[u * 8 + j] * g.alpha + bv[j];
-              if (g.act == ACT_RELU) t = fmaxf(t, 0.f);
-              else if (g.act == ACT_SIGMOID) t = sigmoidf_(t);
-              v[u * 8 + j] = t;
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] += t[j];
+              }
             }
+          }
+          if (g.act == ACT_RELU) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = fmaxf(v[j], 0.f);
+          } else if (g.act == ACT_SIGMOID) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = sigmoidf_(v[j]);
           }
           if (has_ld) {
             const bool w = mbar_wait(my_ldbar, ld_phase);

@@ -289,3 +289,57 @@ class AlignmentRunnerMultimer(AlignmentRunner):
             jobs = [pool.submit(fn, fasta_path, output_dir) for fn in (self._uniref_and_templates, self._mgnify, self._bfd, self._uniprot)]
             for j in jobs:
                 j.result()
+
+
+# ---------------------------------------------------------------------------
+# Multimer (fastfold/data/data_pipeline.py:1010-1189)
+# ---------------------------------------------------------------------------
+class DataPipelineMultimer:
+    """Features of a complex from a multi-sequence FASTA: every distinct chain goes through the monomer pipeline
+    (alignments under ``<alignment_dir>/<chain id>/``), its UniProt hits (``uniprot_hits.sto``) supply the species-tagged
+    rows for cross-chain pairing, then ``msa_pairing.pair_and_merge`` assembles the complex."""
+
+    def __init__(self, monomer_data_pipeline: DataPipeline, max_uniprot_hits: int = 50000):
+        self._monomer = monomer_data_pipeline
+        self._max_uniprot_hits = max_uniprot_hits
+
+    def _all_seq_features(self, chain_alignment_dir, sequence):
+        from . import msa_pairing
+        path = os.path.join(chain_alignment_dir, "uniprot_hits.sto") if chain_alignment_dir else None
+        if not path or not os.path.exists(path):
+            msa, dels, descs = [sequence], [[0] * len(sequence)], ["query"]
+        else:
+            msa, dels, descs = parsers.parse_stockholm(open(path).read())
+            msa, dels, descs = msa[:self._max_uniprot_hits], dels[:self._max_uniprot_hits], descs[:self._max_uniprot_hits]
+        feats = make_msa_features([msa], [dels])
+        species = [msa_pairing.get_identifiers(d).species_id.encode() for d in descs]
+        # make_msa_features removed duplicate rows: keep the identifiers of the rows that survived, in order
+        seen, kept = set(), []
+        for s_, sp in zip(msa, species):
+            if s_ not in seen:
+                seen.add(s_)
+                kept.append(sp)
+        out = {k + "_all_seq": v for k, v in feats.items() if k in ("msa", "deletion_matrix_int")}
+        out["msa_species_identifiers_all_seq"] = np.array(kept, dtype=object)
+        return out
+
+    def _process_chain(self, chain_id, sequence, description, alignment_dir, is_homomer_or_monomer):
+        chain_dir = os.path.join(alignment_dir, chain_id) if alignment_dir else None
+        feats = dict(self._monomer.process_sequence(sequence, description, chain_dir if chain_dir and os.path.isdir(chain_dir) else None))
+        if not is_homomer_or_monomer:
+            feats.update(self._all_seq_features(chain_dir, sequence))
+        return feats
+
+    def process_fasta(self, fasta_path: str, alignment_dir: Optional[str] = None) -> FeatureDict:
+        from . import msa_pairing
+        seqs, descs = parsers.parse_fasta(open(fasta_path).read())
+        is_homomer_or_monomer = len(set(seqs)) == 1
+        cache, all_chains = {}, {}
+        for i, (seq, desc) in enumerate(zip(seqs, descs)):
+            chain_id = desc.split()[0] if desc.split() else "chain_%d" % i
+            if seq not in cache:
+                cache[seq] = self._process_chain(chain_id, seq, desc, alignment_dir, is_homomer_or_monomer)
+            all_chains["%d_%s" % (i, chain_id)] = copy.deepcopy(cache[seq])
+        all_chains = msa_pairing.add_assembly_features(all_chains)
+        example = msa_pairing.pair_and_merge(all_chains)
+        return msa_pairing.pad_msa(example, 512)

@@ -1,0 +1,51 @@
+"""Multimer feature assembly: assembly ids, species pairing, block-diagonal merging."""
+import numpy as np
+
+from fastfold_b200.common import residue_constants as rc
+from fastfold_b200.data import msa_pairing as mp
+from fastfold_b200.data.data_pipeline import DataPipeline, DataPipelineMultimer
+
+
+def test_identifiers():
+    assert mp.get_identifiers("tr|A0A146SKV9|A0A146SKV9_FUNHE/2-98 some text").species_id == "FUNHE"
+    assert mp.get_identifiers("sp|P0C2L1|A3X1_LOXLA").species_id == "LOXLA"
+    assert mp.get_identifiers("UniRef90_XYZ").species_id == ""
+
+
+def _chain(seq, rows, species, ent):
+    ids = lambda s: [rc.HHBLITS_AA_TO_ID[c] for c in s]
+    n = len(seq)
+    return {"aatype": np.eye(21)[[rc.restype_order_with_x[c] for c in seq]], "sequence": np.array([seq.encode()], dtype=object),
+            "seq_length": np.array([n] * n), "residue_index": np.arange(n), "between_segment_residues": np.zeros(n, np.int32),
+            "msa": np.array([ids(seq)] + [ids(r) for r in rows[:1]], dtype=np.int32), "deletion_matrix_int": np.zeros((1 + len(rows[:1]), n), np.int32),
+            "num_alignments": np.array([2] * n), "msa_all_seq": np.array([ids(seq)] + [ids(r) for r in rows], dtype=np.int32),
+            "deletion_matrix_int_all_seq": np.zeros((1 + len(rows), n), np.int32),
+            "msa_species_identifiers_all_seq": np.array([b""] + [s.encode() for s in species], dtype=object)}
+
+
+def test_pair_and_merge_heteromer():
+    a = _chain("ACDEFGHIKL", ["ACDEFGHIKV", "ACDEYGHIKL", "AADEFGHIKL"], ["HUMAN", "MOUSE", "YEAST"], 1)
+    b = _chain("MNPQRSTV", ["MNPQRSTA", "MNPQKSTV"], ["MOUSE", "HUMAN"], 2)
+    chains = mp.add_assembly_features({"0_A": a, "1_B": b})
+    assert sorted(chains) == ["A_1", "B_1"]
+    table = mp.pair_sequences(mp.process_unmerged_features(list(chains.values())))
+    # row 0 pairs the queries; HUMAN and MOUSE exist in both chains, YEAST only in the first
+    assert table.shape == (3, 2) and (table[0] == 0).all()
+    ex = mp.pair_and_merge(chains)
+    n = 18
+    assert ex["aatype"].shape == (n,) and ex["msa"].shape[1] == n
+    assert list(np.unique(ex["asym_id"])) == [1, 2] and list(np.unique(ex["entity_id"])) == [1, 2] and list(np.unique(ex["sym_id"])) == [1]
+    assert ex["seq_mask"].sum() == n
+    # paired rows come first: 3 of them; the remaining rows are block-diagonal (gaps for the other chain)
+    gap = mp.MSA_GAP_IDX
+    tail = ex["msa"][3:]
+    assert all(((row[:10] == gap).all() or (row[10:] == gap).all()) for row in tail)
+    assert not any(((row[:10] == gap).all() or (row[10:] == gap).all()) for row in ex["msa"][:3])
+
+
+def test_homomer_is_not_paired_and_pipeline(tmp_path):
+    fasta = tmp_path / "c.fasta"
+    fasta.write_text(">A first\nACDEFGHIKL\n>B second\nACDEFGHIKL\n")
+    ex = DataPipelineMultimer(DataPipeline()).process_fasta(str(fasta))
+    assert ex["aatype"].shape == (20,) and list(np.unique(ex["sym_id"])) == [1, 2] and list(np.unique(ex["entity_id"])) == [1]
+    assert ex["msa"].shape[0] >= 512 and ex["msa"].shape[1] == 20
