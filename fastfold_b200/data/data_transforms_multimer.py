@@ -1,0 +1,126 @@
+"""Tensor-level feature transforms of the multimer pipeline and the transform list that applies them
+(roles of fastfold/data/data_transforms_multimer.py and input_pipeline_multimer.py).
+
+Differences from the monomer pipeline: cluster centres are drawn by Gumbel-max sampling biased by ``cluster_bias_mask``
+(the query row always wins), the BERT-style corruption draws from the MSA profile of the whole (merged) alignment,
+``target_feat`` is a plain 21-class one-hot, and MSA rows of the paired block count like any other row.
+"""
+import numpy as np
+import torch
+
+from . import data_transforms as dt
+
+MSA_KEYS = ("msa", "deletion_matrix", "msa_mask", "bert_mask", "cluster_bias_mask")
+
+
+def make_msa_profile(batch):
+    """Profile over the 22 HH-suite classes of the whole alignment (masked mean)."""
+    oh = dt.make_one_hot(batch["msa"], 22)
+    mask = batch["msa_mask"][..., None]
+    batch["msa_profile"] = (oh * mask).sum(0) / (mask.sum(0) + 1e-10)
+    return batch
+
+
+def sample_msa(batch, max_seq, max_extra_msa_seq, seed=None):
+    """Gumbel-max sampling of ``max_seq`` cluster centres; the next ``max_extra_msa_seq`` rows become the extra MSA."""
+    g = torch.Generator()
+    g.manual_seed(seed) if seed is not None else g.seed()
+    logits = (torch.clamp(batch["msa_mask"].sum(-1), 0.0, 1.0) - 1.0) * 1e6
+    if "cluster_bias_mask" in batch:
+        bias = batch["cluster_bias_mask"]
+    else:
+        bias = torch.nn.functional.pad(torch.zeros(1), (0, batch["msa"].shape[0] - 1), value=1.0)
+    logits = logits + bias * (-1e6) * 0 + (1.0 - bias) * 1e6        # rows with bias 0 (the query) always come first
+    u = torch.rand(logits.shape, generator=g).clamp_(1e-6, 1 - 1e-6)
+    gumbel = -torch.log(-torch.log(u))
+    order = torch.argsort(logits + gumbel, descending=True)
+    sel, extra = order[:max_seq], order[max_seq:max_seq + max_extra_msa_seq]
+    for k in ("msa", "deletion_matrix", "msa_mask", "bert_mask"):
+        if k in batch:
+            batch["extra_" + k] = batch[k][extra]
+            batch[k] = batch[k][sel]
+    if "cluster_bias_mask" in batch:
+        batch["cluster_bias_mask"] = batch["cluster_bias_mask"][sel]
+    return batch
+
+
+def make_masked_msa(batch, config, replace_fraction, seed=None):
+    g = torch.Generator()
+    g.manual_seed(seed) if seed is not None else g.seed()
+    random_aa = torch.tensor([0.05] * 20 + [0.0, 0.0], dtype=torch.float32)
+    probs = config.uniform_prob * random_aa + config.profile_prob * batch["msa_profile"] + config.same_prob * dt.make_one_hot(batch["msa"], 22)
+    mask_prob = 1.0 - config.profile_prob - config.same_prob - config.uniform_prob
+    probs = torch.nn.functional.pad(probs, (0, 1), value=mask_prob)
+    sh = batch["msa"].shape
+    mask_position = (torch.rand(sh, generator=g) < replace_fraction) & (batch["msa_mask"] > 0)
+    drawn = torch.multinomial(probs.reshape(-1, probs.shape[-1]) + 1e-9, 1, generator=g).reshape(sh)
+    batch["bert_mask"] = mask_position.to(torch.float32)
+    batch["true_msa"] = batch["msa"]
+    batch["msa"] = torch.where(mask_position, drawn, batch["msa"])
+    return batch
+
+
+def nearest_neighbor_clusters(batch, gap_agreement_weight=0.0):
+    """Cluster profile / deletion mean per centre from soft assignment of the extra rows (softmax over agreement)."""
+    weights = torch.tensor([1.0] * 21 + [gap_agreement_weight] + [0.0])
+    msa_oh = dt.make_one_hot(batch["msa"], 23) * batch["msa_mask"][..., None]                  # [n centres, r, 23]
+    extra_oh = dt.make_one_hot(batch["extra_msa"], 23) * batch["extra_msa_mask"][..., None]    # [m extra, r, 23]
+    agreement = torch.einsum("mrc,nrc->mn", extra_oh, weights * msa_oh)
+    valid = batch["extra_msa_mask"].sum(-1).clamp(0, 1)                                        # rows that exist at all
+    assign = torch.softmax(1e3 * agreement, dim=1) * valid[:, None]                            # [m, n], ~one-hot per extra row
+    counts = batch["msa_mask"] + torch.einsum("mn,mr->nr", assign, batch["extra_msa_mask"]) + 1e-6
+    batch["cluster_profile"] = (msa_oh + torch.einsum("mn,mrc->nrc", assign, extra_oh)) / counts[..., None]
+    del_sum = batch["deletion_matrix"] * batch["msa_mask"] + torch.einsum("mn,mr->nr", assign, batch["extra_deletion_matrix"] * batch["extra_msa_mask"])
+    batch["cluster_deletion_mean"] = del_sum / counts
+    return batch
+
+
+def create_msa_feat(batch):
+    """``msa_feat`` (49 channels) from the sampled rows and their cluster summaries."""
+    msa_1hot = dt.make_one_hot(batch["msa"], 23)
+    has_deletion = torch.clamp(batch["deletion_matrix"], 0.0, 1.0)[..., None]
+    deletion_value = (torch.atan(batch["deletion_matrix"] / 3.0) * (2.0 / np.pi))[..., None]
+    deletion_mean_value = (torch.atan(batch["cluster_deletion_mean"] / 3.0) * (2.0 / np.pi))[..., None]
+    batch["msa_feat"] = torch.cat([msa_1hot, has_deletion, deletion_value, batch["cluster_profile"], deletion_mean_value], dim=-1)
+    return batch
+
+
+def create_target_feat(batch):
+    batch["target_feat"] = dt.make_one_hot(batch["aatype"], 21)
+    return batch
+
+
+def create_extra_msa_feature(batch, num_extra_msa):
+    """Trims the extra MSA and derives ``extra_has_deletion`` / ``extra_deletion_value`` (the 25-channel feature itself is
+    assembled inside the model)."""
+    for k in ("extra_msa", "extra_deletion_matrix", "extra_msa_mask"):
+        batch[k] = batch[k][:num_extra_msa]
+    batch["extra_has_deletion"] = torch.clamp(batch["extra_deletion_matrix"], 0.0, 1.0)
+    batch["extra_deletion_value"] = torch.atan(batch["extra_deletion_matrix"] / 3.0) * (2.0 / np.pi)
+    return batch
+
+
+def process_tensors(batch, common_cfg, mode_cfg, seed=0):
+    """One recycling iteration's worth of model features from the merged multimer example (tensors, no batch dim)."""
+    batch = dict(batch)
+    for k in ("msa", "aatype", "asym_id", "entity_id", "sym_id", "residue_index"):
+        if k in batch:
+            batch[k] = batch[k].long()
+    for k in ("deletion_matrix", "msa_mask", "seq_mask"):
+        batch[k] = batch[k].float()
+    batch = make_msa_profile(batch)
+    batch = sample_msa(batch, mode_cfg.max_msa_clusters, mode_cfg.max_extra_msa, seed=seed)
+    if "masked_msa" in common_cfg:
+        batch = make_masked_msa(batch, common_cfg.masked_msa, mode_cfg.masked_msa_replace_fraction, seed=seed)
+    batch["extra_msa_mask"] = batch["extra_msa_mask"].float()
+    batch["extra_deletion_matrix"] = batch["extra_deletion_matrix"].float()
+    batch = nearest_neighbor_clusters(batch)
+    batch = create_msa_feat(batch)
+    batch = create_target_feat(batch)
+    batch = create_extra_msa_feature(batch, mode_cfg.max_extra_msa)
+    batch = dt.make_atom14_masks(batch)
+    batch["msa_row_mask"] = batch["msa_mask"].sum(-1).clamp(0, 1)
+    batch["extra_msa_row_mask"] = batch["extra_msa_mask"].sum(-1).clamp(0, 1)
+    if "template_aatype" in batch:
+        batch["template_mask"] = (batch["template_all_atom_mask"].sum((-1, -2)) > 0).float()
+    return batch

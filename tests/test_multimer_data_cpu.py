@@ -49,3 +49,24 @@ def test_homomer_is_not_paired_and_pipeline(tmp_path):
     ex = DataPipelineMultimer(DataPipeline()).process_fasta(str(fasta))
     assert ex["aatype"].shape == (20,) and list(np.unique(ex["sym_id"])) == [1, 2] and list(np.unique(ex["entity_id"])) == [1]
     assert ex["msa"].shape[0] >= 512 and ex["msa"].shape[1] == 20
+
+
+def test_multimer_tensor_pipeline():
+    import torch
+    from fastfold_b200.config import model_config
+    from fastfold_b200.data import data_transforms_multimer as dtm
+    a = _chain("ACDEFGHIKL", ["ACDEFGHIKV", "ACDEYGHIKL", "AADEFGHIKL"], ["HUMAN", "MOUSE", "YEAST"], 1)
+    b = _chain("MNPQRSTV", ["MNPQRSTA", "MNPQKSTV"], ["MOUSE", "HUMAN"], 2)
+    ex = mp.pair_and_merge(mp.add_assembly_features({"0_A": a, "1_B": b}))
+    cfg = model_config("multimer")
+    cfg.data.predict.max_msa_clusters = 3
+    cfg.data.predict.max_extra_msa = 4
+    tens = {k: torch.tensor(np.asarray(v)) for k, v in ex.items() if np.asarray(v).dtype != object}
+    out = dtm.process_tensors(tens, cfg.data.common, cfg.data.predict, seed=1)
+    assert out["msa_feat"].shape == (3, 18, 49) and out["target_feat"].shape == (18, 21)
+    assert out["extra_msa"].shape[0] <= 4 and out["extra_has_deletion"].shape == out["extra_msa"].shape
+    assert torch.isfinite(out["msa_feat"]).all()
+    # the query row is always the first cluster centre
+    assert (out["true_msa"][0] == tens["msa"][0]).all()
+    prof = out["msa_feat"][..., 25:48]
+    assert torch.allclose(prof.sum(-1)[out["msa_mask"] > 0], torch.ones_like(prof.sum(-1)[out["msa_mask"] > 0]), atol=1e-3)
