@@ -147,12 +147,51 @@ def inject_extra_msa(model):
     model.extra_msa_stack = fast
 
 
+def copy_template_pair_block(fast, ori):
+    _copy_tri_att(fast.TriangleAttentionStartingNode, ori.tri_att_start)
+    _copy_tri_att(fast.TriangleAttentionEndingNode, ori.tri_att_end)
+    _copy_tri_mul(fast.TriangleMultiplicationOutgoing, ori.tri_mul_out)
+    _copy_tri_mul(fast.TriangleMultiplicationIncoming, ori.tri_mul_in)
+    _copy_transition(fast.PairTransition, ori.pair_transition)
+
+
+def inject_template(model):
+    """Swaps the template pair stack (and the pointwise attention wrapper) of the template embedder
+    (fastfold/utils/inject_fastnn.py:356-388)."""
+    from ..models.fastnn.template import TemplatePairStack as FastTemplatePairStack, TemplatePointwiseAttention as FastPointwise
+    emb = model.template_embedder
+    ori = emb.template_pair_stack
+    cfg = model.config.template.template_pair_stack
+    fast = FastTemplatePairStack(c_t=cfg.c_t, c_hidden_tri_att=cfg.c_hidden_tri_att, c_hidden_tri_mul=cfg.c_hidden_tri_mul,
+                                 no_blocks=len(ori.blocks), no_heads=cfg.no_heads, pair_transition_n=cfg.pair_transition_n,
+                                 dropout_rate=cfg.dropout_rate, blocks_per_ckpt=ori.blocks_per_ckpt, inf=cfg.get("inf", 1e9),
+                                 tri_mul_first=bool(cfg.get("tri_mul_first", False)))
+    fast = _like(fast, ori)
+    for fb, ob in zip(fast.blocks, ori.blocks):
+        copy_template_pair_block(fb, ob)
+    _copy_layernorm(fast.layer_norm, ori.layer_norm)
+    fast.train(ori.training)
+    emb.template_pair_stack = fast
+    if hasattr(emb, "template_pointwise_att"):
+        pw = emb.template_pointwise_att
+        fpw = FastPointwise(c_t=pw.c_t, c_z=pw.c_z, c_hidden=pw.c_hidden, no_heads=pw.no_heads, inf=pw.inf)
+        fpw = _like(fpw, pw)
+        fpw.load_state_dict(pw.state_dict())
+        fpw.train(pw.training)
+        emb.template_pointwise_att = fpw
+
+
 def inject_fastnn(model):
-    """Returns ``model`` with ``evoformer`` and ``extra_msa_stack`` replaced by their fast twins (weights copied)."""
+    """Returns ``model`` with ``evoformer``, ``extra_msa_stack`` and the template pair stack replaced by their fast twins
+    (weights copied)."""
     with torch.no_grad():
         inject_evoformer(model)
         if model.config.extra_msa.enabled:
             inject_extra_msa(model)
+        if model.config.template.enabled:
+            inject_template(model)
+        from ..models.fastnn.embedders import inject_embedder
+        inject_embedder(model)
     return model
 
 
@@ -263,4 +302,17 @@ def extract_fastnn(model):
             sd.update(_core_entries(p + "core.", b.communication, b.pair_stack, b.msa_stack.MSATransition))
     else:
         sd.update({k: v for k, v in model.state_dict().items() if k.startswith("extra_msa_stack.")})
+    tps = getattr(getattr(model, "template_embedder", None), "template_pair_stack", None)
+    from ..models.fastnn.template import TemplatePairStack as FastTemplatePairStack
+    if isinstance(tps, FastTemplatePairStack):
+        pre = "template_embedder.template_pair_stack."
+        sd = {k: v for k, v in sd.items() if not k.startswith(pre)}
+        for i, b in enumerate(tps.blocks):
+            p = pre + "blocks.%d." % i
+            sd.update(_tri_att_entries(p + "tri_att_start.", b.TriangleAttentionStartingNode))
+            sd.update(_tri_att_entries(p + "tri_att_end.", b.TriangleAttentionEndingNode))
+            sd.update(_tri_mul_entries(p + "tri_mul_out.", b.TriangleMultiplicationOutgoing))
+            sd.update(_tri_mul_entries(p + "tri_mul_in.", b.TriangleMultiplicationIncoming))
+            sd.update(_transition_entries(p + "pair_transition.", b.PairTransition))
+        sd.update(_ln_entries(pre + "layer_norm.", tps.layer_norm))
     return sd

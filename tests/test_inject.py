@@ -59,3 +59,28 @@ def test_extract_round_trip():
     assert set(sd.keys()) == set(want.keys())
     for k, v in want.items():
         assert torch.equal(sd[k], v), k
+
+
+def test_template_stack_injection_matches_reference_layout():
+    """model_1 (templates on): the injected fast template pair stack reproduces the OpenFold-layout one."""
+    ref, cfg = _small_model(templates=True)
+    batch = random_features(13, 7, 9, n_templ=2, n_recycle=0, seed=5)
+    with torch.no_grad():
+        want = ref(copy.deepcopy(batch))
+    fast = inject_fastnn(copy.deepcopy(ref))
+    from fastfold_b200.models.fastnn.template import TemplatePairStack
+    assert isinstance(fast.template_embedder.template_pair_stack, TemplatePairStack)
+    with torch.no_grad():
+        got = fast(copy.deepcopy(batch))
+    assert (got["pair"] - want["pair"]).abs().mean() < 2e-3
+    assert (got["final_atom_positions"] - want["final_atom_positions"]).abs().max() < 5e-4
+
+
+def test_extract_round_trip_with_templates():
+    ref, cfg = _small_model(templates=True)
+    fast = inject_fastnn(copy.deepcopy(ref))
+    sd = extract_fastnn(fast)
+    want = ref.state_dict()
+    assert set(sd.keys()) == set(want.keys())
+    for k, v in want.items():
+        assert torch.equal(sd[k], v), k
