@@ -23,6 +23,14 @@
 
 namespace ffb {
 
+// Optional phase stamps of block 0 of the copy kernels (profiling builds only: -DFFB_COMM_TRACE).
+#ifdef FFB_COMM_TRACE
+__device__ unsigned long long g_comm_trace[16];
+#define COMM_TRACE(slot_) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_comm_trace[slot_] = globaltimer_ns(); } while (0)
+#else
+#define COMM_TRACE(slot_) do {} while (0)
+#endif
+
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -67,11 +75,16 @@ __device__ __forceinline__ bool wait_peers(const SymmCtx& c, bool ready_not_done
 }
 
 // The block that finishes last raises this rank's flag in every peer's pad (and, for `done`, advances the epoch).
+// Ordering: the block's accesses are collected by the CTA barrier, thread 0 orders them at GPU scope before its
+// counter increment, and only the last block pays for the system-scope fence in front of the remote flag stores
+// (a system-scope fence in every thread cost 3-6 us per kernel).
 __device__ __forceinline__ void last_block_signal(const SymmCtx& c, int slot, uint32_t epoch, bool ready_not_done) {
   __shared__ int s_last;
-  __threadfence_system();
+  COMM_TRACE(8);
   __syncthreads();
+  COMM_TRACE(9);
   if (threadIdx.x == 0) {
+    __threadfence();
     uint32_t* blk = c.flags[c.rank] + w_blocks(slot);
     const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
     s_last = (atomicAdd(blk, 1u) == total - 1) ? 1 : 0;
@@ -85,6 +98,9 @@ __device__ __forceinline__ void last_block_signal(const SymmCtx& c, int slot, ui
   }
 }
 
+constexpr int COPY_U = 8;   // independent 16-byte transfers in flight per thread in the copy kernels
+constexpr int A2A_U = 4;    // rows in flight per warp in the all-to-all + LayerNorm kernel
+
 __device__ __forceinline__ uint32_t next_epoch(const SymmCtx& c, int slot) {
   return reinterpret_cast<volatile uint32_t*>(c.flags[c.rank])[w_epoch(slot)] + 1u;
 }
@@ -94,17 +110,31 @@ __device__ __forceinline__ uint32_t next_epoch(const SymmCtx& c, int slot) {
 // ---------------------------------------------------------------------------
 __global__ void symm_publish_k(SymmCtx c, int slot, long long heap_off, const uint4* __restrict__ src, long long n16) {
   __shared__ uint32_t s_epoch;
+  COMM_TRACE(0);
   if (threadIdx.x == 0) {
     s_epoch = next_epoch(c, slot);
     // the previous use of this slot must have been read by every peer before it is overwritten
     wait_peers(c, false, slot, s_epoch - 1u);
   }
   __syncthreads();
+  COMM_TRACE(1);
   uint4* dst = reinterpret_cast<uint4*>(c.heap[c.rank] + heap_off);
   if (src != nullptr) {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+    // COPY_U independent 16-byte loads in flight per thread before the first store
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride * COPY_U) {
+      uint4 v[COPY_U];
+#pragma unroll
+      for (int u = 0; u < COPY_U; ++u)
+        if (i + u * stride < n16) v[u] = src[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < COPY_U; ++u)
+        if (i + u * stride < n16) dst[i + u * stride] = v[u];
+    }
   }
+  COMM_TRACE(2);
   last_block_signal(c, slot, s_epoch, true);
+  COMM_TRACE(3);
 }
 
 // ---------------------------------------------------------------------------
@@ -120,12 +150,21 @@ __global__ void symm_pull_k(SymmCtx c, int slot, long long heap_off, uint4* __re
   }
   __syncthreads();
   if (s_ok) {
-    const long long total = n16 * c.world;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-      const int r = (int)(i / n16);
-      const long long k = i - (long long)r * n16;
-      const uint4* src = reinterpret_cast<const uint4*>(c.heap[r] + heap_off) + (all_to_all ? (long long)c.rank * n16 : 0) + k;
-      dst[i] = *src;
+    // blockIdx.y = source rank (starting with the farthest data in flight first does not matter: every rank is one
+    // NVSwitch hop away); COPY_U independent peer loads per thread are issued before the first store
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (int r = blockIdx.y; r < c.world; r += gridDim.y) {
+      const uint4* src = reinterpret_cast<const uint4*>(c.heap[r] + heap_off) + (all_to_all ? (long long)c.rank * n16 : 0);
+      uint4* d = dst + (long long)r * n16;
+      for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride * COPY_U) {
+        uint4 v[COPY_U];
+#pragma unroll
+        for (int u = 0; u < COPY_U; ++u)
+          if (i + u * stride < n16) v[u] = src[i + u * stride];
+#pragma unroll
+        for (int u = 0; u < COPY_U; ++u)
+          if (i + u * stride < n16) d[i + u * stride] = v[u];
+      }
     }
   }
   last_block_signal(c, slot, s_epoch, false);
@@ -158,29 +197,46 @@ __global__ void __launch_bounds__(128) symm_a2a_ln_k(SymmCtx c, int slot, long l
   const int lane = threadIdx.x & 31;
   constexpr int NV = VPL / 8;
   if (s_ok) {
-    for (long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5); row < rows; row += (long long)gridDim.x * 4) {
-      const int a = (int)(row / Bd), b = (int)(row - (long long)a * Bd);
-      int r;
-      long long src_row;
-      if (mode == 0) {
-        const int ap = A / P;
-        r = a / ap;
-        src_row = (long long)(a - r * ap) * B + (long long)c.rank * Bd + b;
-      } else {
-        const int bp = B / P;
-        r = b / bp;
-        src_row = (long long)(c.rank * Ad + a) * bp + (b - r * bp);
-      }
-      const bf16* src = reinterpret_cast<const bf16*>(c.heap[r] + heap_off) + src_row * C;
-      float v[VPL];
-      float s = 0.f;
+    // A2A_U rows per warp and step: all their peer loads are issued before the first one is consumed
+    const long long wstride = (long long)gridDim.x * 4;
+    for (long long row0 = (long long)blockIdx.x * 4 + (threadIdx.x >> 5); row0 < rows; row0 += wstride * A2A_U) {
+      uint4 raw[A2A_U][NV];
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int c0 = (i * 32 + lane) * 8;
-        if (c0 < C) {
-          const uint4 u = *reinterpret_cast<const uint4*>(src + c0);
-          if (y_raw) *reinterpret_cast<uint4*>(y_raw + row * C + c0) = u;
-          const bf162* h = reinterpret_cast<const bf162*>(&u);
+      for (int u = 0; u < A2A_U; ++u) {
+        const long long row = row0 + u * wstride;
+        if (row < rows) {
+          const int a = (int)(row / Bd), b = (int)(row - (long long)a * Bd);
+          int r;
+          long long src_row;
+          if (mode == 0) {
+            const int ap = A / P;
+            r = a / ap;
+            src_row = (long long)(a - r * ap) * B + (long long)c.rank * Bd + b;
+          } else {
+            const int bp = B / P;
+            r = b / bp;
+            src_row = (long long)(c.rank * Ad + a) * bp + (b - r * bp);
+          }
+          const bf16* src = reinterpret_cast<const bf16*>(c.heap[r] + heap_off) + src_row * C;
+#pragma unroll
+          for (int i = 0; i < NV; ++i) {
+            const int c0 = (i * 32 + lane) * 8;
+            raw[u][i] = c0 < C ? *reinterpret_cast<const uint4*>(src + c0) : make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < A2A_U; ++u) {
+        const long long row = row0 + u * wstride;
+        if (row >= rows) break;                                   // warp-uniform
+        const int a = (int)(row / Bd), b = (int)(row - (long long)a * Bd);
+        float v[VPL];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c0 = (i * 32 + lane) * 8;
+          if (c0 < C && y_raw) *reinterpret_cast<uint4*>(y_raw + row * C + c0) = raw[u][i];
+          const bf162* h = reinterpret_cast<const bf162*>(&raw[u][i]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float2 f = __bfloat1622float2(h[j]);
@@ -188,41 +244,38 @@ __global__ void __launch_bounds__(128) symm_a2a_ln_k(SymmCtx c, int slot, long l
             v[i * 8 + 2 * j + 1] = f.y;
             s += f.x + f.y;
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[i * 8 + j] = 0.f;
         }
-      }
-      if (y_norm) {
-        const float mean = warp_sum(s) / C;
-        float q = 0.f;
+        if (y_norm) {
+          const float mean = warp_sum(s) / C;
+          float q = 0.f;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-          const int c0 = (i * 32 + lane) * 8;
-          if (c0 < C) {
+          for (int i = 0; i < NV; ++i) {
+            const int c0 = (i * 32 + lane) * 8;
+            if (c0 < C) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float d = v[i * 8 + j] - mean;
-              q += d * d;
+              for (int j = 0; j < 8; ++j) {
+                const float d = v[i * 8 + j] - mean;
+                q += d * d;
+              }
             }
           }
-        }
-        const float rstd = rsqrtf(warp_sum(q) / C + eps);
-        const long long orow = transpose_norm ? ((long long)b * Ad + a) : row;
+          const float rstd = rsqrtf(warp_sum(q) / C + eps);
+          const long long orow = transpose_norm ? ((long long)b * Ad + a) : row;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-          const int c0 = (i * 32 + lane) * 8;
-          if (c0 < C) {
-            const uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0), ub = *reinterpret_cast<const uint4*>(beta + c0);
-            const bf162 *hg = reinterpret_cast<const bf162*>(&ug), *hb = reinterpret_cast<const bf162*>(&ub);
-            uint4 uo;
-            bf162* ho = reinterpret_cast<bf162*>(&uo);
+          for (int i = 0; i < NV; ++i) {
+            const int c0 = (i * 32 + lane) * 8;
+            if (c0 < C) {
+              const uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0), ub = *reinterpret_cast<const uint4*>(beta + c0);
+              const bf162 *hg = reinterpret_cast<const bf162*>(&ug), *hb = reinterpret_cast<const bf162*>(&ub);
+              uint4 uo;
+              bf162* ho = reinterpret_cast<bf162*>(&uo);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 g2 = __bfloat1622float2(hg[j]), b2 = __bfloat1622float2(hb[j]);
-              ho[j] = __floats2bfloat162_rn((v[i * 8 + 2 * j] - mean) * rstd * g2.x + b2.x, (v[i * 8 + 2 * j + 1] - mean) * rstd * g2.y + b2.y);
+              for (int j = 0; j < 4; ++j) {
+                const float2 g2 = __bfloat1622float2(hg[j]), b2 = __bfloat1622float2(hb[j]);
+                ho[j] = __floats2bfloat162_rn((v[i * 8 + 2 * j] - mean) * rstd * g2.x + b2.x, (v[i * 8 + 2 * j + 1] - mean) * rstd * g2.y + b2.y);
+              }
+              *reinterpret_cast<uint4*>(y_norm + orow * C + c0) = uo;
             }
-            *reinterpret_cast<uint4*>(y_norm + orow * C + c0) = uo;
           }
         }
       }
@@ -276,11 +329,12 @@ __global__ void __launch_bounds__(256) symm_allreduce_bf16_k(SymmCtx c, int slot
       for (int r = 0; r < P; ++r) *(reinterpret_cast<uint4*>(c.heap[r] + heap_off) + i) = o;
     }
   }
-  // exit: every rank's range has been written everywhere before anyone reads the result
+  // exit: every rank's range has been written everywhere before anyone reads the result (the block's remote stores
+  // are collected by the barrier and ordered by ONE system-scope fence per block)
   __shared__ int s_last;
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     uint32_t* blk = c.flags[c.rank] + w_blocks(slot);
     s_last = (atomicAdd(blk, 1u) == gridDim.x - 1) ? 1 : 0;
     if (s_last) {
@@ -345,14 +399,17 @@ static int grid_for(long long n, int threads, int cap) {
 int ffb_symm_publish(const SymmCtx* c, int slot, long long heap_off, const void* src, long long bytes, void* stream) {
   if (bytes % 16 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
   const long long n16 = bytes / 16;
-  symm_publish_k<<<grid_for(n16, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, (const uint4*)src, n16);
+  symm_publish_k<<<grid_for((n16 + COPY_U - 1) / COPY_U, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, (const uint4*)src, n16);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int ffb_symm_pull(const SymmCtx* c, int slot, long long heap_off, void* dst, long long bytes_per_rank, int all_to_all, void* stream) {
   if (bytes_per_rank % 16 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
   const long long n16 = bytes_per_rank / 16;
-  symm_pull_k<<<grid_for(n16 * c->world, 256, 592), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, (uint4*)dst, n16, all_to_all);
+  {
+    const int gx = grid_for((n16 + COPY_U - 1) / COPY_U, 256, 592 / c->world > 0 ? 592 / c->world : 1);
+    symm_pull_k<<<dim3(gx, c->world), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, (uint4*)dst, n16, all_to_all);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -386,6 +443,12 @@ int ffb_symm_consume_fence(const SymmCtx* c, int slot, int pre, void* stream) {
   symm_consume_fence_k<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, pre);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+
+#ifdef FFB_COMM_TRACE
+int ffb_comm_trace_read(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_comm_trace, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int ffb_symm_wait_never(const SymmCtx* c, int slot, void* stream) {
   symm_wait_never_k<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot);
