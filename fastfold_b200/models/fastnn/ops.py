@@ -219,6 +219,7 @@ class _OpmCore(torch.autograd.Function):
     def forward(ctx, l2, r2, w, bias, inv_norm, z2):
         out, o4 = _opm_forward(l2, r2, w, bias, inv_norm, z2)
         ctx.save_for_backward(l2, r2, w, inv_norm, o4)
+        ctx.bias_param = bias
         return out
 
     @staticmethod
@@ -228,9 +229,10 @@ class _OpmCore(torch.autograd.Function):
         dout = dout.contiguous()
         dys = dout * inv_norm.to(dout.dtype).unsqueeze(-1)                 # gradient of (o4 W^T + bias)
         dw = db = dl = dr = None
-        if ctx.needs_input_grad[2]:
+        from ...ops.gemm import sink_bias_grad, sink_weight_grad
+        if ctx.needs_input_grad[2] and not sink_weight_grad(w, dys, o4):
             dw = K.weight_grad(dys, o4).to(w.dtype)
-        if ctx.needs_input_grad[3]:
+        if ctx.needs_input_grad[3] and not (ctx.bias_param is not None and sink_bias_grad(ctx.bias_param, dys)):
             db = K.colsum(dys).to(w.dtype)
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
             # d o4 = dys W, stored as the matrix [(i d), (j e)] that the two operand gradients contract with

@@ -59,6 +59,7 @@ class _BiasSigmoidMul(torch.autograd.Function):
         _lib.check(lib.ffb_bias_sigmoid_mul_fwd(_lib.ptr(gc), _lib.ptr(bc), _lib.ptr(oc), _lib.ptr(y), rows, C, _lib.stream_ptr()),
                    "bias_sigmoid_mul_fwd")
         ctx.save_for_backward(gc, bc, oc)
+        ctx.bias_param = bias
         return y
 
     @staticmethod
@@ -71,7 +72,7 @@ class _BiasSigmoidMul(torch.autograd.Function):
         dyc = dy.contiguous()
         _lib.check(lib.ffb_bias_sigmoid_mul_bwd(_lib.ptr(dyc), _lib.ptr(gc), _lib.ptr(bc), _lib.ptr(oc), _lib.ptr(dg), _lib.ptr(do),
                                                 rows, C, _lib.stream_ptr()), "bias_sigmoid_mul_bwd")
-        db = colsum(dg.reshape(rows, C)).to(bc.dtype) if ctx.needs_input_grad[1] else None
+        db = _bias_grad(ctx.bias_param, dg.reshape(rows, C), bc.dtype) if ctx.needs_input_grad[1] else None
         return dg, db, do
 
 
@@ -94,6 +95,7 @@ class _BiasDropoutAdd(torch.autograd.Function):
         ctx.save_for_backward(m2)
         ctx.dm = (div, mod)
         ctx.has_bias = bias is not None
+        ctx.bias_param = bias
         return y
 
     @staticmethod
@@ -108,7 +110,7 @@ class _BiasDropoutAdd(torch.autograd.Function):
                        "mask_mul")
         else:
             dx = dyc
-        db = colsum(dx.reshape(rows, C)).to(dyc.dtype) if (ctx.has_bias and ctx.needs_input_grad[1]) else None
+        db = _bias_grad(ctx.bias_param, dx.reshape(rows, C), dyc.dtype) if (ctx.has_bias and ctx.needs_input_grad[1]) else None
         return dx, db, None, None, None, dyc
 
 
@@ -142,6 +144,7 @@ class _BiasEleDropoutRes(torch.autograd.Function):
                                                     rows, C, div, mod, _lib.stream_ptr()), "bias_ele_dropout_res_fwd")
         ctx.save_for_backward(abc, bc, gc, m2)
         ctx.dm = (div, mod)
+        ctx.bias_param = b
         return y
 
     @staticmethod
@@ -155,7 +158,7 @@ class _BiasEleDropoutRes(torch.autograd.Function):
         _lib.check(lib.ffb_bias_ele_dropout_res_bwd(_lib.ptr(dyc), _lib.ptr(abc), _lib.ptr(bc), _lib.ptr(gc), _lib.ptr(m2),
                                                     _lib.ptr(dab), _lib.ptr(dg), rows, C, ctx.dm[0], ctx.dm[1], _lib.stream_ptr()),
                    "bias_ele_dropout_res_bwd")
-        db = colsum(dab.reshape(rows, C)).to(bc.dtype) if ctx.needs_input_grad[1] else None
+        db = _bias_grad(ctx.bias_param, dab.reshape(rows, C), bc.dtype) if ctx.needs_input_grad[1] else None
         return dab, db, dg, None, None, None, dyc
 
 
@@ -271,12 +274,28 @@ def act_backward(dy2, y2, act):
     return dy2 * y2 * (1 - y2)
 
 
-def colsum(x2):
-    """fp32 column sums of a 2-D tensor."""
+def colsum(x2, out=None):
+    """fp32 column sums of a 2-D tensor; with ``out`` (fp32 ``[C]``) the sums are ADDED into it."""
     if x2.is_cuda and x2.dtype == torch.bfloat16 and x2.shape[-1] % 2 == 0:
         lib = _lib.get()
         xc = x2.contiguous()
-        out = torch.zeros(xc.shape[-1], device=xc.device, dtype=torch.float32)
+        if out is None:
+            out = torch.zeros(xc.shape[-1], device=xc.device, dtype=torch.float32)
         _lib.check(lib.ffb_colsum(_lib.ptr(xc), _lib.ptr(out), xc.shape[0], xc.shape[1], _lib.stream_ptr()), "colsum")
         return out
-    return x2.float().sum(dim=0)
+    r = x2.float().sum(dim=0)
+    if out is not None:
+        out.add_(r)
+        return out
+    return r
+
+
+def _bias_grad(bias_param, d2, dtype):
+    """Bias gradient = column sums of ``d2``: added straight into the parameter's fp32 gradient sink when the trainer
+    provides one (then no gradient tensor is returned to autograd)."""
+    from .gemm import grad_sink
+    sink = grad_sink(bias_param) if bias_param is not None else None
+    if sink is not None and d2.is_cuda and d2.dtype == torch.bfloat16:
+        colsum(d2, out=sink.reshape(-1))
+        return None
+    return colsum(d2).to(dtype)

@@ -221,6 +221,7 @@ class _Linear(torch.autograd.Function):
         ctx.act = act
         ctx.has_bias = bias is not None
         ctx.save_for_backward(x2, w, y if act else None)
+        ctx.bias_ref = bias if (bias is not None and grad_sink(bias) is not None) else None
         ctx.xshape = x.shape
         return y.reshape(*x.shape[:-1], w.shape[0])
 
@@ -236,10 +237,11 @@ class _Linear(torch.autograd.Function):
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).reshape(ctx.xshape)
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[1] and not sink_weight_grad(w, dy2, x2):
             dw = weight_grad(dy2, x2, w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = fused_ops.colsum(dy2).to(w.dtype)
+            if not (ctx.bias_ref is not None and sink_bias_grad(ctx.bias_ref, dy2)):
+                db = fused_ops.colsum(dy2).to(w.dtype)
         return dx, dw, db, None
 
 
@@ -262,10 +264,11 @@ class _LinearT(torch.autograd.Function):
             dx = gemm(dy_t, w, a_mn=True, b_mn=True)              # [tokens, c_in]: contraction over c_out, both operands stored [c_out, .]
         if ctx.needs_input_grad[1]:
             n_out, n_in = w.shape
-            acc = torch.zeros(n_out, n_in, device=w.device, dtype=torch.float32)
+            sink = grad_sink(w)
+            acc = sink if sink is not None else torch.zeros(n_out, n_in, device=w.device, dtype=torch.float32)
             tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
             gemm(dy_t, x2, b_mn=True, out=acc, accumulate=True, splits=_wgrad_splits(x2.shape[0], tiles))   # contraction over tokens
-            dw = acc.to(w.dtype)
+            dw = None if sink is not None else acc.to(w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = torch.sum(dy_t, dim=1, dtype=torch.float32).to(w.dtype)      # converts inside the reduction, no fp32 copy
         return dx, dw, db
@@ -280,6 +283,36 @@ def linear_t(x2, w, bias=None):
     if torch.is_grad_enabled() and (x2.requires_grad or w.requires_grad or (bias is not None and bias.requires_grad)):
         return _LinearT.apply(x2, w, bias)
     return gemm(x2, w, bias=bias, trans_out=True)
+
+
+GRAD_SINK_ATTR = "_ffb_grad32"     # set by the trainer on a parameter: fp32 view of its slice of the flat gradient buffer
+
+
+def grad_sink(param):
+    """The fp32 accumulation buffer of a parameter when a trainer has provided one (gradient kernels then add into it
+    directly and the autograd function returns no gradient for the parameter), else None."""
+    return getattr(param, GRAD_SINK_ATTR, None)
+
+
+def sink_weight_grad(w, dy2, x2):
+    """Adds dy^T @ x into the parameter's fp32 sink with the split-K GEMM; True when it did."""
+    sink = grad_sink(w)
+    n_out, n_in = dy2.shape[1], x2.shape[1]
+    if sink is None or not dy2.is_cuda or n_out < 64 or n_in < 64 or n_out % 8 or n_in % 8:
+        return False
+    tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
+    gemm(dy2, x2, a_mn=True, b_mn=True, out=sink, accumulate=True, splits=_wgrad_splits(dy2.shape[0], tiles))
+    return True
+
+
+def sink_bias_grad(bias, dy2):
+    """Adds the column sums of ``dy2`` into the bias parameter's fp32 sink; True when it did."""
+    sink = grad_sink(bias)
+    if sink is None or not (dy2.is_cuda and dy2.dtype == torch.bfloat16 and dy2.shape[-1] % 2 == 0):
+        return False
+    from . import fused_ops
+    fused_ops.colsum(dy2, out=sink.reshape(-1))
+    return True
 
 
 def weight_grad(dy2, x2, dtype=torch.bfloat16):

@@ -27,9 +27,10 @@ from ..parallel import core
 
 class FlatAdamTrainer:
     def __init__(self, model, loss_fn, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, use_graph=True,
-                 replicated_param_filter=None, grad_reducer=None):
+                 replicated_param_filter=None, grad_reducer=None, grad_sink=True):
         """``loss_fn(model, *inputs) -> scalar loss``.  ``replicated_param_filter(name) -> bool`` marks parameters
-        whose computation is replicated (not sharded) over the DAP group."""
+        whose computation is replicated (not sharded) over the DAP group.  ``grad_sink=False`` routes every parameter
+        gradient through autograd's own accumulation (for comparisons)."""
         self.model = model
         self.loss_fn = loss_fn
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
@@ -61,6 +62,9 @@ class FlatAdamTrainer:
             self.flat_g = self.flat_g_padded[:total]
         else:
             self.flat_g = torch.zeros(total, device=dev, dtype=self.dtype)
+        # fp32 gradient sink: weight- and bias-gradient kernels of the fused ops add straight into it (split-K atomics),
+        # which removes a zero-fill, a conversion and an accumulate kernel per parameter; folded into flat_g once per step
+        self.flat_g32 = torch.zeros(total, device=dev, dtype=torch.float32) if (grad_sink and dev.type == "cuda" and self.dtype == torch.bfloat16) else None
         self.master = torch.empty(total, device=dev, dtype=torch.float32)
         self.exp_avg = torch.zeros(total, device=dev, dtype=torch.float32)
         self.exp_avg_sq = torch.zeros(total, device=dev, dtype=torch.float32)
@@ -78,6 +82,9 @@ class FlatAdamTrainer:
             self.flat_w[off:off + k].copy_(p.data.reshape(-1))
             p.data = self.flat_w[off:off + k].view(p.shape)
             p.grad = self.flat_g[off:off + k].view(p.shape)
+            if self.flat_g32 is not None:
+                from ..ops.gemm import GRAD_SINK_ATTR
+                setattr(p, GRAD_SINK_ATTR, self.flat_g32[off:off + k].view(p.shape))
             rep = bool(replicated_param_filter(n)) if replicated_param_filter else False
             scales.append((off, k, rep))
             off += k
@@ -127,8 +134,12 @@ class FlatAdamTrainer:
 
     def _body(self, inputs):
         self.flat_g.zero_()
+        if self.flat_g32 is not None:
+            self.flat_g32.zero_()
         loss = self.loss_fn(self.model, *inputs)
         loss.backward()
+        if self.flat_g32 is not None:
+            self.flat_g.add_(self.flat_g32)
         self._reduce_grads()
         self._adam()
         return loss.detach()
