@@ -256,6 +256,25 @@ __global__ void __launch_bounds__(1024) ln_bwd_reduce_kernel(const float* __rest
   }
 }
 
+// Same reduction, ADDED into fp32 vectors (a trainer's flat gradient buffer): one writer per column, no atomics.
+__global__ void __launch_bounds__(1024) ln_bwd_reduce_acc_kernel(const float* __restrict__ part, int nblocks, int C,
+                                                                 float* __restrict__ dgamma, float* __restrict__ dbeta) {
+  __shared__ float acc[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  float s = 0.f;
+  if (c < 2 * C)
+    for (int b = ty; b < nblocks; b += 32) s += part[(long long)b * 2 * C + c];
+  acc[ty][tx] = s;
+  __syncthreads();
+  const float v = warp_sum(acc[tx][ty]);
+  const int co = blockIdx.x * 32 + ty;
+  if (tx == 0 && co < 2 * C) {
+    if (co < C) dgamma[co] += v;
+    else dbeta[co - C] += v;
+  }
+}
+
 // LayerNorm over the leading dimension of x[C][rows] (row index contiguous),
 // output y[rows][C].  One thread per row for the statistics (coalesced across
 // the warp), staged through shared memory so that the [rows, C] writes are
@@ -504,9 +523,13 @@ static int ln_fwd_dispatch(const T* x, const T* g, const T* b, T* y, float* mean
 
 template <typename T>
 static int ln_bwd_dispatch(const T* dy, const T* x, const T* g, const float* mean, const float* rstd, T* dx, float* part,
-                           int nblocks, T* dgamma, T* dbeta, long long rows, int C, cudaStream_t st) {
+                           int nblocks, T* dgamma, T* dbeta, long long rows, int C, cudaStream_t st, float* dgamma_acc = nullptr,
+                           float* dbeta_acc = nullptr) {
   constexpr int VEC = 16 / sizeof(T);
-  if (cudaMemsetAsync(part, 0, sizeof(float) * 2 * C * nblocks, st) != cudaSuccess) return -1;
+  const bool aligned0 = (C % VEC == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
+                                            reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(g)) % 16 == 0);
+  const bool multi_row = IsBf16<T>::value && aligned0 && (C == 64 || C == 128 || C == 256);     // writes every partial itself
+  if (!multi_row && cudaMemsetAsync(part, 0, sizeof(float) * 2 * C * nblocks, st) != cudaSuccess) return -1;
   const bool aligned = (C % VEC == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
                                            reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(g)) % 16 == 0);
   if (IsBf16<T>::value && aligned && (C == 64 || C == 128 || C == 256)) {
@@ -519,7 +542,8 @@ static int ln_bwd_dispatch(const T* dy, const T* x, const T* g, const float* mea
   else if (aligned && C <= 64 * VEC) ln_bwd_kernel<T, 2 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
   else if (aligned && C <= 128 * VEC) ln_bwd_kernel<T, 4 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
   else ln_bwd_generic_kernel<T><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
-  ln_bwd_reduce_kernel<T><<<(2 * C + 31) / 32, 1024, 0, st>>>(part, nblocks, C, dgamma, dbeta);
+  if (dgamma_acc) ln_bwd_reduce_acc_kernel<<<(2 * C + 31) / 32, 1024, 0, st>>>(part, nblocks, C, dgamma_acc, dbeta_acc);
+  else ln_bwd_reduce_kernel<T><<<(2 * C + 31) / 32, 1024, 0, st>>>(part, nblocks, C, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -553,6 +577,15 @@ int ffb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
     case 2: return ln_bwd_dispatch<bf16>((const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part, nblocks, (bf16*)dgamma, (bf16*)dbeta, rows, C, st);
   }
   return -2;
+}
+
+// bf16 backward whose dgamma / dbeta are ADDED into fp32 vectors (a trainer's flat gradient buffer).
+int ffb_layernorm_bwd_acc(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                          float* part, int nblocks, float* dgamma_acc, float* dbeta_acc, long long rows, int C, void* stream) {
+  if (rows <= 0) return 0;
+  if (!dgamma_acc || !dbeta_acc) return -2;
+  return ln_bwd_dispatch<bf16>((const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part, nblocks, nullptr, nullptr, rows,
+                               C, reinterpret_cast<cudaStream_t>(stream), dgamma_acc, dbeta_acc);
 }
 
 // x: [C][rows] bf16 -> y: [rows][C] bf16, normalised over C (C <= 256).

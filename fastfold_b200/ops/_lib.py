@@ -56,6 +56,7 @@ def _declare(lib):
         "ffb_attention_bwd_strided": [P, P, P, L, L, L, L, P, P, L, P, P, L, L, P, P, P, P, L, L, L, L, P, I, I, I, I, I, F, P],
         "ffb_layernorm_fwd": [P, P, P, P, P, P, L, I, F, I, P],
         "ffb_layernorm_bwd": [P, P, P, P, P, P, P, I, P, P, L, I, I, P],
+        "ffb_layernorm_bwd_acc": [P, P, P, P, P, P, P, I, P, P, L, I, P],
         "ffb_layernorm_fwd_transposed": [P, P, P, P, P, P, L, I, F, P],
         "ffb_layernorm_bwd_transposed": [P, P, P, P, P, P, P, P, P, L, I, P],
         "ffb_glu_mask_t_fwd": [P, P, P, I, L, P],

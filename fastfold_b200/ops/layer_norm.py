@@ -39,6 +39,7 @@ class _LayerNormFn(torch.autograd.Function):
         _lib.check(lib.ffb_layernorm_fwd(_lib.ptr(xc), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), _lib.ptr(mean), _lib.ptr(rstd),
                                          rows, C, float(eps), _lib.dtype_code(x.dtype), _lib.stream_ptr()), "layernorm_fwd")
         ctx.save_for_backward(xc, w, mean, rstd)
+        ctx.params = (weight, bias)
         del need_stats
         return y
 
@@ -52,6 +53,14 @@ class _LayerNormFn(torch.autograd.Function):
         dx = torch.empty_like(xc)
         nblocks = int(min(1184, max(1, (rows + 3) // 4)))   # 8 blocks per SM: enough warps in flight to hide the per-row reductions
         part = torch.empty(nblocks * 2 * C, device=xc.device, dtype=torch.float32)
+        from .gemm import grad_sink
+        sg, sb = grad_sink(ctx.params[0]), grad_sink(ctx.params[1])
+        if sg is not None and sb is not None and xc.dtype == torch.bfloat16 and _lib.has("ffb_layernorm_bwd_acc"):
+            # gamma / beta gradients go straight into the trainer's fp32 buffer
+            _lib.check(lib.ffb_layernorm_bwd_acc(_lib.ptr(dyc), _lib.ptr(xc), _lib.ptr(w), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(dx),
+                                                 _lib.ptr(part), nblocks, _lib.ptr(sg), _lib.ptr(sb), rows, C, _lib.stream_ptr()),
+                       "layernorm_bwd_acc")
+            return dx, None, None, None
         dg = torch.empty_like(w)
         db = torch.empty_like(w)
         _lib.check(lib.ffb_layernorm_bwd(_lib.ptr(dyc), _lib.ptr(xc), _lib.ptr(w), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(dx),
