@@ -179,6 +179,60 @@ __global__ void colsum_k(const bf16* x, float* out, long long rows, int C, long 
   atomicAdd(out + c + 1, s1);
 }
 
+// Same sums for C % 8 == 0, C <= 2048 with 16-byte loads: a block of 256 threads is (C/8 column groups) x (row lanes);
+// every thread keeps 8 running sums over its rows (4 independent loads in flight), the row lanes are folded through
+// shared memory and one thread per column adds the block's result to `out`.
+__global__ void __launch_bounds__(256) colsum_v8_k(const bf16* __restrict__ x, float* __restrict__ out, long long rows, int C,
+                                                   long long rows_per_block) {
+  extern __shared__ float red[];                 // [row lanes][C]
+  const int groups = C >> 3;                     // column groups of 8
+  const int lanes = 256 / groups;                // row lanes per block (groups <= 256)
+  const int gidx = threadIdx.x % groups, lane = threadIdx.x / groups;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (lane < lanes) {
+    const long long r0 = (long long)blockIdx.x * rows_per_block;
+    long long r1 = r0 + rows_per_block;
+    if (r1 > rows) r1 = rows;
+    const bf16* p = x + gidx * 8;
+    long long r = r0 + lane;
+    for (; r + 3LL * lanes < r1; r += 4LL * lanes) {
+      uint4 u[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) u[k] = *reinterpret_cast<const uint4*>(p + (r + (long long)k * lanes) * C);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const bf162* h = reinterpret_cast<const bf162*>(&u[k]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+    }
+    for (; r < r1; r += lanes) {
+      const uint4 u = *reinterpret_cast<const uint4*>(p + r * C);
+      const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[lane * C + gidx * 8 + j] = acc[j];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += 256) {
+    float t = 0.f;
+    for (int l = 0; l < lanes; ++l) t += red[l * C + c];
+    atomicAdd(out + c, t);
+  }
+}
+
 // Adam on flat buffers: fp32 master weights and moments, bf16 gradients (already
 // reduced over ranks), bf16 working copy refreshed in the same pass.  The step
 // dependent scalars (learning rate, bias corrections) are read from device
@@ -253,6 +307,16 @@ int ffb_act_bwd(const void* dy, const void* y, void* dx, long long rows, int C, 
 int ffb_colsum(const void* x, float* out, long long rows, int C, void* stream) {
   if (rows <= 0) return 0;
   if (C % 2) return -2;
+  if (C % 8 == 0 && C <= 2048 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int groups = C / 8, lanes = 256 / groups;
+    long long blocks = (rows + (long long)lanes * 8 - 1) / ((long long)lanes * 8);
+    if (blocks > 592) blocks = 592;
+    if (blocks < 1) blocks = 1;
+    const long long rpb = (rows + blocks - 1) / blocks;
+    const size_t smem = sizeof(float) * lanes * C;          // = 8 KB
+    colsum_v8_k<<<(unsigned)((rows + rpb - 1) / rpb), 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>((const bf16*)x, out, rows, C, rpb);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  }
   long long chunks = (rows + 255) / 256;
   if (chunks > 512) chunks = 512;
   const long long rpb = (rows + chunks - 1) / chunks;

@@ -179,3 +179,16 @@ def test_trainer_gradient_sink_matches_autograd_accumulation(device_status):
     err = (grads[0] - grads[1]).abs().max().item()
     scale = grads[1].abs().max().item()
     assert err < 2e-2 * max(scale, 1e-3), (err, scale)
+
+
+@pytest.mark.parametrize("rows,C", [(65536, 128), (4099, 256), (777, 384), (5000, 1024), (300, 8), (1000, 6)])
+def test_colsum(rows, C, device_status):
+    from fastfold_b200.ops.fused_ops import colsum
+    torch.manual_seed(rows)
+    x = torch.randn(rows, C, device="cuda").to(torch.bfloat16)
+    got = colsum(x)
+    want = x.float().sum(0)
+    assert (got - want).abs().max() < 1e-2 * max(1.0, want.abs().max().item())
+    acc = torch.ones(C, device="cuda")
+    colsum(x, out=acc)
+    assert (acc - 1 - want).abs().max() < 1e-2 * max(1.0, want.abs().max().item())
