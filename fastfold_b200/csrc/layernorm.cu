@@ -338,6 +338,101 @@ __global__ void __launch_bounds__(256) ln_fwd_transposed_kernel(const bf16* __re
   }
 }
 
+// 64-row tiles: a warp reads 128 contiguous bytes per channel (two rows per lane), four channels in flight per warp,
+// and the normalised rows leave as 16-byte stores.  rows % 2 == 0, C % 8 == 0, C <= 256.
+constexpr int LNT64 = 64;
+__global__ void __launch_bounds__(256) ln_fwd_transposed64_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma,
+                                                                 const bf16* __restrict__ beta, bf16* __restrict__ y,
+                                                                 float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                 long long rows, int C, float eps) {
+  extern __shared__ float tile[];  // [C][LNT64 + 1]
+  __shared__ float s_part[8][LNT64], s_mean[LNT64], s_rstd[LNT64];
+  constexpr int P = LNT64 + 1;
+  const long long r0 = (long long)blockIdx.x * LNT64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long r = r0 + 2 * tx;
+  const bool ok = r < rows;                      // rows is even: the pair is in range together
+  for (int c = ty; c < C; c += 32) {
+    bf162 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int cc = c + 8 * k;
+      v[k] = (ok && cc < C) ? *reinterpret_cast<const bf162*>(x + (long long)cc * rows + r) : __floats2bfloat162_rn(0.f, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int cc = c + 8 * k;
+      if (cc < C) {
+        const float2 f = __bfloat1622float2(v[k]);
+        tile[cc * P + 2 * tx] = f.x;
+        tile[cc * P + 2 * tx + 1] = f.y;
+      }
+    }
+  }
+  __syncthreads();
+  {
+    float a = 0.f, b = 0.f;
+    for (int c = ty; c < C; c += 8) {
+      a += tile[c * P + tx];
+      b += tile[c * P + tx + 32];
+    }
+    s_part[ty][tx] = a;
+    s_part[ty][tx + 32] = b;
+  }
+  __syncthreads();
+  float mu0 = 0.f, mu1 = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    mu0 += s_part[w][tx];
+    mu1 += s_part[w][tx + 32];
+  }
+  mu0 /= C;
+  mu1 /= C;
+  __syncthreads();
+  {
+    float a = 0.f, b = 0.f;
+    for (int c = ty; c < C; c += 8) {
+      const float d0 = tile[c * P + tx] - mu0, d1 = tile[c * P + tx + 32] - mu1;
+      a += d0 * d0;
+      b += d1 * d1;
+    }
+    s_part[ty][tx] = a;
+    s_part[ty][tx + 32] = b;
+  }
+  __syncthreads();
+  if (ty < 2) {
+    const int rr = tx + 32 * ty;
+    float q = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) q += s_part[w][rr];
+    const float mu = ty == 0 ? mu0 : mu1;
+    const float rs = rsqrtf(q / C + eps);
+    s_mean[rr] = mu;
+    s_rstd[rr] = rs;
+    if (r0 + rr < rows) {
+      if (mean_out) mean_out[r0 + rr] = mu;
+      if (rstd_out) rstd_out[r0 + rr] = rs;
+    }
+  }
+  __syncthreads();
+  const int groups = C >> 3;
+  for (int idx = threadIdx.x; idx < LNT64 * groups; idx += 256) {
+    const int rr = idx / groups, c0 = (idx - rr * groups) * 8;
+    if (r0 + rr >= rows) continue;
+    const float mu = s_mean[rr], rs = s_rstd[rr];
+    const uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0), ub = *reinterpret_cast<const uint4*>(beta + c0);
+    const bf162 *hg = reinterpret_cast<const bf162*>(&ug), *hb = reinterpret_cast<const bf162*>(&ub);
+    uint4 uo;
+    bf162* ho = reinterpret_cast<bf162*>(&uo);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g2 = __bfloat1622float2(hg[j]), b2 = __bfloat1622float2(hb[j]);
+      ho[j] = __floats2bfloat162_rn((tile[(c0 + 2 * j) * P + rr] - mu) * rs * g2.x + b2.x, (tile[(c0 + 2 * j + 1) * P + rr] - mu) * rs * g2.y + b2.y);
+    }
+    *reinterpret_cast<uint4*>(y + (r0 + rr) * C + c0) = uo;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // bf16 rows of C = 8 * L elements, L in {8, 16, 32} lanes per row (C = 64, 128, 256 - every LayerNorm of the
 // Evoformer): a warp works on 32 / L rows side by side and on MR_U such groups per step, so that every lane has
@@ -593,6 +688,20 @@ int ffb_layernorm_fwd_transposed(const void* x, const void* gamma, const void* b
                                  long long rows, int C, float eps, void* stream) {
   if (C > 256) return -2;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (rows % 2 == 0 && C % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gamma) |
+                                       reinterpret_cast<uintptr_t>(beta)) & 15) == 0) {
+    static bool attr = false;
+    if (!attr) {
+      if (cudaFuncSetAttribute(ln_fwd_transposed64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * 256 * (LNT64 + 1))) !=
+          cudaSuccess)
+        return -3;
+      attr = true;
+    }
+    const size_t smem64 = sizeof(float) * C * (LNT64 + 1);
+    ln_fwd_transposed64_kernel<<<(unsigned)((rows + LNT64 - 1) / LNT64), 256, smem64, st>>>(
+        (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  }
   const size_t smem = sizeof(float) * C * (LNT_ROWS + 1);
   ln_fwd_transposed_kernel<<<(unsigned)((rows + LNT_ROWS - 1) / LNT_ROWS), 256, smem, st>>>(
       (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
