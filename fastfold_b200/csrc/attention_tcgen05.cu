@@ -23,8 +23,8 @@
 //              thread finishing 16 of the 32 output channels.
 // The issuer runs one block ahead across item boundaries, so S of block g+1 and
 // the PV products of block g overlap the softmax of block g.
-// Masked keys get the logit -1e9 (replaced, not added), as in the reference's
-// softmax kernels (softmax_cuda_kernel.cu:338-423,618-706); keys beyond the
+// Masked keys get a huge negative logit (replaced, not added; -2^30 here, -1e9 in the reference's
+// softmax kernels, softmax_cuda_kernel.cu:338-423,618-706 - same weights); keys beyond the
 // sequence end get -inf.  The kernel also stores log2-domain row statistics
 // L2 = m * log2(e) + log2(l) for the backward kernel.
 //
@@ -94,6 +94,23 @@ __device__ __forceinline__ void key_bits(const bf16* mrow, int kbase, int n_k, i
   keep_hi = __ballot_sync(0xffffffffu, on_b);
 }
 
+// Masked keys take this logit (replaced, not added).  -2^30 instead of the reference's -1e9: its product with log2(e) is
+// exact in fp32, so a fully masked row still comes out as exactly uniform weights from the fused multiply-add form
+// exp2(v * log2e - m * log2e); any finite logit next to it underflows to weight 0 either way.
+constexpr float MASKED_LOGIT = -1073741824.f;
+
+// Per-warp table of the 64 keys of a half block: (keep, penalty) with logit' = logit * keep + penalty, i.e. (1, 0) for a
+// normal key, (0, MASKED_LOGIT) for a masked one, (0, -inf) past the end of the sequence.  One FMA per logit instead of
+// bit tests and selects.
+__device__ __forceinline__ void write_key_table(float2* kp, int lane, uint32_t keep_lo, uint32_t keep_hi, uint32_t valid_lo,
+                                                uint32_t valid_hi) {
+  __syncwarp();                                   // the previous block's reads of the table are done
+  const bool k0 = (keep_lo >> lane) & 1u, v0 = (valid_lo >> lane) & 1u, k1 = (keep_hi >> lane) & 1u, v1 = (valid_hi >> lane) & 1u;
+  kp[lane] = v0 ? (k0 ? make_float2(1.f, 0.f) : make_float2(0.f, MASKED_LOGIT)) : make_float2(0.f, -INFINITY);
+  kp[lane + 32] = v1 ? (k1 ? make_float2(1.f, 0.f) : make_float2(0.f, MASKED_LOGIT)) : make_float2(0.f, -INFINITY);
+  __syncwarp();
+}
+
 struct AttnSmem {
   // offsets (bytes) from the 1024-aligned base
   static constexpr int Q = 0;                                  // 2 x [128][64 B]            16 KB
@@ -101,7 +118,8 @@ struct AttnSmem {
   static constexpr int BIAS = KV + AT_KV_STAGES * 16384;       // 2 x [2 boxes][128][128 B]  64 KB
   static constexpr int P = BIAS + 2 * 32768;                   // 2 x [2 chunks][128][128 B] 64 KB
   static constexpr int XCH = P + 2 * 32768;                    // [2 halves][18][128] floats 18 KB
-  static constexpr int BARS = XCH + 2 * 18 * 128 * 4;
+  static constexpr int KP = XCH + 2 * 18 * 128 * 4;            // [8 warps][64] (keep, penalty) pairs 4 KB
+  static constexpr int BARS = KP + 8 * 64 * 8;
   static constexpr int TOTAL = BARS + 512 + 1024;
 };
 
@@ -343,11 +361,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
           for (int c = 0; c < 64; ++c) s[c] *= a.scale;
         }
         if (!plain) {
+          float2* kp = reinterpret_cast<float2*>(sm + AttnSmem::KP) + (warp - 2) * 64;
+          write_key_table(kp, lane, keep_lo, keep_hi, valid_lo, valid_hi);
 #pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            const uint32_t keep = c < 32 ? keep_lo : keep_hi, valid = c < 32 ? valid_lo : valid_hi;
-            if (!((keep >> (c & 31)) & 1u)) s[c] = -1e9f;
-            if (!((valid >> (c & 31)) & 1u)) s[c] = -INFINITY;
+          for (int c = 0; c < 64; c += 2) {
+            const float4 e = *reinterpret_cast<const float4*>(kp + c);       // same address in every lane: broadcast
+            s[c] = fmaf(s[c], e.x, e.y);
+            s[c + 1] = fmaf(s[c + 1], e.z, e.w);
           }
         }
         float mx0 = m, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
@@ -365,30 +385,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
         // ---- P = exp(s - m) as bf16 into the swizzled A-operand tile ----
         uint8_t* prow = sm + AttnSmem::P + sb * 32768 + half * 16384 + r * 128;
         float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-        if (plain) {
+        {
           const float nm = -mxs * LOG2E;
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             float p[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) p[e] = ex2f(fmaf(s[u * 8 + e], LOG2E, nm));
-            sum0 += p[0] + p[4];
-            sum1 += p[1] + p[5];
-            sum2 += p[2] + p[6];
-            sum3 += p[3] + p[7];
-            uint4 pk;
-            bf162* hp = reinterpret_cast<bf162*>(&pk);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) hp[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
-            *reinterpret_cast<uint4*>(prow + ((u ^ (r & 7)) << 4)) = pk;
-          }
-        } else {
-          // masked logits are huge: subtract first, so that equal logits give exactly 1
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            float p[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) p[e] = ex2f((s[u * 8 + e] - mxs) * LOG2E);
             sum0 += p[0] + p[4];
             sum1 += p[1] + p[5];
             sum2 += p[2] + p[6];
@@ -607,7 +610,8 @@ struct BwdSmem {
   static constexpr int P = BIAS + 2 * 32768;            // 32 KB
   static constexpr int DS = P + 32768;                  // 32 KB
   static constexpr int DROW = DS + 32768;               // float[512] D_i, float[512] L2_i
-  static constexpr int BARS = DROW + 4096;
+  static constexpr int KP = DROW + 4096;                // [8 warps][64] (keep, penalty) pairs 4 KB
+  static constexpr int BARS = KP + 8 * 64 * 8;
   static constexpr int TOTAL = BARS + 512 + 1024;
 };
 
@@ -807,6 +811,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
         for (int i = 0; i < a.n_qt; ++i, ++t) {
           const uint32_t s = t & 1;
           const int qrow = i * AT_BQ + r;
+          // key bits first: their global loads overlap the waits below
+          const int kbase = k0 + half * 64;
+          uint32_t keep_lo, keep_hi, valid_lo, valid_hi;
+          key_bits(mrow, kbase, a.n_k, lane, keep_lo, keep_hi, valid_lo, valid_hi);
+          const bool plain = (keep_lo & keep_hi) == 0xffffffffu;
           bool w = true;
           if (a.has_bias) w = mbar_wait(bias_full + 8 * s, (t >> 1) & 1);
           if (w) w = mbar_wait(sdp_full, t & 1);
@@ -818,10 +827,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
           const bool row_ok = qrow < a.n_q;
           const float Di = drow[qrow];
           const float nL2 = row_ok ? -lrow[qrow] : -INFINITY;     // rows past the end: p = exp2(-inf) = 0
-          const int kbase = k0 + half * 64;
-          uint32_t keep_lo, keep_hi, valid_lo, valid_hi;
-          key_bits(mrow, kbase, a.n_k, lane, keep_lo, keep_hi, valid_lo, valid_hi);
-          const bool plain = (keep_lo & keep_hi) == 0xffffffffu;
+          float2* kp = reinterpret_cast<float2*>(sm + BwdSmem::KP) + (warp - 2) * 64;
+          if (!plain) write_key_table(kp, lane, keep_lo, keep_hi, valid_lo, valid_hi);
           const uint8_t* brow = sm + BwdSmem::BIAS + s * 32768 + half * 16384 + r * 128;
           uint8_t* prow = sm + BwdSmem::P + half * 16384 + r * 128;
           uint8_t* dsrow = sm + BwdSmem::DS + half * 16384 + r * 128;
@@ -854,16 +861,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
 #pragma unroll
               for (int e = 0; e < 8; ++e) pe[e] = ex2f(fmaf(v[e], LOG2E, nL2));
             } else {
-              // masked logits are -1e9: the exponent of a fully masked row is only known to a few hundred units, so it is
-              // clamped to 0 (p <= 1 always); keys past the end get p = 0
+              // masked keys: logit * keep + penalty.  The statistics of a fully masked row carry no usable fraction, so
+              // the exponent is clamped to 0 (p <= 1 always); keys past the end have penalty -inf, hence p = 0
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const int c = u * 8 + e;
-                const uint32_t keep = c < 32 ? keep_lo : keep_hi, valid = c < 32 ? valid_lo : valid_hi;
-                const float vv = ((keep >> (c & 31)) & 1u) ? v[e] : -1e9f;
-                float pp = ex2f(fminf(fmaf(vv, LOG2E, nL2), 0.f));
-                if (!((valid >> (c & 31)) & 1u)) pp = 0.f;
-                pe[e] = pp;
+              for (int e = 0; e < 8; e += 2) {
+                const float4 kk = *reinterpret_cast<const float4*>(kp + u * 8 + e);
+                pe[e] = ex2f(fminf(fmaf(fmaf(v[e], kk.x, kk.y), LOG2E, nL2), 0.f));
+                pe[e + 1] = ex2f(fminf(fmaf(fmaf(v[e + 1], kk.z, kk.w), LOG2E, nL2), 0.f));
               }
             }
 #pragma unroll

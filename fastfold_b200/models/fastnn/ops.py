@@ -344,7 +344,14 @@ class GlobalAttention(nn.Module):
         q = torch.sum(m * mk.unsqueeze(-1), dim=-2) / (torch.sum(mk, dim=-1)[..., None] + self.eps)
         q = self.to_q(q * self.scaling)
         q = q.view(q.shape[:-1] + (self.n_head, -1))                     # [b1, b2, H, c]
-        k, v = self.to_kv(m).chunk(2, dim=-1)                            # [b1, b2, S, c]
+        kv = self.to_kv(m)                                               # [b1, b2, S, 2c]
+        if K.fused_ops.global_attention_supported(q, kv, m):
+            # inference: softmax, both small products and the gate in one kernel (one pass over kv and the gate tensor)
+            gate = self.gating_linear(m)
+            o = K.global_attention_core(q.reshape(-1, self.n_head, self.c), kv.reshape(-1, kv.shape[-2], 2 * self.c),
+                                        mk.reshape(-1, mk.shape[-1]), gate.reshape(-1, gate.shape[-2], gate.shape[-1]), self.gating_bias)
+            return self.o_linear(o.view(gate.shape))
+        k, v = kv.chunk(2, dim=-1)
         logits = torch.matmul(q, k.transpose(-1, -2))                    # [b1, b2, H, S]
         weights = K.fused_softmax(logits, mk)
         o = torch.matmul(weights, v)                                     # [b1, b2, H, c]

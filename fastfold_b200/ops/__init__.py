@@ -1,7 +1,8 @@
 """Hot ops of fastfold_b200: sm_100a kernels on CUDA tensors, PyTorch reference on CPU tensors."""
 from .layer_norm import LayerNorm, FusedLayerNorm, layer_norm, layer_norm_transposed
 from .softmax import fused_softmax
-from .fused_ops import (bias_sigmod_ele, bias_dropout_add, bias_ele_dropout_residual, glu_mask, glu_mask_t, colsum)
+from .fused_ops import (bias_sigmod_ele, bias_dropout_add, bias_ele_dropout_residual, glu_mask, glu_mask_t, colsum,
+                        global_attention_core, global_attention_ref)
 from .gemm import gemm, gemm_ref, linear, linear_t, bmm_nt, weight_grad
 
 __all__ = [

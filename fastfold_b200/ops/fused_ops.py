@@ -259,6 +259,42 @@ def glu_mask_t(pre, mask, split=None):
 
 
 # ---------------------------------------------------------------------------
+def global_attention_ref(q, kv, mask, gate, gate_bias):
+    """fp32 reference of ``global_attention_core`` in plain PyTorch."""
+    c = q.shape[-1]
+    k, v = kv.float()[..., :c], kv.float()[..., c:]
+    logits = torch.einsum("rhc,rsc->rhs", q.float(), k)
+    logits = torch.where(mask[:, None, :] == 0, logits.new_full((), -1e9), logits)
+    o = torch.einsum("rhs,rsc->rhc", torch.softmax(logits, dim=-1), v).reshape(q.shape[0], 1, -1)
+    return torch.sigmoid(gate.float() + gate_bias.float()) * o
+
+
+def global_attention_supported(q, kv, gate):
+    H, c = q.shape[-2:]
+    return (_bf16_cuda(q) and _bf16_cuda(kv) and _bf16_cuda(gate) and not torch.is_grad_enabled() and c in (8, 16, 32) and 256 % H == 0
+            and H * c <= 256 and _lib.has("ffb_global_attention_fwd"))
+
+
+def global_attention_core(q, kv, mask, gate, gate_bias):
+    """One query per (column, head), keys / values shared by the heads:  ``q [R, H, c]`` (projected and scaled),
+    ``kv [R, S, 2c]`` (keys | values), ``mask [R, S]`` (0 = masked key, logit replaced by -1e9), ``gate [R, S, H*c]``
+    (gating projection before bias and sigmoid), ``gate_bias [H*c]``  ->  ``sigmoid(gate + bias) * softmax(q k^T) v``
+    broadcast over S, ``[R, S, H*c]``.  Forward only (inference path of the extra-MSA stack); one kernel, one pass over
+    ``kv`` and ``gate``."""
+    if not global_attention_supported(q, kv, gate):
+        return global_attention_ref(q, kv, mask, gate, gate_bias).to(gate.dtype)
+    R, H, c = q.shape
+    S = kv.shape[1]
+    q, kv, gate = q.contiguous(), kv.contiguous(), gate.contiguous()
+    mask = mask.to(q.dtype).contiguous()
+    out = torch.empty_like(gate)
+    _lib.check(_lib.get().ffb_global_attention_fwd(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(mask), _lib.ptr(gate),
+                                                   _lib.ptr(gate_bias.to(q.dtype).contiguous()), _lib.ptr(out), R, S, H, c, _lib.stream_ptr()),
+               "global_attention_fwd")
+    return out
+
+
+# ---------------------------------------------------------------------------
 def act_backward(dy2, y2, act):
     """dy * act'(pre-activation), expressed through the saved activation output."""
     mode = 1 if act == "relu" else 2

@@ -20,6 +20,15 @@ PREFIX = "alphafold/alphafold_iteration/"
 #        'mha_b'  : jax [H, d]               <-> torch [H*d]
 #        'mha_o'  : jax [H, d, c_out]        <-> torch [c_out, H*d]
 #        'opm_w'  : jax [c, c, c_z]          <-> torch [c_z, c*c]
+#        'mm_w'   : multimer layers, jax [out] (one input feature) or [in, a, b, ...]  <-> torch [out, in]; meta = (a, b, ...)
+#        'mm_b'   : jax [a, b, ...]          <-> torch [a*b*...]
+#        'lin_w_swap' / 'plain_swap': as 'lin_w' / 'plain' with the two halves of the output axis exchanged (the fused
+#                   projection of the incoming triangle multiplication: the archive stores [right | left])
+def _swap_halves(t, dim):
+    a, b = t.chunk(2, dim=dim)
+    return torch.cat((b, a), dim=dim)
+
+
 def _to_torch(a, kind):
     t = torch.as_tensor(np.asarray(a))
     if kind == "lin_w":
@@ -34,6 +43,14 @@ def _to_torch(a, kind):
         return t.reshape(*t.shape[:-3], -1, t.shape[-1]).transpose(-1, -2)
     if kind == "opm_w":
         return t.reshape(*t.shape[:-3], -1, t.shape[-1]).transpose(-1, -2)
+    if kind == "mm_w":
+        return t.unsqueeze(-1) if t.dim() == 1 else t.reshape(t.shape[0], -1).transpose(-1, -2)
+    if kind == "mm_b":
+        return t.reshape(-1)
+    if kind == "lin_w_swap":
+        return _swap_halves(t.transpose(-1, -2), -2)
+    if kind == "plain_swap":
+        return _swap_halves(t, -1)
     raise ValueError(kind)
 
 
@@ -55,6 +72,16 @@ def _to_jax(t, kind, meta):
     if kind == "opm_w":
         w = t.transpose(-1, -2)
         return w.reshape(*w.shape[:-2], meta, meta, w.shape[-1]).contiguous().numpy()
+    if kind == "mm_w":
+        if meta is None:                                # [out, 1] -> [out]
+            return t.squeeze(-1).numpy()
+        return t.transpose(-1, -2).reshape(t.shape[-1], *meta).contiguous().numpy()
+    if kind == "mm_b":
+        return t.reshape(*meta).numpy() if meta else t.numpy()
+    if kind == "lin_w_swap":
+        return _swap_halves(t, -2).transpose(-1, -2).contiguous().numpy()
+    if kind == "plain_swap":
+        return _swap_halves(t, -1).contiguous().numpy()
     raise ValueError(kind)
 
 
@@ -101,9 +128,23 @@ def _tri_att(t):
     return {"query_norm": _layer_norm(t.layer_norm), "feat_2d_weights": _Leaf(t.linear.weight, "lin_w"), "attention": _attention(t.mha)}
 
 
+def _linear_swapped(l):
+    return {"weights": _Leaf(l.weight, "lin_w_swap"), "bias": _Leaf(l.bias, "plain_swap")}
+
+
+def _linear_mm(l, meta=None):
+    d = {"weights": _Leaf(l.weight, "mm_w", meta)}
+    if l.bias is not None:
+        d["bias"] = _Leaf(l.bias, "mm_b", meta)
+    return d
+
+
 def _tri_mul(t):
     if getattr(t, "fused", False):
-        return {"left_norm_input": _layer_norm(t.layer_norm_in), "projection": _linear(t.linear_p), "gate": _linear(t.linear_g),
+        # the module computes incoming as sum_k a[k,i] b[k,j] with (a, b) = halves of the projection; the archive's fused
+        # layer orders the halves the other way round for the incoming update (fastfold/utils/import_weights.py:610-627)
+        proj = _linear if t._outgoing else _linear_swapped
+        return {"left_norm_input": _layer_norm(t.layer_norm_in), "projection": proj(t.linear_p), "gate": proj(t.linear_g),
                 "center_norm": _layer_norm(t.layer_norm_out), "output_projection": _linear(t.linear_z), "gating_linear": _linear(t.linear_gate)}
     return {"layer_norm_input": _layer_norm(t.layer_norm_in), "left_projection": _linear(t.linear_a_p), "right_projection": _linear(t.linear_b_p),
             "left_gate": _linear(t.linear_a_g), "right_gate": _linear(t.linear_b_g), "center_layer_norm": _layer_norm(t.layer_norm_out),
@@ -166,11 +207,29 @@ def _ipa(i):
             "trainable_point_weights": _Leaf(i.head_weights, "plain"), "output_projection": _linear(i.linear_out)}
 
 
+def _ipa_multimer(i):
+    H = i.no_heads
+
+    def pts(pp):
+        return {"point_projection": _linear_mm(pp.linear, (H, 3 * pp.num_points))}
+    return {"q_scalar_projection": _linear_mm(i.linear_q, (H, i.c_hidden)), "k_scalar_projection": _linear_mm(i.linear_k, (H, i.c_hidden)),
+            "v_scalar_projection": _linear_mm(i.linear_v, (H, i.c_hidden)), "q_point_projection": pts(i.linear_q_points),
+            "k_point_projection": pts(i.linear_k_points), "v_point_projection": pts(i.linear_v_points),
+            "attention_2d": _linear(i.linear_b), "trainable_point_weights": _Leaf(i.head_weights, "plain"),
+            "output_projection": _linear(i.linear_out)}
+
+
 def translation_tree(model, version="model_1"):
-    """Nested dict {haiku module path: ... {param name: _Leaf}} describing every parameter of ``model``."""
+    """Nested dict {haiku module path: ... {param name: _Leaf}} describing every parameter of ``model``.  The multimer
+    layout (chain-relative position encoding, nine template-pair input layers, split IPA projections, ``quat_rigid``
+    backbone update) is chosen when ``version`` contains "multimer" (fastfold/utils/import_weights.py:131,470-560)."""
     sm = model.structure_module
-    fold = {"invariant_point_attention": _ipa(sm.ipa), "attention_layer_norm": _layer_norm(sm.layer_norm_ipa),
-            "transition_layer_norm": _layer_norm(sm.transition.layer_norm), "affine_update": _linear(sm.bb_update.linear),
+    is_multimer = "multimer" in version
+    fold = {"invariant_point_attention": _ipa_multimer(sm.ipa) if is_multimer else _ipa(sm.ipa),
+            "attention_layer_norm": _layer_norm(sm.layer_norm_ipa),
+            "transition_layer_norm": _layer_norm(sm.transition.layer_norm),
+            ("quat_rigid" if is_multimer else "affine_update"): ({"rigid": _linear(sm.bb_update.linear)} if is_multimer
+                                                                 else _linear(sm.bb_update.linear)),
             "rigid_sidechain": {"input_projection": _linear(sm.angle_resnet.linear_in), "input_projection_1": _linear(sm.angle_resnet.linear_initial),
                                 "unnormalized_angles": _linear(sm.angle_resnet.linear_out)}}
     for li, layer in enumerate(sm.transition.layers):
@@ -186,14 +245,32 @@ def translation_tree(model, version="model_1"):
         "preprocess_1d": _linear(model.input_embedder.linear_tf_m), "preprocess_msa": _linear(model.input_embedder.linear_msa_m),
         "left_single": _linear(model.input_embedder.linear_tf_z_i), "right_single": _linear(model.input_embedder.linear_tf_z_j),
         "prev_pos_linear": _linear(model.recycling_embedder.linear), "prev_msa_first_row_norm": _layer_norm(model.recycling_embedder.layer_norm_m),
-        "prev_pair_norm": _layer_norm(model.recycling_embedder.layer_norm_z), "pair_activiations": _linear(model.input_embedder.linear_relpos),
+        "prev_pair_norm": _layer_norm(model.recycling_embedder.layer_norm_z),
         "extra_msa_activations": _linear(model.extra_msa_embedder.linear),
         "extra_msa_stack": _stack([_extra_block(b) for b in model.extra_msa_stack.blocks]),
         "evoformer_iteration": _stack([_evo_block(b) for b in model.evoformer.blocks]),
         "single_activations": _linear(model.evoformer.linear),
     }
-    no_templ = any(v in version for v in ("model_3", "model_4", "model_5"))
-    if model.config.template.enabled and not no_templ:
+    if is_multimer:
+        evo["~_relative_encoding"] = {"position_activations": _linear(model.input_embedder.linear_relpos)}
+    else:
+        evo["pair_activiations"] = _linear(model.input_embedder.linear_relpos)
+    no_templ = not is_multimer and any(v in version for v in ("model_3", "model_4", "model_5"))
+    if model.config.template.enabled and is_multimer:
+        te = model.template_embedder
+        pe = te.template_pair_embedder
+        single = {"query_embedding_norm": _layer_norm(pe.query_embedding_layer_norm),
+                  "template_embedding_iteration": _stack([_template_block(b) for b in te.template_pair_stack.blocks]),
+                  "output_layer_norm": _layer_norm(te.template_pair_stack.layer_norm)}
+        inputs = [(pe.dgram_linear, False), (pe.pseudo_beta_mask_linear, True), (pe.aatype_linear_1, False), (pe.aatype_linear_2, False),
+                  (pe.x_linear, True), (pe.y_linear, True), (pe.z_linear, True), (pe.backbone_mask_linear, True),
+                  (pe.query_embedding_linear, False)]
+        for n, (lin, one_feature) in enumerate(inputs):
+            single["template_pair_embedding_%d" % n] = _linear_mm(lin) if one_feature else _linear(lin)
+        evo["template_embedding"] = {"single_template_embedding": single, "output_linear": _linear(te.linear_t)}
+        evo["template_projection"] = _linear(te.template_single_embedder.template_projector)
+        evo["template_single_embedding"] = _linear(te.template_single_embedder.template_single_embedder)
+    elif model.config.template.enabled and not no_templ:
         te = model.template_embedder
         evo["template_embedding"] = {
             "single_template_embedding": {
@@ -220,7 +297,7 @@ def translation_tree(model, version="model_1"):
 
 
 # scopes whose parameters are stored stacked over their blocks (leading axis = block index)
-_STACKED = ("/extra_msa_stack/", "/evoformer_iteration/", "/__layer_stack_no_state/")
+_STACKED = ("/extra_msa_stack/", "/evoformer_iteration/", "/__layer_stack_no_state/", "/template_embedding_iteration/")
 
 
 def _flatten(tree, path=""):

@@ -59,3 +59,53 @@ def test_openfold_state_dict_import():
     import_openfold_state_dict_(dst, sd)
     for k, v in src.state_dict().items():
         assert torch.equal(v, dst.state_dict()[k])
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_multimer_archive_round_trip(fused):
+    """Multimer layout: chain-relative position layer, nine template-pair input layers (five with one input feature,
+    stored as vectors), split IPA projections stored [c_s, H, ...], ``quat_rigid`` backbone update, and - with the fused
+    triangle-multiplication layout of the v3 weights - the exchanged halves of the incoming update's projection."""
+    from fastfold_b200.models.nn.pair import set_fused_triangle_multiplication
+    name = "model_1_multimer_v3" if fused else "model_1_multimer"
+    set_fused_triangle_multiplication(fused)
+    try:
+        c = model_config(name)
+        c.model.evoformer_stack.no_blocks = 2
+        c.model.extra_msa.extra_msa_stack.no_blocks = 1
+        models = []
+        for seed in (0, 1):
+            torch.manual_seed(seed)
+            m = AlphaFold(c)
+            with torch.no_grad():
+                for p in m.parameters():
+                    p.copy_(torch.randn_like(p))
+            models.append(m)
+    finally:
+        set_fused_triangle_multiplication(False)
+    src, dst = models
+    arch = export_jax_weights(src, version=name)
+    ipa = PREFIX + "structure_module/fold_iteration/invariant_point_attention/"
+    H, ch = src.structure_module.ipa.no_heads, src.structure_module.ipa.c_hidden
+    assert arch[ipa + "q_scalar_projection//weights"].shape == (384, H, ch)
+    assert arch[ipa + "k_point_projection/point_projection//weights"].shape == (384, H, 3 * src.structure_module.ipa.no_qk_points)
+    assert arch[ipa + "v_point_projection/point_projection//bias"].shape == (H, 3 * src.structure_module.ipa.no_v_points)
+    assert PREFIX + "structure_module/fold_iteration/quat_rigid/rigid//weights" in arch
+    assert PREFIX + "evoformer/~_relative_encoding/position_activations//weights" in arch
+    st = PREFIX + "evoformer/template_embedding/single_template_embedding/"
+    assert arch[st + "template_pair_embedding_4//weights"].shape == (64,) and arch[st + "template_pair_embedding_0//weights"].shape == (39, 64)
+    assert arch[st + "template_embedding_iteration/pair_transition/transition1//weights"].shape[0] == 2
+    tri = PREFIX + "evoformer/evoformer_iteration/triangle_multiplication_incoming/"
+    if fused:
+        w = src.evoformer.blocks[0].core.tri_mul_in.linear_p.weight.detach()          # [2c, c_z], halves (a | b)
+        a, b = w.chunk(2, dim=0)
+        assert np.array_equal(arch[tri + "projection//weights"][0], torch.cat((b, a), 0).t().numpy())
+        wo = src.evoformer.blocks[0].core.tri_mul_out.linear_p.weight.detach()
+        assert np.array_equal(arch[tri.replace("incoming", "outgoing") + "projection//weights"][0], wo.t().numpy())
+    else:
+        assert tri + "left_projection//weights" in arch
+    import_jax_weights_(dst, arch, version=name)
+    a, b = src.state_dict(), dst.state_dict()
+    assert a.keys() == b.keys()
+    for k in a:
+        assert torch.equal(a[k], b[k]), k

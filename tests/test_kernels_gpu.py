@@ -192,3 +192,40 @@ def test_colsum(rows, C, device_status):
     acc = torch.ones(C, device="cuda")
     colsum(x, out=acc)
     assert (acc - 1 - want).abs().max() < 1e-2 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("R,S,H,c", [(37, 300, 8, 8), (5, 20, 4, 16), (3, 1000, 8, 32), (150, 1024, 8, 8)])
+def test_global_attention_core(R, S, H, c, device_status):
+    """One-kernel global column attention (softmax over the sequences with one query per head, value aggregation, gate)
+    against the fp32 reference; includes a fully masked column (uniform weights) and S smaller than the 32 sequence lanes."""
+    from fastfold_b200.ops.fused_ops import global_attention_supported
+    torch.manual_seed(R + S)
+    q = (torch.randn(R, H, c, device=DEV) * 0.8).bfloat16()
+    kv = torch.randn(R, S, 2 * c, device=DEV).bfloat16()
+    mask = (torch.rand(R, S, device=DEV) > 0.2).bfloat16()
+    mask[1] = 0
+    gate = torch.randn(R, S, H * c, device=DEV).bfloat16()
+    gb = torch.randn(H * c, device=DEV).bfloat16()
+    with torch.no_grad():
+        assert global_attention_supported(q, kv, gate)
+        out = ops.global_attention_core(q, kv, mask, gate, gb)
+    ref = ops.global_attention_ref(q, kv, mask, gate, gb)
+    assert out.shape == gate.shape and out.dtype == torch.bfloat16
+    assert (out.float() - ref).abs().max() < 2e-2
+
+
+def test_global_attention_module_matches_composite(device_status):
+    """The fastnn GlobalAttention module gives the same result with the fused inference kernel (no grad) as with its
+    composite path (grad enabled)."""
+    from fastfold_b200.models.fastnn.ops import GlobalAttention
+    torch.manual_seed(0)
+    ga = GlobalAttention(64, 8, 8, 64).to(DEV, torch.bfloat16)
+    with torch.no_grad():
+        for p in ga.parameters():
+            p.copy_(torch.randn_like(p) * 0.2)
+    m = torch.randn(1, 24, 200, 64, device=DEV).bfloat16()
+    mask = (torch.rand(1, 24, 200, device=DEV) > 0.1).bfloat16()
+    with torch.no_grad():
+        fused = ga(m, mask)
+    comp = ga(m, mask).detach()
+    assert (fused.float() - comp.float()).abs().max() < 3e-2 * max(1.0, comp.float().abs().max().item())

@@ -111,3 +111,25 @@ def test_multimer_preset_forward():
     assert out["final_atom_positions"].shape == (20, 37, 3)
     assert torch.isfinite(out["final_atom_positions"]).all() and torch.isfinite(out["pair"]).all()
     assert out["masked_msa_logits"].shape[-1] == 22
+
+
+def test_global_attention_reference_matches_module_math():
+    """``global_attention_ref`` (the oracle of the fused kernel) is the module's composite path."""
+    import torch
+    from fastfold_b200 import ops
+    from fastfold_b200.models.fastnn.ops import GlobalAttention
+    torch.manual_seed(0)
+    ga = GlobalAttention(16, 4, 2, 16)
+    with torch.no_grad():
+        for p in ga.parameters():
+            p.copy_(torch.randn_like(p) * 0.3)
+    m = torch.randn(1, 5, 7, 16)
+    mask = (torch.rand(1, 5, 7) > 0.3).float()
+    mask[0, 2] = 0
+    want = ga(m, mask)
+    mk = mask
+    q = torch.sum(m * mk.unsqueeze(-1), dim=-2) / (torch.sum(mk, dim=-1)[..., None] + ga.eps)
+    q = ga.to_q(q * ga.scaling).view(5, 2, 4)
+    core = ops.global_attention_ref(q, ga.to_kv(m)[0], mask[0], ga.gating_linear(m)[0], ga.gating_bias)
+    got = ga.o_linear(core.unsqueeze(0))
+    assert torch.allclose(got, want, atol=1e-5)
