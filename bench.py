@@ -30,6 +30,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
 S_MSA, N_RES, C_M, C_Z, C_S, N_BLOCKS = 128, 256, 256, 128, 384, 48
+# Adam learning rate of both arms: the value the reference's warm-up schedule (0 -> 1e-3 over 1000 steps, train.py) reaches after
+# ten steps.  At 1e-3 from the first step this random-init 48-block stack diverges within a few steps (in fp32 on the CPU too),
+# which costs nothing in time but makes the reported loss meaningless.
+LR = 1e-5
 
 
 def parse():
@@ -172,7 +176,7 @@ def run_ours(args):
     def loss_fn(mod, m, z, mm, pm, tm, tz, ts):
         return mse_loss(mod(m, z, mm, pm, None), tm, tz, ts)
 
-    trainer = FlatAdamTrainer(model, loss_fn, lr=1e-3, eps=1e-8, use_graph=use_cuda and not args.no_graph,
+    trainer = FlatAdamTrainer(model, loss_fn, lr=LR, eps=1e-8, use_graph=use_cuda and not args.no_graph,
                               replicated_param_filter=lambda n: n.startswith("linear."))
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device) if use_cuda else None
 
@@ -275,7 +279,7 @@ def run_reference(args):
     model = EvoformerStack(c_m=C_M, c_z=C_Z, c_s=C_S, no_blocks=args.blocks, blocks_per_ckpt=1)
     randomize_zero_weights(torch, model, 99)
     model = model.to(device=device, dtype=dtype).train()
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-8)
+    opt = torch.optim.Adam(model.parameters(), lr=LR, eps=1e-8)
     host = make_inputs(torch, S, N, device, dtype, seed=7)
     dev_in = [t.to(device, non_blocking=True) for t in host]
 

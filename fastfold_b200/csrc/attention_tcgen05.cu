@@ -485,7 +485,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
           }
           *reinterpret_cast<uint4*>(dst + c) = pk;
         }
-        if (a.lse2 && half == 0) a.lse2[((long long)b * a.H + h) * a.n_q + qrow] = mt * LOG2E + log2f(lt);
+        // A row whose keys are all masked has uniform weights; its statistic m * log2e + log2(l) would lose log2(l) to
+        // rounding (|m| = 2^30), so such rows are flagged with -inf and the backward pass uses 1 / n_k for them.
+        if (a.lse2 && half == 0)
+          a.lse2[((long long)b * a.H + h) * a.n_q + qrow] = (mt == MASKED_LOGIT) ? -INFINITY : mt * LOG2E + log2f(lt);
       }
     }
   }
@@ -826,7 +829,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
           tc_fence_after();
           const bool row_ok = qrow < a.n_q;
           const float Di = drow[qrow];
-          const float nL2 = row_ok ? -lrow[qrow] : -INFINITY;     // rows past the end: p = exp2(-inf) = 0
+          // rows past the end: p = exp2(-inf) = 0.  Fully masked rows (flag -inf): every valid key has the logit MASKED_LOGIT,
+          // p = exp2(MASKED_LOGIT * log2e - MASKED_LOGIT * log2e - log2(n_k)) = 1 / n_k exactly.
+          const float lse_row = row_ok ? lrow[qrow] : INFINITY;
+          const bool row_full = lse_row == -INFINITY;
+          const float nL2 = row_full ? -(MASKED_LOGIT * LOG2E) : -lse_row;
+          const float nL2b = row_full ? -log2f((float)a.n_k) : 0.f;
           float2* kp = reinterpret_cast<float2*>(sm + BwdSmem::KP) + (warp - 2) * 64;
           if (!plain) write_key_table(kp, lane, keep_lo, keep_hi, valid_lo, valid_hi);
           const uint8_t* brow = sm + BwdSmem::BIAS + s * 32768 + half * 16384 + r * 128;
@@ -859,19 +867,23 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
             float pe[8], g[8];
             if (plain) {
 #pragma unroll
-              for (int e = 0; e < 8; ++e) pe[e] = ex2f(fmaf(v[e], LOG2E, nL2));
+              for (int e = 0; e < 8; ++e) {
+                pe[e] = ex2f(fmaf(v[e], LOG2E, nL2));
+                g[e] = pe[e] * (dpv[u * 8 + e] - Di);
+              }
             } else {
-              // masked keys: logit * keep + penalty.  The statistics of a fully masked row carry no usable fraction, so
-              // the exponent is clamped to 0 (p <= 1 always); keys past the end have penalty -inf, hence p = 0
+              // masked keys: logit * keep + penalty; keys past the end have penalty -inf, hence p = 0.  The clamp keeps
+              // p <= 1 whatever rounding does to a masked key's exponent.
 #pragma unroll
               for (int e = 0; e < 8; e += 2) {
                 const float4 kk = *reinterpret_cast<const float4*>(kp + u * 8 + e);
-                pe[e] = ex2f(fminf(fmaf(fmaf(v[e], kk.x, kk.y), LOG2E, nL2), 0.f));
-                pe[e + 1] = ex2f(fminf(fmaf(fmaf(v[e + 1], kk.z, kk.w), LOG2E, nL2), 0.f));
+                pe[e] = ex2f(fminf(fmaf(fmaf(v[e], kk.x, kk.y), LOG2E, nL2) + nL2b, 0.f));
+                pe[e + 1] = ex2f(fminf(fmaf(fmaf(v[e + 1], kk.z, kk.w), LOG2E, nL2) + nL2b, 0.f));
+                // a masked logit is a constant: no gradient flows through it (matters in fully masked rows, where p != 0)
+                g[e] = pe[e] * (dpv[u * 8 + e] - Di) * kk.x;
+                g[e + 1] = pe[e + 1] * (dpv[u * 8 + e + 1] - Di) * kk.z;
               }
             }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) g[e] = pe[e] * (dpv[u * 8 + e] - Di);
             uint4 pp, dd, dg;
             bf162 *hpp = reinterpret_cast<bf162*>(&pp), *hdd = reinterpret_cast<bf162*>(&dd), *hdg = reinterpret_cast<bf162*>(&dg);
 #pragma unroll

@@ -69,18 +69,21 @@ def test_backward(B, n, H, use_bias, use_mask, device_status):
         assert berr < 3e-2 * max(1.0, bmax), "dbias err %g (max %g)" % (berr, bmax)
 
 
-def test_backward_fully_masked_row_stays_finite(device_status):
-    """A batch row whose keys are all masked (a padded MSA row) must not poison the other rows' gradients."""
+@pytest.mark.parametrize("n", [256, 200])
+def test_backward_fully_masked_row_is_exact(n, device_status):
+    """A batch row whose keys are all masked (a padded MSA row) has uniform attention weights; its gradients must be
+    those of the uniform softmax (a backward pass that is off by a constant factor there grows exponentially through a
+    deep stack), and the other rows must be unaffected."""
     torch.manual_seed(5)
-    B, n, H = 6, 256, 4
+    B, H = 6, 4
     qkv = (torch.randn(1, B, n, 3, H, 32, device=DEV) * 0.7).to(torch.bfloat16).requires_grad_(True)
     bias = torch.randn(1, 1, H, n, n, device=DEV).to(torch.bfloat16).requires_grad_(True)
     mask = torch.ones(1, B, n, device=DEV, dtype=torch.bfloat16)
     mask[0, 2] = 0
+    mask[0, 4] = 0
     q, k, v = (qkv[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
     out = attention_core(q, k, v, mask, bias)
     g = torch.randn_like(out)
-    g[:, 2] = 0                      # the model multiplies masked rows away downstream
     out.backward(g)
     assert torch.isfinite(out.float()).all()
     assert torch.isfinite(qkv.grad.float()).all() and torch.isfinite(bias.grad.float()).all()
@@ -89,9 +92,12 @@ def test_backward_fully_masked_row_stays_finite(device_status):
     qr, kr, vr = (qkv_r[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
     ref = attention_core_ref(qr, kr, vr, mask.float(), bias_r)
     ref.backward(g.float())
-    keep = [0, 1, 3, 4, 5]
-    gerr = (qkv.grad.float()[:, keep] - qkv_r.grad[:, keep]).abs().max().item()
-    assert gerr < 3e-2 * max(1.0, qkv_r.grad.abs().max().item())
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    gerr = (qkv.grad.float() - qkv_r.grad).abs().max().item()
+    assert gerr < 3e-2 * max(1.0, qkv_r.grad.abs().max().item()), gerr
+    # the masked rows on their own: dV there is mean(dO) / 1, small numbers that a factor-n error would swamp
+    merr = (qkv.grad.float()[:, [2, 4]] - qkv_r.grad[:, [2, 4]]).abs().max().item()
+    assert merr < 3e-2 * max(0.05, qkv_r.grad[:, [2, 4]].abs().max().item()), merr
     berr = (bias.grad.float() - bias_r.grad).abs().max().item()
     assert berr < 3e-2 * max(1.0, bias_r.grad.abs().max().item())
 
