@@ -17,6 +17,7 @@ in ``C`` columns, triangle multiplication slab by slab.  Results do not depend
 on it; it only bounds transient memory.
 """
 import math
+import os
 
 import torch
 import torch.nn as nn
@@ -146,6 +147,11 @@ ChunkTransition = Transition
 # ---------------------------------------------------------------------------
 # Outer product mean
 # ---------------------------------------------------------------------------
+# all-gather fused into the outer-product GEMM's load stage (no-grad pass under DAP); FASTFOLD_OPM_FUSED_GATHER=0 selects
+# the publish + pull all-gather instead
+_OPM_FUSED_GATHER = os.environ.get("FASTFOLD_OPM_FUSED_GATHER", "1") != "0"
+
+
 class OutProductMean(nn.Module):
     def __init__(self, n_feat=64, n_feat_out=128, n_feat_proj=32):
         super().__init__()
@@ -177,11 +183,47 @@ class OutProductMean(nn.Module):
         o = o.reshape(ni, d, N, e).permute(0, 2, 1, 3).reshape(1, ni, N, d * e)
         return Z_raw + self.o_linear(o) * inv_norm.to(o.dtype)
 
+    def _fused_gather(self, M, M_mask, M_mask_col, Z_raw):
+        """No-grad pass under DAP on the GPU: the masked right projection is written straight into a symmetric-heap
+        slot and the outer-product GEMM reads every rank's slab of it tile by tile with TMA over NVLink (B operand,
+        MN-major, gathered along N) - the all-gather and its gathered copy disappear.  Returns None when the shapes do
+        not fit (slab extent a whole number of 128-wide tiles)."""
+        P = core.get_dap_size()
+        if P == 1 or torch.is_grad_enabled() or CHUNK_SIZE is not None or not (M.is_cuda and M.dtype == torch.bfloat16):
+            return None
+        S, ni, e = M.shape[1], M.shape[2], self.n_feat_proj
+        if e != 32 or (ni * e) % 128 or self.o_linear.bias is None:
+            return None
+        from ...parallel import symm
+        heap = symm.get_heap("dap")
+        if heap is None:
+            return None
+        slot = heap.next_ring_slot(S * ni * e * 2)
+        heap.slot_fence(slot, pre=True)
+        r_local = heap.view(slot, (1, S, ni, e), M.dtype)
+        torch.mul(self.linear_b(M), M_mask_col.to(M.dtype), out=r_local)
+        heap.slot_fence(slot, pre=False)
+        left_act = self.linear_a(M) * M_mask_col.to(M.dtype)
+        norm = torch.einsum("bsid,bsjd->bijd", M_mask_col.float(), M_mask.float()) + 1e-3
+        inv_norm = (1.0 / norm).reshape(-1)
+        N = ni * P
+        l2 = left_act.reshape(S, ni * e)
+        heap.consume_fence(slot, pre=True)
+        o4 = K.gemm(l2, r_local.reshape(S, ni * e), a_mn=True, b_mn=True, block_out=((ni * N, 1024), 1, N * 1024, 0, 1024),
+                    peer=("b", heap.peer_addresses(slot, 0)))
+        heap.consume_fence(slot, pre=False)
+        out = K.gemm(o4, self.o_linear.weight, bias=self.o_linear.bias, rowscale=inv_norm, resid=Z_raw.reshape(ni * N, -1))
+        return out.reshape(Z_raw.shape)
+
     def forward(self, M, M_mask, Z_raw):
         M = self.layernormM(M)
-        right_act = self.linear_b(M)
         M_mask = M_mask.unsqueeze(-1)
         M_mask_col = scatter(M_mask, dim=2)
+        if _OPM_FUSED_GATHER:
+            out = self._fused_gather(M, M_mask, M_mask_col, Z_raw)
+            if out is not None:
+                return out
+        right_act = self.linear_b(M)
         # mask before the gather: identical result, and the gathered operand is ready to use
         right_act = right_act * M_mask_col.to(right_act.dtype)
         right_act_all, work = gather_async(right_act, dim=2)

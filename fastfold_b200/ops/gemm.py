@@ -196,7 +196,7 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
                                     a3.stride(0) if a.dim() == 3 else 0, b3.stride(0) if b.dim() == 3 else 0, batch, g,
                                     1 if which == "a" else 2, arr, len(addrs), _lib.stream_ptr())
         _lib.check(rc, "ffb_gemm_bf16_peer(M=%d,N=%d,K=%d,batch=%d,slab=%d)" % (M, N, K, batch, peer_slab))
-        return out
+        return blocked if blocked is not None else out
     rc = lib.ffb_gemm_bf16(_lib.ptr(a3), _lib.ptr(b3), 1 if a_mn else 0, 1 if b_mn else 0, a3.stride(1), b3.stride(1),
                            a3.stride(0) if a.dim() == 3 else 0, b3.stride(0) if b.dim() == 3 else 0, batch, bn, g,
                            _lib.stream_ptr())
