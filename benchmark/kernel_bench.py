@@ -3,6 +3,7 @@
     python benchmark/kernel_bench.py gemm      [--m 65536 --n 512 --k 128] [--bias] [--ref]
     python benchmark/kernel_bench.py attention [--b 128 --h 8 --len 256] [--backward]
     python benchmark/kernel_bench.py layernorm [--rows 65536 --c 128] [--backward]
+    python benchmark/kernel_bench.py global_attention [--b 256 --len 5120 --h 8]
     python benchmark/kernel_bench.py all
 
 Every timing is taken on the device: the op is captured ``--iters`` times in a CUDA graph, each instance preceded
@@ -154,9 +155,24 @@ def bench_layernorm(t, rows, C, backward):
     print("layernorm bwd rows=%d C=%d: %.1f us  (%.0f GB/s -> %.2f %s)" % (rows, C, us, byt / us / 1e3, byt / hbm * 1e6 / us, tag))
 
 
+def bench_global_attention(t, R, S, H):
+    """Global column attention core of the extra-MSA stack (c = 8 per head): R columns, S sequences."""
+    hbm, _, tag = _peaks()
+    c = 8
+    q = _rand(R, H, c, scale=0.8)
+    kv = _rand(R, S, 2 * c)
+    mask = (torch.rand(R, S, device=DEV) > 0.1).to(torch.bfloat16)
+    gate = _rand(R, S, H * c)
+    gb = _rand(H * c)
+    with torch.no_grad():
+        us = t(lambda: K.global_attention_core(q, kv, mask, gate, gb))
+    byt = (kv.numel() + mask.numel() + 2 * gate.numel()) * 2
+    print("global attention R=%d S=%d H=%d c=8: %.1f us  (%.0f GB/s -> %.2f %s)" % (R, S, H, us, byt / us / 1e3, byt / hbm * 1e6 / us, tag))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "all"])
+    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "global_attention", "all"])
     ap.add_argument("--m", type=int, default=65536)
     ap.add_argument("--n", type=int, default=512)
     ap.add_argument("--k", type=int, default=128)
@@ -178,6 +194,8 @@ def main():
         bench_attention(t, args.b, args.h, args.len, args.backward)
     elif args.op == "layernorm":
         bench_layernorm(t, args.rows, args.c, args.backward)
+    elif args.op == "global_attention":
+        bench_global_attention(t, args.b if args.b != 128 else 256, args.len if args.len != 256 else 5120, args.h)
     else:
         for (M, N, Kd) in [(65536, 128, 128), (65536, 512, 128), (65536, 384, 128), (65536, 128, 512), (32768, 768, 256), (32768, 1024, 256),
                            (32768, 256, 1024), (32768, 256, 256), (8192, 8192, 128), (8192, 8192, 8192)]:
@@ -188,6 +206,7 @@ def main():
         for (rows, C) in [(65536, 128), (32768, 256)]:
             bench_layernorm(t, rows, C, False)
             bench_layernorm(t, rows, C, True)
+        bench_global_attention(t, 256, 5120, 8)
     from fastfold_b200.ops import _lib
     st = _lib.read_status()
     if st[0]:
