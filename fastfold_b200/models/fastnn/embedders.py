@@ -41,6 +41,12 @@ class RecyclingEmbedder(ref.RecyclingEmbedder):
         squared_bins = bins ** 2
         upper = torch.cat([squared_bins[1:], squared_bins.new_tensor([self.inf])], dim=-1)
         m_update = self.layer_norm_m(m)
+        from ...ops import embed as kembed
+        if kembed.recycle_pair_embed_supported(z, x):
+            # one pass: distance bin, weight-column gather, LayerNorm and add (no one-hot tensor, no GEMM with K = no_bins)
+            ln = self.layer_norm_z
+            return m_update, kembed.recycle_pair_embed(z, x, squared_bins, self.inf, self.linear.weight, self.linear.bias,
+                                                       ln.weight, ln.bias, ln.eps)
         n = z.shape[-3]
         z_update = torch.empty_like(z)
         for i in range(0, n, ROW_BLOCK):

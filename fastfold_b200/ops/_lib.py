@@ -62,6 +62,7 @@ def _declare(lib):
         "ffb_glu_mask_t_fwd": [P, P, P, I, L, P],
         "ffb_glu_mask_t_bwd": [P, P, P, P, I, L, P],
         "ffb_global_attention_fwd": [P, P, P, P, P, P, L, I, I, I, P],
+        "ffb_recycle_pair_embed": [P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
         "ffb_softmax_fwd": [P, P, P, P, L, L, L, L, I, I, P],
         "ffb_softmax_bwd": [P, P, P, L, I, I, P],
         "ffb_bias_sigmoid_mul_fwd": [P, P, P, P, L, I, P],

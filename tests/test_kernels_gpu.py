@@ -229,3 +229,43 @@ def test_global_attention_module_matches_composite(device_status):
         fused = ga(m, mask)
     comp = ga(m, mask).detach()
     assert (fused.float() - comp.float()).abs().max() < 3e-2 * max(1.0, comp.float().abs().max().item())
+
+
+@pytest.mark.parametrize("N", [64, 200])
+def test_recycle_pair_embed(N, device_status):
+    """Gather-add form of the recycling embedder's pair update against the one-hot composite.  A distance that sits
+    within rounding of a bin edge may fall into the neighbouring bin, so a handful of rows may differ by one weight column."""
+    from fastfold_b200.ops import embed
+    torch.manual_seed(N)
+    z = torch.randn(N, N, 128, device=DEV).bfloat16()
+    x = torch.randn(N, 3, device=DEV) * 8.0
+    bins = torch.linspace(3.25, 20.75, 15, device=DEV) ** 2
+    w = (torch.randn(128, 15, device=DEV) * 0.5).bfloat16()
+    b = (torch.randn(128, device=DEV) * 0.1).bfloat16()
+    g = (torch.randn(128, device=DEV) * 0.3 + 1).bfloat16()
+    be = (torch.randn(128, device=DEV) * 0.1).bfloat16()
+    with torch.no_grad():
+        assert embed.recycle_pair_embed_supported(z, x)
+        out = embed.recycle_pair_embed(z, x, bins, 1e8, w, b, g, be, 1e-5)
+        ref = embed.recycle_pair_embed_ref(z.float(), x, bins, 1e8, w.float(), b.float(), g.float(), be.float(), 1e-5)
+    err = (out.float() - ref).abs().amax(dim=-1)
+    assert (err > 6e-2).float().mean().item() < 1e-3, err.max().item()
+    assert torch.isfinite(out.float()).all()
+
+
+def test_recycling_embedder_module_uses_fused_pair_update(device_status):
+    from fastfold_b200.models.fastnn.embedders import RecyclingEmbedder
+    torch.manual_seed(1)
+    emb = RecyclingEmbedder(c_m=256, c_z=128, min_bin=3.25, max_bin=20.75, no_bins=15, inf=1e8).to(DEV, torch.bfloat16)
+    with torch.no_grad():
+        for p in emb.parameters():
+            p.copy_(torch.randn_like(p) * 0.3)
+    m = torch.randn(96, 256, device=DEV).bfloat16()
+    z = torch.randn(96, 96, 128, device=DEV).bfloat16()
+    x = torch.randn(96, 3, device=DEV) * 8.0
+    with torch.no_grad():
+        m1, z1 = emb(m, z, x)
+    m2, z2 = emb(m, z, x)                    # grad enabled: composite path
+    assert torch.equal(m1, m2.detach())
+    err = (z1.float() - z2.detach().float()).abs().amax(dim=-1)
+    assert (err > 8e-2).float().mean().item() < 1e-3, err.max().item()

@@ -133,3 +133,17 @@ def test_global_attention_reference_matches_module_math():
     core = ops.global_attention_ref(q, ga.to_kv(m)[0], mask[0], ga.gating_linear(m)[0], ga.gating_bias)
     got = ga.o_linear(core.unsqueeze(0))
     assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_recycle_pair_embed_reference_matches_module():
+    """The oracle of the fused recycling pair update equals the recycling embedder's composite forward."""
+    import torch
+    from fastfold_b200.models.fastnn.embedders import RecyclingEmbedder
+    from fastfold_b200.ops import embed
+    torch.manual_seed(0)
+    emb = RecyclingEmbedder(c_m=32, c_z=16, min_bin=3.25, max_bin=20.75, no_bins=15, inf=1e8)
+    m, z, x = torch.randn(10, 32), torch.randn(10, 10, 16), torch.randn(10, 3) * 8
+    _, want = emb(m, z, x)
+    bins = torch.linspace(3.25, 20.75, 15) ** 2
+    got = embed.recycle_pair_embed(z, x, bins, 1e8, emb.linear.weight, emb.linear.bias, emb.layer_norm_z.weight, emb.layer_norm_z.bias, emb.layer_norm_z.eps)
+    assert torch.allclose(got, want, atol=1e-5)
