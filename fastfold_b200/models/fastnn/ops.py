@@ -412,6 +412,14 @@ class GlobalAttention(nn.Module):
 # ---------------------------------------------------------------------------
 # Triangle multiplication
 # ---------------------------------------------------------------------------
+def _dense_fits(z, factor=8, share=0.25):
+    """True when ``factor`` times the bytes of ``z`` are at most ``share`` of the device's memory."""
+    if not z.is_cuda:
+        return True
+    total = torch.cuda.get_device_properties(z.device).total_memory
+    return factor * z.numel() * z.element_size() <= share * total
+
+
 class _TriangleMultiplication(nn.Module):
     """Shared body of the outgoing / incoming triangular multiplicative update.
 
@@ -559,9 +567,13 @@ class _TriangleMultiplication(nn.Module):
             dropmask = F.dropout(torch.ones_like(Z_raw[:, 0:1, :, :]), p=self.p_drop, training=True)
         if not training:
             dropmask = None
-        if CHUNK_SIZE is not None and not torch.is_grad_enabled():
-            return self._chunked(Z_raw, Z_mask)
         can_fuse = _fusable(Z_raw) and (Z_raw.shape[1] * Z_raw.shape[2]) % 8 == 0 and Z_raw.shape[1] % 8 == 0 and Z_raw.shape[2] % 8 == 0
+        if CHUNK_SIZE is not None and not torch.is_grad_enabled():
+            # The slab pipeline bounds memory (its temporaries are one rank's slab) but pays permuted copies of both
+            # operands; the dense no-grad path has none and needs about eight times the local pair tensor, so it is
+            # taken whenever that is a small part of the GPU's memory.
+            if not (can_fuse and _dense_fits(Z_raw)):
+                return self._chunked(Z_raw, Z_mask)
         if can_fuse:
             return self._fused_nograd(Z_raw, Z_mask, dropmask, Z_norm)
         c = self.c

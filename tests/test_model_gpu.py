@@ -70,3 +70,38 @@ def test_stack_gradients_match_fp32_cpu(S, N, device_status, monkeypatch):
     assert worst[0][0] < 0.12, worst[:5]
     mean_err = sum(w for w, _ in worst) / len(worst)
     assert mean_err < 0.04, (mean_err, worst[:5])
+
+
+def test_chunked_inference_paths_agree(device_status, monkeypatch):
+    """No-grad forward of a 2-block stack on the GPU: un-chunked, chunked with the dense triangle multiplication, and
+    chunked with the memory-bounded slab pipeline give the same result up to bf16 rounding."""
+    from fastfold_b200.models.fastnn import EvoformerStack, set_chunk_size
+    from fastfold_b200.models.fastnn import ops as fops
+    torch.manual_seed(7)
+    S, N = 32, 64
+    model = EvoformerStack(256, 128, 384, 2, blocks_per_ckpt=None)
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2 and float(p.abs().sum()) == 0.0:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+    model = model.to("cuda", torch.bfloat16).eval()
+    m = torch.randn(S, N, 256, generator=g).bfloat16().cuda()
+    z = torch.randn(N, N, 128, generator=g).bfloat16().cuda()
+    mm = torch.ones(S, N)
+    mm[3] = 0
+    mm, pm = mm.bfloat16().cuda(), torch.ones(N, N).bfloat16().cuda()
+    outs = []
+    try:
+        with torch.no_grad():
+            outs.append(model(m, z, mm, pm, None))
+            set_chunk_size(16)
+            outs.append(model(m, z, mm, pm, 16))
+            monkeypatch.setattr(fops, "_dense_fits", lambda *a, **k: False)
+            outs.append(model(m, z, mm, pm, 16))
+    finally:
+        set_chunk_size(None)
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            scale = max(1.0, a.float().abs().max().item())
+            assert (a.float() - b.float()).abs().max().item() < 4e-2 * scale
