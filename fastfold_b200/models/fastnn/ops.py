@@ -196,7 +196,7 @@ class OutProductMean(nn.Module):
             return None
         from ...parallel import symm
         heap = symm.get_heap("dap")
-        if heap is None:
+        if heap is None or S * ni * e * 2 > heap.max_message():
             return None
         slot = heap.next_ring_slot(S * ni * e * 2)
         heap.slot_fence(slot, pre=True)
@@ -481,7 +481,7 @@ class _TriangleMultiplication(nn.Module):
             from ...parallel import symm
             heap = symm.get_heap("dap")
             # the gathered operand's slab extent must be a whole number of 128-wide tiles
-            if heap is not None and ((A if self.outgoing else B) % 128 or (2 * c * A * B * 2) % 16):
+            if heap is not None and ((A if self.outgoing else B) % 128 or (2 * c * A * B * 2) % 16 or 2 * c * A * B * 2 > heap.max_message()):
                 heap = None
         if heap is not None:
             # All-gather fused into the contraction GEMM: the projection GEMM writes its (channel-major) result

@@ -42,7 +42,8 @@ def _heap_for(t):
     if h is None:
         return None
     nb = t.numel() * t.element_size()
-    return h if (nb % (16 * h.world) == 0 and nb > 0) else None
+    # messages larger than a ring slot (long sequences) go through NCCL, which is bandwidth-bound there anyway
+    return h if (nb % (16 * h.world) == 0 and 0 < nb <= h.max_message()) else None
 
 
 def _reduce(tensor):

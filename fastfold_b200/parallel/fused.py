@@ -67,6 +67,8 @@ def a2a_layer_norm(x, ln, mode, transpose_norm=False):
     """
     P = core.get_dap_size()
     h = _heap(x) if P > 1 else None
+    if h is not None and x.numel() * x.element_size() > h.max_message():
+        h = None
     if h is None or x.shape[-1] % 8 or ln.weight.dtype != x.dtype:
         raw = comm.row_to_col(x) if mode == 0 else comm.col_to_row(x)
         src = raw.transpose(-2, -3).contiguous() if transpose_norm else raw

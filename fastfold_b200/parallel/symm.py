@@ -98,10 +98,18 @@ class SymmHeap:
             self.ring = [self.slot("ring%d" % i, slot_bytes) for i in range(n_slots)]
         return self.ring
 
-    def next_ring_slot(self, nbytes):
+    def _ensure_ring(self):
         if not self.ring:
             per = min(192 << 20, max(1 << 20, (self.heap_bytes - self._cursor) // 2 // 12))
             self.make_ring(12, per)
+
+    def max_message(self):
+        """Largest message (bytes) that fits a ring slot; callers send anything larger through NCCL instead."""
+        self._ensure_ring()
+        return self.ring[0].nbytes
+
+    def next_ring_slot(self, nbytes):
+        self._ensure_ring()
         s = self.ring[self._seq % len(self.ring)]
         self._seq += 1
         if nbytes > s.nbytes:
