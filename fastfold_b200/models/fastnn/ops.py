@@ -315,9 +315,53 @@ class SelfAttention(nn.Module):
         b = gather_async_opp(*nonbatched_bias, dim=1)
         return b.permute(0, 3, 1, 2).contiguous()          # 'b q k h -> b h q k'
 
+    def _padded_heads(self):
+        """Weights of the same layer with every head widened to the fused attention kernel's 32 channels by zero rows /
+        columns (the extra-MSA stack has 8-channel heads): zero q / k channels leave the logits unchanged, zero v
+        channels give zero outputs that the zero columns of the output projection ignore.  Inference only; cached."""
+        H, d, D = self.n_head, self.c, flash.HEAD_DIM
+        key = (self.to_qkv.weight.data_ptr(), self.to_qkv.weight._version, self.o_linear.weight._version)
+        if getattr(self, "_pad_cache", None) is None or self._pad_cache[0] != key:
+            def rows(w, groups):                      # [groups * H * d, ...] -> [groups * H * D, ...]
+                w = w.detach().reshape(groups, H, d, *w.shape[1:])
+                out = w.new_zeros(groups, H, D, *w.shape[3:])
+                out[:, :, :d] = w
+                return out.reshape(groups * H * D, *w.shape[3:])
+            wq = rows(self.to_qkv.weight, 3)
+            wg = rows(self.gating_linear.weight, 1) if self.gating else None
+            bg = rows(self.gating_bias, 1) if self.gating else None
+            wo = rows(self.o_linear.weight.detach().t().contiguous(), 1).t().contiguous()
+            self._pad_cache = (key, wq, wg, bg, wo)
+        return self._pad_cache[1:]
+
+    def _one_padded(self, x, mask, bias, tail):
+        """No-grad GPU path for heads narrower than the fused kernel's: see ``_padded_heads``."""
+        H, D = self.n_head, flash.HEAD_DIM
+        wq, wg, bg, wo = self._padded_heads()
+        b1, b2, n, _ = x.shape
+        x2 = x.reshape(-1, x.shape[-1])
+        qkv = K.gemm(x2, wq).reshape(b1, b2, n, 3, H, D)
+        bias5 = None if bias is None else bias.unsqueeze(1)
+        if not flash.packed_supported(qkv, mask, bias5):
+            return None
+        o = flash.flash_attention_packed(qkv, mask, bias5, self.scaling).reshape(-1, H * D)
+        if self.gating:
+            o = K.gemm(x2, wg, bias=bg, act="sigmoid", mul=o)
+        if tail is not None:
+            out_bias, dmask, resid = tail
+            out = K.gemm(o, wo, bias=out_bias if out_bias is not None else self.o_linear.bias, dmask=dmask,
+                         resid=resid.reshape(-1, resid.shape[-1]))
+            return out.reshape(resid.shape), True
+        out = K.gemm(o, wo, bias=self.o_linear.bias)
+        return out.reshape(b1, b2, n, -1), False
+
     def _one(self, x, mask, bias, tail, transposed=False):
         """``transposed``: ``x [b1, n, b2, c]`` and the attention runs along dim 1 (``mask [b1, b2, n]``)."""
         H, d = self.n_head, self.c
+        if d < flash.HEAD_DIM and not transposed and _fusable(x) and x.shape[-2] % 8 == 0:
+            res = self._one_padded(x, mask, bias, tail)
+            if res is not None:
+                return res
         bias5 = None if bias is None else bias.unsqueeze(1)
         if transposed:
             b1, n, b2, _ = x.shape

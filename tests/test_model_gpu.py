@@ -105,3 +105,24 @@ def test_chunked_inference_paths_agree(device_status, monkeypatch):
         for a, b in zip(outs[0], other):
             scale = max(1.0, a.float().abs().max().item())
             assert (a.float() - b.float()).abs().max().item() < 4e-2 * scale
+
+
+def test_narrow_head_attention_padded_path(device_status):
+    """Heads of 8 channels (extra-MSA stack) run through the 32-channel fused attention kernel with zero-padded weights
+    at inference; the result equals the composite path (taken when grad is enabled)."""
+    from fastfold_b200.models.fastnn.ops import SelfAttention
+    torch.manual_seed(2)
+    att = SelfAttention(qkv_dim=64, c=8, n_head=8, out_dim=64, gating=True).to("cuda", torch.bfloat16)
+    with torch.no_grad():
+        for p in att.parameters():
+            p.copy_(torch.randn_like(p) * 0.25)
+    x = torch.randn(1, 24, 136, 64, device="cuda").bfloat16()
+    mask = (torch.rand(1, 24, 136, device="cuda") > 0.15).bfloat16()
+    mask[0, 3] = 0
+    bias = torch.randn(1, 8, 136, 136, device="cuda").bfloat16()
+    with torch.no_grad():
+        fast, _ = att(x, mask, (bias, -1))
+        assert att._pad_cache is not None
+    comp, _ = att(x, mask, (bias, -1))
+    err = (fast.float() - comp.detach().float()).abs().max().item()
+    assert err < 4e-2 * max(1.0, comp.detach().float().abs().max().item()), err
