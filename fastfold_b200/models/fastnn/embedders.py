@@ -24,12 +24,14 @@ class InputEmbedder(ref.InputEmbedder):
         tf_emb_j = self.linear_tf_z_j(tf)
         n = tf.shape[-2]
         pair_emb = tf_emb_i.new_empty(tf.shape[:-2] + (n, n, self.c_z))
-        rif = ri.type(tf_emb_i.dtype)
+        # one_hot(nearest bin of i - j) times the weight is a row lookup: bin = clip(i - j, -k, k) + k, computed on the
+        # integer residue indices (in bf16 the indices themselves stop being exact beyond 256)
+        rii = ri.long()
+        table = self.linear_relpos.weight.t()                                   # [2k + 1, c_z]
         for i in range(0, n, ROW_BLOCK):
-            d = rif[..., i:i + ROW_BLOCK, None] - rif[..., None, :]
-            boundaries = torch.arange(start=-self.relpos_k, end=self.relpos_k + 1, device=d.device)
-            oh = ref.one_hot(d, boundaries).type(rif.dtype)
-            pair_emb[..., i:i + ROW_BLOCK, :, :] = self.linear_relpos(oh) + tf_emb_i[..., i:i + ROW_BLOCK, None, :] + tf_emb_j[..., None, :, :]
+            idx = torch.clamp(rii[..., i:i + ROW_BLOCK, None] - rii[..., None, :], -self.relpos_k, self.relpos_k) + self.relpos_k
+            rel = torch.nn.functional.embedding(idx, table) + self.linear_relpos.bias
+            pair_emb[..., i:i + ROW_BLOCK, :, :] = rel + tf_emb_i[..., i:i + ROW_BLOCK, None, :] + tf_emb_j[..., None, :, :]
         n_clust = msa.shape[-3]
         tf_m = self.linear_tf_m(tf).unsqueeze(-3).expand(((-1,) * len(tf.shape[:-2]) + (n_clust, -1, -1)))
         return self.linear_msa_m(msa) + tf_m, pair_emb

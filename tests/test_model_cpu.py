@@ -147,3 +147,22 @@ def test_recycle_pair_embed_reference_matches_module():
     bins = torch.linspace(3.25, 20.75, 15) ** 2
     got = embed.recycle_pair_embed(z, x, bins, 1e8, emb.linear.weight, emb.linear.bias, emb.layer_norm_z.weight, emb.layer_norm_z.bias, emb.layer_norm_z.eps)
     assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_lean_input_embedder_relpos_lookup_matches_one_hot():
+    """The lean input embedder's relative-position term (a table lookup on integer offsets) equals the one-hot + Linear
+    of the OpenFold-layout embedder."""
+    import torch
+    from fastfold_b200.models.fastnn.embedders import InputEmbedder as Lean
+    from fastfold_b200.models.nn.embedders import InputEmbedder as Ref
+    torch.manual_seed(0)
+    ref = Ref(tf_dim=22, msa_dim=49, c_z=16, c_m=24, relpos_k=32)
+    lean = Lean(tf_dim=22, msa_dim=49, c_z=16, c_m=24, relpos_k=32)
+    lean.load_state_dict(ref.state_dict())
+    n = 300
+    tf, msa = torch.randn(n, 22), torch.randn(5, n, 49)
+    ri = torch.arange(n)
+    ri[150:] += 200                      # a chain break: offsets far outside the clipping range
+    m1, z1 = ref(tf, ri, msa)
+    m2, z2 = lean(tf, ri, msa)
+    assert torch.allclose(m1, m2, atol=1e-6) and torch.allclose(z1, z2, atol=1e-5)
