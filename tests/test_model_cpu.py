@@ -166,3 +166,29 @@ def test_lean_input_embedder_relpos_lookup_matches_one_hot():
     m1, z1 = ref(tf, ri, msa)
     m2, z2 = lean(tf, ri, msa)
     assert torch.allclose(m1, m2, atol=1e-6) and torch.allclose(z1, z2, atol=1e-5)
+
+
+def test_padded_head_weights_reproduce_the_layer():
+    """Zero-padding every attention head to the fused kernel's 32 channels leaves projections and output unchanged."""
+    import torch
+    from fastfold_b200.models.fastnn.ops import SelfAttention
+    torch.manual_seed(0)
+    att = SelfAttention(16, 8, 2, 16, gating=True)
+    with torch.no_grad():
+        for p in att.parameters():
+            p.copy_(torch.randn_like(p))
+    wq, wg, bg, wo = att._padded_heads()
+    x = torch.randn(5, 16)
+    qkv = (x @ att.to_qkv.weight.t()).reshape(5, 3, 2, 8)
+    qkv_p = (x @ wq.t()).reshape(5, 3, 2, 32)
+    assert torch.equal(qkv_p[..., :8], qkv) and float(qkv_p[..., 8:].abs().max()) == 0.0
+    o = torch.randn(5, 2, 8)
+    o_p = torch.zeros(5, 2, 32)
+    o_p[..., :8] = o
+    assert torch.allclose(o_p.reshape(5, -1) @ wo.t(), o.reshape(5, -1) @ att.o_linear.weight.t(), atol=1e-5)
+    assert torch.equal(bg.reshape(2, 32)[:, :8].reshape(-1), att.gating_bias) and float(bg.reshape(2, 32)[:, 8:].abs().max()) == 0.0
+    assert torch.equal(wg.reshape(2, 32, 16)[:, :8].reshape(16, 16), att.gating_linear.weight)
+    assert att._padded_heads()[0] is wq                      # cached until a weight changes
+    with torch.no_grad():
+        att.to_qkv.weight.mul_(2.0)
+    assert att._padded_heads()[0] is not wq
