@@ -98,6 +98,47 @@ class DataPipeline:
         return feats
 
 
+def _ground_truth_features(positions, mask, resolution=1.0, is_distillation=False):
+    return {"all_atom_positions": np.asarray(positions, np.float32), "all_atom_mask": np.asarray(mask, np.float32),
+            "resolution": np.array(resolution, np.float32), "is_distillation": np.array(1.0 if is_distillation else 0.0, np.float32)}
+
+
+def _process_structure(self, sequence, description, alignment_dir, positions, mask, resolution, is_distillation):
+    feats = dict(self.process_sequence(sequence, description, alignment_dir))
+    feats.update(_ground_truth_features(positions, mask, resolution, is_distillation))
+    return feats
+
+
+def _process_pdb(self, pdb_path, alignment_dir=None, is_distillation=True, chain_id=None):
+    """Features + ground truth of one chain of a PDB file (fastfold/data/data_pipeline.py:780-828)."""
+    from ..common import protein
+    prot = protein.from_pdb_string(open(pdb_path).read(), chain_id)
+    seq = "".join(rc.restypes_with_x[int(a)] for a in prot.aatype)
+    tag = os.path.splitext(os.path.basename(pdb_path))[0] + ("_" + chain_id if chain_id else "")
+    return _process_structure(self, seq, tag, alignment_dir, prot.atom_positions, prot.atom_mask, 0.0 if is_distillation else 1.0, is_distillation)
+
+
+def _process_mmcif(self, mmcif, alignment_dir=None, chain_id=None):
+    """Features + ground truth of one chain of a parsed mmCIF file (fastfold/data/data_pipeline.py:738-778)."""
+    from . import mmcif_parsing
+    if chain_id is None:
+        chains = list(mmcif.chain_to_seqres)
+        if len(chains) != 1:
+            raise ValueError("chain_id must be given for a file with %d chains" % len(chains))
+        chain_id = chains[0]
+    seq = mmcif.chain_to_seqres[chain_id]
+    pos, mask = mmcif_parsing.get_atom_coords(mmcif, chain_id)
+    res = mmcif.header.get("resolution", 0.0) if isinstance(mmcif.header, dict) else getattr(mmcif.header, "resolution", 0.0)
+    feats = _process_structure(self, seq, "%s_%s" % (mmcif.file_id, chain_id), alignment_dir, pos, mask, float(res or 0.0), False)
+    date = mmcif.header.get("release_date", "") if isinstance(mmcif.header, dict) else getattr(mmcif.header, "release_date", "")
+    feats["release_date"] = np.array([str(date).encode()], dtype=object)
+    return feats
+
+
+DataPipeline.process_pdb = _process_pdb
+DataPipeline.process_mmcif = _process_mmcif
+
+
 def np_to_tensor_dict(np_example, features):
     return {k: torch.tensor(np.asarray(v)) for k, v in np_example.items() if k in features and np.asarray(v).dtype != object}
 
@@ -128,7 +169,11 @@ class FeaturePipeline:
     def __init__(self, config):
         self.config = config      # the ``data`` sub-tree of ``model_config``
 
-    def process_features(self, raw_features: FeatureDict, mode: str = "predict", seed: int = 0):
+    def process_features(self, raw_features: FeatureDict, mode: str = "predict", seed: int = 0, is_multimer=None):
+        if is_multimer is None:
+            is_multimer = "asym_id" in raw_features
+        if is_multimer:
+            return self._process_multimer(raw_features, mode, seed)
         cfg = copy.deepcopy(self.config)
         mode_cfg = cfg[mode]
         raw = dict(raw_features)
@@ -162,6 +207,25 @@ class FeaturePipeline:
             per_iter.append(d)
         out = {k: torch.stack([d[k] for d in per_iter], dim=-1) for k in per_iter[0]}
         return out
+
+
+    def _process_multimer(self, raw_features, mode, seed):
+        """Merged multimer example (``DataPipelineMultimer.process_fasta``) -> model features: one pass of the multimer
+        tensor transforms per recycling iteration (fresh MSA sample each), stacked on a trailing axis
+        (fastfold/data/feature_pipeline.py:100-129, input_pipeline_multimer.py:113-136)."""
+        from . import data_transforms_multimer as dtm
+        cfg = copy.deepcopy(self.config)
+        mode_cfg = cfg[mode]
+        tensors = {k: torch.as_tensor(np.asarray(v)) for k, v in raw_features.items() if np.asarray(v).dtype != object}
+        n_iter = cfg.common.max_recycling_iters + 1
+        per_iter = []
+        for it in range(n_iter):
+            d = dtm.process_tensors({k: v.clone() for k, v in tensors.items()}, cfg.common, mode_cfg, seed=seed + it)
+            # empty placeholders (e.g. ``template_sum_probs`` when no hit carries a score) are not model inputs
+            d = {k: v for k, v in d.items() if isinstance(v, torch.Tensor) and v.numel() > 0}
+            per_iter.append(d)
+        keys = [k for k in per_iter[0] if all(k in d and d[k].shape == per_iter[0][k].shape for d in per_iter)]
+        return {k: torch.stack([d[k] for d in per_iter], dim=-1) for k in keys}
 
 
 # ---------------------------------------------------------------------------

@@ -320,8 +320,11 @@ class SelfAttention(nn.Module):
         columns (the extra-MSA stack has 8-channel heads): zero q / k channels leave the logits unchanged, zero v
         channels give zero outputs that the zero columns of the output projection ignore.  Inference only; cached."""
         H, d, D = self.n_head, self.c, flash.HEAD_DIM
-        key = (self.to_qkv.weight.data_ptr(), self.to_qkv.weight._version, self.o_linear.weight._version)
-        if getattr(self, "_pad_cache", None) is None or self._pad_cache[0] != key:
+        # Cached in eval mode only: an optimiser that updates the parameters through raw pointers (the flat fused Adam)
+        # changes neither ``_version`` nor ``data_ptr``, so in training the widened copies are rebuilt on every call.
+        key = (self.to_qkv.weight.data_ptr(), self.to_qkv.weight._version, self.o_linear.weight._version,
+               self.gating_linear.weight._version if self.gating else 0)
+        if self.training or getattr(self, "_pad_cache", None) is None or self._pad_cache[0] != key:
             def rows(w, groups):                      # [groups * H * d, ...] -> [groups * H * D, ...]
                 w = w.detach().reshape(groups, H, d, *w.shape[1:])
                 out = w.new_zeros(groups, H, D, *w.shape[3:])
@@ -492,8 +495,11 @@ class _TriangleMultiplication(nn.Module):
     def _glu_weights(self):
         """Projection and gate weights interleaved row-wise so that the GEMM epilogue sees (value, gate) pairs."""
         wp, wg = self.left_right_projection.weight, self.left_right_gate.weight
-        key = (wp._version, wg._version, wp.data_ptr(), wg.data_ptr(), wp.dtype)
-        if self._glu_cache is None or self._glu_cache[0] != key:
+        # Cached in eval mode only (see ``SelfAttention._padded_heads``): under the flat fused Adam the parameters change
+        # without a version bump, and a CUDA graph must capture the rebuild so that replays see the current weights.
+        key = (wp._version, wg._version, wp.data_ptr(), wg.data_ptr(), wp.dtype,
+               self.left_right_projection.bias._version, self.left_right_gate.bias._version)
+        if self.training or self._glu_cache is None or self._glu_cache[0] != key:
             w = torch.stack([wp.detach(), wg.detach()], dim=1).reshape(-1, wp.shape[1]).contiguous()
             b = torch.stack([self.left_right_projection.bias.detach(), self.left_right_gate.bias.detach()], dim=1).reshape(-1).contiguous()
             self._glu_cache = (key, w, b)

@@ -17,7 +17,7 @@ from ...parallel import core
 from ...parallel.comm import col_to_row, gather, row_to_col, scatter
 from ...utils.checkpointing import checkpoint_blocks
 from ..nn.template import TemplatePointwiseAttention as _PointwiseAttention
-from .evoformer import pad_amount
+from .evoformer import draw_block_dropout, pad_amount
 from .ops import (AsyncChunkTriangleMultiplicationIncoming, AsyncChunkTriangleMultiplicationOutgoing, ChunkTransition,
                   ChunkTriangleAttentionEndingNode, ChunkTriangleAttentionStartingNode)
 
@@ -47,20 +47,25 @@ class TemplatePairBlock(nn.Module):
         self.TriangleMultiplicationIncoming = AsyncChunkTriangleMultiplicationIncoming(c_t, p_drop=dropout_rate, c=c_hidden_tri_mul)
         self.PairTransition = ChunkTransition(d=c_t, n=pair_transition_n)
 
-    def _attention(self, z, mask_row, mask_col):
-        z = self.TriangleAttentionStartingNode(z, mask_row)
+    def _attention(self, z, mask_row, mask_col, d):
+        z = self.TriangleAttentionStartingNode(z, mask_row, d.get("tri_att_start"))
         z = row_to_col(z)
-        z = self.TriangleAttentionEndingNode(z, mask_col)
+        z = self.TriangleAttentionEndingNode(z, mask_col, d.get("tri_att_end"))
         return col_to_row(z)
 
-    def _multiplication(self, z, mask_row, mask_col):
-        z = self.TriangleMultiplicationOutgoing(z, mask_row)
+    def _multiplication(self, z, mask_row, mask_col, d):
+        z = self.TriangleMultiplicationOutgoing(z, mask_row, d.get("tri_mul_out"))
         z = row_to_col(z)
-        z = self.TriangleMultiplicationIncoming(z, mask_col)
+        dm = d.get("tri_mul_in")
+        if dm is not None:
+            dm = scatter(dm, dim=2)
+        z = self.TriangleMultiplicationIncoming(z, mask_col, dm)
         return col_to_row(z)
 
-    def forward(self, z, mask, chunk_size=None, _mask_trans=True):
-        """``z [*, N_templ, N, N, c_t]`` (full on the first block, row shards afterwards), ``mask [*, N_templ, N, N]``."""
+    def forward(self, z, mask, chunk_size=None, _mask_trans=True, _drop=None):
+        """``z [*, N_templ, N, N, c_t]`` (full on the first block, row shards afterwards), ``mask [*, N_templ, N, N]``.
+        ``_drop``: one dict of axis-shared dropout masks per template (``draw_block_dropout``), drawn by the stack outside
+        its activation-checkpoint boundary so that the recomputation in backward sees the masks of the first pass."""
         P = core.get_dap_size()
         n = mask.shape[-1]
         pad = pad_amount(n, P)
@@ -73,10 +78,13 @@ class TemplatePairBlock(nn.Module):
             s = z[..., i, :, :, :].reshape((1,) + z.shape[-3:])
             m = mask[..., i, :, :].reshape((1,) + mask.shape[-2:])
             m_row, m_col = scatter(m, dim=1), scatter(m, dim=2)
+            d = {}
+            if self.training and self.p_drop > 0:
+                d = _drop[i] if _drop is not None else draw_block_dropout(n + pad, 0, self.c_t, s.device, s.dtype, p_pair=self.p_drop, n_res=n)
             if self.tri_mul_first:
-                s = self._attention(self._multiplication(s, m_row, m_col), m_row, m_col)
+                s = self._attention(self._multiplication(s, m_row, m_col, d), m_row, m_col, d)
             else:
-                s = self._multiplication(self._attention(s, m_row, m_col), m_row, m_col)
+                s = self._multiplication(self._attention(s, m_row, m_col, d), m_row, m_col, d)
             s = self.PairTransition(s)
             outs.append(s)
         z = torch.stack([o[0] for o in outs], dim=0).reshape(z.shape)
@@ -102,8 +110,16 @@ class TemplatePairStack(nn.Module):
             expand_idx = list(mask.shape)
             expand_idx[-3] = t.shape[-4]
             mask = mask.expand(*expand_idx)
-        (t,) = checkpoint_blocks([partial(b, mask=mask, chunk_size=chunk_size, _mask_trans=_mask_trans) for b in self.blocks], args=(t,),
-                                 blocks_per_ckpt=self.blocks_per_ckpt if self.training else None)
+        fns = []
+        n = mask.shape[-1]
+        n_pad = n + pad_amount(n, core.get_dap_size())
+        for b in self.blocks:
+            drop = None
+            if self.training and b.p_drop > 0:
+                # masks are inputs of the checkpointed function, not random draws inside it (no RNG state is saved)
+                drop = [draw_block_dropout(n_pad, 0, b.c_t, t.device, t.dtype, p_pair=b.p_drop, n_res=n) for _ in range(t.shape[-4])]
+            fns.append(partial(b, mask=mask, chunk_size=chunk_size, _mask_trans=_mask_trans, _drop=drop))
+        (t,) = checkpoint_blocks(fns, args=(t,), blocks_per_ckpt=self.blocks_per_ckpt if self.training else None)
         return self.layer_norm(t)
 
     def inplace(self, t, mask, chunk_size=None, _mask_trans=True):

@@ -57,7 +57,7 @@ def load_checkpoint(path, model, trainer, scheduler, device):
 def _load_openfold_named(model, sd):
     """Loads OpenFold-named tensors into an injected model by building an un-injected twin, loading, re-injecting."""
     from ..models.hub import AlphaFold
-    from ..utils.inject_fastnn import copy_evoformer_block, copy_extra_msa_block, _copy_linear
+    from ..utils.inject_fastnn import copy_evoformer_block, copy_extra_msa_block, copy_template_pair_block, _copy_linear
     import copy
     twin = AlphaFold(_config_of(model))
     twin.load_state_dict(sd, strict=True)
@@ -67,9 +67,20 @@ def _load_openfold_named(model, sd):
         _copy_linear(model.evoformer.linear, twin.evoformer.linear)
         for fb, ob in zip(model.extra_msa_stack.blocks, twin.extra_msa_stack.blocks):
             copy_extra_msa_block(fb, ob)
+        tps = getattr(getattr(model, "template_embedder", None), "template_pair_stack", None)
+        skip = ("evoformer.", "extra_msa_stack.")
+        if tps is not None and hasattr(tps.blocks[0], "TriangleAttentionStartingNode"):
+            # injected template stack: fast parameter names, filled through the same copy helpers as ``inject_fastnn``
+            otps = twin.template_embedder.template_pair_stack
+            for fb, ob in zip(tps.blocks, otps.blocks):
+                copy_template_pair_block(fb, ob)
+            tps.layer_norm.load_state_dict(otps.layer_norm.state_dict())
+            skip = skip + ("template_embedder.template_pair_stack.",)
         own = model.state_dict()
         for k, v in twin.state_dict().items():
-            if not (k.startswith("evoformer.") or k.startswith("extra_msa_stack.")):
+            if not k.startswith(skip):
+                if k not in own:
+                    raise KeyError("checkpoint tensor %r has no counterpart in the model" % k)
                 own[k].copy_(v)
 
 

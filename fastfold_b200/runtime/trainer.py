@@ -25,6 +25,43 @@ from ..ops import _lib
 from ..parallel import core
 
 
+# Module paths whose parameters act on DAP-sharded activations (each rank sees its shard only, so their gradients are
+# summed over the DAP group).  Everything else - embedders, the stacks' closing LayerNorm / projection, structure module,
+# heads - runs replicated on the gathered tensors and holds identical gradients on every DAP rank.
+DAP_SHARDED_PREFIXES = ("evoformer.blocks.", "extra_msa_stack.blocks.", "template_embedder.template_pair_stack.blocks.",
+                        "template_pair_stack.blocks.", "blocks.")
+
+
+def default_replicated_param_filter(name):
+    """``True`` for parameters used in computation that is replicated over the DAP group (their summed gradient is
+    divided by the DAP size).  The fast template pair stack scatters its rows between its first and last block, so its
+    blocks count as sharded; its closing LayerNorm runs on the gathered tensor and stays replicated."""
+    return not name.startswith(DAP_SHARDED_PREFIXES)
+
+
+def check_device_status(reader=None):
+    """Reads the kernels' status word where the host synchronises anyway and raises on EVERY rank when any rank's
+    kernels gave up on a bounded wait (a peer that never signalled, a tile that never landed): such a kernel skips the
+    data it could not get, so continuing would train or predict on unwritten buffers.  ``reader`` (tests) replaces the
+    device read and returns the status list."""
+    if reader is None:
+        if not torch.cuda.is_available():
+            return
+        reader = _lib.read_status
+    st = list(reader())
+    code = int(st[0])
+    worst, who = code, core.get_rank()
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
+        t = torch.tensor([code, core.get_rank() if code else -1], device=dev, dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst, who = int(t[0]), int(t[1])
+    if worst != 0:
+        raise RuntimeError("fastfold_b200: device status %d reported on rank %d (local status %s: code, block x/y/z, detail); "
+                           "1 = operand tile never landed, 2 = tensor-core commit missing, 3 = accumulator barrier, "
+                           "4 = a peer GPU never raised its flag" % (worst, who, st[:5]))
+
+
 class FlatAdamTrainer:
     def __init__(self, model, loss_fn, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, use_graph=True,
                  replicated_param_filter=None, grad_reducer=None, grad_sink=True):
@@ -179,6 +216,10 @@ class FlatAdamTrainer:
         self.graph.replay()
         self.step_count += 1
         return self.static_loss
+
+    def check_status(self, reader=None):
+        """Raise (on all ranks) if any rank's kernels recorded a failed wait since the last check; synchronises."""
+        check_device_status(reader)
 
     def state_dict(self):
         return {"step": self.step_count, "master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,

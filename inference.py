@@ -75,8 +75,20 @@ def main(args):
         from fastfold_b200.data.templates import TemplateHitFeaturizer
         featurizer = TemplateHitFeaturizer(mmcif_dir=args.template_mmcif_dir, max_template_date=args.max_template_date, max_hits=4,
                                            kalign_binary_path=args.kalign_binary_path)
-    raw = DataPipeline(template_featurizer=featurizer).process_sequence(seqs[0], tag, alignment_dir)
-    feats = FeaturePipeline(config.data).process_features(raw, mode="predict", seed=args.data_random_seed or 0)
+    if args.model_preset == "multimer":
+        # every chain of the FASTA goes through the monomer pipeline (alignments under <alignment_dir>/<chain id>/), the
+        # chains are paired by species and merged (fastfold inference.py:169-338)
+        from fastfold_b200.data.data_pipeline import DataPipelineMultimer
+        if args.use_precomputed_alignments:
+            alignment_dir = args.use_precomputed_alignments
+        raw = DataPipelineMultimer(DataPipeline(template_featurizer=featurizer)).process_fasta(args.fasta_path, alignment_dir)
+        if int(np.asarray(raw["aatype"]).shape[0]) != sum(len(s_) for s_ in seqs):
+            raise RuntimeError("multimer feature assembly lost residues: %d featurised, %d in the FASTA file"
+                               % (int(np.asarray(raw["aatype"]).shape[0]), sum(len(s_) for s_ in seqs)))
+    else:
+        raw = DataPipeline(template_featurizer=featurizer).process_sequence(seqs[0], tag, alignment_dir)
+    feats = FeaturePipeline(config.data).process_features(raw, mode="predict", seed=args.data_random_seed or 0,
+                                                          is_multimer=args.model_preset == "multimer")
     overrides = {}
     if "template_aatype" not in feats:
         overrides["model.template.enabled"] = False
@@ -85,6 +97,8 @@ def main(args):
     print("Inference time: %.3f s (device-timed), peak memory %.2f GiB" % (out["_seconds"], out["_peak_gib"]))
     plddt_b = np.repeat(out["plddt"][..., None], 37, axis=-1)
     f = {"aatype": feats["aatype"][..., 0].numpy(), "residue_index": feats["residue_index"][..., 0].numpy()}
+    if "asym_id" in feats:
+        f["asym_id"] = feats["asym_id"][..., 0].numpy()
     prot = protein.from_prediction(f, out, b_factors=plddt_b)
     path = os.path.join(args.output_dir, "%s_%s_unrelaxed.pdb" % (tag, args.model_name))
     with open(path, "w") as fh:

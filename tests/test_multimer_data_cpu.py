@@ -70,3 +70,34 @@ def test_multimer_tensor_pipeline():
     assert (out["true_msa"][0] == tens["msa"][0]).all()
     prof = out["msa_feat"][..., 25:48]
     assert torch.allclose(prof.sum(-1)[out["msa_mask"] > 0], torch.ones_like(prof.sum(-1)[out["msa_mask"] > 0]), atol=1e-3)
+
+
+def test_multimer_fasta_to_structure(tmp_path):
+    """All chains of the FASTA file reach the model: features of a two-chain complex -> multimer model -> coordinates."""
+    import torch
+    from fastfold_b200.config import model_config
+    from fastfold_b200.data.data_pipeline import FeaturePipeline
+    from fastfold_b200.models.hub import AlphaFold
+    from fastfold_b200.utils.inject_fastnn import inject_fastnn
+    from fastfold_b200.common import protein
+    fasta = tmp_path / "c.fasta"
+    fasta.write_text(">A first\nACDEFGHIKL\n>B second\nMNPQRSTVWY\n")
+    raw = DataPipelineMultimer(DataPipeline()).process_fasta(str(fasta))
+    cfg = model_config("multimer")
+    cfg.data.predict.max_msa_clusters = 8
+    cfg.data.predict.max_extra_msa = 8
+    cfg.data.common.max_recycling_iters = 1
+    feats = FeaturePipeline(cfg.data).process_features(raw, mode="predict", seed=0)
+    assert feats["aatype"].shape == (20, 2) and feats["msa_feat"].shape == (8, 20, 49, 2)
+    assert sorted(set(feats["asym_id"][..., 0].tolist())) == [1, 2]
+    cfg.model.evoformer_stack.no_blocks = 1
+    cfg.model.extra_msa.extra_msa_stack.no_blocks = 1
+    torch.manual_seed(0)
+    model = inject_fastnn(AlphaFold(cfg)).eval()
+    with torch.no_grad():
+        out = model(feats)
+    assert out["final_atom_positions"].shape == (20, 37, 3) and torch.isfinite(out["final_atom_positions"]).all()
+    f = {"aatype": feats["aatype"][..., 0].numpy(), "residue_index": feats["residue_index"][..., 0].numpy(), "asym_id": feats["asym_id"][..., 0].numpy()}
+    pdb = protein.to_pdb(protein.from_prediction(f, {k: v.numpy() for k, v in out.items() if isinstance(v, torch.Tensor)}))
+    chains = {ln[21] for ln in pdb.splitlines() if ln.startswith("ATOM")}
+    assert chains == {"A", "B"}

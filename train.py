@@ -62,6 +62,7 @@ def main():
     from fastfold_b200.models.hub import AlphaFold, AlphaFoldLoss, AlphaFoldLRScheduler
     from fastfold_b200.parallel import core, init_dap
     from fastfold_b200.runtime import FlatAdamTrainer
+    from fastfold_b200.runtime.trainer import default_replicated_param_filter
     from fastfold_b200.runtime.checkpoint import load_checkpoint, save_checkpoint
     from fastfold_b200.utils.inject_fastnn import inject_fastnn
     from fastfold_b200.utils.tensor_utils import tensor_tree_map
@@ -106,7 +107,7 @@ def main():
     # the full model's feature dict is not a flat tensor list and the number of recycling iterations varies per
     # step, so the step runs eagerly here; the Evoformer benchmark (bench.py) shows the captured-graph path
     trainer = FlatAdamTrainer(model, loss_fn, lr=args.lr, eps=1e-8, use_graph=False,
-                              replicated_param_filter=lambda n: not (n.startswith("evoformer.blocks") or n.startswith("extra_msa_stack.blocks")))
+                              replicated_param_filter=default_replicated_param_filter)
     sched = AlphaFoldLRScheduler(trainer, max_lr=args.lr)
     start_epoch = 0
     if args.resume:
