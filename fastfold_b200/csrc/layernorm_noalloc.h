@@ -17,9 +17,11 @@
 // The call performs no cudaMalloc / cudaFree and calls no allocating library routine; the caller passes every
 // input and output buffer.  The first call on a device resolves the array's device address
 // (cudaGetSymbolAddress) with that device current - make that first call outside any stream capture.  All calls
-// share the one array: it is cleared (cudaMemsetAsync on the given stream) at the start of every call, and two
-// calls that overlap on the GPU (different streams, or different host threads on one device) race on it -
-// serialise them.
+// share the one array, which still holds the previous call's partial sums.  What a call accumulates into is cleared
+// first (cudaMemsetAsync on the given stream); the bf16 kernels for C = 64 / 128 / 256 skip that memset because every
+// block of theirs stores (not adds) each of its partial sums before the final reduction reads them, so stale contents
+// are overwritten.  Two calls that overlap on the GPU (different streams, or different host threads on one device)
+// race on the array - serialise them.
 #pragma once
 
 #define FFB_LN_NOALLOC_BLOCKS 148

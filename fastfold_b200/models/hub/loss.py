@@ -366,7 +366,10 @@ class AlphaFoldLoss(nn.Module):
         for name, fn in loss_fns.items():
             weight = self.config[name].weight
             loss = fn()
-            if torch.isnan(loss) or torch.isinf(loss):
+            if loss.is_cuda and torch.cuda.is_current_stream_capturing():
+                # no host read inside a CUDA-graph capture: a non-finite term is replaced on the device
+                loss = torch.where(torch.isfinite(loss), loss, torch.zeros_like(loss))
+            elif torch.isnan(loss) or torch.isinf(loss):
                 logging.warning("%s loss is NaN. Skipping...", name)
                 loss = loss.new_tensor(0.0, requires_grad=True)
             cum_loss = cum_loss + weight * loss

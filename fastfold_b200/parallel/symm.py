@@ -91,6 +91,13 @@ class SymmHeap:
         dist.barrier(group)            # every pad is zeroed before any rank raises a flag in it
         torch.cuda.synchronize()
 
+    def poison(self):
+        """Fills this rank's slab with 0xFF bytes (NaN in every floating-point format) - test aid: a consumer that reads
+        a peer slot before its producer wrote it, or beyond what was written, then sees NaN instead of stale data."""
+        self.heap.fill_(0xFF)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
     def make_ring(self, n_slots, slot_bytes):
         """A ring of equally sized slots for the activation collectives; consecutive collectives take consecutive
         slots, so a slot is reused only after ``n_slots - 1`` other exchanges (the flag protocol makes reuse safe)."""

@@ -52,6 +52,8 @@ def _worker(rank, world, port, batch, opts, queue):
             e1.record()
             torch.cuda.synchronize()
             seconds = e0.elapsed_time(e1) / 1e3
+            from .trainer import check_device_status
+            check_device_status()        # a kernel that gave up on a wait leaves unwritten outputs: fail on every rank
         else:
             seconds = time.perf_counter() - t0
     peak = torch.cuda.max_memory_allocated() / 2 ** 30 if cuda else 0.0

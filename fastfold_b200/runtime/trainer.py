@@ -76,6 +76,9 @@ class FlatAdamTrainer:
         self.graph = None
         self.static_inputs = None
         self.static_loss = None
+        self.graph_fallback = False  # True: a failed capture switches to eager steps instead of raising
+        self._graphs = {}            # graph_key -> (graph, static inputs, static loss, launches)
+        self._graph_pool = None
         self.grad_reducer = grad_reducer
         self.launches_per_step = None
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
@@ -182,15 +185,36 @@ class FlatAdamTrainer:
         return loss.detach()
 
     # ------------------------------------------------------------------
-    def step(self, *inputs):
-        """One optimisation step; returns the (device) loss tensor of this step."""
+    def step(self, *inputs, graph_key=None):
+        """One optimisation step; returns the (device) loss tensor of this step.
+
+        ``graph_key``: steps whose kernel sequence differs (e.g. the number of recycling iterations of the full model)
+        get one captured graph per key, sharing one memory pool; inputs of a key must keep their shapes."""
         self._set_hp()
+        if self.use_graph and graph_key is not None:
+            if graph_key in self._graphs:
+                self.graph, self.static_inputs, self.static_loss, self.launches_per_step = self._graphs[graph_key]
+            else:
+                self.graph = None
         if not self.use_graph:
             n0 = _lib.LAUNCHES[0]
             loss = self._body(inputs)
             self.launches_per_step = _lib.LAUNCHES[0] - n0
             self.step_count += 1
             return loss
+        if self.graph is None and self.graph_fallback:
+            try:
+                return self._capture_and_replay(inputs, graph_key)
+            except Exception as e:      # noqa: BLE001 - e.g. an op that reads a value on the host during capture
+                import logging
+                logging.getLogger("fastfold_b200").warning("CUDA-graph capture of the training step failed (%s); running eagerly", repr(e)[:200])
+                torch.cuda.synchronize()
+                self.use_graph = False
+                self.graph = None
+                return self.step(*inputs)
+        return self._capture_and_replay(inputs, graph_key)
+
+    def _capture_and_replay(self, inputs, graph_key):
         if self.graph is None:
             self.static_inputs = [x.clone() if isinstance(x, torch.Tensor) else x for x in inputs]
             # warm-up on a side stream (allocator, cuBLAS handles, NCCL channels), then capture
@@ -204,11 +228,15 @@ class FlatAdamTrainer:
             # the two warm-up passes are real optimisation steps and are counted as such
             self.graph = torch.cuda.CUDAGraph()
             n0 = _lib.LAUNCHES[0]
-            with torch.cuda.graph(self.graph):
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(self.graph, pool=self._graph_pool):
                 self.static_loss = self._body(self.static_inputs)
             self.launches_per_step = _lib.LAUNCHES[0] - n0
             self.step_count += 2
             self._set_hp()
+            if graph_key is not None:
+                self._graphs[graph_key] = (self.graph, self.static_inputs, self.static_loss, self.launches_per_step)
         else:
             for dst, src in zip(self.static_inputs, inputs):
                 if isinstance(dst, torch.Tensor) and dst.data_ptr() != src.data_ptr():

@@ -30,3 +30,19 @@ def device_status():
         from fastfold_b200.ops import _lib
         st = _lib.read_status()
         assert st[0] == 0, "device status word: %s" % st[:5]
+
+
+@pytest.fixture(autouse=True)
+def _poison_free_gpu_memory(request):
+    """GPU tests only: fills a block of device memory with 0xFF bytes (NaN as bf16 / fp16 / fp32) and hands it back to the
+    caching allocator, so that the ``torch.empty`` workspaces and outputs of the test start out as NaN - a kernel that
+    leaves part of its output unwritten, or reads scratch it never filled, then fails its comparison instead of passing
+    on stale data of an earlier test."""
+    if "gpu" in request.keywords and torch.cuda.is_available():
+        free, _ = torch.cuda.mem_get_info()
+        n = int(min(2 << 30, free // 4))
+        if n > 0:
+            blocks = [torch.empty(n // 4, dtype=torch.uint8, device="cuda").fill_(0xFF) for _ in range(4)]
+            torch.cuda.synchronize()
+            del blocks
+    yield

@@ -32,10 +32,14 @@ def _worker(rank, world, port, out_path):
     init_dap(world, timeout_s=60)
     dev = torch.device("cuda", rank)
     h = symm.get_heap("dap")
+    h.poison()                       # every slot starts as NaN: reading a slot before it is written cannot pass
+    import time
     res = {}
+    skew = lambda k: time.sleep(0.02 * ((rank * 7 + k) % world))     # ranks reach each collective at different times
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
     # all-gather
     x = torch.randn(64, 40, generator=g).to(dev, torch.bfloat16)
+    skew(0)
     got = h.all_gather(None, x)
     ref = [torch.empty_like(x) for _ in range(world)]
     dist.all_gather(ref, x)
@@ -44,13 +48,15 @@ def _worker(rank, world, port, out_path):
     worst = 0.0
     for it in range(30):
         send = torch.randn(world, 33, 16, generator=g).to(dev, torch.bfloat16)
+        if it % 7 == 0:
+            skew(it)
         recv = h.all_to_all(None, send)
         ref = torch.empty_like(send)
         dist.all_to_all_single(ref, send)
         worst = max(worst, float((recv.float() - ref.float()).abs().max()))
     res["all_to_all"] = worst
     # fused axis switch + LayerNorm, both directions, with and without transposed output
-    A, B, C = 8, 12, 128
+    A, B, C = 8 * world // 2, 12 * world // 2, 128
     gamma = (torch.randn(C, generator=torch.Generator().manual_seed(1)) * 0.3 + 1).to(dev, torch.bfloat16)
     beta = (torch.randn(C, generator=torch.Generator().manual_seed(2)) * 0.1).to(dev, torch.bfloat16)
     full = torch.randn(A, B, C, generator=torch.Generator().manual_seed(3)).to(dev, torch.bfloat16)
@@ -63,6 +69,7 @@ def _worker(rank, world, port, out_path):
             else:
                 shard = full[:, rank * (B // world):(rank + 1) * (B // world)]
                 want = full[rank * (A // world):(rank + 1) * (A // world)]
+            skew(mode * 2 + int(tr))
             raw, norm = h.a2a_layer_norm(None, shard, mode, A, B, C, gamma, beta, 1e-5, True, tr)
             wn = torch.nn.functional.layer_norm(want.float(), (C,), gamma.float(), beta.float(), 1e-5)
             if tr:
@@ -101,7 +108,6 @@ def _worker(rank, world, port, out_path):
     res["status_before"] = _lib.read_status()[0]
     dist.barrier()
     # bounded wait: must come back with ST_TIMEOUT_PEER (4) after about a second
-    import time
     t0 = time.time()
     h.wait_never(h.slot("never", 1024))
     torch.cuda.synchronize()
@@ -113,12 +119,13 @@ def _worker(rank, world, port, out_path):
     shutdown()
 
 
-def test_symm_collectives():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_symm_collectives(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
     with tempfile.TemporaryDirectory() as d:
         out_path = os.path.join(d, "o.pt")
-        mp.spawn(_worker, args=(2, _free_port(), out_path), nprocs=2, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), out_path), nprocs=world, join=True)
         res = torch.load(out_path)
     assert res["all_gather"] == 0.0
     assert res["all_to_all"] == 0.0

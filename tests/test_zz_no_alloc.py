@@ -4,8 +4,8 @@ Some hosts of the library may not allocate device memory while they run (pre-siz
 loops, plug-ins under a foreign allocator); for them ``ffb_layernorm_bwd_noalloc`` keeps its scratch in a static
 device array.  The test calls it with raw pointers, twice in a row (the array keeps the previous call's contents,
 so the second call checks that it is cleared correctly), and compares dx / dgamma / dbeta with the regular entry
-point ``ffb_layernorm_bwd`` on the same inputs; it also checks that a row wider than the built-in capacity is
-refused.  Runs last in the suite (file name) and also on its own in a fresh process.
+point ``ffb_layernorm_bwd`` on the same inputs and with the fp32 gradients of ``torch.nn.functional.layer_norm``; it
+also checks that a row wider than the built-in capacity is refused.  Runs last in the suite (file name) and also on its own in a fresh process.
 """
 import ctypes
 
@@ -59,6 +59,15 @@ def test_noalloc_matches_regular_entry_point_twice(dtype, code, tol):
         assert lib.ffb_layernorm_bwd_noalloc(_p(dy), _p(x), _p(gamma), _p(mean), _p(rstd), _p(dx_b), _p(dg_b), _p(db_b), rows, C, code,
                                              stream) == 0
         torch.cuda.synchronize()
+        # independent oracle: autograd through torch's own LayerNorm in fp32 on the same (rounded) inputs
+        xr = x.float().requires_grad_(True)
+        gr = gamma.float().requires_grad_(True)
+        br = beta.float().requires_grad_(True)
+        torch.nn.functional.layer_norm(xr, (C,), gr, br, 1e-5).backward(dy.float())
+        ref_tol = 5e-2 if dtype == torch.bfloat16 else 1e-3
+        assert (dx_b.float() - xr.grad).abs().max().item() <= ref_tol * max(1.0, xr.grad.abs().max().item())
+        assert (dg_b.float() - gr.grad).abs().max().item() <= ref_tol * max(1.0, gr.grad.abs().max().item())
+        assert (db_b.float() - br.grad).abs().max().item() <= ref_tol * max(1.0, br.grad.abs().max().item())
         assert (dx_a.float() - dx_b.float()).abs().max().item() <= tol
         scale = max(1.0, dg_a.float().abs().max().item())
         assert (dg_a.float() - dg_b.float()).abs().max().item() <= tol * scale

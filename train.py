@@ -52,7 +52,9 @@ def parse():
     p.add_argument("--n_extra", type=int, default=None)
     p.add_argument("--blocks", type=int, default=None, help="override the number of Evoformer blocks (debugging)")
     p.add_argument("--lr", type=float, default=1e-3)
-    p.add_argument("--no_graph", default=False, action="store_true")
+    p.add_argument("--no_graph", default=False, action="store_true", help="run every step eagerly instead of replaying captured CUDA graphs")
+    p.add_argument("--val_interval", type=int, default=1, help="epochs between validation passes")
+    p.add_argument("--val_epoch_len", type=int, default=2, help="(synthetic) validation samples per pass; 0 disables")
     return p.parse_args()
 
 
@@ -97,22 +99,68 @@ def main():
         dataset = StructureDataset(args.train_data_dir, args.train_alignment_dir, config.data, mode="train", seed=args.seed,
                                    dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size())
 
-    def loss_fn(mod, batch):
+    def loss_fn(mod, *tensors):
+        batch = dict(zip(loss_fn.keys, tensors))
         out = mod(batch)
         last = tensor_tree_map(lambda t: t[..., -1], batch)
         loss, parts = criterion(out, last, _return_breakdown=True)
         loss_fn.last = (out, last, parts)
         return loss
 
-    # the full model's feature dict is not a flat tensor list and the number of recycling iterations varies per
-    # step, so the step runs eagerly here; the Evoformer benchmark (bench.py) shows the captured-graph path
-    trainer = FlatAdamTrainer(model, loss_fn, lr=args.lr, eps=1e-8, use_graph=False,
+    # With fixed feature shapes (synthetic data, or cropped + padded training features) the whole step - all recycling
+    # iterations, loss, backward with recomputation, gradient reduction, Adam - is captured as one CUDA graph per number
+    # of recycling iterations and replayed, exactly what bench.py measures on the Evoformer stack.  A capture that fails
+    # (an op that needs a host read) falls back to eager steps.
+    use_graph = cuda and not args.no_graph
+    trainer = FlatAdamTrainer(model, loss_fn, lr=args.lr, eps=1e-8, use_graph=use_graph,
                               replicated_param_filter=default_replicated_param_filter)
+    trainer.graph_fallback = True
     sched = AlphaFoldLRScheduler(trainer, max_lr=args.lr)
     start_epoch = 0
     if args.resume:
         start_epoch = load_checkpoint(args.resume, model, trainer, sched, device)
         log.info("resumed from %s at step %d (epoch %d)", args.resume, trainer.step_count, start_epoch)
+
+    val_dataset = None
+    if args.val_data_dir:
+        from fastfold_b200.data.data_modules import StructureDataset
+        val_dataset = StructureDataset(args.val_data_dir, args.val_alignment_dir, config.data, mode="eval", seed=args.seed,
+                                       dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size())
+    elif args.synthetic and args.val_epoch_len > 0:
+        from fastfold_b200.data.data_modules import SyntheticDataset
+        val_dataset = SyntheticDataset(n_res, n_seq, n_extra, n_recycle=config.data.common.max_recycling_iters, length=args.val_epoch_len,
+                                       seed=args.seed + 7919, dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size(), uniform_recycling=False,
+                                       n_templ=tc.max_templates if config.model.template.enabled else 0)
+
+    def validate(epoch):
+        """Validation pass of the reference's train.py:240-251: eval mode, no gradients, unclamped FAPE, superposition
+        metrics; averages over this replica's samples and over the data-parallel replicas."""
+        model.eval()
+        sums, count = {}, 0
+        with torch.no_grad():
+            for i in range(len(val_dataset)):
+                batch = val_dataset.get(0, i)
+                batch.pop("no_recycling_iters", None)
+                batch = {k: v.to(device, non_blocking=True) for k, v in batch.items()}
+                batch["use_clamped_fape"] = torch.zeros_like(batch["use_clamped_fape"]) if "use_clamped_fape" in batch else torch.zeros(
+                    batch["aatype"].shape[-1], device=device)
+                out = model(batch)
+                last = tensor_tree_map(lambda t: t[..., -1], batch)
+                _, parts = criterion(out, last, _return_breakdown=True)
+                parts.update(validation_metrics(out, last, superimposition_metrics=True))
+                for k, v in parts.items():
+                    sums[k] = sums.get(k, 0.0) + float(v)
+                count += 1
+        model.train()
+        keys = sorted(sums)
+        t = torch.tensor([sums[k] for k in keys] + [float(count)], device=device, dtype=torch.float64)
+        if core.get_world_size() > 1:
+            torch.distributed.all_reduce(t)
+        means = {k: float(t[j] / t[-1].clamp(min=1)) for j, k in enumerate(keys)}
+        if rank == 0:
+            log.info("validation epoch %d (%d samples) | %s", epoch, int(t[-1]), " ".join("%s %.4f" % (k, v) for k, v in means.items()))
+        return means
+
     steps_done = 0
     for epoch in range(start_epoch, args.max_epochs):
         t_epoch = time.time()
@@ -120,20 +168,26 @@ def main():
             batch = dataset.get(epoch, i)
             n_iter = int(batch.pop("no_recycling_iters", torch.tensor(batch["aatype"].shape[-1] - 1)).reshape(-1)[0]) + 1
             batch = {k: v[..., :n_iter].to(device, non_blocking=True) for k, v in batch.items()}
-            loss = trainer.step(batch)
+            loss_fn.keys = sorted(batch)
+            loss = trainer.step(*[batch[k] for k in loss_fn.keys], graph_key=(n_iter,) + tuple(loss_fn.keys))
             sched.step()
             steps_done += 1
-            if rank == 0 and (i + 1) % args.log_interval == 0:
-                out, last, parts = loss_fn.last
-                with torch.no_grad():
-                    metrics = validation_metrics(out, last)
-                log.info("epoch %d step %d lr %.2e loss %.4f | %s | %s", epoch, trainer.step_count, trainer.lr, float(loss),
-                         " ".join("%s %.3f" % (k, float(v)) for k, v in parts.items() if k not in ("loss", "unscaled_loss")),
-                         " ".join("%s %.3f" % (k, float(v)) for k, v in metrics.items()))
+            if (i + 1) % args.log_interval == 0:
+                trainer.check_status()       # every rank: a kernel that gave up on a wait must stop the run, not train on garbage
+                if rank == 0:
+                    out, last, parts = loss_fn.last
+                    with torch.no_grad():
+                        metrics = validation_metrics(out, last)
+                    log.info("epoch %d step %d lr %.2e loss %.4f | %s | %s", epoch, trainer.step_count, trainer.lr, float(loss),
+                             " ".join("%s %.3f" % (k, float(v)) for k, v in parts.items() if k not in ("loss", "unscaled_loss")),
+                             " ".join("%s %.3f" % (k, float(v)) for k, v in metrics.items()))
             if args.max_steps and steps_done >= args.max_steps:
                 break
         log.info("epoch %d done in %.1f s", epoch, time.time() - t_epoch)
+        if val_dataset is not None and (epoch + 1) % args.val_interval == 0:
+            validate(epoch)
         if args.save_ckpt_path and (epoch + 1) % args.save_ckpt_interval == 0:
+            trainer.check_status()
             save_checkpoint(os.path.join(args.save_ckpt_path, "checkpoint.pt"), model, trainer, sched, epoch + 1)
             if rank == 0:
                 log.info("checkpoint written to %s", args.save_ckpt_path)
