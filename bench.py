@@ -47,7 +47,23 @@ def parse():
     ap.add_argument("--no-graph", action="store_true", help="disable CUDA-graph replay of the step")
     ap.add_argument("--msa", type=int, default=S_MSA)
     ap.add_argument("--res", type=int, default=N_RES)
-    return ap.parse_args()
+    ap.add_argument("--metric", default="train", choices=["train", "inference"],
+                    help="train: Evoformer-48 training step (default, the headline); inference: full-model monomer prediction latency")
+    ap.add_argument("--n-res", type=int, default=2048, help="(inference) residues")
+    ap.add_argument("--n-seq", type=int, default=512, help="(inference) clustered MSA rows")
+    ap.add_argument("--n-extra", type=int, default=1024, help="(inference) extra MSA rows")
+    ap.add_argument("--recycles", type=int, default=3, help="(inference) recycling iterations after the first pass")
+    ap.add_argument("--chunk-size", type=int, default=64)
+    ap.add_argument("--no-inplace", action="store_true")
+    a = ap.parse_args()
+    if a.metric == "inference":
+        # one call is seconds long: fewer repetitions unless asked for explicitly
+        argv = " ".join(sys.argv[1:])
+        if "--steps" not in argv:
+            a.steps = 2
+        if "--warmup" not in argv:
+            a.warmup = 1
+    return a
 
 
 class ClockSampler:
@@ -356,6 +372,167 @@ def run_reference(args):
     return 0
 
 
+# ---------------------------------------------------------------------------
+# Second half of the metric: full-model monomer inference latency (N_res 2048, N_seq 512, N_extra 1024, 3 recycles,
+# chunk 64, in place, bf16, no templates), DAP over all ranks.  Both arms get the same synthetic features.
+# ---------------------------------------------------------------------------
+def inference_features(torch, args):
+    """Synthetic monomer features of the named shape, recycling axis last, on pinned host memory (fp32 / int64)."""
+    sys.path.insert(0, ROOT)
+    from fastfold_b200.utils.synthetic import random_features
+    feats = random_features(args.n_res, args.n_seq, args.n_extra, n_templ=0, n_recycle=args.recycles, seed=0)
+    if torch.cuda.is_available():
+        feats = {k: v.pin_memory() for k, v in feats.items()}
+    return feats
+
+
+def _inference_json(args, world, impl, ms, e2e_ms, clocks, h2d, d2h, peak_gib, extra):
+    out = {
+        "metric": "monomer_inference_latency", "value": ms / 1e3, "unit": "s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic features (one-hot / Bernoulli / Dirichlet as in the training benchmark), random-init weights", "impl": impl,
+        "config": {"model": "AlphaFold monomer (model_3 layout: 4 extra-MSA blocks, 48 Evoformer blocks, 8 structure-module iterations, no templates)",
+                   "global_batch": 1, "seq_len": args.n_res, "n_seq": args.n_seq, "n_extra": args.n_extra, "recycles": args.recycles,
+                   "chunk_size": args.chunk_size, "inplace": not args.no_inplace, "parallelism": "dap%d" % world,
+                   "l2": "inputs and activations far larger than L2 (pair tensor %.0f MB)" % (args.n_res * args.n_res * 128 * 2 / 1e6)},
+        "clocks": clocks,
+        "e2e": {"value": e2e_ms / 1e3, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "peak_gib_per_gpu": peak_gib,
+    }
+    out.update(extra)
+    return out
+
+
+def _time_inference(torch, dist, args, device, call, feats):
+    """``call(feats_on_host) -> final positions (device tensor)``; returns (device ms per call, e2e ms per call, clocks, d2h bytes)."""
+    for _ in range(args.warmup):
+        call(feats)
+    fence(torch, dist)
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    dev_feats = {k: v.to(device, non_blocking=True) for k, v in feats.items()}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fence(torch, dist)
+    e0.record()
+    for _ in range(args.steps):
+        call(dev_feats)
+    e1.record()
+    fence(torch, dist)
+    ms = max_over_ranks(torch, dist, e0.elapsed_time(e1) / args.steps, device)
+    del dev_feats
+    # end to end: features from pinned host memory every call, predicted coordinates read back to the host
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fence(torch, dist)
+    e0.record()
+    d2h = 0
+    for _ in range(args.steps):
+        pos = call(feats)
+        host = pos.float().cpu()
+        d2h = host.numel() * host.element_size()
+    e1.record()
+    fence(torch, dist)
+    e2e = max_over_ranks(torch, dist, e0.elapsed_time(e1) / args.steps, device)
+    return ms, e2e, sampler.stop(), d2h
+
+
+def run_ours_inference(args):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    from fastfold_b200.ops import _lib
+    from fastfold_b200.parallel import core, init_dap
+    from fastfold_b200.runtime.inference import load_model, predict
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    init_dap(world)
+    assert torch.cuda.is_available(), "the inference benchmark needs a GPU"
+    device = torch.device("cuda", torch.cuda.current_device())
+    model = load_model("model_3", None, chunk_size=args.chunk_size, inplace=not args.no_inplace, seed=1234, device=device)
+    feats = inference_features(torch, args)
+    h2d = sum(v.numel() * v.element_size() for v in feats.values())
+    _lib.LAUNCHES[0] = 0
+
+    def call(f):
+        out, _ = predict(model, f)
+        return out["final_atom_positions"]
+
+    torch.cuda.reset_peak_memory_stats()
+    ms, e2e, clocks, d2h = _time_inference(torch, dist, args, device, call, feats)
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    status = _lib.read_status()
+    if core.get_rank() == 0:
+        calls = args.warmup + 2 * args.steps
+        print(json.dumps(_inference_json(args, world, "ours", ms, e2e, clocks, h2d, d2h, peak, {
+            "gpu_launches": _lib.LAUNCHES[0] // max(1, calls) * args.steps, "device_status": status[0],
+            "arm": {"kernels": "own sm_100a kernels (tcgen05 GEMM / attention, LayerNorm, IPA, P2P collectives)"}})), flush=True)
+    core.shutdown()
+
+
+def run_reference_inference(args):
+    def unavailable(why):
+        if int(os.environ.get("RANK", 0)) == 0:
+            print(json.dumps({"impl": "reference", "metric": "monomer_inference_latency", "unavailable": why}), flush=True)
+        return 0
+
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "fastfold")):
+        return unavailable("baseline/_ref/fastfold is missing (reference package not installed)")
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        return unavailable("the reference has no CPU path (its kernels are CUDA/Triton only)")
+    feats = inference_features(torch, args)          # generated before the reference's modules shadow any import
+    for n, t in (("int", int), ("float", float), ("bool", bool), ("object", object)):
+        if not hasattr(np, n):                        # aliases the reference's constants tables still use
+            setattr(np, n, t)
+    for m in [k for k in sys.modules if k == "fastfold" or k.startswith("fastfold.")]:
+        del sys.modules[m]
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "stubs"))
+    sys.path.insert(0, ref)
+    try:
+        import fastfold
+        from fastfold.config import model_config
+        from fastfold.distributed import init_dap
+        from fastfold.model.fastnn import set_chunk_size
+        from fastfold.model.hub import AlphaFold
+        from fastfold.utils.inject_fastnn import inject_fastnn
+        assert os.path.abspath(fastfold.__file__).startswith(os.path.abspath(ref)), fastfold.__file__
+    except Exception as e:  # pragma: no cover
+        return unavailable("import of the reference failed: %r" % (e,))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    init_dap(world)
+    device = torch.device("cuda", torch.cuda.current_device())
+    # the reference's own inference path: inference.py:122-159 / demo.py:86-118
+    config = model_config("model_3")
+    config.globals.chunk_size = args.chunk_size
+    config.globals.inplace = not args.no_inplace
+    config.globals.is_multimer = False
+    torch.manual_seed(1234)
+    model = AlphaFold(config)
+    model = inject_fastnn(model).eval().cuda().to(torch.bfloat16)
+    set_chunk_size(model.globals.chunk_size)
+    h2d = sum(v.numel() * v.element_size() for v in feats.values())
+
+    def call(f):
+        with torch.no_grad():
+            batch = {k: torch.as_tensor(v).cuda(non_blocking=True) for k, v in f.items()}
+            return model(batch)["final_atom_positions"]
+
+    torch.cuda.reset_peak_memory_stats()
+    try:
+        ms, e2e, clocks, d2h = _time_inference(torch, dist, args, device, call, feats)
+    except Exception as e:
+        return unavailable("the reference failed at this size: %s" % (repr(e)[:400],))
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    if int(os.environ.get("RANK", 0)) == 0:
+        print(json.dumps(_inference_json(args, world, "reference", ms, e2e, clocks, h2d, d2h, peak, {
+            "arm": {"kernels": "reference Triton LayerNorm/softmax + cuBLAS + NCCL", "path": "AlphaFold + inject_fastnn + set_chunk_size"}})),
+              flush=True)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse()
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -364,6 +541,10 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus), "--master-addr",
                "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29541"), os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
+    if args.metric == "inference":
+        if args.impl == "reference":
+            sys.exit(run_reference_inference(args) or 0)
+        return run_ours_inference(args)
     if args.impl == "reference":
         sys.exit(run_reference(args) or 0)
     run_ours(args)

@@ -128,6 +128,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
                                                                  const __grid_constant__ CUtensorMap tmK,
                                                                  const __grid_constant__ CUtensorMap tmV,
                                                                  const __grid_constant__ CUtensorMap tmBias, const AttnArgs a) {
+  pdl_launch_dependents();
   static_assert(D == 32, "head dim 32");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -179,6 +180,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_fwd_kernel(const __grid_co
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
+  pdl_wait();          // the prologue above touched no global memory; everything below may
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -562,7 +564,7 @@ int ffb_attention_fwd(const void* q, const void* k, const void* v, long long q_b
   }
   // groups of B consecutive items share their bias tiles: give every CTA whole multiples of a sensible chunk
   int grid = items < sm_count ? (int)items : sm_count;
-  attn_fwd_kernel<32><<<grid, AT_THREADS, AttnSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, tb, a);
+  launch_k(attn_fwd_kernel<32>, grid, AT_THREADS, AttnSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream), tq, tk, tv, tb, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -15;
 }
 
@@ -624,6 +626,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
                                                                  const __grid_constant__ CUtensorMap tmV,
                                                                  const __grid_constant__ CUtensorMap tmDO,
                                                                  const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
+  pdl_launch_dependents();
   static_assert(D == 32, "head dim 32");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -666,6 +669,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_bwd_kernel(const __grid_co
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
+  pdl_wait();          // the prologue above touched no global memory; everything below may
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -1046,7 +1050,7 @@ int ffb_attention_bwd_strided(const void* q, const void* k, const void* v, long 
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   const int grid = a.items < sm_count ? a.items : sm_count;
-  attn_bwd_kernel<32><<<grid, AT_THREADS, BwdSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, tdo, tb, a);
+  launch_k(attn_bwd_kernel<32>, grid, AT_THREADS, BwdSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream), tq, tk, tv, tdo, tb, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -16;
 }
 

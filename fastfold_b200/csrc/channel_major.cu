@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(256) ln_bwd_transposed_kernel(const bf16* __re
                                                                const bf16* __restrict__ gamma, const float* __restrict__ mean,
                                                                const float* __restrict__ rstd, bf16* __restrict__ dx,
                                                                float* __restrict__ part, long long rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float sm[];
   float* t_x = sm;                              // [C][33] normalised input
   float* t_g = sm + C * (LTB_ROWS + 1);         // [C][33] dy * gamma
@@ -73,6 +75,8 @@ __global__ void __launch_bounds__(256) ln_bwd_transposed_kernel(const bf16* __re
 // dgamma[c] = sum_b part[b][0][c], dbeta[c] = sum_b part[b][1][c]; block = 32 columns x 32 slices of blocks
 __global__ void __launch_bounds__(1024) ltb_reduce_kernel(const float* __restrict__ part, int nblocks, int C, float* __restrict__ dgamma,
                                                           float* __restrict__ dbeta) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float acc[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
@@ -92,6 +96,8 @@ __global__ void __launch_bounds__(1024) ltb_reduce_kernel(const float* __restric
 // 8 bf16 per thread along the contiguous index
 __global__ void glu_mask_t_fwd_kernel(const bf16* __restrict__ pre, const bf16* __restrict__ mask, bf16* __restrict__ out, int C2,
                                       long long R) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long vec_per_row = R >> 3;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= vec_per_row * C2) return;
@@ -112,6 +118,8 @@ __global__ void glu_mask_t_fwd_kernel(const bf16* __restrict__ pre, const bf16* 
 
 __global__ void glu_mask_t_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ pre, const bf16* __restrict__ mask,
                                       bf16* __restrict__ dpre, int C2, long long R) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long vec_per_row = R >> 3;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= vec_per_row * C2) return;
@@ -164,9 +172,9 @@ int ffb_layernorm_bwd_transposed(const void* dy, const void* x, const void* gamm
   }
   const long long nb = (rows + LTB_ROWS - 1) / LTB_ROWS;
   if (nb > 0x7fffffffLL) return -4;
-  ln_bwd_transposed_kernel<<<(unsigned)nb, 256, smem, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part,
+  launch_k(ln_bwd_transposed_kernel, (unsigned)nb, 256, smem, st, (const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part,
                                                            rows, C);
-  ltb_reduce_kernel<<<(2 * C + 31) / 32, 1024, 0, st>>>(part, (int)nb, C, dgamma, dbeta);
+  launch_k(ltb_reduce_kernel, (2 * C + 31) / 32, 1024, 0, st, part, (int)nb, C, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -175,7 +183,7 @@ int ffb_glu_mask_t_fwd(const void* pre, const void* mask, void* out, int C2, lon
   if (R % 8 || C2 < 1) return -2;
   const long long n = (R >> 3) * C2;
   if (n <= 0) return 0;
-  glu_mask_t_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const bf16*)pre, (const bf16*)mask,
+  launch_k(glu_mask_t_fwd_kernel, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)pre, (const bf16*)mask,
                                                                                                         (bf16*)out, C2, R);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -185,8 +193,7 @@ int ffb_glu_mask_t_bwd(const void* dout, const void* pre, const void* mask, void
   if (R % 8 || C2 < 1) return -2;
   const long long n = (R >> 3) * C2;
   if (n <= 0) return 0;
-  glu_mask_t_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const bf16*)dout, (const bf16*)pre, (const bf16*)mask, (bf16*)dpre, C2, R);
+  launch_k(glu_mask_t_bwd_kernel, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)dout, (const bf16*)pre, (const bf16*)mask, (bf16*)dpre, C2, R);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -4,8 +4,8 @@
 
 #define SYMM_MAX_RANKS 8
 #define SYMM_MAX_SLOTS 64
-// flag pad size in 32-bit words: ready/done (16 per slot) + epoch (1 per slot) + block counter (1 per slot)
-#define SYMM_FLAG_WORDS (SYMM_MAX_SLOTS * 18)
+// flag pad size in 32-bit words: ready/done (16 per slot) + epoch (1 per slot) + two block counters (1 each per slot)
+#define SYMM_FLAG_WORDS (SYMM_MAX_SLOTS * 19)
 
 struct SymmCtx {
   unsigned char* heap[SYMM_MAX_RANKS];   // base of every rank's heap slab, as mapped on THIS GPU

@@ -109,6 +109,8 @@ __device__ __forceinline__ uint32_t next_epoch(const SymmCtx& c, int slot) {
 // publish: src -> own heap slot, then ready[slot][rank] = epoch on every peer
 // ---------------------------------------------------------------------------
 __global__ void symm_publish_k(SymmCtx c, int slot, long long heap_off, const uint4* __restrict__ src, long long n16) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ uint32_t s_epoch;
   COMM_TRACE(0);
   if (threadIdx.x == 0) {
@@ -142,6 +144,8 @@ __global__ void symm_publish_k(SymmCtx c, int slot, long long heap_off, const ui
 // all-to-all: every rank published P chunks; dst[r] = chunk `rank` of peer r
 // ---------------------------------------------------------------------------
 __global__ void symm_pull_k(SymmCtx c, int slot, long long heap_off, uint4* __restrict__ dst, long long n16, int all_to_all) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ uint32_t s_epoch;
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
@@ -184,6 +188,8 @@ template <int VPL>
 __global__ void __launch_bounds__(128) symm_a2a_ln_k(SymmCtx c, int slot, long long heap_off, int mode, int A, int B, int C,
                                                      bf16* __restrict__ y_raw, bf16* __restrict__ y_norm, const bf16* __restrict__ gamma,
                                                      const bf16* __restrict__ beta, float eps, int transpose_norm) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ uint32_t s_epoch;
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
@@ -290,6 +296,8 @@ __global__ void __launch_bounds__(128) symm_a2a_ln_k(SymmCtx c, int slot, long l
 // Ranges are disjoint, so no rank reads what another one is writing.  `scale` is applied to the sum.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) symm_allreduce_bf16_k(SymmCtx c, int slot, long long heap_off, long long n8, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ uint32_t s_epoch;
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
@@ -347,9 +355,268 @@ __global__ void __launch_bounds__(256) symm_allreduce_bf16_k(SymmCtx c, int slot
   }
 }
 
+// ---------------------------------------------------------------------------
+// One-kernel collectives ("push").  The rank's contribution is viewed as [X][Ps][Y] 16-byte units, Ps = P when chunk
+// q of the middle axis is meant for rank q (all-to-all, reduce-scatter) and 1 when every rank gets everything
+// (all-gather).  Phase 1 stores the units straight into the destination ranks' slots over NVLink (a store needs no
+// round trip, so a thread keeps many in flight), laid out [source rank][X][Y] there; the block that finishes last
+// raises ready[slot][rank] on every rank.  Phase 2 waits (bounded) for every rank's ready flag and then reads only
+// LOCAL memory: it copies the slot into the result in the layout the consumer wants, sums the P partial tensors in
+// fp32 (the reduce-scatter of a gathered operand's gradient), or normalises rows on the way (axis switch + LayerNorm).
+// One launch per collective instead of two to five; the grid is capped so that all blocks are resident at once
+// (blocks of phase 2 wait for flags that other ranks raise only after ALL of their blocks finished phase 1).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int w_blocks2(int slot) { return SYMM_MAX_SLOTS * 18 + slot; }                        // local only
+
+struct XchgArgs {
+  const uint4* src;
+  long long X, Y;          // units: src is [X][Ps][Y]
+  long long X2, Y2;        // what arrived from one rank (X * Y units) seen as [X2][Y2] for the placement below
+  int scatter;             // 1: Ps = world, chunk q -> rank q;  0: Ps = 1, everything -> every rank
+  int mode;                // 0: dst[r][x2][y2]   1: dst[x2][r][y2]   2: dst[x2][y2] = sum over r (bf16 in, fp32 accumulate, bf16 out)
+  uint4* dst;
+};
+
+constexpr int XCHG_THREADS = 256;
+constexpr int XCHG_U = 4;
+
+// thread 0 only: wait until every rank (this one included) raised ready[slot] for `epoch`
+__device__ __forceinline__ bool wait_all_ready(const SymmCtx& c, int slot, uint32_t epoch) {
+  bool ok = true;
+  for (int r = 0; r < c.world; ++r) {
+    if (!wait_flag(c.flags[c.rank] + w_ready(slot, r), epoch, c.wait_ns)) {
+      report(ST_TIMEOUT_PEER, (slot << 8) | r | 0x80);
+      ok = false;
+    }
+  }
+  return ok;
+}
+
+// Phase 1 of a push collective; returns the epoch (all threads).  On return this block's stores have been issued and the
+// last block of the grid has raised (or will raise) the ready flags.
+__device__ __forceinline__ uint32_t xchg_push(const SymmCtx& c, int slot, long long heap_off, const uint4* __restrict__ src, long long X,
+                                              long long Y, int scatter) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = next_epoch(c, slot);
+    wait_peers(c, false, slot, s_epoch - 1u);        // every rank has finished with what its slot held before
+  }
+  __syncthreads();
+  const int P = c.world;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (scatter) {
+    const long long n = X * P * Y;
+    for (long long i = t0; i < n; i += stride * XCHG_U) {
+      uint4 v[XCHG_U];
+#pragma unroll
+      for (int u = 0; u < XCHG_U; ++u)
+        if (i + u * stride < n) v[u] = src[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < XCHG_U; ++u) {
+        const long long k = i + u * stride;
+        if (k < n) {
+          const long long xq = k / Y, y = k - xq * Y;
+          const long long x = xq / P;
+          const int q = (int)(xq - x * P);
+          reinterpret_cast<uint4*>(c.heap[q] + heap_off)[((long long)c.rank * X + x) * Y + y] = v[u];
+        }
+      }
+    }
+  } else {
+    const long long n = X * Y;
+    const long long base = (long long)c.rank * n;
+    for (long long i = t0; i < n; i += stride * XCHG_U) {
+      uint4 v[XCHG_U];
+#pragma unroll
+      for (int u = 0; u < XCHG_U; ++u)
+        if (i + u * stride < n) v[u] = src[i + u * stride];
+      for (int qq = 0; qq < P; ++qq) {
+        const int q = (c.rank + qq) % P;               // ranks start on different destinations
+        uint4* d = reinterpret_cast<uint4*>(c.heap[q] + heap_off) + base;
+#pragma unroll
+        for (int u = 0; u < XCHG_U; ++u)
+          if (i + u * stride < n) d[i + u * stride] = v[u];
+      }
+    }
+  }
+  last_block_signal(c, slot, s_epoch, true);
+  return s_epoch;
+}
+
+// End of phase 2: the last block raises done[slot][rank] on every rank and advances the slot's epoch.
+__device__ __forceinline__ void xchg_finish(const SymmCtx& c, int slot, uint32_t epoch) {
+  __shared__ int s_last2;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    uint32_t* blk = c.flags[c.rank] + w_blocks2(slot);
+    s_last2 = (atomicAdd(blk, 1u) == gridDim.x - 1) ? 1 : 0;
+    if (s_last2) {
+      *blk = 0;
+      __threadfence_system();
+      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_done(slot, c.rank), epoch);
+      c.flags[c.rank][w_epoch(slot)] = epoch;
+    }
+  }
+}
+
+__device__ __forceinline__ void acc8(float* a, const uint4& u) {
+  const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h[j]);
+    a[2 * j] += f.x;
+    a[2 * j + 1] += f.y;
+  }
+}
+
+__global__ void __launch_bounds__(XCHG_THREADS) symm_xchg_k(SymmCtx c, int slot, long long heap_off, XchgArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t epoch = xchg_push(c, slot, heap_off, a.src, a.X, a.Y, a.scatter);
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = wait_all_ready(c, slot, epoch) ? 1 : 0;
+  __syncthreads();
+  if (s_ok) {
+    const int P = c.world;
+    const uint4* in = reinterpret_cast<const uint4*>(c.heap[c.rank] + heap_off);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (a.mode == 2) {
+      const long long n = a.X2 * a.Y2;
+      for (long long i = t0; i < n; i += stride) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < P; ++r) acc8(acc, in[(long long)r * n + i]);
+        uint4 o;
+        bf162* ho = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ho[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        a.dst[i] = o;
+      }
+    } else {
+      const long long n = a.X2 * a.Y2 * P;
+      for (long long i = t0; i < n; i += stride * XCHG_U) {
+        uint4 v[XCHG_U];
+#pragma unroll
+        for (int u = 0; u < XCHG_U; ++u)
+          if (i + u * stride < n) v[u] = in[i + u * stride];
+#pragma unroll
+        for (int u = 0; u < XCHG_U; ++u) {
+          const long long k = i + u * stride;
+          if (k < n) {
+            long long o = k;
+            if (a.mode == 1) {
+              const long long rx = k / a.Y2, y = k - rx * a.Y2;
+              const long long r = rx / a.X2, x = rx - r * a.X2;
+              o = (x * P + r) * a.Y2 + y;
+            }
+            a.dst[o] = v[u];
+          }
+        }
+      }
+    }
+  }
+  xchg_finish(c, slot, epoch);
+}
+
+// Axis switch + LayerNorm as one push collective.  mode 0 ("row -> column"): this rank holds X_r [A/P][B][C], the
+// result is Y [A][B/P][C]; mode 1 ("column -> row"): X_r [A][B/P][C] -> Y [A/P][B][C].  The slot receives
+// [source rank][A/P][B/P][C]; phase 2 walks the output rows (one warp per row of C channels), writes the raw row (the
+// residual stream) and, when gamma is given, the normalised row - optionally at the transposed position.
+template <int VPL>
+__global__ void __launch_bounds__(128) symm_xchg_ln_k(SymmCtx c, int slot, long long heap_off, const uint4* __restrict__ src, int mode, int A,
+                                                      int B, int C, bf16* __restrict__ y_raw, bf16* __restrict__ y_norm,
+                                                      const bf16* __restrict__ gamma, const bf16* __restrict__ beta, float eps, int transpose_norm) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int P = c.world;
+  const int Al = A / P, Bl = B / P;
+  const long long yu = (long long)Bl * (C / 8);
+  // mode 0: src [Al][P][Bl*C]; mode 1: src [P][Al][Bl*C] = X 1 with chunks of Al * Bl * C
+  const uint32_t epoch = mode == 0 ? xchg_push(c, slot, heap_off, src, Al, yu, 1) : xchg_push(c, slot, heap_off, src, 1, (long long)Al * yu, 1);
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = wait_all_ready(c, slot, epoch) ? 1 : 0;
+  __syncthreads();
+  const int Ad = mode == 0 ? A : Al, Bd = mode == 0 ? Bl : B;       // output extents
+  const long long rows = (long long)Ad * Bd;
+  const int lane = threadIdx.x & 31;
+  constexpr int NV = VPL / 8;
+  if (s_ok) {
+    const bf16* in = reinterpret_cast<const bf16*>(c.heap[c.rank] + heap_off);
+    const long long wstride = (long long)gridDim.x * 4;
+    for (long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5); row < rows; row += wstride) {
+      const int a = (int)(row / Bd), b = (int)(row - (long long)a * Bd);
+      long long srow = row;                                            // mode 0: the slot IS the result layout
+      if (mode == 1) {
+        const int r = b / Bl;
+        srow = ((long long)r * Al + a) * Bl + (b - r * Bl);
+      }
+      const bf16* sp = in + srow * C;
+      float v[VPL];
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c0 = (i * 32 + lane) * 8;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (c0 < C) {
+          raw = *reinterpret_cast<const uint4*>(sp + c0);
+          if (y_raw) *reinterpret_cast<uint4*>(y_raw + row * C + c0) = raw;
+        }
+        const bf162* h = reinterpret_cast<const bf162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          v[i * 8 + 2 * j] = f.x;
+          v[i * 8 + 2 * j + 1] = f.y;
+          s += f.x + f.y;
+        }
+      }
+      if (y_norm) {
+        const float mean = warp_sum(s) / C;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c0 = (i * 32 + lane) * 8;
+          if (c0 < C) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float d = v[i * 8 + j] - mean;
+              q += d * d;
+            }
+          }
+        }
+        const float rstd = rsqrtf(warp_sum(q) / C + eps);
+        const long long orow = transpose_norm ? ((long long)b * Ad + a) : row;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c0 = (i * 32 + lane) * 8;
+          if (c0 < C) {
+            const uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0), ub = *reinterpret_cast<const uint4*>(beta + c0);
+            const bf162 *hg = reinterpret_cast<const bf162*>(&ug), *hb = reinterpret_cast<const bf162*>(&ub);
+            uint4 uo;
+            bf162* ho = reinterpret_cast<bf162*>(&uo);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 g2 = __bfloat1622float2(hg[j]), b2 = __bfloat1622float2(hb[j]);
+              ho[j] = __floats2bfloat162_rn((v[i * 8 + 2 * j] - mean) * rstd * g2.x + b2.x, (v[i * 8 + 2 * j + 1] - mean) * rstd * g2.y + b2.y);
+            }
+            *reinterpret_cast<uint4*>(y_norm + orow * C + c0) = uo;
+          }
+        }
+      }
+    }
+  }
+  xchg_finish(c, slot, epoch);
+}
+
 // Raises ready[slot][rank] after a producer kernel wrote the slot directly (stream-ordered behind it), waiting first
 // (pre = 1, run BEFORE the producer) for the peers to have finished with the slot's previous contents.
 __global__ void symm_slot_fence_k(SymmCtx c, int slot, int pre) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   const uint32_t e = next_epoch(c, slot);
   if (pre) {
@@ -364,6 +631,8 @@ __global__ void symm_slot_fence_k(SymmCtx c, int slot, int pre) {
 // peer tensor maps): pre = 1 waits for every peer's ready flag (run before the consumer), pre = 0 raises done and
 // advances the epoch (run after it).
 __global__ void symm_consume_fence_k(SymmCtx c, int slot, int pre) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   const uint32_t e = next_epoch(c, slot);
   if (pre) {
@@ -377,6 +646,8 @@ __global__ void symm_consume_fence_k(SymmCtx c, int slot, int pre) {
 
 // Test hook: waits on a ready flag that nothing raises, with a short limit; must time out and report, not hang.
 __global__ void symm_wait_never_k(SymmCtx c, int slot) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     const uint32_t* p = c.flags[c.rank] + w_ready(slot, (c.rank + 1) % (c.world > 1 ? c.world : 2));
     if (!wait_flag(p, 0x7fffffffu, c.wait_ns)) report(ST_TIMEOUT_PEER, slot << 8);
@@ -399,7 +670,7 @@ static int grid_for(long long n, int threads, int cap) {
 int ffb_symm_publish(const SymmCtx* c, int slot, long long heap_off, const void* src, long long bytes, void* stream) {
   if (bytes % 16 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
   const long long n16 = bytes / 16;
-  symm_publish_k<<<grid_for((n16 + COPY_U - 1) / COPY_U, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, (const uint4*)src, n16);
+  launch_k(symm_publish_k, grid_for((n16 + COPY_U - 1) / COPY_U, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, (const uint4*)src, n16);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -408,7 +679,7 @@ int ffb_symm_pull(const SymmCtx* c, int slot, long long heap_off, void* dst, lon
   const long long n16 = bytes_per_rank / 16;
   {
     const int gx = grid_for((n16 + COPY_U - 1) / COPY_U, 256, 592 / c->world > 0 ? 592 / c->world : 1);
-    symm_pull_k<<<dim3(gx, c->world), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, (uint4*)dst, n16, all_to_all);
+    launch_k(symm_pull_k, dim3(gx, c->world), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, (uint4*)dst, n16, all_to_all);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -420,9 +691,46 @@ int ffb_symm_a2a_layernorm(const SymmCtx* c, int slot, long long heap_off, int m
   const long long rows = (long long)(mode == 0 ? A : A / c->world) * (mode == 0 ? B / c->world : B);
   const int grid = grid_for(rows, 4, 1184);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (C <= 256) symm_a2a_ln_k<8><<<grid, 128, 0, st>>>(*c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
-  else if (C <= 512) symm_a2a_ln_k<16><<<grid, 128, 0, st>>>(*c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
-  else symm_a2a_ln_k<32><<<grid, 128, 0, st>>>(*c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  if (C <= 256) launch_k(symm_a2a_ln_k<8>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else if (C <= 512) launch_k(symm_a2a_ln_k<16>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else launch_k(symm_a2a_ln_k<32>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// One-kernel collectives.  The source is [x1][Ps][bytes_chunk / x1] (Ps = world when `scatter`, else 1); what arrives from
+// one rank (bytes_chunk) is placed as [x2][bytes_chunk / x2]:  mode 0: dst [P][x2][.];  1: dst [x2][P][.];
+// 2: dst [x2][.] = sum over source ranks (bf16).  The slot must hold world * bytes_chunk bytes.
+int ffb_symm_xchg(const SymmCtx* c, int slot, long long heap_off, const void* src, long long x1, long long x2, long long bytes_chunk,
+                  int scatter, int mode, void* dst, void* stream) {
+  if (bytes_chunk % 16 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS || x1 < 1 || x2 < 1 || mode < 0 || mode > 2) return -2;
+  const long long units = bytes_chunk / 16;
+  if (units % x1 || units % x2) return -3;
+  XchgArgs a;
+  a.src = (const uint4*)src;
+  a.X = x1;
+  a.Y = units / x1;
+  a.X2 = x2;
+  a.Y2 = units / x2;
+  a.scatter = scatter;
+  a.mode = mode;
+  a.dst = (uint4*)dst;
+  const long long work = units * c->world;
+  const int grid = grid_for((work + XCHG_U - 1) / XCHG_U, XCHG_THREADS, 296);
+  launch_k(symm_xchg_k, grid, XCHG_THREADS, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Axis switch (+ transpose) + LayerNorm in one kernel; same arguments as ffb_symm_a2a_layernorm plus the source shard.
+int ffb_symm_xchg_layernorm(const SymmCtx* c, int slot, long long heap_off, const void* src, int mode, int A, int B, int C, void* y_raw,
+                            void* y_norm, const void* gamma, const void* beta, float eps, int transpose_norm, void* stream) {
+  if (C % 8 || C > 1024 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
+  if (A % c->world || B % c->world) return -3;
+  const long long rows = (long long)(mode == 0 ? A : A / c->world) * (mode == 0 ? B / c->world : B);
+  const int grid = grid_for(rows, 4, 592);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (C <= 256) launch_k(symm_xchg_ln_k<8>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else if (C <= 512) launch_k(symm_xchg_ln_k<16>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else launch_k(symm_xchg_ln_k<32>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -430,17 +738,17 @@ int ffb_symm_allreduce_bf16(const SymmCtx* c, int slot, long long heap_off, long
   if (n_elems % 8 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
   const long long n8 = n_elems / 8;
   const long long per = (n8 + c->world - 1) / c->world;
-  symm_allreduce_bf16_k<<<grid_for(per, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, heap_off, n8, scale);
+  launch_k(symm_allreduce_bf16_k, grid_for(per, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, n8, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int ffb_symm_slot_fence(const SymmCtx* c, int slot, int pre, void* stream) {
-  symm_slot_fence_k<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, pre);
+  launch_k(symm_slot_fence_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, pre);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int ffb_symm_consume_fence(const SymmCtx* c, int slot, int pre, void* stream) {
-  symm_consume_fence_k<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot, pre);
+  launch_k(symm_consume_fence_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, pre);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -451,7 +759,7 @@ int ffb_comm_trace_read(unsigned long long* out) {
 #endif
 
 int ffb_symm_wait_never(const SymmCtx* c, int slot, void* stream) {
-  symm_wait_never_k<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, slot);
+  launch_k(symm_wait_never_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

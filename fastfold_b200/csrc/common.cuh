@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace ffb {
 
@@ -47,6 +48,17 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 
 // Default limit for waits on purely local events (TMA, MMA): 2 s.
 #define FFB_LOCAL_WAIT_NS 2000000000ull
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of this library starts with pdl_launch_dependents() - the next kernel
+// on the stream may then be scheduled as soon as all CTAs of this one are running, so its launch latency and prologue
+// (barrier init, tensor-memory allocation, descriptor prefetch) overlap this kernel's tail - and executes pdl_wait()
+// in every CTA before its first access to global memory: the wait returns when all earlier kernels have completed
+// and their writes are visible.  Because every CTA of every kernel waits before it exits, completion stays
+// transitive along the stream.  Kernels launched without the attribute (FFB_PDL=0) see both as no-ops.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
 // Shared-memory addresses and mbarriers
@@ -223,5 +235,31 @@ template <typename T> __device__ __forceinline__ T from_f(float v);
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16(v); }
 template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half(v); }
+
+// Host side: launches `kern` with the programmatic-stream-serialization attribute (see pdl_wait above) unless the
+// environment variable FFB_PDL is 0.  Works under stream capture: the dependency becomes a programmatic graph edge.
+inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FFB_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 }  // namespace ffb

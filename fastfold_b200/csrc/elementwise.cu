@@ -54,6 +54,8 @@ __device__ __forceinline__ void st8(bf16* p, const V8& r) {
   const long long off = row * C + c;
 
 __global__ void bias_sigmoid_mul_fwd_k(const bf16* g, const bf16* b, const bf16* o, bf16* y, long long rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 gv = ld8(g + off), bv = ld8(b + c), ov = ld8(o + off), r;
 #pragma unroll
@@ -63,6 +65,8 @@ __global__ void bias_sigmoid_mul_fwd_k(const bf16* g, const bf16* b, const bf16*
 
 __global__ void bias_sigmoid_mul_bwd_k(const bf16* dy, const bf16* g, const bf16* b, const bf16* o, bf16* dg, bf16* dob,
                                        long long rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 d = ld8(dy + off), gv = ld8(g + off), bv = ld8(b + c), ov = ld8(o + off), r1, r2;
 #pragma unroll
@@ -77,6 +81,8 @@ __global__ void bias_sigmoid_mul_bwd_k(const bf16* dy, const bf16* g, const bf16
 
 __global__ void bias_dropout_add_fwd_k(const bf16* x, const bf16* b, const bf16* m, const bf16* r, bf16* y, long long rows,
                                        int C, int div, int mod) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 xv = ld8(x + off), rv = ld8(r + off), o;
   V8 bv, mv;
@@ -91,6 +97,8 @@ __global__ void bias_dropout_add_fwd_k(const bf16* x, const bf16* b, const bf16*
 
 // dx = dy * m
 __global__ void mask_mul_k(const bf16* dy, const bf16* m, bf16* dx, long long rows, int C, int div, int mod) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 d = ld8(dy + off), mv = ld8(m + (long long)((row / div) % mod) * C + c), o;
 #pragma unroll
@@ -100,6 +108,8 @@ __global__ void mask_mul_k(const bf16* dy, const bf16* m, bf16* dx, long long ro
 
 __global__ void bias_ele_dropout_res_fwd_k(const bf16* ab, const bf16* b, const bf16* g, const bf16* m, const bf16* r, bf16* y,
                                            long long rows, int C, int div, int mod) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 av = ld8(ab + off), bv = ld8(b + c), gv = ld8(g + off), rv = ld8(r + off), mv, o;
 #pragma unroll
@@ -112,6 +122,8 @@ __global__ void bias_ele_dropout_res_fwd_k(const bf16* ab, const bf16* b, const 
 
 __global__ void bias_ele_dropout_res_bwd_k(const bf16* dy, const bf16* ab, const bf16* b, const bf16* g, const bf16* m,
                                            bf16* dab, bf16* dg, long long rows, int C, int div, int mod) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 d = ld8(dy + off), av = ld8(ab + off), bv = ld8(b + c), gv = ld8(g + off), mv, o1, o2;
 #pragma unroll
@@ -129,6 +141,8 @@ __global__ void bias_ele_dropout_res_bwd_k(const bf16* dy, const bf16* ab, const
 
 // y = rowmask[row] * p * sigmoid(q); p, q, y: [rows, C]
 __global__ void glu_mask_fwd_k(const bf16* p, const bf16* q, const bf16* rowmask, bf16* y, long long rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 pv = ld8(p + off), qv = ld8(q + off), o;
   const float mk = rowmask ? __bfloat162float(rowmask[row]) : 1.f;
@@ -139,6 +153,8 @@ __global__ void glu_mask_fwd_k(const bf16* p, const bf16* q, const bf16* rowmask
 
 __global__ void glu_mask_bwd_k(const bf16* dy, const bf16* p, const bf16* q, const bf16* rowmask, bf16* dp, bf16* dq,
                                long long rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 d = ld8(dy + off), pv = ld8(p + off), qv = ld8(q + off), o1, o2;
   const float mk = rowmask ? __bfloat162float(rowmask[row]) : 1.f;
@@ -155,6 +171,8 @@ __global__ void glu_mask_bwd_k(const bf16* dy, const bf16* p, const bf16* q, con
 
 // mode 1: relu (dx = dy where y > 0), mode 2: sigmoid (dx = dy * y * (1 - y))
 __global__ void act_bwd_k(const bf16* dy, const bf16* y, bf16* dx, long long rows, int C, int mode) {
+  pdl_launch_dependents();
+  pdl_wait();
   FFB_EW_INDEX
   V8 d = ld8(dy + off), yv = ld8(y + off), o;
 #pragma unroll
@@ -164,6 +182,8 @@ __global__ void act_bwd_k(const bf16* dy, const bf16* y, bf16* dx, long long row
 
 // out[c] += sum_rows x[row][c]; grid = (ceil(C/256), nchunks); fp32 atomics.
 __global__ void colsum_k(const bf16* x, float* out, long long rows, int C, long long rows_per_block) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
   if (c >= C) return;
   const long long r0 = (long long)blockIdx.y * rows_per_block;
@@ -184,6 +204,8 @@ __global__ void colsum_k(const bf16* x, float* out, long long rows, int C, long 
 // shared memory and one thread per column adds the block's result to `out`.
 __global__ void __launch_bounds__(256) colsum_v8_k(const bf16* __restrict__ x, float* __restrict__ out, long long rows, int C,
                                                    long long rows_per_block) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float red[];                 // [row lanes][C]
   const int groups = C >> 3;                     // column groups of 8
   const int lanes = 256 / groups;                // row lanes per block (groups <= 256)
@@ -240,6 +262,8 @@ __global__ void __launch_bounds__(256) colsum_v8_k(const bf16* __restrict__ x, f
 //   hp[0] = lr, hp[1] = 1 - beta1^t, hp[2] = 1 - beta2^t, hp[3] = gradient scale
 __global__ void adam_k(float* w, float* m, float* v, const bf16* grad, bf16* w16, long long n, const float* hp, float b1,
                        float b2, float eps, float wd) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float lr = hp[0], bc1 = hp[1], bc2 = hp[2], gscale = hp[3];
@@ -264,7 +288,7 @@ using namespace ffb;
     if (rows <= 0) return 0;                                                            \
     if (C % 8) return -2;                                                               \
     const long long n = rows * (C / 8);                                                 \
-    kern<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(__VA_ARGS__); \
+    launch_k(kern, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), __VA_ARGS__); \
     return cudaGetLastError() == cudaSuccess ? 0 : -1;                                  \
   } while (0)
 
@@ -314,21 +338,21 @@ int ffb_colsum(const void* x, float* out, long long rows, int C, void* stream) {
     if (blocks < 1) blocks = 1;
     const long long rpb = (rows + blocks - 1) / blocks;
     const size_t smem = sizeof(float) * lanes * C;          // = 8 KB
-    colsum_v8_k<<<(unsigned)((rows + rpb - 1) / rpb), 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>((const bf16*)x, out, rows, C, rpb);
+    launch_k(colsum_v8_k, (unsigned)((rows + rpb - 1) / rpb), 256, smem, reinterpret_cast<cudaStream_t>(stream), (const bf16*)x, out, rows, C, rpb);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
   }
   long long chunks = (rows + 255) / 256;
   if (chunks > 512) chunks = 512;
   const long long rpb = (rows + chunks - 1) / chunks;
   dim3 grid((C / 2 + 127) / 128, (unsigned)((rows + rpb - 1) / rpb));
-  colsum_k<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const bf16*)x, out, rows, C, rpb);
+  launch_k(colsum_k, grid, 128, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)x, out, rows, C, rpb);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int ffb_adam(float* w, float* m, float* v, const void* grad, void* w16, long long n, const float* hp, float b1, float b2,
              float eps, float wd, void* stream) {
   if (n <= 0) return 0;
-  adam_k<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(w, m, v, (const bf16*)grad, (bf16*)w16, n, hp,
+  launch_k(adam_k, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), w, m, v, (const bf16*)grad, (bf16*)w16, n, hp,
                                                                                           b1, b2, eps, wd);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -192,6 +192,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
                                                                     const __grid_constant__ CUtensorMap tmRes,
                                                                     const __grid_constant__ PeerMaps pm,
                                                                     const GemmArgs g, int num_tiles, int tiles_m, int tiles_n, int tma_epi) {
+  pdl_launch_dependents();
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -213,12 +214,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kb_total = (g.K + BK - 1) / BK;
-  if (tma_epi && g.bias && g.N <= FAST_BIAS_MAX_N) {
-    // fast epilogue: the whole bias vector as fp32 in shared memory, read back as broadcast 16-byte loads
-    const bf16* bp = reinterpret_cast<const bf16*>(g.bias);
-    for (int i = threadIdx.x; i < FAST_BIAS_MAX_N + 64; i += GEMM_THREADS) s_bias[i] = (i < g.N) ? __bfloat162float(bp[i]) : 0.f;
-  }
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -238,6 +233,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
     __syncwarp();
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
+  }
+  // everything above touches only this CTA's shared and tensor memory; from here on global memory is read
+  pdl_wait();
+  if (tma_epi && g.bias && g.N <= FAST_BIAS_MAX_N) {
+    // fast epilogue: the whole bias vector as fp32 in shared memory, read back as broadcast 16-byte loads
+    const bf16* bp = reinterpret_cast<const bf16*>(g.bias);
+    for (int i = threadIdx.x; i < FAST_BIAS_MAX_N + 64; i += GEMM_THREADS) s_bias[i] = (i < g.N) ? __bfloat162float(bp[i]) : 0.f;
   }
   tc_fence_before();
   __syncthreads();
@@ -825,7 +827,7 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   const int grid = (int)(num_tiles < sm_count ? num_tiles : sm_count);
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(ta, tb, epi[0], epi[1], epi[2], *pm, g, (int)num_tiles, tiles_m, tiles_n, tma_epi);
+  launch_k(kern, grid, GEMM_THREADS, Cfg::SMEM, st, ta, tb, epi[0], epi[1], epi[2], *pm, g, (int)num_tiles, tiles_m, tiles_n, tma_epi);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

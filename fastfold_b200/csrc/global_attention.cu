@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(GA_THREADS) global_attention_kernel(const bf16
                                                                       const bf16* __restrict__ mask, const bf16* __restrict__ gate,
                                                                       const bf16* __restrict__ gate_bias, bf16* __restrict__ out,
                                                                       int S, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float sm[];
   const int lanes = GA_THREADS / H;
   float* s_m = sm;                       // [lanes][H]
@@ -182,6 +184,8 @@ __global__ void __launch_bounds__(GA_THREADS, 2) global_attention_cluster_kernel
                                                                                  const bf16* __restrict__ mask, const bf16* __restrict__ gate,
                                                                                  const bf16* __restrict__ gate_bias, bf16* __restrict__ out,
                                                                                  int S) {
+  pdl_launch_dependents();
+  pdl_wait();
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float s_q[GC_HC];
@@ -379,7 +383,7 @@ int ffb_global_attention_fwd(const void* q, const void* kv, const void* mask, co
 #define FFB_GA_LAUNCH(CC)                                                                                                          \
   do {                                                                                                                             \
     if (smem > 48 * 1024) cudaFuncSetAttribute(global_attention_kernel<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    global_attention_kernel<CC><<<dim3((unsigned)R, (unsigned)parts), GA_THREADS, smem, st>>>((const bf16*)q, (const bf16*)kv, (const bf16*)mask,           \
+    launch_k(global_attention_kernel<CC>, dim3((unsigned)R, (unsigned)parts), GA_THREADS, smem, st, (const bf16*)q, (const bf16*)kv, (const bf16*)mask,           \
                                                                        (const bf16*)gate, (const bf16*)gate_bias, (bf16*)out, S, H); \
   } while (0)
   if (C == 8) FFB_GA_LAUNCH(8);

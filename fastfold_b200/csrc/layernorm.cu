@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_kernel(const T* __restri
                                                               const T* __restrict__ beta, T* __restrict__ y,
                                                               float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                               long long rows, int C, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -93,6 +95,8 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_generic_kernel(const T* 
                                                                       const T* __restrict__ beta, T* __restrict__ y,
                                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                                       long long rows, int C, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -123,6 +127,8 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(const T* __restri
                                                               const T* __restrict__ gamma, const float* __restrict__ mean,
                                                               const float* __restrict__ rstd, T* __restrict__ dx,
                                                               float* __restrict__ part, long long rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int VEC = 16 / sizeof(T);
   constexpr int NV = VPL / VEC;
   __shared__ float red[LN_WARPS][2];
@@ -209,6 +215,8 @@ template <typename T>
 __global__ void ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                                       const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
                                       float* __restrict__ part, long long rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   float* p0 = part + (long long)blockIdx.x * 2 * C;
@@ -238,6 +246,8 @@ __global__ void ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restr
 template <typename T>
 __global__ void __launch_bounds__(1024) ln_bwd_reduce_kernel(const float* __restrict__ part, int nblocks, int C,
                                                              T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  pdl_launch_dependents();
+  pdl_wait();
   // block = 32 columns x 32 row slices: coalesced 128-byte reads, 32 partial sums per column folded through shared memory
   __shared__ float acc[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -259,6 +269,8 @@ __global__ void __launch_bounds__(1024) ln_bwd_reduce_kernel(const float* __rest
 // Same reduction, ADDED into fp32 vectors (a trainer's flat gradient buffer): one writer per column, no atomics.
 __global__ void __launch_bounds__(1024) ln_bwd_reduce_acc_kernel(const float* __restrict__ part, int nblocks, int C,
                                                                  float* __restrict__ dgamma, float* __restrict__ dbeta) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float acc[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
@@ -284,6 +296,8 @@ __global__ void __launch_bounds__(256) ln_fwd_transposed_kernel(const bf16* __re
                                                                const bf16* __restrict__ beta, bf16* __restrict__ y,
                                                                float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                                long long rows, int C, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float tile[];  // [C][LNT_ROWS + 1]
   __shared__ float s_mean[LNT_ROWS], s_rstd[LNT_ROWS];
   const long long r0 = (long long)blockIdx.x * LNT_ROWS;
@@ -345,6 +359,8 @@ __global__ void __launch_bounds__(256) ln_fwd_transposed64_kernel(const bf16* __
                                                                  const bf16* __restrict__ beta, bf16* __restrict__ y,
                                                                  float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                                  long long rows, int C, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float tile[];  // [C][LNT64 + 1]
   __shared__ float s_part[8][LNT64], s_mean[LNT64], s_rstd[LNT64];
   constexpr int P = LNT64 + 1;
@@ -470,6 +486,8 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_mr_kernel(const bf16* __
                                                                  const bf16* __restrict__ beta, bf16* __restrict__ y,
                                                                  float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                                  long long rows, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int C = 8 * L, G = 32 / L;
   const int lane = threadIdx.x & 31, li = lane % L, grp = lane / L;
   const long long base = ((long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5)) * (G * MR_U) + grp;
@@ -516,6 +534,8 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_mr_kernel(const bf16* __
                                                                  const bf16* __restrict__ gamma, const float* __restrict__ mean,
                                                                  const float* __restrict__ rstd, bf16* __restrict__ dx,
                                                                  float* __restrict__ part, long long rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int C = 8 * L, G = 32 / L;
   __shared__ float red[LN_WARPS][2][C];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, li = lane % L, grp = lane / L;
@@ -604,15 +624,15 @@ static int ln_fwd_dispatch(const T* x, const T* g, const T* b, T* y, float* mean
     bf16* yb = reinterpret_cast<bf16*>(y);
     const int rows_per_block = LN_WARPS * MR_U * (256 / C);
     const dim3 gmr((unsigned)((rows + rows_per_block - 1) / rows_per_block));
-    if (C == 64) ln_fwd_mr_kernel<8><<<gmr, LN_WARPS * 32, 0, st>>>(xb, gb, bb, yb, mean, rstd, rows, eps);
-    else if (C == 128) ln_fwd_mr_kernel<16><<<gmr, LN_WARPS * 32, 0, st>>>(xb, gb, bb, yb, mean, rstd, rows, eps);
-    else ln_fwd_mr_kernel<32><<<gmr, LN_WARPS * 32, 0, st>>>(xb, gb, bb, yb, mean, rstd, rows, eps);
+    if (C == 64) launch_k(ln_fwd_mr_kernel<8>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
+    else if (C == 128) launch_k(ln_fwd_mr_kernel<16>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
+    else launch_k(ln_fwd_mr_kernel<32>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
   }
-  if (aligned && C <= 32 * VEC) ln_fwd_kernel<T, VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
-  else if (aligned && C <= 64 * VEC) ln_fwd_kernel<T, 2 * VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
-  else if (aligned && C <= 128 * VEC) ln_fwd_kernel<T, 4 * VEC><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
-  else ln_fwd_generic_kernel<T><<<grid, LN_WARPS * 32, 0, st>>>(x, g, b, y, mean, rstd, rows, C, eps);
+  if (aligned && C <= 32 * VEC) launch_k(ln_fwd_kernel<T, VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
+  else if (aligned && C <= 64 * VEC) launch_k(ln_fwd_kernel<T, 2 * VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
+  else if (aligned && C <= 128 * VEC) launch_k(ln_fwd_kernel<T, 4 * VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
+  else launch_k(ln_fwd_generic_kernel<T>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -630,15 +650,15 @@ static int ln_bwd_dispatch(const T* dy, const T* x, const T* g, const float* mea
   if (IsBf16<T>::value && aligned && (C == 64 || C == 128 || C == 256)) {
     const bf16 *db_ = reinterpret_cast<const bf16*>(dy), *xb = reinterpret_cast<const bf16*>(x), *gb = reinterpret_cast<const bf16*>(g);
     bf16* dxb = reinterpret_cast<bf16*>(dx);
-    if (C == 64) ln_bwd_mr_kernel<8><<<nblocks, LN_WARPS * 32, 0, st>>>(db_, xb, gb, mean, rstd, dxb, part, rows);
-    else if (C == 128) ln_bwd_mr_kernel<16><<<nblocks, LN_WARPS * 32, 0, st>>>(db_, xb, gb, mean, rstd, dxb, part, rows);
-    else ln_bwd_mr_kernel<32><<<nblocks, LN_WARPS * 32, 0, st>>>(db_, xb, gb, mean, rstd, dxb, part, rows);
-  } else if (aligned && C <= 32 * VEC) ln_bwd_kernel<T, VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
-  else if (aligned && C <= 64 * VEC) ln_bwd_kernel<T, 2 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
-  else if (aligned && C <= 128 * VEC) ln_bwd_kernel<T, 4 * VEC><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
-  else ln_bwd_generic_kernel<T><<<nblocks, LN_WARPS * 32, 0, st>>>(dy, x, g, mean, rstd, dx, part, rows, C);
-  if (dgamma_acc) ln_bwd_reduce_acc_kernel<<<(2 * C + 31) / 32, 1024, 0, st>>>(part, nblocks, C, dgamma_acc, dbeta_acc);
-  else ln_bwd_reduce_kernel<T><<<(2 * C + 31) / 32, 1024, 0, st>>>(part, nblocks, C, dgamma, dbeta);
+    if (C == 64) launch_k(ln_bwd_mr_kernel<8>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
+    else if (C == 128) launch_k(ln_bwd_mr_kernel<16>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
+    else launch_k(ln_bwd_mr_kernel<32>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
+  } else if (aligned && C <= 32 * VEC) launch_k(ln_bwd_kernel<T, VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
+  else if (aligned && C <= 64 * VEC) launch_k(ln_bwd_kernel<T, 2 * VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
+  else if (aligned && C <= 128 * VEC) launch_k(ln_bwd_kernel<T, 4 * VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
+  else launch_k(ln_bwd_generic_kernel<T>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
+  if (dgamma_acc) launch_k(ln_bwd_reduce_acc_kernel, (2 * C + 31) / 32, 1024, 0, st, part, nblocks, C, dgamma_acc, dbeta_acc);
+  else launch_k(ln_bwd_reduce_kernel<T>, (2 * C + 31) / 32, 1024, 0, st, part, nblocks, C, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -698,13 +718,11 @@ int ffb_layernorm_fwd_transposed(const void* x, const void* gamma, const void* b
       attr = true;
     }
     const size_t smem64 = sizeof(float) * C * (LNT64 + 1);
-    ln_fwd_transposed64_kernel<<<(unsigned)((rows + LNT64 - 1) / LNT64), 256, smem64, st>>>(
-        (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
+    launch_k(ln_fwd_transposed64_kernel, (unsigned)((rows + LNT64 - 1) / LNT64), 256, smem64, st, (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
   }
   const size_t smem = sizeof(float) * C * (LNT_ROWS + 1);
-  ln_fwd_transposed_kernel<<<(unsigned)((rows + LNT_ROWS - 1) / LNT_ROWS), 256, smem, st>>>(
-      (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
+  launch_k(ln_fwd_transposed_kernel, (unsigned)((rows + LNT_ROWS - 1) / LNT_ROWS), 256, smem, st, (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

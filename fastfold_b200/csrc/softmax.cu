@@ -31,6 +31,8 @@ struct SoftmaxShape {
 template <typename T, int CPT>
 __global__ void __launch_bounds__(SM_WARPS * 32) softmax_fwd_kernel(const T* __restrict__ x, const T* __restrict__ mask,
                                                                    const T* __restrict__ bias, T* __restrict__ y, SoftmaxShape s) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
   if (row >= s.rows) return;
@@ -71,6 +73,8 @@ __global__ void __launch_bounds__(SM_WARPS * 32) softmax_fwd_kernel(const T* __r
 template <typename T>
 __global__ void __launch_bounds__(SM_WARPS * 32) softmax_fwd_loop_kernel(const T* __restrict__ x, const T* __restrict__ mask,
                                                                         const T* __restrict__ bias, T* __restrict__ y, SoftmaxShape s) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
   if (row >= s.rows) return;
@@ -96,6 +100,8 @@ __global__ void __launch_bounds__(SM_WARPS * 32) softmax_fwd_loop_kernel(const T
 template <typename T, int CPT>
 __global__ void __launch_bounds__(SM_WARPS * 32) softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                                    T* __restrict__ dx, long long rows, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -123,6 +129,8 @@ __global__ void __launch_bounds__(SM_WARPS * 32) softmax_bwd_kernel(const T* __r
 template <typename T>
 __global__ void __launch_bounds__(SM_WARPS * 32) softmax_bwd_loop_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                                         T* __restrict__ dx, long long rows, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -138,12 +146,12 @@ static int softmax_fwd_t(const T* x, const T* mask, const T* bias, T* y, Softmax
   const int cpt = (s.K + 31) / 32;
 #define FFB_SM_CASE(N)                                                                 \
   if (cpt <= N) {                                                                      \
-    softmax_fwd_kernel<T, N><<<grid, SM_WARPS * 32, 0, st>>>(x, mask, bias, y, s);     \
+    launch_k(softmax_fwd_kernel<T, N>, grid, SM_WARPS * 32, 0, st, x, mask, bias, y, s);     \
     return cudaGetLastError() == cudaSuccess ? 0 : -1;                                 \
   }
   FFB_SM_CASE(1) FFB_SM_CASE(2) FFB_SM_CASE(4) FFB_SM_CASE(8) FFB_SM_CASE(16) FFB_SM_CASE(32)
 #undef FFB_SM_CASE
-  softmax_fwd_loop_kernel<T><<<grid, SM_WARPS * 32, 0, st>>>(x, mask, bias, y, s);
+  launch_k(softmax_fwd_loop_kernel<T>, grid, SM_WARPS * 32, 0, st, x, mask, bias, y, s);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -153,12 +161,12 @@ static int softmax_bwd_t(const T* dy, const T* y, T* dx, long long rows, int K, 
   const int cpt = (K + 31) / 32;
 #define FFB_SM_CASE(N)                                                                 \
   if (cpt <= N) {                                                                      \
-    softmax_bwd_kernel<T, N><<<grid, SM_WARPS * 32, 0, st>>>(dy, y, dx, rows, K);      \
+    launch_k(softmax_bwd_kernel<T, N>, grid, SM_WARPS * 32, 0, st, dy, y, dx, rows, K);      \
     return cudaGetLastError() == cudaSuccess ? 0 : -1;                                 \
   }
   FFB_SM_CASE(1) FFB_SM_CASE(2) FFB_SM_CASE(4) FFB_SM_CASE(8) FFB_SM_CASE(16) FFB_SM_CASE(32)
 #undef FFB_SM_CASE
-  softmax_bwd_loop_kernel<T><<<grid, SM_WARPS * 32, 0, st>>>(dy, y, dx, rows, K);
+  launch_k(softmax_bwd_loop_kernel<T>, grid, SM_WARPS * 32, 0, st, dy, y, dx, rows, K);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

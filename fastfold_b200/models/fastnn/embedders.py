@@ -12,7 +12,7 @@ import torch
 import torch.nn as nn
 
 from ...utils.feats import build_template_angle_feat, build_template_pair_feat
-from ...utils.tensor_utils import tensor_tree_map
+from ...utils.tensor_utils import const_like, tensor_tree_map
 from ..nn import embedders as ref
 
 ROW_BLOCK = 256
@@ -41,7 +41,7 @@ class RecyclingEmbedder(ref.RecyclingEmbedder):
     def forward(self, m, z, x):
         bins = torch.linspace(self.min_bin, self.max_bin, self.no_bins, dtype=x.dtype, device=x.device, requires_grad=False)
         squared_bins = bins ** 2
-        upper = torch.cat([squared_bins[1:], squared_bins.new_tensor([self.inf])], dim=-1)
+        upper = torch.cat([squared_bins[1:], const_like(squared_bins, [self.inf], "inf_%r" % (self.inf,))], dim=-1)
         m_update = self.layer_norm_m(m)
         from ...ops import embed as kembed
         if kembed.recycle_pair_embed_supported(z, x):
@@ -79,7 +79,7 @@ class TemplateEmbedder(ref.TemplateEmbedder):
         offload = chunk_size is not None and 1 <= chunk_size <= 4 and z.is_cuda
         angles, pairs = [], []
         for i in range(n_templ):
-            idx = batch["template_aatype"].new_tensor(i)
+            idx = const_like(batch["template_aatype"], i, "templ_idx_%d" % i)
             single = tensor_tree_map(lambda t: torch.index_select(t, templ_dim, idx), batch)
             if self.config.embed_angles:
                 angles.append(self.template_angle_embedder(build_template_angle_feat(single)))
@@ -119,6 +119,23 @@ def inject_embedder(model):
             new.template_pair_embedder = old.template_pair_embedder
             new.template_pair_stack = old.template_pair_stack
             new.template_pointwise_att = old.template_pointwise_att
+            new.train(old.training)
+            model.template_embedder = new
+    else:
+        from . import embedders_multimer as mm
+        swap("input_embedder", mm.InputEmbedderMultimer, **c["input_embedder"])
+        if c.template.enabled and hasattr(model.template_embedder, "template_single_embedder"):
+            old = model.template_embedder
+            new = mm.TemplateEmbedderMultimer.__new__(mm.TemplateEmbedderMultimer)
+            nn.Module.__init__(new)
+            new.config = old.config
+            pe = mm.TemplatePairEmbedderMultimer.__new__(mm.TemplatePairEmbedderMultimer)
+            nn.Module.__init__(pe)
+            pe._modules.update(old.template_pair_embedder._modules)           # same parameter objects, lean forward
+            new.template_pair_embedder = pe
+            new.template_single_embedder = old.template_single_embedder
+            new.template_pair_stack = old.template_pair_stack
+            new.linear_t = old.linear_t
             new.train(old.training)
             model.template_embedder = new
     swap("recycling_embedder", RecyclingEmbedder, **c["recycling_embedder"])

@@ -307,8 +307,8 @@ class SelfAttention(nn.Module):
     def _bias(self, nonbatched_bias, transposed=False):
         if nonbatched_bias is None:
             return None
-        if nonbatched_bias[-1] == -1:
-            return nonbatched_bias[0]
+        if isinstance(nonbatched_bias[-1], int) and nonbatched_bias[-1] == -1:
+            return nonbatched_bias[0]          # already ``[b, h, q, k]`` (``pair_bias_hqk``)
         if transposed:      # projected from the un-transposed pair tensor [k, q_local, h]: gather the query axis
             b = gather_async_opp(*nonbatched_bias, dim=2)
             return b.permute(0, 3, 2, 1).contiguous()      # 'b k q h -> b h q k'
@@ -411,6 +411,23 @@ class SelfAttention(nn.Module):
             o, _ = self._one(in_data[:, ax:ax + CHUNK_SIZE], mask[:, ax:ax + CHUNK_SIZE], bias, None)
             outs.append(o)
         return torch.cat(outs, dim=1), False
+
+
+def pair_bias_hqk(Zn, weight):
+    """Pair bias of a row-sharded normalised pair tensor ``Zn [1, A/P, N, c]`` for attention over its second axis:
+    ``[1, H, A, N]`` with ``bias[h, q, k] = Zn[q, k] . weight[h]``.
+
+    On the GPU the projection GEMM stores its result channel-major (``[H, (q k)]``, transposed epilogue), so one rank's
+    slab of the bias is contiguous per head and the all-gather places the slabs straight into ``[H, q, k]`` order - the
+    layout the attention kernel's bias tiles are read from.  No ``'b q k h -> b h q k'`` copy exists, at any DAP size;
+    the gradient of the gathered bias comes back through the matching reduce-scatter.  Returns None when the shapes do
+    not fit that path (the caller then projects channel-last and permutes)."""
+    A, N, H = Zn.shape[1], Zn.shape[2], weight.shape[0]
+    if not (Zn.is_cuda and Zn.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and (A * N) % 8 == 0 and A * N >= 64
+            and Zn.shape[-1] % 8 == 0 and Zn.shape[-1] >= 64 and K.gemm_mod.NARROW_LINEAR_T):
+        return None
+    b_t = K.linear_t(Zn.reshape(A * N, Zn.shape[-1]), weight)            # [H, (q_local k)]
+    return gather(b_t.view(1, H, A, N), dim=2, reduce_grad=True)
 
 
 class GlobalAttention(nn.Module):
@@ -747,8 +764,12 @@ class _TriangleAttention(nn.Module):
             Z = Z_norm
         else:
             Z = self.layernorm1(Z_raw if (self.starting or strided) else Z_raw.transpose(-2, -3).contiguous())
-        b = self.linear_b(Z)
-        b, work = gather_async(b, dim=2 if strided else 1)
+        b = pair_bias_hqk(Z, self.linear_b.weight) if not strided else None
+        if b is not None:
+            work = -1
+        else:
+            b = self.linear_b(Z)
+            b, work = gather_async(b, dim=2 if strided else 1)
         tail = None
         if (self.starting or strided) and _fusable(Z_raw):
             tail = (self.out_bias, None if dropmask is None else _mask_idx(Z_raw, dropmask), Z_raw)
@@ -808,8 +829,12 @@ class ChunkMSARowAttentionWithPairBias(nn.Module):
             dropmask = None
         M = self.layernormM(M_raw)
         Zn = self.layernormZ(Z)
-        b = K.linear(Zn, self.linear_b_weights)
-        b, work = gather_async(b, dim=1)
+        b = pair_bias_hqk(Zn, self.linear_b_weights)
+        if b is not None:
+            work = -1
+        else:
+            b = K.linear(Zn, self.linear_b_weights)
+            b, work = gather_async(b, dim=1)
         tail = None
         if _fusable(M_raw):
             tail = (self.out_bias, None if dropmask is None else _mask_idx(M_raw, dropmask), M_raw)

@@ -80,7 +80,7 @@ class AlphaFold(nn.Module):
             asym = feats["asym_id"]
             multichain_mask_2d = asym[..., None] == asym[..., None, :]
             template_embeds = self.template_embedder(template_feats, z, pair_mask.to(dtype=z.dtype), len(batch_dims), self.globals.chunk_size,
-                                                     multichain_mask_2d=multichain_mask_2d)
+                                                     multichain_mask_2d=multichain_mask_2d, inplace=inplace)
             z = z + template_embeds["template_pair_embedding"]
             if "template_single_embedding" in template_embeds:
                 m = torch.cat([m, template_embeds["template_single_embedding"].to(m.dtype)], dim=-3)

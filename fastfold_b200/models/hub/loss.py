@@ -13,7 +13,7 @@ import torch.nn as nn
 from ...common import residue_constants as rc
 from ...utils import feats
 from ...utils.rigid_utils import Rigid, Rotation
-from ...utils.tensor_utils import batched_gather, masked_mean, permute_final_dims, tensor_tree_map, tree_map
+from ...utils.tensor_utils import batched_gather, const_like, masked_mean, permute_final_dims, tensor_tree_map, tree_map
 
 
 def softmax_cross_entropy(logits, labels):
@@ -86,7 +86,7 @@ def supervised_chi_loss(angles_sin_cos, unnormalized_angles_sin_cos, aatype, seq
     pred_angles = angles_sin_cos[..., 3:, :]
     residue_type_one_hot = torch.nn.functional.one_hot(aatype, rc.restype_num + 1)
     chi_pi_periodic = torch.einsum("...ij,jk->ik", residue_type_one_hot.type(angles_sin_cos.dtype),
-                                   angles_sin_cos.new_tensor(rc.chi_pi_periodic))
+                                   const_like(angles_sin_cos, rc.chi_pi_periodic, "chi_pi_periodic"))
     true_chi = chi_angles_sin_cos[None]
     shifted_mask = (1 - 2 * chi_pi_periodic).unsqueeze(-1)
     true_chi_shifted = shifted_mask * true_chi
@@ -243,15 +243,15 @@ def between_residue_clash_loss(atom14_pred_positions, atom14_atom_exists, atom14
     dists = torch.sqrt(eps + torch.sum((atom14_pred_positions[..., :, None, :, None, :] - atom14_pred_positions[..., None, :, None, :, :]) ** 2, dim=-1))
     dists_mask = (atom14_atom_exists[..., :, None, :, None] * atom14_atom_exists[..., None, :, None, :]).type(fp_type)
     dists_mask = dists_mask * (residue_index[..., :, None, None, None] < residue_index[..., None, :, None, None])
-    c_one_hot = torch.nn.functional.one_hot(residue_index.new_tensor(2), num_classes=14)
+    c_one_hot = torch.nn.functional.one_hot(const_like(residue_index, 2, "idx2"), num_classes=14)
     c_one_hot = c_one_hot.reshape(*((1,) * len(residue_index.shape[:-1])), *c_one_hot.shape).type(fp_type)
-    n_one_hot = torch.nn.functional.one_hot(residue_index.new_tensor(0), num_classes=14)
+    n_one_hot = torch.nn.functional.one_hot(const_like(residue_index, 0, "idx0"), num_classes=14)
     n_one_hot = n_one_hot.reshape(*((1,) * len(residue_index.shape[:-1])), *n_one_hot.shape).type(fp_type)
     neighbour_mask = (residue_index[..., :, None, None, None] + 1) == residue_index[..., None, :, None, None]
     c_n_bonds = neighbour_mask * c_one_hot[..., None, None, :, None] * n_one_hot[..., None, None, None, :]
     dists_mask = dists_mask * (1.0 - c_n_bonds)
     cys_sg_idx = rc.restype_name_to_atom14_names["CYS"].index("SG")
-    cys_sg_one_hot = torch.nn.functional.one_hot(residue_index.new_tensor(cys_sg_idx), num_classes=14)
+    cys_sg_one_hot = torch.nn.functional.one_hot(const_like(residue_index, cys_sg_idx, "cys_sg_idx"), num_classes=14)
     cys_sg_one_hot = cys_sg_one_hot.reshape(*((1,) * len(residue_index.shape[:-1])), *cys_sg_one_hot.shape)
     disulfide_bonds = cys_sg_one_hot[..., None, None, :, None] * cys_sg_one_hot[..., None, None, None, :]
     dists_mask = dists_mask * (1.0 - disulfide_bonds)
@@ -282,13 +282,14 @@ def within_residue_violations(atom14_pred_positions, atom14_atom_exists, atom14_
 def find_structural_violations(batch, atom14_pred_positions, violation_tolerance_factor, clash_overlap_tolerance, **kwargs):
     connection = between_residue_bond_loss(atom14_pred_positions, batch["atom14_atom_exists"], batch["residue_index"], batch["aatype"],
                                            tolerance_factor_soft=violation_tolerance_factor, tolerance_factor_hard=violation_tolerance_factor)
-    atomtype_radius = atom14_pred_positions.new_tensor([rc.van_der_waals_radius[name[0]] for name in rc.atom_types])
+    atomtype_radius = const_like(atom14_pred_positions, [rc.van_der_waals_radius[name[0]] for name in rc.atom_types], "vdw_radius")
     atom14_atom_radius = batch["atom14_atom_exists"] * atomtype_radius[batch["residx_atom14_to_atom37"]]
     clashes = between_residue_clash_loss(atom14_pred_positions, batch["atom14_atom_exists"], atom14_atom_radius, batch["residue_index"],
                                          overlap_tolerance_soft=clash_overlap_tolerance, overlap_tolerance_hard=clash_overlap_tolerance)
     bounds = rc.make_atom14_dists_bounds(overlap_tolerance=clash_overlap_tolerance, bond_length_tolerance_factor=violation_tolerance_factor)
-    lower = atom14_pred_positions.new_tensor(bounds["lower_bound"])[batch["aatype"]]
-    upper = atom14_pred_positions.new_tensor(bounds["upper_bound"])[batch["aatype"]]
+    bkey = "%r_%r" % (clash_overlap_tolerance, violation_tolerance_factor)
+    lower = const_like(atom14_pred_positions, bounds["lower_bound"], "atom14_lower_" + bkey)[batch["aatype"]]
+    upper = const_like(atom14_pred_positions, bounds["upper_bound"], "atom14_upper_" + bkey)[batch["aatype"]]
     within = within_residue_violations(atom14_pred_positions, batch["atom14_atom_exists"], lower, upper, tighten_bounds_for_loss=0.0)
     per_residue = torch.max(torch.stack([connection["per_residue_violation_mask"], torch.max(clashes["per_atom_clash_mask"], dim=-1)[0],
                                          torch.max(within["per_atom_violations"], dim=-1)[0]], dim=-1), dim=-1)[0]
@@ -377,7 +378,7 @@ class AlphaFoldLoss(nn.Module):
         losses["unscaled_loss"] = cum_loss.detach().clone()
         seq_len = torch.mean(batch["seq_length"].float())
         crop_len = batch["aatype"].shape[-1]
-        cum_loss = cum_loss * torch.sqrt(min(seq_len, crop_len))
+        cum_loss = cum_loss * torch.sqrt(torch.clamp(seq_len, max=float(crop_len)))      # min(seq_len, crop) without a host read
         losses["loss"] = cum_loss.detach().clone()
         if not _return_breakdown:
             return cum_loss

@@ -9,7 +9,7 @@ import torch
 import torch.nn as nn
 
 from ...utils.feats import build_template_angle_feat, build_template_pair_feat
-from ...utils.tensor_utils import dict_multimap, one_hot, tensor_tree_map
+from ...utils.tensor_utils import const_like, dict_multimap, one_hot, tensor_tree_map
 from .primitives import LayerNorm, Linear
 from .template import TemplatePairStack, TemplatePointwiseAttention
 
@@ -56,7 +56,7 @@ class RecyclingEmbedder(nn.Module):
         bins = torch.linspace(self.min_bin, self.max_bin, self.no_bins, dtype=x.dtype, device=x.device, requires_grad=False)
         m_update = self.layer_norm_m(m)
         squared_bins = bins ** 2
-        upper = torch.cat([squared_bins[1:], squared_bins.new_tensor([self.inf])], dim=-1)
+        upper = torch.cat([squared_bins[1:], const_like(squared_bins, [self.inf], "inf_%r" % (self.inf,))], dim=-1)
         d = torch.sum((x[..., None, :] - x[..., None, :, :]) ** 2, dim=-1, keepdims=True)
         d = ((d > squared_bins) * (d < upper)).type(x.dtype)
         z_update = self.linear(d.to(z.dtype)) + self.layer_norm_z(z)
@@ -108,7 +108,7 @@ class TemplateEmbedder(nn.Module):
         template_embeds = []
         n_templ = batch["template_aatype"].shape[templ_dim]
         for i in range(n_templ):
-            idx = batch["template_aatype"].new_tensor(i)
+            idx = const_like(batch["template_aatype"], i, "templ_idx_%d" % i)
             single = tensor_tree_map(lambda t: torch.index_select(t, templ_dim, idx), batch)
             emb = {}
             if self.config.embed_angles:

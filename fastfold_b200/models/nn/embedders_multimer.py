@@ -11,7 +11,7 @@ import torch.nn as nn
 
 from ...common import residue_constants as rc
 from ...utils.rigid_utils import Rigid
-from ...utils.tensor_utils import tensor_tree_map
+from ...utils.tensor_utils import const_like, tensor_tree_map
 from .primitives import LayerNorm, Linear
 from .template import TemplatePairStack
 
@@ -164,7 +164,7 @@ class TemplateEmbedderMultimer(nn.Module):
         dist = self.config.distogram
         acc = None
         for i in range(n_templ):
-            idx = batch["template_aatype"].new_tensor(i)
+            idx = const_like(batch["template_aatype"], i, "templ_idx_%d" % i)
             single = tensor_tree_map(lambda t: torch.index_select(t, templ_dim, idx).squeeze(templ_dim), batch)
             pos = single["template_all_atom_positions"].float()
             msk = single["template_all_atom_mask"].float()

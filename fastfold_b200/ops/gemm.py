@@ -274,10 +274,13 @@ class _LinearT(torch.autograd.Function):
         return dx, dw, db
 
 
+NARROW_LINEAR_T = True      # channel-major projections with fewer than 64 outputs (pair-bias heads) on the tcgen05 kernel
+
+
 def linear_t(x2, w, bias=None):
     """``(x2 @ w.T + bias).T`` as a contiguous ``[c_out, tokens]`` tensor."""
     ok = (x2.is_cuda and x2.dtype == torch.bfloat16 and x2.dim() == 2 and x2.shape[1] % 8 == 0 and x2.shape[0] % 8 == 0
-          and w.shape[0] >= 64 and w.shape[1] >= 64 and x2.shape[0] >= 64)
+          and (w.shape[0] >= 64 or NARROW_LINEAR_T) and w.shape[1] >= 64 and x2.shape[0] >= 64 and w.dtype == torch.bfloat16)
     if not ok:
         return torch.nn.functional.linear(x2, w, bias).t().contiguous()
     if torch.is_grad_enabled() and (x2.requires_grad or w.requires_grad or (bias is not None and bias.requires_grad)):

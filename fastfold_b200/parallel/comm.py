@@ -46,6 +46,18 @@ def _heap_for(t):
     return h if (nb % (16 * h.world) == 0 and 0 < nb <= h.max_message()) else None
 
 
+def _unit_ok(t, dim, parts, shrink_dim=None, shrink=1):
+    """True when the contiguous run behind ``dim`` (of ``t`` with ``dim`` split in ``parts``, and ``shrink_dim`` divided by
+    ``shrink``) is a whole number of 16-byte units - the granularity of the push collectives' placement."""
+    shape = list(t.shape)
+    if shrink_dim is not None:
+        shape[shrink_dim] //= shrink
+    run = shape[dim] // parts
+    for d in shape[dim + 1:]:
+        run *= d
+    return (run * t.element_size()) % 16 == 0
+
+
 def _reduce(tensor):
     if _P() == 1:
         return tensor
@@ -67,6 +79,8 @@ def _gather(tensor, dim=-1):
     dim = dim % tensor.dim()
     t = tensor.contiguous()
     h = _heap_for(t)
+    if h is not None and h.fits_push(t.numel() * t.element_size()) and _unit_ok(t, dim, 1):
+        return h.gather_dim(t, dim)          # one kernel, result already concatenated along ``dim``
     if h is not None:
         out = h.all_gather(None, t)
     else:
@@ -90,6 +104,12 @@ def _reduce_scatter(tensor, dim):
     size = divide(tensor.shape[dim], P)
     shape = list(tensor.shape)
     shape[dim] = size
+    if tensor.is_cuda and tensor.dtype == torch.bfloat16:
+        h = _heap_for(tensor)
+        if h is not None and h.fits_push(tensor.numel() * tensor.element_size() // P) and (tensor.numel() // P * tensor.element_size()) % 16 == 0 \
+                and _unit_ok(tensor, dim, P):
+            # one kernel: slice q of every rank lands in rank q's slot and is summed there in fp32
+            return h.reduce_scatter_dim(tensor, dim)
     # bring the P chunks to the front so that the collective works on one contiguous buffer
     t = tensor.reshape(shape[:dim] + [P, size] + shape[dim + 1:]).movedim(dim, 0).contiguous()
     h = _heap_for(t)
@@ -113,6 +133,11 @@ def _all_to_all(tensor, in_dim, out_dim):
     in_dim, out_dim = in_dim % tensor.dim(), out_dim % tensor.dim()
     size = divide(tensor.shape[in_dim], P)
     shape = list(tensor.shape)
+    if tensor.is_cuda:
+        h = _heap_for(tensor)
+        if h is not None and h.fits_push(tensor.numel() * tensor.element_size() // P) and _unit_ok(tensor, in_dim, P) \
+                and _unit_ok(tensor, out_dim, 1, in_dim, P):
+            return h.all_to_all_dims(tensor, in_dim, out_dim)     # one kernel, no permuted copies on either side
     send = tensor.reshape(shape[:in_dim] + [P, size] + shape[in_dim + 1:]).movedim(in_dim, 0).contiguous()
     h = _heap_for(send)
     if h is not None:

@@ -51,13 +51,23 @@ def broadcast_async_opp(tensor, work=None):
     return tensor
 
 
+class _Finished:
+    """``work`` of a collective whose kernel already produced the final layout (one-kernel push collectives)."""
+
+
+_FINISHED = _Finished()
+
+
 def _gather_async(tensor, dim):
     P = core.get_dap_size()
     if P == 1:
         return tensor, None
     t = tensor.contiguous()
-    from .comm import _heap_for
+    from .comm import _heap_for, _unit_ok
     h = _heap_for(t)
+    d = dim % t.dim()
+    if h is not None and h.fits_push(t.numel() * t.element_size()) and _unit_ok(t, d, 1):
+        return h.gather_dim(t, d), _FINISHED      # asynchronous on the stream; already concatenated along ``dim``
     if h is not None:
         return h.all_gather(None, t), None     # the kernels are asynchronous on the stream already
     out = torch.empty((P,) + tuple(t.shape), dtype=t.dtype, device=t.device)
@@ -66,6 +76,8 @@ def _gather_async(tensor, dim):
 
 
 def _finish_gather(out, work, dim):
+    if work is _FINISHED:
+        return out
     if work is not None:
         work.wait()
     if core.get_dap_size() == 1:
@@ -154,6 +166,10 @@ def all_to_all_async(x, in_dim, out_dim):
     in_d = in_dim % x.dim()
     size = divide(x.shape[in_d], P)
     shape = list(x.shape)
+    from .comm import _heap_for as _hf, _unit_ok
+    hp = _hf(x) if x.is_cuda else None
+    if hp is not None and hp.fits_push(x.numel() * x.element_size() // P) and _unit_ok(x, in_d, P) and _unit_ok(x, out_dim % x.dim(), 1, in_d, P):
+        return hp.all_to_all_dims(x, in_d, out_dim % x.dim()), _FINISHED
     send = x.reshape(shape[:in_d] + [P, size] + shape[in_d + 1:]).movedim(in_d, 0).contiguous()
     from .comm import _heap_for
     h = _heap_for(send)
@@ -165,7 +181,7 @@ def all_to_all_async(x, in_dim, out_dim):
 
 
 def all_to_all_async_opp(buf, work, in_dim, out_dim):
-    if core.get_dap_size() == 1 or work is None:
+    if core.get_dap_size() == 1 or work is None or work is _FINISHED:
         return buf
     if isinstance(work, _AsyncHandle):
         return _A2ASync.apply(work.src, work.in_dim, work.out_dim)

@@ -21,7 +21,9 @@ from . import core
 
 MAX_RANKS = 8
 MAX_SLOTS = 64
-FLAG_WORDS = MAX_SLOTS * 18
+# one-kernel collectives (every rank stores into the destination's slot); FASTFOLD_COMM_PUSH=0 selects publish + pull
+PUSH = os.environ.get("FASTFOLD_COMM_PUSH", "1") != "0"
+FLAG_WORDS = MAX_SLOTS * 19
 
 
 class SymmCtx(ctypes.Structure):
@@ -35,6 +37,8 @@ _SIG = {
     "ffb_symm_pull": [ctypes.POINTER(SymmCtx), _I, _L, _P, _L, _I, _P],
     "ffb_symm_a2a_layernorm": [ctypes.POINTER(SymmCtx), _I, _L, _I, _I, _I, _I, _P, _P, _P, _P, _F, _I, _P],
     "ffb_symm_allreduce_bf16": [ctypes.POINTER(SymmCtx), _I, _L, _L, _F, _P],
+    "ffb_symm_xchg": [ctypes.POINTER(SymmCtx), _I, _L, _P, _L, _L, _L, _I, _I, _P, _P],
+    "ffb_symm_xchg_layernorm": [ctypes.POINTER(SymmCtx), _I, _L, _P, _I, _I, _I, _I, _P, _P, _P, _P, _F, _I, _P],
     "ffb_symm_slot_fence": [ctypes.POINTER(SymmCtx), _I, _I, _P],
     "ffb_symm_consume_fence": [ctypes.POINTER(SymmCtx), _I, _I, _P],
     "ffb_symm_wait_never": [ctypes.POINTER(SymmCtx), _I, _P],
@@ -162,10 +166,73 @@ class SymmHeap:
         _lib.check(_libc().ffb_symm_pull(ctypes.byref(self.ctx), slot.index, slot.offset, _lib.ptr(dst), bytes_per_rank, 1 if all_to_all else 0,
                                          _lib.stream_ptr()), "symm_pull")
 
+    # -- one-kernel ("push") collectives -------------------------------------------------------------------
+    def fits_push(self, chunk_bytes):
+        """True when a push collective whose per-source-rank share is ``chunk_bytes`` fits a ring slot (the slot receives
+        one share from every rank) and the share is a whole number of 16-byte units."""
+        return PUSH and chunk_bytes % 16 == 0 and 0 < chunk_bytes * self.world <= self.max_message()
+
+    def _xchg(self, name, src, x1, x2, chunk_bytes, scatter, mode, out):
+        s = self.next_ring_slot(chunk_bytes * self.world) if name is None else self.slot(name, chunk_bytes * self.world)
+        _lib.check(_libc().ffb_symm_xchg(ctypes.byref(self.ctx), s.index, s.offset, _lib.ptr(src), x1, x2, chunk_bytes, 1 if scatter else 0, mode,
+                                         _lib.ptr(out), _lib.stream_ptr()), "symm_xchg")
+        return out
+
+    def gather_dim(self, x, dim, name=None):
+        """All-gather of ``x`` along ``dim`` in ONE kernel: every rank stores its shard into every rank's slot, waits
+        for the others' shards and copies them into the result already concatenated along ``dim``."""
+        x = x.contiguous()
+        dim = dim % x.dim()
+        nb = x.numel() * x.element_size()
+        lead = 1
+        for d in x.shape[:dim]:
+            lead *= d
+        shape = list(x.shape)
+        shape[dim] *= self.world
+        out = torch.empty(shape, dtype=x.dtype, device=x.device)
+        return self._xchg(name, x, 1, lead, nb, False, 1 if lead > 1 else 0, out)
+
+    def all_to_all_dims(self, x, in_dim, out_dim, name=None):
+        """Splits ``in_dim`` of ``x`` over the ranks and concatenates what arrives along ``out_dim``, in ONE kernel."""
+        x = x.contiguous()
+        in_dim, out_dim = in_dim % x.dim(), out_dim % x.dim()
+        P = self.world
+        shape = list(x.shape)
+        shape[in_dim] //= P
+        x1 = 1
+        for d in x.shape[:in_dim]:
+            x1 *= d
+        x2 = 1
+        for d in shape[:out_dim]:
+            x2 *= d
+        chunk = x.numel() * x.element_size() // P
+        oshape = list(shape)
+        oshape[out_dim] *= P
+        out = torch.empty(oshape, dtype=x.dtype, device=x.device)
+        return self._xchg(name, x, x1, x2, chunk, True, 1 if x2 > 1 else 0, out)
+
+    def reduce_scatter_dim(self, x, dim, name=None):
+        """Sum over the ranks, keep this rank's slice along ``dim`` (bf16 in / out, fp32 accumulation), in ONE kernel:
+        slice q of every rank is stored into rank q's slot and summed there."""
+        x = x.contiguous()
+        dim = dim % x.dim()
+        P = self.world
+        shape = list(x.shape)
+        shape[dim] //= P
+        x1 = 1
+        for d in x.shape[:dim]:
+            x1 *= d
+        chunk = x.numel() * x.element_size() // P
+        out = torch.empty(shape, dtype=x.dtype, device=x.device)
+        return self._xchg(name, x, x1, 1, chunk, True, 2, out)
+
     def all_gather(self, name, x):
         """Stacks ``x`` of every rank along a new leading dimension: ``[P, *x.shape]``."""
         x = x.contiguous()
         nb = x.numel() * x.element_size()
+        if self.fits_push(nb):
+            out = torch.empty((self.world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+            return self._xchg(name, x, 1, 1, nb, False, 0, out)
         s = self.next_ring_slot(nb) if name is None else self.slot(name, nb)
         self.publish(s, x)
         out = torch.empty((self.world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
@@ -176,6 +243,8 @@ class SymmHeap:
         """``send [P, ...]``: chunk q goes to rank q; returns ``recv [P, ...]`` with chunk r coming from rank r."""
         send = send.contiguous()
         nb = send.numel() * send.element_size()
+        if self.fits_push(nb // self.world):
+            return self._xchg(name, send, 1, 1, nb // self.world, True, 0, torch.empty_like(send))
         s = self.next_ring_slot(nb) if name is None else self.slot(name, nb)
         self.publish(s, send)
         recv = torch.empty_like(send)
@@ -183,17 +252,24 @@ class SymmHeap:
         return recv
 
     def a2a_layer_norm(self, name, x, mode, A, B, C, gamma, beta, eps, want_raw=True, transpose_norm=False):
-        """Axis switch of the shard ``x`` fused with LayerNorm (see csrc/comm_p2p.cu ``symm_a2a_ln_k``)."""
+        """Axis switch of the shard ``x`` fused with LayerNorm: one kernel that stores the shard's rows into the
+        destination ranks' slots and normalises what arrives (csrc/comm_p2p.cu ``symm_xchg_ln_k``); the two-kernel
+        publish + pull form (``symm_a2a_ln_k``) remains for ``FASTFOLD_COMM_PUSH=0``."""
         x = x.contiguous()
         nb = x.numel() * x.element_size()
-        s = self.next_ring_slot(nb) if name is None else self.slot(name, nb)
-        self.publish(s, x)
         P = self.world
         Ad, Bd = (A, B // P) if mode == 0 else (A // P, B)
         raw = torch.empty(Ad, Bd, C, dtype=x.dtype, device=x.device) if want_raw else None
         norm = None
         if gamma is not None:
             norm = torch.empty((Bd, Ad, C) if transpose_norm else (Ad, Bd, C), dtype=x.dtype, device=x.device)
+        s = self.next_ring_slot(nb) if name is None else self.slot(name, nb)
+        if PUSH:
+            _lib.check(_libc().ffb_symm_xchg_layernorm(ctypes.byref(self.ctx), s.index, s.offset, _lib.ptr(x), mode, A, B, C, _lib.ptr(raw),
+                                                       _lib.ptr(norm), _lib.ptr(gamma), _lib.ptr(beta), float(eps), 1 if transpose_norm else 0,
+                                                       _lib.stream_ptr()), "symm_xchg_layernorm")
+            return raw, norm
+        self.publish(s, x)
         _lib.check(_libc().ffb_symm_a2a_layernorm(ctypes.byref(self.ctx), s.index, s.offset, mode, A, B, C, _lib.ptr(raw), _lib.ptr(norm),
                                                   _lib.ptr(gamma), _lib.ptr(beta), float(eps), 1 if transpose_norm else 0, _lib.stream_ptr()),
                    "symm_a2a_layernorm")

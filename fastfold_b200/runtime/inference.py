@@ -13,37 +13,46 @@ import numpy as np
 import torch
 
 
-def _worker(rank, world, port, batch, opts, queue):
-    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+def load_model(model_name="model_1", param_path=None, chunk_size=None, inplace=False, overrides=None, seed=0, device=None, bf16=True):
+    """Builds the model a prediction runs: ``AlphaFold(model_config(model_name))`` (+ an AlphaFold parameter archive when
+    ``param_path`` exists), fast trunk swapped in, eval mode, on ``device`` in bf16 (GPU) or fp32 (CPU).  ``init_dap`` must
+    have been called.  Sets the process-wide chunk size, as the reference's inference.py:129-145 does."""
     from ..config import model_config
     from ..models.fastnn import set_chunk_size
     from ..models.hub import AlphaFold
-    from ..parallel import init_dap, shutdown
     from ..utils.import_weights import import_jax_weights_
     from ..utils.inject_fastnn import inject_fastnn
-    init_dap()
     cuda = torch.cuda.is_available()
-    device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
-    config = model_config(opts["model_name"])
-    config.globals.chunk_size = opts.get("chunk_size")
-    config.globals.inplace = bool(opts.get("inplace", False))
-    for k, v in (opts.get("overrides") or {}).items():
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+    config = model_config(model_name)
+    config.globals.chunk_size = chunk_size
+    config.globals.inplace = bool(inplace)
+    for k, v in (overrides or {}).items():
         node = config
         parts = k.split(".")
         for p in parts[:-1]:
             node = node[p]
         node[parts[-1]] = v
-    torch.manual_seed(opts.get("seed", 0))
+    torch.manual_seed(seed)
     model = AlphaFold(config)
-    if opts.get("param_path") and os.path.exists(opts["param_path"]):
-        import_jax_weights_(model, opts["param_path"], version=opts["model_name"])
+    if param_path and os.path.exists(param_path):
+        import_jax_weights_(model, param_path, version=model_name)
     model = inject_fastnn(model).eval()
-    model = model.to(device=device, dtype=torch.bfloat16 if (cuda and opts.get("bf16", True)) else torch.float32)
+    model = model.to(device=device, dtype=torch.bfloat16 if (device.type == "cuda" and bf16) else torch.float32)
     set_chunk_size(config.globals.chunk_size)
-    batch = {k: torch.as_tensor(v).to(device) for k, v in batch.items()}
+    return model
+
+
+def predict(model, batch):
+    """One prediction: ``batch`` (features with the recycling dimension last; host or device tensors / arrays) is moved
+    to the model's device, the model runs without gradients, and the outputs come back as device tensors together with
+    the device-timed seconds of the model call.  Raises on every rank if a kernel reported a failed wait."""
+    device = next(model.parameters()).device
+    cuda = device.type == "cuda"
+    batch = {k: torch.as_tensor(v).to(device, non_blocking=True) for k, v in batch.items()}
     with torch.no_grad():
         if cuda:
-            torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         t0 = time.perf_counter()
@@ -56,6 +65,19 @@ def _worker(rank, world, port, batch, opts, queue):
             check_device_status()        # a kernel that gave up on a wait leaves unwritten outputs: fail on every rank
         else:
             seconds = time.perf_counter() - t0
+    return out, seconds
+
+
+def _worker(rank, world, port, batch, opts, queue):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from ..parallel import init_dap, shutdown
+    init_dap()
+    cuda = torch.cuda.is_available()
+    model = load_model(opts["model_name"], opts.get("param_path"), opts.get("chunk_size"), opts.get("inplace", False), opts.get("overrides"),
+                       opts.get("seed", 0), bf16=opts.get("bf16", True))
+    if cuda:
+        torch.cuda.synchronize()
+    out, seconds = predict(model, batch)
     peak = torch.cuda.max_memory_allocated() / 2 ** 30 if cuda else 0.0
     if rank == 0:
         res = {k: v.float().cpu().numpy() for k, v in out.items() if isinstance(v, torch.Tensor)}

@@ -9,14 +9,14 @@ import torch.nn as nn
 
 from ..common import residue_constants as rc
 from .rigid_utils import Rigid, Rotation
-from .tensor_utils import batched_gather, one_hot
+from .tensor_utils import batched_gather, const_like, one_hot
 
 
 def dgram_from_positions(pos, min_bin=3.25, max_bin=50.75, no_bins=39, inf=1e8):
     """One-hot distance histogram ``[*, N, N, no_bins]`` of the pairwise distances of ``pos [*, N, 3]``."""
     dgram = torch.sum((pos[..., None, :] - pos[..., None, :, :]) ** 2, dim=-1, keepdim=True)
     lower = torch.linspace(min_bin, max_bin, no_bins, device=pos.device) ** 2
-    upper = torch.cat([lower[1:], lower.new_tensor([inf])], dim=-1)
+    upper = torch.cat([lower[1:], const_like(lower, [inf], "inf_%r" % (inf,))], dim=-1)
     return ((dgram > lower) * (dgram < upper)).type(dgram.dtype)
 
 

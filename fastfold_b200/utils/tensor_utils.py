@@ -134,3 +134,18 @@ def chunk_layer(layer, inputs, chunk_size, no_batch_dims):
         i += chunk_size
     reshape = lambda t: t.view(orig_batch_dims + t.shape[1:])
     return tensor_tree_map(reshape, out)
+
+
+_CONST_CACHE = {}
+
+
+def const_like(ref, data, key):
+    """``ref.new_tensor(data)``, cached per (key, device, dtype): small constant tables (bin edges, radii, one-hot
+    indices) are uploaded once instead of on every call, which also keeps host-to-device copies out of CUDA-graph
+    capture.  ``key`` names the constant (include any parameter the data depends on)."""
+    k = (key, ref.device, ref.dtype)
+    t = _CONST_CACHE.get(k)
+    if t is None:
+        t = ref.new_tensor(data)
+        _CONST_CACHE[k] = t
+    return t

@@ -155,3 +155,32 @@ def test_outer_product_mean_core_gradients(device_status):
     for got, want, name in zip((l2, r2, w, b, z2), fl, "l r w b z".split()):
         err = (got.grad.float() - want.grad).abs().max().item()
         assert err < 3e-2 * max(1.0, want.grad.abs().max().item()), (name, err)
+
+
+@pytest.mark.parametrize("heads,tokens", [(8, 4096), (4, 2048), (8, 520)])
+def test_narrow_channel_major_projection(heads, tokens, device_status):
+    """Pair-bias projection stored channel-major (``[H, tokens]``), forward and all three gradients, H < 64."""
+    from fastfold_b200.ops import linear_t
+    c = 128
+    x = _rand(tokens, c).requires_grad_(True)
+    w = _rand(heads, c, scale=0.1).requires_grad_(True)
+    y = linear_t(x, w)
+    assert y.shape == (heads, tokens) and y.is_contiguous()
+    ref = (x.detach().float() @ w.detach().float().t()).t()
+    _close(y, ref, c)
+    dy = _rand(heads, tokens)
+    y.backward(dy)
+    dx_ref = dy.float().t() @ w.detach().float()
+    dw_ref = dy.float() @ x.detach().float()
+    _close(x.grad, dx_ref, heads)
+    _close(w.grad, dw_ref, tokens)
+
+
+def test_pair_bias_hqk_matches_permuted_projection(device_status):
+    from fastfold_b200.models.fastnn.ops import pair_bias_hqk
+    zn = _rand(1, 64, 64, 128)
+    w = _rand(8, 128, scale=0.1)
+    b = pair_bias_hqk(zn, w)
+    ref = torch.einsum("bqkc,hc->bhqk", zn.float(), w.float())
+    assert b is not None and b.shape == (1, 8, 64, 64)
+    _close(b, ref, 128)

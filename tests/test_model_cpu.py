@@ -173,7 +173,7 @@ def test_padded_head_weights_reproduce_the_layer():
     import torch
     from fastfold_b200.models.fastnn.ops import SelfAttention
     torch.manual_seed(0)
-    att = SelfAttention(16, 8, 2, 16, gating=True)
+    att = SelfAttention(16, 8, 2, 16, gating=True).eval()      # the cache below applies to eval mode only
     with torch.no_grad():
         for p in att.parameters():
             p.copy_(torch.randn_like(p))
@@ -192,3 +192,9 @@ def test_padded_head_weights_reproduce_the_layer():
     with torch.no_grad():
         att.to_qkv.weight.mul_(2.0)
     assert att._padded_heads()[0] is not wq
+    # in training mode nothing is cached: an optimiser that writes the parameters through raw pointers bumps no version
+    att.train()
+    first = att._padded_heads()[0]
+    att.to_qkv.weight.data.view(-1)[0] = 123.0
+    again = att._padded_heads()[0]
+    assert again is not first and float(again.reshape(-1)[0]) == 123.0

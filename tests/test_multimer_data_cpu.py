@@ -101,3 +101,36 @@ def test_multimer_fasta_to_structure(tmp_path):
     pdb = protein.to_pdb(protein.from_prediction(f, {k: v.numpy() for k, v in out.items() if isinstance(v, torch.Tensor)}))
     chains = {ln[21] for ln in pdb.splitlines() if ln.startswith("ATOM")}
     assert chains == {"A", "B"}
+
+
+def test_lean_multimer_embedders_match_reference_modules():
+    """``inject_fastnn`` swaps in the lean multimer embedders (table-lookup relative positions, stacked single-channel
+    projections, in-place template accumulation); outputs equal the OpenFold-layout modules'."""
+    import copy
+    import torch
+    from fastfold_b200.config import model_config
+    from fastfold_b200.models.fastnn import embedders_multimer as fmm
+    from fastfold_b200.models.hub import AlphaFold
+    from fastfold_b200.utils.inject_fastnn import inject_fastnn
+    from fastfold_b200.utils.synthetic import random_features
+    cfg = model_config("multimer")
+    cfg.model.evoformer_stack.no_blocks = 1
+    cfg.model.extra_msa.extra_msa_stack.no_blocks = 1
+    torch.manual_seed(0)
+    base = AlphaFold(cfg).eval()
+    with torch.no_grad():
+        for p in base.parameters():
+            if p.dim() >= 2 and float(p.abs().sum()) == 0.0:
+                p.normal_(0.0, 0.05)
+    fast = inject_fastnn(copy.deepcopy(base)).eval()
+    assert isinstance(fast.input_embedder, fmm.InputEmbedderMultimer)
+    assert isinstance(fast.template_embedder, fmm.TemplateEmbedderMultimer)
+    feats = random_features(20, 6, 8, n_templ=2, n_recycle=0, seed=1, chains=[12, 8])
+    one = {k: v[..., 0] for k, v in feats.items()}
+    with torch.no_grad():
+        m0, z0 = base.input_embedder(one)
+        m1, z1 = fast.input_embedder(one)
+        assert torch.allclose(m0, m1, atol=1e-5) and torch.allclose(z0, z1, atol=1e-5)
+        out0, out1 = base(feats), fast(feats)
+    assert torch.allclose(out0["final_atom_positions"], out1["final_atom_positions"], atol=5e-3)
+    assert torch.allclose(out0["pair"], out1["pair"], atol=2e-3)

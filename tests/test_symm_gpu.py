@@ -76,6 +76,36 @@ def _worker(rank, world, port, out_path):
                 wn = wn.transpose(0, 1)
             a2a_err = max(a2a_err, float((raw.float() - want.float()).abs().max()), float((norm.float() - wn).abs().max()))
     res["a2a_ln"] = a2a_err
+    # one-kernel push collectives against compositions of NCCL calls
+    push_err = 0.0
+    for dim in (0, 1, 2):
+        x = torch.randn(6, 10, 16, generator=g).to(dev, torch.bfloat16)
+        skew(dim)
+        got = h.gather_dim(x, dim)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        push_err = max(push_err, float((got.float() - torch.cat(parts, dim=dim).float()).abs().max()))
+    for in_dim, out_dim in ((1, 2), (2, 1), (0, 2)):
+        shape = [4, 8 * world // 2, 8 * world // 2, 16]
+        x = torch.randn(*shape, generator=g).to(dev, torch.bfloat16)
+        in_d, out_d = in_dim + (0 if in_dim == 0 else 0), out_dim
+        skew(in_dim + out_dim)
+        got = h.all_to_all_dims(x, in_d, out_d)
+        send = list(x.chunk(world, dim=in_d))
+        recv = [torch.empty_like(send[0]) for _ in range(world)]
+        dist.all_to_all(recv, [t.contiguous() for t in send])
+        push_err = max(push_err, float((got.float() - torch.cat(recv, dim=out_d).float()).abs().max()))
+    res["push_copy"] = push_err
+    rs_err = 0.0
+    for dim in (0, 1):
+        x = torch.randn(8 * world // 2, 4 * world, 24, generator=g).to(dev, torch.bfloat16)
+        skew(dim)
+        got = h.reduce_scatter_dim(x, dim)
+        full = x.float().clone()
+        dist.all_reduce(full)
+        want = full.chunk(world, dim=dim)[rank]
+        rs_err = max(rs_err, float((got.float() - want).abs().max() / (want.abs().max() + 1e-6)))
+    res["push_reduce_scatter"] = rs_err
     # all-reduce of a vector living in the heap, replayed from a CUDA graph
     n = 8 * 1000
     slot = h.slot("t_grads", n * 2)
@@ -130,6 +160,8 @@ def test_symm_collectives(world):
     assert res["all_gather"] == 0.0
     assert res["all_to_all"] == 0.0
     assert res["a2a_ln"] < 5e-2
+    assert res["push_copy"] == 0.0
+    assert res["push_reduce_scatter"] < 1e-2
     assert res["all_reduce"] < 1e-2 and res["all_reduce_graph"] < 1e-2
     assert res["status_before"] == 0
     assert res["status_after"] == 4 and 0.5 < res["timeout_s"] < 10
