@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--recycles", type=int, default=3, help="(inference) recycling iterations after the first pass")
     ap.add_argument("--chunk-size", type=int, default=64)
     ap.add_argument("--no-inplace", action="store_true")
+    ap.add_argument("--shard-pair", action="store_true", help="(inference, ours) keep the pair tensor row-sharded end to end")
+    ap.add_argument("--no-e2e", action="store_true", help="(inference) skip the end-to-end repetition (saves one full call per step)")
     a = ap.parse_args()
     if a.metric == "inference":
         # one call is seconds long: fewer repetitions unless asked for explicitly
@@ -393,10 +395,10 @@ def _inference_json(args, world, impl, ms, e2e_ms, clocks, h2d, d2h, peak_gib, e
         "data": "synthetic features (one-hot / Bernoulli / Dirichlet as in the training benchmark), random-init weights", "impl": impl,
         "config": {"model": "AlphaFold monomer (model_3 layout: 4 extra-MSA blocks, 48 Evoformer blocks, 8 structure-module iterations, no templates)",
                    "global_batch": 1, "seq_len": args.n_res, "n_seq": args.n_seq, "n_extra": args.n_extra, "recycles": args.recycles,
-                   "chunk_size": args.chunk_size, "inplace": not args.no_inplace, "parallelism": "dap%d" % world,
+                   "chunk_size": args.chunk_size, "inplace": not args.no_inplace, "parallelism": "dap%d" % world, "pair_sharded": bool(args.shard_pair),
                    "l2": "inputs and activations far larger than L2 (pair tensor %.0f MB)" % (args.n_res * args.n_res * 128 * 2 / 1e6)},
         "clocks": clocks,
-        "e2e": {"value": e2e_ms / 1e3, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": None if e2e_ms is None else e2e_ms / 1e3, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "peak_gib_per_gpu": peak_gib,
     }
     out.update(extra)
@@ -420,6 +422,8 @@ def _time_inference(torch, dist, args, device, call, feats):
     fence(torch, dist)
     ms = max_over_ranks(torch, dist, e0.elapsed_time(e1) / args.steps, device)
     del dev_feats
+    if args.no_e2e:
+        return ms, None, sampler.stop(), 0
     # end to end: features from pinned host memory every call, predicted coordinates read back to the host
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     fence(torch, dist)
@@ -446,7 +450,8 @@ def run_ours_inference(args):
     init_dap(world)
     assert torch.cuda.is_available(), "the inference benchmark needs a GPU"
     device = torch.device("cuda", torch.cuda.current_device())
-    model = load_model("model_3", None, chunk_size=args.chunk_size, inplace=not args.no_inplace, seed=1234, device=device)
+    model = load_model("model_3", None, chunk_size=args.chunk_size, inplace=not args.no_inplace, seed=1234, device=device,
+                       shard_pair=args.shard_pair)
     feats = inference_features(torch, args)
     h2d = sum(v.numel() * v.element_size() for v in feats.values())
     _lib.LAUNCHES[0] = 0

@@ -4,6 +4,7 @@
     python benchmark/kernel_bench.py attention [--b 128 --h 8 --len 256] [--backward]
     python benchmark/kernel_bench.py layernorm [--rows 65536 --c 128] [--backward]
     python benchmark/kernel_bench.py global_attention [--b 256 --len 5120 --h 8]
+    python benchmark/kernel_bench.py floor     (per-launch floor of small dependent kernels inside a CUDA graph)
     python benchmark/kernel_bench.py all
 
 Every timing is taken on the device: the op is captured ``--iters`` times in a CUDA graph, each instance preceded
@@ -170,9 +171,55 @@ def bench_global_attention(t, R, S, H):
     print("global attention R=%d S=%d H=%d c=8: %.1f us  (%.0f GB/s -> %.2f %s)" % (R, S, H, us, byt / us / 1e3, byt / hbm * 1e6 / us, tag))
 
 
+def bench_floor(iters):
+    """Per-launch time of back-to-back DEPENDENT launches inside one CUDA graph (warm cache): the floor every small
+    kernel of a DAP-sharded step pays, for the kernels of this package, a PyTorch elementwise kernel and cuBLAS.  Each op
+    consumes the previous one's output so that the launches serialise as they do in the model."""
+    n = max(iters, 50)
+    rows = {}
+    for (M, N, Kd) in [(128, 128, 128), (4096, 256, 256), (4096, 1024, 256), (16384, 128, 128)]:
+        a = _rand(M, Kd)
+        w = _rand(N, Kd, scale=0.05)
+        w2 = _rand(Kd, N, scale=0.05)
+
+        def ours():
+            y = K.gemm(a, w)
+            return K.gemm(y, w2)
+
+        def cublas():
+            y = torch.matmul(a, w.t())
+            return torch.matmul(y, w2.t())
+        rows["gemm %dx%dx%d" % (M, N, Kd)] = (_graph_time(ours, n) / 2, _graph_time(cublas, n) / 2)
+    x = _rand(4096, 256)
+    g, b = _rand(256), _rand(256)
+
+    def ln2():
+        y = K.layer_norm(x, g, b, 1e-5)
+        return K.layer_norm(y, g, b, 1e-5)
+
+    def tln2():
+        y = torch.nn.functional.layer_norm(x, (256,), g, b, 1e-5)
+        return torch.nn.functional.layer_norm(y, (256,), g, b, 1e-5)
+    rows["layernorm 4096x256"] = (_graph_time(ln2, n) / 2, _graph_time(tln2, n) / 2)
+
+    def add2():
+        y = x + x
+        return y + x
+    t_add = _graph_time(add2, n) / 2
+    rows["torch add 4096x256"] = (t_add, t_add)
+    qkv = (_rand(1, 16, 256, 3, 8, 32) * 0.5)
+
+    def att():
+        return flash.flash_attention_packed(qkv, None, None, 32 ** -0.5)
+    rows["attention B16 H8 n256"] = (_graph_time(att, n), float("nan"))
+    print("per-launch time inside a CUDA graph, dependent launches, warm cache (us): ours | library")
+    for k, (a_, b_) in rows.items():
+        print("  %-26s %8.2f | %8.2f" % (k, a_, b_))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "global_attention", "all"])
+    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "global_attention", "floor", "all"])
     ap.add_argument("--m", type=int, default=65536)
     ap.add_argument("--n", type=int, default=512)
     ap.add_argument("--k", type=int, default=128)
@@ -194,6 +241,8 @@ def main():
         bench_attention(t, args.b, args.h, args.len, args.backward)
     elif args.op == "layernorm":
         bench_layernorm(t, args.rows, args.c, args.backward)
+    elif args.op == "floor":
+        bench_floor(args.iters)
     elif args.op == "global_attention":
         bench_global_attention(t, args.b if args.b != 128 else 256, args.len if args.len != 256 else 5120, args.h)
     else:

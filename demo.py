@@ -24,6 +24,8 @@ def main():
     ap.add_argument("--param_path", type=str, default=None)
     ap.add_argument("--chunk_size", type=int, default=None)
     ap.add_argument("--inplace", default=False, action="store_true")
+    ap.add_argument("--shard_pair", default=False, action="store_true",
+                    help="with --gpus > 1: keep the pair tensor row-sharded from the embedders to the heads (long sequences)")
     ap.add_argument("--output", type=str, default=None, help="write the prediction as PDB")
     args = ap.parse_args()
     from fastfold_b200.common import protein
@@ -31,7 +33,7 @@ def main():
     from fastfold_b200.utils.synthetic import random_features
     batch = random_features(args.n_res, args.n_seq, args.n_extra, n_templ=args.n_templ, n_recycle=args.recycles, seed=0)
     out = run_inference(batch, gpus=args.gpus, model_name=args.model_name, param_path=args.param_path, chunk_size=args.chunk_size,
-                        inplace=args.inplace)
+                        inplace=args.inplace, shard_pair=args.shard_pair)
     print("Inference time: %.3f s   peak memory: %.2f GiB   mean pLDDT: %.1f" % (out["_seconds"], out["_peak_gib"], float(out["plddt"].mean())))
     if args.output:
         feats = {"aatype": batch["aatype"][..., 0].numpy(), "residue_index": batch["residue_index"][..., 0].numpy()}

@@ -180,7 +180,7 @@ def _base_config():
             "data_module": {"use_small_bfd": False, "data_loaders": {"batch_size": 1, "num_workers": 16}},
         },
         "globals": {"blocks_per_ckpt": blocks_per_ckpt, "chunk_size": chunk_size, "c_z": c_z, "c_m": c_m, "c_t": c_t, "c_e": c_e, "c_s": c_s,
-                    "eps": eps, "inplace": False, "is_multimer": False},
+                    "eps": eps, "inplace": False, "is_multimer": False, "shard_pair": False},
         "model": {
             "_mask_trans": False,
             "input_embedder": {"tf_dim": 22, "msa_dim": 49, "c_z": c_z, "c_m": c_m, "relpos_k": 32},

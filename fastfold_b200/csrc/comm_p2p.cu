@@ -454,7 +454,8 @@ __device__ __forceinline__ void xchg_finish(const SymmCtx& c, int slot, uint32_t
     s_last2 = (atomicAdd(blk, 1u) == gridDim.x - 1) ? 1 : 0;
     if (s_last2) {
       *blk = 0;
-      __threadfence_system();
+      // `done` only tells the peers that this rank has finished READING its slot (the values were consumed by the
+      // stores above, so the loads have completed): the release stores below suffice, no system-scope fence
       for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_done(slot, c.rank), epoch);
       c.flags[c.rank][w_epoch(slot)] = epoch;
     }

@@ -344,6 +344,183 @@ __global__ void __launch_bounds__(GA_THREADS, 2) global_attention_cluster_kernel
   }
 }
 
+// ---------------------------------------------------------------------------
+// Backward of the kernel above (training of the extra-MSA stack).  Per column r, with g = sigmoid(gate + b),
+// w = softmax over s of q[h].k[s] (masked keys at -1e9) and o[h] = sum_s w[h][s] v[s]:
+//     d_o[h][i]    = sum_s dout[s][h*c+i] * g[s][h*c+i]
+//     d_gate[s][j] = dout[s][j] * o[j] * g (1 - g)            (gradient w.r.t. the pre-activation; the bias gradient is its column sum)
+//     d_w[h][s]    = d_o[h] . v[s],   d_logit[h][s] = w[h][s] (d_w[h][s] - d_o[h] . o[h])        (0 for masked keys: their logit is a constant)
+//     d_q[h]       = sum_s d_logit[h][s] k[s],   d_k[s] = sum_h d_logit[h][s] q[h],   d_v[s] = sum_h w[h][s] d_o[h]
+// Pass A streams (k | v) for the softmax statistics and o (as the forward does) and gate / dout for d_o; pass B streams
+// them again and writes d_kv and d_gate.  One CTA per column; thread t works on head t % H and sequence lane t / H in the
+// attention parts and on channel t % (H c) in the gating parts.  The PyTorch composite this replaces materialises the
+// [R, H, S] logits and weights and a broadcast copy of o (fastfold/model/fastnn/ops.py:1175-1236).
+// ---------------------------------------------------------------------------
+template <int C>
+__global__ void __launch_bounds__(GA_THREADS) global_attention_bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
+                                                                          const bf16* __restrict__ mask, const bf16* __restrict__ gate,
+                                                                          const bf16* __restrict__ gate_bias, const bf16* __restrict__ dout,
+                                                                          float* __restrict__ dq, bf16* __restrict__ dkv,
+                                                                          bf16* __restrict__ dgate, int S, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int lanes = GA_THREADS / H;
+  const int HC = H * C;
+  float* s_m = sm;                        // [lanes][H]
+  float* s_l = s_m + GA_THREADS;          // [lanes][H]
+  float* s_acc = s_l + GA_THREADS;        // [lanes][H][C]   (also the d_q fold buffer)
+  float* s_o = s_acc + GA_THREADS * C;    // [H][C]
+  float* s_do = s_o + HC;                 // [H][C]
+  float* s_b = s_do + HC;                 // [H][C]
+  float* s_mt = s_b + HC;                 // [H] final max
+  float* s_il = s_mt + H;                 // [H] 1 / final sum
+  float* s_dl = s_il + H;                 // [H] d_o . o
+  float* s_dofold = s_dl + H;             // [GA_THREADS / HC][HC] partial d_o
+  const long long r = blockIdx.x;
+  const int h = threadIdx.x % H, sl = threadIdx.x / H;
+  float qv[C];
+#pragma unroll
+  for (int i = 0; i < C; ++i) qv[i] = __bfloat162float(q[(r * H + h) * C + i]);
+  for (int i = threadIdx.x; i < HC; i += GA_THREADS) s_b[i] = __bfloat162float(gate_bias[i]);
+  const bf16* kvr = kv + r * (long long)S * 2 * C;
+  const bf16* mr = mask + r * (long long)S;
+  const bf16* gr = gate + r * (long long)S * HC;
+  const bf16* dor = dout + r * (long long)S * HC;
+  __syncthreads();
+  // ---- pass A.1: softmax statistics and o ----
+  float m = -INFINITY, l = 0.f, acc[C];
+#pragma unroll
+  for (int i = 0; i < C; ++i) acc[i] = 0.f;
+  for (int s = sl; s < S; s += lanes) {
+    float d = 0.f, vv[C];
+#pragma unroll
+    for (int i = 0; i < C; ++i) {
+      d = fmaf(qv[i], __bfloat162float(kvr[(long long)s * 2 * C + i]), d);
+      vv[i] = __bfloat162float(kvr[(long long)s * 2 * C + C + i]);
+    }
+    if (__bfloat162float(mr[s]) == 0.f) d = GA_MASKED;
+    const float mn = fmaxf(m, d);
+    const float a = __expf(m - mn), p = __expf(d - mn);
+    l = l * a + p;
+#pragma unroll
+    for (int i = 0; i < C; ++i) acc[i] = fmaf(p, vv[i], acc[i] * a);
+    m = mn;
+  }
+  s_m[sl * H + h] = m;
+  s_l[sl * H + h] = l;
+#pragma unroll
+  for (int i = 0; i < C; ++i) s_acc[(sl * H + h) * C + i] = acc[i];
+  // ---- pass A.2: d_o[j] = sum_s dout[s][j] * sigmoid(gate[s][j] + b[j]) ----
+  {
+    const int j = threadIdx.x % HC, gl = threadIdx.x / HC, gls = GA_THREADS / HC;
+    float part = 0.f;
+    const float bj = s_b[j];
+    for (int s = gl; s < S; s += gls) {
+      const float g = sigmoidf_(__bfloat162float(gr[(long long)s * HC + j]) + bj);
+      part = fmaf(__bfloat162float(dor[(long long)s * HC + j]), g, part);
+    }
+    s_dofold[gl * HC + j] = part;
+  }
+  __syncthreads();
+  if (threadIdx.x < HC) {
+    const int hh = threadIdx.x / C, i = threadIdx.x - hh * C;
+    float mx = -INFINITY;
+    for (int j = 0; j < lanes; ++j) mx = fmaxf(mx, s_m[j * H + hh]);
+    float lt = 0.f, at = 0.f;
+    for (int j = 0; j < lanes; ++j) {
+      const float mj = s_m[j * H + hh];
+      const float w = (mj == -INFINITY) ? 0.f : __expf(mj - mx);
+      lt = fmaf(s_l[j * H + hh], w, lt);
+      at = fmaf(s_acc[(j * H + hh) * C + i], w, at);
+    }
+    s_o[threadIdx.x] = lt > 0.f ? at / lt : 0.f;
+    float dsum = 0.f;
+    for (int gl = 0; gl < GA_THREADS / HC; ++gl) dsum += s_dofold[gl * HC + threadIdx.x];
+    s_do[threadIdx.x] = dsum;
+    if (i == 0) {
+      s_mt[hh] = mx;
+      s_il[hh] = lt > 0.f ? 1.f / lt : 0.f;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < H) {
+    float d = 0.f;
+    for (int i = 0; i < C; ++i) d = fmaf(s_do[threadIdx.x * C + i], s_o[threadIdx.x * C + i], d);
+    s_dl[threadIdx.x] = d;
+  }
+  __syncthreads();
+  // ---- pass B.1: d_logit, d_q (thread-local), d_k / d_v (folded over the H threads of a sequence: consecutive lanes) ----
+  {
+    float dov[C], dqa[C];
+#pragma unroll
+    for (int i = 0; i < C; ++i) {
+      dov[i] = s_do[h * C + i];
+      dqa[i] = 0.f;
+    }
+    const float mt = s_mt[h], il = s_il[h], dl = s_dl[h];
+    const int s_iters = (S + lanes - 1) / lanes;
+    for (int it = 0; it < s_iters; ++it) {
+      const int s = it * lanes + sl;
+      const bool in = s < S;                         // every thread runs every iteration, so the shuffles below are warp-wide
+      float kk[C], vv[C], d = 0.f, dw = 0.f;
+#pragma unroll
+      for (int i = 0; i < C; ++i) {
+        kk[i] = in ? __bfloat162float(kvr[(long long)s * 2 * C + i]) : 0.f;
+        vv[i] = in ? __bfloat162float(kvr[(long long)s * 2 * C + C + i]) : 0.f;
+        d = fmaf(qv[i], kk[i], d);
+        dw = fmaf(dov[i], vv[i], dw);
+      }
+      const bool masked = in && (__bfloat162float(mr[s]) == 0.f);
+      if (masked) d = GA_MASKED;
+      const float w = in ? __expf(d - mt) * il : 0.f;
+      const float dlg = masked ? 0.f : w * (dw - dl);
+      float dk[C], dv[C];
+#pragma unroll
+      for (int i = 0; i < C; ++i) {
+        dqa[i] = fmaf(dlg, kk[i], dqa[i]);
+        dk[i] = dlg * qv[i];
+        dv[i] = w * dov[i];
+      }
+      // sum over the H heads: threads sl * H + 0 .. H - 1 are consecutive lanes of one warp (H divides 32)
+      for (int off = H >> 1; off > 0; off >>= 1) {
+#pragma unroll
+        for (int i = 0; i < C; ++i) {
+          dk[i] += __shfl_xor_sync(0xffffffffu, dk[i], off);
+          dv[i] += __shfl_xor_sync(0xffffffffu, dv[i], off);
+        }
+      }
+      if (in && h == 0) {
+#pragma unroll
+        for (int i = 0; i < C; ++i) {
+          dkv[(r * S + s) * 2 * C + i] = __float2bfloat16(dk[i]);
+          dkv[(r * S + s) * 2 * C + C + i] = __float2bfloat16(dv[i]);
+        }
+      }
+    }
+    __syncthreads();                                  // s_acc (read in the fold above) is reused
+#pragma unroll
+    for (int i = 0; i < C; ++i) s_acc[(sl * H + h) * C + i] = dqa[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < HC) {
+    const int hh = threadIdx.x / C, i = threadIdx.x - hh * C;
+    float t = 0.f;
+    for (int j = 0; j < lanes; ++j) t += s_acc[(j * H + hh) * C + i];
+    dq[r * HC + threadIdx.x] = t;
+  }
+  // ---- pass B.2: d_gate[s][j] = dout[s][j] * o[j] * g (1 - g) ----
+  {
+    const int j = threadIdx.x % HC, gl = threadIdx.x / HC, gls = GA_THREADS / HC;
+    const float bj = s_b[j], oj = s_o[j];
+    bf16* dgr = dgate + r * (long long)S * HC;
+    for (int s = gl; s < S; s += gls) {
+      const float g = sigmoidf_(__bfloat162float(gr[(long long)s * HC + j]) + bj);
+      dgr[(long long)s * HC + j] = __float2bfloat16(__bfloat162float(dor[(long long)s * HC + j]) * oj * g * (1.f - g));
+    }
+  }
+}
+
 }  // namespace ffb
 
 extern "C" {
@@ -390,6 +567,28 @@ int ffb_global_attention_fwd(const void* q, const void* kv, const void* mask, co
   else if (C == 16) FFB_GA_LAUNCH(16);
   else FFB_GA_LAUNCH(32);
 #undef FFB_GA_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Gradients of ffb_global_attention_fwd: dq fp32 [R][H][C], dkv bf16 [R][S][2C], dgate bf16 [R][S][H*C] (w.r.t. the gate
+// before bias and sigmoid).  H must divide 32 and H * C must divide 256.
+int ffb_global_attention_bwd(const void* q, const void* kv, const void* mask, const void* gate, const void* gate_bias, const void* dout,
+                             float* dq, void* dkv, void* dgate, long long R, int S, int H, int C, void* stream) {
+  using namespace ffb;
+  if (R <= 0 || S <= 0) return 0;
+  if (H <= 0 || (32 % H) || (GA_THREADS % (H * C)) || !(C == 8 || C == 16 || C == 32)) return -2;
+  auto st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)(2 * GA_THREADS + GA_THREADS * C + 3 * H * C + 3 * H + GA_THREADS) * sizeof(float);
+#define FFB_GAB_LAUNCH(CC)                                                                                                              \
+  do {                                                                                                                                  \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(global_attention_bwd_kernel<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    launch_k(global_attention_bwd_kernel<CC>, dim3((unsigned)R), GA_THREADS, smem, st, (const bf16*)q, (const bf16*)kv, (const bf16*)mask, \
+             (const bf16*)gate, (const bf16*)gate_bias, (const bf16*)dout, dq, (bf16*)dkv, (bf16*)dgate, S, H);                         \
+  } while (0)
+  if (C == 8) FFB_GAB_LAUNCH(8);
+  else if (C == 16) FFB_GAB_LAUNCH(16);
+  else FFB_GAB_LAUNCH(32);
+#undef FFB_GAB_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

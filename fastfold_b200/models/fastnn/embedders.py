@@ -19,10 +19,24 @@ ROW_BLOCK = 256
 
 
 class InputEmbedder(ref.InputEmbedder):
-    def forward(self, tf, ri, msa):
+    def forward(self, tf, ri, msa, rows=None):
+        """``rows=(r0, r1)``: build only those rows of the pair embedding (a DAP rank's shard)."""
         tf_emb_i = self.linear_tf_z_i(tf)
         tf_emb_j = self.linear_tf_z_j(tf)
         n = tf.shape[-2]
+        if rows is not None:
+            r0, r1 = rows
+            rii = ri.long()
+            table = self.linear_relpos.weight.t()
+            pair_emb = tf_emb_i.new_empty(tf.shape[:-2] + (r1 - r0, n, self.c_z))
+            for i in range(r0, r1, ROW_BLOCK):
+                e = min(i + ROW_BLOCK, r1)
+                idx = torch.clamp(rii[..., i:e, None] - rii[..., None, :], -self.relpos_k, self.relpos_k) + self.relpos_k
+                rel = torch.nn.functional.embedding(idx, table) + self.linear_relpos.bias
+                pair_emb[..., i - r0:e - r0, :, :] = rel + tf_emb_i[..., i:e, None, :] + tf_emb_j[..., None, :, :]
+            n_clust = msa.shape[-3]
+            tf_m = self.linear_tf_m(tf).unsqueeze(-3).expand(((-1,) * len(tf.shape[:-2]) + (n_clust, -1, -1)))
+            return self.linear_msa_m(msa) + tf_m, pair_emb
         pair_emb = tf_emb_i.new_empty(tf.shape[:-2] + (n, n, self.c_z))
         # one_hot(nearest bin of i - j) times the weight is a row lookup: bin = clip(i - j, -k, k) + k, computed on the
         # integer residue indices (in bf16 the indices themselves stop being exact beyond 256)
@@ -38,12 +52,22 @@ class InputEmbedder(ref.InputEmbedder):
 
 
 class RecyclingEmbedder(ref.RecyclingEmbedder):
-    def forward(self, m, z, x):
+    def forward(self, m, z, x, row0=0):
+        """``z`` may be a row shard ``[n_local, N, c]`` of the pair tensor whose first row is residue ``row0``."""
         bins = torch.linspace(self.min_bin, self.max_bin, self.no_bins, dtype=x.dtype, device=x.device, requires_grad=False)
         squared_bins = bins ** 2
         upper = torch.cat([squared_bins[1:], const_like(squared_bins, [self.inf], "inf_%r" % (self.inf,))], dim=-1)
         m_update = self.layer_norm_m(m)
         from ...ops import embed as kembed
+        if z.shape[-3] != x.shape[-2]:
+            nl = z.shape[-3]
+            z_update = torch.empty_like(z)
+            for i in range(0, nl, ROW_BLOCK):
+                e = min(i + ROW_BLOCK, nl)
+                d = torch.sum((x[..., row0 + i:row0 + e, None, :] - x[..., None, :, :]) ** 2, dim=-1, keepdims=True)
+                d = ((d > squared_bins) * (d < upper)).type(z.dtype)
+                z_update[..., i:e, :, :] = self.linear(d) + self.layer_norm_z(z[..., i:e, :, :])
+            return m_update, z_update
         if kembed.recycle_pair_embed_supported(z, x):
             # one pass: distance bin, weight-column gather, LayerNorm and add (no one-hot tensor, no GEMM with K = no_bins)
             ln = self.layer_norm_z

@@ -25,6 +25,7 @@ from ...utils.checkpointing import checkpoint_blocks
 from .msa import MSACore
 from .ops import Linear, OutProductMean
 from .triangle import PairCore, pad_amount
+from . import ops as fops
 
 
 def draw_block_dropout(n_res_padded, c_m, c_z, device, dtype, p_msa=0.15, p_pair=0.25, generator=None, n_res=None):
@@ -58,6 +59,9 @@ class Evoformer(nn.Module):
         self.communication = OutProductMean(n_feat=c_m, n_feat_out=c_z, n_feat_proj=32)
         self.pair = PairCore(d_pair=c_z)
         self.is_multimer = is_multimer
+        # True: the last block returns the pair tensor as this rank's row shard [N/P, N, c] instead of gathering it on
+        # every rank (long sequences: structure module, heads and recycling then work on the shard)
+        self.keep_pair_sharded = False
 
     def forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
         P = core.get_dap_size()
@@ -65,9 +69,12 @@ class Evoformer(nn.Module):
         pad = pad_amount(seq_length, P)
         if self.first_block:
             m = F.pad(m.unsqueeze(0), (0, 0, 0, pad))
-            z = F.pad(z.unsqueeze(0), (0, 0, 0, pad, 0, pad))
             m = scatter(m, dim=2) if self.is_multimer else scatter(m, dim=1)
-            z = scatter(z, dim=1)
+            if P > 1 and pad == 0 and z.shape[0] * P == seq_length:
+                z = z.unsqueeze(0)                      # the caller keeps the pair tensor row-sharded between the stacks
+            else:
+                z = F.pad(z.unsqueeze(0), (0, 0, 0, pad, 0, pad))
+                z = scatter(z, dim=1)
         msa_mask = F.pad(msa_mask.unsqueeze(0), (0, pad))
         pair_mask = F.pad(pair_mask.unsqueeze(0), (0, pad, 0, pad))
         if _drop is None and self.training:
@@ -81,7 +88,7 @@ class Evoformer(nn.Module):
             m = all_to_all_async_opp(m, work, 1, 2)
         else:
             z = self.communication(m, msa_mask, z)
-            z_ori = z
+            z_ori = z.clone() if fops.INPLACE else z          # the MSA stack below reads the pair tensor of BEFORE the pair stack
             m, work = all_to_all_async(m, 1, 2)
             z = self.pair(z, pair_mask, _drop)
             m = all_to_all_async_opp(m, work, 1, 2)
@@ -90,13 +97,15 @@ class Evoformer(nn.Module):
             m = m.squeeze(0)
             z = z.squeeze(0)
             m = gather(m, dim=1) if self.is_multimer else gather(m, dim=0)
-            z = gather(z, dim=0)
             m = m[:, :seq_length, :]
-            z = z[:seq_length, :seq_length, :]
+            if not (self.keep_pair_sharded and P > 1 and pad == 0):
+                z = gather(z, dim=0)
+                z = z[:seq_length, :seq_length, :]
         return m, z
 
     def inplace(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
-        m[0], z[0] = self.forward(m[0], z[0], msa_mask, pair_mask, chunk_size, _mask_trans, _drop)
+        with fops.inplace_scope():
+            m[0], z[0] = self.forward(m[0], z[0], msa_mask, pair_mask, chunk_size, _mask_trans, _drop)
         return m, z
 
 
@@ -133,5 +142,6 @@ class EvoformerStack(nn.Module):
         return m, z, s
 
     def inplace(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True):
-        m[0], z[0], s = self.forward(m[0], z[0], msa_mask, pair_mask, chunk_size, _mask_trans)
+        with fops.inplace_scope():
+            m[0], z[0], s = self.forward(m[0], z[0], msa_mask, pair_mask, chunk_size, _mask_trans)
         return m, z, s

@@ -12,6 +12,7 @@ from ...utils.checkpointing import checkpoint_blocks
 from .ops import (ChunkMSARowAttentionWithPairBias, ChunkMSAColumnGlobalAttention, ChunkTransition, GlobalAttention,
                   OutProductMean, SelfAttention, Transition, _fusable)
 from .triangle import PairCore, pad_amount
+from . import ops as fops
 
 
 class MSARowAttentionWithPairBias(ChunkMSARowAttentionWithPairBias):
@@ -39,7 +40,7 @@ class MSAColumnAttention(nn.Module):
             return False
         if not (like.is_cuda and like.dtype == torch.bfloat16 and self.c == flash.HEAD_DIM and n_seq % 8 == 0):
             return False
-        return not (torch.is_grad_enabled() and n_seq > 512)
+        return True
 
     def forward(self, M_raw, M_mask, M_norm_t=None, strided=None):
         """``M_norm_t``: ``layernormM`` of the input when the caller already has it - transposed ``[1, N/P, S, c]`` unless
@@ -49,10 +50,10 @@ class MSAColumnAttention(nn.Module):
         if strided:
             M = self.layernormM(M_raw) if M_norm_t is None else M_norm_t
             out, _ = self.attention(M, M_mask.transpose(-1, -2).contiguous(), transposed=True)
-            return M_raw + out
+            return M_raw.add_(out) if fops.INPLACE else M_raw + out
         M = self.layernormM(M_raw.transpose(-2, -3).contiguous()) if M_norm_t is None else M_norm_t
         out, _ = self.attention(M, M_mask.transpose(-1, -2).contiguous())
-        return M_raw + out.transpose(-2, -3)
+        return M_raw.add_(out.transpose(-2, -3)) if fops.INPLACE else M_raw + out.transpose(-2, -3)
 
 
 class MSAColumnGlobalAttention(ChunkMSAColumnGlobalAttention):
@@ -95,7 +96,8 @@ class ExtraMSACore(nn.Module):
         return node
 
     def inplace(self, node, pair, node_mask, dropmask=None):
-        node[0] = self.forward(node[0], pair[0] if isinstance(pair, list) else pair, node_mask, dropmask)
+        with fops.inplace_scope():
+            node[0] = self.forward(node[0], pair[0] if isinstance(pair, list) else pair, node_mask, dropmask)
         return node
 
 
@@ -109,6 +111,7 @@ class ExtraMSABlock(nn.Module):
         self.communication = OutProductMean(n_feat=c_m, n_feat_out=c_z, n_feat_proj=32)
         self.pair_stack = PairCore(d_pair=c_z)
         self.is_multimer = is_multimer
+        self.keep_pair_sharded = False                  # see ``Evoformer.keep_pair_sharded``
 
     def forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
         P = core.get_dap_size()
@@ -116,9 +119,12 @@ class ExtraMSABlock(nn.Module):
         len_pad = pad_amount(pair_mask.size(-1), P)
         if self.first_block:
             m = F.pad(m.unsqueeze(0), (0, 0, 0, len_pad, 0, cnt_pad))
-            z = F.pad(z.unsqueeze(0), (0, 0, 0, len_pad, 0, len_pad))
             m = scatter(m, dim=1) if not self.is_multimer else scatter(m, dim=2)
-            z = scatter(z, dim=1)
+            if P > 1 and len_pad == 0 and z.shape[0] * P == pair_mask.size(-1):
+                z = z.unsqueeze(0)                      # already this rank's row shard
+            else:
+                z = F.pad(z.unsqueeze(0), (0, 0, 0, len_pad, 0, len_pad))
+                z = scatter(z, dim=1)
         msa_mask = F.pad(msa_mask.unsqueeze(0), (0, len_pad, 0, cnt_pad))
         pair_mask = F.pad(pair_mask.unsqueeze(0), (0, len_pad, 0, len_pad))
         d_msa = None if _drop is None else _drop.get("msa_row")
@@ -130,20 +136,24 @@ class ExtraMSABlock(nn.Module):
             m = all_to_all_async_opp(m, work, 1, 2)
         else:
             z = self.communication(m, msa_mask, z)
-            z_ori = z
+            z_ori = z.clone() if fops.INPLACE else z          # the MSA stack below reads the pair tensor of BEFORE the pair stack
             m, work = all_to_all_async(m, 1, 2)
             z = self.pair_stack(z, pair_mask, _drop)
             m = all_to_all_async_opp(m, work, 1, 2)
             m = self.msa_stack(m, z_ori, msa_mask, d_msa)
         if self.last_block:
             m = gather(m, dim=1) if not self.is_multimer else gather(m, dim=2)
-            z = gather(z, dim=1)
             m = m[:, :m.shape[1] - cnt_pad, :m.shape[2] - len_pad, :].squeeze(0)
-            z = z[:, :z.shape[1] - len_pad, :z.shape[2] - len_pad, :].squeeze(0)
+            if self.keep_pair_sharded and P > 1 and len_pad == 0:
+                z = z.squeeze(0)
+            else:
+                z = gather(z, dim=1)
+                z = z[:, :z.shape[1] - len_pad, :z.shape[2] - len_pad, :].squeeze(0)
         return m, z
 
     def inplace(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
-        m[0], z[0] = self.forward(m[0], z[0], msa_mask, pair_mask, chunk_size, _mask_trans, _drop)
+        with fops.inplace_scope():
+            m[0], z[0] = self.forward(m[0], z[0], msa_mask, pair_mask, chunk_size, _mask_trans, _drop)
         return m, z
 
 
@@ -166,6 +176,7 @@ class ExtraMSAStack(nn.Module):
         return z
 
     def inplace(self, m, z, chunk_size=None, msa_mask=None, pair_mask=None, _mask_trans=True):
-        z[0] = self.forward(m[0], z[0], chunk_size, msa_mask, pair_mask, _mask_trans)
+        with fops.inplace_scope():
+            z[0] = self.forward(m[0], z[0], chunk_size, msa_mask, pair_mask, _mask_trans)
         m[0] = None
         return z

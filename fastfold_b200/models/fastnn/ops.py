@@ -33,6 +33,29 @@ from .initializer import glorot_uniform_af
 
 CHUNK_SIZE = None
 DEBUG = False
+# True while an ``.inplace`` entry point runs (inference only): residual-carrying GEMM epilogues then write their result
+# tile over the residual tile they just read (same warp, same tile: read before write), so a module's output replaces
+# its input in the same storage and no second copy of the MSA / pair tensor exists at any time.
+INPLACE = False
+
+
+class inplace_scope:
+    """``with inplace_scope():`` - modules called inside overwrite their residual input (see ``INPLACE``)."""
+
+    def __enter__(self):
+        global INPLACE
+        self.prev, INPLACE = INPLACE, (not torch.is_grad_enabled())
+        return self
+
+    def __exit__(self, *exc):
+        global INPLACE
+        INPLACE = self.prev
+        return False
+
+
+def _res_out(resid2d):
+    """``out=`` argument of a residual GEMM: the residual's own storage in in-place mode, else a fresh tensor."""
+    return resid2d if (INPLACE and resid2d.is_contiguous()) else None
 
 
 def set_chunk_size(chunk_size):
@@ -121,7 +144,7 @@ class Transition(nn.Module):
         h = self.linear1(x, act="relu")
         if _fusable(src):
             s2 = src.reshape(-1, src.shape[-1])
-            out = K.gemm(h.reshape(-1, h.shape[-1]), self.linear2.weight, bias=self.linear2.bias, resid=s2)
+            out = K.gemm(h.reshape(-1, h.shape[-1]), self.linear2.weight, bias=self.linear2.bias, resid=s2, out=_res_out(s2))
             return out.reshape(src.shape)
         return src + self.linear2(h)
 
@@ -129,15 +152,17 @@ class Transition(nn.Module):
         if CHUNK_SIZE is None:
             return self._one(src)
         step = CHUNK_SIZE * 48
-        out = torch.empty_like(src)
+        out = src if INPLACE else torch.empty_like(src)
         for ax in range(0, src.shape[1], step):
-            out[:, ax:ax + step] = self._one(src[:, ax:ax + step])
+            part = src[:, ax:ax + step]
+            res = self._one(part)
+            if res.data_ptr() != part.data_ptr():
+                out[:, ax:ax + step] = res
         return out
 
     def inplace(self, src):
-        step = src[0].shape[1] if CHUNK_SIZE is None else CHUNK_SIZE * 48
-        for ax in range(0, src[0].shape[1], step):
-            src[0][:, ax:ax + step] = self._one(src[0][:, ax:ax + step])
+        with inplace_scope():
+            src[0] = self.forward(src[0])
         return src
 
 
@@ -212,7 +237,8 @@ class OutProductMean(nn.Module):
         o4 = K.gemm(l2, r_local.reshape(S, ni * e), a_mn=True, b_mn=True, block_out=((ni * N, 1024), 1, N * 1024, 0, 1024),
                     peer=("b", heap.peer_addresses(slot, 0)))
         heap.consume_fence(slot, pre=False)
-        out = K.gemm(o4, self.o_linear.weight, bias=self.o_linear.bias, rowscale=inv_norm, resid=Z_raw.reshape(ni * N, -1))
+        z2 = Z_raw.reshape(ni * N, -1)
+        out = K.gemm(o4, self.o_linear.weight, bias=self.o_linear.bias, rowscale=inv_norm, resid=z2, out=_res_out(z2))
         return out.reshape(Z_raw.shape)
 
     def forward(self, M, M_mask, Z_raw):
@@ -233,14 +259,17 @@ class OutProductMean(nn.Module):
         right_act_all = gather_async_opp(right_act_all, work, dim=2)
         if CHUNK_SIZE is None:
             return self._outer(left_act, right_act_all, inv_norm, Z_raw)
-        out = torch.empty_like(Z_raw)
+        out = Z_raw if INPLACE else torch.empty_like(Z_raw)
         for ax in range(0, left_act.shape[2], CHUNK_SIZE):
-            out[:, ax:ax + CHUNK_SIZE] = self._outer(left_act[:, :, ax:ax + CHUNK_SIZE].contiguous(), right_act_all,
-                                                     inv_norm[:, ax:ax + CHUNK_SIZE], Z_raw[:, ax:ax + CHUNK_SIZE])
+            zpart = Z_raw[:, ax:ax + CHUNK_SIZE]
+            res = self._outer(left_act[:, :, ax:ax + CHUNK_SIZE].contiguous(), right_act_all, inv_norm[:, ax:ax + CHUNK_SIZE], zpart)
+            if res.data_ptr() != zpart.data_ptr():
+                out[:, ax:ax + CHUNK_SIZE] = res
         return out
 
     def inplace(self, M, M_mask, Z_raw):
-        Z_raw[0] = self.forward(M, M_mask, Z_raw[0])
+        with inplace_scope():
+            Z_raw[0] = self.forward(M, M_mask, Z_raw[0])
         return Z_raw
 
 
@@ -249,7 +278,7 @@ def _opm_forward(l2, r2, w, bias, inv_norm, z2):
     S = l2.shape[0]
     ni, N = l2.shape[1] // 32, r2.shape[1] // 32
     o4 = K.gemm(l2, r2, a_mn=True, b_mn=True, block_out=((ni * N, 1024), 1, N * 1024, 0, 1024))
-    out = K.gemm(o4, w, bias=bias, rowscale=inv_norm, resid=z2)
+    out = K.gemm(o4, w, bias=bias, rowscale=inv_norm, resid=z2, out=_res_out(z2) if not torch.is_grad_enabled() else None)
     return out, o4
 
 
@@ -334,8 +363,41 @@ class SelfAttention(nn.Module):
             wg = rows(self.gating_linear.weight, 1) if self.gating else None
             bg = rows(self.gating_bias, 1) if self.gating else None
             wo = rows(self.o_linear.weight.detach().t().contiguous(), 1).t().contiguous()
+            if self.training:
+                # never kept: the parameters may change without a version bump, and tensors built while a CUDA graph is
+                # being captured live in the graph's memory pool, whose contents later eager code must not rely on
+                self._pad_cache = None
+                return wq, wg, bg, wo
             self._pad_cache = (key, wq, wg, bg, wo)
         return self._pad_cache[1:]
+
+    def _padded_heads_differentiable(self):
+        """The widened weights of ``_padded_heads`` built with differentiable ops (training): gradients flow back to the
+        narrow parameters through the padding, the zero rows / columns receive none."""
+        H, d, D = self.n_head, self.c, flash.HEAD_DIM
+        wq = F.pad(self.to_qkv.weight.reshape(3, H, d, -1), (0, 0, 0, D - d)).reshape(3 * H * D, -1)
+        wg = bg = None
+        if self.gating:
+            wg = F.pad(self.gating_linear.weight.reshape(H, d, -1), (0, 0, 0, D - d)).reshape(H * D, -1)
+            bg = F.pad(self.gating_bias.reshape(H, d), (0, D - d)).reshape(H * D)
+        wo = F.pad(self.o_linear.weight.reshape(-1, H, d), (0, D - d)).reshape(-1, H * D)
+        return wq, wg, bg, wo
+
+    def _one_padded_train(self, x, mask, bias):
+        """Training on the GPU with heads narrower than the fused kernel's 32 channels (extra-MSA row attention: 8,
+        template triangle attention: 16): the same zero-padding as in inference, built differentiably, so that forward and
+        backward run on the fused attention kernels instead of a composite that materialises the logits."""
+        H, D = self.n_head, flash.HEAD_DIM
+        b1, b2, n, _ = x.shape
+        wq, wg, bg, wo = self._padded_heads_differentiable()
+        qkv = K.linear(x, wq).reshape(b1, b2, n, 3, H, D)
+        bias5 = None if bias is None else bias.unsqueeze(1)
+        if not flash.packed_supported(qkv, mask, bias5):
+            return None
+        o = flash.flash_attention_packed(qkv, mask, bias5, self.scaling)
+        if self.gating:
+            o = K.bias_sigmod_ele(K.linear(x, wg), bg, o)
+        return K.linear(o, wo, self.o_linear.bias), False
 
     def _one_padded(self, x, mask, bias, tail):
         """No-grad GPU path for heads narrower than the fused kernel's: see ``_padded_heads``."""
@@ -352,8 +414,8 @@ class SelfAttention(nn.Module):
             o = K.gemm(x2, wg, bias=bg, act="sigmoid", mul=o)
         if tail is not None:
             out_bias, dmask, resid = tail
-            out = K.gemm(o, wo, bias=out_bias if out_bias is not None else self.o_linear.bias, dmask=dmask,
-                         resid=resid.reshape(-1, resid.shape[-1]))
+            r2 = resid.reshape(-1, resid.shape[-1])
+            out = K.gemm(o, wo, bias=out_bias if out_bias is not None else self.o_linear.bias, dmask=dmask, resid=r2, out=_res_out(r2))
             return out.reshape(resid.shape), True
         out = K.gemm(o, wo, bias=self.o_linear.bias)
         return out.reshape(b1, b2, n, -1), False
@@ -363,6 +425,11 @@ class SelfAttention(nn.Module):
         H, d = self.n_head, self.c
         if d < flash.HEAD_DIM and not transposed and _fusable(x) and x.shape[-2] % 8 == 0:
             res = self._one_padded(x, mask, bias, tail)
+            if res is not None:
+                return res
+        if (d < flash.HEAD_DIM and not transposed and torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16
+                and x.shape[-2] % 8 == 0 and flash.HEAD_DIM % d == 0):
+            res = self._one_padded_train(x, mask, bias)
             if res is not None:
                 return res
         bias5 = None if bias is None else bias.unsqueeze(1)
@@ -394,8 +461,9 @@ class SelfAttention(nn.Module):
                 o = K.bias_sigmod_ele(self.gating_linear(x), self.gating_bias, o)
         if tail is not None and fused:
             out_bias, dmask, resid = tail
+            r2 = resid.reshape(-1, resid.shape[-1])
             out = K.gemm(o.reshape(-1, H * d), self.o_linear.weight, bias=out_bias if out_bias is not None else self.o_linear.bias,
-                         dmask=dmask, resid=resid.reshape(-1, resid.shape[-1]))
+                         dmask=dmask, resid=r2, out=_res_out(r2))
             return out.reshape(resid.shape), True
         return self.o_linear(o), False
 
@@ -519,6 +587,9 @@ class _TriangleMultiplication(nn.Module):
         if self.training or self._glu_cache is None or self._glu_cache[0] != key:
             w = torch.stack([wp.detach(), wg.detach()], dim=1).reshape(-1, wp.shape[1]).contiguous()
             b = torch.stack([self.left_right_projection.bias.detach(), self.left_right_gate.bias.detach()], dim=1).reshape(-1).contiguous()
+            if self.training:
+                self._glu_cache = None          # see ``SelfAttention._padded_heads``
+                return w, b
             self._glu_cache = (key, w, b)
         return self._glu_cache[1], self._glu_cache[2]
 
@@ -580,8 +651,9 @@ class _TriangleMultiplication(nn.Module):
             p = K.gemm(left_t, right_t, a_mn=True, b_mn=True)                                  # [c, i, j]
         n_i, n_j = p.shape[1], p.shape[2]
         ab = K.layer_norm_transposed(p.reshape(c, n_i * n_j), self.layernorm2.weight, self.layernorm2.bias, self.layernorm2.eps)
+        zr2 = Z_raw.reshape(A * B, -1)
         out = K.gemm(ab, self.output_projection.weight, bias=self.output_bias, mul=g,
-                     dmask=None if dropmask is None else _mask_idx(Z_raw, dropmask), resid=Z_raw.reshape(A * B, -1))
+                     dmask=None if dropmask is None else _mask_idx(Z_raw, dropmask), resid=zr2, out=_res_out(zr2))
         return out.reshape(Z_raw.shape)
 
     def _chunked(self, Z_raw, Z_mask):
@@ -687,7 +759,8 @@ class _TriangleMultiplication(nn.Module):
         return K.bias_ele_dropout_residual(ab, self.output_bias, g, dropmask, Z_raw, prob=0.0, training=training)
 
     def inplace(self, Z_raw, Z_mask, dropmask=None):
-        Z_raw[0] = self.forward(Z_raw[0], Z_mask, dropmask)
+        with inplace_scope():
+            Z_raw[0] = self.forward(Z_raw[0], Z_mask, dropmask)
         return Z_raw
 
 
@@ -793,10 +866,11 @@ class _TriangleAttention(nn.Module):
             return False
         if not (like.is_cuda and like.dtype == torch.bfloat16 and self.c == flash.HEAD_DIM and n_attn % 8 == 0):
             return False
-        return not (torch.is_grad_enabled() and n_attn > 512)
+        return True
 
     def inplace(self, Z_raw, Z_mask, dropmask=None):
-        Z_raw[0] = self.forward(Z_raw[0], Z_mask, dropmask)
+        with inplace_scope():
+            Z_raw[0] = self.forward(Z_raw[0], Z_mask, dropmask)
         return Z_raw
 
 
@@ -844,7 +918,8 @@ class ChunkMSARowAttentionWithPairBias(nn.Module):
         return K.bias_dropout_add(out, self.out_bias, dropmask, M_raw, prob=0.0, training=training)
 
     def inplace(self, M_raw, Z, M_mask, dropmask=None):
-        M_raw[0] = self.forward(M_raw[0], Z, M_mask, dropmask)
+        with inplace_scope():
+            M_raw[0] = self.forward(M_raw[0], Z, M_mask, dropmask)
         return M_raw
 
 
@@ -858,8 +933,11 @@ class ChunkMSAColumnGlobalAttention(nn.Module):
     def forward(self, M_raw, M_mask):
         M = self.layernormM(M_raw.transpose(-2, -3).contiguous())
         M = self.global_attention(M, M_mask.transpose(-1, -2).contiguous())
+        if INPLACE:
+            return M_raw.add_(M.transpose(-2, -3))
         return M_raw + M.transpose(-2, -3)
 
     def inplace(self, M_raw, M_mask):
-        M_raw[0] = self.forward(M_raw[0], M_mask)
+        with inplace_scope():
+            M_raw[0] = self.forward(M_raw[0], M_mask)
         return M_raw

@@ -68,5 +68,7 @@ class PairCore(nn.Module):
         return pair
 
     def inplace(self, pair, pair_mask, _drop=None):
-        pair[0] = self.forward(pair[0], pair_mask, _drop)
+        from . import ops as fops
+        with fops.inplace_scope():
+            pair[0] = self.forward(pair[0], pair_mask, _drop)
         return pair

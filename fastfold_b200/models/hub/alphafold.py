@@ -58,16 +58,33 @@ class AlphaFold(nn.Module):
         inplace = bool(self.globals.get("inplace", False)) and not (self.training or torch.is_grad_enabled())
 
         is_multimer = bool(self.globals.get("is_multimer", False))
+        # Long sequences under DAP (``globals.shard_pair``): the pair tensor exists only as this rank's row shard
+        # [N/P, N, c_z] from the embedders to the heads - the stacks neither scatter nor gather it, the structure module
+        # attends row-parallel, recycling and the distogram head work on the shard.  Outputs ``pair`` and
+        # ``distogram_logits`` are then row shards too.
+        from ...parallel import core as _core
+        P = _core.get_dap_size()
+        shard = (bool(self.globals.get("shard_pair", False)) and P > 1 and n % P == 0 and not is_multimer and not self.config.template.enabled
+                 and not torch.is_grad_enabled() and not batch_dims and hasattr(self.evoformer.blocks[-1], "keep_pair_sharded"))
+        for stack in (self.evoformer, self.extra_msa_stack):
+            if hasattr(stack.blocks[-1], "keep_pair_sharded"):
+                stack.blocks[-1].keep_pair_sharded = shard
+        row0 = _core.get_dap_rank() * (n // P) if shard else 0
         if is_multimer:
             m, z = self.input_embedder(feats)
+        elif shard:
+            m, z = self.input_embedder(feats["target_feat"], feats["residue_index"], feats["msa_feat"], rows=(row0, row0 + n // P))
         else:
             m, z = self.input_embedder(feats["target_feat"], feats["residue_index"], feats["msa_feat"])
         if None in [m_1_prev, z_prev, x_prev]:
             m_1_prev = m.new_zeros((*batch_dims, n, self.config.input_embedder.c_m), requires_grad=False)
-            z_prev = z.new_zeros((*batch_dims, n, n, self.config.input_embedder.c_z), requires_grad=False)
+            z_prev = z.new_zeros(z.shape, requires_grad=False)
             x_prev = z.new_zeros((*batch_dims, n, rc.atom_type_num, 3), requires_grad=False)
         x_prev = pseudo_beta_fn(feats["aatype"], x_prev, None).to(dtype=z.dtype)
-        m_1_prev_emb, z_prev_emb = self.recycling_embedder(m_1_prev, z_prev, x_prev)
+        if shard:
+            m_1_prev_emb, z_prev_emb = self.recycling_embedder(m_1_prev, z_prev, x_prev, row0=row0)
+        else:
+            m_1_prev_emb, z_prev_emb = self.recycling_embedder(m_1_prev, z_prev, x_prev)
         if not _recycle:
             m_1_prev_emb = m_1_prev_emb * 0
             z_prev_emb = z_prev_emb * 0

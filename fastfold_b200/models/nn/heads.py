@@ -66,6 +66,12 @@ class DistogramHead(nn.Module):
 
     def forward(self, z):
         logits = self.linear(z)
+        if z.shape[-3] != z.shape[-2]:
+            # row shard [N/P, N, c] under DAP: the transposed term logits[j, i] for the local rows i is the column shard
+            # of the logits, obtained with one axis switch
+            from ...parallel import comm
+            cols = comm.row_to_col(logits.unsqueeze(0)).squeeze(0)            # [N, N/P, bins]
+            return logits + cols.transpose(-2, -3)
         return logits + logits.transpose(-2, -3)
 
 

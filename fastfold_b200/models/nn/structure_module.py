@@ -124,6 +124,37 @@ class InvariantPointAttention(nn.Module):
             kv_pts = r[..., None].apply(kv_pts)
             kv_pts = kv_pts.view(kv_pts.shape[:-2] + (H, -1, 3))
             k_pts, v_pts = torch.split(kv_pts, [self.no_qk_points, self.no_v_points], dim=-2)
+        head_w = self.softplus(self.head_weights) * math.sqrt(1.0 / (3 * (self.no_qk_points * 9.0 / 2)))
+        from ...ops import ipa as ipa_op
+        if s.dim() == 2 and z.shape[-3] != s.shape[-2]:
+            # Row-parallel attention over the DAP group: this rank holds rows [row0, row0 + n_local) of the pair tensor,
+            # which is all that queries row0 .. need (bias b[i, j] and o_pair[i] = sum_j a[i, j] z[i, j] use row i only).
+            # Projections of s are replicated (tiny); the per-query outputs are all-gathered (N x 2016 floats).
+            from ...parallel import comm, core
+            assert not torch.is_grad_enabled(), "row-parallel invariant point attention is an inference path"
+            row0 = core.get_dap_rank() * z.shape[-3]
+            o, o_pt, o_pair = ipa_op.ipa_core(q, k, v, q_pts, k_pts, v_pts, z.contiguous(), self.linear_b.weight, self.linear_b.bias, head_w, mask,
+                                              math.sqrt(1.0 / (3 * self.c_hidden)), math.sqrt(1.0 / 3), self.inf, row0=row0)
+            o, o_pt, o_pair = (comm._gather(t.contiguous(), dim=0) for t in (o, o_pt, o_pair))
+            o = flatten_final_dims(o, 2)
+            o_pt = r[..., None, None].invert_apply(o_pt)
+            o_pt_norm = flatten_final_dims(torch.sqrt(torch.sum(o_pt ** 2, dim=-1) + self.eps), 2)
+            o_pt = o_pt.reshape(*o_pt.shape[:-3], -1, 3)
+            o_pair = flatten_final_dims(o_pair, 2)
+            cat = torch.cat((o, *torch.unbind(o_pt, dim=-1), o_pt_norm, o_pair), dim=-1).to(dtype=z.dtype)
+            return self.linear_out(cat)
+        if s.dim() == 2 and ipa_op.supported(q, q_pts, v_pts, z):
+            # inference on the GPU: logits, softmax and the three weighted sums in one kernel; the pair row is read once
+            # and neither the [H, N, N] attention tensor nor the [N, N, H, P, 3] point differences are materialised
+            o, o_pt, o_pair = ipa_op.ipa_core(q, k, v, q_pts, k_pts, v_pts, z, self.linear_b.weight, self.linear_b.bias, head_w, mask,
+                                              math.sqrt(1.0 / (3 * self.c_hidden)), math.sqrt(1.0 / 3), self.inf)
+            o = flatten_final_dims(o, 2)
+            o_pt = r[..., None, None].invert_apply(o_pt)
+            o_pt_norm = flatten_final_dims(torch.sqrt(torch.sum(o_pt ** 2, dim=-1) + self.eps), 2)
+            o_pt = o_pt.reshape(*o_pt.shape[:-3], -1, 3)
+            o_pair = flatten_final_dims(o_pair, 2)
+            cat = torch.cat((o, *torch.unbind(o_pt, dim=-1), o_pt_norm, o_pair), dim=-1).to(dtype=z.dtype)
+            return self.linear_out(cat)
         b = self.linear_b(z)
         a = torch.matmul(permute_final_dims(q.float(), (1, 0, 2)), permute_final_dims(k.float(), (1, 2, 0)))
         a = a * math.sqrt(1.0 / (3 * self.c_hidden))

@@ -9,6 +9,7 @@ import torch
 from . import _lib
 
 HEAD_DIM = 32
+MAX_BWD_QUERIES = 512      # queries of one (row, head) whose gradient the backward kernel holds in tensor memory
 
 
 def _layout(t):
@@ -133,8 +134,6 @@ def packed_supported(qkv, mask, bias, transposed=False):
     n = qkv.shape[1] if transposed else qkv.shape[2]
     if n % 8:
         return False
-    if torch.is_grad_enabled() and (qkv.requires_grad or (bias is not None and bias.requires_grad)) and n > 512:
-        return False
     if bias is not None and (bias.dim() != 5 or bias.shape[0] != 1 or bias.shape[1] != 1):
         return False
     return True
@@ -183,16 +182,41 @@ class _FlashPackedFn(torch.autograd.Function):
         HD = H * d
         do = do.contiguous()
         dqkv = torch.empty_like(qkv)
-        ds = torch.empty(B, H, n, n, device=qkv.device, dtype=qkv.dtype) if b3 is not None else None
         base, gbase = qkv.data_ptr(), dqkv.data_ptr()
-        rc = lib.ffb_attention_bwd_strided(base, base + 2 * HD, base + 4 * HD, bs, rs, bs, rs, _lib.ptr(b3), _lib.ptr(m2), n, _lib.ptr(out),
-                                           _lib.ptr(do), obs, ors, _lib.ptr(lse), gbase, gbase + 2 * HD, gbase + 4 * HD, bs, rs, bs, rs,
-                                           _lib.ptr(ds), B, H, n, n, d, float(ctx.scale), _lib.stream_ptr())
-        _lib.check(rc, "ffb_attention_bwd_strided (B=%d,H=%d,n=%d)" % (B, H, n))
-        dbias = None
-        if ds is not None and ctx.needs_input_grad[2]:
-            dbias = ds.sum(dim=0).reshape(ctx.bias_shape)
-        return dqkv, None, dbias, None, None
+        want_dbias = b3 is not None and ctx.needs_input_grad[2]
+        if n <= MAX_BWD_QUERIES:
+            ds = torch.empty(B, H, n, n, device=qkv.device, dtype=qkv.dtype) if b3 is not None else None
+            rc = lib.ffb_attention_bwd_strided(base, base + 2 * HD, base + 4 * HD, bs, rs, bs, rs, _lib.ptr(b3), _lib.ptr(m2), n, _lib.ptr(out),
+                                               _lib.ptr(do), obs, ors, _lib.ptr(lse), gbase, gbase + 2 * HD, gbase + 4 * HD, bs, rs, bs, rs,
+                                               _lib.ptr(ds), B, H, n, n, d, float(ctx.scale), _lib.stream_ptr())
+            _lib.check(rc, "ffb_attention_bwd_strided (B=%d,H=%d,n=%d)" % (B, H, n))
+            dbias = ds.sum(dim=0).reshape(ctx.bias_shape) if want_dbias else None
+            return dqkv, None, dbias, None, None
+        # Long rows: the kernel keeps the query gradients of one (row, head) in tensor memory, which holds 512 queries.
+        # Longer rows go through it in blocks of 512 queries against ALL keys: each call writes its block of dq in place
+        # and a partial dk / dv over the whole row, which are summed in fp32 across the blocks.
+        es = qkv.element_size()
+        part = torch.empty(2, B, n, HD, device=qkv.device, dtype=qkv.dtype)
+        acc = torch.zeros(2, B, n, HD, device=qkv.device, dtype=torch.float32)
+        dbias = torch.empty(H, n, n, device=qkv.device, dtype=qkv.dtype) if want_dbias else None
+        for c0 in range(0, n, MAX_BWD_QUERIES):
+            nq = min(MAX_BWD_QUERIES, n - c0)
+            lse_c = lse[:, :, c0:c0 + nq].contiguous()
+            b_c = b3[:, c0:c0 + nq].contiguous() if b3 is not None else None
+            ds = torch.empty(B, H, nq, n, device=qkv.device, dtype=qkv.dtype) if b3 is not None else None
+            rc = lib.ffb_attention_bwd_strided(base + c0 * rs * es, base + 2 * HD, base + 4 * HD, bs, rs, bs, rs, _lib.ptr(b_c), _lib.ptr(m2), n,
+                                               out.data_ptr() + c0 * ors * es, do.data_ptr() + c0 * ors * es, obs, ors, _lib.ptr(lse_c),
+                                               gbase + c0 * rs * es, _lib.ptr(part[0]), _lib.ptr(part[1]), bs, rs, n * HD, HD, _lib.ptr(ds),
+                                               B, H, nq, n, d, float(ctx.scale), _lib.stream_ptr())
+            _lib.check(rc, "ffb_attention_bwd_strided (B=%d,H=%d,n=%d, queries %d..%d)" % (B, H, n, c0, c0 + nq))
+            acc += part
+            if want_dbias:
+                dbias[:, c0:c0 + nq] = ds.sum(dim=0)
+            del ds
+        # dk / dv slabs of the packed gradient: element (b, i, h, c) at gbase + (1 | 2) * HD + b * bs + i * rs
+        gk = torch.as_strided(dqkv, (2, B, n, HD), (HD, bs, rs, 1), storage_offset=dqkv.storage_offset() + HD)
+        gk.copy_(acc)
+        return dqkv, None, (dbias.reshape(ctx.bias_shape) if want_dbias else None), None, None
 
 
 def flash_attention_packed(qkv, mask, bias, scale, transposed=False):

@@ -271,27 +271,71 @@ def global_attention_ref(q, kv, mask, gate, gate_bias):
 
 def global_attention_supported(q, kv, gate):
     H, c = q.shape[-2:]
-    return (_bf16_cuda(q) and _bf16_cuda(kv) and _bf16_cuda(gate) and not torch.is_grad_enabled() and c in (8, 16, 32) and 256 % H == 0
-            and H * c <= 256 and _lib.has("ffb_global_attention_fwd"))
+    ok = (_bf16_cuda(q) and _bf16_cuda(kv) and _bf16_cuda(gate) and c in (8, 16, 32) and 256 % H == 0 and H * c <= 256
+          and _lib.has("ffb_global_attention_fwd"))
+    if ok and torch.is_grad_enabled() and (q.requires_grad or kv.requires_grad or gate.requires_grad):
+        # training: the backward kernel folds the heads of one sequence with warp shuffles
+        ok = 32 % H == 0 and 256 % (H * c) == 0 and _lib.has("ffb_global_attention_bwd")
+    return ok
+
+
+def _global_attention_fwd(q, kv, mask, gate, gate_bias):
+    R, H, c = q.shape
+    S = kv.shape[1]
+    out = torch.empty_like(gate)
+    _lib.check(_lib.get().ffb_global_attention_fwd(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(mask), _lib.ptr(gate), _lib.ptr(gate_bias), _lib.ptr(out),
+                                                   R, S, H, c, _lib.stream_ptr()), "global_attention_fwd")
+    return out
+
+
+class _GlobalAttentionFn(torch.autograd.Function):
+    """Forward and backward of the global-attention core on the kernels of csrc/global_attention.cu."""
+
+    @staticmethod
+    def forward(ctx, q, kv, mask, gate, gate_bias):
+        q, kv, gate = q.contiguous(), kv.contiguous(), gate.contiguous()
+        mask = mask.to(q.dtype).contiguous()
+        gb = gate_bias.to(q.dtype).contiguous()
+        ctx.save_for_backward(q, kv, mask, gate, gb)
+        ctx.bias_ref = gate_bias
+        return _global_attention_fwd(q, kv, mask, gate, gb)
+
+    @staticmethod
+    def backward(ctx, dout):
+        import ctypes
+        q, kv, mask, gate, gb = ctx.saved_tensors
+        R, H, c = q.shape
+        S = kv.shape[1]
+        dout = dout.contiguous()
+        dq = torch.empty(R, H, c, device=q.device, dtype=torch.float32)
+        dkv = torch.empty_like(kv)
+        dgate = torch.empty_like(gate)
+        lib = _lib.get()
+        P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        lib.ffb_global_attention_bwd.argtypes = [P] * 9 + [L, I, I, I, P]
+        lib.ffb_global_attention_bwd.restype = I
+        _lib.check(lib.ffb_global_attention_bwd(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(mask), _lib.ptr(gate), _lib.ptr(gb), _lib.ptr(dout), _lib.ptr(dq),
+                                                _lib.ptr(dkv), _lib.ptr(dgate), R, S, H, c, _lib.stream_ptr()), "global_attention_bwd")
+        dgb = None
+        if ctx.needs_input_grad[4]:
+            from .gemm import sink_bias_grad
+            if not sink_bias_grad(ctx.bias_ref, dgate.reshape(-1, H * c)):
+                dgb = colsum(dgate.reshape(-1, H * c)).to(ctx.bias_ref.dtype)
+        return dq.to(q.dtype), dkv, None, dgate, dgb
 
 
 def global_attention_core(q, kv, mask, gate, gate_bias):
     """One query per (column, head), keys / values shared by the heads:  ``q [R, H, c]`` (projected and scaled),
     ``kv [R, S, 2c]`` (keys | values), ``mask [R, S]`` (0 = masked key, logit replaced by -1e9), ``gate [R, S, H*c]``
     (gating projection before bias and sigmoid), ``gate_bias [H*c]``  ->  ``sigmoid(gate + bias) * softmax(q k^T) v``
-    broadcast over S, ``[R, S, H*c]``.  Forward only (inference path of the extra-MSA stack); one kernel, one pass over
-    ``kv`` and ``gate``."""
+    broadcast over S, ``[R, S, H*c]``.  One kernel forward (one pass over ``kv`` and ``gate``), one kernel backward
+    (``_GlobalAttentionFn``)."""
     if not global_attention_supported(q, kv, gate):
         return global_attention_ref(q, kv, mask, gate, gate_bias).to(gate.dtype)
-    R, H, c = q.shape
-    S = kv.shape[1]
+    if torch.is_grad_enabled() and (q.requires_grad or kv.requires_grad or gate.requires_grad or gate_bias.requires_grad):
+        return _GlobalAttentionFn.apply(q, kv, mask, gate, gate_bias)
     q, kv, gate = q.contiguous(), kv.contiguous(), gate.contiguous()
-    mask = mask.to(q.dtype).contiguous()
-    out = torch.empty_like(gate)
-    _lib.check(_lib.get().ffb_global_attention_fwd(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(mask), _lib.ptr(gate),
-                                                   _lib.ptr(gate_bias.to(q.dtype).contiguous()), _lib.ptr(out), R, S, H, c, _lib.stream_ptr()),
-               "global_attention_fwd")
-    return out
+    return _global_attention_fwd(q, kv, mask.to(q.dtype).contiguous(), gate, gate_bias.to(q.dtype).contiguous())
 
 
 # ---------------------------------------------------------------------------

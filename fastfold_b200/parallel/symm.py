@@ -111,6 +111,14 @@ class SymmHeap:
 
     def _ensure_ring(self):
         if not self.ring:
+            want = _WANT_MESSAGE[0]
+            if want:
+                # sized from the model's shapes (``request_message_bytes``): every activation collective fits a slot;
+                # large slots get a shorter ring (reuse is made safe by the flag protocol, it only costs waiting)
+                n = 12 if want <= (256 << 20) else 6
+                per = min(want, (self.heap_bytes - self._cursor) // n)
+                self.make_ring(n, per // 1024 * 1024)
+                return
             per = min(192 << 20, max(1 << 20, (self.heap_bytes - self._cursor) // 2 // 12))
             self.make_ring(12, per)
 
@@ -302,6 +310,26 @@ class SymmHeap:
 
 
 _HEAPS = {}
+_WANT_MESSAGE = [0]
+
+
+def request_message_bytes(nbytes):
+    """Tells the heap, before it is created, how large the largest activation collective of the coming run is (per
+    rank); the heap is then sized so that a ring slot holds it and nothing falls back to NCCL.  ``ring_bytes_for`` gives
+    the number for a model call."""
+    _WANT_MESSAGE[0] = max(_WANT_MESSAGE[0], (int(nbytes) + 1023) // 1024 * 1024)
+
+
+def ring_bytes_for(n_res, n_seq, n_extra, world, c_z=128, c_m=256, c_e=64, elem=2):
+    """Largest per-rank message of one model call over ``world`` DAP ranks: the pair shard's axis switch, the MSA / extra
+    MSA shards, and the slot a rank's projected triangle-multiplication operands (both, channel-major) are written to
+    for the peers' GEMMs to read."""
+    if world <= 1:
+        return 0
+    pad = (-n_res) % world
+    n = n_res + pad
+    z_shard = n * n // world * c_z * elem
+    return max(2 * z_shard, n_seq * n // world * c_m * elem * 2, n_extra * n // world * c_e * elem * 2)
 
 
 def get_heap(kind="dap", heap_bytes=None, wait_s=None):
@@ -326,6 +354,9 @@ def get_heap(kind="dap", heap_bytes=None, wait_s=None):
             h = _HEAPS["world"]
         else:
             nbytes = heap_bytes or int(os.environ.get("FASTFOLD_SYMM_HEAP_MB", "2048")) * (1 << 20)
+            if _WANT_MESSAGE[0]:
+                n = 12 if _WANT_MESSAGE[0] <= (256 << 20) else 6
+                nbytes = max(nbytes, n * _WANT_MESSAGE[0] + (512 << 20))
             h = SymmHeap(group, nbytes, wait_s=wait_s if wait_s is not None else float(os.environ.get("FASTFOLD_SYMM_WAIT_S", "20")))
         _HEAPS[kind] = h
     return h

@@ -13,7 +13,8 @@ import numpy as np
 import torch
 
 
-def load_model(model_name="model_1", param_path=None, chunk_size=None, inplace=False, overrides=None, seed=0, device=None, bf16=True):
+def load_model(model_name="model_1", param_path=None, chunk_size=None, inplace=False, overrides=None, seed=0, device=None, bf16=True,
+               shard_pair=False):
     """Builds the model a prediction runs: ``AlphaFold(model_config(model_name))`` (+ an AlphaFold parameter archive when
     ``param_path`` exists), fast trunk swapped in, eval mode, on ``device`` in bf16 (GPU) or fp32 (CPU).  ``init_dap`` must
     have been called.  Sets the process-wide chunk size, as the reference's inference.py:129-145 does."""
@@ -28,6 +29,7 @@ def load_model(model_name="model_1", param_path=None, chunk_size=None, inplace=F
     config = model_config(model_name)
     config.globals.chunk_size = chunk_size
     config.globals.inplace = bool(inplace)
+    config.globals.shard_pair = bool(shard_pair)      # long sequences under DAP: the pair tensor stays a row shard end to end
     for k, v in (overrides or {}).items():
         node = config
         parts = k.split(".")
@@ -50,6 +52,14 @@ def predict(model, batch):
     the device-timed seconds of the model call.  Raises on every rank if a kernel reported a failed wait."""
     device = next(model.parameters()).device
     cuda = device.type == "cuda"
+    if cuda:
+        # size the symmetric heap (created at the first collective) from the shapes, so that every axis switch and
+        # gather of this call runs on the package's own NVLink kernels instead of falling back to NCCL
+        from ..parallel import core, symm
+        P = core.get_dap_size()
+        if P > 1:
+            symm.request_message_bytes(symm.ring_bytes_for(int(batch["aatype"].shape[0]), int(batch["msa_feat"].shape[0]),
+                                                           int(batch["extra_msa"].shape[0]) if "extra_msa" in batch else 0, P))
     batch = {k: torch.as_tensor(v).to(device, non_blocking=True) for k, v in batch.items()}
     with torch.no_grad():
         if cuda:
@@ -74,7 +84,7 @@ def _worker(rank, world, port, batch, opts, queue):
     init_dap()
     cuda = torch.cuda.is_available()
     model = load_model(opts["model_name"], opts.get("param_path"), opts.get("chunk_size"), opts.get("inplace", False), opts.get("overrides"),
-                       opts.get("seed", 0), bf16=opts.get("bf16", True))
+                       opts.get("seed", 0), bf16=opts.get("bf16", True), shard_pair=opts.get("shard_pair", False))
     if cuda:
         torch.cuda.synchronize()
     out, seconds = predict(model, batch)
@@ -89,10 +99,12 @@ def _worker(rank, world, port, batch, opts, queue):
     shutdown()
 
 
-def run_inference(batch, gpus=1, model_name="model_1", param_path=None, chunk_size=None, inplace=False, seed=0, overrides=None, port=None):
+def run_inference(batch, gpus=1, model_name="model_1", param_path=None, chunk_size=None, inplace=False, seed=0, overrides=None, port=None,
+                  shard_pair=False):
     """Runs the model on ``batch`` (features with the recycling dimension last) over ``gpus`` DAP ranks; returns numpy outputs."""
     import torch.multiprocessing as mp
-    opts = {"model_name": model_name, "param_path": param_path, "chunk_size": chunk_size, "inplace": inplace, "seed": seed, "overrides": overrides}
+    opts = {"model_name": model_name, "param_path": param_path, "chunk_size": chunk_size, "inplace": inplace, "seed": seed, "overrides": overrides,
+            "shard_pair": shard_pair}
     batch = {k: (v.cpu().numpy() if isinstance(v, torch.Tensor) else np.asarray(v)) for k, v in batch.items()}
     ctx = mp.get_context("spawn")
     manager = ctx.Manager()

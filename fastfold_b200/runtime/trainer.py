@@ -77,6 +77,8 @@ class FlatAdamTrainer:
         self.static_inputs = None
         self.static_loss = None
         self.graph_fallback = False  # True: a failed capture switches to eager steps instead of raising
+        self.aux_getter = None       # callable returning the step's auxiliary outputs (set by the loss function); kept per graph
+        self.aux = None
         self._graphs = {}            # graph_key -> (graph, static inputs, static loss, launches)
         self._graph_pool = None
         self.grad_reducer = grad_reducer
@@ -104,7 +106,22 @@ class FlatAdamTrainer:
             self.flat_g = torch.zeros(total, device=dev, dtype=self.dtype)
         # fp32 gradient sink: weight- and bias-gradient kernels of the fused ops add straight into it (split-K atomics),
         # which removes a zero-fill, a conversion and an accumulate kernel per parameter; folded into flat_g once per step
-        self.flat_g32 = torch.zeros(total, device=dev, dtype=torch.float32) if (grad_sink and dev.type == "cuda" and self.dtype == torch.bfloat16) else None
+        self.flat_g32_padded = torch.zeros(padded, device=dev, dtype=torch.float32) if (grad_sink and dev.type == "cuda" and self.dtype == torch.bfloat16) else None
+        self.flat_g32 = None if self.flat_g32_padded is None else self.flat_g32_padded[:total]
+        if self.grad_heap is None:
+            self.flat_g_padded = None
+        import os as _os
+        self.overlap = _os.environ.get("FASTFOLD_GRAD_OVERLAP", "1") != "0"
+        self._overlap_active = False
+        self._covered = []
+        self._pending = None
+        self.bucket_segments = int(_os.environ.get("FASTFOLD_GRAD_BUCKET_SEGMENTS", "12"))
+        self._range_of = {}
+        self._side = torch.cuda.Stream() if dev.type == "cuda" else None
+        if self.grad_heap is not None:
+            from ..utils import checkpointing as _ckpt
+            _ckpt.POST_BACKWARD_HOOKS[:] = [h for h in _ckpt.POST_BACKWARD_HOOKS if getattr(h, "__self__", None).__class__ is not FlatAdamTrainer]
+            _ckpt.POST_BACKWARD_HOOKS.append(self._on_segment_backward)
         self.master = torch.empty(total, device=dev, dtype=torch.float32)
         self.exp_avg = torch.zeros(total, device=dev, dtype=torch.float32)
         self.exp_avg_sq = torch.zeros(total, device=dev, dtype=torch.float32)
@@ -127,6 +144,7 @@ class FlatAdamTrainer:
                 setattr(p, GRAD_SINK_ATTR, self.flat_g32[off:off + k].view(p.shape))
             rep = bool(replicated_param_filter(n)) if replicated_param_filter else False
             scales.append((off, k, rep))
+            self._range_of[id(p)] = (off, off + k)
             off += k
         self.master.copy_(self.flat_w.float())
         self.base_gscale = 1.0 / D
@@ -145,14 +163,92 @@ class FlatAdamTrainer:
         self.hp_host[3] = self.base_gscale
         self.hp.copy_(self.hp_host, non_blocking=True)
 
+    # -- gradient reduction overlapped with backward --------------------------------------------------------------
+    # Activation checkpointing runs backward segment by segment (last block first).  As soon as a segment's backward
+    # has been enqueued, its slice of the flat gradient buffer is final: a side stream folds the fp32 sink into it and
+    # runs the two-shot NVLink all-reduce on just that slice while the main stream goes on with the next segment.
+    # What no segment covers (embedders, heads, closing projections) is reduced after backward.  Inside a captured
+    # step the side stream is a forked branch of the graph.
+    def _segment_range(self, fn):
+        blocks = getattr(fn, "__blocks__", None) or [fn]
+        lo, hi = None, None
+        for b in blocks:
+            mod = getattr(b, "func", b)
+            mod = getattr(mod, "__self__", mod)
+            if not isinstance(mod, torch.nn.Module):
+                return None
+            for p in mod.parameters():
+                r = self._range_of.get(id(p))
+                if r is None:
+                    continue
+                lo = r[0] if lo is None else min(lo, r[0])
+                hi = r[1] if hi is None else max(hi, r[1])
+        return None if lo is None else (lo, hi)
+
+    def _reduce_range(self, lo, hi):
+        """Fold the fp32 sink into ``flat_g[lo:hi]`` and sum that slice over the ranks (``lo``, ``hi`` multiples of 8)."""
+        if hi <= lo:
+            return
+        if self.flat_g32 is not None:
+            self.flat_g_padded[lo:hi].add_(self.flat_g32_padded[lo:hi])
+        from ..parallel import symm
+        _lib.check(symm._libc().ffb_symm_allreduce_bf16(__import__("ctypes").byref(self.grad_heap.ctx), self.grad_slot.index,
+                                                        self.grad_slot.offset + lo * 2, hi - lo, 1.0, _lib.stream_ptr()), "symm_allreduce_bf16")
+
+    def _on_segment_backward(self, fn):
+        if not self._overlap_active:
+            return
+        r = self._segment_range(fn)
+        if r is None:
+            return
+        # elements below the next multiple of 8 belong to the previous segment's slice (reduced later), those up to the
+        # next multiple of 8 past the end belong to a segment that is already complete
+        lo, hi = (r[0] + 7) // 8 * 8, min((r[1] + 7) // 8 * 8, self.flat_g_padded.numel())
+        if hi <= lo:
+            return
+        # segments arrive back to front and are adjacent in the flat buffer: merge `bucket_segments` of them into one
+        # reduction (a fork of the side stream per segment costs more than the small slices are worth)
+        if self._pending is not None and self._pending[0] == hi:
+            self._pending = (lo, self._pending[1], self._pending[2] + 1)
+        else:
+            self._flush_pending()
+            self._pending = (lo, hi, 1)
+        if self._pending[2] >= self.bucket_segments:
+            self._flush_pending()
+
+    def _flush_pending(self):
+        if self._pending is None:
+            return
+        lo, hi, _ = self._pending
+        self._pending = None
+        main = torch.cuda.current_stream()
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            self._reduce_range(lo, hi)
+        self._covered.append((lo, hi))
+
     def _reduce_grads(self):
         if core.get_world_size() > 1:
             if self.grad_reducer is not None:
                 self.grad_reducer(self.flat_g)
+            elif self.grad_heap is not None and (self._covered or self._pending is not None):
+                self._flush_pending()
+                torch.cuda.current_stream().wait_stream(self._side)
+                pos = 0
+                for lo, hi in sorted(self._covered):
+                    self._reduce_range(pos, lo)
+                    pos = max(pos, hi)
+                self._reduce_range(pos, self.flat_g_padded.numel())
             elif self.grad_heap is not None:
+                if self.flat_g32 is not None:
+                    self.flat_g.add_(self.flat_g32)
                 self.grad_heap.all_reduce_(self.grad_slot, self.flat_g_padded.numel())
             else:
+                if self.flat_g32 is not None:
+                    self.flat_g.add_(self.flat_g32)
                 dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM)
+        elif self.flat_g32 is not None:
+            self.flat_g.add_(self.flat_g32)
         if self.rep_scale is not None:
             self.flat_g.mul_(self.rep_scale)
 
@@ -177,9 +273,13 @@ class FlatAdamTrainer:
         if self.flat_g32 is not None:
             self.flat_g32.zero_()
         loss = self.loss_fn(self.model, *inputs)
-        loss.backward()
-        if self.flat_g32 is not None:
-            self.flat_g.add_(self.flat_g32)
+        self._covered = []
+        self._pending = None
+        self._overlap_active = self.overlap and self.grad_heap is not None and self.grad_reducer is None
+        try:
+            loss.backward()
+        finally:
+            self._overlap_active = False
         self._reduce_grads()
         self._adam()
         return loss.detach()
@@ -193,7 +293,7 @@ class FlatAdamTrainer:
         self._set_hp()
         if self.use_graph and graph_key is not None:
             if graph_key in self._graphs:
-                self.graph, self.static_inputs, self.static_loss, self.launches_per_step = self._graphs[graph_key]
+                self.graph, self.static_inputs, self.static_loss, self.launches_per_step, self.aux = self._graphs[graph_key]
             else:
                 self.graph = None
         if not self.use_graph:
@@ -201,6 +301,7 @@ class FlatAdamTrainer:
             loss = self._body(inputs)
             self.launches_per_step = _lib.LAUNCHES[0] - n0
             self.step_count += 1
+            self.aux = self.aux_getter() if self.aux_getter is not None else None
             return loss
         if self.graph is None and self.graph_fallback:
             try:
@@ -235,8 +336,9 @@ class FlatAdamTrainer:
             self.launches_per_step = _lib.LAUNCHES[0] - n0
             self.step_count += 2
             self._set_hp()
+            self.aux = self.aux_getter() if self.aux_getter is not None else None
             if graph_key is not None:
-                self._graphs[graph_key] = (self.graph, self.static_inputs, self.static_loss, self.launches_per_step)
+                self._graphs[graph_key] = (self.graph, self.static_inputs, self.static_loss, self.launches_per_step, self.aux)
         else:
             for dst, src in zip(self.static_inputs, inputs):
                 if isinstance(dst, torch.Tensor) and dst.data_ptr() != src.data_ptr():

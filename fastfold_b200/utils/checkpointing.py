@@ -15,6 +15,11 @@ def _flatten_tensors(args):
     return tuple(a for a in args if isinstance(a, torch.Tensor))
 
 
+# Called with the checkpointed function right after its backward (recomputation + gradient kernels of its blocks) has
+# been enqueued: the trainer uses it to start reducing that segment's weight gradients while backward continues.
+POST_BACKWARD_HOOKS = []
+
+
 class _Checkpoint(torch.autograd.Function):
     @staticmethod
     def forward(ctx, fn, n_args, *args):
@@ -35,6 +40,8 @@ class _Checkpoint(torch.autograd.Function):
         if pairs:
             torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
         in_grads = tuple(t.grad if t.requires_grad else None for t in inputs)
+        for hook in POST_BACKWARD_HOOKS:
+            hook(ctx.fn)
         # trailing entries: parameters passed only so that autograd records a dependency
         return (None, None) + in_grads + (None,) * (len(ctx.needs_input_grad) - 2 - len(in_grads))
 

@@ -165,3 +165,71 @@ def test_ending_node_strided_matches_transposed_reference(device_status):
     for (n_, p), q in zip(ref.named_parameters(), gpu.parameters()):
         e = (q.grad.float().cpu() - p.grad).abs().max().item()
         assert e < 0.06 * max(1.0, p.grad.abs().max().item()), (n_, e)
+
+
+@pytest.mark.parametrize("B,n,H,use_bias,transposed", [(3, 640, 4, True, False), (2, 1024, 4, True, False), (2, 1024, 8, False, True),
+                                                        (1, 2048, 4, True, False)])
+def test_packed_backward_long_rows(B, n, H, use_bias, transposed, device_status):
+    """Rows longer than the 512 queries whose gradient fits tensor memory: backward runs in blocks of 512 queries and sums
+    the key / value gradients across the blocks; forward and all gradients against the fp32 reference."""
+    torch.manual_seed(B * 31 + n)
+    shape = (1, n, B, 3, H, 32) if transposed else (1, B, n, 3, H, 32)
+    qkv = (torch.randn(*shape, device=DEV) * 0.7).to(torch.bfloat16).requires_grad_(True)
+    bias = (torch.randn(1, 1, H, n, n, device=DEV)).to(torch.bfloat16).requires_grad_(True) if use_bias else None
+    mask = (torch.rand(1, B, n, device=DEV) > 0.2).to(torch.bfloat16)
+    mask[..., 0] = 1
+    assert flash.packed_supported(qkv, mask, bias, transposed=transposed)
+    out = flash.flash_attention_packed(qkv, mask, bias, 32 ** -0.5, transposed=transposed)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qkv_r = qkv.detach().float().requires_grad_(True)
+    bias_r = bias.detach().float().requires_grad_(True) if use_bias else None
+    src = qkv_r.transpose(1, 2) if transposed else qkv_r
+    qr, kr, vr = (src[:, :, :, i].permute(0, 1, 3, 2, 4) for i in range(3))
+    ref = attention_core_ref(qr, kr, vr, mask.float(), bias_r).permute(0, 1, 3, 2, 4).reshape(1, B, n, H * 32)
+    if transposed:
+        ref = ref.transpose(1, 2)
+    ref.backward(g.float())
+    assert (out.float() - ref).abs().max() < 2e-2
+    gerr = (qkv.grad.float() - qkv_r.grad).abs().max().item()
+    assert gerr < 3e-2 * max(1.0, qkv_r.grad.abs().max().item()), gerr
+    if use_bias:
+        berr = (bias.grad.float() - bias_r.grad).abs().max().item()
+        assert berr < 3e-2 * max(1.0, bias_r.grad.abs().max().item()), berr
+
+
+@pytest.mark.parametrize("c,heads", [(8, 8), (16, 4)])
+def test_narrow_heads_train_on_the_fused_kernels(c, heads, device_status):
+    """Gated self attention with 8- / 16-channel heads (extra-MSA rows, template triangles) under autograd: the module runs
+    the fused kernels through differentiably zero-padded weights; outputs and every gradient against fp32 on the CPU."""
+    from fastfold_b200.models.fastnn.ops import SelfAttention
+    from fastfold_b200.ops import _lib
+    torch.manual_seed(c)
+    att = SelfAttention(64, c, heads, 64, gating=True)
+    with torch.no_grad():
+        for p in att.parameters():
+            p.copy_(torch.randn_like(p) * 0.2)
+    gpu = SelfAttention(64, c, heads, 64, gating=True)
+    gpu.load_state_dict(att.state_dict())
+    gpu = gpu.to(DEV, torch.bfloat16)
+    with torch.no_grad():
+        for p, q in zip(att.parameters(), gpu.parameters()):
+            p.copy_(q.float().cpu())
+    x = torch.randn(1, 6, 72, 64)
+    xg = x.to(DEV, torch.bfloat16).requires_grad_(True)
+    xr = xg.detach().float().cpu().requires_grad_(True)
+    mask = (torch.rand(1, 6, 72) > 0.2).float()
+    mask[..., 0] = 1
+    bias = torch.randn(1, heads, 72, 72)
+    n0 = _lib.LAUNCHES[0]
+    out, _ = gpu(xg, mask.to(DEV, torch.bfloat16), (bias.to(DEV, torch.bfloat16), -1))
+    assert _lib.LAUNCHES[0] - n0 >= 3
+    ref, _ = att(xr, mask, (bias, -1))
+    assert (out.float().cpu() - ref.detach()).abs().max() < 6e-2 * max(1.0, ref.abs().max().item())
+    g = torch.randn_like(ref)
+    ref.backward(g)
+    out.backward(g.to(DEV, torch.bfloat16))
+    assert (xg.grad.float().cpu() - xr.grad).abs().max() < 6e-2 * max(1.0, xr.grad.abs().max().item())
+    for (name, p), q in zip(att.named_parameters(), gpu.parameters()):
+        e = (q.grad.float().cpu() - p.grad).abs().max().item()
+        assert e < 8e-2 * max(1.0, p.grad.abs().max().item()), (name, e)

@@ -214,6 +214,29 @@ def test_global_attention_core(R, S, H, c, device_status):
     assert (out.float() - ref).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("R,S,H,c", [(9, 300, 8, 8), (5, 45, 4, 16), (3, 700, 8, 32)])
+def test_global_attention_core_backward(R, S, H, c, device_status):
+    """Backward kernel of the global column attention (d q, d kv, d gate, d gate-bias) against autograd through the fp32
+    reference; includes a fully masked column."""
+    torch.manual_seed(R * S)
+    q = (torch.randn(R, H, c, device=DEV) * 0.8).bfloat16().requires_grad_(True)
+    kv = torch.randn(R, S, 2 * c, device=DEV).bfloat16().requires_grad_(True)
+    mask = (torch.rand(R, S, device=DEV) > 0.2).bfloat16()
+    mask[1] = 0
+    gate = torch.randn(R, S, H * c, device=DEV).bfloat16().requires_grad_(True)
+    gb = torch.randn(H * c, device=DEV).bfloat16().requires_grad_(True)
+    dout = torch.randn(R, S, H * c, device=DEV).bfloat16()
+    out = ops.global_attention_core(q, kv, mask, gate, gb)
+    assert out.grad_fn is not None and "GlobalAttention" in type(out.grad_fn).__name__
+    out.backward(dout)
+    got = [t.grad.float().clone() for t in (q, kv, gate, gb)]
+    ref_in = [t.detach().float().requires_grad_(True) for t in (q, kv, gate, gb)]
+    ops.global_attention_ref(ref_in[0], ref_in[1], mask, ref_in[2], ref_in[3]).backward(dout.float())
+    for name, a, b in zip(("dq", "dkv", "dgate", "dgate_bias"), got, [t.grad for t in ref_in]):
+        tol = 3e-2 * max(1.0, b.abs().max().item())
+        assert (a - b).abs().max().item() <= tol, "%s: max err %g (ref max %g)" % (name, (a - b).abs().max().item(), b.abs().max().item())
+
+
 def test_global_attention_module_matches_composite(device_status):
     """The fastnn GlobalAttention module gives the same result with the fused inference kernel (no grad) as with its
     composite path (grad enabled)."""
@@ -227,8 +250,10 @@ def test_global_attention_module_matches_composite(device_status):
     mask = (torch.rand(1, 24, 200, device=DEV) > 0.1).bfloat16()
     with torch.no_grad():
         fused = ga(m, mask)
-    comp = ga(m, mask).detach()
-    assert (fused.float() - comp.float()).abs().max() < 3e-2 * max(1.0, comp.float().abs().max().item())
+    trained = ga(m, mask)                       # grad enabled: forward kernel under the autograd wrapper
+    comp = ga.float().cpu()(m.float().cpu(), mask.float().cpu()).detach()
+    assert (fused.float().cpu() - comp).abs().max() < 3e-2 * max(1.0, comp.abs().max().item())
+    assert (trained.detach().float().cpu() - comp).abs().max() < 3e-2 * max(1.0, comp.abs().max().item())
 
 
 @pytest.mark.parametrize("N", [64, 200])

@@ -115,6 +115,7 @@ def main():
     trainer = FlatAdamTrainer(model, loss_fn, lr=args.lr, eps=1e-8, use_graph=use_graph,
                               replicated_param_filter=default_replicated_param_filter)
     trainer.graph_fallback = True
+    trainer.aux_getter = lambda: getattr(loss_fn, "last", None)
     sched = AlphaFoldLRScheduler(trainer, max_lr=args.lr)
     start_epoch = 0
     if args.resume:
@@ -135,6 +136,9 @@ def main():
     def validate(epoch):
         """Validation pass of the reference's train.py:240-251: eval mode, no gradients, unclamped FAPE, superposition
         metrics; averages over this replica's samples and over the data-parallel replicas."""
+        bad = [n for n, p_ in model.named_parameters() if not bool(torch.isfinite(p_).all())]
+        if bad:
+            raise RuntimeError("non-finite parameters before validation: %s%s" % (", ".join(bad[:5]), " ..." if len(bad) > 5 else ""))
         model.eval()
         sums, count = {}, 0
         with torch.no_grad():
@@ -170,6 +174,7 @@ def main():
             batch = {k: v[..., :n_iter].to(device, non_blocking=True) for k, v in batch.items()}
             loss_fn.keys = sorted(batch)
             loss = trainer.step(*[batch[k] for k in loss_fn.keys], graph_key=(n_iter,) + tuple(loss_fn.keys))
+            loss_fn.last = trainer.aux if trainer.aux is not None else loss_fn.last      # the replayed graph's own output tensors
             sched.step()
             steps_done += 1
             if (i + 1) % args.log_interval == 0:
