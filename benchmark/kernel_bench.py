@@ -4,6 +4,8 @@
     python benchmark/kernel_bench.py attention [--b 128 --h 8 --len 256] [--backward]
     python benchmark/kernel_bench.py layernorm [--rows 65536 --c 128] [--backward]
     python benchmark/kernel_bench.py global_attention [--b 256 --len 5120 --h 8]
+    python benchmark/kernel_bench.py global_attention_bwd [--b 256 --len 5120 --h 8]
+    python benchmark/kernel_bench.py ipa       [--len 1024]
     python benchmark/kernel_bench.py floor     (per-launch floor of small dependent kernels inside a CUDA graph)
     python benchmark/kernel_bench.py all
 
@@ -171,6 +173,41 @@ def bench_global_attention(t, R, S, H):
     print("global attention R=%d S=%d H=%d c=8: %.1f us  (%.0f GB/s -> %.2f %s)" % (R, S, H, us, byt / us / 1e3, byt / hbm * 1e6 / us, tag))
 
 
+def bench_global_attention_bwd(t, R, S, H):
+    """Backward of the global column attention core (d q, d kv, d gate): two passes over kv, gate and dout, two writes."""
+    hbm, _, tag = _peaks()
+    c = 8
+    q = _rand(R, H, c, scale=0.8).requires_grad_(True)
+    kv = _rand(R, S, 2 * c).requires_grad_(True)
+    mask = (torch.rand(R, S, device=DEV) > 0.1).to(torch.bfloat16)
+    gate = _rand(R, S, H * c).requires_grad_(True)
+    gb = _rand(H * c)
+    out = K.global_attention_core(q, kv, mask, gate, gb)
+    dout = _rand(R, S, H * c)
+    us = t(lambda: torch.autograd.grad(out, (q, kv, gate), dout, retain_graph=True))
+    byt = (2 * kv.numel() + 2 * mask.numel() + 2 * gate.numel() + 2 * dout.numel() + kv.numel() + gate.numel()) * 2
+    print("global attention backward R=%d S=%d H=%d c=8: %.1f us  (%.0f GB/s -> %.2f %s)" % (R, S, H, us, byt / us / 1e3, byt / hbm * 1e6 / us, tag))
+
+
+def bench_ipa(t, N):
+    """Invariant point attention core (12 heads, 16 channels, 4 + 8 points, c_z 128): the pair tensor [N, N, 128] is read once."""
+    import math
+    from fastfold_b200.ops.ipa import ipa_core
+    hbm, _, tag = _peaks()
+    H, C, PQ, PV, CZ = 12, 16, 4, 8, 128
+    f = lambda *s: torch.randn(*s, device=DEV)
+    q, k, v = f(N, H, C), f(N, H, C), f(N, H, C)
+    qp, kp, vp = f(N, H, PQ, 3) * 8, f(N, H, PQ, 3) * 8, f(N, H, PV, 3) * 8
+    z = _rand(N, N, CZ)
+    wb, bb, gamma, mask = f(H, CZ) * 0.1, f(H) * 0.1, torch.rand(H, device=DEV) * 0.1, torch.ones(N, device=DEV)
+    with torch.no_grad():
+        us = t(lambda: ipa_core(q, k, v, qp, kp, vp, z, wb, bb, gamma, mask, math.sqrt(1 / 48), math.sqrt(1 / 3), 1e5))
+    byt = z.numel() * 2
+    flops = 2.0 * N * N * H * (C + 3 * PQ + CZ + C + 3 * PV + CZ)
+    print("ipa core N=%d: %.1f us  (pair tensor %.0f MB -> %.0f GB/s, %.2f %s; %.1f fp32 TFLOP/s)" % (
+        N, us, byt / 1e6, byt / us / 1e3, byt / hbm * 1e6 / us, tag, flops / us / 1e6))
+
+
 def bench_floor(iters):
     """Per-launch time of back-to-back DEPENDENT launches inside one CUDA graph (warm cache): the floor every small
     kernel of a DAP-sharded step pays, for the kernels of this package, a PyTorch elementwise kernel and cuBLAS.  Each op
@@ -219,7 +256,7 @@ def bench_floor(iters):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "global_attention", "floor", "all"])
+    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "global_attention", "global_attention_bwd", "ipa", "floor", "all"])
     ap.add_argument("--m", type=int, default=65536)
     ap.add_argument("--n", type=int, default=512)
     ap.add_argument("--k", type=int, default=128)
@@ -241,6 +278,10 @@ def main():
         bench_attention(t, args.b, args.h, args.len, args.backward)
     elif args.op == "layernorm":
         bench_layernorm(t, args.rows, args.c, args.backward)
+    elif args.op == "ipa":
+        bench_ipa(t, args.len if args.len != 256 else 1024)
+    elif args.op == "global_attention_bwd":
+        bench_global_attention_bwd(t, args.b if args.b != 128 else 256, args.len if args.len != 256 else 5120, args.h)
     elif args.op == "floor":
         bench_floor(args.iters)
     elif args.op == "global_attention":
@@ -256,6 +297,9 @@ def main():
             bench_layernorm(t, rows, C, False)
             bench_layernorm(t, rows, C, True)
         bench_global_attention(t, 256, 5120, 8)
+        bench_global_attention_bwd(t, 256, 5120, 8)
+        bench_ipa(t, 1024)
+        bench_ipa(t, 2048)
     from fastfold_b200.ops import _lib
     st = _lib.read_status()
     if st[0]:

@@ -39,6 +39,18 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Raises one flag word on every rank: ONE system-scope fence orders everything this thread has observed (its block's
+// accesses through the CTA barrier, the other blocks' through the block counter) before the flag stores, which then go
+// out back to back.  A release store per rank instead would serialise one NVLink round trip per rank - measured 39 us
+// per small collective at 8 ranks against 15 us at 2.
+__device__ __forceinline__ void signal_all(const SymmCtx& c, int word, uint32_t value) {
+  __threadfence_system();
+  for (int r = 0; r < c.world; ++r) st_relaxed_sys(c.flags[r] + word, value);
+}
 
 // flag pad layout (uint32 words)
 __device__ __forceinline__ int w_ready(int slot, int r) { return slot * 16 + r; }
@@ -90,9 +102,7 @@ __device__ __forceinline__ void last_block_signal(const SymmCtx& c, int slot, ui
     s_last = (atomicAdd(blk, 1u) == total - 1) ? 1 : 0;
     if (s_last) {
       *blk = 0;
-      __threadfence_system();
-      for (int r = 0; r < c.world; ++r)
-        st_release_sys(c.flags[r] + (ready_not_done ? w_ready(slot, c.rank) : w_done(slot, c.rank)), epoch);
+      signal_all(c, ready_not_done ? w_ready(slot, c.rank) : w_done(slot, c.rank), epoch);
       if (!ready_not_done) c.flags[c.rank][w_epoch(slot)] = epoch;
     }
   }
@@ -303,10 +313,7 @@ __global__ void __launch_bounds__(256) symm_allreduce_bf16_k(SymmCtx c, int slot
   if (threadIdx.x == 0) {
     s_epoch = next_epoch(c, slot);
     // entry: every rank announces that its gradients are complete (this kernel runs after backward on the stream)
-    if (blockIdx.x == 0) {
-      __threadfence_system();
-      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_ready(slot, c.rank), s_epoch);
-    }
+    if (blockIdx.x == 0) signal_all(c, w_ready(slot, c.rank), s_epoch);
     s_ok = wait_peers(c, true, slot, s_epoch) ? 1 : 0;
   }
   __syncthreads();
@@ -347,8 +354,7 @@ __global__ void __launch_bounds__(256) symm_allreduce_bf16_k(SymmCtx c, int slot
     s_last = (atomicAdd(blk, 1u) == gridDim.x - 1) ? 1 : 0;
     if (s_last) {
       *blk = 0;
-      __threadfence_system();
-      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_done(slot, c.rank), s_epoch);
+      signal_all(c, w_done(slot, c.rank), s_epoch);
       wait_peers(c, false, slot, s_epoch);
       c.flags[c.rank][w_epoch(slot)] = s_epoch;
     }
@@ -380,28 +386,39 @@ struct XchgArgs {
 constexpr int XCHG_THREADS = 256;
 constexpr int XCHG_U = 4;
 
-// thread 0 only: wait until every rank (this one included) raised ready[slot] for `epoch`
+// Whole block: wait until every rank (this one included) raised ready[slot] for `epoch`.  Thread r polls rank r's flag,
+// so the polls of the (up to 8) flags overlap instead of running one after the other; returns the verdict to all threads.
 __device__ __forceinline__ bool wait_all_ready(const SymmCtx& c, int slot, uint32_t epoch) {
-  bool ok = true;
-  for (int r = 0; r < c.world; ++r) {
+  int ok = 1;
+  if ((int)threadIdx.x < c.world) {
+    const int r = threadIdx.x;
     if (!wait_flag(c.flags[c.rank] + w_ready(slot, r), epoch, c.wait_ns)) {
       report(ST_TIMEOUT_PEER, (slot << 8) | r | 0x80);
-      ok = false;
+      ok = 0;
     }
   }
-  return ok;
+  return __syncthreads_and(ok) != 0;
+}
+
+// Whole block: wait until every peer has raised done[slot] for `want` (the slot's previous contents have been consumed).
+__device__ __forceinline__ bool wait_all_done(const SymmCtx& c, int slot, uint32_t want) {
+  int ok = 1;
+  if ((int)threadIdx.x < c.world && (int)threadIdx.x != c.rank) {
+    const int r = threadIdx.x;
+    if (!wait_flag(c.flags[c.rank] + w_done(slot, r), want, c.wait_ns)) {
+      report(ST_TIMEOUT_PEER, (slot << 8) | r);
+      ok = 0;
+    }
+  }
+  return __syncthreads_and(ok) != 0;
 }
 
 // Phase 1 of a push collective; returns the epoch (all threads).  On return this block's stores have been issued and the
 // last block of the grid has raised (or will raise) the ready flags.
 __device__ __forceinline__ uint32_t xchg_push(const SymmCtx& c, int slot, long long heap_off, const uint4* __restrict__ src, long long X,
                                               long long Y, int scatter) {
-  __shared__ uint32_t s_epoch;
-  if (threadIdx.x == 0) {
-    s_epoch = next_epoch(c, slot);
-    wait_peers(c, false, slot, s_epoch - 1u);        // every rank has finished with what its slot held before
-  }
-  __syncthreads();
+  const uint32_t s_epoch = next_epoch(c, slot);       // the epoch word only changes when the LAST block of a kernel finishes
+  wait_all_done(c, slot, s_epoch - 1u);              // every rank has finished with what its slot held before
   const int P = c.world;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -454,9 +471,9 @@ __device__ __forceinline__ void xchg_finish(const SymmCtx& c, int slot, uint32_t
     s_last2 = (atomicAdd(blk, 1u) == gridDim.x - 1) ? 1 : 0;
     if (s_last2) {
       *blk = 0;
-      // `done` only tells the peers that this rank has finished READING its slot (the values were consumed by the
-      // stores above, so the loads have completed): the release stores below suffice, no system-scope fence
-      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_done(slot, c.rank), epoch);
+      // `done` tells the peers that this rank has finished READING its slot; no remote access of this kernel is still
+      // outstanding here, so the fence inside is cheap
+      signal_all(c, w_done(slot, c.rank), epoch);
       c.flags[c.rank][w_epoch(slot)] = epoch;
     }
   }
@@ -476,9 +493,7 @@ __global__ void __launch_bounds__(XCHG_THREADS) symm_xchg_k(SymmCtx c, int slot,
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t epoch = xchg_push(c, slot, heap_off, a.src, a.X, a.Y, a.scatter);
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = wait_all_ready(c, slot, epoch) ? 1 : 0;
-  __syncthreads();
+  const bool s_ok = wait_all_ready(c, slot, epoch);
   if (s_ok) {
     const int P = c.world;
     const uint4* in = reinterpret_cast<const uint4*>(c.heap[c.rank] + heap_off);
@@ -538,73 +553,100 @@ __global__ void __launch_bounds__(128) symm_xchg_ln_k(SymmCtx c, int slot, long 
   const long long yu = (long long)Bl * (C / 8);
   // mode 0: src [Al][P][Bl*C]; mode 1: src [P][Al][Bl*C] = X 1 with chunks of Al * Bl * C
   const uint32_t epoch = mode == 0 ? xchg_push(c, slot, heap_off, src, Al, yu, 1) : xchg_push(c, slot, heap_off, src, 1, (long long)Al * yu, 1);
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = wait_all_ready(c, slot, epoch) ? 1 : 0;
-  __syncthreads();
+  const bool s_ok = wait_all_ready(c, slot, epoch);
   const int Ad = mode == 0 ? A : Al, Bd = mode == 0 ? Bl : B;       // output extents
   const long long rows = (long long)Ad * Bd;
   const int lane = threadIdx.x & 31;
   constexpr int NV = VPL / 8;
+  // lanes per row: a row of C channels is C / 8 16-byte units; narrow rows share a warp (C = 128: two rows per warp,
+  // C = 64: four), so that every lane carries data.  LN_U row groups are in flight per warp and step.
+  int lpr = 32;
+  if (NV == 1) {
+    while (lpr > 1 && (lpr >> 1) * 8 >= C) lpr >>= 1;
+  }
+  const int rpw = 32 / lpr;                                           // rows per warp and step
+  const int sub = lane / lpr, l = lane - sub * lpr;
+  constexpr int LN_U = 4;
   if (s_ok) {
     const bf16* in = reinterpret_cast<const bf16*>(c.heap[c.rank] + heap_off);
-    const long long wstride = (long long)gridDim.x * 4;
-    for (long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5); row < rows; row += wstride) {
-      const int a = (int)(row / Bd), b = (int)(row - (long long)a * Bd);
-      long long srow = row;                                            // mode 0: the slot IS the result layout
-      if (mode == 1) {
-        const int r = b / Bl;
-        srow = ((long long)r * Al + a) * Bl + (b - r * Bl);
-      }
-      const bf16* sp = in + srow * C;
-      float v[VPL];
-      float s = 0.f;
+    const long long wstride = (long long)gridDim.x * 4 * rpw;
+    // the loop bound depends on the warp's first row only, so all lanes of a warp run the same iterations (the
+    // shuffles below are warp-wide)
+    for (long long base = ((long long)blockIdx.x * 4 + (threadIdx.x >> 5)) * rpw; base < rows; base += wstride * LN_U) {
+      const long long row0 = base + sub;
+      uint4 raw[LN_U][NV];
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int c0 = (i * 32 + lane) * 8;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (c0 < C) {
-          raw = *reinterpret_cast<const uint4*>(sp + c0);
-          if (y_raw) *reinterpret_cast<uint4*>(y_raw + row * C + c0) = raw;
-        }
-        const bf162* h = reinterpret_cast<const bf162*>(&raw);
+      for (int u = 0; u < LN_U; ++u) {
+        const long long row = row0 + u * wstride;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(h[j]);
-          v[i * 8 + 2 * j] = f.x;
-          v[i * 8 + 2 * j + 1] = f.y;
-          s += f.x + f.y;
-        }
-      }
-      if (y_norm) {
-        const float mean = warp_sum(s) / C;
-        float q = 0.f;
+        for (int i = 0; i < NV; ++i) raw[u][i] = make_uint4(0, 0, 0, 0);
+        if (row < rows) {
+          long long srow = row;                                        // mode 0: the slot IS the result layout
+          if (mode == 1) {
+            const int a = (int)(row / Bd), b = (int)(row - (long long)a * Bd);
+            const int r = b / Bl;
+            srow = ((long long)r * Al + a) * Bl + (b - r * Bl);
+          }
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-          const int c0 = (i * 32 + lane) * 8;
-          if (c0 < C) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float d = v[i * 8 + j] - mean;
-              q += d * d;
-            }
+          for (int i = 0; i < NV; ++i) {
+            const int c0 = (i * lpr + l) * 8;
+            if (c0 < C) raw[u][i] = *reinterpret_cast<const uint4*>(in + srow * C + c0);
           }
         }
-        const float rstd = rsqrtf(warp_sum(q) / C + eps);
-        const long long orow = transpose_norm ? ((long long)b * Ad + a) : row;
+      }
+#pragma unroll
+      for (int u = 0; u < LN_U; ++u) {
+        const long long row = row0 + u * wstride;
+        const bool live = row < rows;                                  // lanes of a finished row group still take part in the shuffles
+        const int a = live ? (int)(row / Bd) : 0, b = live ? (int)(row - (long long)a * Bd) : 0;
+        float v[VPL];
+        float s = 0.f;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-          const int c0 = (i * 32 + lane) * 8;
-          if (c0 < C) {
-            const uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0), ub = *reinterpret_cast<const uint4*>(beta + c0);
-            const bf162 *hg = reinterpret_cast<const bf162*>(&ug), *hb = reinterpret_cast<const bf162*>(&ub);
-            uint4 uo;
-            bf162* ho = reinterpret_cast<bf162*>(&uo);
+          const int c0 = (i * lpr + l) * 8;
+          if (live && c0 < C && y_raw) *reinterpret_cast<uint4*>(y_raw + row * C + c0) = raw[u][i];
+          const bf162* h = reinterpret_cast<const bf162*>(&raw[u][i]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 g2 = __bfloat1622float2(hg[j]), b2 = __bfloat1622float2(hb[j]);
-              ho[j] = __floats2bfloat162_rn((v[i * 8 + 2 * j] - mean) * rstd * g2.x + b2.x, (v[i * 8 + 2 * j + 1] - mean) * rstd * g2.y + b2.y);
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            v[i * 8 + 2 * j] = f.x;
+            v[i * 8 + 2 * j + 1] = f.y;
+            s += f.x + f.y;
+          }
+        }
+        if (y_norm) {
+          for (int o = lpr >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          const float mean = s / C;
+          float q = 0.f;
+#pragma unroll
+          for (int i = 0; i < NV; ++i) {
+            const int c0 = (i * lpr + l) * 8;
+            if (c0 < C) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float d = v[i * 8 + j] - mean;
+                q += d * d;
+              }
             }
-            *reinterpret_cast<uint4*>(y_norm + orow * C + c0) = uo;
+          }
+          for (int o = lpr >> 1; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+          const float rstd = rsqrtf(q / C + eps);
+          const long long orow = transpose_norm ? ((long long)b * Ad + a) : row;
+#pragma unroll
+          for (int i = 0; i < NV; ++i) {
+            const int c0 = (i * lpr + l) * 8;
+            if (live && c0 < C) {
+              const uint4 ug = *reinterpret_cast<const uint4*>(gamma + c0), ub = *reinterpret_cast<const uint4*>(beta + c0);
+              const bf162 *hg = reinterpret_cast<const bf162*>(&ug), *hb = reinterpret_cast<const bf162*>(&ub);
+              uint4 uo;
+              bf162* ho = reinterpret_cast<bf162*>(&uo);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 g2 = __bfloat1622float2(hg[j]), b2 = __bfloat1622float2(hb[j]);
+                ho[j] = __floats2bfloat162_rn((v[i * 8 + 2 * j] - mean) * rstd * g2.x + b2.x, (v[i * 8 + 2 * j + 1] - mean) * rstd * g2.y + b2.y);
+              }
+              *reinterpret_cast<uint4*>(y_norm + orow * C + c0) = uo;
+            }
           }
         }
       }
@@ -623,8 +665,7 @@ __global__ void symm_slot_fence_k(SymmCtx c, int slot, int pre) {
   if (pre) {
     wait_peers(c, false, slot, e - 1u);
   } else {
-    __threadfence_system();
-    for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_ready(slot, c.rank), e);
+    signal_all(c, w_ready(slot, c.rank), e);
   }
 }
 
@@ -639,8 +680,7 @@ __global__ void symm_consume_fence_k(SymmCtx c, int slot, int pre) {
   if (pre) {
     wait_peers(c, true, slot, e);
   } else {
-    __threadfence_system();
-    for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + w_done(slot, c.rank), e);
+    signal_all(c, w_done(slot, c.rank), e);
     c.flags[c.rank][w_epoch(slot)] = e;
   }
 }
@@ -727,7 +767,9 @@ int ffb_symm_xchg_layernorm(const SymmCtx* c, int slot, long long heap_off, cons
   if (C % 8 || C > 1024 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
   if (A % c->world || B % c->world) return -3;
   const long long rows = (long long)(mode == 0 ? A : A / c->world) * (mode == 0 ? B / c->world : B);
-  const int grid = grid_for(rows, 4, 592);
+  // all blocks must be resident at once (they wait for flags that peers raise after ALL of their blocks pushed): four
+  // 128-thread blocks per SM for the narrow instantiation (92 registers), fewer for the wide ones
+  const int grid = grid_for(rows, 4, C <= 256 ? 592 : (C <= 512 ? 296 : 148));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (C <= 256) launch_k(symm_xchg_ln_k<8>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
   else if (C <= 512) launch_k(symm_xchg_ln_k<16>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);

@@ -114,3 +114,50 @@ def test_inference_is_bitwise_reproducible(device_status):
         for a, b in zip(first, again):
             if a is not None:
                 assert torch.equal(a, b)
+
+
+def _full_model_worker(rank, world, port, shard, out_dir):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, ROOT)
+    from fastfold_b200.ops import _lib
+    from fastfold_b200.parallel import init_dap, shutdown
+    from fastfold_b200.runtime.inference import load_model, predict
+    from fastfold_b200.utils.synthetic import random_features
+    init_dap(world, timeout_s=120)
+    model = load_model("model_3", None, chunk_size=None, inplace=True, seed=5, shard_pair=shard,
+                       overrides={"model.evoformer_stack.no_blocks": 2, "model.extra_msa.extra_msa_stack.no_blocks": 1})
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2 and float(p.abs().sum()) == 0.0:
+                p.normal_(0.0, 0.05)
+    batch = random_features(128, 16, 32, n_templ=0, n_recycle=1, seed=2)
+    out, _ = predict(model, batch)
+    torch.cuda.synchronize()
+    st = _lib.read_status()
+    torch.save({"pos": out["final_atom_positions"].float().cpu(), "single": out["single"].float().cpu(), "pair": out["pair"].float().cpu(),
+                "dist": out["distogram_logits"].float().cpu(), "status": st}, os.path.join(out_dir, "r%d.pt" % rank))
+    shutdown()
+
+
+def test_full_model_with_row_sharded_pair_tensor():
+    """Full (reduced-depth) model over two GPUs, in place, with the pair tensor kept as row shards from the embedders to the
+    heads (row-parallel invariant point attention kernel, sharded recycling and distogram head) against the run that
+    gathers the pair tensor after every stack."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = {}
+    for shard in (False, True):
+        with tempfile.TemporaryDirectory() as d:
+            mp.spawn(_full_model_worker, args=(2, _free_port(), shard, d), nprocs=2, join=True)
+            res[shard] = [torch.load(os.path.join(d, "r%d.pt" % r)) for r in range(2)]
+    full, sh = res[False], res[True]
+    assert all(r["status"][0] == 0 for r in full + sh)
+    assert sh[0]["pair"].shape[0] * 2 == full[0]["pair"].shape[0]
+    pair = torch.cat([sh[0]["pair"], sh[1]["pair"]], dim=0)
+    dist = torch.cat([sh[0]["dist"], sh[1]["dist"]], dim=0)
+    scale = lambda t: max(1.0, t.abs().mean().item())
+    assert (pair - full[0]["pair"]).abs().mean().item() < 3e-2 * scale(full[0]["pair"])
+    assert (dist - full[0]["dist"]).abs().mean().item() < 3e-2 * scale(full[0]["dist"])
+    assert (sh[0]["single"] - full[0]["single"]).abs().mean().item() < 3e-2 * scale(full[0]["single"])
+    assert torch.isfinite(sh[0]["pos"]).all() and torch.isfinite(full[0]["pos"]).all()

@@ -127,3 +127,45 @@ def test_narrow_head_attention_padded_path(device_status):
     comp = comp.to("cuda")
     err = (fast.float() - comp.detach().float()).abs().max().item()
     assert err < 4e-2 * max(1.0, comp.detach().float().abs().max().item()), err
+
+
+def test_first_pass_uses_current_weights_after_optimizer_steps(device_status):
+    """After optimiser steps that write the parameters through raw pointers (flat fused Adam), the no-grad pass of a block
+    (checkpoint first pass, recycling iterations: fused kernels with derived interleaved / padded weights) must give what
+    the grad-enabled pass gives with the live weights - nothing derived from an earlier step's weights may be reused."""
+    from fastfold_b200.models.fastnn import EvoformerStack
+    from fastfold_b200.models.fastnn.evoformer import draw_block_dropout
+    from fastfold_b200.runtime import FlatAdamTrainer
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    S, N = 32, 64
+    model = EvoformerStack(256, 128, 384, 1, blocks_per_ckpt=1)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2 and float(p.abs().sum()) == 0.0:
+                p.normal_(std=0.05)
+    model = model.to(dev, torch.bfloat16).train()
+    m = torch.randn(S, N, 256, device=dev, dtype=torch.bfloat16)
+    z = torch.randn(N, N, 128, device=dev, dtype=torch.bfloat16)
+    mm = torch.ones(S, N, device=dev, dtype=torch.bfloat16)
+    pm = torch.ones(N, N, device=dev, dtype=torch.bfloat16)
+
+    def loss_fn(mod, m, z, mm, pm):
+        om, oz, s = mod(m, z, mm, pm, None)
+        return om.float().pow(2).mean() + oz.float().pow(2).mean() + s.float().pow(2).mean()
+
+    blk = model.blocks[0]
+    drop = draw_block_dropout(N, 256, 128, dev, torch.bfloat16)
+    with torch.no_grad():
+        before = blk(m, z, mm, pm, _drop=drop)
+    tr = FlatAdamTrainer(model, loss_fn, lr=2e-2, use_graph=False)      # large steps: stale weights would be far off
+    for _ in range(3):
+        tr.step(m, z, mm, pm)
+    with torch.no_grad():
+        first_pass = blk(m, z, mm, pm, _drop=drop)
+    recomputed = blk(m.clone().requires_grad_(True), z.clone().requires_grad_(True), mm, pm, _drop=drop)
+    for a, b, c in zip(first_pass, recomputed, before):
+        moved = (a.float() - c.float()).abs().mean().item()
+        err = (a.float() - b.detach().float()).abs().mean().item()
+        assert moved > 1e-3, "the optimiser steps did not change the block's output"
+        assert err < 0.1 * moved + 2e-2 * max(1.0, b.detach().float().abs().mean().item()), (err, moved)

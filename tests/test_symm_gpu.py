@@ -86,7 +86,7 @@ def _worker(rank, world, port, out_path):
         dist.all_gather(parts, x)
         push_err = max(push_err, float((got.float() - torch.cat(parts, dim=dim).float()).abs().max()))
     for in_dim, out_dim in ((1, 2), (2, 1), (0, 2)):
-        shape = [4, 8 * world // 2, 8 * world // 2, 16]
+        shape = [2 * world, 4 * world, 4 * world, 16]          # every split dimension divides by the world size
         x = torch.randn(*shape, generator=g).to(dev, torch.bfloat16)
         in_d, out_d = in_dim + (0 if in_dim == 0 else 0), out_dim
         skew(in_dim + out_dim)

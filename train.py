@@ -51,6 +51,7 @@ def parse():
     p.add_argument("--n_seq", type=int, default=None)
     p.add_argument("--n_extra", type=int, default=None)
     p.add_argument("--blocks", type=int, default=None, help="override the number of Evoformer blocks (debugging)")
+    p.add_argument("--recycles", type=int, default=None, help="(synthetic) fixed number of recycling iterations per step instead of a uniform draw")
     p.add_argument("--lr", type=float, default=1e-3)
     p.add_argument("--no_graph", default=False, action="store_true", help="run every step eagerly instead of replaying captured CUDA graphs")
     p.add_argument("--val_interval", type=int, default=1, help="epochs between validation passes")
@@ -91,9 +92,9 @@ def main():
     n_res, n_seq, n_extra = args.n_res or tc.crop_size, args.n_seq or tc.max_msa_clusters, args.n_extra or tc.max_extra_msa
     if args.synthetic or not args.train_data_dir:
         from fastfold_b200.data.data_modules import SyntheticDataset
-        dataset = SyntheticDataset(n_res, n_seq, n_extra, n_recycle=config.data.common.max_recycling_iters, length=args.train_epoch_len,
-                                   seed=args.seed, dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size(),
-                                   n_templ=tc.max_templates if config.model.template.enabled else 0)
+        dataset = SyntheticDataset(n_res, n_seq, n_extra, n_recycle=config.data.common.max_recycling_iters if args.recycles is None else args.recycles,
+                                   length=args.train_epoch_len, seed=args.seed, dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size(),
+                                   n_templ=tc.max_templates if config.model.template.enabled else 0, uniform_recycling=args.recycles is None)
     else:
         from fastfold_b200.data.data_modules import StructureDataset
         dataset = StructureDataset(args.train_data_dir, args.train_alignment_dir, config.data, mode="train", seed=args.seed,
@@ -173,6 +174,7 @@ def main():
             n_iter = int(batch.pop("no_recycling_iters", torch.tensor(batch["aatype"].shape[-1] - 1)).reshape(-1)[0]) + 1
             batch = {k: v[..., :n_iter].to(device, non_blocking=True) for k, v in batch.items()}
             loss_fn.keys = sorted(batch)
+            t_step = time.time()
             loss = trainer.step(*[batch[k] for k in loss_fn.keys], graph_key=(n_iter,) + tuple(loss_fn.keys))
             loss_fn.last = trainer.aux if trainer.aux is not None else loss_fn.last      # the replayed graph's own output tensors
             sched.step()
@@ -183,7 +185,8 @@ def main():
                     out, last, parts = loss_fn.last
                     with torch.no_grad():
                         metrics = validation_metrics(out, last)
-                    log.info("epoch %d step %d lr %.2e loss %.4f | %s | %s", epoch, trainer.step_count, trainer.lr, float(loss),
+                    loss_value = float(loss)                      # synchronises: the step's kernels have finished
+                    log.info("epoch %d step %d (%.3f s) lr %.2e loss %.4f | %s | %s", epoch, trainer.step_count, time.time() - t_step, trainer.lr, loss_value,
                              " ".join("%s %.3f" % (k, float(v)) for k, v in parts.items() if k not in ("loss", "unscaled_loss")),
                              " ".join("%s %.3f" % (k, float(v)) for k, v in metrics.items()))
             if args.max_steps and steps_done >= args.max_steps:
