@@ -172,9 +172,9 @@ int ffb_layernorm_bwd_transposed(const void* dy, const void* x, const void* gamm
   }
   const long long nb = (rows + LTB_ROWS - 1) / LTB_ROWS;
   if (nb > 0x7fffffffLL) return -4;
-  launch_k(ln_bwd_transposed_kernel, (unsigned)nb, 256, smem, st, (const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part,
+  launch_light(ln_bwd_transposed_kernel, (unsigned)nb, 256, smem, st, (const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part,
                                                            rows, C);
-  launch_k(ltb_reduce_kernel, (2 * C + 31) / 32, 1024, 0, st, part, (int)nb, C, dgamma, dbeta);
+  launch_light(ltb_reduce_kernel, (2 * C + 31) / 32, 1024, 0, st, part, (int)nb, C, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -183,7 +183,7 @@ int ffb_glu_mask_t_fwd(const void* pre, const void* mask, void* out, int C2, lon
   if (R % 8 || C2 < 1) return -2;
   const long long n = (R >> 3) * C2;
   if (n <= 0) return 0;
-  launch_k(glu_mask_t_fwd_kernel, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)pre, (const bf16*)mask,
+  launch_light(glu_mask_t_fwd_kernel, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)pre, (const bf16*)mask,
                                                                                                         (bf16*)out, C2, R);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -193,7 +193,7 @@ int ffb_glu_mask_t_bwd(const void* dout, const void* pre, const void* mask, void
   if (R % 8 || C2 < 1) return -2;
   const long long n = (R >> 3) * C2;
   if (n <= 0) return 0;
-  launch_k(glu_mask_t_bwd_kernel, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)dout, (const bf16*)pre, (const bf16*)mask, (bf16*)dpre, C2, R);
+  launch_light(glu_mask_t_bwd_kernel, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)dout, (const bf16*)pre, (const bf16*)mask, (bf16*)dpre, C2, R);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -424,6 +424,8 @@ __device__ __forceinline__ uint32_t xchg_push(const SymmCtx& c, int slot, long l
   const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (scatter) {
     const long long n = X * P * Y;
+    const bool small = n < (1ll << 31);
+    const uint32_t Y32 = (uint32_t)Y;
     for (long long i = t0; i < n; i += stride * XCHG_U) {
       uint4 v[XCHG_U];
 #pragma unroll
@@ -433,9 +435,19 @@ __device__ __forceinline__ uint32_t xchg_push(const SymmCtx& c, int slot, long l
       for (int u = 0; u < XCHG_U; ++u) {
         const long long k = i + u * stride;
         if (k < n) {
-          const long long xq = k / Y, y = k - xq * Y;
-          const long long x = xq / P;
-          const int q = (int)(xq - x * P);
+          long long x, y;
+          int q;
+          if (small) {                                   // 32-bit divisions: a fifth of the instructions of the 64-bit ones
+            const uint32_t k32 = (uint32_t)k, xq = k32 / Y32;
+            y = k32 - xq * Y32;
+            x = xq / (uint32_t)P;
+            q = (int)(xq - (uint32_t)x * (uint32_t)P);
+          } else {
+            const long long xq = k / Y;
+            y = k - xq * Y;
+            x = xq / P;
+            q = (int)(xq - x * P);
+          }
           reinterpret_cast<uint4*>(c.heap[q] + heap_off)[((long long)c.rank * X + x) * Y + y] = v[u];
         }
       }
@@ -525,9 +537,16 @@ __global__ void __launch_bounds__(XCHG_THREADS) symm_xchg_k(SymmCtx c, int slot,
           if (k < n) {
             long long o = k;
             if (a.mode == 1) {
-              const long long rx = k / a.Y2, y = k - rx * a.Y2;
-              const long long r = rx / a.X2, x = rx - r * a.X2;
-              o = (x * P + r) * a.Y2 + y;
+              if (n < (1ll << 31)) {
+                const uint32_t k32 = (uint32_t)k, y2 = (uint32_t)a.Y2, x2 = (uint32_t)a.X2;
+                const uint32_t rx = k32 / y2, y = k32 - rx * y2;
+                const uint32_t r = rx / x2, x = rx - r * x2;
+                o = ((long long)x * P + r) * a.Y2 + y;
+              } else {
+                const long long rx = k / a.Y2, y = k - rx * a.Y2;
+                const long long r = rx / a.X2, x = rx - r * a.X2;
+                o = (x * P + r) * a.Y2 + y;
+              }
             }
             a.dst[o] = v[u];
           }
@@ -711,7 +730,7 @@ static int grid_for(long long n, int threads, int cap) {
 int ffb_symm_publish(const SymmCtx* c, int slot, long long heap_off, const void* src, long long bytes, void* stream) {
   if (bytes % 16 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
   const long long n16 = bytes / 16;
-  launch_k(symm_publish_k, grid_for((n16 + COPY_U - 1) / COPY_U, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, (const uint4*)src, n16);
+  launch_light(symm_publish_k, grid_for((n16 + COPY_U - 1) / COPY_U, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, (const uint4*)src, n16);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -720,7 +739,7 @@ int ffb_symm_pull(const SymmCtx* c, int slot, long long heap_off, void* dst, lon
   const long long n16 = bytes_per_rank / 16;
   {
     const int gx = grid_for((n16 + COPY_U - 1) / COPY_U, 256, 592 / c->world > 0 ? 592 / c->world : 1);
-    launch_k(symm_pull_k, dim3(gx, c->world), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, (uint4*)dst, n16, all_to_all);
+    launch_light(symm_pull_k, dim3(gx, c->world), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, (uint4*)dst, n16, all_to_all);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -732,9 +751,9 @@ int ffb_symm_a2a_layernorm(const SymmCtx* c, int slot, long long heap_off, int m
   const long long rows = (long long)(mode == 0 ? A : A / c->world) * (mode == 0 ? B / c->world : B);
   const int grid = grid_for(rows, 4, 1184);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (C <= 256) launch_k(symm_a2a_ln_k<8>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
-  else if (C <= 512) launch_k(symm_a2a_ln_k<16>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
-  else launch_k(symm_a2a_ln_k<32>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  if (C <= 256) launch_light(symm_a2a_ln_k<8>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else if (C <= 512) launch_light(symm_a2a_ln_k<16>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else launch_light(symm_a2a_ln_k<32>, grid, 128, 0, st, *c, slot, heap_off, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -757,7 +776,7 @@ int ffb_symm_xchg(const SymmCtx* c, int slot, long long heap_off, const void* sr
   a.dst = (uint4*)dst;
   const long long work = units * c->world;
   const int grid = grid_for((work + XCHG_U - 1) / XCHG_U, XCHG_THREADS, 296);
-  launch_k(symm_xchg_k, grid, XCHG_THREADS, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, a);
+  launch_light(symm_xchg_k, grid, XCHG_THREADS, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -771,9 +790,9 @@ int ffb_symm_xchg_layernorm(const SymmCtx* c, int slot, long long heap_off, cons
   // 128-thread blocks per SM for the narrow instantiation (92 registers), fewer for the wide ones
   const int grid = grid_for(rows, 4, C <= 256 ? 592 : (C <= 512 ? 296 : 148));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (C <= 256) launch_k(symm_xchg_ln_k<8>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
-  else if (C <= 512) launch_k(symm_xchg_ln_k<16>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
-  else launch_k(symm_xchg_ln_k<32>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  if (C <= 256) launch_light(symm_xchg_ln_k<8>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else if (C <= 512) launch_light(symm_xchg_ln_k<16>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
+  else launch_light(symm_xchg_ln_k<32>, grid, 128, 0, st, *c, slot, heap_off, (const uint4*)src, mode, A, B, C, (bf16*)y_raw, (bf16*)y_norm, (const bf16*)gamma, (const bf16*)beta, eps, transpose_norm);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -781,17 +800,17 @@ int ffb_symm_allreduce_bf16(const SymmCtx* c, int slot, long long heap_off, long
   if (n_elems % 8 || heap_off % 16 || slot < 0 || slot >= SYMM_MAX_SLOTS) return -2;
   const long long n8 = n_elems / 8;
   const long long per = (n8 + c->world - 1) / c->world;
-  launch_k(symm_allreduce_bf16_k, grid_for(per, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, n8, scale);
+  launch_light(symm_allreduce_bf16_k, grid_for(per, 256, 296), 256, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, heap_off, n8, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int ffb_symm_slot_fence(const SymmCtx* c, int slot, int pre, void* stream) {
-  launch_k(symm_slot_fence_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, pre);
+  launch_light(symm_slot_fence_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, pre);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int ffb_symm_consume_fence(const SymmCtx* c, int slot, int pre, void* stream) {
-  launch_k(symm_consume_fence_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, pre);
+  launch_light(symm_consume_fence_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot, pre);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -802,7 +821,7 @@ int ffb_comm_trace_read(unsigned long long* out) {
 #endif
 
 int ffb_symm_wait_never(const SymmCtx* c, int slot, void* stream) {
-  launch_k(symm_wait_never_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot);
+  launch_light(symm_wait_never_k, 1, 32, 0, reinterpret_cast<cudaStream_t>(stream), *c, slot);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -236,19 +236,23 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16(v); }
 template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half(v); }
 
-// Host side: launches `kern` with the programmatic-stream-serialization attribute (see pdl_wait above) unless the
-// environment variable FFB_PDL is 0.  Works under stream capture: the dependency becomes a programmatic graph edge.
-inline bool pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
+// Host side: launches `kern` with the programmatic-stream-serialization attribute (see pdl_wait above).  Works under
+// stream capture: the dependency becomes a programmatic graph edge.  Environment variable FFB_PDL selects which
+// kernels get the attribute: 0 = none, 1 = all (default), 2 = only the kernels with a long prologue (tensor maps, barrier set-up,
+// TMEM allocation: the GEMM and attention kernels, launched through launch_k); the short streaming kernels go
+// through launch_light.
+inline int pdl_mode() {
+  static int mode = -1;
+  if (mode < 0) {
     const char* e = getenv("FFB_PDL");
-    on = (e && e[0] == '0') ? 0 : 1;
+    mode = (e && e[0] >= '0' && e[0] <= '2') ? (e[0] - '0') : 1;
   }
-  return on != 0;
+  return mode;
 }
+inline bool pdl_enabled() { return pdl_mode() != 0; }
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+inline cudaError_t launch_attr(bool pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -258,8 +262,18 @@ inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  return launch_attr(pdl_mode() != 0, kern, grid, block, smem, st, static_cast<Args&&>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_light(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  return launch_attr(pdl_mode() == 1, kern, grid, block, smem, st, static_cast<Args&&>(args)...);
 }
 
 }  // namespace ffb

@@ -288,7 +288,7 @@ using namespace ffb;
     if (rows <= 0) return 0;                                                            \
     if (C % 8) return -2;                                                               \
     const long long n = rows * (C / 8);                                                 \
-    launch_k(kern, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), __VA_ARGS__); \
+    launch_light(kern, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), __VA_ARGS__); \
     return cudaGetLastError() == cudaSuccess ? 0 : -1;                                  \
   } while (0)
 
@@ -338,21 +338,21 @@ int ffb_colsum(const void* x, float* out, long long rows, int C, void* stream) {
     if (blocks < 1) blocks = 1;
     const long long rpb = (rows + blocks - 1) / blocks;
     const size_t smem = sizeof(float) * lanes * C;          // = 8 KB
-    launch_k(colsum_v8_k, (unsigned)((rows + rpb - 1) / rpb), 256, smem, reinterpret_cast<cudaStream_t>(stream), (const bf16*)x, out, rows, C, rpb);
+    launch_light(colsum_v8_k, (unsigned)((rows + rpb - 1) / rpb), 256, smem, reinterpret_cast<cudaStream_t>(stream), (const bf16*)x, out, rows, C, rpb);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
   }
   long long chunks = (rows + 255) / 256;
   if (chunks > 512) chunks = 512;
   const long long rpb = (rows + chunks - 1) / chunks;
   dim3 grid((C / 2 + 127) / 128, (unsigned)((rows + rpb - 1) / rpb));
-  launch_k(colsum_k, grid, 128, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)x, out, rows, C, rpb);
+  launch_light(colsum_k, grid, 128, 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)x, out, rows, C, rpb);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int ffb_adam(float* w, float* m, float* v, const void* grad, void* w16, long long n, const float* hp, float b1, float b2,
              float eps, float wd, void* stream) {
   if (n <= 0) return 0;
-  launch_k(adam_k, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), w, m, v, (const bf16*)grad, (bf16*)w16, n, hp,
+  launch_light(adam_k, (unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream), w, m, v, (const bf16*)grad, (bf16*)w16, n, hp,
                                                                                           b1, b2, eps, wd);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -100,7 +100,7 @@ int ffb_recycle_pair_embed(const void* z, const void* x, const void* sq_bins, co
   const long long want = (rows + RE_WARPS - 1) / RE_WARPS;
   const unsigned grid = (unsigned)(want < 148 * 8 ? want : 148 * 8);
   const size_t smem = (size_t)(nb * RE_C + 3 * RE_C + nb) * sizeof(float);
-  launch_k(recycle_pair_embed_kernel, grid, RE_WARPS * 32, smem, reinterpret_cast<cudaStream_t>(stream), (const bf16*)z, (const float*)x, (const float*)sq_bins, (const bf16*)w, (const bf16*)bias, (const bf16*)gamma, (const bf16*)beta,
+  launch_light(recycle_pair_embed_kernel, grid, RE_WARPS * 32, smem, reinterpret_cast<cudaStream_t>(stream), (const bf16*)z, (const float*)x, (const float*)sq_bins, (const bf16*)w, (const bf16*)bias, (const bf16*)gamma, (const bf16*)beta,
       (bf16*)out, n_i, i0, N, nb, eps, inf);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

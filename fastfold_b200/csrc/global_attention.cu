@@ -560,7 +560,7 @@ int ffb_global_attention_fwd(const void* q, const void* kv, const void* mask, co
 #define FFB_GA_LAUNCH(CC)                                                                                                          \
   do {                                                                                                                             \
     if (smem > 48 * 1024) cudaFuncSetAttribute(global_attention_kernel<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    launch_k(global_attention_kernel<CC>, dim3((unsigned)R, (unsigned)parts), GA_THREADS, smem, st, (const bf16*)q, (const bf16*)kv, (const bf16*)mask,           \
+    launch_light(global_attention_kernel<CC>, dim3((unsigned)R, (unsigned)parts), GA_THREADS, smem, st, (const bf16*)q, (const bf16*)kv, (const bf16*)mask,           \
                                                                        (const bf16*)gate, (const bf16*)gate_bias, (bf16*)out, S, H); \
   } while (0)
   if (C == 8) FFB_GA_LAUNCH(8);
@@ -582,7 +582,7 @@ int ffb_global_attention_bwd(const void* q, const void* kv, const void* mask, co
 #define FFB_GAB_LAUNCH(CC)                                                                                                              \
   do {                                                                                                                                  \
     if (smem > 48 * 1024) cudaFuncSetAttribute(global_attention_bwd_kernel<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    launch_k(global_attention_bwd_kernel<CC>, dim3((unsigned)R), GA_THREADS, smem, st, (const bf16*)q, (const bf16*)kv, (const bf16*)mask, \
+    launch_light(global_attention_bwd_kernel<CC>, dim3((unsigned)R), GA_THREADS, smem, st, (const bf16*)q, (const bf16*)kv, (const bf16*)mask, \
              (const bf16*)gate, (const bf16*)gate_bias, (const bf16*)dout, dq, (bf16*)dkv, (bf16*)dgate, S, H);                         \
   } while (0)
   if (C == 8) FFB_GAB_LAUNCH(8);

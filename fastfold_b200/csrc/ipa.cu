@@ -218,7 +218,7 @@ int ffb_ipa_fwd(const float* q, const float* k, const float* v, const float* q_p
   a.w_c = w_c; a.w_b = w_b; a.inf = inf;
   constexpr int HH = 12, CC = 16, PQ = 4, PV = 8, CZZ = 128;
   const size_t smem = IPA_J * (CZZ + IPA_ZP) * 2 + sizeof(float) * (CZZ * (HH + 1) + HH * CC + HH * PQ * 3 + HH * IPA_J + 3 * HH);
-  launch_k(ipa_fwd_kernel<HH, CC, PQ, PV, CZZ>, rows, IPA_THREADS, smem, reinterpret_cast<cudaStream_t>(stream), a);
+  launch_light(ipa_fwd_kernel<HH, CC, PQ, PV, CZZ>, rows, IPA_THREADS, smem, reinterpret_cast<cudaStream_t>(stream), a);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

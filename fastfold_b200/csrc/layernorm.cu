@@ -624,15 +624,15 @@ static int ln_fwd_dispatch(const T* x, const T* g, const T* b, T* y, float* mean
     bf16* yb = reinterpret_cast<bf16*>(y);
     const int rows_per_block = LN_WARPS * MR_U * (256 / C);
     const dim3 gmr((unsigned)((rows + rows_per_block - 1) / rows_per_block));
-    if (C == 64) launch_k(ln_fwd_mr_kernel<8>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
-    else if (C == 128) launch_k(ln_fwd_mr_kernel<16>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
-    else launch_k(ln_fwd_mr_kernel<32>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
+    if (C == 64) launch_light(ln_fwd_mr_kernel<8>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
+    else if (C == 128) launch_light(ln_fwd_mr_kernel<16>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
+    else launch_light(ln_fwd_mr_kernel<32>, gmr, LN_WARPS * 32, 0, st, xb, gb, bb, yb, mean, rstd, rows, eps);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
   }
-  if (aligned && C <= 32 * VEC) launch_k(ln_fwd_kernel<T, VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
-  else if (aligned && C <= 64 * VEC) launch_k(ln_fwd_kernel<T, 2 * VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
-  else if (aligned && C <= 128 * VEC) launch_k(ln_fwd_kernel<T, 4 * VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
-  else launch_k(ln_fwd_generic_kernel<T>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
+  if (aligned && C <= 32 * VEC) launch_light(ln_fwd_kernel<T, VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
+  else if (aligned && C <= 64 * VEC) launch_light(ln_fwd_kernel<T, 2 * VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
+  else if (aligned && C <= 128 * VEC) launch_light(ln_fwd_kernel<T, 4 * VEC>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
+  else launch_light(ln_fwd_generic_kernel<T>, grid, LN_WARPS * 32, 0, st, x, g, b, y, mean, rstd, rows, C, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -650,15 +650,15 @@ static int ln_bwd_dispatch(const T* dy, const T* x, const T* g, const float* mea
   if (IsBf16<T>::value && aligned && (C == 64 || C == 128 || C == 256)) {
     const bf16 *db_ = reinterpret_cast<const bf16*>(dy), *xb = reinterpret_cast<const bf16*>(x), *gb = reinterpret_cast<const bf16*>(g);
     bf16* dxb = reinterpret_cast<bf16*>(dx);
-    if (C == 64) launch_k(ln_bwd_mr_kernel<8>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
-    else if (C == 128) launch_k(ln_bwd_mr_kernel<16>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
-    else launch_k(ln_bwd_mr_kernel<32>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
-  } else if (aligned && C <= 32 * VEC) launch_k(ln_bwd_kernel<T, VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
-  else if (aligned && C <= 64 * VEC) launch_k(ln_bwd_kernel<T, 2 * VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
-  else if (aligned && C <= 128 * VEC) launch_k(ln_bwd_kernel<T, 4 * VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
-  else launch_k(ln_bwd_generic_kernel<T>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
-  if (dgamma_acc) launch_k(ln_bwd_reduce_acc_kernel, (2 * C + 31) / 32, 1024, 0, st, part, nblocks, C, dgamma_acc, dbeta_acc);
-  else launch_k(ln_bwd_reduce_kernel<T>, (2 * C + 31) / 32, 1024, 0, st, part, nblocks, C, dgamma, dbeta);
+    if (C == 64) launch_light(ln_bwd_mr_kernel<8>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
+    else if (C == 128) launch_light(ln_bwd_mr_kernel<16>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
+    else launch_light(ln_bwd_mr_kernel<32>, nblocks, LN_WARPS * 32, 0, st, db_, xb, gb, mean, rstd, dxb, part, rows);
+  } else if (aligned && C <= 32 * VEC) launch_light(ln_bwd_kernel<T, VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
+  else if (aligned && C <= 64 * VEC) launch_light(ln_bwd_kernel<T, 2 * VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
+  else if (aligned && C <= 128 * VEC) launch_light(ln_bwd_kernel<T, 4 * VEC>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
+  else launch_light(ln_bwd_generic_kernel<T>, nblocks, LN_WARPS * 32, 0, st, dy, x, g, mean, rstd, dx, part, rows, C);
+  if (dgamma_acc) launch_light(ln_bwd_reduce_acc_kernel, (2 * C + 31) / 32, 1024, 0, st, part, nblocks, C, dgamma_acc, dbeta_acc);
+  else launch_light(ln_bwd_reduce_kernel<T>, (2 * C + 31) / 32, 1024, 0, st, part, nblocks, C, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -718,11 +718,11 @@ int ffb_layernorm_fwd_transposed(const void* x, const void* gamma, const void* b
       attr = true;
     }
     const size_t smem64 = sizeof(float) * C * (LNT64 + 1);
-    launch_k(ln_fwd_transposed64_kernel, (unsigned)((rows + LNT64 - 1) / LNT64), 256, smem64, st, (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
+    launch_light(ln_fwd_transposed64_kernel, (unsigned)((rows + LNT64 - 1) / LNT64), 256, smem64, st, (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
   }
   const size_t smem = sizeof(float) * C * (LNT_ROWS + 1);
-  launch_k(ln_fwd_transposed_kernel, (unsigned)((rows + LNT_ROWS - 1) / LNT_ROWS), 256, smem, st, (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
+  launch_light(ln_fwd_transposed_kernel, (unsigned)((rows + LNT_ROWS - 1) / LNT_ROWS), 256, smem, st, (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, (bf16*)y, mean, rstd, rows, C, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -146,12 +146,12 @@ static int softmax_fwd_t(const T* x, const T* mask, const T* bias, T* y, Softmax
   const int cpt = (s.K + 31) / 32;
 #define FFB_SM_CASE(N)                                                                 \
   if (cpt <= N) {                                                                      \
-    launch_k(softmax_fwd_kernel<T, N>, grid, SM_WARPS * 32, 0, st, x, mask, bias, y, s);     \
+    launch_light(softmax_fwd_kernel<T, N>, grid, SM_WARPS * 32, 0, st, x, mask, bias, y, s);     \
     return cudaGetLastError() == cudaSuccess ? 0 : -1;                                 \
   }
   FFB_SM_CASE(1) FFB_SM_CASE(2) FFB_SM_CASE(4) FFB_SM_CASE(8) FFB_SM_CASE(16) FFB_SM_CASE(32)
 #undef FFB_SM_CASE
-  launch_k(softmax_fwd_loop_kernel<T>, grid, SM_WARPS * 32, 0, st, x, mask, bias, y, s);
+  launch_light(softmax_fwd_loop_kernel<T>, grid, SM_WARPS * 32, 0, st, x, mask, bias, y, s);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -161,12 +161,12 @@ static int softmax_bwd_t(const T* dy, const T* y, T* dx, long long rows, int K, 
   const int cpt = (K + 31) / 32;
 #define FFB_SM_CASE(N)                                                                 \
   if (cpt <= N) {                                                                      \
-    launch_k(softmax_bwd_kernel<T, N>, grid, SM_WARPS * 32, 0, st, dy, y, dx, rows, K);      \
+    launch_light(softmax_bwd_kernel<T, N>, grid, SM_WARPS * 32, 0, st, dy, y, dx, rows, K);      \
     return cudaGetLastError() == cudaSuccess ? 0 : -1;                                 \
   }
   FFB_SM_CASE(1) FFB_SM_CASE(2) FFB_SM_CASE(4) FFB_SM_CASE(8) FFB_SM_CASE(16) FFB_SM_CASE(32)
 #undef FFB_SM_CASE
-  launch_k(softmax_bwd_loop_kernel<T>, grid, SM_WARPS * 32, 0, st, dy, y, dx, rows, K);
+  launch_light(softmax_bwd_loop_kernel<T>, grid, SM_WARPS * 32, 0, st, dy, y, dx, rows, K);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

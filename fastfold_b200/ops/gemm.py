@@ -11,6 +11,8 @@ Stands in for the cuBLAS calls behind ``torch.matmul`` / ``nn.Linear`` /
 ``torch.einsum`` in the reference (fastfold/model/fastnn/ops.py:79-82,
 143-160, 275-324, 393-404).
 """
+import os
+
 import torch
 
 from . import _lib
@@ -265,10 +267,14 @@ class _LinearT(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             n_out, n_in = w.shape
             sink = grad_sink(w)
-            acc = sink if sink is not None else torch.zeros(n_out, n_in, device=w.device, dtype=torch.float32)
             tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
-            gemm(dy_t, x2, b_mn=True, out=acc, accumulate=True, splits=_wgrad_splits(x2.shape[0], tiles))   # contraction over tokens
-            dw = None if sink is not None else acc.to(w.dtype)
+            splits = _wgrad_splits(x2.shape[0], tiles)
+            if sink is not None:                                  # contraction over tokens, added into the trainer's buffer
+                _ParamGradStream.run(lambda: gemm(dy_t, x2, b_mn=True, out=sink, accumulate=True, splits=splits), dy_t, x2)
+            else:
+                acc = torch.zeros(n_out, n_in, device=w.device, dtype=torch.float32)
+                gemm(dy_t, x2, b_mn=True, out=acc, accumulate=True, splits=splits)
+                dw = acc.to(w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = torch.sum(dy_t, dim=1, dtype=torch.float32).to(w.dtype)      # converts inside the reduction, no fp32 copy
         return dx, dw, db
@@ -297,6 +303,45 @@ def grad_sink(param):
     return getattr(param, GRAD_SINK_ATTR, None)
 
 
+class _ParamGradStream:
+    """Parameter gradients off the critical path of backward.
+
+    The gradient of an activation is needed by the next backward node; the gradient of a weight or bias only by the
+    optimiser.  While a trainer has set ``active`` (around ``loss.backward()``), the kernels that add a parameter gradient
+    into its fp32 sink are enqueued on a side stream that waits for the main stream at the point of the call, so they run
+    beside the input-gradient chain (inside a captured step: a parallel branch of the graph).  The operands are kept
+    alive in ``keep`` until ``join()``, which makes the main stream wait for the side stream; the trainer joins after
+    every checkpointed segment and after backward.  FASTFOLD_WGRAD_STREAM=0 turns the side stream off."""
+    enabled = os.environ.get("FASTFOLD_WGRAD_STREAM", "1") != "0"
+    active = False
+    stream = None
+    keep = []
+    forked = False
+
+    @classmethod
+    def run(cls, fn, *operands):
+        if not (cls.active and cls.enabled and operands[0].is_cuda):
+            fn()
+            return
+        if cls.stream is None:
+            cls.stream = torch.cuda.Stream()
+        cls.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(cls.stream):
+            fn()
+        cls.keep.extend(operands)
+        cls.forked = True
+
+    @classmethod
+    def join(cls):
+        if cls.forked:
+            torch.cuda.current_stream().wait_stream(cls.stream)
+            cls.forked = False
+        cls.keep.clear()
+
+
+param_grad_stream = _ParamGradStream
+
+
 def sink_weight_grad(w, dy2, x2):
     """Adds dy^T @ x into the parameter's fp32 sink with the split-K GEMM; True when it did."""
     sink = grad_sink(w)
@@ -304,7 +349,8 @@ def sink_weight_grad(w, dy2, x2):
     if sink is None or not dy2.is_cuda or n_out < 64 or n_in < 64 or n_out % 8 or n_in % 8:
         return False
     tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
-    gemm(dy2, x2, a_mn=True, b_mn=True, out=sink, accumulate=True, splits=_wgrad_splits(dy2.shape[0], tiles))
+    splits = _wgrad_splits(dy2.shape[0], tiles)
+    _ParamGradStream.run(lambda: gemm(dy2, x2, a_mn=True, b_mn=True, out=sink, accumulate=True, splits=splits), dy2, x2)
     return True
 
 
@@ -314,7 +360,7 @@ def sink_bias_grad(bias, dy2):
     if sink is None or not (dy2.is_cuda and dy2.dtype == torch.bfloat16 and dy2.shape[-1] % 2 == 0):
         return False
     from . import fused_ops
-    fused_ops.colsum(dy2, out=sink.reshape(-1))
+    _ParamGradStream.run(lambda: fused_ops.colsum(dy2, out=sink.reshape(-1)), dy2)
     return True
 
 

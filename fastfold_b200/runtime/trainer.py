@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
+from ..ops.gemm import param_grad_stream
 from ..parallel import core
 
 
@@ -196,6 +197,7 @@ class FlatAdamTrainer:
                                                         self.grad_slot.offset + lo * 2, hi - lo, 1.0, _lib.stream_ptr()), "symm_allreduce_bf16")
 
     def _on_segment_backward(self, fn):
+        param_grad_stream.join()          # the segment's weight / bias gradients (side stream) are complete from here on
         if not self._overlap_active:
             return
         r = self._segment_range(fn)
@@ -276,10 +278,13 @@ class FlatAdamTrainer:
         self._covered = []
         self._pending = None
         self._overlap_active = self.overlap and self.grad_heap is not None and self.grad_reducer is None
+        param_grad_stream.active = True
         try:
             loss.backward()
         finally:
             self._overlap_active = False
+            param_grad_stream.active = False
+            param_grad_stream.join()
         self._reduce_grads()
         self._adam()
         return loss.detach()
