@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256) ln_bwd_transposed_kernel(const bf16* __re
 
 // dgamma[c] = sum_b part[b][0][c], dbeta[c] = sum_b part[b][1][c]; block = 32 columns x 32 slices of blocks
 __global__ void __launch_bounds__(1024) ltb_reduce_kernel(const float* __restrict__ part, int nblocks, int C, float* __restrict__ dgamma,
-                                                          float* __restrict__ dbeta) {
+                                                          float* __restrict__ dbeta, int accumulate) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float acc[32][33];
@@ -88,8 +88,8 @@ __global__ void __launch_bounds__(1024) ltb_reduce_kernel(const float* __restric
   const float v = warp_sum(acc[tx][ty]);
   const int co = blockIdx.x * 32 + ty;
   if (tx == 0 && co < 2 * C) {
-    if (co < C) dgamma[co] = v;
-    else dbeta[co - C] = v;
+    float* dst = co < C ? dgamma + co : dbeta + (co - C);
+    *dst = accumulate ? *dst + v : v;
   }
 }
 
@@ -157,8 +157,8 @@ long long ffb_layernorm_bwd_transposed_workspace(long long rows, int C) {
 
 // dy: bf16 [rows][C]; x: bf16 [C][rows]; mean / rstd: fp32 [rows] (saved by the forward); dx: bf16 [C][rows];
 // dgamma / dbeta: fp32 [C]; part: fp32 workspace (ffb_layernorm_bwd_transposed_workspace words).
-int ffb_layernorm_bwd_transposed(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
-                                 float* part, float* dgamma, float* dbeta, long long rows, int C, void* stream) {
+static int layernorm_bwd_transposed_impl(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                                         float* part, float* dgamma, float* dbeta, long long rows, int C, int accumulate, void* stream) {
   if (C > 256 || C < 1) return -2;
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -174,8 +174,19 @@ int ffb_layernorm_bwd_transposed(const void* dy, const void* x, const void* gamm
   if (nb > 0x7fffffffLL) return -4;
   launch_light(ln_bwd_transposed_kernel, (unsigned)nb, 256, smem, st, (const bf16*)dy, (const bf16*)x, (const bf16*)gamma, mean, rstd, (bf16*)dx, part,
                                                            rows, C);
-  launch_light(ltb_reduce_kernel, (2 * C + 31) / 32, 1024, 0, st, part, (int)nb, C, dgamma, dbeta);
+  launch_light(ltb_reduce_kernel, (2 * C + 31) / 32, 1024, 0, st, part, (int)nb, C, dgamma, dbeta, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int ffb_layernorm_bwd_transposed(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                                 float* part, float* dgamma, float* dbeta, long long rows, int C, void* stream) {
+  return layernorm_bwd_transposed_impl(dy, x, gamma, mean, rstd, dx, part, dgamma, dbeta, rows, C, 0, stream);
+}
+
+// Same, but the column sums are ADDED to dgamma / dbeta (a trainer's fp32 gradient buffer).
+int ffb_layernorm_bwd_transposed_acc(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                                     float* part, float* dgamma, float* dbeta, long long rows, int C, void* stream) {
+  return layernorm_bwd_transposed_impl(dy, x, gamma, mean, rstd, dx, part, dgamma, dbeta, rows, C, 1, stream);
 }
 
 // pre: bf16 [2 * C2][R] (rows [0, C2) values, rows [C2, 2 C2) gates); mask: bf16 [R]; out: bf16 [C2][R].  R % 8 == 0.

@@ -21,6 +21,7 @@ import torch.nn.functional as F
 from ...parallel import core
 from ...parallel.comm import gather, scatter, col_to_row
 from ...parallel.comm_async import all_to_all_async, all_to_all_async_opp
+from ...utils import memo
 from ...utils.checkpointing import checkpoint_blocks
 from .msa import MSACore
 from .ops import Linear, OutProductMean
@@ -63,7 +64,11 @@ class Evoformer(nn.Module):
         # every rank (long sequences: structure module, heads and recycling then work on the shard)
         self.keep_pair_sharded = False
 
-    def forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
+    def forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None, _memo=None):
+        with memo.use(_memo):
+            return self._forward(m, z, msa_mask, pair_mask, chunk_size, _mask_trans, _drop)
+
+    def _forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
         P = core.get_dap_size()
         seq_length = pair_mask.size(-1)
         pad = pad_amount(seq_length, P)
@@ -75,8 +80,8 @@ class Evoformer(nn.Module):
             else:
                 z = F.pad(z.unsqueeze(0), (0, 0, 0, pad, 0, pad))
                 z = scatter(z, dim=1)
-        msa_mask = F.pad(msa_mask.unsqueeze(0), (0, pad))
-        pair_mask = F.pad(pair_mask.unsqueeze(0), (0, pad, 0, pad))
+        msa_mask = memo.cached(("pad_msa", pad), (msa_mask,), lambda: F.pad(msa_mask.unsqueeze(0), (0, pad)))
+        pair_mask = memo.cached(("pad_pair", pad), (pair_mask,), lambda: F.pad(pair_mask.unsqueeze(0), (0, pad, 0, pad)))
         if _drop is None and self.training:
             _drop = draw_block_dropout(seq_length + pad, self.c_m, self.c_z, m.device, m.dtype, n_res=seq_length)
         d_msa = None if _drop is None else _drop.get("msa_row")
@@ -115,9 +120,10 @@ def run_blocks(blocks, m, z, msa_mask, pair_mask, chunk_size, _mask_trans, train
     P = core.get_dap_size()
     n_pad = pair_mask.size(-1) + pad_amount(pair_mask.size(-1), P)
     fns = []
+    mm = memo.Memo()        # mask-derived tensors are computed once for all blocks and both passes (utils/memo.py)
     for b in blocks:
         drop = draw_block_dropout(n_pad, c_m, c_z, m.device, m.dtype, n_res=pair_mask.size(-1)) if training else None
-        fns.append(partial(b, msa_mask=msa_mask, pair_mask=pair_mask, chunk_size=chunk_size, _mask_trans=_mask_trans, _drop=drop))
+        fns.append(partial(b, msa_mask=msa_mask, pair_mask=pair_mask, chunk_size=chunk_size, _mask_trans=_mask_trans, _drop=drop, _memo=mm))
     return checkpoint_blocks(fns, args=(m, z), blocks_per_ckpt=blocks_per_ckpt)
 
 

@@ -5,9 +5,10 @@ import torch.nn.functional as F
 
 from ... import ops as K
 from ...parallel import core
-from ...parallel.comm import gather, scatter, row_to_col, col_to_row
+from ...parallel.comm import gather, scatter, scatter_mask, row_to_col, col_to_row
 from ...parallel.comm_async import all_to_all_async, all_to_all_async_opp
 from ...parallel.fused import a2a_layer_norm
+from ...utils import memo
 from ...utils.checkpointing import checkpoint_blocks
 from .ops import (ChunkMSARowAttentionWithPairBias, ChunkMSAColumnGlobalAttention, ChunkTransition, GlobalAttention,
                   OutProductMean, SelfAttention, Transition, _fusable)
@@ -49,10 +50,10 @@ class MSAColumnAttention(nn.Module):
             strided = M_norm_t is None and self.strided_for(M_raw.shape[1], M_raw)
         if strided:
             M = self.layernormM(M_raw) if M_norm_t is None else M_norm_t
-            out, _ = self.attention(M, M_mask.transpose(-1, -2).contiguous(), transposed=True)
+            out, _ = self.attention(M, memo.cached("mask_t", (M_mask,), lambda: M_mask.transpose(-1, -2).contiguous()), transposed=True)
             return M_raw.add_(out) if fops.INPLACE else M_raw + out
         M = self.layernormM(M_raw.transpose(-2, -3).contiguous()) if M_norm_t is None else M_norm_t
-        out, _ = self.attention(M, M_mask.transpose(-1, -2).contiguous())
+        out, _ = self.attention(M, memo.cached("mask_t", (M_mask,), lambda: M_mask.transpose(-1, -2).contiguous()))
         return M_raw.add_(out.transpose(-2, -3)) if fops.INPLACE else M_raw + out.transpose(-2, -3)
 
 
@@ -68,12 +69,12 @@ class MSACore(nn.Module):
         self.MSATransition = Transition(d=d_node)
 
     def forward(self, node, pair, node_mask, dropmask=None):
-        node_mask_row = scatter(node_mask, dim=1)
+        node_mask_row = scatter_mask(node_mask, dim=1)
         node = self.MSARowAttentionWithPairBias(node, pair, node_mask_row, dropmask)
         # row -> column switch fused with the transpose + LayerNorm of the column attention
         strided = self.MSAColumnAttention.strided_for(node.shape[1] * core.get_dap_size(), node)     # full sequence count after the switch
         node, node_nt = a2a_layer_norm(node, self.MSAColumnAttention.layernormM, 0, transpose_norm=not strided)
-        node_mask_col = scatter(node_mask, dim=2)
+        node_mask_col = scatter_mask(node_mask, dim=2)
         node = self.MSAColumnAttention(node, node_mask_col, M_norm_t=node_nt, strided=strided)
         node = self.MSATransition(node)
         return node
@@ -87,10 +88,10 @@ class ExtraMSACore(nn.Module):
         self.MSATransition = ChunkTransition(d=d_node)
 
     def forward(self, node, pair, node_mask, dropmask=None):
-        node_mask_row = scatter(node_mask, dim=1)
+        node_mask_row = scatter_mask(node_mask, dim=1)
         node = self.MSARowAttentionWithPairBias(node, pair, node_mask_row, dropmask)
         node = row_to_col(node)
-        node_mask_col = scatter(node_mask, dim=2)
+        node_mask_col = scatter_mask(node_mask, dim=2)
         node = self.MSAColumnAttention(node, node_mask_col)
         node = self.MSATransition(node)
         return node
@@ -113,7 +114,11 @@ class ExtraMSABlock(nn.Module):
         self.is_multimer = is_multimer
         self.keep_pair_sharded = False                  # see ``Evoformer.keep_pair_sharded``
 
-    def forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
+    def forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None, _memo=None):
+        with memo.use(_memo):
+            return self._forward(m, z, msa_mask, pair_mask, chunk_size, _mask_trans, _drop)
+
+    def _forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _mask_trans=True, _drop=None):
         P = core.get_dap_size()
         cnt_pad = pad_amount(msa_mask.size(-2), P)
         len_pad = pad_amount(pair_mask.size(-1), P)
@@ -125,8 +130,8 @@ class ExtraMSABlock(nn.Module):
             else:
                 z = F.pad(z.unsqueeze(0), (0, 0, 0, len_pad, 0, len_pad))
                 z = scatter(z, dim=1)
-        msa_mask = F.pad(msa_mask.unsqueeze(0), (0, len_pad, 0, cnt_pad))
-        pair_mask = F.pad(pair_mask.unsqueeze(0), (0, len_pad, 0, len_pad))
+        msa_mask = memo.cached(("pad_msa", len_pad, cnt_pad), (msa_mask,), lambda: F.pad(msa_mask.unsqueeze(0), (0, len_pad, 0, cnt_pad)))
+        pair_mask = memo.cached(("pad_pair", len_pad), (pair_mask,), lambda: F.pad(pair_mask.unsqueeze(0), (0, len_pad, 0, len_pad)))
         d_msa = None if _drop is None else _drop.get("msa_row")
         if not self.is_multimer:
             m = self.msa_stack(m, z, msa_mask, d_msa)

@@ -27,7 +27,8 @@ from ... import ops as K
 from ...ops import flash
 from ...ops.attention import attention_core
 from ...parallel import comm, core
-from ...parallel.comm import gather, scatter
+from ...parallel.comm import gather, scatter, scatter_mask
+from ...utils import memo
 from ...parallel.comm_async import (gather_async, gather_async_opp, broadcast_async, broadcast_async_opp)
 from .initializer import glorot_uniform_af
 
@@ -208,7 +209,7 @@ class OutProductMean(nn.Module):
         o = o.reshape(ni, d, N, e).permute(0, 2, 1, 3).reshape(1, ni, N, d * e)
         return Z_raw + self.o_linear(o) * inv_norm.to(o.dtype)
 
-    def _fused_gather(self, M, M_mask, M_mask_col, Z_raw):
+    def _fused_gather(self, M, M_mask, M_mask_col, Z_raw, src):
         """No-grad pass under DAP on the GPU: the masked right projection is written straight into a symmetric-heap
         slot and the outer-product GEMM reads every rank's slab of it tile by tile with TMA over NVLink (B operand,
         MN-major, gathered along N) - the all-gather and its gathered copy disappear.  Returns None when the shapes do
@@ -226,11 +227,12 @@ class OutProductMean(nn.Module):
         slot = heap.next_ring_slot(S * ni * e * 2)
         heap.slot_fence(slot, pre=True)
         r_local = heap.view(slot, (1, S, ni, e), M.dtype)
-        torch.mul(self.linear_b(M), M_mask_col.to(M.dtype), out=r_local)
+        mask_col_a = memo.cached(("opm_mask_col_as", M.dtype), (src,), lambda: M_mask_col.to(M.dtype))
+        torch.mul(self.linear_b(M), mask_col_a, out=r_local)
         heap.slot_fence(slot, pre=False)
-        left_act = self.linear_a(M) * M_mask_col.to(M.dtype)
-        norm = torch.einsum("bsid,bsjd->bijd", M_mask_col.float(), M_mask.float()) + 1e-3
-        inv_norm = (1.0 / norm).reshape(-1)
+        left_act = self.linear_a(M) * mask_col_a
+        inv_norm = memo.cached("opm_inv_norm", (src,), lambda: 1.0 / (torch.einsum("bsid,bsjd->bijd", M_mask_col.float(), M_mask.float()) + 1e-3))
+        inv_norm = inv_norm.reshape(-1)
         N = ni * P
         l2 = left_act.reshape(S, ni * e)
         heap.consume_fence(slot, pre=True)
@@ -243,19 +245,20 @@ class OutProductMean(nn.Module):
 
     def forward(self, M, M_mask, Z_raw):
         M = self.layernormM(M)
-        M_mask = M_mask.unsqueeze(-1)
-        M_mask_col = scatter(M_mask, dim=2)
+        src = M_mask                                     # the tensors below depend on the mask only: once per stack call
+        M_mask = memo.cached("opm_mask", (src,), lambda: src.unsqueeze(-1))
+        M_mask_col = memo.cached("opm_mask_col", (src,), lambda: scatter_mask(M_mask, dim=2))
         if _OPM_FUSED_GATHER:
-            out = self._fused_gather(M, M_mask, M_mask_col, Z_raw)
+            out = self._fused_gather(M, M_mask, M_mask_col, Z_raw, src)
             if out is not None:
                 return out
+        mask_col_a = memo.cached(("opm_mask_col_as", M.dtype), (src,), lambda: M_mask_col.to(M.dtype))
         right_act = self.linear_b(M)
         # mask before the gather: identical result, and the gathered operand is ready to use
-        right_act = right_act * M_mask_col.to(right_act.dtype)
+        right_act = right_act * mask_col_a
         right_act_all, work = gather_async(right_act, dim=2)
-        left_act = self.linear_a(M) * M_mask_col.to(M.dtype)
-        norm = torch.einsum("bsid,bsjd->bijd", M_mask_col.float(), M_mask.float()) + 1e-3
-        inv_norm = 1.0 / norm
+        left_act = self.linear_a(M) * mask_col_a
+        inv_norm = memo.cached("opm_inv_norm", (src,), lambda: 1.0 / (torch.einsum("bsid,bsjd->bijd", M_mask_col.float(), M_mask.float()) + 1e-3))
         right_act_all = gather_async_opp(right_act_all, work, dim=2)
         if CHUNK_SIZE is None:
             return self._outer(left_act, right_act_all, inv_norm, Z_raw)
@@ -741,9 +744,10 @@ class _TriangleMultiplication(nn.Module):
         c = self.c
         A, B = Z_raw.shape[1], Z_raw.shape[2]
         z2 = Z.reshape(A * B, -1)
-        w = torch.cat([self.left_right_projection.weight, self.left_right_gate.weight], dim=0)          # [4c, d]: values, then gates
-        b = torch.cat([self.left_right_projection.bias, self.left_right_gate.bias], dim=0)
-        left_t, right_t = K.glu_mask_t(K.linear_t(z2, w, b), Z_mask.reshape(-1), split=c)              # 2 x [c, A*B]
+        # [4c, tokens]: values, then gates; each projection's gradient goes straight to its own buffer
+        pre_t = K.linear_t_multi(z2, (self.left_right_projection.weight, self.left_right_gate.weight),
+                                 (self.left_right_projection.bias, self.left_right_gate.bias))
+        left_t, right_t = K.glu_mask_t(pre_t, Z_mask.reshape(-1), split=c)                               # 2 x [c, A*B]
         left_t = left_t.reshape(c, A, B)
         right_t = right_t.reshape(c, A, B)
         g = self.output_gate(Z, act="sigmoid")
@@ -826,7 +830,7 @@ class _TriangleAttention(nn.Module):
             if dropmask is None and training and self.p_drop > 0:
                 dropmask = F.dropout(torch.ones_like(Z_raw[:, 0:1, :, :]), p=self.p_drop, training=True)
         else:
-            mask = Z_mask.transpose(-1, -2).contiguous()
+            mask = memo.cached("mask_t", (Z_mask,), lambda: Z_mask.transpose(-1, -2).contiguous())
             if dropmask is None and training and self.p_drop > 0:
                 dropmask = F.dropout(torch.ones_like(Z_raw[:, :, 0:1, :]), p=self.p_drop, training=True)
         if not training:

@@ -1,7 +1,7 @@
 """Pair half of the Evoformer block (names as in fastfold/model/fastnn/triangle.py)."""
 import torch.nn as nn
 
-from ...parallel.comm import scatter, row_to_col, col_to_row
+from ...parallel.comm import scatter, scatter_mask, row_to_col, col_to_row
 from ...parallel.fused import a2a_layer_norm
 from .ops import (AsyncChunkTriangleMultiplicationOutgoing, AsyncChunkTriangleMultiplicationIncoming,
                   ChunkTriangleAttentionStartingNode, ChunkTriangleAttentionEndingNode, ChunkTransition)
@@ -48,8 +48,8 @@ class PairCore(nn.Module):
 
     def forward(self, pair, pair_mask, _drop=None):
         d = _drop or {}
-        pair_mask_row = scatter(pair_mask, dim=1)
-        pair_mask_col = scatter(pair_mask, dim=2)
+        pair_mask_row = scatter_mask(pair_mask, dim=1)
+        pair_mask_col = scatter_mask(pair_mask, dim=2)
         # each axis switch is fused with the LayerNorm (and transpose) of the module that consumes its result
         pair = self.TriangleMultiplicationOutgoing(pair, pair_mask_row, d.get("tri_mul_out"))
         pair, pn = a2a_layer_norm(pair, self.TriangleMultiplicationIncoming.layernorm1, 0)

@@ -59,6 +59,7 @@ def _declare(lib):
         "ffb_layernorm_bwd_acc": [P, P, P, P, P, P, P, I, P, P, L, I, P],
         "ffb_layernorm_fwd_transposed": [P, P, P, P, P, P, L, I, F, P],
         "ffb_layernorm_bwd_transposed": [P, P, P, P, P, P, P, P, P, L, I, P],
+        "ffb_layernorm_bwd_transposed_acc": [P, P, P, P, P, P, P, P, P, L, I, P],
         "ffb_glu_mask_t_fwd": [P, P, P, I, L, P],
         "ffb_glu_mask_t_bwd": [P, P, P, P, I, L, P],
         "ffb_global_attention_fwd": [P, P, P, P, P, P, L, I, I, I, P],

@@ -280,6 +280,65 @@ class _LinearT(torch.autograd.Function):
         return dx, dw, db
 
 
+class _LinearTMulti(torch.autograd.Function):
+    """``linear_t`` with the weight given as several parameters stacked along the output dimension (the four GLU
+    projections of the triangle multiplication).  Forward concatenates them; backward computes one input-gradient GEMM
+    and writes each parameter's gradient straight into its fp32 sink (on the parameter-gradient stream) instead of
+    producing the concatenated gradient and letting autograd split and accumulate it."""
+
+    @staticmethod
+    def forward(ctx, x2, n, *wb):
+        ws, bs = wb[:n], wb[n:]
+        w = torch.cat([t.detach() for t in ws], dim=0)
+        b = torch.cat([t.detach() for t in bs], dim=0)
+        ctx.save_for_backward(x2, w)
+        ctx.ws, ctx.bs = ws, bs
+        return gemm(x2, w, bias=b, trans_out=True)
+
+    @staticmethod
+    def backward(ctx, dy_t):
+        x2, w = ctx.saved_tensors
+        dy_t = dy_t.contiguous()                                  # [sum c_out, tokens]
+        dx = gemm(dy_t, w, a_mn=True, b_mn=True) if ctx.needs_input_grad[0] else None
+        n_in = w.shape[1]
+        grads_w, grads_b = [], []
+        rowsum = torch.sum(dy_t, dim=1, dtype=torch.float32)
+        off = 0
+        for wi, bi in zip(ctx.ws, ctx.bs):
+            n_out = wi.shape[0]
+            sl = dy_t[off:off + n_out]
+            tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
+            splits = _wgrad_splits(x2.shape[0], tiles)
+            sink = grad_sink(wi)
+            if sink is not None:
+                _ParamGradStream.run(lambda sl=sl, sink=sink, splits=splits: gemm(sl, x2, b_mn=True, out=sink, accumulate=True, splits=splits), sl, x2)
+                grads_w.append(None)
+            else:
+                acc = torch.zeros(n_out, n_in, device=w.device, dtype=torch.float32)
+                gemm(sl, x2, b_mn=True, out=acc, accumulate=True, splits=splits)
+                grads_w.append(acc.to(wi.dtype))
+            sb = grad_sink(bi)
+            rs = rowsum[off:off + n_out]
+            if sb is not None:
+                _ParamGradStream.run(lambda sb=sb, rs=rs: sb.reshape(-1).add_(rs), rs)
+                grads_b.append(None)
+            else:
+                grads_b.append(rs.to(bi.dtype))
+            off += n_out
+        return (dx, None) + tuple(grads_w) + tuple(grads_b)
+
+
+def linear_t_multi(x2, weights, biases):
+    """``linear_t(x2, cat(weights), cat(biases))`` whose backward feeds each parameter's gradient sink directly."""
+    n_out = sum(w.shape[0] for w in weights)
+    ok = (x2.is_cuda and x2.dtype == torch.bfloat16 and x2.dim() == 2 and x2.shape[1] % 8 == 0 and x2.shape[0] % 8 == 0 and n_out >= 64
+          and weights[0].shape[1] >= 64 and x2.shape[0] >= 64 and all(w.dtype == torch.bfloat16 and w.shape[0] % 8 == 0 for w in weights)
+          and torch.is_grad_enabled())
+    if not ok:
+        return linear_t(x2, torch.cat(list(weights), dim=0), torch.cat(list(biases), dim=0))
+    return _LinearTMulti.apply(x2, len(weights), *weights, *biases)
+
+
 NARROW_LINEAR_T = True      # channel-major projections with fewer than 64 outputs (pair-bias heads) on the tcgen05 kernel
 
 
@@ -346,8 +405,13 @@ def sink_weight_grad(w, dy2, x2):
     """Adds dy^T @ x into the parameter's fp32 sink with the split-K GEMM; True when it did."""
     sink = grad_sink(w)
     n_out, n_in = dy2.shape[1], x2.shape[1]
-    if sink is None or not dy2.is_cuda or n_out < 64 or n_in < 64 or n_out % 8 or n_in % 8:
+    if sink is None or not dy2.is_cuda:
         return False
+    if n_out < 64 or n_in < 64 or n_out % 8 or n_in % 8:
+        # narrow projections (32-wide outer-product factors): the MN-major tile is 64 wide, so the product is a library
+        # call; it still leaves the critical path and lands in the fp32 buffer without an autograd accumulation
+        _ParamGradStream.run(lambda: sink.add_(torch.matmul(dy2.t(), x2)), dy2, x2)
+        return True
     tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
     splits = _wgrad_splits(dy2.shape[0], tiles)
     _ParamGradStream.run(lambda: gemm(dy2, x2, a_mn=True, b_mn=True, out=sink, accumulate=True, splits=splits), dy2, x2)

@@ -99,6 +99,7 @@ class _LayerNormTFn(torch.autograd.Function):
     def forward(ctx, x_cm, weight, bias, eps):
         y, x_c, mean, rstd = _ln_t_forward(x_cm, weight, bias, eps, True)
         ctx.save_for_backward(x_c, weight, mean, rstd)
+        ctx.params = (weight, bias)
         return y
 
     @staticmethod
@@ -109,6 +110,14 @@ class _LayerNormTFn(torch.autograd.Function):
         dy = dy.contiguous()
         dx = torch.empty_like(x_cm)
         part = torch.empty(((rows + 31) // 32) * 2 * C, device=dy.device, dtype=torch.float32)
+        from .gemm import grad_sink
+        sg, sb = grad_sink(ctx.params[0]), grad_sink(ctx.params[1])
+        if sg is not None and sb is not None and weight.is_contiguous() and _lib.has("ffb_layernorm_bwd_transposed_acc"):
+            # gamma / beta gradients go straight into the trainer's fp32 buffer
+            _lib.check(lib.ffb_layernorm_bwd_transposed_acc(_lib.ptr(dy), _lib.ptr(x_cm), _lib.ptr(weight), _lib.ptr(mean), _lib.ptr(rstd),
+                                                            _lib.ptr(dx), _lib.ptr(part), _lib.ptr(sg), _lib.ptr(sb), rows, C, _lib.stream_ptr()),
+                       "layernorm_bwd_transposed_acc")
+            return dx, None, None, None
         dg = torch.empty(C, device=dy.device, dtype=torch.float32)
         db = torch.empty(C, device=dy.device, dtype=torch.float32)
         _lib.check(lib.ffb_layernorm_bwd_transposed(_lib.ptr(dy), _lib.ptr(x_cm), _lib.ptr(weight.contiguous()), _lib.ptr(mean), _lib.ptr(rstd),

@@ -223,6 +223,15 @@ def scatter(x, dim=-1):
     return _split(x, dim)
 
 
+def scatter_mask(x, dim=-1):
+    """``scatter`` for a mask (no gradient, read-only): every block of a stack scatters the same tensor, so the shard
+    is computed once per stack call (utils/memo.py)."""
+    if _P() == 1:
+        return x
+    from ..utils import memo
+    return memo.cached(("split", dim % x.dim()), (x,), lambda: _split(x, dim))
+
+
 def reduce(x):
     if _P() == 1:
         return x
