@@ -45,14 +45,20 @@ __device__ int g_status[8];
 
 // Optional phase timeline of CTA 0 (compiled in only for profiling builds: -DFFB_GEMM_TRACE).
 #ifdef FFB_GEMM_TRACE
-__device__ unsigned long long g_gemm_trace[256 + 4 * 160];     // [15 tiles][16 slots] of CTA 0, then [CTA][4] phase stamps
+__device__ unsigned long long g_gemm_trace[256 + 8 * 160];     // [15 tiles][16 slots] of CTA 0, then [CTA][8] phase stamps
+// the "memory" clobber keeps the timer read on its side of barriers and waits
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+  return t;
+}
 #define GEMM_TRACE(tile_local, slot)                                                        \
   do {                                                                                      \
-    if (blockIdx.x == 0 && (tile_local) < 15) g_gemm_trace[(tile_local) * 16 + (slot)] = globaltimer_ns(); \
+    if (blockIdx.x == 0 && (tile_local) < 15) g_gemm_trace[(tile_local) * 16 + (slot)] = trace_now(); \
   } while (0)
 #define GEMM_TRACE_CTA(slot)                                                                \
   do {                                                                                      \
-    if (threadIdx.x == 0 && blockIdx.x < 160) g_gemm_trace[256 + blockIdx.x * 4 + (slot)] = globaltimer_ns(); \
+    if (threadIdx.x == 0 && blockIdx.x < 160) g_gemm_trace[256 + blockIdx.x * 8 + (slot)] = trace_now(); \
   } while (0)
 #else
 #define GEMM_TRACE(tile_local, slot) do {} while (0)
@@ -234,18 +240,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
-  // everything above touches only this CTA's shared and tensor memory; from here on global memory is read
-  pdl_wait();
-  if (tma_epi && g.bias && g.N <= FAST_BIAS_MAX_N) {
-    // fast epilogue: the whole bias vector as fp32 in shared memory, read back as broadcast 16-byte loads
-    const bf16* bp = reinterpret_cast<const bf16*>(g.bias);
-    for (int i = threadIdx.x; i < FAST_BIAS_MAX_N + 64; i += GEMM_THREADS) s_bias[i] = (i < g.N) ? __bfloat162float(bp[i]) : 0.f;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  GEMM_TRACE_CTA(1);   // start of the main phase
+  GEMM_TRACE_CTA(1);   // barriers initialised, tensor memory allocated
+  // everything above touches only this CTA's shared and tensor memory; from here on global memory is read
+  pdl_wait();
+  if (warp >= 2 && tma_epi && g.bias && g.N <= FAST_BIAS_MAX_N) {
+    // fast epilogue: the whole bias vector as fp32 in shared memory, read back as broadcast 16-byte loads.  Only the
+    // epilogue warps fill and wait for it (named barrier 1), so the producer's first loads do not queue behind it.
+    const bf16* bp = reinterpret_cast<const bf16*>(g.bias);
+    for (int i = threadIdx.x - 64; i < FAST_BIAS_MAX_N + 64; i += EPI_WARPS * 32) s_bias[i] = (i < g.N) ? __bfloat162float(bp[i]) : 0.f;
+    asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+  }
+  GEMM_TRACE_CTA(2);   // start of the main phase
 
   if (warp == 0) {
     if (lane == 0) {
@@ -777,21 +786,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
   }
   tc_fence_before();
   __syncthreads();
-  GEMM_TRACE_CTA(2);   // end of the main phase
+  GEMM_TRACE_CTA(3);   // end of the main phase
+#ifdef FFB_GEMM_TRACE_EXTRA
+  // The same moment stamped by an epilogue thread: the assembler may schedule thread 0's timer read above the barrier
+  // (thread 0 is the producer lane and reaches the barrier microseconds before the epilogue warps), so slot 3 can read
+  // early; slot 6 cannot, because the epilogue warps arrive last.
+  if (threadIdx.x == 64 && blockIdx.x < 160) g_gemm_trace[256 + blockIdx.x * 8 + 6] = trace_now();
+#endif
+#ifdef FFB_GEMM_TRACE_EXTRA
+  // where does the time between the end of the main phase and the exit go: the bulk stores still in flight
+  // (slot 4: when they have completed) or the TMEM release (slot 5)?
+  if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  __syncthreads();
+  GEMM_TRACE_CTA(4);
+#endif
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
-  GEMM_TRACE_CTA(3);
-#ifdef FFB_GEMM_TRACE_EXTRA
-  if (threadIdx.x == 0 && blockIdx.x < 160) {
-    // how long do the bulk stores still in flight take to complete (they hold the CTA's shared memory until then)?
-    g_gemm_trace[256 + blockIdx.x * 4 + 0] = g_gemm_trace[256 + blockIdx.x * 4 + 3];
-  }
-  if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-  __syncthreads();
-  GEMM_TRACE_CTA(3);
-#endif
+  GEMM_TRACE_CTA(5);
 }
 
 // ---------------------------------------------------------------------------
@@ -972,7 +985,7 @@ int ffb_gemm_bf16_peer(const void* A, const void* B, int a_mn, int b_mn, long lo
 
 #ifdef FFB_GEMM_TRACE
 int ffb_gemm_trace_read(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * (256 + 4 * 160)) == cudaSuccess ? 0 : -1;
+  return cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * (256 + 8 * 160)) == cudaSuccess ? 0 : -1;
 }
 #endif
 
