@@ -367,6 +367,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
       const TileCoord tc = tile_coord(tile, tiles_n, tiles_m, g.splits);
       const int n0 = tc.n0 * BN;
       const uint32_t as = lt & 1;
+      // TMA epilogue with mul / residual tiles: the loads of this warp's first chunk go out BEFORE the wait for the
+      // accumulator, so their latency hides behind the MMAs of the tile instead of sitting inside the epilogue
+      bool pre_issued = false;
+      if (tma_epi == 1 && (g.mul != nullptr || g.resid != nullptr)) {
+        const int prow0 = tc.m0 + quad * 32, pcol0 = n0 + half * 64;
+        if (half < BN / 64 && pcol0 < g.N && prow0 < g.M) {
+          if (lane == 0) {
+            if (g.mul) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            mbar_expect_tx(my_ldbar, (g.mul ? 4096u : 0u) + (g.resid ? 4096u : 0u));
+            if (g.resid) tma_load_3d(epi_smem + out_buf * 4096, &tmRes, my_ldbar, pcol0, prow0, tc.batch);
+            if (g.mul) tma_load_3d(epi_smem + (out_buf ^ 1) * 4096, &tmMul, my_ldbar, pcol0, prow0, tc.batch);
+          }
+          pre_issued = true;
+        }
+      }
       bool ok = mbar_wait(bar_accf + 8 * as, (lt >> 1) & 1);
       if (!ok && lane == 0 && *abort_flag == 0) report(ST_TIMEOUT_EPI, 0);
       ok = __all_sync(0xffffffffu, ok);
@@ -451,9 +467,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
           out_buf ^= 1;
         }
       } else if (tma_epi == 3) {
-        // Fast transposed path (bf16 C^T, at most bias + activation): the 32 x 64 warp tile is transposed on its way into
-        // shared memory ([64 columns][32 rows], 64-byte lines written by whole warps) and leaves as one TMA store.
+        // Fast transposed path (bf16 C^T; bias, activation, GLU pairing, row scale): the 32 x 64 warp tile is transposed on
+        // its way into shared memory ([64 columns][32 rows], 64-byte lines written by whole warps) and leaves as one TMA
+        // store.  With GLU the 64 accumulator columns are 32 (value, gate) pairs and the tile that leaves is [32][32].
         const int row0 = tc.m0 + quad * 32;
+        const float rs3 = (g.rowscale && row0 + lane < g.M) ? g.rowscale[(long long)tc.batch * g.rs_bstride + row0 + lane] : 1.f;
 #pragma unroll 1
         for (int c = half; c < BN / 64; c += 2) {
           const int col0 = n0 + c * 64;
@@ -483,13 +501,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
             for (int j = 0; j < 64; ++j) v[j] = sigmoidf_(v[j]);
           }
           bf16* obuf = reinterpret_cast<bf16*>(reinterpret_cast<uint8_t*>(stg) + out_buf * 4096) + lane;
+          if (g.glu) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) obuf[j * 32] = __float2bfloat16(v[j]);
+            for (int j = 0; j < 32; ++j) obuf[j * 32] = __float2bfloat16(v[2 * j] * sigmoidf_(v[2 * j + 1]) * rs3);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) obuf[j * 32] = __float2bfloat16(v[j] * rs3);
+          }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
             asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&tmC),
-                         "r"(epi_smem + out_buf * 4096), "r"(row0), "r"(col0), "r"(tc.batch)
+                         "r"(epi_smem + out_buf * 4096), "r"(row0), "r"(g.glu ? (col0 >> 1) : col0), "r"(tc.batch)
                          : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
@@ -509,7 +532,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(const __grid
           if (col0 >= g.N || row0 >= g.M) break;           // warp-uniform
           // tile[out_buf] receives the residual (if any) and then the result; tile[out_buf ^ 1] receives mul (if any).
           // A tile may be refilled only after the bulk store that last read it has finished reading.
-          if (lane == 0) {
+          if (lane == 0 && !(pre_issued && c == half)) {
             if (g.mul) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             if (has_ld) {
@@ -940,10 +963,12 @@ static int gemm_launch(const void* A, const void* B, int a_mn, int b_mn, long lo
     if (tma_epi && g.resid && make_tmap_bf16(&epi[2], g.resid, g.M, g.N, g.ldres, batch, g.res_bstride, 64, 32)) tma_epi = 0;
   }
   if (tma_epi && !g.mul && !g.resid && !g.rowscale && !g.dmask && g.alpha == 1.0f) tma_epi = 2;   // fast epilogue
-  if (!tma_epi && g.trans_out && g.out_mode == OUT_BF16 && !g.glu && !g.mul && !g.resid && !g.rowscale && !g.dmask && g.alpha == 1.0f &&
+  if (!tma_epi && g.trans_out && g.out_mode == OUT_BF16 && !g.mul && !g.resid && !g.dmask && g.alpha == 1.0f &&
       (!g.bias || g.N <= FAST_BIAS_MAX_N) && al16(g.C, g.ldc, g.c_bstride) && (batch == 1 || g.c_bstride != 0) && g.M >= 32) {
-    // fast transposed epilogue: C^T is a [N][M] matrix with row stride ldc; tiles of 64 rows x 32 contiguous elements
-    if (encode_tmap3_bf16(&epi[0], g.C, g.M, g.N, batch, g.ldc, g.c_bstride, 32, 64, 0) == 0) tma_epi = 3;
+    // fast transposed epilogue: C^T is a [N][M] matrix ([N / 2][M] with GLU) with row stride ldc; tiles of 64 (32) rows x
+    // 32 contiguous elements
+    const int n_out = g.glu ? (g.N >> 1) : g.N;
+    if (encode_tmap3_bf16(&epi[0], g.C, g.M, n_out, batch, g.ldc, g.c_bstride, 32, g.glu ? 32 : 64, 0) == 0) tma_epi = 3;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (peer_which == 1) {

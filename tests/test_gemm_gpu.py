@@ -89,6 +89,30 @@ def test_epilogues(device_status):
     _close(gemm(a, b, out_dtype=torch.float32), gemm_ref(a, b, out_dtype=torch.float32), K)
 
 
+def test_epilogues_many_tiles(device_status):
+    """Several tiles per CTA and the 256-wide tile (two column chunks per epilogue warp): the mul / residual tiles of a
+    warp's first chunk are requested before the accumulator is complete, those of its second chunk after the first."""
+    torch.manual_seed(11)
+    M, N, K = 19200, 512, 128
+    a, b = _rand(M, K), _rand(N, K, scale=0.2)
+    bias, mul, resid = _rand(N), _rand(M, N), _rand(M, N)
+    rowscale = torch.rand(M, device=DEV)
+    _close(gemm(a, b, bias=bias, act="sigmoid", mul=mul), gemm_ref(a, b, bias=bias, act="sigmoid", mul=mul, out_dtype=torch.float32), K)
+    _close(gemm(a, b, bias=bias, resid=resid), gemm_ref(a, b, bias=bias, resid=resid, out_dtype=torch.float32), K)
+    _close(gemm(a, b, bias=bias, mul=mul, rowscale=rowscale, resid=resid),
+           gemm_ref(a, b, bias=bias, mul=mul, rowscale=rowscale, resid=resid, out_dtype=torch.float32), K)
+    for bn in (128, 256):
+        out = gemm(a, b, bias=bias, glu=True, rowscale=rowscale, trans_out=True, bn=bn)
+        assert out.shape == (N // 2, M)
+        _close(out, gemm_ref(a, b, bias=bias, glu=True, rowscale=rowscale, trans_out=True, out_dtype=torch.float32), K)
+        _close(gemm(a, b, bias=bias, rowscale=rowscale, trans_out=True, bn=bn),
+               gemm_ref(a, b, bias=bias, rowscale=rowscale, trans_out=True, out_dtype=torch.float32), K)
+    # in place: the residual tile is read and the result written through the same storage
+    r2 = resid.clone()
+    ref = gemm_ref(a, b, bias=bias, resid=resid, out_dtype=torch.float32)
+    _close(gemm(a, b, bias=bias, resid=r2, out=r2), ref, K)
+
+
 def test_linear_autograd(device_status):
     x = _rand(4, 96, 256).requires_grad_(True)
     w = _rand(512, 256, scale=0.05).requires_grad_(True)
