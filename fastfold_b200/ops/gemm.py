@@ -209,7 +209,9 @@ def gemm(a, b, *, a_mn=False, b_mn=False, alpha=1.0, bias=None, act=None, glu=Fa
 def _wgrad_splits(tokens, n_out_tiles):
     """Split-K factor so that a weight-gradient GEMM (few output tiles, long contraction) fills the 148 SMs."""
     kb = (tokens + 63) // 64
-    want = max(1, (2 * 148) // max(1, n_out_tiles))
+    # one work item per SM (half of that for a single output tile): measured faster than two per SM at every shape of
+    # the model - the fp32 reductions of the splits into the same tile contend in L2
+    want = max(1, (74 if n_out_tiles == 1 else 148) // max(1, n_out_tiles))
     return max(1, min(kb, want))
 
 
