@@ -55,7 +55,60 @@ _ALIASES = {
     "fastfold.data.data_pipeline": "fastfold_b200.data.data_pipeline",
     "fastfold.data.data_transforms": "fastfold_b200.data.data_transforms",
     "fastfold.data.parsers": "fastfold_b200.data.parsers",
+    "fastfold.data.data_modules": "fastfold_b200.data.data_modules",
+    "fastfold.data.data_transforms_multimer": "fastfold_b200.data.data_transforms_multimer",
+    "fastfold.data.feature_pipeline": "fastfold_b200.data.feature_pipeline",
+    "fastfold.data.input_pipeline": "fastfold_b200.data.input_pipeline",
+    "fastfold.data.input_pipeline_multimer": "fastfold_b200.data.input_pipeline_multimer",
+    "fastfold.data.feature_processing_multimer": "fastfold_b200.data.feature_processing_multimer",
+    "fastfold.data.msa_pairing": "fastfold_b200.data.msa_pairing",
+    "fastfold.data.msa_identifiers": "fastfold_b200.data.msa_identifiers",
+    "fastfold.data.templates": "fastfold_b200.data.templates",
+    "fastfold.data.mmcif_parsing": "fastfold_b200.data.mmcif_parsing",
+    "fastfold.data.errors": "fastfold_b200.data.errors",
+    "fastfold.data.tools": "fastfold_b200.data.tools",
+    "fastfold.data.tools.jackhmmer": "fastfold_b200.data.tools.jackhmmer",
+    "fastfold.data.tools.hhblits": "fastfold_b200.data.tools.hhblits",
+    "fastfold.data.tools.hhsearch": "fastfold_b200.data.tools.hhsearch",
+    "fastfold.data.tools.hmmsearch": "fastfold_b200.data.tools.hmmsearch",
+    "fastfold.data.tools.hmmbuild": "fastfold_b200.data.tools.hmmbuild",
+    "fastfold.data.tools.kalign": "fastfold_b200.data.tools.kalign",
+    "fastfold.data.tools.utils": "fastfold_b200.data.tools.utils",
+    "fastfold.workflow": "fastfold_b200.workflow",
+    "fastfold.workflow.workflow_run": "fastfold_b200.workflow.workflow_run",
+    "fastfold.workflow.factory": "fastfold_b200.workflow.factory",
+    "fastfold.workflow.template": "fastfold_b200.workflow.template",
+    "fastfold.relax": "fastfold_b200.relax",
+    "fastfold.relax.relax": "fastfold_b200.relax.relax",
+    "fastfold.relax.amber_minimize": "fastfold_b200.relax.amber_minimize",
+    "fastfold.relax.cleanup": "fastfold_b200.relax.cleanup",
+    "fastfold.relax.utils": "fastfold_b200.relax.utils",
+    "fastfold.utils.all_atom_multimer": "fastfold_b200.utils.all_atom_multimer",
+    "fastfold.utils.superimposition": "fastfold_b200.utils.superimposition",
+    "fastfold.utils.test_utils": "fastfold_b200.utils.test_utils",
+    "fastfold.utils.geometry": "fastfold_b200.utils.geometry",
+    "fastfold.utils.geometry.vector": "fastfold_b200.utils.geometry",
+    "fastfold.utils.geometry.rotation_matrix": "fastfold_b200.utils.geometry",
+    "fastfold.utils.geometry.rigid_matrix_vector": "fastfold_b200.utils.geometry",
+    "fastfold.utils.geometry.quat_rigid": "fastfold_b200.utils.geometry",
+    "fastfold.utils.geometry.utils": "fastfold_b200.utils.geometry",
+    "fastfold.utils.geometry.test_utils": "fastfold_b200.utils.geometry",
+    "fastfold.model.fastnn.template": "fastfold_b200.models.fastnn.template",
+    "fastfold.model.fastnn.embedders": "fastfold_b200.models.fastnn.embedders",
+    "fastfold.model.fastnn.embedders_multimer": "fastfold_b200.models.fastnn.embedders_multimer",
+    "fastfold.model.fastnn.initializer": "fastfold_b200.models.fastnn.initializer",
+    "fastfold.model.nn.embedders_multimer": "fastfold_b200.models.nn.embedders_multimer",
 }
+
+# modules of the OpenFold-layout model that the reference splits over more files than this package does
+_ALIASES.update({
+    "fastfold.model.nn.msa": "fastfold_b200.models.nn.msa",
+    "fastfold.model.nn.dropout": "fastfold_b200.models.nn.dropout",
+    "fastfold.model.nn.pair_transition": "fastfold_b200.models.nn.pair",
+    "fastfold.model.nn.outer_product_mean": "fastfold_b200.models.nn.pair",
+    "fastfold.model.nn.triangular_attention": "fastfold_b200.models.nn.pair",
+    "fastfold.model.nn.triangular_multiplicative_update": "fastfold_b200.models.nn.pair",
+})
 
 
 class _AliasFinder:

@@ -111,3 +111,36 @@ def from_pdb_string(pdb_str: str, chain_id: Optional[str] = None) -> Protein:
 
 def ideal_atom_mask(prot: Protein) -> np.ndarray:
     return rc.STANDARD_ATOM_MASK[prot.aatype]
+
+
+PICO_TO_ANGSTROM = 0.01
+
+
+def from_proteinnet_string(proteinnet_str: str) -> Protein:
+    """One ProteinNet text record (``[PRIMARY]`` sequence, ``[TERTIARY]`` three rows x / y / z of N, CA, C coordinates in
+    picometres, ``[MASK]`` of ``+`` / ``-`` per residue) as a backbone-only ``Protein`` in angstroms."""
+    import re
+    fields, key = {}, None
+    for line in proteinnet_str.splitlines():
+        m = re.fullmatch(r"\[([A-Z]+)\]", line.strip())
+        if m:
+            key = m.group(1)
+            fields[key] = []
+        elif key is not None and line.strip():
+            fields[key].append(line.strip())
+    seq = "".join(fields["PRIMARY"])
+    aatype = np.array([rc.restype_order.get(ch, rc.restype_num) for ch in seq], dtype=np.int64)
+    n = len(seq)
+    backbone = [rc.atom_order[a] for a in ("N", "CA", "C")]
+    positions = np.zeros((n, rc.atom_type_num, 3), dtype=np.float32)
+    if "TERTIARY" in fields:
+        xyz = np.array([[float(v) for v in row.split()] for row in fields["TERTIARY"][:3]], dtype=np.float32)     # [3, 3 n]
+        for i, slot in enumerate(backbone):
+            positions[:, slot, :] = xyz[:, i::3].T * PICO_TO_ANGSTROM
+    present = np.ones(n, dtype=np.float32)
+    if "MASK" in fields:
+        present = np.array([1.0 if ch == "+" else 0.0 for ch in "".join(fields["MASK"])], dtype=np.float32)
+    mask = np.zeros((n, rc.atom_type_num), dtype=np.float32)
+    mask[:, backbone] = present[:, None]
+    return Protein(atom_positions=positions, atom_mask=mask, aatype=aatype, residue_index=np.arange(n), b_factors=np.zeros_like(mask))
+

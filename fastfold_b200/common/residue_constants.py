@@ -8,6 +8,7 @@ No dm-tree or network access is needed, unlike the reference's module (fastfold/
 :460-463), which downloads ``stereo_chemical_props.txt`` to build its within-residue bond bounds; here those bounds
 are derived from the idealised coordinates themselves (see ``make_atom14_dists_bounds``).
 """
+import collections
 import functools
 import json
 import os
@@ -109,6 +110,57 @@ def _ideal_atom14_coordinates():
             p = np.append(restype_atom14_rigid_group_positions[r, a], 1.0)
             coords[r, a] = (to_bb[g] @ p)[:3]
     return coords
+
+
+Bond = collections.namedtuple("Bond", ["atom1_name", "atom2_name", "length", "stddev"])
+BondAngle = collections.namedtuple("BondAngle", ["atom1_name", "atom2_name", "atom3name", "angle_rad", "stddev"])
+
+
+@functools.lru_cache(maxsize=None)
+def load_stereo_chemical_props():
+    """``(residue_bonds, residue_virtual_bonds, residue_bond_angles)`` keyed by three-letter residue name.
+
+    The reference reads these from the stereo_chemical_props.txt table of the AlphaFold distribution
+    (fastfold/common/residue_constants.py:404-470).  That file is not shipped here; the same quantities are derived
+    from the idealised residue geometry this package already carries (``rigid_group_atom_positions``): two heavy
+    atoms closer than 1.95 A are bonded (ideal length = their distance), two bonds sharing an atom define a bond
+    angle, and the two outer atoms of an angle a virtual bond whose length follows from the law of cosines.  The
+    spreads are nominal (0.02 A for lengths, 0.035 rad for angles), not the per-bond literature values of that file.
+    """
+    ideal = _ideal_atom14_coordinates()
+    bonds, virtual, angles = {}, {}, {}
+    for r, letter in enumerate(restypes):
+        res = restype_1to3[letter]
+        names = [a for a in restype_name_to_atom14_names[res] if a]
+        blist = []
+        for i in range(len(names)):
+            for j in range(i + 1, len(names)):
+                d = float(np.linalg.norm(ideal[r, i] - ideal[r, j]))
+                if d < 1.95:
+                    blist.append(Bond(names[i], names[j], d, 0.02))
+        bonds[res] = blist
+        alist, vlist = [], []
+        for a in range(len(blist)):
+            for b in range(a + 1, len(blist)):
+                shared = {blist[a].atom1_name, blist[a].atom2_name} & {blist[b].atom1_name, blist[b].atom2_name}
+                if len(shared) != 1:
+                    continue
+                centre = shared.pop()
+                end1 = blist[a].atom1_name if blist[a].atom2_name == centre else blist[a].atom2_name
+                end3 = blist[b].atom1_name if blist[b].atom2_name == centre else blist[b].atom2_name
+                p1, p2, p3 = (ideal[r, names.index(n)] for n in (end1, centre, end3))
+                v1, v3 = p1 - p2, p3 - p2
+                ang = float(np.arccos(np.clip(np.dot(v1, v3) / (np.linalg.norm(v1) * np.linalg.norm(v3)), -1.0, 1.0)))
+                alist.append(BondAngle(end1, centre, end3, ang, 0.035))
+                l1, l3 = blist[a].length, blist[b].length
+                length = float(np.sqrt(l1 ** 2 + l3 ** 2 - 2 * l1 * l3 * np.cos(ang)))
+                dl_outer = 0.5 / length * (2 * l1 * l3 * np.sin(ang))
+                dl_1 = 0.5 / length * (2 * l1 - 2 * l3 * np.cos(ang))
+                dl_3 = 0.5 / length * (2 * l3 - 2 * l1 * np.cos(ang))
+                sd = float(np.sqrt((dl_outer * 0.035) ** 2 + (dl_1 * 0.02) ** 2 + (dl_3 * 0.02) ** 2))
+                vlist.append(Bond(end1, end3, length, sd))
+        angles[res], virtual[res] = alist, vlist
+    return bonds, virtual, angles
 
 
 def make_atom14_dists_bounds(overlap_tolerance=1.5, bond_length_tolerance_factor=15):

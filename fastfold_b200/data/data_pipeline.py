@@ -55,6 +55,116 @@ def empty_template_features(num_res: int) -> FeatureDict:
             "template_sequence": np.zeros((0,), object), "template_sum_probs": np.zeros((0, 1), np.float32)}
 
 
+empty_template_feats = empty_template_features          # the reference's name for the same function
+
+
+def make_template_features(input_sequence: str, hits, template_featurizer, query_pdb_code=None, query_release_date=None) -> FeatureDict:
+    """Template features of one query from parsed search hits (``{file name: [hits]}`` or a flat list); the empty
+    feature set when there is no featuriser, no hit, or no hit survives the featuriser's filters."""
+    flat = sum(hits.values(), []) if isinstance(hits, Mapping) else list(hits or [])
+    if not flat or template_featurizer is None:
+        return empty_template_features(len(input_sequence))
+    try:
+        result = template_featurizer.get_templates(input_sequence, flat, query_pdb_code=query_pdb_code, query_release_date=query_release_date)
+    except TypeError:          # featurisers without the query-identity filters (hmmsearch hits of the multimer pipeline)
+        result = template_featurizer.get_templates(input_sequence, flat)
+    feats = result.features
+    if feats["template_aatype"].shape[0] == 0:
+        return empty_template_features(len(input_sequence))
+    return feats
+
+
+def make_protein_features(protein_object, description: str, _is_distillation: bool = False) -> FeatureDict:
+    """Sequence features + all-atom ground truth of a ``common.protein.Protein``."""
+    aatype = np.asarray(protein_object.aatype)
+    sequence = "".join(rc.restypes_with_x[int(a)] for a in aatype)
+    feats = dict(make_sequence_features(sequence, description, len(aatype)))
+    feats.update(_ground_truth_features(protein_object.atom_positions, protein_object.atom_mask, 0.0, _is_distillation))
+    return feats
+
+
+def make_pdb_features(protein_object, description: str, is_distillation: bool = True, confidence_threshold: float = 50.0) -> FeatureDict:
+    """As ``make_protein_features``; for self-distillation targets (predicted structures with the confidence in the
+    B-factor column) atoms of residues below ``confidence_threshold`` are masked out of the ground truth."""
+    feats = make_protein_features(protein_object, description, _is_distillation=True)
+    if is_distillation:
+        confident = (np.asarray(protein_object.b_factors) > confidence_threshold).astype(np.float32)
+        feats["all_atom_mask"] = feats["all_atom_mask"] * confident
+    else:
+        feats["is_distillation"] = np.array(0.0, np.float32)
+    return feats
+
+
+def make_mmcif_features(mmcif_object, chain_id: str) -> FeatureDict:
+    """Sequence features + ground truth + resolution / release date of one chain of a parsed mmCIF file."""
+    from . import mmcif_parsing
+    sequence = mmcif_object.chain_to_seqres[chain_id]
+    feats = dict(make_sequence_features(sequence, "%s_%s" % (mmcif_object.file_id, chain_id), len(sequence)))
+    pos, mask = mmcif_parsing.get_atom_coords(mmcif_object, chain_id)
+    header = mmcif_object.header
+    get = header.get if isinstance(header, dict) else (lambda k, d=None: getattr(header, k, d))
+    feats.update(_ground_truth_features(pos, mask, float(get("resolution", 0.0) or 0.0), False))
+    feats["release_date"] = np.array([str(get("release_date", "")).encode()], dtype=object)
+    return feats
+
+
+def run_msa_tool(msa_runner, fasta_path: str, msa_out_path: str, msa_format: str, max_sto_sequences: Optional[int] = None):
+    """Runs one alignment tool on a FASTA file and writes its result (``sto`` or ``a3m`` text) to ``msa_out_path``."""
+    if msa_format == "sto" and max_sto_sequences is not None:
+        result = msa_runner.query(fasta_path, max_sto_sequences)
+    else:
+        result = msa_runner.query(fasta_path)
+    result = result[0] if isinstance(result, (list, tuple)) else result
+    text = result[msa_format] if isinstance(result, Mapping) else result
+    with open(msa_out_path, "w") as fh:
+        fh.write(text)
+    return result
+
+
+import contextlib
+import tempfile
+
+
+@contextlib.contextmanager
+def temp_fasta_file(fasta_str: str):
+    """Path of a temporary FASTA file holding ``fasta_str`` (deleted on exit)."""
+    with tempfile.NamedTemporaryFile("w", suffix=".fasta") as fh:
+        fh.write(fasta_str)
+        fh.flush()
+        yield fh.name
+
+
+def convert_monomer_features(monomer_features: FeatureDict, chain_id: str) -> FeatureDict:
+    """Monomer-pipeline features in the form the multimer assembly expects: scalars without their leading axis, residue
+    types as indices in this package's order, the template mask under its model-side name."""
+    out = {"auth_chain_id": np.asarray(chain_id, dtype=object)}
+    for name, value in monomer_features.items():
+        if name in ("sequence", "domain_name", "num_alignments", "seq_length"):
+            value = np.asarray(value[0], dtype=np.asarray(value).dtype)
+        elif name == "aatype":
+            value = np.argmax(value, axis=-1).astype(np.int32)
+        elif name == "template_aatype":
+            idx = np.argmax(value, axis=-1).astype(np.int32)
+            value = np.take(np.asarray(rc.MAP_HHBLITS_AATYPE_TO_OUR_AATYPE), idx, axis=0)
+        elif name == "template_all_atom_masks":
+            name = "template_all_atom_mask"
+        out[name] = value
+    return out
+
+
+def int_id_to_str_id(num: int) -> str:
+    """1 -> A, 2 -> B, ..., 26 -> Z, 27 -> AA, 28 -> BA, 29 -> CA, ...: chain names as mmCIF files count them (least
+    significant letter first)."""
+    if num <= 0:
+        raise ValueError("Only positive integers allowed, got %d." % num)
+    num -= 1
+    letters = []
+    while num >= 0:
+        letters.append(chr(ord("A") + num % 26))
+        num = num // 26 - 1
+    return "".join(letters)
+
+
 class DataPipeline:
     def __init__(self, template_featurizer=None):
         self.template_featurizer = template_featurizer
@@ -143,28 +253,6 @@ def np_to_tensor_dict(np_example, features):
     return {k: torch.tensor(np.asarray(v)) for k, v in np_example.items() if k in features and np.asarray(v).dtype != object}
 
 
-def _nonensembled(cfg_common, cfg_mode):
-    t = [dt.cast_to_64bit_ints, dt.correct_msa_restypes, dt.squeeze_features, dt.randomly_replace_msa_with_unknown(0.0), dt.make_seq_mask,
-         dt.make_msa_mask, dt.make_hhblits_profile]
-    t.append(dt.make_atom14_masks)
-    if cfg_mode.supervised:
-        t += [dt.make_atom14_positions, dt.atom37_to_frames, dt.atom37_to_torsion_angles(""), dt.make_pseudo_beta(""), dt.get_backbone_frames,
-              dt.get_chi_angles]
-    return t
-
-
-def _ensembled(cfg_common, cfg_mode, seed):
-    max_msa = cfg_mode.max_msa_clusters
-    t = [dt.sample_msa(max_msa, keep_extra=True, seed=seed)]
-    if "masked_msa" in cfg_common:
-        t.append(dt.make_masked_msa(cfg_common.masked_msa, cfg_mode.masked_msa_replace_fraction))
-    if cfg_common.msa_cluster_features:
-        t += [dt.nearest_neighbor_clusters(), dt.summarize_clusters]
-    t.append(dt.crop_extra_msa(cfg_mode.max_extra_msa) if cfg_mode.max_extra_msa else dt.delete_extra_msa)
-    t.append(dt.make_msa_feat)
-    return t
-
-
 class FeaturePipeline:
     def __init__(self, config):
         self.config = config      # the ``data`` sub-tree of ``model_config``
@@ -174,40 +262,18 @@ class FeaturePipeline:
             is_multimer = "asym_id" in raw_features
         if is_multimer:
             return self._process_multimer(raw_features, mode, seed)
+        from . import feature_pipeline as fp
         cfg = copy.deepcopy(self.config)
-        mode_cfg = cfg[mode]
         raw = dict(raw_features)
-        num_res = int(np.asarray(raw["seq_length"]).reshape(-1)[0])
-        if "deletion_matrix_int" in raw:
-            raw["deletion_matrix"] = np.asarray(raw.pop("deletion_matrix_int")).astype(np.float32)
-        names = list(cfg.common.unsupervised_features) + ["deletion_matrix"]
-        if mode_cfg.supervised:
-            names += list(cfg.supervised.supervised_features)
-        tensors = np_to_tensor_dict(raw, names)
-        for fn in _nonensembled(cfg.common, mode_cfg):
-            tensors = fn(tensors)
-        n_iter = cfg.common.max_recycling_iters + 1
-        keep = [k for k in cfg.common.feat.keys() if not k.startswith("template_")]
-        per_iter = []
-        for it in range(n_iter):
-            d = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in tensors.items()}
-            s = seed + it if cfg.common.resample_msa_in_recycling else seed
-            torch.manual_seed(s)
-            for fn in _ensembled(cfg.common, mode_cfg, s):
-                d = fn(d)
-            d["seq_length"] = torch.tensor(num_res)
-            if mode_cfg.crop and mode_cfg.crop_size:
-                schema = {k: v for k, v in cfg.common.feat.items()}
-                d = dt.random_crop_to_size(mode_cfg.crop_size, mode_cfg.max_templates, schema, mode_cfg.subsample_templates, seed=seed)(d)
-            d = {k: v for k, v in d.items() if k in keep}
-            if mode_cfg.fixed_size:
-                nres = mode_cfg.crop_size if (mode_cfg.crop and mode_cfg.crop_size) else num_res
-                schema = {k: cfg.common.feat[k] for k in d}
-                d = dt.make_fixed_size(schema, mode_cfg.max_msa_clusters, mode_cfg.max_extra_msa, nres, 0)(d)
-            per_iter.append(d)
-        out = {k: torch.stack([d[k] for d in per_iter], dim=-1) for k in per_iter[0]}
-        return out
-
+        # templates take part only when the configuration uses them AND the example has at least one hit; the caller
+        # switches the model's template stack off when no template features come back
+        t = raw.get("template_aatype")
+        has_templates = bool(cfg.common.use_templates) and t is not None and np.asarray(t).shape[0] > 0
+        cfg.common.use_templates = has_templates
+        feats = fp.np_example_to_features(raw, cfg, mode, seed=seed)
+        if not has_templates:
+            feats = {k: v for k, v in feats.items() if not k.startswith("template_")}
+        return feats
 
     def _process_multimer(self, raw_features, mode, seed):
         """Merged multimer example (``DataPipelineMultimer.process_fasta``) -> model features: one pass of the multimer

@@ -250,6 +250,83 @@ def sample_msa(protein, max_seq, keep_extra, seed=None):
     return protein
 
 
+def make_all_atom_aatype(protein):
+    """``all_atom_aatype`` is the residue type the all-atom ground truth is indexed by (same tensor as ``aatype``)."""
+    protein["all_atom_aatype"] = protein["aatype"]
+    return protein
+
+
+def fix_templates_aatype(protein):
+    """Template residue types arrive one-hot in the HHblits alphabet: to indices, then to this package's residue order."""
+    t = protein["template_aatype"]
+    if t.dim() == 3:                 # also with zero templates, so that the transforms after this one see [T, N]
+        idx = t.argmax(dim=-1)
+        table = torch.tensor(rc.MAP_HHBLITS_AATYPE_TO_OUR_AATYPE, dtype=torch.int64, device=idx.device)
+        protein["template_aatype"] = table[idx]
+    return protein
+
+
+@curry1
+def add_distillation_flag(protein, distillation):
+    protein["is_distillation"] = distillation
+    return protein
+
+
+@curry1
+def sample_msa_distillation(protein, max_seq):
+    """Self-distillation examples are subsampled to ``max_seq`` rows before anything else sees the MSA."""
+    if int(protein["is_distillation"]) == 1:
+        protein = sample_msa(max_seq, keep_extra=False)(protein)
+    return protein
+
+
+@curry1
+def block_delete_msa(protein, config, seed=None):
+    """Training-time augmentation: removes ``num_blocks`` contiguous runs of MSA rows, each ``msa_fraction_per_block`` of
+    the alignment long, never the query row.  ``config.randomize_num_blocks`` draws the number of runs uniformly from
+    ``0 .. num_blocks``.  (Same augmentation as fastfold/data/data_transforms.py:245-276, stated with index sets.)"""
+    num_seq = protein["msa"].shape[0]
+    g = torch.Generator()
+    if seed is not None:
+        g.manual_seed(seed)
+    else:
+        g.seed()
+    block_len = int(num_seq * float(config.msa_fraction_per_block))
+    n_blocks = int(config.num_blocks)
+    if getattr(config, "randomize_num_blocks", False):
+        n_blocks = int(torch.randint(0, n_blocks + 1, (1,), generator=g))
+    keep = torch.ones(num_seq, dtype=torch.bool)
+    if block_len > 0 and n_blocks > 0:
+        starts = torch.randint(0, num_seq, (n_blocks,), generator=g)
+        rows = (starts[:, None] + torch.arange(block_len)[None, :]).clamp_(max=num_seq - 1).reshape(-1)
+        keep[rows] = False
+    keep[0] = True
+    keep_indices = torch.nonzero(keep).reshape(-1)
+    for k in MSA_FEATURE_NAMES:
+        if k in protein:
+            protein[k] = torch.index_select(protein[k], 0, keep_indices)
+    return protein
+
+
+@curry1
+def add_constant_field(protein, key, value):
+    protein[key] = torch.tensor(value, device=protein["msa"].device)
+    return protein
+
+
+def shaped_categorical(probs, epsilon=1e-10):
+    """One categorical draw per leading index of ``probs [..., classes]``; returns the class indices ``[...]``."""
+    flat = (probs + epsilon).reshape(-1, probs.shape[-1])
+    return torch.multinomial(flat, 1).reshape(probs.shape[:-1])
+
+
+def make_atom14_masks_np(batch):
+    """``make_atom14_masks`` on a dict of numpy arrays (used by the relaxation code, which works in numpy)."""
+    as_t = {k: torch.as_tensor(v) if isinstance(v, np.ndarray) else v for k, v in batch.items()}
+    out = make_atom14_masks(as_t)
+    return {k: v.numpy() if torch.is_tensor(v) else v for k, v in out.items()}
+
+
 @curry1
 def crop_extra_msa(protein, max_extra_msa):
     num_seq = protein["extra_msa"].shape[0]

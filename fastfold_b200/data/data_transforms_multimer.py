@@ -21,6 +21,25 @@ def make_msa_profile(batch):
     return batch
 
 
+def gumbel_noise(shape, device=None, eps=1e-6, generator=None):
+    """Samples of the standard Gumbel distribution: ``-log(-log(U))`` with ``U`` uniform on (0, 1)."""
+    u = torch.rand(tuple(shape), dtype=torch.float32, device=device, generator=generator)
+    return -torch.log(-torch.log(u + eps) + eps)
+
+
+def gumbel_max_sample(logits, generator=None):
+    """One draw from ``softmax(logits)`` along the last axis, one-hot (argmax of the logits plus Gumbel noise)."""
+    z = gumbel_noise(logits.shape, device=logits.device, generator=generator)
+    return torch.nn.functional.one_hot(torch.argmax(logits + z, dim=-1), logits.shape[-1])
+
+
+def gumbel_argsort_sample_idx(logits, generator=None):
+    """A random permutation of the indices: sampling without replacement with probabilities ``softmax(logits)`` -
+    the order of the logits after Gumbel noise was added, largest first."""
+    z = gumbel_noise(logits.shape, device=logits.device, generator=generator)
+    return torch.argsort(logits + z, dim=-1, descending=True)
+
+
 def sample_msa(batch, max_seq, max_extra_msa_seq, seed=None):
     """Gumbel-max sampling of ``max_seq`` cluster centres; the next ``max_extra_msa_seq`` rows become the extra MSA."""
     g = torch.Generator()

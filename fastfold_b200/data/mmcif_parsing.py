@@ -36,6 +36,26 @@ class ResidueAtPosition:
 
 
 @dataclasses.dataclass(frozen=True)
+class Monomer:
+    """One residue of an entity's polymer sequence (``_entity_poly_seq``): its three-letter id and its position."""
+    id: str
+    num: int
+
+
+@dataclasses.dataclass(frozen=True)
+class AtomSite:
+    """The columns of one ``_atom_site`` row that link an atom to its residue and chain."""
+    residue_name: str
+    author_chain_id: str
+    mmcif_chain_id: str
+    author_seq_num: str
+    mmcif_seq_num: int
+    insertion_code: str
+    hetatm_atom: str
+    model_num: int
+
+
+@dataclasses.dataclass(frozen=True)
 class MmcifObject:
     file_id: str
     header: PdbHeader

@@ -156,6 +156,76 @@ def deduplicate_unpaired_sequences(chains: Sequence[MutableMapping[str, np.ndarr
 # ---------------------------------------------------------------------------
 # merging
 # ---------------------------------------------------------------------------
+def block_diag(*arrs: np.ndarray, pad_value: float = 0.0) -> np.ndarray:
+    """Block-diagonal arrangement of 2-D (or higher: leading two axes) arrays with ``pad_value`` off the diagonal."""
+    return _block_diag(list(arrs), pad_value)
+
+
+def pad_features(feature: np.ndarray, feature_name: str) -> np.ndarray:
+    """Appends the "absent partner" row to a paired (``*_all_seq``) MSA feature: the row a chain contributes to a
+    paired alignment row in which it has no sequence.  Other features are returned unchanged."""
+    if feature_name in ("msa_all_seq", "msa_mask_all_seq", "deletion_matrix_all_seq", "deletion_matrix_int_all_seq"):
+        pad = np.full((1,) + feature.shape[1:], MSA_PAD_VALUES[feature_name], dtype=feature.dtype)
+        return np.concatenate([feature, pad], axis=0)
+    if feature_name == "msa_species_identifiers_all_seq":
+        return np.concatenate([np.asarray(feature, dtype=object), np.array([b""], dtype=object)], axis=0)
+    return feature
+
+
+def reorder_paired_rows(all_paired_msa_rows_dict: Mapping[int, np.ndarray]) -> np.ndarray:
+    """``{number of chains a row covers: [rows, chains] index table}`` -> one table: rows covering more chains first,
+    within a group the rows whose indices are smallest (most query-like in every chain) first."""
+    out = []
+    for n_chains in sorted(all_paired_msa_rows_dict, reverse=True):
+        rows = np.asarray(all_paired_msa_rows_dict[n_chains])
+        if rows.size == 0:
+            continue
+        rank = np.abs(np.prod(rows.astype(np.float64), axis=1))
+        out.extend(rows[np.argsort(rank, kind="stable")])
+    return np.array(out)
+
+
+def crop_chains(chains_list: Sequence[MutableMapping[str, np.ndarray]], msa_crop_size: int, pair_msa_sequences: bool,
+                max_templates: int) -> List[MutableMapping[str, np.ndarray]]:
+    """Caps the MSA depth and the template count of every chain before merging.  With pairing, at most half of the
+    budget goes to the paired block, and the unpaired rows get what is left after the chain's NON-GAP paired rows were
+    counted, so that every chain ends up with about ``msa_crop_size`` sequences of its own
+    (fastfold/data/feature_processing_multimer.py:87-166)."""
+    out = []
+    for chain in chains_list:
+        chain = dict(chain)
+        depth = int(chain["msa"].shape[0])
+        keep_paired = 0
+        if pair_msa_sequences and "msa_all_seq" in chain:
+            depth_paired = int(chain["msa_all_seq"].shape[0])
+            keep_paired = min(depth_paired, msa_crop_size // 2)
+            block = chain["msa_all_seq"][:keep_paired]
+            own_rows = int(np.sum(np.any(block != MSA_GAP_IDX, axis=1)))
+            keep = min(depth, max(msa_crop_size - min(own_rows, keep_paired), 0))
+        else:
+            keep = min(depth, msa_crop_size)
+        n_templates = None
+        if "template_aatype" in chain and max_templates:
+            n_templates = min(chain["template_aatype"].shape[0], max_templates)
+        for k in list(chain):
+            base = k.split("_all_seq")[0]
+            if base in TEMPLATE_FEATURES and n_templates is not None:
+                chain[k] = chain[k][:n_templates]
+            elif base in MSA_FEATURES or base == "msa_species_identifiers":
+                if "_all_seq" in k:
+                    if pair_msa_sequences:
+                        chain[k] = chain[k][:keep_paired]
+                else:
+                    chain[k] = chain[k][:keep]
+        chain["num_alignments"] = np.asarray(keep, dtype=np.int32)
+        if n_templates is not None:
+            chain["num_templates"] = np.asarray(n_templates, dtype=np.int32)
+        if pair_msa_sequences and "msa_all_seq" in chain:
+            chain["num_alignments_all_seq"] = np.asarray(keep_paired, dtype=np.int32)
+        out.append(chain)
+    return out
+
+
 def _block_diag(arrs: Sequence[np.ndarray], pad_value) -> np.ndarray:
     rows = sum(a.shape[0] for a in arrs)
     cols = sum(a.shape[1] for a in arrs)
@@ -262,20 +332,7 @@ def pair_and_merge(all_chain_features: Mapping[str, MutableMapping[str, np.ndarr
     if pair:
         chains = create_paired_features(chains)
         chains = deduplicate_unpaired_sequences(chains)
-    for c in chains:          # crop MSA depth per chain
-        limit = max_msa_crop
-        if pair and "msa_all_seq" in c:
-            keep_paired = min(c["msa_all_seq"].shape[0], max_msa_crop // 2)
-            for k in list(c):
-                if "_all_seq" in k and k.split("_all_seq")[0] in MSA_FEATURES + ("msa_species_identifiers",):
-                    c[k] = c[k][:keep_paired]
-            limit = max(max_msa_crop - keep_paired, 0)
-        for k in MSA_FEATURES:
-            if k in c:
-                c[k] = c[k][:limit]
-        for k in TEMPLATE_FEATURES:
-            if k in c:
-                c[k] = c[k][:max_templates]
+    chains = crop_chains(chains, msa_crop_size=max_msa_crop, pair_msa_sequences=pair, max_templates=max_templates)
     merged = merge_chain_features(chains, pair_msa_sequences=pair, max_templates=max_templates)
     n_msa = merged["msa"].shape[0]
     merged["cluster_bias_mask"] = np.pad(np.zeros(1), (0, n_msa - 1), constant_values=1.0).astype(np.float32)

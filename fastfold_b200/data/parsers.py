@@ -282,3 +282,55 @@ def parse_hmmsearch_a3m(query_sequence: str, a3m_string: str, skip_first: bool =
         cols = [k for k, ch in enumerate(seq) if not ch.islower()]
         hits.append(TemplateHit(i, name, aligned, None, query_sequence, "".join(upper[k] for k in cols), iq, [ih[k] for k in cols]))
     return hits
+
+
+def parse_hmmsearch_sto(output_string: str, input_sequence: str) -> Sequence[TemplateHit]:
+    """Template hits straight from hmmsearch's Stockholm output: converted to A3M with the query row's gaps kept (the hit
+    rows are aligned to the query as searched), every row a candidate."""
+    a3m = convert_stockholm_to_a3m(output_string, remove_first_row_gaps=False)
+    return parse_hmmsearch_a3m(query_sequence=input_sequence, a3m_string=a3m, skip_first=False)
+
+
+@dataclasses.dataclass(frozen=True)
+class HitMetadata:
+    """The fields of an hmmsearch hit description ``<pdb>_<chain>/<start>-<end> mol:protein length:<n>  <text>``."""
+    pdb_id: str
+    chain: str
+    start: int
+    end: int
+    length: int
+    text: str
+
+
+def parse_hmmsearch_description(description: str) -> HitMetadata:
+    m = re.match(r"^>?([a-zA-Z\d]{4})_([a-zA-Z0-9.]+)/(\d+)-(\d+).*?length:(\d+) *(.*)$", description.strip())
+    if not m:
+        raise ValueError("Could not parse hmmsearch description %r" % description)
+    return HitMetadata(pdb_id=m.group(1), chain=m.group(2), start=int(m.group(3)), end=int(m.group(4)), length=int(m.group(5)), text=m.group(6))
+
+
+@dataclasses.dataclass(frozen=True)
+class Msa:
+    """A parsed alignment file: rows, per-row deletion counts and row descriptions, all of the same length."""
+    sequences: Sequence[str]
+    deletion_matrix: DeletionMatrix
+    descriptions: Sequence[str]
+
+    def __post_init__(self):
+        if not (len(self.sequences) == len(self.deletion_matrix) == len(self.descriptions)):
+            raise ValueError("All fields of an MSA must have the same length")
+
+    def __len__(self):
+        return len(self.sequences)
+
+    def truncate(self, max_seqs: int) -> "Msa":
+        return Msa(self.sequences[:max_seqs], self.deletion_matrix[:max_seqs], self.descriptions[:max_seqs])
+
+    @classmethod
+    def from_a3m(cls, a3m_string: str) -> "Msa":
+        return cls(*parse_a3m(a3m_string))
+
+    @classmethod
+    def from_stockholm(cls, stockholm_string: str) -> "Msa":
+        return cls(*parse_stockholm(stockholm_string))
+

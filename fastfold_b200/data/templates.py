@@ -65,6 +65,10 @@ class PrefilterError(Exception):
     pass
 
 
+class PdbIdError(PrefilterError):
+    """The hit is the query's own PDB entry."""
+
+
 class DateError(PrefilterError):
     pass
 
@@ -108,6 +112,30 @@ def _parse_release_dates(path: str) -> Mapping[str, datetime.datetime]:
         if len(parts) >= 2:
             out[parts[0].strip().lower()] = datetime.datetime.strptime(parts[1][:10], "%Y-%m-%d")
     return out
+
+
+def generate_release_dates_cache(mmcif_dir: str, out_path: str) -> Mapping[str, str]:
+    """Parses every ``*.cif`` of ``mmcif_dir`` once and writes ``{pdb id: {"release_date": "YYYY-MM-DD"}}`` as JSON: the
+    cache ``TemplateHitFeaturizer(release_dates_path=...)`` reads, so that hits can be date-filtered without opening
+    their files."""
+    import json
+    dates = {}
+    for name in sorted(os.listdir(mmcif_dir)):
+        if not name.endswith(".cif"):
+            continue
+        file_id = os.path.splitext(name)[0]
+        with open(os.path.join(mmcif_dir, name)) as fh:
+            parsed = mmcif_parsing.parse(file_id=file_id, mmcif_string=fh.read())
+        if parsed.mmcif_object is None:
+            log.info("Failed to parse %s. Skipping...", name)
+            continue
+        header = parsed.mmcif_object.header
+        date = header.get("release_date") if isinstance(header, dict) else getattr(header, "release_date", None)
+        if date:
+            dates[file_id] = {"release_date": str(date)}
+    with open(out_path, "w") as fh:
+        json.dump(dates, fh)
+    return dates
 
 
 def _parse_obsolete(path: str) -> Mapping[str, Optional[str]]:
@@ -297,6 +325,13 @@ class TemplateSearchResult:
     warnings: Sequence[str]
 
 
+@dataclasses.dataclass(frozen=True)
+class PrefilterResult:
+    valid: bool
+    error: Optional[str]
+    warning: Optional[str]
+
+
 class TemplateHitFeaturizer:
     """Turns HHSearch hits into template features (fastfold/data/templates.py:828-1063)."""
 
@@ -363,12 +398,29 @@ class TemplateHitFeaturizer:
                 pdb_id, chain_id, hit.sum_probs, hit.index, e), None)
 
     # -- all hits ------------------------------------------------------------
-    def get_templates(self, query_sequence: str, hits: Sequence[parsers.TemplateHit]) -> TemplateSearchResult:
+    def get_templates(self, query_sequence: str, hits: Sequence[parsers.TemplateHit], query_pdb_code: Optional[str] = None,
+                      query_release_date: Optional[datetime.datetime] = None) -> TemplateSearchResult:
+        """``query_pdb_code`` / ``query_release_date`` (training on PDB entries): the query's own entry is never its
+        template, and the date cutoff moves to 60 days before the query's release when that is earlier than
+        ``max_template_date`` (fastfold/data/templates.py:1000-1063)."""
         log.info("Searching for template for: %s", query_sequence)
         collected = {k: [] for k in TEMPLATE_FEATURES}
         errors, warnings = [], []
         candidates = []
+        saved_cutoff = self._max_template_date
+        if query_release_date is not None:
+            if isinstance(query_release_date, str):
+                query_release_date = datetime.datetime.strptime(query_release_date, "%Y-%m-%d")
+            self._max_template_date = min(saved_cutoff, query_release_date - datetime.timedelta(days=60))
+        try:
+            return self._get_templates(query_sequence, hits, query_pdb_code, collected, errors, warnings, candidates)
+        finally:
+            self._max_template_date = saved_cutoff
+
+    def _get_templates(self, query_sequence, hits, query_pdb_code, collected, errors, warnings, candidates):
         for hit in sorted(hits, key=lambda h: h.sum_probs if h.sum_probs is not None else 0.0, reverse=True):
+            if query_pdb_code is not None and _hit_pdb_id_and_chain(hit)[0].lower() == query_pdb_code.lower():
+                continue
             rejected = self._prefilter(query_sequence, hit)
             if rejected is None:
                 candidates.append(hit)
@@ -422,9 +474,9 @@ class HmmsearchHitFeaturizer(TemplateHitFeaturizer):
             return SingleHitResult(None, None, None)
         return None
 
-    def get_templates(self, query_sequence, hits):
+    def get_templates(self, query_sequence, hits, query_pdb_code=None, query_release_date=None):
         ordered = [dataclasses.replace(h, sum_probs=float(len(hits) - i)) if h.sum_probs is None else h for i, h in enumerate(hits)]
-        res = super().get_templates(query_sequence, ordered)
+        res = super().get_templates(query_sequence, ordered, query_pdb_code, query_release_date)
         feats = dict(res.features)
         feats["template_sum_probs"] = np.zeros_like(feats["template_sum_probs"])
         return TemplateSearchResult(features=feats, errors=res.errors, warnings=res.warnings)

@@ -305,6 +305,74 @@ def find_structural_violations(batch, atom14_pred_positions, violation_tolerance
     }
 
 
+def find_structural_violations_np(batch, atom14_pred_positions, config):
+    """``find_structural_violations`` on numpy inputs, numpy out (the relaxation loop works in numpy)."""
+    import numpy as np
+    as_t = lambda x: torch.as_tensor(x)
+    out = find_structural_violations(tree_map(as_t, dict(batch), np.ndarray), as_t(atom14_pred_positions), **config)
+    return tensor_tree_map(lambda t: t.detach().cpu().numpy(), out)
+
+
+def extreme_ca_ca_distance_violations(pred_atom_positions, pred_atom_mask, residue_index, max_angstrom_tolerance=1.5, eps=1e-6):
+    """Fraction of consecutive residue pairs (no chain break between them, both CA present) whose CA-CA distance is more
+    than ``max_angstrom_tolerance`` above the ideal 3.80 A; positions are atom14 / atom37 (CA is slot 1 in both)."""
+    this_ca, next_ca = pred_atom_positions[..., :-1, 1, :], pred_atom_positions[..., 1:, 1, :]
+    pair_mask = pred_atom_mask[..., :-1, 1] * pred_atom_mask[..., 1:, 1]
+    pair_mask = pair_mask * ((residue_index[..., 1:] - residue_index[..., :-1]) == 1.0).to(pair_mask.dtype)
+    dist = torch.sqrt(eps + torch.sum((this_ca - next_ca) ** 2, dim=-1))
+    return masked_mean(pair_mask, ((dist - rc.ca_ca) > max_angstrom_tolerance).to(pair_mask.dtype), -1)
+
+
+def compute_violation_metrics(batch, atom14_pred_positions, violations):
+    """Per-structure summaries of ``find_structural_violations``: fractions of residues with a broken peptide bond, a
+    clash, a within-residue violation or any of them, and the fraction of stretched CA-CA steps."""
+    between, within = violations["between_residues"], violations["within_residues"]
+    seq_mask = batch["seq_mask"]
+    return {
+        "violations_extreme_ca_ca_distance": extreme_ca_ca_distance_violations(atom14_pred_positions, batch["atom14_atom_exists"],
+                                                                                batch["residue_index"]),
+        "violations_between_residue_bond": masked_mean(seq_mask, between["connections_per_residue_violation_mask"], dim=-1),
+        "violations_between_residue_clash": masked_mean(seq_mask, torch.max(between["clashes_per_atom_clash_mask"], dim=-1)[0], dim=-1),
+        "violations_within_residue": masked_mean(seq_mask, torch.max(within["per_atom_violations"], dim=-1)[0], dim=-1),
+        "violations_per_residue": masked_mean(seq_mask, violations["total_per_residue_violations_mask"], dim=-1),
+    }
+
+
+def compute_violation_metrics_np(batch, atom14_pred_positions, violations):
+    import numpy as np
+    as_t = lambda x: torch.as_tensor(x)
+    out = compute_violation_metrics(tree_map(as_t, dict(batch), np.ndarray), as_t(atom14_pred_positions),
+                                    tree_map(as_t, violations, np.ndarray))
+    return {k: v.detach().cpu().numpy() for k, v in out.items()}
+
+
+def torsion_angle_loss(a, a_gt, a_alt_gt):
+    """Algorithm 27 on raw angle predictions ``a [*, N, 7, 2]``: squared chord distance of the normalised prediction to
+    the nearer of the true and the pi-shifted ("alt") angle, plus 0.02 x the deviation of the raw norm from 1."""
+    norm = torch.norm(a, dim=-1)
+    unit = a / norm.unsqueeze(-1)
+    d_gt = torch.sum((unit - a_gt) ** 2, dim=-1)
+    d_alt = torch.sum((unit - a_alt_gt) ** 2, dim=-1)
+    return torch.mean(torch.minimum(d_gt, d_alt), dim=(-1, -2)) + 0.02 * torch.mean(torch.abs(norm - 1), dim=(-1, -2))
+
+
+def compute_drmsd(structure_1, structure_2, mask=None):
+    """Distance-matrix RMSD of two point sets ``[*, N, 3]``: root mean square difference of all pairwise distances."""
+    if mask is not None:
+        structure_1 = structure_1 * mask[..., None]
+        structure_2 = structure_2 * mask[..., None]
+    d1 = torch.cdist(structure_1, structure_1)
+    d2 = torch.cdist(structure_2, structure_2)
+    sq = torch.sum((d1 - d2) ** 2, dim=(-1, -2))
+    n = d1.shape[-1] if mask is None else torch.sum(mask, dim=-1)
+    n = torch.as_tensor(n, dtype=sq.dtype, device=sq.device)
+    return torch.sqrt(torch.where(n > 1, sq / (n * (n - 1)).clamp(min=1), torch.zeros_like(sq)))
+
+
+def compute_drmsd_np(structure_1, structure_2, mask=None):
+    return compute_drmsd(torch.as_tensor(structure_1), torch.as_tensor(structure_2), None if mask is None else torch.as_tensor(mask))
+
+
 def violation_loss(violations, atom14_atom_exists, eps=1e-6, **kwargs):
     num_atoms = torch.sum(atom14_atom_exists)
     l_clash = torch.sum(violations["between_residues"]["clashes_per_atom_loss_sum"] + violations["within_residues"]["per_atom_loss_sum"])

@@ -90,6 +90,27 @@ def _finish_gather(out, work, dim):
     return body.reshape(shape)
 
 
+class GatherAsyncOpp(torch.autograd.Function):
+    """The layout step that completes an asynchronous gather along dim 2 in the reference
+    (fastfold/distributed/comm_async.py:98-110): the P received slabs, stacked along dim 1 as ``[n, (x h), w, c]``, are
+    laid side by side along dim 2 -> ``[n, h, (x w), c]``.  Backward is the exact inverse rearrangement (the reference
+    resizes the gradient buffer in place instead).  ``gather_async_opp`` of this package does this step itself; the
+    class is kept for programs that call it directly."""
+
+    @staticmethod
+    def forward(ctx, input):
+        x = get_world_size()
+        n, xh, w, c = input.shape
+        ctx.x = x
+        return input.reshape(n, x, xh // x, w, c).permute(0, 2, 1, 3, 4).reshape(n, xh // x, x * w, c)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x = ctx.x
+        n, h, xw, c = grad_output.shape
+        return grad_output.reshape(n, h, x, xw // x, c).permute(0, 2, 1, 3, 4).reshape(n, x * h, xw // x, c)
+
+
 class GatherAsync(torch.autograd.Function):
     """Launch + wait fused in one autograd node; forward returns the gathered tensor.
 

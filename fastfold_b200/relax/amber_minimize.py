@@ -153,6 +153,40 @@ def _clean_for_openmm(prot: protein.Protein) -> str:
     return cleanup.fix_pdb_string(pdb_str)
 
 
+def will_restrain(atom, rset: str) -> bool:
+    """Whether the harmonic position restraint of set ``rset`` (``non_hydrogen`` / ``c_alpha``) applies to an OpenMM atom."""
+    if rset == "non_hydrogen":
+        return atom.element.name != "hydrogen"
+    if rset == "c_alpha":
+        return atom.name == "CA"
+    raise ValueError("unknown restraint set %r" % rset)
+
+
+def clean_protein(prot: protein.Protein, checks: bool = True) -> str:
+    """PDB text of ``prot`` ready for the force field: the atom mask must be the ideal one for the sequence (every heavy
+    atom present), then pdbfixer adds hydrogens / fixes residues (OpenMM back end only)."""
+    if checks:
+        ideal = protein.ideal_atom_mask(prot)
+        utils.assert_equal_nonterminal_atom_types(np.asarray(prot.atom_mask), ideal)
+    return _clean_for_openmm(prot)
+
+
+def get_violation_metrics(prot: protein.Protein, device="cpu") -> Dict[str, Any]:
+    """Violations of ``prot`` with the indices of the violating residues (what the outer relaxation loop frees next)."""
+    v = find_violations(prot, device)
+    idx = np.flatnonzero(v["per_residue_mask"])
+    metrics = dict(v)
+    metrics.update({"residue_violations": idx, "num_residue_violations": len(idx), "structural_violations": v})
+    return metrics
+
+
+def get_initial_energies(pdb_strs: Sequence[str], stiffness: float = 0.0, restraint_set: str = "non_hydrogen",
+                         exclude_residues: Optional[Sequence[int]] = None):
+    """Potential energy (kcal/mol) of each ready-to-minimise PDB string before any minimisation step (OpenMM back end)."""
+    return [_openmm_minimize(s_, max_iterations=1, tolerance=2.39, stiffness=stiffness, restraint_set=restraint_set,
+                             exclude_residues=list(exclude_residues or []), use_gpu=False)["einit"] for s_ in pdb_strs]
+
+
 # ---------------------------------------------------------------------------
 # pipeline
 # ---------------------------------------------------------------------------

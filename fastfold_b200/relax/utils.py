@@ -53,3 +53,22 @@ def assert_equal_nonterminal_atom_types(atom_mask: np.ndarray, ref_atom_mask: np
     keep = np.ones_like(atom_mask, dtype=bool)
     keep[..., oxt] = False
     np.testing.assert_almost_equal(ref_atom_mask[keep], atom_mask[keep])
+
+
+def mask_mean_np(mask, value, axis=None, drop_mask_channel=False, eps=1e-10):
+    """Mean of ``value`` over ``axis`` (all axes when None) counting only entries where ``mask`` is set; mask axes of
+    extent 1 broadcast."""
+    mask, value = np.asarray(mask), np.asarray(value)
+    if drop_mask_channel:
+        mask = mask[..., 0]
+    assert mask.ndim == value.ndim
+    axes = list(range(mask.ndim)) if axis is None else ([axis] if np.isscalar(axis) else list(axis))
+    broadcast = 1.0
+    for a in axes:
+        if mask.shape[a] == 1:
+            broadcast *= value.shape[a]
+        else:
+            assert mask.shape[a] == value.shape[a]
+    axes = tuple(axes)
+    return np.sum(mask * value, axis=axes) / (np.sum(mask, axis=axes) * broadcast + eps)
+

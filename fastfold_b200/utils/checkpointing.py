@@ -97,3 +97,18 @@ def checkpoint_blocks(blocks, args, blocks_per_ckpt):
         else:
             args = run(*args)
     return args
+
+
+def get_checkpoint_fn():
+    """``checkpoint(fn, *args)``: runs ``fn`` without saving its intermediates and recomputes it in backward (this
+    package's own autograd function, the one ``checkpoint_blocks`` uses).  Returns what ``fn`` returns."""
+    def checkpoint(fn, *args):
+        single = []
+
+        def block(*a):
+            out = fn(*a)
+            single.append(not isinstance(out, tuple))
+            return out
+        out = checkpoint_blocks([block], tuple(args), blocks_per_ckpt=1)
+        return out[0] if single and single[-1] else out
+    return checkpoint

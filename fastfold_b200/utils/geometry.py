@@ -64,6 +64,18 @@ class Vec3Array:
     def to_tensor(self):
         return torch.stack([self.x, self.y, self.z], dim=-1)
 
+    def clone(self):
+        return self.map_tensor_fn(torch.clone)
+
+    def reshape(self, new_shape):
+        return self.map_tensor_fn(lambda t: t.reshape(new_shape))
+
+    def sum(self, dim: int):
+        return self.map_tensor_fn(lambda t: t.sum(dim=dim))
+
+    def unsqueeze(self, dim: int):
+        return self.map_tensor_fn(lambda t: t.unsqueeze(dim))
+
     @classmethod
     def from_array(cls, t):
         return cls(*torch.unbind(t, dim=-1))
@@ -72,6 +84,31 @@ class Vec3Array:
     def zeros(cls, shape, device="cpu", dtype=torch.float32):
         z = torch.zeros(shape, dtype=dtype, device=device)
         return cls(z, z.clone(), z.clone())
+
+    @classmethod
+    def cat(cls, vecs, dim: int):
+        return cls(torch.cat([v.x for v in vecs], dim=dim), torch.cat([v.y for v in vecs], dim=dim), torch.cat([v.z for v in vecs], dim=dim))
+
+
+def dot(vector1: Vec3Array, vector2: Vec3Array):
+    return vector1.dot(vector2)
+
+
+def cross(vector1: Vec3Array, vector2: Vec3Array) -> Vec3Array:
+    return vector1.cross(vector2)
+
+
+def norm(vector: Vec3Array, epsilon: float = 1e-6):
+    return vector.norm(epsilon)
+
+
+def normalized(vector: Vec3Array, epsilon: float = 1e-6) -> Vec3Array:
+    return vector.normalized(epsilon)
+
+
+def get_field_names(cls):
+    """Names of the tensor components of one of the struct-of-arrays classes, in declaration order."""
+    return [f.name for f in dataclasses.fields(cls)]
 
 
 def square_euclidean_distance(a: Vec3Array, b: Vec3Array, epsilon: float = 1e-6):
@@ -129,6 +166,22 @@ class Rot3Array:
         return torch.stack([torch.stack([self.xx, self.xy, self.xz], -1), torch.stack([self.yx, self.yy, self.yz], -1),
                             torch.stack([self.zx, self.zy, self.zz], -1)], dim=-2)
 
+    def map_tensor_fn(self, fn):
+        return Rot3Array(*(fn(getattr(self, f.name)) for f in dataclasses.fields(self)))
+
+    def unsqueeze(self, dim: int):
+        return self.map_tensor_fn(lambda t: t.unsqueeze(dim))
+
+    def reshape(self, new_shape):
+        return self.map_tensor_fn(lambda t: t.reshape(new_shape))
+
+    def stop_gradient(self):
+        return self.map_tensor_fn(lambda t: t.detach())
+
+    @classmethod
+    def cat(cls, rots, dim: int):
+        return cls(*(torch.cat([getattr(r, f.name) for r in rots], dim=dim) for f in dataclasses.fields(cls)))
+
     @classmethod
     def from_array(cls, t):
         r = [torch.unbind(row, dim=-1) for row in torch.unbind(t, dim=-2)]
@@ -184,6 +237,53 @@ class Rigid3Array:
     def scale_translation(self, factor):
         return Rigid3Array(self.rotation, self.translation * factor)
 
+    def map_tensor_fn(self, fn):
+        return Rigid3Array(self.rotation.map_tensor_fn(fn), self.translation.map_tensor_fn(fn))
+
+    def apply(self, point: torch.Tensor) -> Vec3Array:
+        """``apply_to_point`` for a plain ``[..., 3]`` tensor."""
+        return self.apply_to_point(Vec3Array.from_array(point))
+
+    def compose_rotation(self, other_rotation: Rot3Array):
+        return Rigid3Array(self.rotation @ other_rotation, self.translation)
+
+    def compose(self, other_rigid):
+        return self @ other_rigid
+
+    def unsqueeze(self, dim: int):
+        return self.map_tensor_fn(lambda t: t.unsqueeze(dim))
+
+    def reshape(self, new_shape):
+        return self.map_tensor_fn(lambda t: t.reshape(new_shape))
+
+    def stop_rot_gradient(self):
+        return Rigid3Array(self.rotation.stop_gradient(), self.translation)
+
+    @property
+    def dtype(self):
+        return self.rotation.xx.dtype
+
+    @property
+    def device(self):
+        return self.rotation.xx.device
+
+    def to_tensor(self) -> torch.Tensor:
+        """``[..., 3, 4]``: the rotation matrix with the translation as the fourth column."""
+        return torch.cat([self.rotation.to_tensor(), self.translation.to_tensor()[..., None]], dim=-1)
+
+    @classmethod
+    def from_array(cls, array):
+        """Inverse of ``to_tensor``."""
+        return cls(Rot3Array.from_array(array[..., :3]), Vec3Array.from_array(array[..., 3]))
+
+    @classmethod
+    def from_array4x4(cls, array):
+        return cls.from_tensor_4x4(array)
+
+    @classmethod
+    def cat(cls, rigids, dim: int):
+        return cls(Rot3Array.cat([r.rotation for r in rigids], dim), Vec3Array.cat([r.translation for r in rigids], dim))
+
     def to_tensor_4x4(self):
         rot = self.rotation.to_tensor()
         top = torch.cat([rot, self.translation.to_tensor()[..., None]], dim=-1)
@@ -219,3 +319,72 @@ class QuatRigid(torch.nn.Module):
             qx, qy, qz = out[:3]
             qw = torch.ones_like(qx)
         return Rigid3Array(Rot3Array.from_quaternion(qw, qx, qy, qz, normalize=True), Vec3Array(*out[-3:]))
+
+
+# ---------------------------------------------------------------------------
+# assertions for tests (fastfold/utils/geometry/test_utils.py)
+# ---------------------------------------------------------------------------
+def _np(t):
+    return t.detach().cpu().numpy() if torch.is_tensor(t) else t
+
+
+def assert_rotation_matrix_equal(matrix1: Rot3Array, matrix2: Rot3Array):
+    import numpy as np
+    for f in dataclasses.fields(Rot3Array):
+        np.testing.assert_array_equal(_np(getattr(matrix1, f.name)), _np(getattr(matrix2, f.name)))
+
+
+def assert_rotation_matrix_close(mat1: Rot3Array, mat2: Rot3Array, atol=1e-6):
+    import numpy as np
+    np.testing.assert_allclose(_np(mat1.to_tensor()), _np(mat2.to_tensor()), atol=atol)
+
+
+def assert_array_equal_to_rotation_matrix(array, matrix: Rot3Array):
+    import numpy as np
+    np.testing.assert_array_equal(_np(matrix.to_tensor()), _np(array))
+
+
+def assert_array_close_to_rotation_matrix(array, matrix: Rot3Array, atol=1e-6):
+    import numpy as np
+    np.testing.assert_allclose(_np(matrix.to_tensor()), _np(array), atol=atol)
+
+
+def assert_vectors_equal(vec1: Vec3Array, vec2: Vec3Array):
+    import numpy as np
+    for a, b in zip(vec1, vec2):
+        np.testing.assert_array_equal(_np(a), _np(b))
+
+
+def assert_vectors_close(vec1: Vec3Array, vec2: Vec3Array, atol=1e-6):
+    import numpy as np
+    for a, b in zip(vec1, vec2):
+        np.testing.assert_allclose(_np(a), _np(b), atol=atol)
+
+
+def assert_array_close_to_vector(array, vec: Vec3Array, atol=1e-6):
+    import numpy as np
+    np.testing.assert_allclose(_np(vec.to_tensor()), _np(array), atol=atol)
+
+
+def assert_array_equal_to_vector(array, vec: Vec3Array):
+    import numpy as np
+    np.testing.assert_array_equal(_np(vec.to_tensor()), _np(array))
+
+
+def assert_rigid_equal_to_rigid(rigid1: Rigid3Array, rigid2: Rigid3Array):
+    assert_rot_trans_equal_to_rigid(rigid1.rotation, rigid1.translation, rigid2)
+
+
+def assert_rigid_close_to_rigid(rigid1: Rigid3Array, rigid2: Rigid3Array, atol=1e-6):
+    assert_rot_trans_close_to_rigid(rigid1.rotation, rigid1.translation, rigid2, atol)
+
+
+def assert_rot_trans_equal_to_rigid(rot: Rot3Array, trans: Vec3Array, rigid: Rigid3Array):
+    assert_rotation_matrix_equal(rot, rigid.rotation)
+    assert_vectors_equal(trans, rigid.translation)
+
+
+def assert_rot_trans_close_to_rigid(rot: Rot3Array, trans: Vec3Array, rigid: Rigid3Array, atol=1e-6):
+    assert_rotation_matrix_close(rot, rigid.rotation, atol)
+    assert_vectors_close(trans, rigid.translation, atol)
+

@@ -315,6 +315,45 @@ def flat_translation(model, version="model_1"):
     return {PREFIX + k: v for k, v in _flatten(translation_tree(model, version)).items()}
 
 
+# ---------------------------------------------------------------------------
+# The reference's vocabulary for the same table (fastfold/utils/import_weights.py:25-70): a ``Param`` names the target
+# tensor(s), how the archive's array maps onto them (``ParamType``) and whether the archive entry stacks one array per block.
+# ---------------------------------------------------------------------------
+import enum
+
+
+class ParamType(enum.Enum):
+    LinearWeight = "lin_w"
+    LinearWeightMHA = "mha_w"
+    LinearMHAOutputWeight = "mha_o"
+    LinearBiasMHA = "mha_b"
+    LinearWeightOPM = "opm_w"
+    LinearWeightMultimer = "mm_w"
+    LinearBiasMultimer = "mm_b"
+    LinearWeightSwapped = "lin_w_swap"
+    OtherSwapped = "plain_swap"
+    Other = "plain"
+
+
+class Param:
+    """``param``: the model tensor, or the list of per-block tensors of a stacked entry; ``param_type``; ``stacked``."""
+
+    def __init__(self, param, param_type=ParamType.Other, stacked=False, meta=None):
+        self.param, self.param_type, self.stacked, self.meta = param, param_type, stacked, meta
+
+    def __repr__(self):
+        return "Param(%s, stacked=%s)" % (self.param_type.name, self.stacked)
+
+
+def get_translation_dict(model, version="model_1"):
+    """``{archive key: Param}`` for every array of an AlphaFold parameter archive that ``model`` consumes."""
+    out = {}
+    for key, leaf in flat_translation(model, version).items():
+        stacked = len(leaf.tensors) > 1 or any(tag in key for tag in _STACKED)
+        out[key] = Param(leaf.tensors if stacked else leaf.tensors[0], ParamType(leaf.kind), stacked, leaf.meta)
+    return out
+
+
 def import_jax_weights_(model, npz_path, version="model_1"):
     data = np.load(npz_path) if isinstance(npz_path, str) else npz_path
     flat = flat_translation(model, version)

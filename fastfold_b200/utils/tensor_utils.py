@@ -53,6 +53,11 @@ def dict_multimap(fn, dicts):
     return out
 
 
+def dict_map(fn, dic, leaf_type):
+    """``tree_map`` over the values of a (possibly nested) dict."""
+    return {k: (dict_map(fn, v, leaf_type) if type(v) is dict else tree_map(fn, v, leaf_type)) for k, v in dic.items()}
+
+
 def tree_map(fn, tree, leaf_type):
     if isinstance(tree, dict):
         return {k: tree_map(fn, v, leaf_type) for k, v in tree.items()}

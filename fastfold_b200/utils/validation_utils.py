@@ -65,3 +65,14 @@ def validation_metrics(outputs, batch, superimposition_metrics=False):
         metrics["gdt_ts"] = torch.mean(gdt_ts(sup, gt_ca, mask_ca))
         metrics["gdt_ha"] = torch.mean(gdt_ha(sup, gt_ca, mask_ca))
     return metrics
+
+
+def drmsd_np(structure_1, structure_2, mask=None):
+    """``drmsd`` on numpy inputs (returns a tensor, like the reference's helper of that name)."""
+    return drmsd(torch.as_tensor(structure_1), torch.as_tensor(structure_2), None if mask is None else torch.as_tensor(mask))
+
+
+def compute_validation_metrics(batch, outputs, superimposition_metrics=False):
+    """The reference's argument order (``batch`` first) for ``validation_metrics``."""
+    return validation_metrics(outputs, batch, superimposition_metrics=superimposition_metrics)
+
