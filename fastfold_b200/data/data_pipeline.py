@@ -245,8 +245,18 @@ def _process_mmcif(self, mmcif, alignment_dir=None, chain_id=None):
     return feats
 
 
+def _process_core(self, core_path, alignment_dir=None):
+    """Features + backbone ground truth of a ProteinNet ``.core`` record (fastfold/data/data_pipeline.py:1049-1079)."""
+    from ..common import protein
+    prot = protein.from_proteinnet_string(open(core_path).read())
+    seq = "".join(rc.restypes_with_x[int(a)] for a in prot.aatype)
+    tag = os.path.splitext(os.path.basename(core_path))[0].upper()
+    return _process_structure(self, seq, tag, alignment_dir, prot.atom_positions, prot.atom_mask, 0.0, False)
+
+
 DataPipeline.process_pdb = _process_pdb
 DataPipeline.process_mmcif = _process_mmcif
+DataPipeline.process_core = _process_core
 
 
 def np_to_tensor_dict(np_example, features):

@@ -62,6 +62,13 @@ class TemplatePairBlock(nn.Module):
         z = self.TriangleMultiplicationIncoming(z, mask_col, dm)
         return col_to_row(z)
 
+    def inplace(self, z, mask, chunk_size=None, _mask_trans=True, _drop=None):
+        """``z`` is a one-element list whose tensor is updated through the in-place residual epilogues."""
+        from . import ops as fops
+        with fops.inplace_scope():
+            z[0] = self.forward(z[0], mask, chunk_size, _mask_trans, _drop)
+        return z
+
     def forward(self, z, mask, chunk_size=None, _mask_trans=True, _drop=None):
         """``z [*, N_templ, N, N, c_t]`` (full on the first block, row shards afterwards), ``mask [*, N_templ, N, N]``.
         ``_drop``: one dict of axis-shared dropout masks per template (``draw_block_dropout``), drawn by the stack outside

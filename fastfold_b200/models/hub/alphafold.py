@@ -152,6 +152,12 @@ class AlphaFold(nn.Module):
         x_prev = outputs["final_atom_positions"]
         return outputs, m_1_prev, z_prev, x_prev
 
+    def embed_templates(self, batch, z, pair_mask, templ_dim):
+        """Template embeddings for ``batch`` (the ``template_*`` features): ``{"template_pair_embedding": [*, N, N, c_z],
+        "template_angle_embedding": ...}``.  The work is done by ``self.template_embedder`` (OpenFold-layout or, after
+        ``inject_fastnn``, the fast one); the method keeps the entry point of fastfold/model/hub/alphafold.py:107-171."""
+        return self.template_embedder(batch, z, pair_mask, templ_dim, self.globals.chunk_size)
+
     def _set_ckpt(self, enabled):
         bpc = self.globals.blocks_per_ckpt if enabled else None
         for mod in (self.template_embedder.template_pair_stack if hasattr(self.template_embedder, "template_pair_stack") else None, self.evoformer):

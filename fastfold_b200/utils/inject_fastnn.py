@@ -147,6 +147,9 @@ def inject_extra_msa(model):
     model.extra_msa_stack = fast
 
 
+inject_extramsa = inject_extra_msa          # the reference's spelling (fastfold/utils/inject_fastnn.py:341)
+
+
 def copy_template_pair_block(fast, ori):
     _copy_tri_att(fast.TriangleAttentionStartingNode, ori.tri_att_start)
     _copy_tri_att(fast.TriangleAttentionEndingNode, ori.tri_att_end)

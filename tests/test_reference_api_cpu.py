@@ -112,6 +112,16 @@ def test_data_pipeline_helpers(tmp_path):
     assert out.read_text() == "STO 7"
 
 
+def test_process_core_record(tmp_path):
+    rec = "[ID]\n1abc\n[PRIMARY]\nACDEF\n[TERTIARY]\n" + " ".join(str(100 * i) for i in range(15)) + "\n" + " ".join("1" for _ in range(15)) + \
+          "\n" + " ".join("0" for _ in range(15)) + "\n[MASK]\n++-++\n"
+    path = tmp_path / "1abc_1_a.core"
+    path.write_text(rec)
+    feats = dp.DataPipeline().process_core(str(path))
+    assert feats["aatype"].shape == (5, 21) and feats["all_atom_positions"].shape == (5, 37, 3)
+    assert feats["all_atom_mask"][:, 1].tolist() == [1.0, 1.0, 0.0, 1.0, 1.0] and feats["msa"].shape == (1, 5)
+
+
 def test_parsers_and_pairing_helpers():
     meta = parsers.parse_hmmsearch_description(">4pqx_A/2-217 [subseq from] mol:protein length:217  Free text")
     assert (meta.pdb_id, meta.chain, meta.start, meta.end, meta.length, meta.text) == ("4pqx", "A", 2, 217, 217, "Free text")
