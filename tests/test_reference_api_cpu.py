@@ -243,3 +243,34 @@ def test_misc_utils_and_import_paths():
     from fastfold.utils.geometry.rigid_matrix_vector import Rigid3Array          # noqa: F401
     from fastfold.model.nn.triangular_multiplicative_update import TriangleMultiplicationIncoming          # noqa: F401
     from fastfold.utils.import_weights import Param, ParamType, get_translation_dict          # noqa: F401
+
+
+def test_template_features_flow_into_the_model():
+    """Raw example with two templates -> feature pipeline -> full model (OpenFold layout and injected fast modules)."""
+    from fastfold_b200.models.hub import AlphaFold
+    from fastfold_b200.utils.inject_fastnn import inject_fastnn
+    cfg = model_config("model_1")
+    cfg.model.evoformer_stack.no_blocks = 1
+    cfg.model.extra_msa.extra_msa_stack.no_blocks = 1
+    cfg.model.template.template_pair_stack.no_blocks = 1
+    cfg.model.structure_module.no_blocks = 1
+    cfg.data.common.max_recycling_iters = 0
+    cfg.data.predict.max_msa_clusters = 8
+    cfg.data.predict.max_extra_msa = 16
+    feats = dp.FeaturePipeline(cfg.data).process_features(_raw_example(2), mode="predict", seed=1)
+    assert feats["template_mask"][:, 0].tolist() == [1.0, 1.0, 0.0, 0.0]
+    torch.manual_seed(0)
+    model = AlphaFold(cfg).eval()
+    with torch.no_grad():
+        for p in model.parameters():          # the zero-initialised output layers would hide the template path
+            if p.abs().sum() == 0:
+                p.normal_(0, 0.02)
+        out = model(feats)
+        no_templ = dict(feats)
+        no_templ["template_mask"] = torch.zeros_like(feats["template_mask"])
+        out_masked = model(no_templ)
+        fast = inject_fastnn(model)
+        out_fast = fast(feats)
+    assert torch.isfinite(out["final_atom_positions"]).all()
+    assert (out["pair"] - out_masked["pair"]).abs().max() > 1e-4          # the templates do change the pair representation
+    assert (out_fast["pair"] - out["pair"]).abs().max() < 5e-4
