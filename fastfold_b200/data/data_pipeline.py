@@ -194,17 +194,19 @@ class DataPipeline:
             raise ValueError("More than one input sequence found in %s." % fasta_path)
         return self.process_sequence(seqs[0], descs[0], alignment_dir)
 
-    def process_sequence(self, sequence, description="query", alignment_dir=None) -> FeatureDict:
+    def process_sequence(self, sequence, description="query", alignment_dir=None, query_pdb_code=None, query_release_date=None) -> FeatureDict:
+        """``query_pdb_code`` / ``query_release_date``: identity of the target when it is itself a PDB entry (training),
+        so that the entry and anything released within 60 days before it are not used as templates."""
         n = len(sequence)
         feats = dict(make_sequence_features(sequence, description, n))
         msas, dels = self._read_alignments(alignment_dir, sequence)
         feats.update(make_msa_features(msas, dels))
-        templ = None
+        hits = []
         if self.template_featurizer is not None and alignment_dir:
             hhr = os.path.join(alignment_dir, "pdb70_hits.hhr")
             if os.path.exists(hhr):
-                templ = self.template_featurizer.get_templates(sequence, parsers.parse_hhr(open(hhr).read())).features
-        feats.update(templ if templ is not None else empty_template_features(n))
+                hits = parsers.parse_hhr(open(hhr).read())
+        feats.update(make_template_features(sequence, hits, self.template_featurizer, query_pdb_code, query_release_date))
         return feats
 
 
@@ -213,8 +215,9 @@ def _ground_truth_features(positions, mask, resolution=1.0, is_distillation=Fals
             "resolution": np.array(resolution, np.float32), "is_distillation": np.array(1.0 if is_distillation else 0.0, np.float32)}
 
 
-def _process_structure(self, sequence, description, alignment_dir, positions, mask, resolution, is_distillation):
-    feats = dict(self.process_sequence(sequence, description, alignment_dir))
+def _process_structure(self, sequence, description, alignment_dir, positions, mask, resolution, is_distillation, query_pdb_code=None,
+                       query_release_date=None):
+    feats = dict(self.process_sequence(sequence, description, alignment_dir, query_pdb_code, query_release_date))
     feats.update(_ground_truth_features(positions, mask, resolution, is_distillation))
     return feats
 
@@ -239,8 +242,9 @@ def _process_mmcif(self, mmcif, alignment_dir=None, chain_id=None):
     seq = mmcif.chain_to_seqres[chain_id]
     pos, mask = mmcif_parsing.get_atom_coords(mmcif, chain_id)
     res = mmcif.header.get("resolution", 0.0) if isinstance(mmcif.header, dict) else getattr(mmcif.header, "resolution", 0.0)
-    feats = _process_structure(self, seq, "%s_%s" % (mmcif.file_id, chain_id), alignment_dir, pos, mask, float(res or 0.0), False)
     date = mmcif.header.get("release_date", "") if isinstance(mmcif.header, dict) else getattr(mmcif.header, "release_date", "")
+    feats = _process_structure(self, seq, "%s_%s" % (mmcif.file_id, chain_id), alignment_dir, pos, mask, float(res or 0.0), False,
+                               query_pdb_code=mmcif.file_id, query_release_date=str(date) if date else None)
     feats["release_date"] = np.array([str(date).encode()], dtype=object)
     return feats
 

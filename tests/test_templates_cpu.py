@@ -74,6 +74,13 @@ def test_template_featurizer(tmp_path):
     assert np.allclose(feats["template_all_atom_positions"][0, 2 + 2, ca], [3.8 * 2 + 0.1, 2.0, -1.5], atol=1e-3)
     assert feats["template_sequence"][0].decode() == "--" + SEQ + "--"
     assert abs(feats["template_sum_probs"][0, 0] - 12.0) < 1e-6
+    # training on PDB entries: the query's own entry is never its template, and the date cutoff follows the query
+    assert f.get_templates(query, [hit, late], query_pdb_code="1ABC").features["template_aatype"].shape[0] == 0
+    assert f.get_templates(query, [hit, late], query_release_date="1999-06-01").features["template_aatype"].shape[0] == 0    # 60-day margin
+    assert f.get_templates(query, [hit, late], query_release_date="1999-09-01").features["template_aatype"].shape[0] == 1
+    assert f.get_templates(query, [hit, late]).features["template_aatype"].shape[0] == 1                                        # cutoff restored
+    from fastfold_b200.data.data_pipeline import make_template_features
+    assert make_template_features(query, {"pdb70_hits.hhr": [hit, late]}, f, query_pdb_code="1abc")["template_aatype"].shape == (0, len(query), 22)
 
 
 def test_prefilter_rules():
