@@ -279,10 +279,11 @@ class FeaturePipeline:
         from . import feature_pipeline as fp
         cfg = copy.deepcopy(self.config)
         raw = dict(raw_features)
-        # templates take part only when the configuration uses them AND the example has at least one hit; the caller
-        # switches the model's template stack off when no template features come back
+        # prediction: templates take part only when the configuration uses them AND the example has at least one hit (the
+        # caller switches the model's template stack off when no template features come back).  Training / evaluation
+        # keep the static shapes: an example without hits gets zero-padded template features with ``template_mask`` 0.
         t = raw.get("template_aatype")
-        has_templates = bool(cfg.common.use_templates) and t is not None and np.asarray(t).shape[0] > 0
+        has_templates = bool(cfg.common.use_templates) and t is not None and (np.asarray(t).shape[0] > 0 or mode != "predict")
         cfg.common.use_templates = has_templates
         feats = fp.np_example_to_features(raw, cfg, mode, seed=seed)
         if not has_templates:

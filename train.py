@@ -46,6 +46,21 @@ def parse():
     p.add_argument("--val_data_dir", type=str, default=None)
     p.add_argument("--val_alignment_dir", type=str, default=None)
     p.add_argument("--template_mmcif_dir", type=str, default=None)
+    p.add_argument("--train_chain_data_cache_path", type=str, default=None, help="chain-level cache (resolution, cluster size, sequence) "
+                   "for the stochastic training filters")
+    p.add_argument("--distillation_data_dir", type=str, default=None, help="directory of self-distillation PDB files")
+    p.add_argument("--distillation_alignment_dir", type=str, default=None)
+    p.add_argument("--distillation_chain_data_cache_path", type=str, default=None)
+    p.add_argument("--kalign_binary_path", type=str, default="/usr/bin/kalign")
+    p.add_argument("--train_filter_path", type=str, default=None, help="text file with the names of the training examples to use, one per line")
+    p.add_argument("--distillation_filter_path", type=str, default=None, help="as --train_filter_path, for the distillation set")
+    p.add_argument("--obsolete_pdbs_file_path", type=str, default=None)
+    p.add_argument("--template_release_dates_cache_path", type=str, default=None)
+    p.add_argument("--_alignment_index_path", type=str, default=None)
+    p.add_argument("--_distillation_structure_index_path", type=str, default=None)
+    p.add_argument("--distillation_alignment_index_path", type=str, default=None)
+    p.add_argument("--plain_dataset", default=False, action="store_true", help="read --train_data_dir file by file in order "
+                   "(no stochastic filtering, no distillation mix, no template search) instead of the filtered mixture dataset")
     p.add_argument("--max_template_date", type=str, default="2021-10-10")
     p.add_argument("--n_res", type=int, default=None, help="(synthetic) crop size; default from the preset")
     p.add_argument("--n_seq", type=int, default=None)
@@ -57,6 +72,24 @@ def parse():
     p.add_argument("--val_interval", type=int, default=1, help="epochs between validation passes")
     p.add_argument("--val_epoch_len", type=int, default=2, help="(synthetic) validation samples per pass; 0 disables")
     return p.parse_args()
+
+
+class _LoaderDataset:
+    """``len`` / ``get(epoch, i)`` over an ``OpenFoldDataLoader``: a new pass over the loader (and a re-draw of the
+    filtered training mixture) whenever the epoch changes."""
+
+    def __init__(self, loader):
+        self.loader, self._it, self._epoch = loader, None, None
+
+    def __len__(self):
+        return len(self.loader)
+
+    def get(self, epoch, i):
+        if self._it is None or epoch != self._epoch or i == 0:
+            if self._epoch is not None and epoch != self._epoch and hasattr(self.loader.dataset, "reroll"):
+                self.loader.dataset.reroll()
+            self._it, self._epoch = iter(self.loader), epoch
+        return dict(next(self._it))
 
 
 def main():
@@ -84,6 +117,13 @@ def main():
     config = model_config(args.config_preset, train=True)
     if args.blocks:
         config.model.evoformer_stack.no_blocks = args.blocks
+    for mode_cfg in (config.data.train, config.data.eval):          # the size overrides apply to real data as well
+        if args.n_res:
+            mode_cfg.crop_size = args.n_res
+        if args.n_seq:
+            mode_cfg.max_msa_clusters = args.n_seq
+        if args.n_extra:
+            mode_cfg.max_extra_msa = args.n_extra
     model = inject_fastnn(AlphaFold(config))
     model = model.to(device=device, dtype=torch.bfloat16 if cuda else torch.float32).train()
     criterion = AlphaFoldLoss(config.loss)
@@ -95,10 +135,27 @@ def main():
         dataset = SyntheticDataset(n_res, n_seq, n_extra, n_recycle=config.data.common.max_recycling_iters if args.recycles is None else args.recycles,
                                    length=args.train_epoch_len, seed=args.seed, dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size(),
                                    n_templ=tc.max_templates if config.model.template.enabled else 0, uniform_recycling=args.recycles is None)
-    else:
+    elif args.plain_dataset:
         from fastfold_b200.data.data_modules import StructureDataset
         dataset = StructureDataset(args.train_data_dir, args.train_alignment_dir, config.data, mode="train", seed=args.seed,
                                    dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size())
+    else:
+        # the reference's data path (train.py:177-203): filtered mixture of PDB and distillation chains, template search
+        # with the date / identity filters, per-batch clamping and recycling draws, one share of the epoch per DP replica
+        from fastfold_b200.data.data_modules import SetupTrainDataset, TrainDataLoader
+        train_set, val_set = SetupTrainDataset(
+            config=config.data, template_mmcif_dir=args.template_mmcif_dir, max_template_date=args.max_template_date,
+            train_data_dir=args.train_data_dir, train_alignment_dir=args.train_alignment_dir,
+            train_chain_data_cache_path=args.train_chain_data_cache_path, distillation_data_dir=args.distillation_data_dir,
+            distillation_alignment_dir=args.distillation_alignment_dir,
+            distillation_chain_data_cache_path=args.distillation_chain_data_cache_path, val_data_dir=args.val_data_dir,
+            val_alignment_dir=args.val_alignment_dir, kalign_binary_path=args.kalign_binary_path, train_mapping_path=args.train_filter_path,
+            distillation_mapping_path=args.distillation_filter_path, obsolete_pdbs_file_path=args.obsolete_pdbs_file_path,
+            template_release_dates_cache_path=args.template_release_dates_cache_path, train_epoch_len=args.train_epoch_len,
+            _alignment_index_path=args._alignment_index_path)
+        train_loader, val_loader = TrainDataLoader(config=config.data, train_dataset=train_set, test_dataset=val_set, batch_seed=args.seed)
+        dataset = _LoaderDataset(train_loader)
+        loader_val_dataset = _LoaderDataset(val_loader) if val_loader is not None else None
 
     def loss_fn(mod, *tensors):
         batch = dict(zip(loss_fn.keys, tensors))
@@ -124,7 +181,9 @@ def main():
         log.info("resumed from %s at step %d (epoch %d)", args.resume, trainer.step_count, start_epoch)
 
     val_dataset = None
-    if args.val_data_dir:
+    if args.val_data_dir and not args.synthetic and not args.plain_dataset and args.train_data_dir:
+        val_dataset = loader_val_dataset
+    elif args.val_data_dir:
         from fastfold_b200.data.data_modules import StructureDataset
         val_dataset = StructureDataset(args.val_data_dir, args.val_alignment_dir, config.data, mode="eval", seed=args.seed,
                                        dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size())
