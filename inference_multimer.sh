@@ -1,0 +1,19 @@
+# see inference.sh for the optional flags (--gpus, --enable_workflow, --use_precomputed_alignments, --chunk_size, --inplace)
+
+python inference.py target.fasta data/pdb_mmcif/mmcif_files \
+    --output_dir ./ \
+    --gpus 1 \
+    --uniref90_database_path data/uniref90/uniref90.fasta \
+    --mgnify_database_path data/mgnify/mgy_clusters_2022_05.fa \
+    --pdb70_database_path data/pdb70/pdb70 \
+    --pdb_seqres_database_path data/pdb_seqres/pdb_seqres.txt \
+    --uniprot_database_path data/uniprot/uniprot.fasta \
+    --uniclust30_database_path data/uniref30/UniRef30_2021_03 \
+    --bfd_database_path data/bfd/bfd_metaclust_clu_complete_id30_c90_final_seq.sorted_opt \
+    --jackhmmer_binary_path `which jackhmmer` \
+    --hhblits_binary_path `which hhblits` \
+    --hhsearch_binary_path `which hhsearch` \
+    --kalign_binary_path `which kalign` \
+    --model_preset multimer \
+    --param_path data/params/params_model_1_multimer_v3.npz \
+    --model_name model_1_multimer
