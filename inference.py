@@ -24,6 +24,8 @@ def add_data_args(parser):
     for name in ("uniref90_database_path", "mgnify_database_path", "pdb70_database_path", "uniclust30_database_path", "bfd_database_path",
                  "uniprot_database_path", "pdb_seqres_database_path"):
         parser.add_argument("--" + name, type=str, default=None)
+    # UniRef30 is the successor of UniClust30 and is searched the same way (hhblits); either flag names the database
+    parser.add_argument("--uniref30_database_path", dest="uniclust30_database_path", type=str, default=None)
     parser.add_argument("--jackhmmer_binary_path", type=str, default="/usr/bin/jackhmmer")
     parser.add_argument("--hhblits_binary_path", type=str, default="/usr/bin/hhblits")
     parser.add_argument("--hhsearch_binary_path", type=str, default="/usr/bin/hhsearch")

@@ -8,7 +8,7 @@ python inference.py target.fasta data/pdb_mmcif/mmcif_files \
     --pdb70_database_path data/pdb70/pdb70 \
     --pdb_seqres_database_path data/pdb_seqres/pdb_seqres.txt \
     --uniprot_database_path data/uniprot/uniprot.fasta \
-    --uniclust30_database_path data/uniref30/UniRef30_2021_03 \
+    --uniref30_database_path data/uniref30/UniRef30_2021_03 \
     --bfd_database_path data/bfd/bfd_metaclust_clu_complete_id30_c90_final_seq.sorted_opt \
     --jackhmmer_binary_path `which jackhmmer` \
     --hhblits_binary_path `which hhblits` \
