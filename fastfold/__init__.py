@@ -77,7 +77,15 @@ _ALIASES = {
     "fastfold.workflow": "fastfold_b200.workflow",
     "fastfold.workflow.workflow_run": "fastfold_b200.workflow.workflow_run",
     "fastfold.workflow.factory": "fastfold_b200.workflow.factory",
+    "fastfold.workflow.factory.task_factory": "fastfold_b200.workflow.factory.task_factory",
+    "fastfold.workflow.factory.jackhmmer": "fastfold_b200.workflow.factory.jackhmmer",
+    "fastfold.workflow.factory.hhblits": "fastfold_b200.workflow.factory.hhblits",
+    "fastfold.workflow.factory.hhsearch": "fastfold_b200.workflow.factory.hhsearch",
+    "fastfold.workflow.factory.hhfilter": "fastfold_b200.workflow.factory.hhfilter",
+    "fastfold.workflow.factory.hmmsearch": "fastfold_b200.workflow.factory.hmmsearch",
     "fastfold.workflow.template": "fastfold_b200.workflow.template",
+    "fastfold.workflow.template.fastfold_data_workflow": "fastfold_b200.workflow.template.fastfold_data_workflow",
+    "fastfold.workflow.template.fastfold_multimer_data_workflow": "fastfold_b200.workflow.template.fastfold_multimer_data_workflow",
     "fastfold.relax": "fastfold_b200.relax",
     "fastfold.relax.relax": "fastfold_b200.relax.relax",
     "fastfold.relax.amber_minimize": "fastfold_b200.relax.amber_minimize",
