@@ -32,6 +32,20 @@ _ALIASES = {
     "fastfold.model.fastnn.triangle": "fastfold_b200.models.fastnn.triangle",
     "fastfold.model.fastnn.evoformer": "fastfold_b200.models.fastnn.evoformer",
     "fastfold.model.fastnn.kernel": "fastfold_b200.ops.compat",
+    # the reference's kernel back ends (Triton, CUDA extension, TorchScript) are one set of sm_100a kernels here
+    "fastfold.model.fastnn.kernel.attention_core": "fastfold_b200.ops.attention",
+    "fastfold.model.fastnn.kernel.softmax": "fastfold_b200.ops.softmax",
+    "fastfold.model.fastnn.kernel.layer_norm": "fastfold_b200.ops.layer_norm",
+    "fastfold.model.fastnn.kernel.jit": "fastfold_b200.ops.compat",
+    "fastfold.model.fastnn.kernel.jit.fused_ops": "fastfold_b200.ops.fused_ops",
+    "fastfold.model.fastnn.kernel.jit.options": "fastfold_b200.ops.compat",
+    "fastfold.model.fastnn.kernel.triton": "fastfold_b200.ops.compat",
+    "fastfold.model.fastnn.kernel.triton.attention_core": "fastfold_b200.ops.attention",
+    "fastfold.model.fastnn.kernel.triton.softmax": "fastfold_b200.ops.softmax",
+    "fastfold.model.fastnn.kernel.triton.layer_norm": "fastfold_b200.ops.layer_norm",
+    "fastfold.model.fastnn.kernel.cuda_native": "fastfold_b200.ops.compat",
+    "fastfold.model.fastnn.kernel.cuda_native.softmax": "fastfold_b200.ops.softmax",
+    "fastfold.model.fastnn.kernel.cuda_native.layer_norm": "fastfold_b200.ops.layer_norm",
     "fastfold.model.nn": "fastfold_b200.models.nn",
     "fastfold.model.nn.primitives": "fastfold_b200.models.nn.primitives",
     "fastfold.model.nn.evoformer": "fastfold_b200.models.nn.evoformer",

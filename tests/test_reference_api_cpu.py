@@ -239,6 +239,11 @@ def test_misc_utils_and_import_paths():
     import fastfold
     for name in sorted(fastfold._ALIASES):
         importlib.import_module(name)
+    # every module of the reference package except its Habana port (paths listed from its source tree)
+    for name in ("fastfold.model.fastnn.kernel.triton.softmax", "fastfold.model.fastnn.kernel.cuda_native.layer_norm",
+                 "fastfold.model.fastnn.kernel.jit.options", "fastfold.workflow.factory.hhfilter", "fastfold.data.tools.kalign",
+                 "fastfold.utils.geometry.quat_rigid", "fastfold.model.nn.outer_product_mean", "fastfold.relax.cleanup"):
+        importlib.import_module(name)
     from fastfold.data.input_pipeline import process_tensors_from_config          # noqa: F401
     from fastfold.utils.geometry.rigid_matrix_vector import Rigid3Array          # noqa: F401
     from fastfold.model.nn.triangular_multiplicative_update import TriangleMultiplicationIncoming          # noqa: F401
