@@ -54,3 +54,36 @@ def test_amber_relaxation_api():
     pdb, debug, viol = relaxer.process(prot=prot)
     assert pdb.startswith(("ATOM", "MODEL", "PARENT", "REMARK")) and viol.shape == (8,)
     assert {"initial_energy", "final_energy", "rmsd", "backend"} <= set(debug)
+
+
+def test_openmm_back_end_control_flow_against_a_fake():
+    """OpenMM is not installed on the test machines: a stand-in with the same call surface checks that the back end
+    cleans the structure, restrains exactly the heavy atoms of the non-excluded residues, reports energies in order and
+    returns a structure with the same atoms."""
+    from fakes import fake_openmm
+    names = fake_openmm.install()
+    try:
+        assert amber_minimize.openmm_available()
+        prot = _helix(6)
+        moved = protein.Protein(atom_positions=prot.atom_positions + 0.0, aatype=prot.aatype, atom_mask=prot.atom_mask,
+                                residue_index=prot.residue_index, b_factors=prot.b_factors)
+        res = amber_minimize.run_pipeline(moved, stiffness=10.0, max_iterations=5, max_outer_iterations=1, backend="openmm",
+                                          exclude_residues=[2], checks=True)
+        assert res["backend"] == "openmm" and res["efinal"] <= res["einit"] and "ATOM" in res["min_pdb"]
+        fixer = fake_openmm.PDBFixer.instances[-1]
+        assert fixer.steps == ["findNonstandardResidues", "replaceNonstandardResidues", "removeHeterogens", "findMissingResidues",
+                               "findMissingAtoms", "addMissingAtoms", "addMissingHydrogens"]
+        force = fake_openmm.CustomExternalForce.instances[-1]
+        n_heavy_per_res = int(prot.atom_mask[0].sum())
+        assert len(force.particles) == n_heavy_per_res * 5                      # residue 2 is free
+        assert force.per_particle == ["x0", "y0", "z0"] and "k" in force.globals
+        assert fake_openmm.Platform.requested[-1] == "CPU"
+        back = res["final_protein"]
+        assert np.allclose(back.atom_mask, prot.atom_mask)
+        assert amber_minimize.get_initial_energies([protein.to_pdb(prot)], stiffness=10.0)[0] == pytest.approx(100.0)
+        relaxer = AmberRelaxation(max_iterations=5, tolerance=2.39, stiffness=10.0, exclude_residues=[], max_outer_iterations=1,
+                                  use_gpu=False, backend="openmm")
+        pdb, debug, viol = relaxer.process(prot=prot)
+        assert debug["backend"] == "openmm" and viol.shape == (6,)
+    finally:
+        fake_openmm.uninstall(names)
