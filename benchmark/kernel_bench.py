@@ -195,6 +195,56 @@ def bench_global_attention_bwd(t, R, S, H):
     print("global attention backward R=%d S=%d H=%d c=8: %.1f us  (%.0f GB/s -> %.2f %s)" % (R, S, H, us, byt / us / 1e3, byt / hbm * 1e6 / us, tag))
 
 
+def bench_epilogues(t):
+    """Every fused GEMM epilogue the model uses against the fast-path GEMM followed by the separate kernel it replaces
+    (a fused path must beat its unfused equivalent, not only sit at some fraction of a roofline)."""
+    line = lambda name, us: print("  %-62s %8.1f us" % (name, us))
+    for (M, N, Kd) in [(65536, 128, 128), (32768, 256, 256), (65536, 128, 512), (32768, 256, 1024)]:
+        a, w, bias = _rand(M, Kd), _rand(N, Kd), _rand(N)
+        res, mul = _rand(M, N), _rand(M, N)
+        out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        dm = (torch.rand(256, N, device=DEV) > 0.15).to(torch.bfloat16)
+        rs = torch.rand(M, device=DEV)
+        print("gemm epilogues M=%d N=%d K=%d" % (M, N, Kd))
+        with torch.no_grad():
+            line("plain + bias (fast path)", t(lambda: K.gemm(a, w, bias=bias, out=out)))
+            line("bias + resid", t(lambda: K.gemm(a, w, bias=bias, resid=res, out=out)))
+            line("bias + resid, in place (out = resid)", t(lambda: K.gemm(a, w, bias=bias, resid=res, out=res)))
+            line("bias + sigmoid * mul", t(lambda: K.gemm(a, w, bias=bias, act="sigmoid", mul=mul, out=out)))
+            line("bias + dmask + resid", t(lambda: K.gemm(a, w, bias=bias, dmask=(dm, M // 256, 256), resid=res, out=out)))
+            line("bias + rowscale + resid", t(lambda: K.gemm(a, w, bias=bias, rowscale=rs, resid=res, out=out)))
+            line("unfused: gemm + bias, then torch add of the residual", t(lambda: torch.add(K.gemm(a, w, bias=bias, out=out), res)))
+            line("unfused: gemm, then the bias-sigmoid-mul kernel", t(lambda: K.bias_sigmod_ele(K.gemm(a, w, out=out), bias, mul)))
+            w2, b2 = _rand(2 * N, Kd), _rand(2 * N)
+            line("GLU pairing + row scale, transposed store (2N -> N)", t(lambda: K.gemm(a, w2, bias=b2, glu=True, rowscale=rs, trans_out=True)))
+            line("plain transposed store (2N)", t(lambda: K.gemm(a, w2, bias=b2, trans_out=True)))
+
+
+def bench_grad_gemms(t):
+    """Weight-gradient (split-K into an fp32 buffer) and input-gradient GEMMs at the model's shapes against torch.matmul."""
+    from fastfold_b200.ops.gemm import _wgrad_splits
+    hbm, _, tag = _peaks()
+    shapes = [(128, 128, 65536), (512, 128, 65536), (384, 128, 65536), (128, 512, 65536), (768, 256, 32768), (256, 256, 32768),
+              (1024, 256, 32768), (256, 1024, 32768)]
+    print("weight gradient dW[n_out, n_in] += dY^T X (tokens contracted)")
+    for (no, ni, T) in shapes:
+        dy, x = _rand(T, no), _rand(T, ni)
+        sink = torch.zeros(no, ni, device=DEV)
+        sp = _wgrad_splits(T, ((no + 127) // 128) * ((ni + 127) // 128))
+        us = t(lambda: K.gemm(dy, x, a_mn=True, b_mn=True, out=sink, accumulate=True, splits=sp))
+        ref = t(lambda: torch.matmul(dy.t(), x))
+        print("  n_out %4d n_in %4d tokens %d: %.1f us (splits %d) | torch.matmul %.1f us | HBM floor %.1f us %s" % (
+            no, ni, T, us, sp, ref, (T * no + T * ni) * 2 / hbm * 1e6, tag))
+    print("input gradient dX[tokens, n_in] = dY W (W stored [n_out, n_in])")
+    for (no, ni, T) in shapes:
+        dy, w = _rand(T, no), _rand(no, ni)
+        out = torch.empty(T, ni, device=DEV, dtype=torch.bfloat16)
+        us = t(lambda: K.gemm(dy, w, b_mn=True, out=out))
+        ref = t(lambda: torch.matmul(dy, w, out=out))
+        print("  n_out %4d n_in %4d tokens %d: %.1f us | torch.matmul %.1f us | HBM floor %.1f us %s" % (
+            no, ni, T, us, ref, (T * no + T * ni) * 2 / hbm * 1e6, tag))
+
+
 def bench_ipa(t, N):
     """Invariant point attention core (12 heads, 16 channels, 4 + 8 points, c_z 128): the pair tensor [N, N, 128] is read once."""
     import math
@@ -262,7 +312,7 @@ def bench_floor(iters):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "global_attention", "global_attention_bwd", "ipa", "floor", "all"])
+    ap.add_argument("op", choices=["gemm", "attention", "layernorm", "global_attention", "global_attention_bwd", "ipa", "floor", "epilogues", "grad_gemms", "all"])
     ap.add_argument("--m", type=int, default=65536)
     ap.add_argument("--n", type=int, default=512)
     ap.add_argument("--k", type=int, default=128)
@@ -288,6 +338,10 @@ def main():
         bench_ipa(t, args.len if args.len != 256 else 1024)
     elif args.op == "global_attention_bwd":
         bench_global_attention_bwd(t, args.b if args.b != 128 else 256, args.len if args.len != 256 else 5120, args.h)
+    elif args.op == "epilogues":
+        bench_epilogues(t)
+    elif args.op == "grad_gemms":
+        bench_grad_gemms(t)
     elif args.op == "floor":
         bench_floor(args.iters)
     elif args.op == "global_attention":
