@@ -190,3 +190,12 @@ def make_atom14_dists_bounds(overlap_tolerance=1.5, bond_length_tolerance_factor
                 lower[r, i, j] = lower[r, j, i] = lo
                 upper[r, i, j] = upper[r, j, i] = up
     return {"lower_bound": lower, "upper_bound": upper, "stddev": stddev}
+
+
+def get_cache_path():
+    """``~/.fastfold`` (created on demand): where the reference keeps downloaded tables (fastfold/common/residue_constants.py:438-442).
+    Nothing in this package downloads anything; the directory is only offered to callers that used it."""
+    import os
+    path = os.path.join(os.path.expanduser("~"), ".fastfold")
+    os.makedirs(path, exist_ok=True)
+    return path

@@ -488,3 +488,7 @@ class DataPipelineMultimer:
         all_chains = msa_pairing.add_assembly_features(all_chains)
         example = msa_pairing.pair_and_merge(all_chains)
         return msa_pairing.pad_msa(example, 512)
+
+
+# fastfold/data/data_pipeline.py:727-781 defines these two beside the pipelines; they live with the other assembly code.
+from .msa_pairing import add_assembly_features, pad_msa  # noqa: E402,F401

@@ -506,3 +506,15 @@ def random_crop_to_size(protein, crop_size, max_templates, shape_schema, subsamp
         protein[k] = v[tuple(slices)]
     protein["seq_length"] = protein["seq_length"].new_tensor(num_res_crop_size)
     return protein
+
+
+def pseudo_beta_fn(aatype, all_atom_positions, all_atom_mask):
+    """CB position (CA for glycine) and its mask (fastfold/data/data_transforms.py:353-376); one definition, in utils.feats."""
+    from ..utils.feats import pseudo_beta_fn as fn
+    return fn(aatype, all_atom_positions, all_atom_mask)
+
+
+def get_chi_atom_indices():
+    """``[21][4][4]`` nested list of atom37 indices of the atoms that define each chi angle; zeros where the residue type
+    has no such angle, last row = unknown residue (fastfold/data/data_transforms.py:914-942)."""
+    return _chi_atom_indices()

@@ -143,3 +143,13 @@ def process_tensors(batch, common_cfg, mode_cfg, seed=0):
     if "template_aatype" in batch:
         batch["template_mask"] = (batch["template_all_atom_mask"].sum((-1, -2)) > 0).float()
     return batch
+
+
+def build_extra_msa_feat(batch):
+    """``[N_extra, N_res, 25]``: one-hot of the un-clustered rows (23 classes), has-deletion flag, squashed deletion count
+    ``atan(d / 3) * 2 / pi``, computed late because the one-hot is large (fastfold/data/data_transforms_multimer.py:222-249)."""
+    dels = batch["extra_deletion_matrix"].float()
+    one_hot = torch.nn.functional.one_hot(batch["extra_msa"].long(), 23).to(dels.dtype)
+    has_del = dels.clamp(0.0, 1.0)[..., None]
+    value = (torch.atan(dels / 3.0) * (2.0 / np.pi))[..., None]
+    return torch.cat([one_hot, has_del, value], dim=-1)

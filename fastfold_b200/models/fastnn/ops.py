@@ -29,6 +29,7 @@ from ...ops.attention import attention_core
 from ...parallel import comm, core
 from ...parallel.comm import gather, scatter, scatter_mask
 from ...utils import memo
+from ...utils.tensor_utils import permute_final_dims  # noqa: F401  (public name of this module in the reference)
 from ...parallel.comm_async import (gather_async, gather_async_opp, broadcast_async, broadcast_async_opp)
 from .initializer import glorot_uniform_af
 
@@ -945,3 +946,12 @@ class ChunkMSAColumnGlobalAttention(nn.Module):
         with inplace_scope():
             M_raw[0] = self.forward(M_raw[0], M_mask)
         return M_raw
+
+
+def __getattr__(name):
+    # fastfold/model/fastnn/ops.py:1238-1420 defines the lean input / recycling embedders in this module; here they live
+    # in embedders.py (which builds on models.nn.embedders) and are reachable under the old names.
+    if name in ("InputEmbedder", "RecyclingEmbedder"):
+        from . import embedders
+        return getattr(embedders, name)
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))

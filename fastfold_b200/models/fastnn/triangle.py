@@ -3,6 +3,7 @@ import torch.nn as nn
 
 from ...parallel.comm import scatter, scatter_mask, row_to_col, col_to_row
 from ...parallel.fused import a2a_layer_norm
+from ...utils.tensor_utils import permute_final_dims  # noqa: F401
 from .ops import (AsyncChunkTriangleMultiplicationOutgoing, AsyncChunkTriangleMultiplicationIncoming,
                   ChunkTriangleAttentionStartingNode, ChunkTriangleAttentionEndingNode, ChunkTransition)
 

@@ -451,3 +451,7 @@ class AlphaFoldLoss(nn.Module):
         if not _return_breakdown:
             return cum_loss
         return cum_loss, losses
+
+
+# confidence summaries live with the heads that produce their logits; fastfold/model/hub/loss.py:1437-1532 defines them here too
+from ..nn.heads import compute_plddt, compute_predicted_aligned_error, compute_tm  # noqa: E402,F401

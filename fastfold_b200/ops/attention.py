@@ -2,10 +2,10 @@
 
 ``q, k, v`` are ``[b1, b2, H, n, d]``; ``mask`` is ``[b1, b2, n_k]`` with zeros at
 masked keys; ``bias`` is ``[b1, 1, H, n_q, n_k]`` (the pair bias, shared by all
-``b2`` rows).  Same contract as the reference's ``fused_attention_core``
-(fastfold/model/fastnn/kernel/attention_core.py:34-53), which is forward-only
-and not wired into its model; here the op has a backward and is the one every
-attention module calls.
+``b2`` rows).  ``attention_core`` returns ``[b1, b2, H, n, d]`` and is the one every
+attention module calls; ``fused_attention_core`` wraps it in the reference's
+contract (fastfold/model/fastnn/kernel/attention_core.py:34-53, forward-only
+there and not wired into its model).
 """
 import torch
 
@@ -47,6 +47,19 @@ def attention_core(q, k, v, mask=None, bias=None, scale=None, chunk=None):
     return torch.cat(outs, dim=1)
 
 
-def fused_attention_core(q, k, v, mask, bias):
-    """Reference-compatible call: ``q`` is expected pre-scaled (as the reference's modules do)."""
-    return attention_core(q, k, v, mask, bias, scale=1.0)
+def fused_attention_core(q, k, v, mask=None, bias=None):
+    """The reference's call (fastfold/model/fastnn/kernel/attention_core.py:17-53): ``q`` un-scaled (the op applies
+    ``1 / sqrt(d)``), result with the heads merged, ``[b1, b2, n, H * d]``.  Differentiable here."""
+    o = attention_core(q, k, v, mask, bias)
+    return o.transpose(-2, -3).reshape(*o.shape[:-3], o.shape[-2], o.shape[-3] * o.shape[-1])
+
+
+class FusedAttenionCoreFunc:
+    """Call-compatible stand-in for the reference's autograd Function of this (mis-spelt) name: ``.apply(q, k, v, mask, bias)``."""
+    apply = staticmethod(fused_attention_core)
+
+
+def attention_core_triton_kernel_wrapper(q, k, v, mask, bias):
+    """Forward only, as the reference's Triton launcher (kernel/triton/attention_core.py:124-190): no graph is recorded."""
+    with torch.no_grad():
+        return fused_attention_core(q, k, v, mask, bias)

@@ -157,3 +157,22 @@ class LayerNorm(nn.Module):
 
 
 FusedLayerNorm = LayerNorm
+
+
+class FusedLayerNormAffineFunction:
+    """Call-compatible stand-in for the reference's CUDA-extension Function (kernel/cuda_native/layer_norm.py:8-38):
+    ``.apply(input, weight, bias, normalized_shape, eps)``; differentiable in input, weight and bias."""
+
+    @staticmethod
+    def apply(input, weight, bias, normalized_shape, eps):
+        assert tuple(normalized_shape) == (input.shape[-1],), "LayerNorm normalises the last dimension"
+        return layer_norm(input, weight, bias, eps)
+
+
+class LayerNormTritonFunc:
+    """Call-compatible stand-in for the reference's Triton Function (kernel/triton/layer_norm.py:146-212), whose
+    argument order differs: ``.apply(a_raw, normalized_shape, weight, bias, eps)``."""
+
+    @staticmethod
+    def apply(a_raw, normalized_shape, weight, bias, eps):
+        return FusedLayerNormAffineFunction.apply(a_raw, weight, bias, normalized_shape, eps)

@@ -75,3 +75,53 @@ def fused_softmax(x, mask=None, bias=None):
             v = torch.where(m == 0, torch.full_like(v, -1e9), v)
         return torch.softmax(v, dim=-1)
     return _SoftmaxFn.apply(x, mask, bias)
+
+
+# ---------------------------------------------------------------------------
+# The reference's lower-level names (kernel/softmax.py:21-59, kernel/cuda_native/softmax.py:6-22,
+# kernel/triton/softmax.py:153-215): its two back ends are one set of kernels here.
+# ---------------------------------------------------------------------------
+FusedSoftmaxFunc = _SoftmaxFn
+
+
+def _softmax_forward_only(input_, mask_, bias_, rows=None, cols=None):
+    """Masked, biased softmax without recording a graph; ``rows`` / ``cols`` are implied by the shape and only checked."""
+    if cols is not None and cols != input_.shape[-1]:
+        raise ValueError("cols = %d but the last dimension has %d entries" % (cols, input_.shape[-1]))
+    if rows is not None and rows != input_.numel() // input_.shape[-1]:
+        raise ValueError("rows = %d but the input has %d rows" % (rows, input_.numel() // input_.shape[-1]))
+    with torch.no_grad():
+        return fused_softmax(input_, mask_, bias_)
+
+
+def _softmax_backward_only(grad_output, output, rows=None, cols=None):
+    """``dx = y * (dy - sum(dy * y))`` over the last dimension (masked entries have y = 0, so their gradient is 0)."""
+    K = output.shape[-1]
+    if cols is not None and cols != K:
+        raise ValueError("cols = %d but the last dimension has %d entries" % (cols, K))
+    if rows is not None and rows != output.numel() // K:
+        raise ValueError("rows = %d but the output has %d rows" % (rows, output.numel() // K))
+    if output.is_cuda and output.dtype in _lib._DT:
+        y, dy = output.contiguous(), grad_output.contiguous()
+        dx = torch.empty_like(y)
+        _lib.check(_lib.get().ffb_softmax_bwd(_lib.ptr(dy), _lib.ptr(y), _lib.ptr(dx), y.numel() // K, K, _lib.dtype_code(y.dtype),
+                                              _lib.stream_ptr()), "softmax_bwd")
+        return dx
+    y, dy = output.float(), grad_output.float()
+    return (y * (dy - (dy * y).sum(-1, keepdim=True))).to(output.dtype)
+
+
+def softmax_cuda_kernel_wrapper(input_, mask_, bias_, rows, cols):
+    return _softmax_forward_only(input_, mask_, bias_, rows, cols)
+
+
+def softmax_grad_cuda_kernel_wrapper(grad_output, output, mask_, rows, cols):
+    return _softmax_backward_only(grad_output, output, rows, cols)
+
+
+def softmax_triton_kernel_wrapper(x, mask, bias, n_rows, n_cols):
+    return _softmax_forward_only(x, mask, bias, n_rows, n_cols)
+
+
+def softmax_grad_triton_kernel_wrapper(grad_output, output, n_rows, n_cols):
+    return _softmax_backward_only(grad_output, output, n_rows, n_cols)

@@ -236,3 +236,19 @@ def run_pipeline(prot: protein.Protein, stiffness: float, use_gpu: bool = False,
     out["opt_time"] = time.time() - t0
     out["min_attempts"] = iteration
     return out
+
+
+def make_atom14_positions(prot):
+    """Adds the 14-slot (per-residue-type) view of a structure given as numpy arrays ``aatype [N]``, ``all_atom_positions
+    [N, 37, 3]``, ``all_atom_mask [N, 37]``: index maps both ways, existence masks, positions, and the alternative naming
+    of the 180-degree-symmetric side chains (fastfold/relax/amber_minimize.py:185-312).  Same code as the training
+    transforms, run on tensors and handed back as numpy."""
+    from ..data import data_transforms as dt
+    t = {k: torch.as_tensor(np.asarray(v)) for k, v in prot.items() if isinstance(v, (np.ndarray, list, tuple)) or torch.is_tensor(v)}
+    t["aatype"] = t["aatype"].long()
+    t["all_atom_positions"] = t["all_atom_positions"].float()
+    t["all_atom_mask"] = t["all_atom_mask"].float()
+    t = dt.make_atom14_positions(dt.make_atom14_masks(t))
+    for k, v in t.items():
+        prot[k] = v.numpy()
+    return prot

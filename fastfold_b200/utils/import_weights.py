@@ -354,6 +354,35 @@ def get_translation_dict(model, version="model_1"):
     return out
 
 
+def stacked(param_dict_list, out=None):
+    """Merges a list of identically shaped (nested) ``{name: Param}`` trees - one per block - into one tree whose leaves are
+    stacked ``Param``s holding the list of per-block tensors (fastfold/utils/import_weights.py:81-107)."""
+    out = {} if out is None else out
+    first = param_dict_list[0]
+    for k, v0 in first.items():
+        column = [d[k] for d in param_dict_list]
+        if isinstance(v0, dict):
+            out[k] = stacked(column, out={})
+        elif isinstance(v0, Param):
+            out[k] = Param([p.param for p in column], v0.param_type, True, v0.meta)
+    return out
+
+
+def assign(translation_dict, orig_weights):
+    """Copies the arrays of ``orig_weights`` into the tensors of a flat ``{archive key: Param}`` table, applying each entry's
+    layout transformation; a stacked entry is split along its leading axis (fastfold/utils/import_weights.py:110-129)."""
+    with torch.no_grad():
+        for key, param in translation_dict.items():
+            t = _to_torch(orig_weights[key], param.param_type.value)
+            dsts, srcs = (param.param, torch.unbind(t, dim=0)) if param.stacked else ([param.param], [t])
+            if len(dsts) != len(srcs):
+                raise ValueError("%s: %d arrays for %d tensors" % (key, len(srcs), len(dsts)))
+            for dst, src in zip(dsts, srcs):
+                if dst.numel() != src.numel():
+                    raise ValueError("%s: archive shape %s does not fit parameter shape %s" % (key, tuple(src.shape), tuple(dst.shape)))
+                dst.copy_(src.reshape(dst.shape).to(dst.dtype))
+
+
 def import_jax_weights_(model, npz_path, version="model_1"):
     data = np.load(npz_path) if isinstance(npz_path, str) else npz_path
     flat = flat_translation(model, version)

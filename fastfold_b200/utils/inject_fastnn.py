@@ -199,6 +199,92 @@ def inject_fastnn(model):
 
 
 # ---------------------------------------------------------------------------
+# The reference's helper names (fastfold/utils/inject_fastnn.py:24-318): scripts that build a fast module by hand and fill
+# it from an OpenFold-layout module call these directly.
+# ---------------------------------------------------------------------------
+copy_layernorm = _copy_layernorm
+copy_linear = _copy_linear
+copy_native_linear = _copy_linear
+copy_attention = _copy_attention
+copy_transition = _copy_transition
+copy_triangle = _copy_tri_mul
+copy_triangle_att = _copy_tri_att
+copy_global_attention = _copy_global_attention
+copy_evoformer_para = copy_evoformer_block
+copy_extra_msa_para = copy_extra_msa_block
+copy_template_pair_stack_para = copy_template_pair_block
+
+
+def _copy_stacked(fast, oris):
+    _cp(fast.weight, torch.cat([o.weight for o in oris], dim=0))
+    if getattr(fast, "bias", None) is not None and all(getattr(o, "bias", None) is not None for o in oris):
+        _cp(fast.bias, torch.cat([o.bias for o in oris], dim=0))
+
+
+def copy_kv_linear(model_fast, ori_k, ori_v):
+    """Fills a fused ``[k; v]`` projection from the two separate ones."""
+    _copy_stacked(model_fast, [ori_k, ori_v])
+
+
+def copy_qkv_linear(model_fast, ori_q, ori_k, ori_v):
+    """Fills a fused ``[q; k; v]`` projection from the three separate ones."""
+    _copy_stacked(model_fast, [ori_q, ori_k, ori_v])
+
+
+def copy_left_right(model_fast, ori_left, ori_right):
+    """Fills a fused ``[left; right]`` triangle-multiplication projection (or gate) from its two halves."""
+    _copy_stacked(model_fast, [ori_left, ori_right])
+
+
+def copy_native_att(model_fast, model_ori):
+    """Attention kept in the OpenFold layout on both sides (template pointwise attention): separate q / k / v / g / o."""
+    for name in ("linear_q", "linear_k", "linear_v", "linear_g", "linear_o"):
+        if hasattr(model_ori, name) and getattr(model_ori, name) is not None:
+            _copy_linear(getattr(model_fast, name), getattr(model_ori, name))
+
+
+def copy_template_pair_block_para(fast_module, target_module):
+    """Every block of a template pair stack; a block in eval mode puts its twin in eval mode."""
+    with torch.no_grad():
+        for fb, ob in zip(fast_module.blocks, target_module.blocks):
+            copy_template_pair_block(fb, ob)
+            if not ob.training:
+                fb.eval()
+
+
+def copy_template_para(block_fast, block_ori):
+    """A whole monomer template embedder (angle embedder, pair embedder, pair stack, pointwise attention)."""
+    _copy_linear(block_fast.template_angle_embedder.linear_1, block_ori.template_angle_embedder.linear_1)
+    _copy_linear(block_fast.template_angle_embedder.linear_2, block_ori.template_angle_embedder.linear_2)
+    _copy_linear(block_fast.template_pair_embedder.linear, block_ori.template_pair_embedder.linear)
+    copy_template_pair_block_para(block_fast.template_pair_stack, block_ori.template_pair_stack)
+    _copy_layernorm(block_fast.template_pair_stack.layer_norm, block_ori.template_pair_stack.layer_norm)
+    copy_native_att(block_fast.template_pointwise_att.mha, block_ori.template_pointwise_att.mha)
+
+
+def copy_template_multimer_para(block_fast, block_ori):
+    """A whole multimer template embedder: the pair embedder's per-feature projections, the single embedder, the pair
+    stack and the final projection."""
+    fp, op = block_fast.template_pair_embedder, block_ori.template_pair_embedder
+    for name in ("dgram_linear", "aatype_linear_1", "aatype_linear_2", "query_embedding_linear", "pseudo_beta_mask_linear",
+                 "x_linear", "y_linear", "z_linear", "backbone_mask_linear"):
+        _copy_linear(getattr(fp, name), getattr(op, name))
+    _copy_layernorm(fp.query_embedding_layer_norm, op.query_embedding_layer_norm)
+    fs, os_ = block_fast.template_single_embedder, block_ori.template_single_embedder
+    _copy_linear(fs.template_single_embedder, os_.template_single_embedder)
+    _copy_linear(fs.template_projector, os_.template_projector)
+    copy_template_pair_block_para(block_fast.template_pair_stack, block_ori.template_pair_stack)
+    _copy_layernorm(block_fast.template_pair_stack.layer_norm, block_ori.template_pair_stack.layer_norm)
+    _copy_linear(block_fast.linear_t, block_ori.linear_t)
+
+
+def inject_embedder(model):
+    """Swaps the input and recycling embedders for the lean ones (fastfold/utils/inject_fastnn.py:376-415)."""
+    from ..models.fastnn.embedders import inject_embedder as fn
+    return fn(model)
+
+
+# ---------------------------------------------------------------------------
 # inverse direction: OpenFold-named tensors out of a fast stack
 # ---------------------------------------------------------------------------
 def _split(t, n):

@@ -279,3 +279,114 @@ def test_template_features_flow_into_the_model():
     assert torch.isfinite(out["final_atom_positions"]).all()
     assert (out["pair"] - out_masked["pair"]).abs().max() > 1e-4          # the templates do change the pair representation
     assert (out_fast["pair"] - out["pair"]).abs().max() < 5e-4
+
+
+def test_kernel_level_names_keep_the_reference_contracts():
+    """fastfold/model/fastnn/kernel/{attention_core,softmax,layer_norm}.py and its back-end sub-modules."""
+    import math
+    from fastfold.model.fastnn.kernel import fused_attention_core
+    from fastfold.model.fastnn.kernel.attention_core import FusedAttenionCoreFunc
+    from fastfold.model.fastnn.kernel.triton.attention_core import attention_core_triton_kernel_wrapper
+    from fastfold.model.fastnn.kernel.cuda_native.softmax import softmax_cuda_kernel_wrapper, softmax_grad_cuda_kernel_wrapper
+    from fastfold.model.fastnn.kernel.triton.softmax import softmax_triton_kernel_wrapper, softmax_grad_triton_kernel_wrapper
+    from fastfold.model.fastnn.kernel.softmax import FusedSoftmaxFunc  # noqa: F401
+    from fastfold.model.fastnn.kernel.cuda_native.layer_norm import FusedLayerNormAffineFunction
+    from fastfold.model.fastnn.kernel.triton.layer_norm import LayerNormTritonFunc
+    torch.manual_seed(0)
+    b1, b2, h, n, d = 1, 3, 2, 5, 4
+    q, k, v = (torch.randn(b1, b2, h, n, d) for _ in range(3))
+    mask = (torch.rand(b1, b2, n) > 0.3).float()
+    mask[..., 0] = 1
+    bias = torch.randn(b1, 1, h, n, n)
+    # the reference's composite: q scaled inside, heads merged in the result
+    logits = torch.matmul(q / math.sqrt(d), k.transpose(-1, -2)) + bias + (1e20 * (mask - 1))[..., :, None, None, :]
+    want = torch.matmul(torch.softmax(logits, -1), v).permute(0, 1, 3, 2, 4).reshape(b1, b2, n, h * d)
+    for fn in (fused_attention_core, FusedAttenionCoreFunc.apply, attention_core_triton_kernel_wrapper):
+        got = fn(q, k, v, mask, bias)
+        assert got.shape == want.shape and torch.allclose(got, want, atol=1e-5)
+    # softmax: forward wrappers agree with the oracle, backward wrappers with autograd
+    x = torch.randn(b1, b2, h, n, n, requires_grad=True)
+    y_ref = torch.softmax(x + bias + (1e9 * (mask - 1))[..., :, None, None, :], -1)
+    dy = torch.randn_like(y_ref)
+    (dx_ref,) = torch.autograd.grad(y_ref, x, dy)
+    rows, cols = x.numel() // n, n
+    for fwd in (softmax_cuda_kernel_wrapper, softmax_triton_kernel_wrapper):
+        assert torch.allclose(fwd(x.detach(), mask, bias, rows, cols), y_ref, atol=1e-6)
+    assert torch.allclose(softmax_grad_cuda_kernel_wrapper(dy, y_ref.detach(), mask, rows, cols), dx_ref, atol=1e-6)
+    assert torch.allclose(softmax_grad_triton_kernel_wrapper(dy, y_ref.detach(), rows, cols), dx_ref, atol=1e-6)
+    with pytest.raises(ValueError):
+        softmax_cuda_kernel_wrapper(x.detach(), mask, bias, rows, cols + 1)
+    # LayerNorm: the two argument orders
+    a = torch.randn(7, 16)
+    w, b = torch.randn(16), torch.randn(16)
+    want = torch.nn.functional.layer_norm(a, (16,), w, b, 1e-5)
+    assert torch.allclose(FusedLayerNormAffineFunction.apply(a, w, b, (16,), 1e-5), want, atol=1e-6)
+    assert torch.allclose(LayerNormTritonFunc.apply(a, (16,), w, b, 1e-5), want, atol=1e-6)
+
+
+def test_weight_copy_helpers_and_translation_tables():
+    """fastfold/utils/inject_fastnn.py:24-318 (copy_*), fastfold/utils/import_weights.py:81-129 (stacked, assign)."""
+    inj = importlib.import_module("fastfold.utils.inject_fastnn")       # the package exports a function of the same name
+    iw = importlib.import_module("fastfold.utils.import_weights")
+    from fastfold_b200.models.nn.primitives import Attention, Linear
+    from fastfold_b200.models.fastnn.ops import SelfAttention
+    torch.manual_seed(0)
+    ori = Attention(16, 16, 16, 8, 2)
+    for p in ori.parameters():
+        torch.nn.init.normal_(p, std=0.3)
+    fast = SelfAttention(qkv_dim=16, c=8, n_head=2, out_dim=16, gating=True, last_bias_fuse=False)
+    inj.copy_attention(fast, ori)
+    x = torch.randn(1, 3, 5, 16)
+    want = ori(x, x, biases=None)
+    got, tail_done = fast(x, torch.ones(1, 3, 5), None)
+    assert not tail_done
+    assert torch.allclose(got, want, atol=1e-5)
+    fused = torch.nn.Linear(16, 48, bias=False)
+    inj.copy_qkv_linear(fused, ori.linear_q, ori.linear_k, ori.linear_v)
+    assert torch.equal(fused.weight[16:32], ori.linear_k.weight)
+    kv = torch.nn.Linear(16, 32, bias=False)
+    inj.copy_kv_linear(kv, ori.linear_k, ori.linear_v)
+    assert torch.equal(kv.weight[16:], ori.linear_v.weight)
+    left, right, both = Linear(8, 4), Linear(8, 4), Linear(8, 8)
+    inj.copy_left_right(both, left, right)
+    assert torch.equal(both.weight[4:], right.weight) and torch.equal(both.bias[:4], left.bias)
+    twin = Attention(16, 16, 16, 8, 2)
+    inj.copy_native_att(twin, ori)
+    assert torch.equal(twin.linear_o.weight, ori.linear_o.weight) and torch.equal(twin.linear_g.bias, ori.linear_g.bias)
+    # stacked / assign: two blocks' trees become one stacked table; archive arrays land transposed
+    l1, l2 = torch.nn.Linear(3, 4), torch.nn.Linear(3, 4)
+    tree = [{"a": {"w": iw.Param(l.weight, iw.ParamType.LinearWeight), "b": iw.Param(l.bias)}} for l in (l1, l2)]
+    st = iw.stacked(tree)
+    assert st["a"]["w"].stacked and len(st["a"]["w"].param) == 2
+    W, B = np.random.randn(2, 3, 4).astype(np.float32), np.random.randn(2, 4).astype(np.float32)
+    iw.assign({"a/w": st["a"]["w"], "a/b": st["a"]["b"]}, {"a/w": W, "a/b": B})
+    assert np.allclose(l2.weight.detach().numpy(), W[1].T) and np.allclose(l1.bias.detach().numpy(), B[0])
+    with pytest.raises(ValueError):
+        iw.assign({"a/b": st["a"]["b"]}, {"a/b": B[:1]})
+
+
+def test_remaining_small_names():
+    from fastfold.data import data_pipeline, data_transforms, data_transforms_multimer
+    from fastfold.model.hub import loss
+    from fastfold.model.fastnn import ops as fops, triangle
+    from fastfold.relax import amber_minimize
+    from fastfold.common import residue_constants
+    assert data_pipeline.add_assembly_features is msa_pairing.add_assembly_features and callable(data_pipeline.pad_msa)
+    chi = data_transforms.get_chi_atom_indices()
+    assert len(chi) == 21 and len(chi[0]) == 4 and chi[rc.restype_order["G"]] == [[0, 0, 0, 0]] * 4
+    n = 6
+    aatype = torch.tensor([rc.restype_order[c] for c in "GAVLKD"])
+    pos, m37 = torch.randn(n, 37, 3), torch.ones(n, 37)
+    pb, pbm = data_transforms.pseudo_beta_fn(aatype, pos, m37)
+    assert torch.equal(pb[0], pos[0, rc.atom_order["CA"]]) and torch.equal(pb[1], pos[1, rc.atom_order["CB"]]) and pbm.shape == (n,)
+    feat = data_transforms_multimer.build_extra_msa_feat({"extra_msa": torch.randint(0, 23, (4, n)), "extra_deletion_matrix": torch.tensor([[0., 3., 0., 0., 1., 0.]] * 4)})
+    assert feat.shape == (4, n, 25) and feat[0, 1, 23] == 1 and abs(float(feat[0, 1, 24]) - 0.5) < 1e-6 and feat[0, 0, 24] == 0
+    assert loss.compute_plddt(torch.randn(n, 50)).shape == (n,) and callable(loss.compute_tm) and callable(loss.compute_predicted_aligned_error)
+    assert fops.InputEmbedder.__name__ == "InputEmbedder" and fops.RecyclingEmbedder.__name__ == "RecyclingEmbedder"
+    assert callable(fops.permute_final_dims) and callable(triangle.permute_final_dims)
+    prot = {"aatype": aatype.numpy(), "all_atom_positions": pos.numpy(), "all_atom_mask": (m37 * torch.tensor(rc.restype_atom37_mask)[aatype]).numpy()}
+    out = amber_minimize.make_atom14_positions(prot)
+    assert out["atom14_gt_positions"].shape == (n, 14, 3) and out["residx_atom14_to_atom37"].shape == (n, 14)
+    assert out["atom14_gt_exists"][0].sum() == 4 and out["atom14_atom_is_ambiguous"][5].sum() == 2      # GLY has 4 atoms; ASP OD1 / OD2
+    import os
+    assert os.path.isdir(residue_constants.get_cache_path())
