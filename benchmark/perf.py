@@ -30,6 +30,9 @@ def main():
     p.add_argument("--openfold", action="store_true", help="time the OpenFold-layout reference modules instead of the fast ones")
     p.add_argument("--fwd", action="store_true", help="forward only")
     p.add_argument("--prof", action="store_true", help="record a torch.profiler trace under ./log/fastfold")
+    p.add_argument("--nvtx", action="store_true", help="one NVTX range per sub-module call (for a timeline viewer)")
+    p.add_argument("--module-times", action="store_true",
+                   help="after the run, print device time per module class over the timed trials (forward only; max over ranks)")
     args = p.parse_args()
     from fastfold_b200.parallel import init_dap, barrier, core
     from fastfold_b200.models.fastnn import Evoformer
@@ -56,8 +59,14 @@ def main():
         prof = torch.profiler.profile(schedule=torch.profiler.schedule(wait=1, warmup=args.warmup_trials, active=args.trials, repeat=1),
                                       on_trace_ready=torch.profiler.tensorboard_trace_handler("./log/fastfold"))
         prof.start()
+    from fastfold_b200.utils import tracing
+    stack = torch.nn.ModuleList(layers)
+    ranges = tracing.annotate(stack, max_depth=3) if args.nvtx else None
+    timer = None
     f_ms = b_ms = 0.0
     for t in range(args.trials + args.warmup_trials):
+        if args.module_times and t == args.warmup_trials:
+            timer = tracing.ModuleTimer(stack, max_depth=3)
         barrier()
         torch.cuda.synchronize()
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
@@ -77,6 +86,13 @@ def main():
             prof.step()
     if prof:
         prof.stop()
+    if ranges:
+        ranges.remove()
+    if timer:
+        table = timer.table(by="class")
+        timer.remove()
+        if core.get_rank() == 0:
+            print(table)
     vals = torch.tensor([f_ms, b_ms], device=dev, dtype=torch.float64) / (args.trials * args.layers)
     if core.get_world_size() > 1:
         torch.distributed.all_reduce(vals, op=torch.distributed.ReduceOp.MAX)

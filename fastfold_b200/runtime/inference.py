@@ -46,10 +46,12 @@ def load_model(model_name="model_1", param_path=None, chunk_size=None, inplace=F
     return model
 
 
-def predict(model, batch):
+def predict(model, batch, module_times=None):
     """One prediction: ``batch`` (features with the recycling dimension last; host or device tensors / arrays) is moved
     to the model's device, the model runs without gradients, and the outputs come back as device tensors together with
-    the device-timed seconds of the model call.  Raises on every rank if a kernel reported a failed wait."""
+    the device-timed seconds of the model call.  Raises on every rank if a kernel reported a failed wait.
+    ``module_times``: a dict that receives ``{"table": str, "summary": dict}`` - device time per top-level module of the
+    model (max over ranks, ``utils.tracing.ModuleTimer``); the hooks add a few event records per module call."""
     device = next(model.parameters()).device
     cuda = device.type == "cuda"
     if cuda:
@@ -65,6 +67,10 @@ def predict(model, batch):
         if cuda:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
+        timer = None
+        if module_times is not None:
+            from ..utils import tracing
+            timer = tracing.ModuleTimer(model, max_depth=1)
         t0 = time.perf_counter()
         out = model(batch)
         if cuda:
@@ -75,6 +81,10 @@ def predict(model, batch):
             check_device_status()        # a kernel that gave up on a wait leaves unwritten outputs: fail on every rank
         else:
             seconds = time.perf_counter() - t0
+        if timer is not None:
+            module_times["summary"] = timer.summary(by="path")
+            module_times["table"] = timer.table(by="path")
+            timer.remove()
     return out, seconds
 
 
@@ -87,12 +97,15 @@ def _worker(rank, world, port, batch, opts, queue):
                        opts.get("seed", 0), bf16=opts.get("bf16", True), shard_pair=opts.get("shard_pair", False))
     if cuda:
         torch.cuda.synchronize()
-    out, seconds = predict(model, batch)
+    times = {} if opts.get("module_times") else None
+    out, seconds = predict(model, batch, module_times=times)
     peak = torch.cuda.max_memory_allocated() / 2 ** 30 if cuda else 0.0
     if rank == 0:
         res = {k: v.float().cpu().numpy() for k, v in out.items() if isinstance(v, torch.Tensor)}
         res["_seconds"] = seconds
         res["_peak_gib"] = peak
+        if times:
+            res["_module_times"] = times["table"]
         queue.put(res)
     from ..parallel import barrier
     barrier()
@@ -100,11 +113,11 @@ def _worker(rank, world, port, batch, opts, queue):
 
 
 def run_inference(batch, gpus=1, model_name="model_1", param_path=None, chunk_size=None, inplace=False, seed=0, overrides=None, port=None,
-                  shard_pair=False):
+                  shard_pair=False, module_times=False):
     """Runs the model on ``batch`` (features with the recycling dimension last) over ``gpus`` DAP ranks; returns numpy outputs."""
     import torch.multiprocessing as mp
     opts = {"model_name": model_name, "param_path": param_path, "chunk_size": chunk_size, "inplace": inplace, "seed": seed, "overrides": overrides,
-            "shard_pair": shard_pair}
+            "shard_pair": shard_pair, "module_times": module_times}
     batch = {k: (v.cpu().numpy() if isinstance(v, torch.Tensor) else np.asarray(v)) for k, v in batch.items()}
     ctx = mp.get_context("spawn")
     manager = ctx.Manager()

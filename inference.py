@@ -38,6 +38,23 @@ def add_data_args(parser):
     parser.add_argument("--chunk_size", type=int, default=None)
     parser.add_argument("--enable_workflow", default=False, action="store_true")
     parser.add_argument("--inplace", default=False, action="store_true")
+    parser.add_argument("--module_times", default=False, action="store_true",
+                        help="print the device time of every top-level module of the model (max over ranks)")
+
+
+def parse_overrides(items):
+    """``["a.b=3", "c.d=True"]`` -> ``{"a.b": 3, "c.d": True}``; values that are no Python literal stay strings."""
+    import ast
+    out = {}
+    for item in items or ():
+        key, sep, value = item.partition("=")
+        if not sep or not key:
+            raise ValueError("--config_override expects KEY=VALUE, got %r" % item)
+        try:
+            out[key.strip()] = ast.literal_eval(value)
+        except (ValueError, SyntaxError):
+            out[key.strip()] = value
+    return out
 
 
 def main(args):
@@ -94,9 +111,12 @@ def main(args):
     overrides = {}
     if "template_aatype" not in feats:
         overrides["model.template.enabled"] = False
+    overrides.update(parse_overrides(args.config_override))
     out = run_inference(feats, gpus=args.gpus, model_name=args.model_name, param_path=args.param_path, chunk_size=args.chunk_size,
-                        inplace=args.inplace, overrides=overrides)
+                        inplace=args.inplace, overrides=overrides, module_times=args.module_times)
     print("Inference time: %.3f s (device-timed), peak memory %.2f GiB" % (out["_seconds"], out["_peak_gib"]))
+    if "_module_times" in out:
+        print(out.pop("_module_times"))
     plddt_b = np.repeat(out["plddt"][..., None], 37, axis=-1)
     f = {"aatype": feats["aatype"][..., 0].numpy(), "residue_index": feats["residue_index"][..., 0].numpy()}
     if "asym_id" in feats:
@@ -133,6 +153,9 @@ if __name__ == "__main__":
     p.add_argument("--relaxation", action="store_true", default=False)
     p.add_argument("--save_prediction_result", action="store_true", default=False)
     p.add_argument("--data_random_seed", type=int, default=None)
+    p.add_argument("--config_override", action="append", default=[], metavar="KEY=VALUE",
+                   help="set one entry of the model config, e.g. model.evoformer_stack.no_blocks=8 (repeatable; the value is "
+                        "read as a Python literal).  For reduced models; published parameter archives need the stock config")
     add_data_args(p)
     a = p.parse_args()
     if a.param_path is None:
