@@ -198,3 +198,65 @@ def test_padded_head_weights_reproduce_the_layer():
     att.to_qkv.weight.data.view(-1)[0] = 123.0
     again = att._padded_heads()[0]
     assert again is not first and float(again.reshape(-1)[0]) == 123.0
+
+
+def test_full_model_train_step_matches_reference_layout(monkeypatch):
+    """One optimiser step of the whole model with the fast trunk against the OpenFold-layout model: loss, every gradient
+    (fused / re-laid-out parameters compared after mapping back to the OpenFold names) and the updated parameters.  The
+    reference's tests/test_train.py:60-106 compares identically named parameters only; dropout is switched off here because
+    the two layouts draw their masks differently."""
+    from functools import partial
+    from fastfold_b200.models.fastnn import evoformer as fast_evoformer
+    from fastfold_b200.utils.inject_fastnn import extract_fastnn
+    # the fast trunk's dropout rates are constants (0.15 / 0.25, as in the reference's fast modules): draw keep-all masks
+    monkeypatch.setattr(fast_evoformer, "draw_block_dropout", partial(fast_evoformer.draw_block_dropout, p_msa=0.0, p_pair=0.0))
+    c = _tiny("model_1_ptm")
+    c.model.template.template_pair_stack.dropout_rate = 0.0
+    for stack in (c.model.evoformer_stack, c.model.extra_msa.extra_msa_stack):
+        stack.msa_dropout = 0.0
+        stack.pair_dropout = 0.0
+    c.model.structure_module.dropout_rate = 0.0
+    torch.manual_seed(0)
+    ref = AlphaFold(c)
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for p in ref.parameters():
+            if float(p.abs().sum()) == 0.0:
+                p.copy_(torch.randn(p.shape, generator=g) * (0.02 if p.dim() < 2 else 0.5 / p.shape[-1] ** 0.5))
+    fast = inject_fastnn(copy.deepcopy(ref))
+    batch = random_features(10, 5, 6, n_templ=2, n_recycle=1, seed=2, supervised=True)
+    last = tensor_tree_map(lambda t: t[..., -1], batch)
+    crit = AlphaFoldLoss(c.loss)
+    state = {}
+    for name, model in (("ref", ref), ("fast", fast)):
+        model.train()
+        opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-6)
+        loss = crit(model(batch), last)
+        loss.backward()
+        if name == "fast":
+            # gradients and parameters of the swapped stacks under their OpenFold names
+            live = dict(model.named_parameters())
+            for p in live.values():
+                p.data, p.grad = p.grad, p.data
+            grads = {k: v.clone() for k, v in extract_fastnn(model).items()}
+            for p in live.values():
+                p.data, p.grad = p.grad, p.data
+        else:
+            grads = {k: p.grad.clone() for k, p in model.named_parameters() if p.grad is not None}
+        opt.step()
+        params = extract_fastnn(model) if name == "fast" else {k: p.detach() for k, p in model.named_parameters()}
+        state[name] = (float(loss), grads, params)
+    (l0, g0, p0), (l1, g1, p1) = state["ref"], state["fast"]
+    assert abs(l0 - l1) < 1e-4 * abs(l0)
+    trunk = [k for k in g0 if k.startswith(("evoformer.", "extra_msa_stack.", "template_embedder.template_pair_stack."))]
+    assert len(trunk) > 150 and all(k in g1 for k in trunk), [k for k in trunk if k not in g1][:5]
+    scale = max(float(v.abs().max()) for v in g0.values())
+    for k, v in g0.items():
+        if k in g1:
+            assert (g1[k] - v).abs().max() < 5e-3 * max(scale * 1e-2, float(v.abs().max())), k
+    moved = 0
+    for k, v in p0.items():
+        if k in p1:
+            assert (p1[k] - v).abs().max() < 1e-3, k
+            moved += 1
+    assert moved > 200
