@@ -228,6 +228,7 @@ def main():
     steps_done = 0
     for epoch in range(start_epoch, args.max_epochs):
         t_epoch = time.time()
+        epoch_steps = 0
         for i in range(len(dataset)):
             batch = dataset.get(epoch, i)
             n_iter = int(batch.pop("no_recycling_iters", torch.tensor(batch["aatype"].shape[-1] - 1)).reshape(-1)[0]) + 1
@@ -238,6 +239,7 @@ def main():
             loss_fn.last = trainer.aux if trainer.aux is not None else loss_fn.last      # the replayed graph's own output tensors
             sched.step()
             steps_done += 1
+            epoch_steps += 1
             if (i + 1) % args.log_interval == 0:
                 trainer.check_status()       # every rank: a kernel that gave up on a wait must stop the run, not train on garbage
                 if rank == 0:
@@ -250,7 +252,13 @@ def main():
                              " ".join("%s %.3f" % (k, float(v)) for k, v in metrics.items()))
             if args.max_steps and steps_done >= args.max_steps:
                 break
-        log.info("epoch %d done in %.1f s", epoch, time.time() - t_epoch)
+        if device.type == "cuda":
+            torch.cuda.synchronize()
+        dt = max(time.time() - t_epoch, 1e-9)
+        # throughput over the whole job: every data-parallel replica trains one sample per step
+        log.info("epoch %d done in %.1f s: %d steps, %.3f samples/s over %d replica(s)%s", epoch, dt, epoch_steps,
+                 epoch_steps * core.get_dp_size() / dt, core.get_dp_size(),
+                 ", peak device memory %.2f GiB" % (torch.cuda.max_memory_allocated() / 2 ** 30) if device.type == "cuda" else "")
         if val_dataset is not None and (epoch + 1) % args.val_interval == 0:
             validate(epoch)
         if args.save_ckpt_path and (epoch + 1) % args.save_ckpt_interval == 0:
