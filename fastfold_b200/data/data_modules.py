@@ -118,9 +118,12 @@ class OpenFoldSingleDataset(torch.utils.data.Dataset):
 
     def raw(self, idx):
         name = self.idx_to_chain_id(idx)
-        aln = os.path.join(self.alignment_dir, name)
+        aln, index = os.path.join(self.alignment_dir, name), None
+        if self._alignment_index is not None:
+            # all targets' search outputs live in concatenated files under alignment_dir; the index says where
+            aln, index = self.alignment_dir, self._alignment_index[name]
         if self.mode == "predict":
-            return self.data_pipeline.process_fasta(os.path.join(self.data_dir, name, name + ".fasta"), aln)
+            return self.data_pipeline.process_fasta(os.path.join(self.data_dir, name, name + ".fasta"), aln, _alignment_index=index)
         file_id, chain_id = (name.rsplit("_", 1) + [None])[:2] if "_" in name else (name, None)
         base = os.path.join(self.data_dir, file_id)
         if os.path.exists(base + ".cif"):
@@ -128,10 +131,13 @@ class OpenFoldSingleDataset(torch.utils.data.Dataset):
             res = mmcif_parsing.parse(file_id=file_id, mmcif_string=open(base + ".cif").read())
             if res.mmcif_object is None:
                 raise list(res.errors.values())[0]
-            return self.data_pipeline.process_mmcif(res.mmcif_object, aln, chain_id)
+            return self.data_pipeline.process_mmcif(res.mmcif_object, aln, chain_id, _alignment_index=index)
+        if os.path.exists(base + ".core"):
+            return self.data_pipeline.process_core(base + ".core", aln, _alignment_index=index)
         if os.path.exists(base + ".pdb"):
-            return self.data_pipeline.process_pdb(base + ".pdb", aln, is_distillation=self.treat_pdb_as_distillation, chain_id=chain_id)
-        raise ValueError("no .cif or .pdb file for %r under %s" % (name, self.data_dir))
+            return self.data_pipeline.process_pdb(base + ".pdb", aln, is_distillation=self.treat_pdb_as_distillation, chain_id=chain_id,
+                                                  _alignment_index=index)
+        raise ValueError("no .cif, .core or .pdb file for %r under %s" % (name, self.data_dir))
 
     def __getitem__(self, idx):
         data = self.raw(idx)

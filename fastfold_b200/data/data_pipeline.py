@@ -65,9 +65,9 @@ def make_template_features(input_sequence: str, hits, template_featurizer, query
     if not flat or template_featurizer is None:
         return empty_template_features(len(input_sequence))
     try:
-        result = template_featurizer.get_templates(input_sequence, flat, query_pdb_code=query_pdb_code, query_release_date=query_release_date)
+        result = template_featurizer.get_templates(input_sequence, hits=flat, query_pdb_code=query_pdb_code, query_release_date=query_release_date)
     except TypeError:          # featurisers without the query-identity filters (hmmsearch hits of the multimer pipeline)
-        result = template_featurizer.get_templates(input_sequence, flat)
+        result = template_featurizer.get_templates(input_sequence, hits=flat)
     feats = result.features
     if feats["template_aatype"].shape[0] == 0:
         return empty_template_features(len(input_sequence))
@@ -83,13 +83,14 @@ def make_protein_features(protein_object, description: str, _is_distillation: bo
     return feats
 
 
-def make_pdb_features(protein_object, description: str, is_distillation: bool = True, confidence_threshold: float = 50.0) -> FeatureDict:
+def make_pdb_features(protein_object, description: str, confidence_threshold: float = 50.0, is_distillation: bool = True) -> FeatureDict:
     """As ``make_protein_features``; for self-distillation targets (predicted structures with the confidence in the
-    B-factor column) atoms of residues below ``confidence_threshold`` are masked out of the ground truth."""
+    B-factor column) a residue none of whose atoms exceeds ``confidence_threshold`` is masked out of the ground truth
+    (fastfold/data/data_pipeline.py:185-202, whose default of 0.5 on a 0-100 confidence scale keeps everything)."""
     feats = make_protein_features(protein_object, description, _is_distillation=True)
     if is_distillation:
-        confident = (np.asarray(protein_object.b_factors) > confidence_threshold).astype(np.float32)
-        feats["all_atom_mask"] = feats["all_atom_mask"] * confident
+        confident = (np.asarray(protein_object.b_factors) > confidence_threshold).any(axis=-1).astype(np.float32)
+        feats["all_atom_mask"] = feats["all_atom_mask"] * confident[:, None]
     else:
         feats["is_distillation"] = np.array(0.0, np.float32)
     return feats
@@ -170,42 +171,69 @@ class DataPipeline:
         self.template_featurizer = template_featurizer
 
     @staticmethod
-    def _read_alignments(alignment_dir, query):
-        msas, dels = [], []
-        if alignment_dir and os.path.isdir(alignment_dir):
+    def _alignment_files(alignment_dir, _alignment_index=None):
+        """``(file name, text)`` of every search output of one target, in name order.  They are the files of
+        ``alignment_dir``, or - with ``_alignment_index = {"db": file, "files": [(name, offset, size), ...]}`` - byte ranges
+        of one concatenated file ``alignment_dir/db`` (millions of small files become one; fastfold/data/data_pipeline.py:792-843)."""
+        if _alignment_index is not None:
+            with open(os.path.join(alignment_dir, _alignment_index["db"]), "rb") as fp:
+                for name, start, size in sorted(_alignment_index["files"], key=lambda e: e[0]):
+                    fp.seek(int(start))
+                    yield name, fp.read(int(size)).decode("utf-8")
+        elif alignment_dir and os.path.isdir(alignment_dir):
             for f in sorted(os.listdir(alignment_dir)):
                 path = os.path.join(alignment_dir, f)
-                if f.endswith(".a3m"):
-                    m, d, _ = parsers.parse_a3m(open(path).read())
-                elif f.endswith(".sto"):
-                    m, d, _ = parsers.parse_stockholm(open(path).read())
-                else:
-                    continue
-                if m and len(m[0]) == len(query):
-                    msas.append(m)
-                    dels.append(d)
+                if os.path.isfile(path) and os.path.splitext(f)[1] in (".a3m", ".sto", ".hhr"):
+                    with open(path) as fp:
+                        yield f, fp.read()
+
+    @classmethod
+    def _read_alignments(cls, alignment_dir, query, _alignment_index=None):
+        msas, dels = [], []
+        for name, text in cls._alignment_files(alignment_dir, _alignment_index):
+            stem, ext = os.path.splitext(name)
+            if ext == ".a3m":
+                m, d, _ = parsers.parse_a3m(text)
+            elif ext == ".sto" and stem not in ("hmm_output", "hmmsearch_output"):       # those hold template hits, not an MSA
+                m, d, _ = parsers.parse_stockholm(text)
+            else:
+                continue
+            if m and len(m[0]) == len(query):
+                msas.append(m)
+                dels.append(d)
         if not msas:      # single-sequence mode
             msas, dels = [[query]], [[[0] * len(query)]]
         return msas, dels
 
-    def process_fasta(self, fasta_path: str, alignment_dir: Optional[str] = None) -> FeatureDict:
+    @classmethod
+    def _read_template_hits(cls, alignment_dir, input_sequence=None, _alignment_index=None):
+        """``{file name: [TemplateHit]}``: hhsearch results (``*.hhr``) and, for the multimer pipeline, the hmmsearch
+        alignment against the PDB sequences (``hmm_output.sto``; fastfold/data/data_pipeline.py:845-890)."""
+        hits = {}
+        for name, text in cls._alignment_files(alignment_dir, _alignment_index):
+            if name.endswith(".hhr"):
+                hits[name] = parsers.parse_hhr(text)
+            elif name in ("hmm_output.sto", "hmmsearch_output.sto") and input_sequence is not None:
+                hits[name] = parsers.parse_hmmsearch_sto(text, input_sequence)
+        return hits
+
+    def process_fasta(self, fasta_path: str, alignment_dir: Optional[str] = None, _alignment_index=None) -> FeatureDict:
         seqs, descs = parsers.parse_fasta(open(fasta_path).read())
         if len(seqs) != 1:
             raise ValueError("More than one input sequence found in %s." % fasta_path)
-        return self.process_sequence(seqs[0], descs[0], alignment_dir)
+        return self.process_sequence(seqs[0], descs[0], alignment_dir, _alignment_index=_alignment_index)
 
-    def process_sequence(self, sequence, description="query", alignment_dir=None, query_pdb_code=None, query_release_date=None) -> FeatureDict:
+    def process_sequence(self, sequence, description="query", alignment_dir=None, query_pdb_code=None, query_release_date=None,
+                         _alignment_index=None) -> FeatureDict:
         """``query_pdb_code`` / ``query_release_date``: identity of the target when it is itself a PDB entry (training),
         so that the entry and anything released within 60 days before it are not used as templates."""
         n = len(sequence)
         feats = dict(make_sequence_features(sequence, description, n))
-        msas, dels = self._read_alignments(alignment_dir, sequence)
+        msas, dels = self._read_alignments(alignment_dir, sequence, _alignment_index)
         feats.update(make_msa_features(msas, dels))
-        hits = []
+        hits = {}
         if self.template_featurizer is not None and alignment_dir:
-            hhr = os.path.join(alignment_dir, "pdb70_hits.hhr")
-            if os.path.exists(hhr):
-                hits = parsers.parse_hhr(open(hhr).read())
+            hits = self._read_template_hits(alignment_dir, sequence, _alignment_index)
         feats.update(make_template_features(sequence, hits, self.template_featurizer, query_pdb_code, query_release_date))
         return feats
 
@@ -216,22 +244,31 @@ def _ground_truth_features(positions, mask, resolution=1.0, is_distillation=Fals
 
 
 def _process_structure(self, sequence, description, alignment_dir, positions, mask, resolution, is_distillation, query_pdb_code=None,
-                       query_release_date=None):
-    feats = dict(self.process_sequence(sequence, description, alignment_dir, query_pdb_code, query_release_date))
+                       query_release_date=None, _alignment_index=None):
+    feats = dict(self.process_sequence(sequence, description, alignment_dir, query_pdb_code, query_release_date, _alignment_index=_alignment_index))
     feats.update(_ground_truth_features(positions, mask, resolution, is_distillation))
     return feats
 
 
-def _process_pdb(self, pdb_path, alignment_dir=None, is_distillation=True, chain_id=None):
-    """Features + ground truth of one chain of a PDB file (fastfold/data/data_pipeline.py:780-828)."""
+def _process_pdb(self, pdb_path, alignment_dir=None, is_distillation=True, chain_id=None, _structure_index=None, _alignment_index=None):
+    """Features + ground truth of one chain of a PDB file; with ``_structure_index`` (same form as an alignment index) the
+    text is a byte range of one concatenated file beside ``pdb_path`` (fastfold/data/data_pipeline.py:1000-1047)."""
     from ..common import protein
-    prot = protein.from_pdb_string(open(pdb_path).read(), chain_id)
+    if _structure_index is not None:
+        _, offset, length = _structure_index["files"][0]
+        with open(os.path.join(os.path.dirname(pdb_path), _structure_index["db"]), "rb") as fp:
+            fp.seek(int(offset))
+            pdb_str = fp.read(int(length)).decode("utf-8")
+    else:
+        pdb_str = open(pdb_path).read()
+    prot = protein.from_pdb_string(pdb_str, chain_id)
     seq = "".join(rc.restypes_with_x[int(a)] for a in prot.aatype)
     tag = os.path.splitext(os.path.basename(pdb_path))[0] + ("_" + chain_id if chain_id else "")
-    return _process_structure(self, seq, tag, alignment_dir, prot.atom_positions, prot.atom_mask, 0.0 if is_distillation else 1.0, is_distillation)
+    return _process_structure(self, seq, tag, alignment_dir, prot.atom_positions, prot.atom_mask, 0.0 if is_distillation else 1.0, is_distillation,
+                              _alignment_index=_alignment_index)
 
 
-def _process_mmcif(self, mmcif, alignment_dir=None, chain_id=None):
+def _process_mmcif(self, mmcif, alignment_dir=None, chain_id=None, _alignment_index=None):
     """Features + ground truth of one chain of a parsed mmCIF file (fastfold/data/data_pipeline.py:738-778)."""
     from . import mmcif_parsing
     if chain_id is None:
@@ -244,18 +281,18 @@ def _process_mmcif(self, mmcif, alignment_dir=None, chain_id=None):
     res = mmcif.header.get("resolution", 0.0) if isinstance(mmcif.header, dict) else getattr(mmcif.header, "resolution", 0.0)
     date = mmcif.header.get("release_date", "") if isinstance(mmcif.header, dict) else getattr(mmcif.header, "release_date", "")
     feats = _process_structure(self, seq, "%s_%s" % (mmcif.file_id, chain_id), alignment_dir, pos, mask, float(res or 0.0), False,
-                               query_pdb_code=mmcif.file_id, query_release_date=str(date) if date else None)
+                               query_pdb_code=mmcif.file_id, query_release_date=str(date) if date else None, _alignment_index=_alignment_index)
     feats["release_date"] = np.array([str(date).encode()], dtype=object)
     return feats
 
 
-def _process_core(self, core_path, alignment_dir=None):
+def _process_core(self, core_path, alignment_dir=None, _alignment_index=None):
     """Features + backbone ground truth of a ProteinNet ``.core`` record (fastfold/data/data_pipeline.py:1049-1079)."""
     from ..common import protein
     prot = protein.from_proteinnet_string(open(core_path).read())
     seq = "".join(rc.restypes_with_x[int(a)] for a in prot.aatype)
     tag = os.path.splitext(os.path.basename(core_path))[0].upper()
-    return _process_structure(self, seq, tag, alignment_dir, prot.atom_positions, prot.atom_mask, 0.0, False)
+    return _process_structure(self, seq, tag, alignment_dir, prot.atom_positions, prot.atom_mask, 0.0, False, _alignment_index=_alignment_index)
 
 
 DataPipeline.process_pdb = _process_pdb
@@ -322,8 +359,9 @@ class AlignmentRunner:
 
     def __init__(self, jackhmmer_binary_path=None, hhblits_binary_path=None, hhsearch_binary_path=None, uniref90_database_path=None,
                  mgnify_database_path=None, bfd_database_path=None, uniref30_database_path=None, pdb70_database_path=None,
-                 use_small_bfd=None, no_cpus=None, uniref_max_hits: int = 10000, mgnify_max_hits: int = 5000):
+                 use_small_bfd=None, no_cpus=None, uniref_max_hits: int = 10000, mgnify_max_hits: int = 5000, uniprot_max_hits: int = 50000):
         from . import tools
+        self.uniprot_max_hits = uniprot_max_hits       # used by the multimer runner's UniProt search
         groups = {"jackhmmer": (jackhmmer_binary_path, [uniref90_database_path, mgnify_database_path, bfd_database_path if use_small_bfd else None]),
                   "hhblits": (hhblits_binary_path, [bfd_database_path if not use_small_bfd else None]),
                   "hhsearch": (hhsearch_binary_path, [pdb70_database_path])}

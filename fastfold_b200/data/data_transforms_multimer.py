@@ -40,16 +40,18 @@ def gumbel_argsort_sample_idx(logits, generator=None):
     return torch.argsort(logits + z, dim=-1, descending=True)
 
 
-def sample_msa(batch, max_seq, max_extra_msa_seq, seed=None):
-    """Gumbel-max sampling of ``max_seq`` cluster centres; the next ``max_extra_msa_seq`` rows become the extra MSA."""
+def sample_msa(batch, max_seq, max_extra_msa_seq, seed=None, inf=1e6):
+    """Gumbel-max sampling of ``max_seq`` cluster centres; the next ``max_extra_msa_seq`` rows become the extra MSA.
+    Rows without any residue (padding) score ``-inf`` and come last; rows flagged in ``cluster_bias_mask`` (default: the
+    first row) score ``+inf`` and are always among the centres (fastfold/data/data_transforms_multimer.py:253-289)."""
     g = torch.Generator()
     g.manual_seed(seed) if seed is not None else g.seed()
-    logits = (torch.clamp(batch["msa_mask"].sum(-1), 0.0, 1.0) - 1.0) * 1e6
+    logits = (torch.clamp(batch["msa_mask"].sum(-1), 0.0, 1.0) - 1.0) * inf
     if "cluster_bias_mask" in batch:
-        bias = batch["cluster_bias_mask"]
+        bias = batch["cluster_bias_mask"].to(logits.dtype)
     else:
-        bias = torch.nn.functional.pad(torch.zeros(1), (0, batch["msa"].shape[0] - 1), value=1.0)
-    logits = logits + bias * (-1e6) * 0 + (1.0 - bias) * 1e6        # rows with bias 0 (the query) always come first
+        bias = torch.nn.functional.pad(torch.zeros(batch["msa"].shape[0] - 1), (1, 0), value=1.0)
+    logits = logits + bias * inf
     u = torch.rand(logits.shape, generator=g).clamp_(1e-6, 1 - 1e-6)
     gumbel = -torch.log(-torch.log(u))
     order = torch.argsort(logits + gumbel, descending=True)
@@ -63,7 +65,7 @@ def sample_msa(batch, max_seq, max_extra_msa_seq, seed=None):
     return batch
 
 
-def make_masked_msa(batch, config, replace_fraction, seed=None):
+def make_masked_msa(batch, config, replace_fraction, seed=None, eps=1e-6):
     g = torch.Generator()
     g.manual_seed(seed) if seed is not None else g.seed()
     random_aa = torch.tensor([0.05] * 20 + [0.0, 0.0], dtype=torch.float32)
@@ -72,8 +74,10 @@ def make_masked_msa(batch, config, replace_fraction, seed=None):
     probs = torch.nn.functional.pad(probs, (0, 1), value=mask_prob)
     sh = batch["msa"].shape
     mask_position = (torch.rand(sh, generator=g) < replace_fraction) & (batch["msa_mask"] > 0)
-    drawn = torch.multinomial(probs.reshape(-1, probs.shape[-1]) + 1e-9, 1, generator=g).reshape(sh)
-    batch["bert_mask"] = mask_position.to(torch.float32)
+    drawn = torch.multinomial(probs.reshape(-1, probs.shape[-1]) + eps, 1, generator=g).reshape(sh)
+    # a ``bert_mask`` that comes with the features marks the positions that may be scored at all (a row's own chain)
+    scored = mask_position.to(torch.float32)
+    batch["bert_mask"] = batch["bert_mask"].to(torch.float32) * scored if "bert_mask" in batch else scored
     batch["true_msa"] = batch["msa"]
     batch["msa"] = torch.where(mask_position, drawn, batch["msa"])
     return batch

@@ -307,9 +307,9 @@ def parse(*, file_id: str, mmcif_string: str, catch_all_errors: bool = True) -> 
         return ParsingResult(None, errors)
 
 
-def get_atom_coords(mmcif_object: MmcifObject, chain_id: str):
-    """All-atom positions (atom37 order) and mask of one chain, indexed by SEQRES position
-    (fastfold/data/mmcif_parsing.py:419-485)."""
+def get_atom_coords(mmcif_object: MmcifObject, chain_id: str, _zero_center_positions: bool = True):
+    """All-atom positions (atom37 order) and mask of one chain, indexed by SEQRES position; by default translated so that
+    the resolved atoms have zero mean (fastfold/data/mmcif_parsing.py:432-485)."""
     import numpy as np
     seq_map = mmcif_object.seqres_to_structure[chain_id]
     chain_atoms = mmcif_object.atoms.get(chain_id, {})
@@ -335,4 +335,7 @@ def get_atom_coords(mmcif_object: MmcifObject, chain_id: str):
                 i1, i2 = rc.atom_order["NH1"], rc.atom_order["NH2"]
                 pos[i, [i1, i2]] = pos[i, [i2, i1]]
                 mask[i, [i1, i2]] = mask[i, [i2, i1]]
+    if _zero_center_positions and mask.any():
+        present = mask.astype(bool)
+        pos[present] -= pos[present].mean(axis=0)
     return pos, mask

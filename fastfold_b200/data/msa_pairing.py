@@ -334,9 +334,26 @@ def pair_and_merge(all_chain_features: Mapping[str, MutableMapping[str, np.ndarr
         chains = deduplicate_unpaired_sequences(chains)
     chains = crop_chains(chains, msa_crop_size=max_msa_crop, pair_msa_sequences=pair, max_templates=max_templates)
     merged = merge_chain_features(chains, pair_msa_sequences=pair, max_templates=max_templates)
-    n_msa = merged["msa"].shape[0]
-    merged["cluster_bias_mask"] = np.pad(np.zeros(1), (0, n_msa - 1), constant_values=1.0).astype(np.float32)
-    merged["bert_mask"] = np.zeros_like(merged["msa"], dtype=np.float32)
+    # ``cluster_bias_mask``: 1 on the rows that must always be among the cluster centres - the first row of the merged MSA
+    # when rows are paired, the first row (the chain's own sequence) of every block of the block-diagonal MSA otherwise.
+    # ``bert_mask``: 1 where a row really has a residue of that chain (the off-diagonal padding of the block-diagonal
+    # rows is never scored by the masked-MSA loss).  fastfold/data/msa_pairing.py:287-330.
+    own_rows = _block_diag([np.ones(c["msa"].shape, dtype=np.float32) for c in chains], 0)
+    if pair:
+        bias = np.zeros(merged["msa"].shape[0], dtype=np.float32)
+        bias[0] = 1.0
+        paired_rows = np.concatenate([np.ones(c["msa_all_seq"].shape, dtype=np.float32) for c in chains], axis=1)
+        merged["bert_mask"] = np.concatenate([paired_rows, own_rows], axis=0)
+    else:
+        parts = []
+        for c in chains:
+            part = np.zeros(c["msa"].shape[0], dtype=np.float32)
+            part[0] = 1.0
+            parts.append(part)
+        bias = np.concatenate(parts)
+        merged["bert_mask"] = own_rows
+    assert merged["bert_mask"].shape == merged["msa"].shape and bias.shape[0] == merged["msa"].shape[0]
+    merged["cluster_bias_mask"] = bias
     return process_final(merged)
 
 

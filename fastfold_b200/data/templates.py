@@ -263,7 +263,7 @@ def _check_residue_distances(all_positions: np.ndarray, all_positions_mask: np.n
 def _get_atom_positions(mmcif_object, auth_chain_id: str, max_ca_ca_distance: float) -> Tuple[np.ndarray, np.ndarray]:
     if auth_chain_id not in mmcif_object.chain_to_seqres:
         raise NoChainsError("chain %s not in %s" % (auth_chain_id, mmcif_object.file_id))
-    pos, mask = mmcif_parsing.get_atom_coords(mmcif_object, auth_chain_id)
+    pos, mask = mmcif_parsing.get_atom_coords(mmcif_object, auth_chain_id, _zero_center_positions=False)
     _check_residue_distances(pos, mask, max_ca_ca_distance)
     return pos, mask
 
@@ -398,11 +398,16 @@ class TemplateHitFeaturizer:
                 pdb_id, chain_id, hit.sum_probs, hit.index, e), None)
 
     # -- all hits ------------------------------------------------------------
-    def get_templates(self, query_sequence: str, hits: Sequence[parsers.TemplateHit], query_pdb_code: Optional[str] = None,
-                      query_release_date: Optional[datetime.datetime] = None) -> TemplateSearchResult:
-        """``query_pdb_code`` / ``query_release_date`` (training on PDB entries): the query's own entry is never its
-        template, and the date cutoff moves to 60 days before the query's release when that is earlier than
-        ``max_template_date`` (fastfold/data/templates.py:1000-1063)."""
+    def get_templates(self, query_sequence: str, query_release_date: Optional[datetime.datetime] = None,
+                      hits: Optional[Sequence[parsers.TemplateHit]] = None, query_pdb_code: Optional[str] = None) -> TemplateSearchResult:
+        """Argument order of fastfold/data/templates.py:995-1001; ``get_templates(query_sequence, hits)`` (the order of the
+        hmmsearch featurizer, :1110-1114) is understood too.  ``query_pdb_code`` / ``query_release_date`` (training on PDB
+        entries): the query's own entry is never its template, and the date cutoff moves to 60 days before the query's
+        release when that is earlier than ``max_template_date`` (:1003-1063)."""
+        if hits is None and isinstance(query_release_date, (list, tuple)):
+            hits, query_release_date = query_release_date, None
+        if hits is None:
+            raise TypeError("get_templates() needs the template hits")
         log.info("Searching for template for: %s", query_sequence)
         collected = {k: [] for k in TEMPLATE_FEATURES}
         errors, warnings = [], []
@@ -476,7 +481,7 @@ class HmmsearchHitFeaturizer(TemplateHitFeaturizer):
 
     def get_templates(self, query_sequence, hits, query_pdb_code=None, query_release_date=None):
         ordered = [dataclasses.replace(h, sum_probs=float(len(hits) - i)) if h.sum_probs is None else h for i, h in enumerate(hits)]
-        res = super().get_templates(query_sequence, ordered, query_pdb_code, query_release_date)
+        res = super().get_templates(query_sequence, query_release_date=query_release_date, hits=ordered, query_pdb_code=query_pdb_code)
         feats = dict(res.features)
         feats["template_sum_probs"] = np.zeros_like(feats["template_sum_probs"])
         return TemplateSearchResult(features=feats, errors=res.errors, warnings=res.warnings)

@@ -14,7 +14,7 @@ class HHBlits:
 
     def __init__(self, *, binary_path: str, databases: Sequence[str], n_cpu: int = 4, n_iter: int = 3, e_value: float = 0.001,
                  maxseq: int = 1_000_000, realign_max: int = 100_000, maxfilt: int = 100_000, min_prefilter_hits: int = 1000,
-                 all_seqs: bool = False, alt: Optional[int] = None, p: int = 20, z: int = 500):
+                 all_seqs: bool = False, alt: Optional[int] = None, p: int = 20, z: int = 500, cov: int = 0):
         self.binary_path = _need_binary(binary_path, "hhblits")
         self.databases = list(databases)
         for db in self.databases:
@@ -23,6 +23,7 @@ class HHBlits:
         self.n_cpu, self.n_iter, self.e_value, self.maxseq = n_cpu, n_iter, e_value, maxseq
         self.realign_max, self.maxfilt, self.min_prefilter_hits = realign_max, maxfilt, min_prefilter_hits
         self.all_seqs, self.alt, self.p, self.z = all_seqs, alt, p, z
+        self.cov = cov              # minimum coverage of the query (%), 0 = no filter
 
     def query(self, input_fasta_path: str) -> Mapping[str, Any]:
         with tmpdir_manager() as tmp:
@@ -38,6 +39,8 @@ class HHBlits:
                 cmd += ["-p", str(self.p)]
             if self.z != 500:
                 cmd += ["-Z", str(self.z)]
+            if self.cov:
+                cmd += ["-cov", str(self.cov)]
             for db in self.databases:
                 cmd += ["-d", db]
             stdout, stderr = _run(cmd, "HHblits")

@@ -10,9 +10,10 @@ log = logging.getLogger(__name__)
 class Hmmbuild:
     """Profile HMM from an alignment (fastfold/data/tools/hmmbuild.py:25-137)."""
 
-    def __init__(self, *, binary_path: str, singlemer: bool = False):
+    def __init__(self, *, binary_path: str, singlemx: bool = False):
+        """``singlemx``: use the substitution score matrix also for alignments of more than one sequence."""
         self.binary_path = _need_binary(binary_path, "hmmbuild")
-        self.singlemer = singlemer
+        self.singlemx = singlemx
 
     def build_profile_from_sto(self, sto: str, model_construction: str = "fast") -> str:
         return self._build(sto, model_construction)
@@ -32,7 +33,7 @@ class Hmmbuild:
             cmd = [self.binary_path]
             if model_construction == "hand":
                 cmd.append("--hand")
-            if self.singlemer:
+            if self.singlemx:
                 cmd.append("--singlemx")
             _run(cmd + ["--amino", out, inp], "hmmbuild")
             return open(out).read()

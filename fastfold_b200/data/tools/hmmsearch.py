@@ -13,12 +13,14 @@ log = logging.getLogger(__name__)
 class Hmmsearch:
     """Search a profile HMM against a sequence database (fastfold/data/tools/hmmsearch.py:27-139)."""
 
-    def __init__(self, *, binary_path: str, hmmbuild_binary_path: str, database_path: str, flags: Optional[Sequence[str]] = None):
+    def __init__(self, *, binary_path: str, hmmbuild_binary_path: str, database_path: str, n_cpu: int = 8,
+                 flags: Optional[Sequence[str]] = None):
         self.binary_path = _need_binary(binary_path, "hmmsearch")
         self.hmmbuild_runner = Hmmbuild(binary_path=hmmbuild_binary_path)
         if not os.path.exists(database_path):
             raise ValueError("Could not find hmmsearch database %s" % database_path)
         self.database_path = database_path
+        self.n_cpu = n_cpu
         if flags is None:      # defaults of the multimer template search
             flags = ["--F1", "0.1", "--F2", "0.1", "--F3", "0.1", "--incE", "100", "-E", "100", "--domE", "100", "--incdomE", "100"]
         self.flags = list(flags)
@@ -36,7 +38,7 @@ class Hmmsearch:
             sto = os.path.join(out_dir, "hmm_output.sto")
             with open(hmm_path, "w") as f:
                 f.write(hmm)
-            cmd = [self.binary_path, "--noali", "--cpu", "8"] + self.flags + ["-A", sto, hmm_path, self.database_path]
+            cmd = [self.binary_path, "--noali", "--cpu", str(self.n_cpu)] + self.flags + ["-A", sto, hmm_path, self.database_path]
             _run(cmd, "hmmsearch (%s)" % os.path.basename(self.database_path))
             return open(sto).read()
 

@@ -83,7 +83,12 @@ class ExtraMSABlock(nn.Module):
     def forward(self, m, z, msa_mask, pair_mask, chunk_size=None, _chunk_logits=1024, _mask_trans=True):
         if self.is_multimer:
             z = z + self.core.outer_product_mean(m, mask=msa_mask, chunk_size=chunk_size)
-        m = m + self.msa_dropout_layer(self.msa_att_row(m.clone(), z=z.clone(), mask=msa_mask, chunk_size=chunk_size))
+        # with gradients the row attention runs ``_chunk_logits`` rows at a time (checkpointed when the block is): the
+        # logits of all N_extra rows at once are what makes this stack run out of memory in training
+        grad = torch.is_grad_enabled()
+        m = m + self.msa_dropout_layer(self.msa_att_row(m.clone(), z=z.clone(), mask=msa_mask, chunk_size=chunk_size,
+                                                        _chunk_logits=_chunk_logits if grad else None,
+                                                        _checkpoint_chunks=self.ckpt if grad else False))
         m = m + self.msa_att_col(m, mask=msa_mask, chunk_size=chunk_size)
         if self.is_multimer:
             c = self.core

@@ -32,7 +32,29 @@ class MSAAttention(nn.Module):
             z = permute_final_dims(z, (2, 0, 1)).unsqueeze(-4)
         return m, mask_bias, z
 
-    def forward(self, m, z=None, mask=None, chunk_size=None):
+    def _chunked_rows(self, m, z, mask, rows_per_chunk, checkpoint):
+        """Rows of the alignment attend independently: evaluate ``rows_per_chunk`` of them at a time, so that only their
+        logits ``[rows, H, N, N]`` exist at once, each piece under activation checkpointing when ``checkpoint`` is set -
+        the memory bound that makes the extra-MSA stack (thousands of rows) trainable
+        (fastfold/model/nn/msa.py:117-161)."""
+        m, mask_bias, z = self._prep_inputs(m, z, mask)
+
+        def piece(m_c, mask_c, z_b):
+            return self.mha(q_x=m_c, kv_x=m_c, biases=[mask_c] + ([z_b] if z_b is not None else []))
+
+        outs = []
+        for s in range(0, m.shape[-3], rows_per_chunk):
+            m_c, mask_c = m[..., s:s + rows_per_chunk, :, :], mask_bias[..., s:s + rows_per_chunk, :, :, :]
+            if checkpoint and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint as ckpt
+                outs.append(ckpt(piece, m_c, mask_c, z, use_reentrant=False))
+            else:
+                outs.append(piece(m_c, mask_c, z))
+        return torch.cat(outs, dim=-3)
+
+    def forward(self, m, z=None, mask=None, chunk_size=None, _chunk_logits=None, _checkpoint_chunks=None):
+        if _chunk_logits is not None:
+            return self._chunked_rows(m, z, mask, _chunk_logits, bool(_checkpoint_chunks))
         m, mask_bias, z = self._prep_inputs(m, z, mask)
         biases = [mask_bias]
         if z is not None:

@@ -56,15 +56,16 @@ class PointProjection(nn.Module):
     ``[head][x | y | z][point]`` (fastfold/model/nn/structure_module.py:160-193); returns global-frame points
     ``[*, N, H, P, 3]``."""
 
-    def __init__(self, c_hidden, num_points, no_heads):
+    def __init__(self, c_hidden, num_points, no_heads, return_local_points=False):
         super().__init__()
-        self.no_heads, self.num_points = no_heads, num_points
+        self.no_heads, self.num_points, self.return_local_points = no_heads, num_points, return_local_points
         self.linear = Linear(c_hidden, no_heads * 3 * num_points)
 
     def forward(self, activations, rigids):
         p = self.linear(activations)
         p = p.reshape(*p.shape[:-1], self.no_heads, 3, self.num_points).transpose(-1, -2)       # [*, N, H, P, 3]
-        return rigids[..., None, None].apply(p)
+        g = rigids[..., None, None].apply(p)
+        return (g, p) if self.return_local_points else g
 
 
 class InvariantPointAttention(nn.Module):

@@ -149,8 +149,14 @@ class LayerNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(*normalized_shape))
         self.bias = nn.Parameter(torch.zeros(*normalized_shape))
 
+    def reset_parameters(self):
+        nn.init.ones_(self.weight)
+        nn.init.zeros_(self.bias)
+
     def forward(self, x):
         return layer_norm(x, self.weight, self.bias, self.eps)
+
+    kernel_forward = forward       # the reference's forward chunks long inputs and calls this per chunk (kernel/layer_norm.py:36-60)
 
     def extra_repr(self):
         return "%s, eps=%g" % (tuple(self.normalized_shape), self.eps)

@@ -31,7 +31,14 @@ def atom14_to_atom37(atom14_data, aatype):
     return out * mask.reshape(mask.shape + (1,) * extra).to(out.dtype)
 
 
-def atom37_to_atom14(atom37_data, aatype):
+def atom37_to_atom14(atom37_data, aatype, all_atom_mask=None):
+    """``atom37_to_atom14(data [*, N, 37, ...], aatype)`` gathers any per-atom quantity into the 14-slot layout (slots a
+    residue type does not have are zeroed).  The reference's call, ``atom37_to_atom14(aatype, all_atom_pos, all_atom_mask)
+    -> (positions14, mask14)`` (fastfold/utils/all_atom_multimer.py:57-79), is recognised by its third argument."""
+    if all_atom_mask is not None:
+        aatype, positions = atom37_data, aatype
+        mask14 = atom37_to_atom14(all_atom_mask.to(torch.float32), aatype)
+        return atom37_to_atom14(positions, aatype) * mask14[..., None].to(positions.dtype), mask14
     idx = _table(rc.restype_atom14_to_atom37, aatype).long()
     mask = get_atom14_mask(aatype)
     extra = atom37_data.dim() - idx.dim()

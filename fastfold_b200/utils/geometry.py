@@ -201,9 +201,10 @@ class Rot3Array:
         return cls(e0.x, e1.x, e2.x, e0.y, e1.y, e2.y, e0.z, e1.z, e2.z)
 
     @classmethod
-    def from_quaternion(cls, w, x, y, z, normalize=True, epsilon=1e-6):
+    def from_quaternion(cls, w, x, y, z, normalize=True, eps=1e-6, epsilon=None):
+        eps = eps if epsilon is None else epsilon
         if normalize:
-            inv = torch.rsqrt(torch.clamp(w * w + x * x + y * y + z * z, min=epsilon))
+            inv = torch.rsqrt(torch.clamp(w * w + x * x + y * y + z * z, min=eps))
             w, x, y, z = w * inv, x * inv, y * inv, z * inv
         return cls(1 - 2 * (y * y + z * z), 2 * (x * y - w * z), 2 * (x * z + w * y), 2 * (x * y + w * z), 1 - 2 * (x * x + z * z),
                    2 * (y * z - w * x), 2 * (x * z - w * y), 2 * (y * z + w * x), 1 - 2 * (x * x + y * y))

@@ -73,72 +73,80 @@ def tree_map(fn, tree, leaf_type):
 tensor_tree_map = partial(tree_map, leaf_type=torch.Tensor)
 
 
-def _fetch_dims(tree):
-    shapes = []
+def _leaves(tree):
+    """Tensors of a nest of dicts / lists / tuples, depth first."""
+    if isinstance(tree, torch.Tensor):
+        return [tree]
     if isinstance(tree, dict):
-        for v in tree.values():
-            shapes.extend(_fetch_dims(v))
-    elif isinstance(tree, (list, tuple)):
-        for t in tree:
-            shapes.extend(_fetch_dims(t))
-    elif isinstance(tree, torch.Tensor):
-        shapes.append(tree.shape)
+        tree = tree.values()
+    elif not isinstance(tree, (list, tuple)):
+        raise ValueError("unsupported tree node %r" % type(tree))
+    return [t for sub in tree for t in _leaves(sub)]
+
+
+def _fetch_dims(tree):
+    return [t.shape for t in _leaves(tree)]
+
+
+def _store(dst, src, lo, hi):
+    """Writes the leaves of ``src`` into rows ``lo:hi`` of the matching leaves of ``dst`` (same nesting)."""
+    if isinstance(src, torch.Tensor):
+        dst[lo:hi] = src
+    elif isinstance(src, dict):
+        for k, v in src.items():
+            _store(dst[k], v, lo, hi)
+    elif isinstance(src, (list, tuple)):
+        for d, v in zip(dst, src):
+            _store(d, v, lo, hi)
     else:
-        raise ValueError("unsupported tree node")
-    return shapes
+        raise ValueError("unsupported layer output %r" % type(src))
 
 
-def chunk_layer(layer, inputs, chunk_size, no_batch_dims):
-    """Applies ``layer(**inputs)`` over flattened leading (batch-like) dims in pieces of ``chunk_size``.
+def chunk_layer(layer, inputs, chunk_size, no_batch_dims, low_mem=False):
+    """Runs ``layer(**inputs)`` on ``chunk_size`` batch entries at a time and reassembles the result.
 
-    Inputs are broadcast against each other over their first ``no_batch_dims`` dims, flattened to one
-    batch dim, sliced, run, and the outputs (tensor / tuple / dict) reassembled - OpenFold's chunking
-    technique (supplement 1.11.8), same contract as fastfold/utils/tensor_utils.py:298-415.
+    The first ``no_batch_dims`` dims of every input tensor are batch-like and broadcast against each other; their product
+    is the number of entries.  An input whose batch dims are all 1 (a bias shared by every entry) is handed to the layer
+    whole.  Outputs (tensor, tuple / list or dict of tensors, nested) come back with the broadcast batch dims restored.
+    By default every other input is expanded and flattened to one batch dim up front, which copies inputs that were
+    broadcast; with ``low_mem`` only the entries of the current chunk are gathered from the un-flattened (expanded, not
+    copied) input.  Contract of fastfold/utils/tensor_utils.py:298-415 (OpenFold's chunking, AlphaFold supplement 1.11.8).
     """
-    if not len(inputs) > 0:
+    shapes = _fetch_dims(inputs)
+    if not shapes:
         raise ValueError("Must provide at least one input")
-    initial_dims = [shape[:no_batch_dims] for shape in _fetch_dims(inputs)]
-    orig_batch_dims = tuple(max(s) for s in zip(*initial_dims))
+    batch = tuple(max(dims) for dims in zip(*[sh[:no_batch_dims] for sh in shapes]))
+    total = 1
+    for d in batch:
+        total *= d
 
-    def prep(t):
-        # inputs whose batch dims are all 1 (e.g. a bias shared by every row) stay un-expanded and are not sliced
-        if not sum(t.shape[:no_batch_dims]) == no_batch_dims:
-            t = t.expand(orig_batch_dims + t.shape[no_batch_dims:])
-        return t.reshape(-1, *t.shape[no_batch_dims:])
+    def shared(t):
+        return all(d == 1 for d in t.shape[:no_batch_dims])
 
-    prepped = tensor_tree_map(prep, inputs)
-    flat_batch_dim = 1
-    for d in orig_batch_dims:
-        flat_batch_dim *= d
-    no_chunks = flat_batch_dim // chunk_size + (flat_batch_dim % chunk_size != 0)
-    i = 0
+    def flatten(t):
+        rest = t.shape[no_batch_dims:]
+        return t.reshape(1, *rest) if shared(t) else t.expand(batch + rest).reshape(total, *rest)
+
+    staged = inputs if low_mem else tensor_tree_map(flatten, inputs)
     out = None
-    for _ in range(no_chunks):
-        def sel(t):
-            return t[i:i + chunk_size] if t.shape[0] != 1 else t
-        chunks = tensor_tree_map(sel, prepped)
-        output_chunk = layer(**chunks)
-        if out is None:
-            alloc = lambda t: t.new_zeros((flat_batch_dim,) + t.shape[1:])
-            out = tensor_tree_map(alloc, output_chunk)
-        if isinstance(output_chunk, dict):
-            def assign(d1, d2):
-                for k, v in d1.items():
-                    if isinstance(v, dict):
-                        assign(v, d2[k])
-                    else:
-                        v[i:i + chunk_size] = d2[k]
-            assign(out, output_chunk)
-        elif isinstance(output_chunk, tuple):
-            for x1, x2 in zip(out, output_chunk):
-                x1[i:i + chunk_size] = x2
-        elif isinstance(output_chunk, torch.Tensor):
-            out[i:i + chunk_size] = output_chunk
+    for lo in range(0, total, chunk_size):
+        hi = min(total, lo + chunk_size)
+        if low_mem:
+            where = torch.unravel_index(torch.arange(lo, hi), batch)
+
+            def take(t):
+                rest = t.shape[no_batch_dims:]
+                if shared(t):
+                    return t.reshape(1, *rest)
+                return t.expand(batch + rest)[tuple(w.to(t.device) for w in where)]
         else:
-            raise ValueError("unsupported layer output")
-        i += chunk_size
-    reshape = lambda t: t.view(orig_batch_dims + t.shape[1:])
-    return tensor_tree_map(reshape, out)
+            def take(t):
+                return t if t.shape[0] == 1 else t[lo:hi]
+        piece = layer(**tensor_tree_map(take, staged))
+        if out is None:
+            out = tensor_tree_map(lambda t: t.new_empty((total,) + t.shape[1:]), piece)
+        _store(out, piece, lo, hi)
+    return tensor_tree_map(lambda t: t.reshape(batch + t.shape[1:]), out)
 
 
 _CONST_CACHE = {}

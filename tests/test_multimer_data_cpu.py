@@ -134,3 +134,41 @@ def test_lean_multimer_embedders_match_reference_modules():
         out0, out1 = base(feats), fast(feats)
     assert torch.allclose(out0["final_atom_positions"], out1["final_atom_positions"], atol=5e-3)
     assert torch.allclose(out0["pair"], out1["pair"], atol=2e-3)
+
+
+def test_cluster_bias_and_bert_masks_follow_the_block_structure():
+    """fastfold/data/msa_pairing.py:287-330 and data_transforms_multimer.py:83-119, 253-289."""
+    import torch
+    from fastfold_b200.config import model_config
+    from fastfold_b200.data import data_transforms_multimer as dtm
+    a = _chain("ACDEFGHIKL", ["ACDEFGHIKV", "ACDEYGHIKL", "AADEFGHIKL"], ["HUMAN", "MOUSE", "YEAST"], 1)
+    b = _chain("MNPQRSTV", ["MNPQRSTA", "MNPQKSTV"], ["MOUSE", "HUMAN"], 2)
+    ex = mp.pair_and_merge(mp.add_assembly_features({"0_A": a, "1_B": b}))
+    # paired: only the first row is pinned; paired rows may be scored everywhere, block rows only inside their own chain
+    assert ex["cluster_bias_mask"][0] == 1 and ex["cluster_bias_mask"][1:].sum() == 0
+    assert (ex["bert_mask"][:3] == 1).all()
+    gap = mp.MSA_GAP_IDX
+    for row, scored in zip(ex["msa"][3:], ex["bert_mask"][3:]):
+        own = slice(0, 10) if (row[10:] == gap).all() else slice(10, 18)
+        assert scored[own].all() and scored.sum() == (own.stop - own.start)
+    # homomer (no pairing): the first row of every chain's block is pinned
+    h = mp.pair_and_merge(mp.add_assembly_features({"0_A": _chain("ACDEFGHIKL", ["ACDEFGHIKV"], ["HUMAN"], 1),
+                                                     "1_B": _chain("ACDEFGHIKL", ["ACDEFGHIKV"], ["HUMAN"], 1)}))
+    pinned = np.nonzero(h["cluster_bias_mask"])[0]
+    assert len(pinned) == 2 and pinned[0] == 0 and (h["msa"][pinned[1]][:10] == gap).all()
+    # sampling: pinned rows always come first, empty (padding) rows always last, whatever the seed
+    padded = mp.pad_msa(h, 12)
+    t = {k: torch.tensor(np.asarray(v)) for k, v in padded.items() if np.asarray(v).dtype != object}
+    t["msa_mask"] = torch.cat([torch.ones(h["msa"].shape), torch.zeros(12 - h["msa"].shape[0], 20)])
+    n_real = h["msa"].shape[0]
+    for seed in range(5):
+        s = dtm.sample_msa({k: v.clone() for k, v in t.items()}, max_seq=n_real, max_extra_msa_seq=4, seed=seed)
+        assert s["msa_mask"].sum(-1).min() > 0 and s["extra_msa_mask"].sum() == 0          # every real row before any padding row
+        first_two = {tuple(r.tolist()) for r in s["msa"][:2]}
+        assert first_two == {tuple(h["msa"][p].tolist()) for p in pinned}
+    # corruption: positions outside a row's own chain are never scored
+    cfg = model_config("multimer")
+    tens = {k: torch.tensor(np.asarray(v)) for k, v in ex.items() if np.asarray(v).dtype != object}
+    tens = dtm.make_msa_profile(tens)
+    out = dtm.make_masked_msa(tens, cfg.data.common.masked_msa, replace_fraction=0.9, seed=0)
+    assert (out["bert_mask"] <= torch.tensor(ex["bert_mask"])).all() and out["bert_mask"].sum() > 0

@@ -390,3 +390,46 @@ def test_remaining_small_names():
     assert out["atom14_gt_exists"][0].sum() == 4 and out["atom14_atom_is_ambiguous"][5].sum() == 2      # GLY has 4 atoms; ASP OD1 / OD2
     import os
     assert os.path.isdir(residue_constants.get_cache_path())
+
+
+def test_alignment_and_structure_indices(tmp_path):
+    """Search outputs of all targets concatenated into one file + an index of byte ranges (fastfold/data/data_pipeline.py:792-843,
+    1000-1021; data_modules.py:168-209) give the same features as one directory per target."""
+    from fastfold_b200.data.data_modules import OpenFoldSingleDataset
+    seqs = {"1abc_A": "MKTAYIAKQRQ", "2xyz_A": "GSHMLEDPVK"}
+    aln, flat, data = tmp_path / "aln", tmp_path / "flat", tmp_path / "data"
+    flat.mkdir(), data.mkdir()
+    index, blob = {}, b""
+    for name, seq in seqs.items():
+        (aln / name).mkdir(parents=True)
+        a3m = ">query\n%s\n>hit1\n%s\n>hit2\n%s-\n" % (seq, seq[:-1] + "A", seq[:-1])
+        sto = "# STOCKHOLM 1.0\nquery %s\nother %s\n//\n" % (seq, "A" + seq[1:])
+        files = {"bfd_uniclust_hits.a3m": a3m, "mgnify_hits.sto": sto}
+        entries = []
+        for fname, text in files.items():
+            (aln / name / fname).write_text(text)
+            entries.append([fname, len(blob), len(text.encode())])
+            blob += text.encode()
+        index[name] = {"db": "alignments.db", "files": entries}
+        prot = protein.Protein(atom_positions=np.random.RandomState(len(seq)).randn(len(seq), 37, 3).astype(np.float32),
+                               aatype=np.array([rc.restype_order[c] for c in seq]), atom_mask=np.tile(np.array(rc.restype_atom37_mask)[[rc.restype_order[c] for c in seq]], 1).astype(np.float32),
+                               residue_index=np.arange(len(seq)), b_factors=np.full((len(seq), 37), 90.0), chain_index=np.zeros(len(seq), dtype=np.int64))
+        (data / (name.split("_")[0] + ".pdb")).write_text(protein.to_pdb(prot))
+    (flat / "alignments.db").write_bytes(blob)
+    by_dir = OpenFoldSingleDataset(str(data), str(aln), config=None, mode="train", _output_raw=True)
+    by_index = OpenFoldSingleDataset(str(data), str(flat), config=None, mode="train", _output_raw=True, _alignment_index=index)
+    assert sorted(by_index._chain_ids) == sorted(seqs)
+    for name in seqs:
+        a, b = by_dir[by_dir.chain_id_to_idx(name)], by_index[by_index.chain_id_to_idx(name)]
+        assert a["msa"].shape[0] == 4 and set(a) == set(b)           # query + 2 a3m hits + 1 stockholm row (duplicate query dropped)
+        for k in a:
+            if a[k].dtype != object:
+                assert np.array_equal(a[k], b[k]), k
+    # structure index: the PDB text as a byte range of one concatenated file beside the path
+    texts = [(data / "1abc.pdb").read_text(), (data / "2xyz.pdb").read_text()]
+    (data / "structures.db").write_text("".join(texts))
+    sidx = {"db": "structures.db", "files": [["2xyz.pdb", len(texts[0].encode()), len(texts[1].encode())]]}
+    p = dp.DataPipeline(None)
+    via_index = p.process_pdb(str(data / "missing.pdb"), None, is_distillation=False, _structure_index=sidx)
+    direct = p.process_pdb(str(data / "2xyz.pdb"), None, is_distillation=False)
+    assert np.array_equal(via_index["all_atom_positions"], direct["all_atom_positions"]) and np.array_equal(via_index["aatype"], direct["aatype"])

@@ -41,7 +41,10 @@ def test_mmcif_reader():
     assert obj.header["release_date"] == "1999-05-01" and abs(obj.header["resolution"] - 1.8) < 1e-6
     assert obj.seqres_to_structure["A"][3].is_missing and not obj.seqres_to_structure["A"][4].is_missing
     assert obj.seqres_to_structure["A"][0].position.residue_number == 11
-    pos, mask = mmcif_parsing.get_atom_coords(obj, "A")
+    pos, mask = mmcif_parsing.get_atom_coords(obj, "A", _zero_center_positions=False)
+    centred, _ = mmcif_parsing.get_atom_coords(obj, "A")               # default: resolved atoms translated to zero mean
+    assert np.abs(centred[mask.astype(bool)].mean(axis=0)).max() < 1e-4
+    assert np.allclose((centred - pos)[mask.astype(bool)], (centred - pos)[mask.astype(bool)][0], atol=1e-4)
     assert pos.shape == (len(SEQ), 37, 3) and mask[3].sum() == 0 and mask[0, rc.atom_order["CA"]] == 1
     assert np.allclose(pos[2, rc.atom_order["CA"]], [3.8 * 2 + 0.1, 2.0, -1.5], atol=1e-3)
 
@@ -75,9 +78,9 @@ def test_template_featurizer(tmp_path):
     assert feats["template_sequence"][0].decode() == "--" + SEQ + "--"
     assert abs(feats["template_sum_probs"][0, 0] - 12.0) < 1e-6
     # training on PDB entries: the query's own entry is never its template, and the date cutoff follows the query
-    assert f.get_templates(query, [hit, late], query_pdb_code="1ABC").features["template_aatype"].shape[0] == 0
-    assert f.get_templates(query, [hit, late], query_release_date="1999-06-01").features["template_aatype"].shape[0] == 0    # 60-day margin
-    assert f.get_templates(query, [hit, late], query_release_date="1999-09-01").features["template_aatype"].shape[0] == 1
+    assert f.get_templates(query, hits=[hit, late], query_pdb_code="1ABC").features["template_aatype"].shape[0] == 0
+    assert f.get_templates(query, "1999-06-01", [hit, late]).features["template_aatype"].shape[0] == 0    # 60-day margin
+    assert f.get_templates(query, hits=[hit, late], query_release_date="1999-09-01").features["template_aatype"].shape[0] == 1
     assert f.get_templates(query, [hit, late]).features["template_aatype"].shape[0] == 1                                        # cutoff restored
     from fastfold_b200.data.data_pipeline import make_template_features
     assert make_template_features(query, {"pdb70_hits.hhr": [hit, late]}, f, query_pdb_code="1abc")["template_aatype"].shape == (0, len(query), 22)
