@@ -134,7 +134,9 @@ def process_tensors(batch, common_cfg, mode_cfg, seed=0):
     batch = make_msa_profile(batch)
     batch = sample_msa(batch, mode_cfg.max_msa_clusters, mode_cfg.max_extra_msa, seed=seed)
     if "masked_msa" in common_cfg:
-        batch = make_masked_msa(batch, common_cfg.masked_msa, mode_cfg.masked_msa_replace_fraction, seed=seed)
+        # a different stream from the one that ordered the rows (fastfold/data/input_pipeline_multimer.py:68-74)
+        batch = make_masked_msa(batch, common_cfg.masked_msa, mode_cfg.masked_msa_replace_fraction,
+                                seed=None if seed is None else seed + 1)
     batch["extra_msa_mask"] = batch["extra_msa_mask"].float()
     batch["extra_deletion_matrix"] = batch["extra_deletion_matrix"].float()
     batch = nearest_neighbor_clusters(batch)

@@ -16,7 +16,7 @@ import torch.nn as nn
 from ...common import residue_constants as rc
 from ...utils.tensor_utils import const_like, tensor_tree_map
 from ..nn import embedders_multimer as ref
-from ..nn.embedders_multimer import _backbone_frames_and_mask, _one_hot, _pseudo_beta
+from ..nn.embedders_multimer import _backbone_frames_and_mask, _one_hot, _template_pseudo_beta
 
 
 class InputEmbedderMultimer(ref.InputEmbedderMultimer):
@@ -75,7 +75,7 @@ class TemplateEmbedderMultimer(ref.TemplateEmbedderMultimer):
             single = tensor_tree_map(lambda t: torch.index_select(t, templ_dim, idx).squeeze(templ_dim), batch)
             pos = single["template_all_atom_positions"].float()
             msk = single["template_all_atom_mask"].float()
-            pb, pb_mask = _pseudo_beta(single["template_aatype"], pos, msk)
+            pb, pb_mask = _template_pseudo_beta(single, pos, msk)
             d2 = torch.sum((pb[..., None, :] - pb[..., None, :, :]) ** 2, dim=-1, keepdim=True)
             lower = torch.linspace(dist["min_bin"], dist["max_bin"], dist["no_bins"], device=pos.device) ** 2
             upper = torch.cat([lower[1:], const_like(lower, [self.config.inf], "inf_%r" % (self.config.inf,))], dim=-1)

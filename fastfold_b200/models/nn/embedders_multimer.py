@@ -135,11 +135,22 @@ class TemplateSingleEmbedderMultimer(nn.Module):
 
 
 def _backbone_frames_and_mask(aatype, all_atom_positions, all_atom_mask):
+    """Backbone frames in the multimer convention - origin CA, C on the POSITIVE x axis, N in the xy plane with y > 0
+    (fastfold/utils/all_atom_multimer.py:447-493) - which is the monomer frame turned by 180 degrees about y.  Written
+    through ``from_3_points``, whose first argument lies on the negative x axis: the mirror image of C through CA."""
     n, ca, c = (rc.atom_order[a] for a in ("N", "CA", "C"))
-    frames = Rigid.from_3_points(p_neg_x_axis=all_atom_positions[..., c, :], origin=all_atom_positions[..., ca, :],
+    origin = all_atom_positions[..., ca, :]
+    frames = Rigid.from_3_points(p_neg_x_axis=2.0 * origin - all_atom_positions[..., c, :], origin=origin,
                                  p_xy_plane=all_atom_positions[..., n, :], eps=1e-8)
     mask = all_atom_mask[..., n] * all_atom_mask[..., ca] * all_atom_mask[..., c]
     return frames, mask
+
+
+def _template_pseudo_beta(single, positions, masks):
+    """The pseudo-beta atoms the data pipeline stored with the template (``make_pseudo_beta("template_")``), else computed."""
+    if "template_pseudo_beta" in single and "template_pseudo_beta_mask" in single:
+        return single["template_pseudo_beta"].float(), single["template_pseudo_beta_mask"].float()
+    return _pseudo_beta(single["template_aatype"], positions, masks)
 
 
 def _pseudo_beta(aatype, positions, masks):
@@ -168,7 +179,7 @@ class TemplateEmbedderMultimer(nn.Module):
             single = tensor_tree_map(lambda t: torch.index_select(t, templ_dim, idx).squeeze(templ_dim), batch)
             pos = single["template_all_atom_positions"].float()
             msk = single["template_all_atom_mask"].float()
-            pb, pb_mask = _pseudo_beta(single["template_aatype"], pos, msk)
+            pb, pb_mask = _template_pseudo_beta(single, pos, msk)
             d2 = torch.sum((pb[..., None, :] - pb[..., None, :, :]) ** 2, dim=-1, keepdim=True)
             lower = torch.linspace(dist["min_bin"], dist["max_bin"], dist["no_bins"], device=pos.device) ** 2
             upper = torch.cat([lower[1:], lower.new_tensor([self.config.inf])], dim=-1)

@@ -1,0 +1,88 @@
+"""Runs the installed reference package (``baseline/_ref``, with the import stand-ins of ``baseline/stubs``) on CPU as an
+oracle.  Started as a script in its own process - the reference is a package called ``fastfold`` and must not share an
+interpreter with this repository's ``fastfold`` compatibility namespace:
+
+    python reference_oracle.py <mode> <input.pt> <output.pt>
+
+``mode``: ``model`` (full ``AlphaFold`` forward in the OpenFold layout), ``loss`` (``AlphaFoldLoss`` with the per-term
+breakdown), ``multimer_parts`` (input embedder, structure module and template embedder of the multimer model, called
+one by one: the reference's OpenFold-layout trunk does not implement the multimer block ordering, so whole multimer
+models cannot be compared).  The input file holds the state dict (OpenFold names), the features and the config edits.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def _setup():
+    for name, typ in (("int", int), ("float", float), ("bool", bool), ("object", object)):
+        if not hasattr(np, name):                 # aliases numpy 2 dropped and the reference's tables still use
+            setattr(np, name, typ)
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "stubs"))
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    import fastfold
+    assert os.path.abspath(fastfold.__file__).startswith(os.path.join(ROOT, "baseline", "_ref")), fastfold.__file__
+
+
+def _config(d):
+    from fastfold.config import model_config
+    c = model_config(d["name"], train=d.get("train", False))
+    for key, value in d["edits"].items():
+        node = c
+        parts = key.split(".")
+        for p in parts[:-1]:
+            node = node[p]
+        node[parts[-1]] = value
+    c.globals.is_multimer = "multimer" in d["name"]
+    c.globals.inplace = False
+    c.globals.chunk_size = None
+    return c
+
+
+def _tensors(tree):
+    if torch.is_tensor(tree):
+        return tree
+    if hasattr(tree, "to_tensor_4x4"):
+        return tree.to_tensor_4x4()
+    if isinstance(tree, dict):
+        return {k: _tensors(v) for k, v in tree.items() if torch.is_tensor(v) or isinstance(v, dict) or hasattr(v, "to_tensor_4x4")}
+    return tree
+
+
+def main(mode, src, dst):
+    _setup()
+    d = torch.load(src, weights_only=False)
+    if mode == "loss":
+        from fastfold.model.hub.loss import AlphaFoldLoss
+        loss, parts = AlphaFoldLoss(_config(d).loss)(d["out"], d["batch"], _return_breakdown=True)
+        torch.save({"loss": float(loss), "parts": {k: float(v) for k, v in parts.items()}}, dst)
+        return
+    from fastfold.model.hub import AlphaFold
+    model = AlphaFold(_config(d)).eval()
+    own = model.state_dict()
+    res = {"missing": [k for k in own if k not in d["state"]], "unexpected": [k for k in d["state"] if k not in own]}
+    model.load_state_dict(d["state"], strict=False)
+    with torch.no_grad():
+        if mode == "model":
+            res["out"] = _tensors(model(d["batch"]))
+        elif mode == "multimer_parts":
+            f = d["f"]
+            res["sm"] = _tensors(model.structure_module(d["s"], d["z"], f["aatype"], mask=f["seq_mask"]))
+            m, z = model.input_embedder(f)
+            res["m"], res["z"] = m, z
+            pair_mask = f["seq_mask"][..., None] * f["seq_mask"][..., None, :]
+            asym = f["asym_id"]
+            templ = {k: v for k, v in f.items() if k.startswith("template_")}
+            res["te"] = _tensors(model.template_embedder(templ, z, pair_mask.to(z.dtype), 0, chunk_size=None,
+                                                         multichain_mask_2d=asym[..., None] == asym[..., None, :]))
+        else:
+            raise SystemExit("unknown mode %r" % mode)
+    torch.save(res, dst)
+
+
+if __name__ == "__main__":
+    main(*sys.argv[1:4])

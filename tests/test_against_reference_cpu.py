@@ -1,0 +1,121 @@
+"""The installed reference package as the oracle (CPU, fp32, identical weights through the shared OpenFold parameter names).
+
+Skipped when ``baseline/_ref`` is not installed.  The reference runs in a child process (tests/helpers/reference_oracle.py).
+Its fast modules need its CUDA / Triton kernels, so the comparison is with its OpenFold-layout modules - the same oracle
+its own tests use (tests/test_fastnn/test_evoformer_stack.py:16-46, tests/test_inference.py:30-76).
+"""
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE = os.path.join(ROOT, "tests", "helpers", "reference_oracle.py")
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "fastfold")),
+                                reason="the reference package is not installed under baseline/_ref")
+
+EDITS = {"model.evoformer_stack.no_blocks": 2, "model.extra_msa.extra_msa_stack.no_blocks": 1, "model.structure_module.no_blocks": 2}
+
+
+def _oracle(mode, payload, tmp_path):
+    src, dst = str(tmp_path / (mode + "_in.pt")), str(tmp_path / (mode + "_out.pt"))
+    torch.save(payload, src)
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, ORACLE, mode, src, dst], capture_output=True, text=True, timeout=900, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr[-3000:]
+    return torch.load(dst, weights_only=False)
+
+
+def _model(name, edits, train=False):
+    from fastfold_b200.config import model_config
+    from fastfold_b200.models.hub import AlphaFold
+    c = model_config(name, train=train)
+    for key, value in edits.items():
+        node = c
+        parts = key.split(".")
+        for p in parts[:-1]:
+            node = node[p]
+        node[parts[-1]] = value
+    torch.manual_seed(0)
+    model = AlphaFold(c).eval()
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():          # the stock initialisation ends every residual branch in a zero layer: randomise those
+        for p in model.parameters():
+            if float(p.abs().sum()) == 0.0:
+                p.copy_(torch.randn(p.shape, generator=g) * (0.02 if p.dim() < 2 else 0.5 / p.shape[-1] ** 0.5))
+    return c, model
+
+
+def _close(ours, ref, tol, what):
+    assert ours.shape == ref.shape, (what, tuple(ours.shape), tuple(ref.shape))
+    err = float((ours.float() - ref.float()).abs().max())
+    assert err <= tol * max(1.0, float(ref.abs().max())), "%s: max |diff| %.3e" % (what, err)
+
+
+def test_monomer_model_with_templates_recycling_and_tm_head(tmp_path):
+    from fastfold_b200.utils.synthetic import random_features
+    c, model = _model("model_1_ptm", EDITS)
+    batch = random_features(12, 5, 6, n_templ=2, n_recycle=1, seed=2)
+    with torch.no_grad():
+        out = model(batch)
+    ref = _oracle("model", {"name": "model_1_ptm", "edits": EDITS, "state": model.state_dict(), "batch": batch}, tmp_path)
+    assert ref["missing"] == [] and ref["unexpected"] == []            # the two packages name every parameter alike
+    compared = 0
+    for k, v in out.items():
+        if torch.is_tensor(v) and k in ref["out"]:
+            _close(v, ref["out"][k], 2e-5, k)
+            compared += 1
+    for k in ("frames", "sidechain_frames", "unnormalized_angles", "angles", "positions", "single"):
+        _close(out["sm"][k], ref["out"]["sm"][k], 2e-5, "sm." + k)
+    assert compared >= 16
+
+
+def test_every_loss_term(tmp_path):
+    from fastfold_b200.models.hub import AlphaFoldLoss
+    from fastfold_b200.utils.synthetic import random_features
+    from fastfold_b200.utils.tensor_utils import tensor_tree_map
+    edits = dict(EDITS, **{"loss.violation.weight": 1.0, "loss.experimentally_resolved.weight": 0.01})
+    c, model = _model("model_1_ptm", edits, train=True)
+    batch = random_features(12, 5, 6, n_templ=2, n_recycle=0, seed=2, supervised=True)
+    with torch.no_grad():
+        out = model(batch)
+    last = tensor_tree_map(lambda t: t[..., -1], batch)
+    # the violation statistics travel with the outputs: the reference would otherwise download its bond-length table
+    loss, parts = AlphaFoldLoss(c.loss)(out, last, _return_breakdown=True)
+    assert "violation" in out
+    ref = _oracle("loss", {"name": "model_1_ptm", "edits": edits, "train": True, "out": out, "batch": last}, tmp_path)
+    for k in ("distogram", "experimentally_resolved", "fape", "lddt", "masked_msa", "supervised_chi", "violation", "tm"):
+        assert math.isclose(float(parts[k]), ref["parts"][k], rel_tol=1e-5, abs_tol=1e-6), (k, float(parts[k]), ref["parts"][k])
+    assert math.isclose(float(loss), ref["loss"], rel_tol=1e-5)
+
+
+def test_multimer_embedders_and_structure_module(tmp_path):
+    """Input embedder (relative positions with chain and entity terms), structure module (point projections, quaternion
+    update) and template embedder (backbone frames with C on the positive x axis, chain-restricted masks) of the multimer
+    model.  The template pair stack runs in the reference's block order here; the model's default is tri-mul first."""
+    from fastfold_b200.utils.synthetic import random_features
+    from fastfold_b200.utils.tensor_utils import tensor_tree_map
+    edits = dict(EDITS, **{"model.template.template_pair_stack.tri_mul_first": False})
+    c, model = _model("multimer", edits)
+    f = tensor_tree_map(lambda t: t[..., -1], random_features(12, 5, 6, n_templ=2, n_recycle=0, seed=2, chains=[7, 5]))
+    g = torch.Generator().manual_seed(3)
+    s, z = torch.randn(12, 384, generator=g), torch.randn(12, 12, 128, generator=g)
+    with torch.no_grad():
+        sm = model.structure_module(s, z, f["aatype"], mask=f["seq_mask"])
+        m, zz = model.input_embedder(f)
+        pair_mask = f["seq_mask"][..., None] * f["seq_mask"][..., None, :]
+        asym = f["asym_id"]
+        te = model.template_embedder({k: v for k, v in f.items() if k.startswith("template_")}, zz, pair_mask.to(zz.dtype), 0, None,
+                                     multichain_mask_2d=asym[..., None] == asym[..., None, :])
+    ref_edits = {k: v for k, v in edits.items() if "tri_mul_first" not in k}
+    ref = _oracle("multimer_parts", {"name": "multimer", "edits": ref_edits, "state": model.state_dict(), "f": f, "s": s, "z": z}, tmp_path)
+    assert ref["missing"] == [] and ref["unexpected"] == []
+    _close(m, ref["m"], 1e-6, "input_embedder.m")
+    _close(zz, ref["z"], 1e-6, "input_embedder.z")
+    for k in ("sidechain_frames", "unnormalized_angles", "angles", "positions", "single"):
+        _close(sm[k], ref["sm"][k], 1e-5, "sm." + k)
+    for k in ("template_pair_embedding", "template_single_embedding", "template_mask"):
+        _close(te[k], ref["te"][k], 1e-5, "template." + k)
