@@ -481,14 +481,24 @@ def random_crop_to_size(protein, crop_size, max_templates, shape_schema, subsamp
     seq_length = int(protein["seq_length"])
     num_templates = protein["template_mask"].shape[-1] if "template_mask" in protein else 0
     num_res_crop_size = min(seq_length, crop_size)
-    n = seq_length - num_res_crop_size
-    right_anchor = n
-    if "use_clamped_fape" in protein and float(protein["use_clamped_fape"]) == 1.0:
-        right_anchor = n
-    num_res_crop_start = int(torch.randint(0, right_anchor + 1, (1,), generator=g)[0])
-    templ_start = int(torch.randint(0, num_templates + 1, (1,), generator=g)[0]) if (subsample_templates and num_templates) else 0
-    templates_select = torch.randperm(num_templates, generator=g) if num_templates else None
+
+    def draw(upper):                                   # uniform on 0 .. upper inclusive
+        return int(torch.randint(0, upper + 1, (1,), generator=g)[0])
+
+    # Draw order and distributions of fastfold/data/data_transforms.py:1165-1184 (so that equal seeds give equal crops):
+    # template window and permutation first; then the residue window - uniform over all positions for samples trained with
+    # the clamped FAPE, otherwise uniform below a bound that is itself drawn uniformly, which favours early windows.
+    templ_start, templates_select = 0, None
+    if subsample_templates and num_templates:
+        templ_start = draw(num_templates)
+        templates_select = torch.randperm(num_templates, generator=g)
     num_templates_crop = min(num_templates - templ_start, max_templates)
+    n = seq_length - num_res_crop_size
+    if "use_clamped_fape" in protein and float(protein["use_clamped_fape"]) == 1.0:
+        bound = n
+    else:
+        bound = n - draw(n)
+    num_res_crop_start = draw(bound)
     for k, v in protein.items():
         if k not in shape_schema or ("template" not in k and NUM_RES not in shape_schema[k]):
             continue

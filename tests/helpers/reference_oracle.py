@@ -4,7 +4,8 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``model`` (full ``AlphaFold`` forward in the OpenFold layout), ``loss`` (``AlphaFoldLoss`` with the per-term
+``mode``: ``features`` (the tensor pipeline on a raw feature dict: the un-ensembled transforms, then one ensemble member
+with the given seed and MSA resampling switched off), ``model`` (full ``AlphaFold`` forward in the OpenFold layout), ``loss`` (``AlphaFoldLoss`` with the per-term
 breakdown), ``multimer_parts`` (input embedder, structure module and template embedder of the multimer model, called
 one by one: the reference's OpenFold-layout trunk does not implement the multimer block ordering, so whole multimer
 models cannot be compared).  The input file holds the state dict (OpenFold names), the features and the config edits.
@@ -56,6 +57,21 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "features":
+        from fastfold.data import feature_pipeline, input_pipeline
+        config = _config(d)
+        raw = dict(d["raw"])
+        cfg, names = feature_pipeline.make_data_config(config.data, mode=d["mode"], num_res=int(raw["seq_length"][0]))
+        if "deletion_matrix_int" in raw:
+            raw["deletion_matrix"] = raw.pop("deletion_matrix_int").astype(np.float32)
+        t = feature_pipeline.np_to_tensor_dict(np_example=raw, features=names)
+        torch.manual_seed(d["torch_seed"])
+        with torch.no_grad():
+            t = input_pipeline.compose(input_pipeline.nonensembled_transform_fns(cfg.common, cfg[d["mode"]]))(t)
+            non = {k: v.clone() for k, v in t.items()}
+            ens = input_pipeline.compose(input_pipeline.ensembled_transform_fns(cfg.common, cfg[d["mode"]], d["seed"]))(dict(t))
+        torch.save({"non": non, "ens": ens}, dst)
+        return
     if mode == "loss":
         from fastfold.model.hub.loss import AlphaFoldLoss
         loss, parts = AlphaFoldLoss(_config(d).loss)(d["out"], d["batch"], _return_breakdown=True)

@@ -119,3 +119,61 @@ def test_multimer_embedders_and_structure_module(tmp_path):
         _close(sm[k], ref["sm"][k], 1e-5, "sm." + k)
     for k in ("template_pair_embedding", "template_single_embedding", "template_mask"):
         _close(te[k], ref["te"][k], 1e-5, "template." + k)
+
+
+def _raw_example(mode):
+    """A raw (numpy) feature dict: query, 40 aligned rows with deletions, two templates, and - for training - a structure."""
+    import numpy as np
+    from fastfold_b200.common import residue_constants as rc
+    from fastfold_b200.data import data_pipeline as dp
+    rng = np.random.RandomState(0)
+    letters = list("ACDEFGHIKLMNPQRSTVWY")
+    seq = "".join(rng.choice(letters, 30))
+    n = len(seq)
+    rows = [seq] + ["".join(c if rng.rand() > 0.3 else rng.choice(letters + ["-"]) for c in seq) for _ in range(40)]
+    dels = [[int(rng.rand() < 0.05) * int(rng.randint(1, 4)) for _ in range(n)] for _ in rows]
+    raw = dict(dp.make_sequence_features(seq, "q", n))
+    raw.update(dp.make_msa_features([rows], [dels]))
+    t = 2
+    raw.update({"template_aatype": np.eye(22, dtype=np.float32)[rng.randint(0, 22, (t, n))],
+                "template_all_atom_positions": (rng.randn(t, n, 37, 3) * 5).astype(np.float32),
+                "template_all_atom_mask": (rng.rand(t, n, 37) > 0.3).astype(np.float32), "template_sum_probs": rng.rand(t, 1).astype(np.float32),
+                "template_domain_names": np.array([b"1abc_A", b"2xyz_B"], dtype=object),
+                "template_sequence": np.array([b"A" * n, b"C" * n], dtype=object)})
+    if mode != "predict":
+        aatype = np.array([rc.restype_order[c] for c in seq])
+        raw.update({"all_atom_positions": (np.cumsum(rng.randn(n, 1, 3) * 2, 0) + rng.randn(n, 37, 3)).astype(np.float32),
+                    "all_atom_mask": (np.array(rc.restype_atom37_mask)[aatype] * (rng.rand(n, 37) > 0.1)).astype(np.float32),
+                    "resolution": np.array([2.0], np.float32), "is_distillation": np.array(0.0, np.float32)})
+    return raw
+
+
+@pytest.mark.parametrize("mode", ["predict", "train"])
+def test_feature_pipeline(mode, tmp_path):
+    """Every feature of the tensor pipeline - index maps, ground-truth frames and torsions, template features, MSA sampling,
+    BERT-style corruption, clustering, ``msa_feat`` / ``target_feat``, cropping and padding - with equal seeds.  (With MSA
+    resampling on, the reference draws a fresh random row order per recycling iteration, so that switch is off here.)"""
+    import numpy as np
+    from fastfold_b200.config import model_config
+    from fastfold_b200.data import data_pipeline as dp, feature_pipeline, input_pipeline
+    raw = _raw_example(mode)
+    edits = {"data.common.resample_msa_in_recycling": False}
+    ref = _oracle("features", {"name": "model_1", "train": mode == "train", "edits": edits, "raw": raw, "mode": mode, "seed": 7, "torch_seed": 5}, tmp_path)
+    config = model_config("model_1", train=mode == "train")
+    config.data.common.resample_msa_in_recycling = False
+    cfg, names = feature_pipeline.make_data_config(config.data, mode=mode, num_res=int(raw["seq_length"][0]))
+    example = dict(raw)
+    example["deletion_matrix"] = example.pop("deletion_matrix_int").astype(np.float32)
+    t = dp.np_to_tensor_dict(example, names)
+    torch.manual_seed(5)
+    with torch.no_grad():
+        t = input_pipeline.compose(input_pipeline.nonensembled_transform_fns(cfg.common, cfg[mode]))(t)
+        non = {k: v.clone() for k, v in t.items()}
+        ens = input_pipeline.compose(input_pipeline.ensembled_transform_fns(cfg.common, cfg[mode], 7))(dict(t))
+    for part, ours in (("non", non), ("ens", ens)):
+        assert set(ours) == set(ref[part]), (part, sorted(set(ours) ^ set(ref[part])))
+        for k, v in ref[part].items():
+            assert ours[k].shape == v.shape, (part, k, tuple(ours[k].shape), tuple(v.shape))
+            if v.numel():
+                assert float((ours[k].float() - v.float()).abs().max()) < 2e-4, (part, k)      # torsions of random (degenerate) template atoms
+    assert len(ens) >= (45 if mode == "train" else 25)
