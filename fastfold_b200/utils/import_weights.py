@@ -146,8 +146,13 @@ def _tri_mul(t):
         proj = _linear if t._outgoing else _linear_swapped
         return {"left_norm_input": _layer_norm(t.layer_norm_in), "projection": proj(t.linear_p), "gate": proj(t.linear_g),
                 "center_norm": _layer_norm(t.layer_norm_out), "output_projection": _linear(t.linear_z), "gating_linear": _linear(t.linear_gate)}
-    return {"layer_norm_input": _layer_norm(t.layer_norm_in), "left_projection": _linear(t.linear_a_p), "right_projection": _linear(t.linear_b_p),
-            "left_gate": _linear(t.linear_a_g), "right_gate": _linear(t.linear_b_g), "center_layer_norm": _layer_norm(t.layer_norm_out),
+    # The module computes outgoing as sum_k a[i,k] b[j,k] and incoming as sum_k a[k,i] b[k,j].  AlphaFold's incoming update is
+    # einsum('kjc,kic->ijc', left, right) = sum_k right[k,i] left[k,j]: its "left" is this module's b and its "right" this module's
+    # a, for projections and gates alike (fastfold/utils/import_weights.py:226-239).
+    left_p, right_p, left_g, right_g = ((t.linear_a_p, t.linear_b_p, t.linear_a_g, t.linear_b_g) if t._outgoing else
+                                        (t.linear_b_p, t.linear_a_p, t.linear_b_g, t.linear_a_g))
+    return {"layer_norm_input": _layer_norm(t.layer_norm_in), "left_projection": _linear(left_p), "right_projection": _linear(right_p),
+            "left_gate": _linear(left_g), "right_gate": _linear(right_g), "center_layer_norm": _layer_norm(t.layer_norm_out),
             "output_projection": _linear(t.linear_z), "gating_linear": _linear(t.linear_g)}
 
 

@@ -4,7 +4,8 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``features`` (the tensor pipeline on a raw feature dict: the un-ensembled transforms, then one ensemble member
+``mode``: ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
+``features`` (the tensor pipeline on a raw feature dict: the un-ensembled transforms, then one ensemble member
 with the given seed and MSA resampling switched off), ``model`` (full ``AlphaFold`` forward in the OpenFold layout), ``loss`` (``AlphaFoldLoss`` with the per-term
 breakdown), ``multimer_parts`` (input embedder, structure module and template embedder of the multimer model, called
 one by one: the reference's OpenFold-layout trunk does not implement the multimer block ordering, so whole multimer
@@ -79,6 +80,11 @@ def main(mode, src, dst):
         return
     from fastfold.model.hub import AlphaFold
     model = AlphaFold(_config(d)).eval()
+    if mode == "import_weights":
+        from fastfold.utils.import_weights import import_jax_weights_
+        import_jax_weights_(model, d["npz"], version=d["name"])
+        torch.save({"state": model.state_dict()}, dst)
+        return
     own = model.state_dict()
     res = {"missing": [k for k in own if k not in d["state"]], "unexpected": [k for k in d["state"] if k not in own]}
     model.load_state_dict(d["state"], strict=False)
