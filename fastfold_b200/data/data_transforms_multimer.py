@@ -17,7 +17,7 @@ def make_msa_profile(batch):
     """Profile over the 22 HH-suite classes of the whole alignment (masked mean)."""
     oh = dt.make_one_hot(batch["msa"], 22)
     mask = batch["msa_mask"][..., None]
-    batch["msa_profile"] = (oh * mask).sum(0) / (mask.sum(0) + 1e-10)
+    batch["msa_profile"] = (oh * mask).sum(0) / (mask.sum(0) + 1e-4)       # same smoothing as the reference's masked_mean
     return batch
 
 
@@ -51,10 +51,7 @@ def sample_msa(batch, max_seq, max_extra_msa_seq, seed=None, inf=1e6):
         bias = batch["cluster_bias_mask"].to(logits.dtype)
     else:
         bias = torch.nn.functional.pad(torch.zeros(batch["msa"].shape[0] - 1), (1, 0), value=1.0)
-    logits = logits + bias * inf
-    u = torch.rand(logits.shape, generator=g).clamp_(1e-6, 1 - 1e-6)
-    gumbel = -torch.log(-torch.log(u))
-    order = torch.argsort(logits + gumbel, descending=True)
+    order = gumbel_argsort_sample_idx(logits + bias * inf, generator=g)
     sel, extra = order[:max_seq], order[max_seq:max_seq + max_extra_msa_seq]
     for k in ("msa", "deletion_matrix", "msa_mask", "bert_mask"):
         if k in batch:
@@ -66,35 +63,42 @@ def sample_msa(batch, max_seq, max_extra_msa_seq, seed=None, inf=1e6):
 
 
 def make_masked_msa(batch, config, replace_fraction, seed=None, eps=1e-6):
+    """BERT-style corruption of the cluster centres (fastfold/data/data_transforms_multimer.py:70-120): a fraction of the
+    positions is redrawn from a mixture of the uniform amino-acid distribution, the alignment profile, the residue itself
+    and a mask token; the replacement is a Gumbel-max draw from the seeded generator.  Positions outside ``msa_mask`` are
+    never corrupted and end up as class 0.  Which positions are redrawn comes from the same generator here (the reference
+    takes them from the global random state)."""
     g = torch.Generator()
     g.manual_seed(seed) if seed is not None else g.seed()
     random_aa = torch.tensor([0.05] * 20 + [0.0, 0.0], dtype=torch.float32)
     probs = config.uniform_prob * random_aa + config.profile_prob * batch["msa_profile"] + config.same_prob * dt.make_one_hot(batch["msa"], 22)
     mask_prob = 1.0 - config.profile_prob - config.same_prob - config.uniform_prob
     probs = torch.nn.functional.pad(probs, (0, 1), value=mask_prob)
-    sh = batch["msa"].shape
-    mask_position = (torch.rand(sh, generator=g) < replace_fraction) & (batch["msa_mask"] > 0)
-    drawn = torch.multinomial(probs.reshape(-1, probs.shape[-1]) + eps, 1, generator=g).reshape(sh)
+    drawn = torch.argmax(gumbel_max_sample(torch.log(probs + eps), generator=g), dim=-1)
+    mask_position = (torch.rand(batch["msa"].shape, generator=g) < replace_fraction) & (batch["msa_mask"] > 0)
     # a ``bert_mask`` that comes with the features marks the positions that may be scored at all (a row's own chain)
     scored = mask_position.to(torch.float32)
     batch["bert_mask"] = batch["bert_mask"].to(torch.float32) * scored if "bert_mask" in batch else scored
     batch["true_msa"] = batch["msa"]
-    batch["msa"] = torch.where(mask_position, drawn, batch["msa"])
+    batch["msa"] = torch.where(mask_position, drawn, batch["msa"]) * batch["msa_mask"].to(batch["msa"].dtype)
     return batch
 
 
 def nearest_neighbor_clusters(batch, gap_agreement_weight=0.0):
-    """Cluster profile / deletion mean per centre from soft assignment of the extra rows (softmax over agreement)."""
+    """Profile and mean deletion count of every cluster: each extra row is softly assigned to the centre it agrees with
+    most (gap agreement down-weighted, the mask token never counted), weighted by the number of positions both rows cover,
+    and a centre's summary is normalised by its total weight plus one for the centre itself - AlphaFold-Multimer's
+    definition, per centre rather than per position as in the monomer pipeline
+    (fastfold/data/data_transforms_multimer.py:124-180)."""
     weights = torch.tensor([1.0] * 21 + [gap_agreement_weight] + [0.0])
-    msa_oh = dt.make_one_hot(batch["msa"], 23) * batch["msa_mask"][..., None]                  # [n centres, r, 23]
-    extra_oh = dt.make_one_hot(batch["extra_msa"], 23) * batch["extra_msa_mask"][..., None]    # [m extra, r, 23]
-    agreement = torch.einsum("mrc,nrc->mn", extra_oh, weights * msa_oh)
-    valid = batch["extra_msa_mask"].sum(-1).clamp(0, 1)                                        # rows that exist at all
-    assign = torch.softmax(1e3 * agreement, dim=1) * valid[:, None]                            # [m, n], ~one-hot per extra row
-    counts = batch["msa_mask"] + torch.einsum("mn,mr->nr", assign, batch["extra_msa_mask"]) + 1e-6
-    batch["cluster_profile"] = (msa_oh + torch.einsum("mn,mrc->nrc", assign, extra_oh)) / counts[..., None]
-    del_sum = batch["deletion_matrix"] * batch["msa_mask"] + torch.einsum("mn,mr->nr", assign, batch["extra_deletion_matrix"] * batch["extra_msa_mask"])
-    batch["cluster_deletion_mean"] = del_sum / counts
+    msa_mask, extra_mask = batch["msa_mask"].float(), batch["extra_msa_mask"].float()
+    centre = dt.make_one_hot(batch["msa"], 23) * msa_mask[..., None]                 # [n, r, 23]
+    extra = dt.make_one_hot(batch["extra_msa"], 23) * extra_mask[..., None]          # [m, r, 23]
+    agreement = torch.einsum("nrc,mrc->nm", weights * centre, extra)
+    assign = torch.softmax(1e3 * agreement, dim=0) * (msa_mask @ extra_mask.t())     # [n, m]
+    total = assign.sum(-1) + 1.0
+    batch["cluster_profile"] = (torch.einsum("nm,mrc->nrc", assign, extra) + centre) / total[:, None, None]
+    batch["cluster_deletion_mean"] = (assign @ (extra_mask * batch["extra_deletion_matrix"].float()) + batch["deletion_matrix"]) / total[:, None]
     return batch
 
 

@@ -238,44 +238,78 @@ def _block_diag(arrs: Sequence[np.ndarray], pad_value) -> np.ndarray:
     return out
 
 
-def _pad_templates(chains, min_templates=4):
-    n = max([min_templates] + [c["template_aatype"].shape[0] for c in chains if "template_aatype" in c])
+def _pad_templates(chains, max_templates=4):
+    """Every chain gets exactly ``max_templates`` template slots (zero-filled), so the template axis lines up when the
+    chains are concatenated along the residues."""
     for c in chains:
         for k in TEMPLATE_FEATURES:
             if k in c:
-                pad = n - c[k].shape[0]
+                pad = max_templates - c[k].shape[0]
                 if pad > 0:
                     c[k] = np.pad(c[k], [(0, pad)] + [(0, 0)] * (c[k].ndim - 1))
     return chains
 
 
-def merge_chain_features(chains: Sequence[MutableMapping[str, np.ndarray]], pair_msa_sequences: bool, max_templates: int = 4) -> Dict[str, np.ndarray]:
-    chains = _pad_templates([dict(c) for c in chains], max_templates)
+def _merge_group(chains, dense: bool) -> Dict[str, np.ndarray]:
+    """One feature dict from several: per-residue features are concatenated, template features concatenated along the
+    residues, per-chain counts added up, anything else taken from the first chain.  Alignment features are concatenated
+    along the residues when ``dense`` (the chains share their rows) - as the ``*_all_seq`` (paired) blocks always are - and
+    laid out block-diagonally, gap-filled, otherwise."""
     merged: Dict[str, np.ndarray] = {}
-    keys = set(chains[0])
-    for k in keys:
-        vals = [c[k] for c in chains if k in c]
+    for k in chains[0]:
+        vals = [c[k] for c in chains]
         base = k.split("_all_seq")[0]
         if base in MSA_FEATURES:
-            if pair_msa_sequences or "_all_seq" in k:
-                merged[k] = np.concatenate(vals, axis=1)
-            else:
-                merged[k] = _block_diag(vals, MSA_PAD_VALUES[k])
-        elif k in SEQ_FEATURES:
+            merged[k] = np.concatenate(vals, axis=1) if (dense or "_all_seq" in k) else _block_diag(vals, MSA_PAD_VALUES[k])
+        elif base in SEQ_FEATURES:
             merged[k] = np.concatenate(vals, axis=0)
-        elif k in TEMPLATE_FEATURES:
+        elif base in TEMPLATE_FEATURES:
             merged[k] = np.concatenate(vals, axis=1)
-        elif k in CHAIN_FEATURES:
-            merged[k] = np.sum([np.asarray(v) for v in vals]).astype(np.int32)
+        elif base in CHAIN_FEATURES:
+            merged[k] = np.sum([np.asarray(v) for v in vals], axis=0).astype(np.int32)
         else:
             merged[k] = vals[0]
+    return merged
+
+
+def _merge_homomers_dense_msa(chains) -> List[Dict[str, np.ndarray]]:
+    """Copies of one sequence (same ``entity_id``) share their alignment: they are merged first, their rows side by side,
+    which keeps the MSA of a homo-oligomer dense instead of block-diagonal (fastfold/data/msa_pairing.py:391-415)."""
+    by_entity: Dict[int, list] = collections.defaultdict(list)
+    for c in chains:
+        by_entity[int(np.asarray(c["entity_id"]).reshape(-1)[0])].append(c)
+    return [_merge_group(by_entity[e], dense=True) for e in sorted(by_entity)]
+
+
+def merge_chain_features(np_chains_list: Sequence[MutableMapping[str, np.ndarray]], pair_msa_sequences: bool, max_templates: int = 4) -> Dict[str, np.ndarray]:
+    """All chains into one example (fastfold/data/msa_pairing.py:270-333, 433-460): templates padded to a common count,
+    copies of one sequence merged densely, the entities' own rows laid out block-diagonally, the species-paired rows (if
+    any) stacked on top, then the features that only exist for the whole complex:
+
+    * ``seq_length`` (total, repeated per residue) and ``num_alignments``;
+    * ``cluster_bias_mask``: 1 on the rows that must always be among the cluster centres - the first row of the merged MSA
+      when rows are paired, else the first row (the entity's own sequence) of every diagonal block;
+    * ``bert_mask``: 1 where a row really covers a residue; the gap-filled off-diagonal area is never scored.
+    """
+    chains = _pad_templates([dict(c) for c in np_chains_list], max_templates)
+    groups = _merge_homomers_dense_msa(chains)
+    merged = _merge_group(groups, dense=False)
+    own_rows = _block_diag([np.ones(g["msa"].shape, dtype=np.float32) for g in groups], 0)
     if pair_msa_sequences:
-        # paired block on top of the block-diagonal unpaired rows
         for k in MSA_FEATURES:
-            if k + "_all_seq" in merged and k in merged:
-                unpaired = _block_diag([c[k] for c in chains], MSA_PAD_VALUES[k])
-                merged[k] = np.concatenate([merged[k + "_all_seq"], unpaired], axis=0)
-        merged["num_alignments"] = np.asarray(merged["msa"].shape[0], dtype=np.int32)
+            if k in merged and k + "_all_seq" in merged:
+                merged[k] = np.concatenate([merged[k + "_all_seq"], merged[k]], axis=0)
+        bias = np.zeros(merged["msa"].shape[0])
+        bias[0] = 1
+        paired_rows = np.concatenate([np.ones(g["msa_all_seq"].shape, dtype=np.float32) for g in groups], axis=1)
+        merged["bert_mask"] = np.concatenate([paired_rows, own_rows], axis=0)
+    else:
+        bias = np.concatenate([np.eye(1, g["msa"].shape[0])[0] for g in groups])
+        merged["bert_mask"] = own_rows
+    merged["cluster_bias_mask"] = bias
+    num_res = merged["aatype"].shape[0]
+    merged["seq_length"] = np.asarray([num_res] * num_res, dtype=np.int32)
+    merged["num_alignments"] = np.asarray(merged["msa"].shape[0], dtype=np.int32)
     return merged
 
 
@@ -306,6 +340,10 @@ def process_unmerged_features(chains: Sequence[MutableMapping[str, np.ndarray]])
         c["msa_mask"] = np.ones(c["msa"].shape, dtype=np.float32)
         if "msa_all_seq" in c:
             c["msa_mask_all_seq"] = np.ones(c["msa_all_seq"].shape, dtype=np.float32)
+        if "all_atom_mask" not in c:
+            # inference has no structure: the atoms each residue type has, at the origin (fastfold/data/feature_processing_multimer.py:235-241)
+            c["all_atom_mask"] = np.asarray(rc.restype_atom37_mask, dtype=np.int32)[np.clip(c["aatype"], 0, 20)]
+            c["all_atom_positions"] = np.zeros(c["all_atom_mask"].shape + (3,))
         c["assembly_num_chains"] = np.asarray(n_chains)
         c["entity_mask"] = (c["entity_id"] != 0).astype(np.int32)
         out.append(c)
@@ -319,7 +357,7 @@ def process_final(example: MutableMapping[str, np.ndarray]) -> Dict[str, np.ndar
     example["msa_mask"] = (example["msa"] != MSA_GAP_IDX).astype(np.float32) if "msa_mask" not in example else example["msa_mask"].astype(np.float32)
     first_row_ok = example["seq_mask"]
     example["msa_mask"] = example["msa_mask"] * first_row_ok[None]
-    if "template_aatype" in example:
+    if "template_aatype" in example and "num_templates" not in example:     # else: the first chain's count after cropping
         example["num_templates"] = np.asarray(example["template_aatype"].shape[0], dtype=np.int32)
     return {k: v for k, v in example.items() if k in REQUIRED_FEATURES or k.startswith("template_") or k in ("cluster_bias_mask",)}
 
@@ -334,26 +372,6 @@ def pair_and_merge(all_chain_features: Mapping[str, MutableMapping[str, np.ndarr
         chains = deduplicate_unpaired_sequences(chains)
     chains = crop_chains(chains, msa_crop_size=max_msa_crop, pair_msa_sequences=pair, max_templates=max_templates)
     merged = merge_chain_features(chains, pair_msa_sequences=pair, max_templates=max_templates)
-    # ``cluster_bias_mask``: 1 on the rows that must always be among the cluster centres - the first row of the merged MSA
-    # when rows are paired, the first row (the chain's own sequence) of every block of the block-diagonal MSA otherwise.
-    # ``bert_mask``: 1 where a row really has a residue of that chain (the off-diagonal padding of the block-diagonal
-    # rows is never scored by the masked-MSA loss).  fastfold/data/msa_pairing.py:287-330.
-    own_rows = _block_diag([np.ones(c["msa"].shape, dtype=np.float32) for c in chains], 0)
-    if pair:
-        bias = np.zeros(merged["msa"].shape[0], dtype=np.float32)
-        bias[0] = 1.0
-        paired_rows = np.concatenate([np.ones(c["msa_all_seq"].shape, dtype=np.float32) for c in chains], axis=1)
-        merged["bert_mask"] = np.concatenate([paired_rows, own_rows], axis=0)
-    else:
-        parts = []
-        for c in chains:
-            part = np.zeros(c["msa"].shape[0], dtype=np.float32)
-            part[0] = 1.0
-            parts.append(part)
-        bias = np.concatenate(parts)
-        merged["bert_mask"] = own_rows
-    assert merged["bert_mask"].shape == merged["msa"].shape and bias.shape[0] == merged["msa"].shape[0]
-    merged["cluster_bias_mask"] = bias
     return process_final(merged)
 
 
@@ -366,7 +384,8 @@ def add_assembly_features(all_chain_features: Mapping[str, MutableMapping[str, n
     seq_to_entity: Dict[str, int] = {}
     grouped: Dict[int, List[MutableMapping[str, np.ndarray]]] = collections.defaultdict(list)
     for feats in all_chain_features.values():
-        seq = feats["sequence"][0].decode() if isinstance(feats["sequence"][0], bytes) else str(feats["sequence"][0])
+        first = np.asarray(feats["sequence"]).reshape(-1)[0]          # [1] from the monomer pipeline, 0-d after convert_monomer_features
+        seq = first.decode() if isinstance(first, bytes) else str(first)
         ent = seq_to_entity.setdefault(seq, len(seq_to_entity) + 1)
         grouped[ent].append(feats)
     out, chain_no = {}, 1

@@ -4,7 +4,9 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
+``mode``: ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
+``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
+corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
 ``features`` (the tensor pipeline on a raw feature dict: the un-ensembled transforms, then one ensemble member
 with the given seed and MSA resampling switched off), ``model`` (full ``AlphaFold`` forward in the OpenFold layout), ``loss`` (``AlphaFoldLoss`` with the per-term
 breakdown), ``multimer_parts`` (input embedder, structure module and template embedder of the multimer model, called
@@ -21,7 +23,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 
 
 def _setup():
-    for name, typ in (("int", int), ("float", float), ("bool", bool), ("object", object)):
+    for name, typ in (("int", int), ("float", float), ("bool", bool), ("object", object), ("string_", np.bytes_)):
         if not hasattr(np, name):                 # aliases numpy 2 dropped and the reference's tables still use
             setattr(np, name, typ)
     sys.path.insert(0, os.path.join(ROOT, "baseline", "stubs"))
@@ -58,6 +60,26 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "multimer_merge":
+        from fastfold.data import feature_processing_multimer
+        torch.save({"example": dict(feature_processing_multimer.pair_and_merge(d["chains"]))}, dst)
+        return
+    if mode == "multimer_tensors":
+        from fastfold.data import data_transforms_multimer as dtm, input_pipeline_multimer as ipm
+        config = _config(d)
+        common, mode_cfg = config.data.common, config.data[d["mode"]]
+        t = {k: torch.as_tensor(np.asarray(v)) for k, v in d["example"].items() if np.asarray(v).dtype != object}
+        with torch.no_grad():
+            t = ipm.compose(ipm.nonensembled_transform_fns(common, mode_cfg))(t)
+            non = {k: v.clone() for k, v in t.items()}
+            t = dtm.sample_msa(d["max_seq"], d["max_extra"], seed=d["seed"])(dict(t))
+            sampled = {k: v.clone() for k, v in t.items()}
+            torch.manual_seed(d["torch_seed"])
+            t = dtm.make_masked_msa(common.masked_msa, mode_cfg.masked_msa_replace_fraction, seed=d["seed"] + 1)(t)
+            masked = {k: v.clone() for k, v in t.items()}
+            t = dtm.create_msa_feat(dtm.nearest_neighbor_clusters()(t))
+        torch.save({"non": non, "sampled": sampled, "masked": masked, "final": dict(t)}, dst)
+        return
     if mode == "features":
         from fastfold.data import feature_pipeline, input_pipeline
         config = _config(d)

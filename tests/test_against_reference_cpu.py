@@ -202,3 +202,84 @@ def test_parameter_archives_written_here_are_read_alike_by_the_reference(name, t
             continue
         assert v.shape == own[k].shape and torch.equal(v, own[k]), k
     assert len(ref) - skipped > 300
+
+
+def _multimer_chains(kind):
+    """Per-chain feature dicts as the multimer data pipeline hands them to the merge: a hetero-dimer with species-tagged
+    rows for pairing (4 and 3 species, 2 in common), or a homo-dimer."""
+    import numpy as np
+    from fastfold_b200.data import data_pipeline as dp, msa_pairing
+    rng = np.random.RandomState(1)
+    letters = list("ACDEFGHIKLMNPQRSTVWY")
+
+    def mutate(seq):
+        return "".join(c if rng.rand() > 0.3 else rng.choice(letters + ["-"]) for c in seq)
+
+    def chain(seq, cid, n_rows, species):
+        n = len(seq)
+        rows = [seq] + [mutate(seq) for _ in range(n_rows)]
+        dels = [[int(rng.rand() < 0.05) * int(rng.randint(1, 4)) for _ in range(n)] for _ in rows]
+        f = dict(dp.make_sequence_features(seq, cid, n))
+        f.update(dp.make_msa_features([rows], [dels]))
+        f.update({"template_aatype": np.eye(22, dtype=np.float32)[rng.randint(0, 22, (2, n))],
+                  "template_all_atom_positions": (rng.randn(2, n, 37, 3) * 5).astype(np.float32),
+                  "template_all_atom_masks": (rng.rand(2, n, 37) > 0.3).astype(np.float32), "template_sum_probs": rng.rand(2, 1).astype(np.float32),
+                  "template_domain_names": np.array([b"1abc_A", b"2xyz_B"], dtype=object),
+                  "template_sequence": np.array([b"A" * n, b"C" * n], dtype=object)})
+        if species:
+            a = dp.make_msa_features([[seq] + [mutate(seq) for _ in species]], [[[0] * n] * (len(species) + 1)])
+            f["msa_all_seq"], f["deletion_matrix_int_all_seq"] = a["msa"], a["deletion_matrix_int"]
+            f["msa_species_identifiers_all_seq"] = np.array([b""] + [x.encode() for x in species][: a["msa"].shape[0] - 1], dtype=object)
+        return dp.convert_monomer_features(f, cid)
+
+    if kind == "hetero":
+        s1, s2 = "".join(rng.choice(letters, 14)), "".join(rng.choice(letters, 9))
+        chains = {"A": chain(s1, "A", 6, ["HUMAN", "MOUSE", "YEAST", "RAT"]), "B": chain(s2, "B", 4, ["MOUSE", "HUMAN", "BOVIN"])}
+    else:
+        s1 = "".join(rng.choice(letters, 11))
+        chains = {"A": chain(s1, "A", 5, []), "B": chain(s1, "B", 5, [])}
+    return msa_pairing.add_assembly_features(chains)
+
+
+@pytest.mark.parametrize("kind", ["hetero", "homo"])
+def test_multimer_feature_assembly_and_tensor_pipeline(kind, tmp_path):
+    """Species pairing, de-duplication, cropping, dense merge of identical chains, block-diagonal merge of different ones,
+    masks of the merged example; then the tensor pipeline: profile, target feature, seeded Gumbel row sampling (exact),
+    and - on the reference's corrupted alignment, whose positions come from the global random state - the cluster
+    summaries and ``msa_feat``."""
+    import copy
+    import numpy as np
+    from fastfold_b200.config import model_config
+    from fastfold_b200.data import data_transforms as dt, data_transforms_multimer as dtm, msa_pairing
+    chains = _multimer_chains(kind)
+    ref = _oracle("multimer_merge", {"chains": copy.deepcopy(chains)}, tmp_path)["example"]
+    ours = msa_pairing.pair_and_merge(copy.deepcopy(chains))
+    assert not [k for k in ref if k not in ours]
+    for k, v in ref.items():
+        a, b = np.asarray(ours[k]), np.asarray(v)
+        assert a.shape == b.shape and a.dtype.kind == b.dtype.kind, (k, a.shape, b.shape, a.dtype, b.dtype)
+        assert np.allclose(a.astype(np.float64), b.astype(np.float64), atol=1e-6), k
+    # tensor pipeline
+    seed, max_seq, max_extra = 11, 4, 3
+    stages = _oracle("multimer_tensors", {"name": "multimer", "edits": {}, "example": ref, "mode": "predict", "seed": seed, "torch_seed": 3,
+                                          "max_seq": max_seq, "max_extra": max_extra}, tmp_path)
+    cfg = model_config("multimer")
+    t = {k: torch.as_tensor(np.asarray(v)) for k, v in ours.items() if np.asarray(v).dtype != object}
+    for k in ("msa", "aatype", "asym_id", "entity_id", "sym_id", "residue_index", "template_aatype"):
+        t[k] = t[k].long()
+    t = dtm.create_target_feat(dtm.make_msa_profile(t))
+    for k in ("msa_profile", "target_feat"):
+        assert torch.allclose(t[k].float(), stages["non"][k].float(), atol=1e-6), k
+    s = dtm.sample_msa({k: v.clone() for k, v in t.items()}, max_seq, max_extra, seed=seed)
+    for k in ("msa", "deletion_matrix", "msa_mask", "bert_mask", "extra_msa", "extra_deletion_matrix", "extra_msa_mask"):
+        assert torch.equal(s[k].float(), stages["sampled"][k].float()), k
+    m = {k: v.clone() for k, v in stages["masked"].items()}
+    out = dtm.create_msa_feat(dtm.nearest_neighbor_clusters(m))
+    for k in ("cluster_profile", "cluster_deletion_mean", "msa_feat"):
+        assert torch.allclose(out[k].float(), stages["final"][k].float(), atol=1e-5), k
+    # our corruption obeys the same rules as the reference's: only positions inside ``msa_mask`` change, scored positions
+    # are a subset of the incoming ``bert_mask``, about ``replace_fraction`` of them
+    c = dtm.make_masked_msa({k: v.clone() for k, v in s.items()}, cfg.data.common.masked_msa, 0.5, seed=seed + 1)
+    changed = c["msa"] != c["true_msa"]
+    assert not (changed & (s["msa_mask"] == 0) & (c["true_msa"] == 0)).any() and (c["bert_mask"] <= s["bert_mask"]).all()
+    assert 0.2 < float(c["bert_mask"].sum() / s["bert_mask"].sum()) < 0.8

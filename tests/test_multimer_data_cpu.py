@@ -151,9 +151,15 @@ def test_cluster_bias_and_bert_masks_follow_the_block_structure():
     for row, scored in zip(ex["msa"][3:], ex["bert_mask"][3:]):
         own = slice(0, 10) if (row[10:] == gap).all() else slice(10, 18)
         assert scored[own].all() and scored.sum() == (own.stop - own.start)
-    # homomer (no pairing): the first row of every chain's block is pinned
-    h = mp.pair_and_merge(mp.add_assembly_features({"0_A": _chain("ACDEFGHIKL", ["ACDEFGHIKV"], ["HUMAN"], 1),
-                                                     "1_B": _chain("ACDEFGHIKL", ["ACDEFGHIKV"], ["HUMAN"], 1)}))
+    # homo-dimer: copies of one sequence share their rows - the MSA is dense (both copies side by side), one pinned row
+    dense = mp.pair_and_merge(mp.add_assembly_features({"0_A": _chain("ACDEFGHIKL", ["ACDEFGHIKV"], ["HUMAN"], 1),
+                                                         "1_B": _chain("ACDEFGHIKL", ["ACDEFGHIKV"], ["HUMAN"], 1)}))
+    assert dense["msa"].shape == (2, 20) and (dense["msa"][:, :10] == dense["msa"][:, 10:]).all() and (dense["bert_mask"] == 1).all()
+    assert list(np.nonzero(dense["cluster_bias_mask"])[0]) == [0] and (dense["seq_length"] == 20).all()
+    # two different chains without species-tagged rows: nothing to pair, one block per chain, each block's first row pinned
+    def unpaired(seq, rows):
+        return {k: v for k, v in _chain(seq, rows, ["HUMAN"] * len(rows), 1).items() if "_all_seq" not in k}
+    h = mp.pair_and_merge(mp.add_assembly_features({"0_A": unpaired("ACDEFGHIKL", ["ACDEFGHIKV"]), "1_B": unpaired("MNPQRSTVWY", ["MNPQRSTVWA"])}))
     pinned = np.nonzero(h["cluster_bias_mask"])[0]
     assert len(pinned) == 2 and pinned[0] == 0 and (h["msa"][pinned[1]][:10] == gap).all()
     # sampling: pinned rows always come first, empty (padding) rows always last, whatever the seed
