@@ -127,7 +127,8 @@ NUM_TEMPLATES = "num templates placeholder"
 def _base_config():
     c_z, c_m, c_t, c_e, c_s = (Ref(128, "c_z"), Ref(256, "c_m"), Ref(64, "c_t"), Ref(64, "c_e"), Ref(384, "c_s"))
     blocks_per_ckpt = Ref(None, "blocks_per_ckpt")
-    chunk_size = Ref(4, "chunk_size")
+    chunk_size = Ref(None, "chunk_size")
+    max_extra_msa = Ref(1024, "max_extra_msa")        # one value for every mode, also reachable as data.common.max_extra_msa
     aux_distogram_bins = Ref(64, "aux_distogram_bins")
     tm_enabled = Ref(False, "tm_enabled")
     eps = Ref(1e-8, "eps")
@@ -135,7 +136,7 @@ def _base_config():
     embed_template_torsion_angles = Ref(True, "embed_template_torsion_angles")
     shared = {"c_z": c_z, "c_m": c_m, "c_t": c_t, "c_e": c_e, "c_s": c_s, "blocks_per_ckpt": blocks_per_ckpt, "chunk_size": chunk_size,
               "aux_distogram_bins": aux_distogram_bins, "tm_enabled": tm_enabled, "eps": eps, "templates_enabled": templates_enabled,
-              "embed_template_torsion_angles": embed_template_torsion_angles}
+              "embed_template_torsion_angles": embed_template_torsion_angles, "max_extra_msa": max_extra_msa}
     feat = {
         "aatype": [NUM_RES], "all_atom_mask": [NUM_RES, None], "all_atom_positions": [NUM_RES, None, None],
         "alt_chi_angles": [NUM_RES, None], "atom14_alt_gt_exists": [NUM_RES, None], "atom14_alt_gt_positions": [NUM_RES, None, None],
@@ -158,14 +159,14 @@ def _base_config():
         "template_torsion_angles_sin_cos": [NUM_TEMPLATES, NUM_RES, None, None], "true_msa": [NUM_MSA_SEQ, NUM_RES], "use_clamped_fape": [],
     }
     mode_common = {"fixed_size": True, "subsample_templates": False, "masked_msa_replace_fraction": 0.15, "max_msa_clusters": 128,
-                   "max_extra_msa": 1024, "max_template_hits": 4, "max_templates": 4, "crop": False, "crop_size": None, "supervised": False,
+                   "max_extra_msa": max_extra_msa, "max_template_hits": 4, "max_templates": 4, "crop": False, "crop_size": None, "supervised": False,
                    "uniform_recycling": False}
     cfg = {
         "data": {
             "common": {
                 "feat": feat,
                 "masked_msa": {"profile_prob": 0.1, "same_prob": 0.1, "uniform_prob": 0.1},
-                "max_recycling_iters": 3, "msa_cluster_features": True, "reduce_msa_clusters_by_max_templates": False, "resample_msa_in_recycling": True,
+                "max_extra_msa": max_extra_msa, "max_recycling_iters": 3, "msa_cluster_features": True, "reduce_msa_clusters_by_max_templates": False, "resample_msa_in_recycling": True,
                 "template_features": ["template_all_atom_positions", "template_sum_probs", "template_aatype", "template_all_atom_mask"],
                 "unsupervised_features": ["aatype", "residue_index", "msa", "num_alignments", "seq_length", "between_segment_residues", "deletion_matrix",
                                           "no_recycling_iters"],
@@ -176,7 +177,7 @@ def _base_config():
             "predict": dict(mode_common, masked_msa_replace_fraction=0.15),
             "eval": dict(mode_common, subsample_templates=False, supervised=True),
             "train": dict(mode_common, subsample_templates=True, crop=True, crop_size=256, supervised=True, clamp_prob=0.9,
-                          max_distillation_msa_clusters=1000, uniform_recycling=True, distillation_prob=0.75),
+                          max_distillation_msa_clusters=1000, uniform_recycling=True, distillation_prob=0.75, shuffle_top_k_prefiltered=20),
             "data_module": {"use_small_bfd": False, "data_loaders": {"batch_size": 1, "num_workers": 16}},
         },
         "globals": {"blocks_per_ckpt": blocks_per_ckpt, "chunk_size": chunk_size, "c_z": c_z, "c_m": c_m, "c_t": c_t, "c_e": c_e, "c_s": c_s,
@@ -192,13 +193,13 @@ def _base_config():
                 "template_pair_stack": {"c_t": c_t, "c_hidden_tri_att": 16, "c_hidden_tri_mul": 64, "no_blocks": 2, "no_heads": 4,
                                         "pair_transition_n": 2, "dropout_rate": 0.25, "blocks_per_ckpt": blocks_per_ckpt, "inf": 1e9},
                 "template_pointwise_attention": {"c_t": c_t, "c_z": c_z, "c_hidden": 16, "no_heads": 4, "inf": 1e5},
-                "inf": 1e5, "eps": 1e-6, "enabled": templates_enabled, "embed_angles": embed_template_torsion_angles, "use_unit_vector": False,
+                "inf": 1e5, "eps": eps, "enabled": templates_enabled, "embed_angles": embed_template_torsion_angles, "use_unit_vector": False,
             },
             "extra_msa": {
                 "extra_msa_embedder": {"c_in": 25, "c_out": c_e},
                 "extra_msa_stack": {"c_m": c_e, "c_z": c_z, "c_hidden_msa_att": 8, "c_hidden_opm": 32, "c_hidden_mul": 128, "c_hidden_pair_att": 32,
                                     "no_heads_msa": 8, "no_heads_pair": 4, "no_blocks": 4, "transition_n": 4, "msa_dropout": 0.15, "pair_dropout": 0.25,
-                                    "clear_cache_between_blocks": True, "inf": 1e9, "eps": eps, "ckpt": False},
+                                    "clear_cache_between_blocks": True, "inf": 1e9, "eps": eps, "ckpt": True},
                 "enabled": True,
             },
             "evoformer_stack": {"c_m": c_m, "c_z": c_z, "c_hidden_msa_att": 32, "c_hidden_opm": 32, "c_hidden_mul": 128, "c_hidden_pair_att": 32,
@@ -244,8 +245,7 @@ def set_shared(config, name, value):
 def _multimer_overrides(c):
     c.globals.is_multimer = True
     c.data.predict.max_msa_clusters = 252
-    c.data.predict.max_extra_msa = 1152
-    c.data.common.max_recycling_iters = 20
+    c.data.common.unsupervised_features = list(c.data.common.unsupervised_features) + ["msa_mask", "seq_mask", "asym_id", "entity_id", "sym_id"]
     c.model.input_embedder.update_from({"tf_dim": 21, "max_relative_idx": 32, "use_chain_relative": True, "max_relative_chain": 2})
     c.model.template.update_from({"template_single_embedder": {"c_in": 34, "c_m": c.globals.c_m},
                                   "template_pair_embedder": {"c_z": c.globals.c_z, "c_out": 64, "c_dgram": 39, "c_aatype": 22},

@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
+``mode``: ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
 ``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
 corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
 ``features`` (the tensor pipeline on a raw feature dict: the un-ensembled transforms, then one ensemble member
@@ -60,6 +60,19 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "config":
+        from fastfold.config import model_config
+
+        def flat(c, pre=""):
+            out = {}
+            for k, v in c.items():
+                if hasattr(v, "items"):
+                    out.update(flat(v, pre + k + "."))
+                else:
+                    out[pre + k] = repr(v)
+            return out
+        torch.save({"%s|%s" % (n, t): flat(model_config(n, train=t)) for n in d["names"] for t in (False, True)}, dst)
+        return
     if mode == "multimer_merge":
         from fastfold.data import feature_processing_multimer
         torch.save({"example": dict(feature_processing_multimer.pair_and_merge(d["chains"]))}, dst)
