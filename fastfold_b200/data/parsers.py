@@ -78,25 +78,39 @@ def parse_stockholm(stockholm_string: str) -> Tuple[List[str], DeletionMatrix, L
     return msa, deletion_matrix, list(name_to_seq.keys())
 
 
+def _stockholm_line_kept(line: str, names) -> bool:
+    """Which lines of a Stockholm file survive when only the sequences in ``names`` are kept: blank lines, the header, the
+    terminator and the reference annotation always; ``#=GS`` descriptions and alignment rows of kept sequences; no other
+    markup."""
+    text = line.strip()
+    if not text or text == "//" or line.startswith("# STOCKHOLM") or line.startswith("#=GC RF"):
+        return True
+    if line.startswith("#=GS"):
+        return line.split(maxsplit=2)[1] in names
+    if line.startswith("#"):
+        return False
+    return line.partition(" ")[0] in names
+
+
 def deduplicate_stockholm_msa(stockholm_msa: str) -> str:
-    seen, keep = set(), set()
+    """Keeps the first of every set of sequences that are equal once the columns the query (first sequence) has a gap in
+    are ignored; rows are joined over the blocks of the file first (fastfold/data/parsers.py:354-386)."""
+    rows: Dict[str, str] = {}
     for line in stockholm_msa.splitlines():
         if line.strip() and not line.startswith(("#", "//")):
-            name, seq = line.split()
-            if seq not in seen:
-                seen.add(seq)
-                keep.add(name)
-    out = []
-    for line in stockholm_msa.splitlines():
-        if not line.strip() or line.startswith("//") or line.startswith("# STOCKHOLM"):
-            out.append(line)
-        elif line.startswith("#"):
-            parts = line.split()
-            if len(parts) > 1 and (parts[1] in keep or parts[0] == "#=GC"):
-                out.append(line)
-        elif line.split()[0] in keep:
-            out.append(line)
-    return "\n".join(out) + "\n"
+            name, part = line.split()
+            rows[name] = rows.get(name, "") + part
+    if not rows:
+        return stockholm_msa
+    query = next(iter(rows.values()))
+    match_cols = [i for i, ch in enumerate(query) if ch != "-"]
+    seen, keep = set(), set()
+    for name, row in rows.items():
+        key = "".join(row[i] for i in match_cols if i < len(row))
+        if key not in seen:
+            seen.add(key)
+            keep.add(name)
+    return "\n".join(ln for ln in stockholm_msa.splitlines() if _stockholm_line_kept(ln, keep)) + "\n"
 
 
 def _iter_hhr_hits(lines):
@@ -170,37 +184,24 @@ def truncate_stockholm_msa(stockholm_msa_path: str, max_sequences: int) -> str:
 
 
 def remove_empty_columns_from_stockholm_msa(stockholm_msa: str) -> str:
-    """Drop the columns that are gaps in the query (first sequence) of every block."""
-    out, block = [], []
-
-    def flush():
-        rows = [ln for ln in block if ln.strip() and not ln.startswith("#")]
-        if not rows:
-            out.extend(block)
-            return
-        first = rows[0].split()[1]
-        keep = [i for i, ch in enumerate(first) if ch != "-"]
-        for ln in block:
-            if not ln.strip():
-                out.append(ln)
-                continue
-            if ln.startswith("#=GC") or ln.startswith("#=GR") or not ln.startswith("#"):
-                head, _, data = ln.rpartition(" ")
-                if len(data) == len(first):
-                    data = "".join(data[i] for i in keep)
-                    out.append(head + " " + data)
-                    continue
-            out.append(ln)
-
-    for line in stockholm_msa.splitlines():
-        if not line.strip() or line.startswith("//"):
-            flush()
-            block = []
-            out.append(line)
-        else:
-            block.append(line)
-    flush()
-    return "\n".join(out) + "\n"
+    """Drops the columns in which every sequence has a gap.  A file is processed chunk by chunk, a chunk being the alignment
+    rows up to and including their ``#=GC RF`` line, which is trimmed with them; a chunk left without columns becomes empty
+    lines (fastfold/data/parsers.py:314-351)."""
+    lines = stockholm_msa.splitlines()
+    out = list(lines)
+    chunk = []                                   # indices of the alignment rows collected since the last annotation line
+    for i, line in enumerate(lines):
+        if line.startswith("#=GC RF"):
+            width = len(line.rpartition(" ")[2])
+            datas = [lines[j].rpartition(" ")[2] for j in chunk]
+            keep = [c for c in range(width) if any(d[c] != "-" for d in datas)]
+            for j in chunk + [i]:
+                head, _, data = lines[j].rpartition(" ")
+                out[j] = (head + " " + "".join(data[c] for c in keep)) if keep else ""
+            chunk = []
+        elif line.strip() and not line.startswith(("#", "//")):
+            chunk.append(i)
+    return "\n".join(out)
 
 
 def convert_stockholm_to_a3m(stockholm_format: str, max_sequences: Optional[int] = None, remove_first_row_gaps: bool = True) -> str:

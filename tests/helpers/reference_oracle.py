@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
+``mode``: ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
 ``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
 corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
 ``features`` (the tensor pipeline on a raw feature dict: the un-ensembled transforms, then one ensemble member
@@ -60,6 +60,31 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "parsers":
+        import dataclasses
+        from fastfold.data import parsers
+
+        def plain(x):
+            if dataclasses.is_dataclass(x):
+                return {f.name: plain(getattr(x, f.name)) for f in dataclasses.fields(x)}
+            if isinstance(x, (list, tuple)):
+                return [plain(v) for v in x]
+            if isinstance(x, dict):
+                return {k: plain(v) for k, v in x.items()}
+            if hasattr(x, "sequences") and hasattr(x, "deletion_matrix"):
+                return {"sequences": list(x.sequences), "deletion_matrix": plain(x.deletion_matrix), "descriptions": list(x.descriptions)}
+            return x
+        t = d["texts"]
+        out = {"fasta": plain(parsers.parse_fasta(t["fasta"])), "a3m": plain(parsers.parse_a3m(t["a3m"])),
+               "sto": plain(parsers.parse_stockholm(t["sto"])), "sto_to_a3m": parsers.convert_stockholm_to_a3m(t["sto"]),
+               "sto_to_a3m_keep": parsers.convert_stockholm_to_a3m(t["sto"], remove_first_row_gaps=False),
+               "sto_to_a3m_max2": parsers.convert_stockholm_to_a3m(t["sto"], max_sequences=2),
+               "sto_dedup": parsers.deduplicate_stockholm_msa(t["sto"]),
+               "sto_no_empty": parsers.remove_empty_columns_from_stockholm_msa(t["sto_gappy"]),
+               "hhr": plain(parsers.parse_hhr(t["hhr"])), "tblout": plain(parsers.parse_e_values_from_tblout(t["tblout"])),
+               "hmmsearch": plain(parsers.parse_hmmsearch_sto(t["hmmsearch_sto"], t["query"]))}
+        torch.save(out, dst)
+        return
     if mode == "config":
         from fastfold.config import model_config
 

@@ -331,3 +331,60 @@ def test_configuration_presets(tmp_path):
             assert same(ours[k], v), (key, k, ours[k], v)
             compared += 1
     assert compared > 5000
+
+
+PARSER_TEXTS = {
+    "query": "MKTAYIAKQRQISFVK",
+    "fasta": ">sp|P1|ONE first protein\nMKTAYIAKQR\nQISFVK\n\n>two\nACDEFG\n>three extra words here\nGGGG\n",
+    "a3m": ">query\nMKTAYIAKQRQISFVK\n>hit1 desc\nMKTAYIAKaaQRQISFVK\n>hit2\n--TAYIAKQRQISF--\n>hit3\nMKTAYIAKQRQISFVKc\n",
+    "sto": ("# STOCKHOLM 1.0\n#=GF ID test\n#=GS hit1/2-17 DE first hit\n#=GS hit2/1-14 DE second hit\n\n"
+            "query        MKTAY-IAKQ\nhit1/2-17    MKTAYGIAKQ\nhit2/1-14    MK-AY-IAKQ\ndup/1-16     MKTAYGIAKQ\n#=GC RF      xxxxx.xxxx\n\n"
+            "query        RQISFVK\nhit1/2-17    RQISFVK\nhit2/1-14    RQ--FVK\ndup/1-16     RQISFVK\n#=GC RF      xxxxxxx\n//\n"),
+    "sto_gappy": ("# STOCKHOLM 1.0\n\nquery   MK-TA--YI\nhit1    MKGTA-CYI\nhit2    MK-TA--YV\n#=GC RF xx.xx..xx\n//\n"),
+    "hhr": ("Query         query\nMatch_columns 16\nNo_of_seqs    5 out of 10\n\n"
+            " No Hit                             Prob E-value P-value  Score    SS Cols Query HMM  Template HMM\n"
+            "  1 1abc_A test template            99.0 1.0E-10 1.0E-14   50.0   0.0   12    2-13      5-16 (120)\n"
+            "  2 2xyz_B another                  80.0 1.0E-03 1.0E-07   20.0   0.0    8    5-13      1-8 (60)\n\n"
+            "No 1\n>1abc_A test template; some protein\n"
+            "Probab=99.00  E-value=1e-10  Score=50.00  Aligned_cols=12  Identities=75%  Similarity=1.500  Sum_probs=10.5  Template_Neff=5.000\n\n"
+            "Q query             2 KTAYIA-KQRQIS   13 (16)\nQ Consensus         2 ktayia-kqrqis   13 (16)\n                      |||||| ||||||\n"
+            "T Consensus         5 ktayiagkq-qis   16 (120)\nT 1abc_A            5 KTAYIAGKQ-QIS   16 (120)\nT ss_dssp             CCCCHHHHH-HHH\nT ss_pred             cccchhhhh-hhh\n\n"
+            "No 2\n>2xyz_B another\n"
+            "Probab=80.00  E-value=0.001  Score=20.00  Aligned_cols=8  Identities=50%  Similarity=0.700  Sum_probs=6.1  Template_Neff=4.000\n\n"
+            "Q query             5 YIAKQRQIS   13 (16)\nQ Consensus         5 yiakqrqis   13 (16)\n                      ||||.||||\n"
+            "T Consensus         1 yiak-rqis    8 (60)\nT 2xyz_B            1 YIAK-RQIS    8 (60)\n\n"),
+    "tblout": ("#                                                               --- full sequence ---- --- best 1 domain ----\n"
+               "# target name        accession  query name           accession    E-value  score  bias   E-value  score  bias   exp reg clu  ov env dom rep inc description\n"
+               "#------------------- ---------- -------------------- ---------- --------- ------ ----- --------- ------ -----   --- --- --- --- --- --- --- --- -----------\n"
+               "hitA/1-30            -          query                -            1.2e-20   70.1   0.1   1.5e-20   69.8   0.1   1.0   1   0   0   1   1   1   1 -\n"
+               "hitB/5-40            -          query                -              0.003   10.0   0.0     0.004    9.5   0.0   1.1   1   0   0   1   1   1   1 -\n#\n"),
+    "hmmsearch_sto": ("# STOCKHOLM 1.0\n#=GS 4pqx_A/2-15 DE [subseq from] mol:protein length:217  Free text\n"
+                      "#=GS 5g3r_B/1-12 DE [subseq from] mol:protein length:352\n#=GS 1rna_C/1-9 DE [subseq from] mol:na length:9\n\n"
+                      "4pqx_A/2-15    KTAYIAKQRQISFV--\n5g3r_B/1-12    MKTA-IAKQ-QISF--\n1rna_C/1-9     ---------ACGUACGU\n#=GC RF        xxxxxxxxxxxxxxxx\n//\n"),
+}
+
+
+def test_alignment_parsers(tmp_path):
+    from fastfold_b200.data import parsers
+    t = PARSER_TEXTS
+    ref = _oracle("parsers", {"texts": t}, tmp_path)
+
+    def hits(seq):
+        import dataclasses
+        return [dataclasses.asdict(h) for h in seq]
+
+    def msa(parsed):
+        sequences, deletions, descriptions = parsed[:3]
+        return {"sequences": list(sequences), "deletion_matrix": [list(r) for r in deletions], "descriptions": list(descriptions)}
+    seqs, descs = parsers.parse_fasta(t["fasta"])
+    assert [list(seqs), list(descs)] == ref["fasta"]
+    assert msa(parsers.parse_a3m(t["a3m"])) == ref["a3m"]
+    assert msa(parsers.parse_stockholm(t["sto"])) == ref["sto"]
+    assert parsers.convert_stockholm_to_a3m(t["sto"]) == ref["sto_to_a3m"]
+    assert parsers.convert_stockholm_to_a3m(t["sto"], remove_first_row_gaps=False) == ref["sto_to_a3m_keep"]
+    assert parsers.convert_stockholm_to_a3m(t["sto"], max_sequences=2) == ref["sto_to_a3m_max2"]
+    assert parsers.deduplicate_stockholm_msa(t["sto"]) == ref["sto_dedup"]
+    assert parsers.remove_empty_columns_from_stockholm_msa(t["sto_gappy"]) == ref["sto_no_empty"]
+    assert hits(parsers.parse_hhr(t["hhr"])) == ref["hhr"] and len(ref["hhr"]) == 2
+    assert parsers.parse_e_values_from_tblout(t["tblout"]) == ref["tblout"]
+    assert hits(parsers.parse_hmmsearch_sto(t["hmmsearch_sto"], t["query"])) == ref["hmmsearch"] and len(ref["hmmsearch"]) == 2
