@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
+``mode``: ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
 ``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
 corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
 ``features`` (the tensor pipeline on a raw feature dict: the un-ensembled transforms, then one ensemble member
@@ -60,6 +60,29 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "utils":
+        from fastfold.common import protein
+        from fastfold.model.hub.lr_scheduler import AlphaFoldLRScheduler
+        from fastfold.utils import validation_utils as vu
+        prot = protein.from_prediction(d["features"], d["result"], b_factors=d["b_factors"])
+        out = {"pdb": protein.to_pdb(prot), "ideal_atom_mask": protein.ideal_atom_mask(prot)}
+        a, b, mask = d["structures"]
+        out["drmsd"] = vu.drmsd(a[0], b[0], mask[0])              # the reference's version takes one structure at a time
+        out["drmsd_nomask"] = vu.drmsd(a[0], b[0])
+        out["gdt_ts"], out["gdt_ha"] = vu.gdt_ts(a, b, mask), vu.gdt_ha(a, b, mask)
+        from fastfold.utils.superimposition import superimpose
+        out["superimposed"], out["rmsd"] = superimpose(a, b, mask)
+        opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.1)
+        # its constructor passes ``verbose`` to a base class that no longer takes it: evaluate the schedule itself
+        sched = AlphaFoldLRScheduler.__new__(AlphaFoldLRScheduler)
+        sched.__dict__.update(d["schedule"], optimizer=opt, _get_lr_called_within_step=True)
+        lrs = []
+        for step in range(1, d["steps"] + 1):
+            sched.last_epoch = step
+            lrs.append(sched.get_lr()[0])
+        out["lrs"] = lrs
+        torch.save(out, dst)
+        return
     if mode == "parsers":
         import dataclasses
         from fastfold.data import parsers

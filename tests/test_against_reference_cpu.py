@@ -388,3 +388,48 @@ def test_alignment_parsers(tmp_path):
     assert hits(parsers.parse_hhr(t["hhr"])) == ref["hhr"] and len(ref["hhr"]) == 2
     assert parsers.parse_e_values_from_tblout(t["tblout"]) == ref["tblout"]
     assert hits(parsers.parse_hmmsearch_sto(t["hmmsearch_sto"], t["query"])) == ref["hmmsearch"] and len(ref["hmmsearch"]) == 2
+
+
+def test_pdb_writer_metrics_and_schedule(tmp_path):
+    import numpy as np
+    from fastfold_b200.common import protein, residue_constants as rc
+    from fastfold_b200.models.hub import AlphaFoldLRScheduler
+    from fastfold_b200.utils import validation_utils as vu
+    rng = np.random.RandomState(0)
+    n = 17
+    aatype = rng.randint(0, 20, n)
+    mask = np.array(rc.restype_atom37_mask)[aatype].astype(np.float32)
+    mask[3, 5:] = 0                                        # a residue with missing side-chain atoms
+    features = {"aatype": aatype, "residue_index": np.concatenate([np.arange(9), np.arange(8) + 40]), "asym_id": np.array([1] * 9 + [2] * 8)}
+    result = {"final_atom_positions": (rng.randn(n, 37, 3) * 30).astype(np.float32), "final_atom_mask": mask}
+    b_factors = np.repeat(rng.rand(n, 1) * 100, 37, axis=1).astype(np.float32)
+    g = torch.Generator().manual_seed(0)
+    a, b = torch.randn(2, 25, 3, generator=g) * 8, torch.randn(2, 25, 3, generator=g) * 8
+    m = (torch.rand(2, 25, generator=g) > 0.2).float()
+    schedule = {"base_lr": 0.0, "max_lr": 1e-3, "warmup_no_steps": 5, "start_decay_after_n_steps": 12, "decay_every_n_steps": 4, "decay_factor": 0.9}
+    # chain letters: the reference indexes the letters with the 1-based ``asym_id`` (first chain "B"); here the first chain is "A"
+    shifted = dict(features, asym_id=features["asym_id"] - 1)
+    ref = _oracle("utils", {"features": shifted, "result": result, "b_factors": b_factors, "structures": (a, b, m), "schedule": schedule, "steps": 30},
+                  tmp_path)
+    prot = protein.from_prediction(features, result, b_factors=b_factors)
+    assert protein.to_pdb(prot) == ref["pdb"]                       # byte for byte: chains, TER records, numbering, B-factors
+    assert np.array_equal(protein.ideal_atom_mask(prot), ref["ideal_atom_mask"])
+    back = protein.from_pdb_string(ref["pdb"])
+    assert np.array_equal(back.aatype, aatype) and np.allclose(back.atom_positions, result["final_atom_positions"] * mask[..., None], atol=1e-3)
+    assert torch.allclose(vu.drmsd(a[0], b[0], m[0]), ref["drmsd"], atol=1e-5) and torch.allclose(vu.drmsd(a[0], b[0]), ref["drmsd_nomask"], atol=1e-5)
+    assert torch.allclose(vu.drmsd(a, b, m)[0], ref["drmsd"], atol=1e-5)                     # batched here
+    # one score per structure here; the reference averages over the batch
+    assert torch.allclose(vu.gdt_ts(a, b, m).mean(), ref["gdt_ts"], atol=1e-6) and torch.allclose(vu.gdt_ha(a, b, m).mean(), ref["gdt_ha"], atol=1e-6)
+    # superposition (the reference calls a singular-value-decomposition routine of a third-party package, for which the
+    # baseline carries a stand-in; the check is therefore of the masking and batching around it, and of our own solver)
+    from fastfold_b200.utils.superimposition import superimpose
+    sup, rmsd = superimpose(a, b, m)
+    assert torch.allclose(rmsd, ref["rmsd"], atol=1e-4) and torch.allclose(sup * m[..., None], ref["superimposed"] * m[..., None], atol=1e-3)
+    opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.1)
+    sched = AlphaFoldLRScheduler(opt, **schedule)
+    lrs = []
+    for _ in range(30):
+        opt.step()
+        sched.step()
+        lrs.append(opt.param_groups[0]["lr"])
+    assert np.allclose(lrs, ref["lrs"], rtol=1e-9, atol=0)
