@@ -50,7 +50,7 @@ def make_msa_features(msas: Sequence[Sequence[str]], deletion_matrices: Sequence
 
 
 def empty_template_features(num_res: int) -> FeatureDict:
-    return {"template_aatype": np.zeros((0, num_res, 22), np.float32), "template_all_atom_masks": np.zeros((0, num_res, 37), np.float32),
+    return {"template_aatype": np.zeros((0, num_res, 22), np.float32), "template_all_atom_mask": np.zeros((0, num_res, 37), np.float32),
             "template_all_atom_positions": np.zeros((0, num_res, 37, 3), np.float32), "template_domain_names": np.zeros((0,), object),
             "template_sequence": np.zeros((0,), object), "template_sum_probs": np.zeros((0, 1), np.float32)}
 

@@ -16,6 +16,16 @@ from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
 
 from ..common import residue_constants as rc
 
+# Parent amino acid of the modified residues that occur most often in the sequence records of PDB entries (selenomethionine
+# above all: crystallographers' stand-in for methionine).  The reference looks names up in BioPython's much longer SCOP table
+# (fastfold/data/mmcif_parsing.py:284); a name in neither table is read as X.
+MODIFIED_RESIDUE_LETTERS = {
+    "MSE": "M", "SEC": "U", "PYL": "O", "SEP": "S", "TPO": "T", "PTR": "Y", "HYP": "P", "MLY": "K", "CSO": "C", "CME": "C", "OCS": "C",
+    "CSD": "C", "KCX": "K", "LLP": "K", "M3L": "K", "MLZ": "K", "ALY": "K", "PCA": "E", "CGU": "E", "FME": "M", "MHO": "M", "NLE": "L",
+    "ABA": "A", "AIB": "A", "DAL": "A", "HIC": "H", "NEP": "H", "TYS": "Y", "TRO": "W", "DPR": "P", "SAC": "S", "BMT": "T", "UNK": "X",
+}
+
+
 ChainId = str
 PdbHeader = Mapping[str, Any]
 
@@ -293,7 +303,7 @@ def parse(*, file_id: str, mmcif_string: str, catch_all_errors: bool = True) -> 
                 if num in seen:
                     continue
                 seen.add(num)
-                code = rc.restype_3to1.get(mon, "X")
+                code = rc.restype_3to1.get(mon) or MODIFIED_RESIDUE_LETTERS.get(mon, "X")
                 letters.append(code if len(code) == 1 else "X")
             chain_to_seqres[author] = "".join(letters)
             author_seq_to_structure[author] = seq_to_pos[chain]

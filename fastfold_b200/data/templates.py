@@ -85,7 +85,7 @@ class LengthError(PrefilterError):
     pass
 
 
-TEMPLATE_FEATURES = {"template_aatype": np.int64, "template_all_atom_masks": np.float32, "template_all_atom_positions": np.float32,
+TEMPLATE_FEATURES = {"template_aatype": np.int64, "template_all_atom_mask": np.float32, "template_all_atom_positions": np.float32,
                      "template_domain_names": object, "template_sequence": object, "template_sum_probs": np.float32}
 
 
@@ -158,16 +158,24 @@ def _is_after_cutoff(pdb_id, release_dates, cutoff: Optional[datetime.datetime])
 
 
 def build_query_to_hit_index_mapping(hit_query_sequence, hit_sequence, indices_hit, indices_query, original_query_sequence) -> Dict[int, int]:
-    """Query index -> index in the template's aligned sequence, for the columns where both are residues."""
+    """Index in the original query -> index in the hit's (gap-free) aligned sequence, for the columns where both have a
+    residue.  The alignment's own indices (``-1`` = gap) are first made relative to their smallest entry on both sides; the
+    query side is then moved to where the aligned query segment occurs in the original query - the search may have been
+    run with a part of it.  Pairs that would fall outside either sequence are dropped (fastfold/data/templates.py:681-738)."""
     if not hit_query_sequence:
         return {}
     offset = original_query_sequence.find(hit_query_sequence.replace("-", ""))
-    fixed_hit = [x for x in indices_hit if x != -1]
-    min_idx = min(fixed_hit) if fixed_hit else 0
+    n_hit = len(hit_sequence.replace("-", ""))
+
+    def relative(indices):
+        present = [x for x in indices if x > -1]
+        low = min(present) if present else 0
+        return [x - low if x > -1 else -1 for x in indices]
+
     mapping = {}
-    for q_i, q_t in zip(indices_query, indices_hit):
-        if q_t != -1 and q_i != -1:
-            mapping[q_i + offset] = q_t - min_idx
+    for q, t in zip(relative(indices_query), relative(indices_hit)):
+        if q != -1 and t != -1 and t < n_hit and q + offset < len(original_query_sequence):
+            mapping[q + offset] = t
     return mapping
 
 
@@ -260,16 +268,16 @@ def _check_residue_distances(all_positions: np.ndarray, all_positions_mask: np.n
         prev_known = known
 
 
-def _get_atom_positions(mmcif_object, auth_chain_id: str, max_ca_ca_distance: float) -> Tuple[np.ndarray, np.ndarray]:
+def _get_atom_positions(mmcif_object, auth_chain_id: str, max_ca_ca_distance: float, _zero_center_positions: bool = True) -> Tuple[np.ndarray, np.ndarray]:
     if auth_chain_id not in mmcif_object.chain_to_seqres:
         raise NoChainsError("chain %s not in %s" % (auth_chain_id, mmcif_object.file_id))
-    pos, mask = mmcif_parsing.get_atom_coords(mmcif_object, auth_chain_id, _zero_center_positions=False)
+    pos, mask = mmcif_parsing.get_atom_coords(mmcif_object, auth_chain_id, _zero_center_positions=_zero_center_positions)
     _check_residue_distances(pos, mask, max_ca_ca_distance)
     return pos, mask
 
 
 def extract_template_features(mmcif_object, pdb_id: str, mapping: Mapping[int, int], template_sequence: str, query_sequence: str,
-                              template_chain_id: str, kalign_binary_path: Optional[str]) -> Tuple[Dict[str, Any], Optional[str]]:
+                              template_chain_id: str, kalign_binary_path: Optional[str], _zero_center_positions: bool = True) -> Tuple[Dict[str, Any], Optional[str]]:
     if mmcif_object is None or not mmcif_object.chain_to_seqres:
         raise NoChainsError("No chains in PDB: %s_%s" % (pdb_id, template_chain_id))
     warning = None
@@ -284,7 +292,7 @@ def extract_template_features(mmcif_object, pdb_id: str, mapping: Mapping[int, i
         seqres, mapping = _realign_pdb_template_to_query(template_sequence, template_chain_id, mmcif_object, mapping, kalign_binary_path)
         offset = 0
     try:
-        all_pos, all_mask = _get_atom_positions(mmcif_object, chain_id, max_ca_ca_distance=150.0)
+        all_pos, all_mask = _get_atom_positions(mmcif_object, chain_id, max_ca_ca_distance=150.0, _zero_center_positions=_zero_center_positions)
     except (CaDistanceError, KeyError) as e:
         raise NoAtomDataInTemplateError("Could not get atom data (%s_%s): %s" % (pdb_id, chain_id, e))
     n = len(query_sequence)
@@ -304,7 +312,7 @@ def extract_template_features(mmcif_object, pdb_id: str, mapping: Mapping[int, i
             pdb_id, chain_id, min(mapping.values(), default=0) + offset, max(mapping.values(), default=0) + offset))
     out_seq = "".join(out_seq)
     aatype = rc.sequence_to_onehot(out_seq, rc.HHBLITS_AA_TO_ID)
-    return ({"template_all_atom_positions": out_pos, "template_all_atom_masks": out_mask, "template_sequence": out_seq.encode(),
+    return ({"template_all_atom_positions": out_pos, "template_all_atom_mask": out_mask, "template_sequence": out_seq.encode(),
              "template_aatype": np.array(aatype), "template_domain_names": ("%s_%s" % (pdb_id.lower(), chain_id)).encode()}, warning)
 
 
@@ -386,7 +394,7 @@ class TemplateHitFeaturizer:
                 return SingleHitResult(None, msg if self._strict_error_check else None, None)
         try:
             feats, warning = extract_template_features(parsed.mmcif_object, pdb_id, mapping, template_sequence, query_sequence, chain_id,
-                                                       self._kalign_binary_path)
+                                                       self._kalign_binary_path, _zero_center_positions=self._zero_center_positions)
             feats["template_sum_probs"] = [hit.sum_probs if hit.sum_probs is not None else 0.0]
             return SingleHitResult(feats, None, warning)
         except (NoChainsError, NoAtomDataInTemplateError, TemplateAtomMaskAllZerosError) as e:
@@ -454,7 +462,7 @@ class TemplateHitFeaturizer:
         if accepted:
             feats = {k: np.stack(collected[k], axis=0).astype(TEMPLATE_FEATURES[k]) for k in collected}
         else:
-            feats = {"template_aatype": np.zeros((0, n, 22), np.int64), "template_all_atom_masks": np.zeros((0, n, rc.atom_type_num), np.float32),
+            feats = {"template_aatype": np.zeros((0, n, 22), np.int64), "template_all_atom_mask": np.zeros((0, n, rc.atom_type_num), np.float32),
                      "template_all_atom_positions": np.zeros((0, n, rc.atom_type_num, 3), np.float32),
                      "template_domain_names": np.zeros((0,), object), "template_sequence": np.zeros((0,), object),
                      "template_sum_probs": np.zeros((0, 1), np.float32)}

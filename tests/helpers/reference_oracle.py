@@ -4,7 +4,8 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
+``mode``: ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
+the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
 ``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
 corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
 ``features`` (the tensor pipeline on a raw feature dict: the un-ensembled transforms, then one ensemble member
@@ -60,6 +61,43 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "mmcif":
+        import dataclasses
+        import datetime
+        from fastfold.data import mmcif_parsing, parsers, templates
+
+        def plain(x):
+            if dataclasses.is_dataclass(x):
+                return {f.name: plain(getattr(x, f.name)) for f in dataclasses.fields(x)}
+            if isinstance(x, dict):
+                return {k: plain(v) for k, v in x.items()}
+            if isinstance(x, (list, tuple)):
+                return [plain(v) for v in x]
+            return x
+        out = {"files": {}}
+        for file_id, chain in d["parse"]:
+            text = open(os.path.join(d["mmcif_dir"], file_id + ".cif")).read()
+            res = mmcif_parsing.parse(file_id=file_id, mmcif_string=text)
+            obj = res.mmcif_object
+            entry = {"errors": {str(k): repr(v) for k, v in res.errors.items()}}
+            if obj is not None:
+                pos, mask = mmcif_parsing.get_atom_coords(obj, chain)
+                raw, rawmask = mmcif_parsing.get_atom_coords(obj, chain, _zero_center_positions=False)
+                entry.update(chain_to_seqres=dict(obj.chain_to_seqres), header=dict(obj.header), seqres_to_structure=plain(obj.seqres_to_structure),
+                             pos=pos, mask=mask, raw_pos=raw)
+            out["files"][file_id + "/" + chain] = entry
+        hits = [parsers.TemplateHit(**h) for h in d["hits"]]
+        featurizer = templates.TemplateHitFeaturizer(mmcif_dir=d["mmcif_dir"], max_template_date=d["max_template_date"], max_hits=d["max_hits"],
+                                                     kalign_binary_path=d.get("kalign"), obsolete_pdbs_path=d.get("obsolete"))
+        runs = {}
+        for name, kw in d["queries"].items():
+            date = kw.get("query_release_date")
+            date = datetime.datetime.strptime(date, "%Y-%m-%d") if date else None
+            r = featurizer.get_templates(query_sequence=d["query"], query_release_date=date, hits=hits, query_pdb_code=kw.get("query_pdb_code"))
+            runs[name] = {"features": dict(r.features), "errors": list(r.errors), "warnings": list(r.warnings)}
+        out["templates"] = runs
+        torch.save(out, dst)
+        return
     if mode == "utils":
         from fastfold.common import protein
         from fastfold.model.hub.lr_scheduler import AlphaFoldLRScheduler

@@ -433,3 +433,103 @@ def test_pdb_writer_metrics_and_schedule(tmp_path):
         sched.step()
         lrs.append(opt.param_groups[0]["lr"])
     assert np.allclose(lrs, ref["lrs"], rtol=1e-9, atol=0)
+
+
+def _cif_text(pdb_id, date, chains, resolution="1.80"):
+    """A small but fussy mmCIF file.  ``chains``: ``{label chain: (author chain, sequence)}``; residue 4 of every chain has
+    no coordinates, residue 2 is selenomethionine written as HETATM when the sequence has M there, author numbering starts
+    at 11 with an insertion code on residue 6, waters follow, and a second model repeats the first atom."""
+    from fastfold_b200.common import residue_constants as rc
+    three = {c: [rc.restype_1to3[a] if a != "M" else "MSE" for a in seq] for c, (_, seq) in chains.items()}
+    comps = sorted({t for v in three.values() for t in v} | {"HOH"})
+    lines = ["data_%s" % pdb_id.upper(), "#", "_entry.id %s" % pdb_id.upper(), "_exptl.method 'X-RAY DIFFRACTION'", "_refine.ls_d_res_high %s" % resolution,
+             "#", "loop_", "_pdbx_audit_revision_history.ordinal", "_pdbx_audit_revision_history.revision_date", "1 %s" % date, "2 2031-07-13", "#",
+             "loop_", "_struct_asym.id", "_struct_asym.entity_id"] + ["%s %d" % (c, i + 1) for i, c in enumerate(chains)] + ["W %d" % (len(chains) + 1), "#",
+             "loop_", "_chem_comp.id", "_chem_comp.type", "_chem_comp.name"]
+    lines += ["%s %s '%s'" % (t, "non-polymer" if t == "HOH" else "'L-peptide linking'", "water" if t == "HOH" else "amino acid; %s" % t.lower()) for t in comps]
+    lines += ["#", "loop_", "_entity_poly_seq.entity_id", "_entity_poly_seq.num", "_entity_poly_seq.mon_id", "_entity_poly_seq.hetero"]
+    for e, c in enumerate(chains):
+        lines += ["%d %d %s n" % (e + 1, i + 1, t) for i, t in enumerate(three[c])]
+    lines += ["#", "loop_"] + ["_atom_site." + k for k in ("group_PDB", "id", "type_symbol", "label_atom_id", "label_alt_id", "label_comp_id",
+                                                         "label_asym_id", "label_entity_id", "label_seq_id", "pdbx_PDB_ins_code", "Cartn_x",
+                                                         "Cartn_y", "Cartn_z", "occupancy", "B_iso_or_equiv", "auth_seq_id", "auth_asym_id",
+                                                         "pdbx_PDB_model_num")]
+    k = 1
+    for e, (c, (author, seq)) in enumerate(chains.items()):
+        for i, t in enumerate(three[c]):
+            if i == 3:
+                continue
+            atoms = ["N", "CA", "C", "O"] + (["CB"] if t != "GLY" else []) + (["SE"] if t == "MSE" else []) + (["CD", "NH1", "NH2"] if t == "ARG" else [])
+            number, icode = (i + 11, "?") if i < 6 else (i + 10, "A") if i == 6 else (i + 10, "?")
+            for a, name in enumerate(atoms):
+                x, y, z = 3.8 * i + 0.37 * a + 40.0 * e, 1.0 + 1.1 * a - 0.01 * i * a, -2.0 + 0.5 * a + 7.0 * e
+                lines.append("%s %d %s %s . %s %s %d %d %s %.3f %.3f %.3f 1.00 20.00 %d %s 1" % (
+                    "HETATM" if t == "MSE" else "ATOM", k, name[0], name, t, c, e + 1, i + 1, icode, x, y, z, number, author))
+                k += 1
+    lines.append("HETATM %d O O . HOH W %d . ? 1.000 2.000 3.000 1.00 30.00 201 %s 1" % (k, len(chains) + 1, list(chains.values())[0][0]))
+    lines.append("ATOM %d N N . %s %s 1 1 ? 9.000 9.000 9.000 1.00 20.00 11 %s 2" % (k + 1, list(three.values())[0][0], list(chains)[0], list(chains.values())[0][0]))
+    return "\n".join(lines) + "\n#\n"
+
+
+def test_mmcif_reader_and_template_featuriser(tmp_path):
+    """mmCIF reading (chains, SEQRES-to-structure map, header, coordinates incl. selenomethionine and arginine naming) and
+    the hhsearch template featuriser (date and identity filters, hit-to-query mapping, features) on a directory of files.
+    The reference reads the files through a BioPython stand-in written independently of this package's reader."""
+    import dataclasses
+    import numpy as np
+    from fastfold_b200.data import mmcif_parsing, parsers, templates
+    d = tmp_path / "mmcif"
+    d.mkdir()
+    seq_a, seq_b = "ACMEFGRIKLMNPQ", "GSHRLEDPVK"
+    (d / "1abc.cif").write_text(_cif_text("1abc", "1999-05-01", {"A": ("A", seq_a), "B": ("C", seq_b)}))
+    (d / "2xyz.cif").write_text(_cif_text("2xyz", "2030-01-01", {"A": ("A", seq_a)}))
+    (d / "3old.cif").write_text(_cif_text("3old", "1990-01-01", {"A": ("A", seq_a[:5] + seq_a[6:12])}, resolution="2.50"))    # lacks residue 5 of the query
+    query = "MM" + seq_a + "WW" + seq_b
+
+    def hit(i, name, q, h, iq, ih, sum_probs):
+        return dict(index=i, name=name, aligned_cols=len([c for c in h if c != "-"]), sum_probs=sum_probs, query=q, hit_sequence=h, indices_query=iq, indices_hit=ih)
+    hits = [hit(1, "1abc_A some protein", seq_a, seq_a, list(range(2, 2 + len(seq_a))), list(range(len(seq_a))), 12.0),
+            hit(2, "2xyz_A too recent", seq_a, seq_a, list(range(2, 2 + len(seq_a))), list(range(len(seq_a))), 11.0),
+            hit(3, "3old_A shorter with a gap", seq_a[:12], seq_a[:5] + "-" + seq_a[6:12], list(range(2, 14)), [0, 1, 2, 3, 4, -1, 6, 7, 8, 9, 10, 11], 9.0),
+            hit(4, "1abc_C other chain", seq_b, seq_b, list(range(18, 18 + len(seq_b))), list(range(len(seq_b))), 5.0)]
+    queries = {"plain": {}, "own_entry": {"query_pdb_code": "1abc"}, "dated": {"query_release_date": "1999-06-01"}}
+    ref = _oracle("mmcif", {"mmcif_dir": str(d), "parse": [("1abc", "A"), ("1abc", "C"), ("3old", "A")], "hits": hits, "query": query,
+                            "max_template_date": "2020-01-01", "max_hits": 4, "queries": queries}, tmp_path)
+
+    def plain(x):
+        if dataclasses.is_dataclass(x):
+            return {f.name: plain(getattr(x, f.name)) for f in dataclasses.fields(x)}
+        if isinstance(x, dict):
+            return {k: plain(v) for k, v in x.items()}
+        if isinstance(x, (list, tuple)):
+            return [plain(v) for v in x]
+        return x
+    for (file_id, chain) in [("1abc", "A"), ("1abc", "C"), ("3old", "A")]:
+        theirs = ref["files"][file_id + "/" + chain]
+        assert not theirs["errors"], theirs["errors"]
+        res = mmcif_parsing.parse(file_id=file_id, mmcif_string=(d / (file_id + ".cif")).read_text())
+        assert not res.errors, res.errors
+        obj = res.mmcif_object
+        assert dict(obj.chain_to_seqres) == theirs["chain_to_seqres"]
+        for k in ("structure_method", "release_date", "resolution"):
+            assert obj.header[k] == theirs["header"][k], k
+        assert plain(obj.seqres_to_structure) == theirs["seqres_to_structure"]
+        pos, mask = mmcif_parsing.get_atom_coords(obj, chain)
+        raw, _ = mmcif_parsing.get_atom_coords(obj, chain, _zero_center_positions=False)
+        assert np.array_equal(mask, theirs["mask"]) and np.allclose(pos, theirs["pos"], atol=1e-4) and np.allclose(raw, theirs["raw_pos"], atol=1e-4)
+    f = templates.TemplateHitFeaturizer(mmcif_dir=str(d), max_template_date="2020-01-01", max_hits=4, kalign_binary_path=None)
+    ours_hits = [parsers.TemplateHit(**h) for h in hits]
+    for name, kw in queries.items():
+        r = f.get_templates(query, hits=ours_hits, **kw)
+        theirs = ref["templates"][name]
+        assert set(r.features) == set(theirs["features"]), name
+        for k, v in theirs["features"].items():
+            a, b = np.asarray(r.features[k]), np.asarray(v)
+            assert a.shape == b.shape, (name, k, a.shape, b.shape)
+            if b.dtype == object:
+                assert list(a) == list(b), (name, k)
+            else:
+                assert np.allclose(a.astype(np.float64), b.astype(np.float64), atol=1e-4), (name, k)
+    assert ref["templates"]["plain"]["features"]["template_aatype"].shape[0] == 3            # 2xyz is after the date cutoff
+    assert ref["templates"]["own_entry"]["features"]["template_aatype"].shape[0] == 1       # only 3old is left
+    assert ref["templates"]["dated"]["features"]["template_aatype"].shape[0] == 1           # 1abc is too close to the query's release

@@ -62,18 +62,19 @@ def test_template_featurizer(tmp_path):
                               indices_query=list(range(2, 2 + len(SEQ))), indices_hit=list(range(len(SEQ))))
     late = parsers.TemplateHit(index=2, name="2xyz_A too new", aligned_cols=len(SEQ), sum_probs=20.0, query=SEQ, hit_sequence=SEQ,
                                indices_query=list(range(2, 2 + len(SEQ))), indices_hit=list(range(len(SEQ))))
-    # indices_query are relative to the aligned query fragment, which the featuriser locates inside the full query
-    hit = parsers.TemplateHit(**{**hit.__dict__, "indices_query": list(range(len(SEQ)))})
-    late = parsers.TemplateHit(**{**late.__dict__, "indices_query": list(range(len(SEQ)))})
-    f = templates.TemplateHitFeaturizer(mmcif_dir=str(tmp_path), max_template_date="2020-01-01", max_hits=4)
+    # indices_query are positions in the query as an HHR file gives them; a hit whose indices are relative to the aligned
+    # fragment (the fragment is located inside the full query) maps to the same residues
+    relative = parsers.TemplateHit(**{**hit.__dict__, "indices_query": list(range(len(SEQ)))})
+    f = templates.TemplateHitFeaturizer(mmcif_dir=str(tmp_path), max_template_date="2020-01-01", max_hits=4, _zero_center_positions=False)
+    assert np.array_equal(f.get_templates(query, [relative]).features["template_all_atom_mask"], f.get_templates(query, [hit]).features["template_all_atom_mask"])
     res = f.get_templates(query, [hit, late])
     feats = res.features
     assert feats["template_aatype"].shape == (1, len(query), 22)
     assert feats["template_all_atom_positions"].shape == (1, len(query), 37, 3)
     assert feats["template_domain_names"][0] == b"1abc_A"
     ca = rc.atom_order["CA"]
-    assert feats["template_all_atom_masks"][0, 2, ca] == 1 and feats["template_all_atom_masks"][0, 0, ca] == 0
-    assert feats["template_all_atom_masks"][0, 2 + 3].sum() == 0                         # the residue without coordinates
+    assert feats["template_all_atom_mask"][0, 2, ca] == 1 and feats["template_all_atom_mask"][0, 0, ca] == 0
+    assert feats["template_all_atom_mask"][0, 2 + 3].sum() == 0                         # the residue without coordinates
     assert np.allclose(feats["template_all_atom_positions"][0, 2 + 2, ca], [3.8 * 2 + 0.1, 2.0, -1.5], atol=1e-3)
     assert feats["template_sequence"][0].decode() == "--" + SEQ + "--"
     assert abs(feats["template_sum_probs"][0, 0] - 12.0) < 1e-6
