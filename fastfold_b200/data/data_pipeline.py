@@ -33,20 +33,31 @@ def make_sequence_features(sequence: str, description: str, num_res: int) -> Fea
     }
 
 
-def make_msa_features(msas: Sequence[Sequence[str]], deletion_matrices: Sequence[parsers.DeletionMatrix]) -> FeatureDict:
+def make_msa_features(msas, deletion_matrices: Optional[Sequence[parsers.DeletionMatrix]] = None, descriptions=None) -> FeatureDict:
+    """Rows of several alignments stacked in order, each distinct row once (first occurrence), as HH-suite residue ids, with
+    their deletion counts and the species tag of their description (empty when the description has none; used to pair rows
+    across chains).  ``msas``: ``parsers.Msa`` objects (fastfold/data/data_pipeline.py:205-240), or lists of rows together with
+    ``deletion_matrices`` (and optionally ``descriptions``)."""
     if not msas:
         raise ValueError("At least one MSA must be provided.")
-    int_msa, deletion_matrix, seen = [], [], set()
-    for msa, dels in zip(msas, deletion_matrices):
-        for seq, d in zip(msa, dels):
+    if deletion_matrices is not None:
+        descriptions = descriptions if descriptions is not None else [[""] * len(m) for m in msas]
+        msas = [parsers.Msa(list(m), list(d), list(t)) for m, d, t in zip(msas, deletion_matrices, descriptions)]
+    from .msa_pairing import get_identifiers
+    int_msa, deletion_matrix, species, seen = [], [], [], set()
+    for index, msa in enumerate(msas):
+        if not len(msa):
+            raise ValueError("MSA %d must contain at least one sequence." % index)
+        for seq, dels, desc in zip(msa.sequences, msa.deletion_matrix, msa.descriptions):
             if seq in seen:
                 continue
             seen.add(seq)
             int_msa.append([rc.HHBLITS_AA_TO_ID[r] for r in seq])
-            deletion_matrix.append(d)
-    num_res = len(msas[0][0])
+            deletion_matrix.append(dels)
+            species.append(get_identifiers(desc).species_id.encode("utf-8"))
+    num_res = len(msas[0].sequences[0])
     return {"deletion_matrix_int": np.array(deletion_matrix, dtype=np.int32), "msa": np.array(int_msa, dtype=np.int32),
-            "num_alignments": np.array([len(int_msa)] * num_res, dtype=np.int32)}
+            "num_alignments": np.array([len(int_msa)] * num_res, dtype=np.int32), "msa_species_identifiers": np.array(species, dtype=np.object_)}
 
 
 def empty_template_features(num_res: int) -> FeatureDict:
@@ -189,21 +200,20 @@ class DataPipeline:
 
     @classmethod
     def _read_alignments(cls, alignment_dir, query, _alignment_index=None):
-        msas, dels = [], []
+        msas = []
         for name, text in cls._alignment_files(alignment_dir, _alignment_index):
             stem, ext = os.path.splitext(name)
             if ext == ".a3m":
-                m, d, _ = parsers.parse_a3m(text)
+                msa = parsers.Msa(*parsers.parse_a3m(text)[:3])
             elif ext == ".sto" and stem not in ("hmm_output", "hmmsearch_output"):       # those hold template hits, not an MSA
-                m, d, _ = parsers.parse_stockholm(text)
+                msa = parsers.Msa(*parsers.parse_stockholm(text)[:3])
             else:
                 continue
-            if m and len(m[0]) == len(query):
-                msas.append(m)
-                dels.append(d)
+            if len(msa) and len(msa.sequences[0]) == len(query):
+                msas.append(msa)
         if not msas:      # single-sequence mode
-            msas, dels = [[query]], [[[0] * len(query)]]
-        return msas, dels
+            msas = [parsers.Msa([query], [[0] * len(query)], ["dummy"])]
+        return msas
 
     @classmethod
     def _read_template_hits(cls, alignment_dir, input_sequence=None, _alignment_index=None):
@@ -229,8 +239,7 @@ class DataPipeline:
         so that the entry and anything released within 60 days before it are not used as templates."""
         n = len(sequence)
         feats = dict(make_sequence_features(sequence, description, n))
-        msas, dels = self._read_alignments(alignment_dir, sequence, _alignment_index)
-        feats.update(make_msa_features(msas, dels))
+        feats.update(make_msa_features(self._read_alignments(alignment_dir, sequence, _alignment_index)))
         hits = {}
         if self.template_featurizer is not None and alignment_dir:
             hits = self._read_template_hits(alignment_dir, sequence, _alignment_index)
@@ -240,7 +249,7 @@ class DataPipeline:
 
 def _ground_truth_features(positions, mask, resolution=1.0, is_distillation=False):
     return {"all_atom_positions": np.asarray(positions, np.float32), "all_atom_mask": np.asarray(mask, np.float32),
-            "resolution": np.array(resolution, np.float32), "is_distillation": np.array(1.0 if is_distillation else 0.0, np.float32)}
+            "resolution": np.array([resolution], np.float32), "is_distillation": np.array(1.0 if is_distillation else 0.0, np.float32)}
 
 
 def _process_structure(self, sequence, description, alignment_dir, positions, mask, resolution, is_distillation, query_pdb_code=None,
@@ -494,17 +503,8 @@ class DataPipelineMultimer:
         else:
             msa, dels, descs = parsers.parse_stockholm(open(path).read())
             msa, dels, descs = msa[:self._max_uniprot_hits], dels[:self._max_uniprot_hits], descs[:self._max_uniprot_hits]
-        feats = make_msa_features([msa], [dels])
-        species = [msa_pairing.get_identifiers(d).species_id.encode() for d in descs]
-        # make_msa_features removed duplicate rows: keep the identifiers of the rows that survived, in order
-        seen, kept = set(), []
-        for s_, sp in zip(msa, species):
-            if s_ not in seen:
-                seen.add(s_)
-                kept.append(sp)
-        out = {k + "_all_seq": v for k, v in feats.items() if k in ("msa", "deletion_matrix_int")}
-        out["msa_species_identifiers_all_seq"] = np.array(kept, dtype=object)
-        return out
+        feats = make_msa_features([parsers.Msa(list(msa), list(dels), list(descs))])
+        return {k + "_all_seq": feats[k] for k in ("msa", "deletion_matrix_int", "msa_species_identifiers")}
 
     def _process_chain(self, chain_id, sequence, description, alignment_dir, is_homomer_or_monomer):
         chain_dir = os.path.join(alignment_dir, chain_id) if alignment_dir else None

@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
+``mode``: ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
 ``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
 corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
@@ -61,6 +61,16 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "pipeline":
+        from fastfold.data import data_pipeline, mmcif_parsing, templates
+        featurizer = templates.TemplateHitFeaturizer(mmcif_dir=d["mmcif_dir"], max_template_date=d["max_template_date"], max_hits=4, kalign_binary_path=None)
+        pipe = data_pipeline.DataPipeline(template_featurizer=featurizer)
+        out = {"fasta": dict(pipe.process_fasta(d["fasta"], d["alignment_dir"]))}
+        text = open(os.path.join(d["mmcif_dir"], d["target"][0] + ".cif")).read()
+        obj = mmcif_parsing.parse(file_id=d["target"][0], mmcif_string=text).mmcif_object
+        out["mmcif"] = dict(pipe.process_mmcif(obj, d["target_alignment_dir"], d["target"][1]))
+        torch.save(out, dst)
+        return
     if mode == "mmcif":
         import dataclasses
         import datetime

@@ -533,3 +533,56 @@ def test_mmcif_reader_and_template_featuriser(tmp_path):
     assert ref["templates"]["plain"]["features"]["template_aatype"].shape[0] == 3            # 2xyz is after the date cutoff
     assert ref["templates"]["own_entry"]["features"]["template_aatype"].shape[0] == 1       # only 3old is left
     assert ref["templates"]["dated"]["features"]["template_aatype"].shape[0] == 1           # 1abc is too close to the query's release
+
+
+def test_raw_feature_pipeline_from_alignment_directories(tmp_path):
+    """FASTA + alignment directory (A3M, Stockholm, HHR) -> raw features, and mmCIF chain + alignment directory -> raw
+    training features (sequence, MSA with deletion counts and de-duplication across files, templates with the release-date
+    margin, ground-truth coordinates, resolution)."""
+    import numpy as np
+    from fastfold_b200.data import mmcif_parsing
+    from fastfold_b200.data.data_pipeline import DataPipeline
+    from fastfold_b200.data.templates import TemplateHitFeaturizer
+    mm = tmp_path / "mmcif"
+    mm.mkdir()
+    seq_a = "ACMEFGRIKLMNPQ"
+    (mm / "1abc.cif").write_text(_cif_text("1abc", "1999-05-01", {"A": ("A", seq_a)}))
+    (mm / "4tgt.cif").write_text(_cif_text("4tgt", "2005-03-01", {"A": ("A", "MM" + seq_a + "WW")}))
+    query = "MM" + seq_a + "WW"
+    hhr = PARSER_TEXTS["hhr"].replace("Match_columns 16", "Match_columns 18")
+    # one hit that aligns residues 3-16 of the query with residues 1-14 of 1abc chain A
+    hhr = ("Query         query\nMatch_columns 18\n\nNo 1\n>1abc_A test template\n"
+           "Probab=99.00  E-value=1e-10  Score=50.00  Aligned_cols=14  Identities=100%  Similarity=1.500  Sum_probs=13.5  Template_Neff=5.000\n\n"
+           "Q query             3 ACMEFGRIKLMNPQ   16 (18)\nQ Consensus         3 acmefgriklmnpq   16 (18)\n                      ||||||||||||||\n"
+           "T Consensus         1 acmefgriklmnpq   14 (14)\nT 1abc_A            1 ACMEFGRIKLMNPQ   14 (14)\n\n")
+    a3m = ">query\n%s\n>h1\n%s\n>h2 with insertions\n%s\n>h1 duplicate\n%s\n" % (query, "MMACMEFGRIKLMNPQWA", "MMACMEFGRIKaaaLMNPQW-", "MMACMEFGRIKLMNPQWA")
+    sto = "# STOCKHOLM 1.0\n\nquery %s\nother %s\ngappy %s\n//\n" % (query, "MAACMEFGRIKLMNPQWW", "--ACMEFGRIKLMN----")
+    for name in ("aln_fasta", "aln_target"):
+        a = tmp_path / name
+        a.mkdir()
+        (a / "pdb70_hits.hhr").write_text(hhr)
+        (a / "bfd_uniclust_hits.a3m").write_text(a3m)
+    (tmp_path / "aln_target" / "mgnify_hits.sto").write_text(sto)
+    fasta = tmp_path / "q.fasta"
+    fasta.write_text(">query test\n%s\n" % query)
+    ref = _oracle("pipeline", {"mmcif_dir": str(mm), "max_template_date": "2020-01-01", "fasta": str(fasta), "alignment_dir": str(tmp_path / "aln_fasta"),
+                               "target": ("4tgt", "A"), "target_alignment_dir": str(tmp_path / "aln_target")}, tmp_path)
+    pipe = DataPipeline(template_featurizer=TemplateHitFeaturizer(mmcif_dir=str(mm), max_template_date="2020-01-01", max_hits=4, kalign_binary_path=None))
+    ours = {"fasta": pipe.process_fasta(str(fasta), str(tmp_path / "aln_fasta"))}
+    obj = mmcif_parsing.parse(file_id="4tgt", mmcif_string=(mm / "4tgt.cif").read_text()).mmcif_object
+    ours["mmcif"] = pipe.process_mmcif(obj, str(tmp_path / "aln_target"), "A")
+    for part in ("fasta", "mmcif"):
+        theirs = ref[part]
+        assert not [k for k in theirs if k not in ours[part]], (part, [k for k in theirs if k not in ours[part]])
+        for k, v in theirs.items():
+            a, b = np.asarray(ours[part][k]), np.asarray(v)
+            assert a.shape == b.shape, (part, k, a.shape, b.shape)
+            if k in ("msa", "deletion_matrix_int", "msa_species_identifiers"):
+                continue                          # row order follows the directory listing order in the reference: compared as sets below
+            if b.dtype == object or b.dtype.kind in "SU":
+                assert [x for x in a.ravel()] == [x for x in b.ravel()], (part, k)
+            else:
+                assert np.allclose(a.astype(np.float64), b.astype(np.float64), atol=1e-4), (part, k)
+        rows = lambda e: sorted(zip(map(tuple, np.asarray(e["msa"]).tolist()), map(tuple, np.asarray(e["deletion_matrix_int"]).tolist())))
+        assert rows(ours[part]) == rows(theirs), part
+    assert ref["fasta"]["template_aatype"].shape[0] == 1 and ref["mmcif"]["msa"].shape[0] == 5
