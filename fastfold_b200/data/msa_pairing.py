@@ -408,7 +408,7 @@ def pad_msa(example: MutableMapping[str, np.ndarray], min_num_seq: int) -> Mutab
         pad = min_num_seq - n
         for k in ("msa", "deletion_matrix", "bert_mask", "msa_mask"):
             if k in example:
-                example[k] = np.pad(example[k], ((0, pad), (0, 0)), constant_values=MSA_PAD_VALUES.get(k, 0) if k == "msa" else 0)
+                example[k] = np.pad(example[k], ((0, pad), (0, 0)))      # zeros everywhere: the rows are switched off by msa_mask
         if "cluster_bias_mask" in example:
             example["cluster_bias_mask"] = np.pad(example["cluster_bias_mask"], ((0, pad),))
     return example

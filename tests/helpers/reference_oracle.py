@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
+``mode``: ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
 ``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
 corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
@@ -61,6 +61,13 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "multimer_pipeline":
+        from fastfold.data import data_pipeline
+        from fastfold.data import templates
+        featurizer = templates.TemplateHitFeaturizer(mmcif_dir=d["mmcif_dir"], max_template_date="2100-01-01", max_hits=4, kalign_binary_path=None)
+        pipe = data_pipeline.DataPipelineMultimer(data_pipeline.DataPipeline(template_featurizer=featurizer))
+        torch.save({"example": dict(pipe.process_fasta(d["fasta"], d["alignment_dir"]))}, dst)
+        return
     if mode == "pipeline":
         from fastfold.data import data_pipeline, mmcif_parsing, templates
         featurizer = templates.TemplateHitFeaturizer(mmcif_dir=d["mmcif_dir"], max_template_date=d["max_template_date"], max_hits=4, kalign_binary_path=None)

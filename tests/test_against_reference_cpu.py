@@ -586,3 +586,51 @@ def test_raw_feature_pipeline_from_alignment_directories(tmp_path):
         rows = lambda e: sorted(zip(map(tuple, np.asarray(e["msa"]).tolist()), map(tuple, np.asarray(e["deletion_matrix_int"]).tolist())))
         assert rows(ours[part]) == rows(theirs), part
     assert ref["fasta"]["template_aatype"].shape[0] == 1 and ref["mmcif"]["msa"].shape[0] == 5
+
+
+@pytest.mark.parametrize("kind", ["hetero", "homo"])
+def test_multimer_pipeline_from_fasta_and_chain_directories(kind, tmp_path):
+    """Multi-sequence FASTA + one alignment directory per chain (own alignment, species-tagged UniProt hits) -> merged
+    example, padded to 512 rows."""
+    import numpy as np
+    from fastfold_b200.data.data_pipeline import DataPipeline, DataPipelineMultimer
+    rng = np.random.RandomState(4)
+    letters = list("ACDEFGHIKLMNPQRSTVWY")
+
+    def mutate(seq):
+        return "".join(c if rng.rand() > 0.3 else rng.choice(letters) for c in seq)
+    s1, s2 = "".join(rng.choice(letters, 13)), "".join(rng.choice(letters, 12))     # templates shorter than 10 residues are rejected
+    chains = {"A": s1, "B": s2 if kind == "hetero" else s1}
+    species = {"A": ["HUMAN", "MOUSE", "YEAST", "RAT", "MOUSE"], "B": ["MOUSE", "HUMAN", "BOVIN", "HUMAN"]}
+    aln = tmp_path / "aln"
+    for cid, seq in chains.items():
+        d = aln / cid
+        d.mkdir(parents=True)
+        (d / "bfd_uniclust_hits.a3m").write_text(">query\n%s\n" % seq + "".join(">h%d\n%s\n" % (i, mutate(seq)) for i in range(5)))
+        rows = ["query %s" % seq] + ["tr|Q%05d|Q%05d_%s/1-%d %s" % (i, i, sp, len(seq), mutate(seq)) for i, sp in enumerate(species[cid])]
+        (d / "uniprot_hits.sto").write_text("# STOCKHOLM 1.0\n\n" + "\n".join(rows) + "\n//\n")
+    # one template per chain (the reference's merge cannot handle a chain without any)
+    from fastfold_b200.data.templates import TemplateHitFeaturizer
+    mm = tmp_path / "mmcif"
+    mm.mkdir()
+    for cid, seq in chains.items():
+        pdb_id = "1aa" + cid.lower()
+        query_seq, seq = seq, "W" + seq[1:4] + "Y" + seq[5:]          # an exact copy of the query would be rejected as a duplicate
+        (mm / (pdb_id + ".cif")).write_text(_cif_text(pdb_id, "1999-05-01", {"A": ("A", seq)}))
+        n = len(seq)
+        (aln / cid / "pdb70_hits.hhr").write_text(
+            "Query         query\nMatch_columns %d\n\nNo 1\n>%s_A template\n"
+            "Probab=99.00  E-value=1e-10  Score=50.00  Aligned_cols=%d  Identities=100%%  Similarity=1.500  Sum_probs=%d.5  Template_Neff=5.000\n\n"
+            "Q query             1 %s   %d (%d)\nQ Consensus         1 %s   %d (%d)\n                      %s\n"
+            "T Consensus         1 %s   %d (%d)\nT %s_A            1 %s   %d (%d)\n\n" % (n, pdb_id, n, n, query_seq, n, n, query_seq.lower(), n, n, "|" * n, seq.lower(), n, n, pdb_id, seq, n, n))
+    fasta = tmp_path / "complex.fasta"
+    fasta.write_text("".join(">%s\n%s\n" % (c, s) for c, s in chains.items()))
+    ref = _oracle("multimer_pipeline", {"fasta": str(fasta), "alignment_dir": str(aln), "mmcif_dir": str(mm)}, tmp_path)["example"]
+    featurizer = TemplateHitFeaturizer(mmcif_dir=str(mm), max_template_date="2100-01-01", max_hits=4, kalign_binary_path=None)
+    ours = DataPipelineMultimer(DataPipeline(template_featurizer=featurizer)).process_fasta(str(fasta), str(aln))
+    assert not [k for k in ref if k not in ours]
+    for k, v in ref.items():
+        a, b = np.asarray(ours[k]), np.asarray(v)
+        assert a.shape == b.shape, (k, a.shape, b.shape)
+        assert np.allclose(a.astype(np.float64), b.astype(np.float64), atol=1e-6), k
+    assert ref["msa"].shape[0] == 512 and ref["aatype"].shape[0] == sum(len(s) for s in chains.values())
