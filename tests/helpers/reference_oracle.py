@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
+``mode``: ``data_modules`` (training-set filters, ``OpenFoldSingleDataset`` items, the batch collator), ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
 ``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
 corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
@@ -61,6 +61,21 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "data_modules":
+        from fastfold.data import data_modules as dm
+        config = _config(d)
+        out = {"filters": [(dm.deterministic_train_filter(e), dm.get_stochastic_train_filter_prob(e)) for e in d["cache_entries"]]}
+        ds = dm.OpenFoldSingleDataset(data_dir=d["data_dir"], alignment_dir=d["alignment_dir"], template_mmcif_dir=d["mmcif_dir"],
+                                      max_template_date="2100-01-01", config=config.data, kalign_binary_path=None, mode="train", _output_raw=True)
+        out["chain_ids"] = [ds.idx_to_chain_id(i) for i in range(len(ds))]
+        out["raw"] = {ds.idx_to_chain_id(i): dict(ds[i]) for i in range(len(ds))}
+        feats = dm.OpenFoldSingleDataset(data_dir=d["data_dir"], alignment_dir=d["alignment_dir"], template_mmcif_dir=d["mmcif_dir"],
+                                         max_template_date="2100-01-01", config=config.data, kalign_binary_path=None, mode="eval")
+        out["eval_shapes"] = {k: tuple(v.shape) for k, v in feats[0].items()}
+        collated = dm.OpenFoldBatchCollator(config.data, "eval")([ds[0]])           # raw examples in, features out, no batch dim for one
+        out["collated_shapes"] = {k: tuple(v.shape) for k, v in collated.items()}
+        torch.save(out, dst)
+        return
     if mode == "multimer_pipeline":
         from fastfold.data import data_pipeline
         from fastfold.data import templates

@@ -634,3 +634,54 @@ def test_multimer_pipeline_from_fasta_and_chain_directories(kind, tmp_path):
         assert a.shape == b.shape, (k, a.shape, b.shape)
         assert np.allclose(a.astype(np.float64), b.astype(np.float64), atol=1e-6), k
     assert ref["msa"].shape[0] == 512 and ref["aatype"].shape[0] == sum(len(s) for s in chains.values())
+
+
+def test_training_data_modules(tmp_path):
+    """Hard and stochastic training-set filters, ``OpenFoldSingleDataset`` (chain ids from the alignment directory, mmCIF
+    targets, raw and processed items) and the batch collator (one example -> no batch dimension)."""
+    import numpy as np
+    from fastfold_b200.config import model_config
+    from fastfold_b200.data import data_modules as dm
+    seq_a = "ACMEFGRIKLMNPQ"
+    data, mm, aln = tmp_path / "data", tmp_path / "mmcif", tmp_path / "aln"
+    for p in (data, mm, aln):
+        p.mkdir()
+    (mm / "1abc.cif").write_text(_cif_text("1abc", "1999-05-01", {"A": ("A", "W" + seq_a[1:])}))
+    targets = {"4tgt_A": "MM" + seq_a + "WW", "5tgt_A": "GG" + seq_a + "KK"}
+    for name, seq in targets.items():
+        (data / (name[:4] + ".cif")).write_text(_cif_text(name[:4], "2005-03-01", {"A": ("A", seq)}))
+        d = aln / name
+        d.mkdir()
+        (d / "bfd_uniclust_hits.a3m").write_text(">query\n%s\n>h1\n%s\n>h2\n%s\n" % (seq, seq[:-1] + "A", "A" + seq[1:]))
+        (d / "pdb70_hits.hhr").write_text(
+            "Query         query\nMatch_columns 18\n\nNo 1\n>1abc_A template\n"
+            "Probab=99.00  E-value=1e-10  Score=50.00  Aligned_cols=14  Identities=90%  Similarity=1.500  Sum_probs=13.5  Template_Neff=5.000\n\n"
+            "Q query             3 ACMEFGRIKLMNPQ   16 (18)\nQ Consensus         3 acmefgriklmnpq   16 (18)\n                      ||||||||||||||\n"
+            "T Consensus         1 wcmefgriklmnpq   14 (14)\nT 1abc_A            1 WCMEFGRIKLMNPQ   14 (14)\n\n")
+    entries = [{"seq": "ACDEFGHIKLMNPQRSTVWY" * 3, "resolution": 2.5, "cluster_size": 4}, {"seq": "A" * 50 + "CD", "resolution": 1.0},
+               {"seq": "ACDEFGHIKL" * 60, "resolution": 10.0, "cluster_size": 1}, {"seq": "ACDEFGHIKL" * 30, "cluster_size": 0}]
+    ref = _oracle("data_modules", {"name": "model_1", "train": True, "edits": {}, "cache_entries": entries, "data_dir": str(data), "alignment_dir": str(aln),
+                                   "mmcif_dir": str(mm)}, tmp_path)
+    for e, (keep, prob) in zip(entries, ref["filters"]):
+        assert dm.deterministic_train_filter(e) == keep and abs(dm.get_stochastic_train_filter_prob(e) - prob) < 1e-12
+    config = model_config("model_1", train=True)
+    ds = dm.OpenFoldSingleDataset(data_dir=str(data), alignment_dir=str(aln), template_mmcif_dir=str(mm), max_template_date="2100-01-01",
+                                  config=config.data, kalign_binary_path=None, mode="train", _output_raw=True)
+    assert sorted(ds.idx_to_chain_id(i) for i in range(len(ds))) == sorted(ref["chain_ids"])
+    for name, theirs in ref["raw"].items():
+        ours = ds[ds.chain_id_to_idx(name)]
+        assert not [k for k in theirs if k not in ours], [k for k in theirs if k not in ours]
+        for k, v in theirs.items():
+            a, b = np.asarray(ours[k]), np.asarray(v)
+            assert a.shape == b.shape, (name, k, a.shape, b.shape)
+            if b.dtype == object or b.dtype.kind in "SU":
+                assert [x for x in a.ravel()] == [x for x in b.ravel()], (name, k)
+            else:
+                assert np.allclose(a.astype(np.float64), b.astype(np.float64), atol=1e-4), (name, k)
+        assert theirs["template_aatype"].shape[0] == 1
+    feats = dm.OpenFoldSingleDataset(data_dir=str(data), alignment_dir=str(aln), template_mmcif_dir=str(mm), max_template_date="2100-01-01",
+                                     config=config.data, kalign_binary_path=None, mode="eval")
+    shapes = {k: tuple(v.shape) for k, v in feats[0].items()}
+    assert shapes == ref["eval_shapes"]
+    collated = dm.OpenFoldBatchCollator(config.data, "eval")([ds[0]])
+    assert {k: tuple(v.shape) for k, v in collated.items()} == ref["collated_shapes"]
