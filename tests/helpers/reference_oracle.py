@@ -4,7 +4,9 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``data_modules`` (training-set filters, ``OpenFoldSingleDataset`` items, the batch collator), ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
+``mode``: ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
+inference runs - with its two GPU-only kernel entry points, fused LayerNorm and fused softmax, replaced by their PyTorch
+definitions so that the path runs on CPU; DAP size 1), ``data_modules`` (training-set filters, ``OpenFoldSingleDataset`` items, the batch collator), ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
 ``multimer_tensors`` (the multimer tensor pipeline stage by stage: un-ensembled transforms, seeded row sampling, BERT-style
 corruption, clustering and ``msa_feat``), ``import_weights`` (its ``import_jax_weights_`` applied to a parameter archive; returns the state dict),
@@ -232,6 +234,36 @@ def main(mode, src, dst):
         torch.save({"loss": float(loss), "parts": {k: float(v) for k, v in parts.items()}}, dst)
         return
     from fastfold.model.hub import AlphaFold
+    if mode == "fast_model":
+        import importlib
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", str(d.get("port", 29533)))
+
+        def softmax(x, mask=None, bias=None):          # fastfold/model/fastnn/kernel/softmax.py: softmax(x + 1e9 (mask - 1) + bias)
+            if mask is not None:
+                while mask.dim() < x.dim():
+                    mask = mask.unsqueeze(-2)
+                x = x + 1e9 * (mask - 1)
+            return torch.softmax(x if bias is None else x + bias, dim=-1)
+
+        class LayerNorm(torch.nn.LayerNorm):
+            def __init__(self, normalized_shape, eps=1e-5):
+                super().__init__(normalized_shape, eps=eps)
+        for name in ("ops", "msa", "triangle", "evoformer", "template", "embedders", "embedders_multimer", "kernel"):
+            module = importlib.import_module("fastfold.model.fastnn." + name)
+            if hasattr(module, "LayerNorm"):
+                module.LayerNorm = LayerNorm
+            if hasattr(module, "fused_softmax"):
+                module.fused_softmax = softmax
+        from fastfold.distributed import init_dap
+        from fastfold.utils.inject_fastnn import inject_fastnn
+        init_dap(1)
+        model = AlphaFold(_config(d)).eval()
+        model.load_state_dict(d["state"], strict=True)
+        model = inject_fastnn(model)
+        with torch.no_grad():
+            torch.save({"out": _tensors(model(d["batch"]))}, dst)
+        return
     model = AlphaFold(_config(d)).eval()
     if mode == "import_weights":
         from fastfold.utils.import_weights import import_jax_weights_

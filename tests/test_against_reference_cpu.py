@@ -685,3 +685,37 @@ def test_training_data_modules(tmp_path):
     assert shapes == ref["eval_shapes"]
     collated = dm.OpenFoldBatchCollator(config.data, "eval")([ds[0]])
     assert {k: tuple(v.shape) for k, v in collated.items()} == ref["collated_shapes"]
+
+
+@pytest.mark.parametrize("name", ["model_1_ptm", "multimer"])
+def test_whole_model_against_the_reference_fast_path(name, tmp_path):
+    """The reference's production path - its own weight injection and fast modules - as the oracle, for the monomer and
+    the multimer model (templates, extra-MSA stack, recycling, multimer block order in both stacks).  Only its fused
+    LayerNorm and softmax kernels are replaced by PyTorch so that it runs on CPU.  The multimer template stack runs in the
+    reference's block order here."""
+    import math
+    from fastfold_b200.utils.inject_fastnn import inject_fastnn
+    from fastfold_b200.utils.synthetic import random_features
+    multimer = "multimer" in name
+    edits = dict(EDITS, **({"model.template.template_pair_stack.tri_mul_first": False} if multimer else {}))
+    c, model = _model(name, edits)
+    batch = random_features(12, 5, 6, n_templ=2, n_recycle=1, seed=2, chains=[7, 5] if multimer else None)
+    if multimer:      # the reference's multimer model builds the extra-MSA feature from the raw deletion counts
+        g = torch.Generator().manual_seed(5)
+        counts = torch.randint(0, 5, batch["extra_msa"].shape, generator=g).float() * (torch.rand(batch["extra_msa"].shape, generator=g) < 0.3)
+        batch["extra_deletion_matrix"] = counts
+        batch["extra_has_deletion"] = counts.clamp(0, 1)
+        batch["extra_deletion_value"] = torch.atan(counts / 3.0) * (2.0 / math.pi)
+    state = model.state_dict()
+    with torch.no_grad():
+        out = model(batch)
+        fast = inject_fastnn(model)(batch)                      # this package's fast modules on the same weights
+    ref = _oracle("fast_model", {"name": name, "edits": {k: v for k, v in edits.items() if "tri_mul_first" not in k}, "state": state,
+                                 "batch": batch, "port": 29533 + (1 if multimer else 0)}, tmp_path)["out"]
+    compared = 0
+    for k, v in ref.items():
+        if torch.is_tensor(v) and k in out and out[k].shape == v.shape:
+            _close(out[k], v, 2e-5, k)
+            _close(fast[k], v, 1e-4, "fast modules: " + k)
+            compared += 1
+    assert compared >= 14
