@@ -45,8 +45,8 @@ def _config(d):
             node = node[p]
         node[parts[-1]] = value
     c.globals.is_multimer = "multimer" in d["name"]
-    c.globals.inplace = False
-    c.globals.chunk_size = None
+    c.globals.inplace = bool(d.get("inplace", False))
+    c.globals.chunk_size = d.get("chunk_size")
     return c
 
 
@@ -261,6 +261,8 @@ def main(mode, src, dst):
         model = AlphaFold(_config(d)).eval()
         model.load_state_dict(d["state"], strict=True)
         model = inject_fastnn(model)
+        from fastfold.model.fastnn import set_chunk_size
+        set_chunk_size(d.get("chunk_size"))
         with torch.no_grad():
             torch.save({"out": _tensors(model(d["batch"]))}, dst)
         return

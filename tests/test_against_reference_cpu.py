@@ -687,8 +687,8 @@ def test_training_data_modules(tmp_path):
     assert {k: tuple(v.shape) for k, v in collated.items()} == ref["collated_shapes"]
 
 
-@pytest.mark.parametrize("name", ["model_1_ptm", "multimer"])
-def test_whole_model_against_the_reference_fast_path(name, tmp_path):
+@pytest.mark.parametrize("name,chunk,inplace", [("model_1_ptm", None, False), ("multimer", None, False), ("model_1_ptm", 4, True), ("multimer", 4, True)])
+def test_whole_model_against_the_reference_fast_path(name, chunk, inplace, tmp_path):
     """The reference's production path - its own weight injection and fast modules - as the oracle, for the monomer and
     the multimer model (templates, extra-MSA stack, recycling, multimer block order in both stacks).  Only its fused
     LayerNorm and softmax kernels are replaced by PyTorch so that it runs on CPU.  The multimer template stack runs in the
@@ -710,8 +710,10 @@ def test_whole_model_against_the_reference_fast_path(name, tmp_path):
     with torch.no_grad():
         out = model(batch)
         fast = inject_fastnn(model)(batch)                      # this package's fast modules on the same weights
+    # chunked, in-place evaluation on the reference's side must give what the plain evaluation gives here
     ref = _oracle("fast_model", {"name": name, "edits": {k: v for k, v in edits.items() if "tri_mul_first" not in k}, "state": state,
-                                 "batch": batch, "port": 29533 + (1 if multimer else 0)}, tmp_path)["out"]
+                                 "batch": batch, "port": 29533 + (1 if multimer else 0) + (2 if chunk else 0), "chunk_size": chunk, "inplace": inplace},
+                  tmp_path)["out"]
     compared = 0
     for k, v in ref.items():
         if torch.is_tensor(v) and k in out and out[k].shape == v.shape:
