@@ -258,13 +258,25 @@ def main(mode, src, dst):
         from fastfold.distributed import init_dap
         from fastfold.utils.inject_fastnn import inject_fastnn
         init_dap(1)
+        if "stack" in d:                  # forward and backward of a bare fast Evoformer stack (as benchmark/perf.py builds it)
+            from fastfold.model.fastnn import EvoformerStack
+            k = d["stack"]
+            stack = EvoformerStack(c_m=k["c_m"], c_z=k["c_z"], c_s=k["c_s"], no_blocks=k["no_blocks"], blocks_per_ckpt=None,
+                                   is_multimer=k["is_multimer"]).eval()
+            stack.load_state_dict(d["state"], strict=True)
+            m, z = d["m"].clone().requires_grad_(True), d["z"].clone().requires_grad_(True)
+            om, oz, s = stack(m, z, d["msa_mask"], d["pair_mask"], chunk_size=None)
+            (om.pow(2).mean() + oz.pow(2).mean() + s.pow(2).mean()).backward()
+            torch.save({"m": om.detach(), "z": oz.detach(), "s": s.detach(), "dm": m.grad, "dz": z.grad,
+                        "grads": {n: p.grad for n, p in stack.named_parameters()}}, dst)
+            return
         model = AlphaFold(_config(d)).eval()
         model.load_state_dict(d["state"], strict=True)
         model = inject_fastnn(model)
         from fastfold.model.fastnn import set_chunk_size
         set_chunk_size(d.get("chunk_size"))
         with torch.no_grad():
-            torch.save({"out": _tensors(model(d["batch"]))}, dst)
+            torch.save({"out": _tensors(model(d["batch"])), "fast_state": model.state_dict()}, dst)
         return
     model = AlphaFold(_config(d)).eval()
     if mode == "import_weights":

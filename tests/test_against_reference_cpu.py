@@ -711,9 +711,16 @@ def test_whole_model_against_the_reference_fast_path(name, chunk, inplace, tmp_p
         out = model(batch)
         fast = inject_fastnn(model)(batch)                      # this package's fast modules on the same weights
     # chunked, in-place evaluation on the reference's side must give what the plain evaluation gives here
-    ref = _oracle("fast_model", {"name": name, "edits": {k: v for k, v in edits.items() if "tri_mul_first" not in k}, "state": state,
+    res = _oracle("fast_model", {"name": name, "edits": {k: v for k, v in edits.items() if "tri_mul_first" not in k}, "state": state,
                                  "batch": batch, "port": 29533 + (1 if multimer else 0) + (2 if chunk else 0), "chunk_size": chunk, "inplace": inplace},
-                  tmp_path)["out"]
+                  tmp_path)
+    ref = res["out"]
+    # the injected models name, shape and fill every parameter alike (fused q/k/v, stacked left / right projections, biases
+    # moved next to their fused epilogues): a checkpoint of either package's fast model loads into the other's
+    injected = model.state_dict()
+    assert set(injected) == set(res["fast_state"])
+    for k, v in res["fast_state"].items():
+        assert v.shape == injected[k].shape and torch.equal(v, injected[k]), k
     compared = 0
     for k, v in ref.items():
         if torch.is_tensor(v) and k in out and out[k].shape == v.shape:
@@ -721,3 +728,36 @@ def test_whole_model_against_the_reference_fast_path(name, chunk, inplace, tmp_p
             _close(fast[k], v, 1e-4, "fast modules: " + k)
             compared += 1
     assert compared >= 14
+
+
+@pytest.mark.parametrize("is_multimer", [False, True])
+def test_fast_evoformer_stack_forward_and_backward(is_multimer, tmp_path):
+    """A bare fast Evoformer stack (as the headline benchmark builds it), with masks that have holes: outputs, input gradients
+    and every parameter gradient against the reference's fast stack on the same weights (same parameter names)."""
+    from fastfold_b200.models.fastnn import EvoformerStack
+    torch.manual_seed(0)
+    c_m, c_z, c_s, blocks, S, N = 32, 16, 24, 2, 6, 9
+    stack = EvoformerStack(c_m, c_z, c_s, blocks, None, is_multimer=is_multimer).eval()
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for p in stack.parameters():
+            if float(p.abs().sum()) == 0.0:
+                p.copy_(torch.randn(p.shape, generator=g) * (0.02 if p.dim() < 2 else 0.5 / p.shape[-1] ** 0.5))
+    m, z = torch.randn(S, N, c_m, generator=g), torch.randn(N, N, c_z, generator=g)
+    msa_mask, pair_mask = (torch.rand(S, N, generator=g) > 0.15).float(), (torch.rand(N, N, generator=g) > 0.15).float()
+    ref = _oracle("fast_model", {"name": "multimer" if is_multimer else "model_1", "edits": {}, "port": 29560 + int(is_multimer),
+                                 "stack": {"c_m": c_m, "c_z": c_z, "c_s": c_s, "no_blocks": blocks, "is_multimer": is_multimer},
+                                 "state": stack.state_dict(), "m": m, "z": z, "msa_mask": msa_mask, "pair_mask": pair_mask}, tmp_path)
+    m_, z_ = m.clone().requires_grad_(True), z.clone().requires_grad_(True)
+    om, oz, s = stack(m_, z_, msa_mask, pair_mask, None)
+    (om.pow(2).mean() + oz.pow(2).mean() + s.pow(2).mean()).backward()
+    for name, ours, theirs in (("m", om, ref["m"]), ("z", oz, ref["z"]), ("s", s, ref["s"]), ("dm", m_.grad, ref["dm"]), ("dz", z_.grad, ref["dz"])):
+        _close(ours.detach(), theirs, 2e-5, name)
+    grads = dict(stack.named_parameters())
+    assert set(grads) == set(ref["grads"])
+    scale = max(float(v.abs().max()) for v in ref["grads"].values() if v is not None)
+    for k, v in ref["grads"].items():
+        if v is None:
+            assert grads[k].grad is None or float(grads[k].grad.abs().max()) == 0.0, k
+        else:
+            assert float((grads[k].grad - v).abs().max()) <= 2e-5 * max(scale * 1e-2, float(v.abs().max())) + 1e-9, k
