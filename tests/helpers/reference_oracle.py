@@ -275,6 +275,16 @@ def main(mode, src, dst):
         model = inject_fastnn(model)
         from fastfold.model.fastnn import set_chunk_size
         set_chunk_size(d.get("chunk_size"))
+        if d.get("loss"):                 # gradients of the training loss (eval mode: no dropout) with respect to every parameter
+            from fastfold.model.hub.loss import AlphaFoldLoss
+            out = model(d["batch"])
+            out["violation"] = d["violation"]          # computed by the caller: the reference would download its bond-length table
+            last = {k: v[..., -1] for k, v in d["batch"].items()}
+            loss, parts = AlphaFoldLoss(_config(d).loss)(out, last, _return_breakdown=True)
+            loss.backward()
+            torch.save({"loss": float(loss), "parts": {k: float(v) for k, v in parts.items()},
+                        "grads": {n: p.grad for n, p in model.named_parameters()}}, dst)
+            return
         with torch.no_grad():
             torch.save({"out": _tensors(model(d["batch"])), "fast_state": model.state_dict()}, dst)
         return

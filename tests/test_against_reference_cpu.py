@@ -761,3 +761,49 @@ def test_fast_evoformer_stack_forward_and_backward(is_multimer, tmp_path):
             assert grads[k].grad is None or float(grads[k].grad.abs().max()) == 0.0, k
         else:
             assert float((grads[k].grad - v).abs().max()) <= 2e-5 * max(scale * 1e-2, float(v.abs().max())) + 1e-9, k
+
+
+def test_training_loss_gradients_through_the_whole_model(tmp_path):
+    """Gradient of the full training loss with respect to every parameter, this package's fast model against the reference's
+    fast path (eval mode, two recycling iterations: only the last carries gradients).  Equal values at one point do not show
+    where gradients are stopped - the structure module's rotations, the recycled tensors; equal gradients do.  A preset
+    without templates: the reference's fast template stack writes into a view in place and cannot be differentiated."""
+    from fastfold_b200.models.hub import AlphaFoldLoss
+    from fastfold_b200.utils.inject_fastnn import inject_fastnn
+    from fastfold_b200.utils.synthetic import random_features
+    from fastfold_b200.utils.tensor_utils import tensor_tree_map
+    edits = dict(EDITS, **{"loss.violation.weight": 1.0, "loss.experimentally_resolved.weight": 0.01})
+    c, model = _model("model_3_ptm", edits, train=True)
+    batch = random_features(12, 5, 6, n_templ=0, n_recycle=1, seed=2, supervised=True)
+    state = model.state_dict()
+    model = inject_fastnn(model).eval()
+    out = model(batch)
+    last = tensor_tree_map(lambda t: t[..., -1], batch)
+    # The violation statistics are computed here and handed to both sides as constants (the reference would have to download
+    # its bond-length table to compute them), so the violation term carries no gradient in this comparison.
+    from fastfold_b200.models.hub.loss import find_structural_violations
+    with torch.no_grad():
+        violation = find_structural_violations(last, out["sm"]["positions"][-1], **c.loss.violation)
+    out["violation"] = violation
+    loss, parts = AlphaFoldLoss(c.loss)(out, last, _return_breakdown=True)
+    loss.backward()
+    ref = _oracle("fast_model", {"name": "model_3_ptm", "train": True, "edits": edits, "state": state, "batch": batch, "loss": True,
+                                 "violation": violation, "port": 29570}, tmp_path)
+    assert abs(float(loss) - ref["loss"]) < 1e-4 * abs(ref["loss"])
+    ours = dict(model.named_parameters())
+    # the unused template embedder keeps its OpenFold-layout names here and gets the fast names there: no gradients either way
+    assert all(k.startswith("template_embedder.") for k in set(ours) ^ set(ref["grads"]))
+    scale = max(float(v.abs().max()) for v in ref["grads"].values() if v is not None)
+    checked = 0
+    for k, v in ref["grads"].items():
+        if k not in ours:
+            assert v is None or float(v.abs().max()) == 0.0, k
+            continue
+        if v is None:
+            assert ours[k].grad is None or float(ours[k].grad.abs().max()) == 0.0, k
+            continue
+        assert ours[k].grad is not None, k
+        err = float((ours[k].grad - v).abs().max())
+        assert err <= 1e-3 * max(scale * 1e-3, float(v.abs().max())), (k, err, float(v.abs().max()))
+        checked += 1
+    assert checked > 300
