@@ -225,7 +225,10 @@ def between_residue_bond_loss(pred_atom_positions, pred_atom_mask, residue_index
         return loss, per_res, m * (err > (tolerance_factor_hard * gt[1]))
 
     m1 = this_ca_mask * this_c_mask * next_n_mask * has_no_gap_mask
-    ca_c_n_loss, ca_c_n_per, ca_c_n_viol = angle_term(torch.sum(c_ca_unit * c_n_unit, dim=-1), rc.between_res_cos_angles_ca_c_n, m1)
+    # AlphaFold (and the reference, fastfold/model/hub/loss.py:808-811) scale this angle's tolerance by the C-N BOND LENGTH
+    # deviation (0.014) instead of the angle's own cosine deviation (0.031); kept, since published models were trained with it
+    ca_c_n_target = (rc.between_res_cos_angles_ca_c_n[0], rc.between_res_bond_length_stddev_c_n[0])
+    ca_c_n_loss, ca_c_n_per, ca_c_n_viol = angle_term(torch.sum(c_ca_unit * c_n_unit, dim=-1), ca_c_n_target, m1)
     m2 = this_c_mask * next_n_mask * next_ca_mask * has_no_gap_mask
     c_n_ca_loss, c_n_ca_per, c_n_ca_viol = angle_term(torch.sum((-c_n_unit) * n_ca_unit, dim=-1), rc.between_res_cos_angles_c_n_ca, m2)
     per_residue_loss_sum = c_n_loss_per_residue + ca_c_n_per + c_n_ca_per

@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
+``mode``: ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
 inference runs - with its two GPU-only kernel entry points, fused LayerNorm and fused softmax, replaced by their PyTorch
 definitions so that the path runs on CPU; DAP size 1), ``data_modules`` (training-set filters, ``OpenFoldSingleDataset`` items, the batch collator), ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
@@ -50,6 +50,14 @@ def _config(d):
     return c
 
 
+def _detach(tree):
+    if torch.is_tensor(tree):
+        return tree.detach()
+    if isinstance(tree, dict):
+        return {k: _detach(v) for k, v in tree.items()}
+    return tree
+
+
 def _tensors(tree):
     if torch.is_tensor(tree):
         return tree
@@ -63,6 +71,22 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "violations":
+        from fastfold.model.hub import loss as L
+        pos = d["pos"].clone().requires_grad_(True)
+        out = {"bond": L.between_residue_bond_loss(pos, d["exists"], d["residue_index"], d["aatype"], tolerance_factor_soft=12.0, tolerance_factor_hard=12.0),
+               "clash": L.between_residue_clash_loss(pos, d["exists"], d["radius"], d["residue_index"], overlap_tolerance_soft=1.5, overlap_tolerance_hard=1.5),
+               "within": L.within_residue_violations(pos, d["exists"], d["lower"], d["upper"], tighten_bounds_for_loss=0.0),
+               "ca_ca": L.extreme_ca_ca_distance_violations(pos, d["exists"], d["residue_index"])}
+        total = out["bond"]["c_n_loss_mean"] + out["bond"]["ca_c_n_loss_mean"] + out["bond"]["c_n_ca_loss_mean"] + \
+            out["clash"]["mean_loss"] + out["within"]["per_atom_loss_sum"].sum()
+        total.backward()
+        out["grad"] = pos.grad
+        out["violation_loss"] = L.violation_loss(d["violations"], d["exists"])
+        out["metrics"] = L.compute_violation_metrics({"atom14_atom_exists": d["exists"], "residue_index": d["residue_index"], "seq_mask": d["seq_mask"]},
+                                                     d["pos"], d["violations"])
+        torch.save(_detach(out), dst)
+        return
     if mode == "data_modules":
         from fastfold.data import data_modules as dm
         config = _config(d)

@@ -807,3 +807,47 @@ def test_training_loss_gradients_through_the_whole_model(tmp_path):
         assert err <= 1e-3 * max(scale * 1e-3, float(v.abs().max())), (k, err, float(v.abs().max()))
         checked += 1
     assert checked > 300
+
+
+def test_structural_violation_terms(tmp_path):
+    """Peptide-bond geometry, between-residue clashes, within-residue bounds (with this package's bounds handed to both sides:
+    the reference downloads its own), CA-CA breaks: values and the gradient with respect to the coordinates; the weighted
+    violation loss and the reported metrics on the same violation statistics."""
+    from fastfold_b200.common import residue_constants as rc
+    from fastfold_b200.models.hub import loss as L
+    from fastfold_b200.utils.tensor_utils import tensor_tree_map
+    g = torch.Generator().manual_seed(0)
+    n = 24
+    aatype = torch.randint(0, 20, (n,), generator=g)
+    exists = torch.tensor(rc.restype_atom14_mask)[aatype].float()
+    residue_index = torch.cat([torch.arange(14), torch.arange(10) + 30])             # one chain break
+    # a crowded chain: consecutive residues 3.3 A apart with 1.2 A of noise per atom gives bond, clash and bound violations
+    pos = torch.cumsum(torch.randn(n, 1, 3, generator=g) * 1.9, 0) + torch.randn(n, 14, 3, generator=g) * 1.2
+    radius = torch.tensor([rc.van_der_waals_radius[name[0]] for name in rc.atom_types])[torch.tensor(rc.restype_atom14_to_atom37)[aatype]] * exists
+    bounds = rc.make_atom14_dists_bounds(overlap_tolerance=1.5, bond_length_tolerance_factor=12.0)
+    lower, upper = torch.tensor(bounds["lower_bound"])[aatype], torch.tensor(bounds["upper_bound"])[aatype]
+    batch = {"atom14_atom_exists": exists, "residue_index": residue_index, "aatype": aatype, "seq_mask": torch.ones(n),
+             "residx_atom14_to_atom37": torch.tensor(rc.restype_atom14_to_atom37)[aatype]}
+    violations = tensor_tree_map(lambda t: t.detach(), L.find_structural_violations(batch, pos, violation_tolerance_factor=12.0, clash_overlap_tolerance=1.5))
+    ref = _oracle("violations", {"pos": pos, "exists": exists, "residue_index": residue_index, "aatype": aatype, "radius": radius, "lower": lower,
+                                 "upper": upper, "seq_mask": torch.ones(n), "violations": violations}, tmp_path)
+    p = pos.clone().requires_grad_(True)
+    ours = {"bond": L.between_residue_bond_loss(p, exists, residue_index, aatype, tolerance_factor_soft=12.0, tolerance_factor_hard=12.0),
+            "clash": L.between_residue_clash_loss(p, exists, radius, residue_index, overlap_tolerance_soft=1.5, overlap_tolerance_hard=1.5),
+            "within": L.within_residue_violations(p, exists, lower, upper, tighten_bounds_for_loss=0.0),
+            "ca_ca": L.extreme_ca_ca_distance_violations(p, exists, residue_index)}
+    total = ours["bond"]["c_n_loss_mean"] + ours["bond"]["ca_c_n_loss_mean"] + ours["bond"]["c_n_ca_loss_mean"] + ours["clash"]["mean_loss"] + \
+        ours["within"]["per_atom_loss_sum"].sum()
+    total.backward()
+    for group in ("bond", "clash", "within"):
+        assert set(ours[group]) == set(ref[group]), group
+        for k, v in ref[group].items():
+            _close(ours[group][k].detach().float(), v.float(), 1e-5, group + "." + k)
+    _close(ours["ca_ca"].detach(), ref["ca_ca"], 1e-6, "ca_ca")
+    _close(p.grad, ref["grad"], 1e-4, "gradient")
+    assert float(ref["clash"]["mean_loss"]) > 0 and float(ref["bond"]["c_n_loss_mean"]) > 0 and float(ref["within"]["per_atom_loss_sum"].sum()) > 0
+    _close(L.violation_loss(violations, exists).detach(), ref["violation_loss"], 1e-6, "violation_loss")
+    metrics = L.compute_violation_metrics(batch, pos, violations)
+    assert set(metrics) == set(ref["metrics"])
+    for k, v in ref["metrics"].items():
+        _close(metrics[k].float(), v.float(), 1e-6, k)
