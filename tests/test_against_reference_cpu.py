@@ -20,7 +20,16 @@ pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(ROOT, "baseline",
 EDITS = {"model.evoformer_stack.no_blocks": 2, "model.extra_msa.extra_msa_stack.no_blocks": 1, "model.structure_module.no_blocks": 2}
 
 
+def _free_port():
+    import socket
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
 def _oracle(mode, payload, tmp_path):
+    if "port" in payload:
+        payload = dict(payload, port=_free_port())         # the reference's process-group bootstrap (world size 1) needs one
     src, dst = str(tmp_path / (mode + "_in.pt")), str(tmp_path / (mode + "_out.pt"))
     torch.save(payload, src)
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
