@@ -5,52 +5,48 @@ import torch
 
 
 def permute_final_dims(tensor, inds):
-    zero_index = -1 * len(inds)
-    first = list(range(len(tensor.shape[:zero_index])))
-    return tensor.permute(first + [zero_index + i for i in inds])
+    """Permutes the last ``len(inds)`` dims among themselves (``inds`` counts from the first of them); leading dims stay."""
+    lead = tensor.dim() - len(inds)
+    return tensor.permute(*range(lead), *(lead + i for i in inds))
 
 
 def flatten_final_dims(t, no_dims):
-    return t.reshape(t.shape[:-no_dims] + (-1,))
+    """Merges the last ``no_dims`` dims into one."""
+    return t.reshape(*t.shape[:t.dim() - no_dims], -1)
 
 
 def masked_mean(mask, value, dim, eps=1e-4):
-    mask = mask.expand(*value.shape)
-    return torch.sum(mask * value, dim=dim) / (eps + torch.sum(mask, dim=dim))
+    """Mean of ``value`` over ``dim`` counting only entries where ``mask`` (broadcast to ``value``) is set."""
+    weight = mask.expand_as(value)
+    return (weight * value).sum(dim=dim) / (weight.sum(dim=dim) + eps)
 
 
 def pts_to_distogram(pts, min_bin=2.3125, max_bin=21.6875, no_bins=64):
-    boundaries = torch.linspace(min_bin, max_bin, no_bins - 1, device=pts.device)
-    dists = torch.sqrt(torch.sum((pts.unsqueeze(-2) - pts.unsqueeze(-3)) ** 2, dim=-1))
-    return torch.bucketize(dists, boundaries)
+    """Bin index of every pairwise distance of ``pts [*, N, 3]`` against ``no_bins - 1`` equally spaced boundaries."""
+    edges = torch.linspace(min_bin, max_bin, no_bins - 1, device=pts.device)
+    gaps = pts[..., :, None, :] - pts[..., None, :, :]
+    return torch.bucketize(gaps.pow(2).sum(dim=-1).sqrt(), edges)
 
 
 def one_hot(x, v_bins):
     """Nearest-bin one-hot of ``x`` against bin centres ``v_bins``."""
-    diffs = x[..., None] - v_bins.reshape((1,) * x.dim() + (len(v_bins),))
-    am = torch.argmin(torch.abs(diffs), dim=-1)
-    return torch.nn.functional.one_hot(am, num_classes=len(v_bins)).float()
+    nearest = (x.unsqueeze(-1) - v_bins).abs().argmin(dim=-1)
+    return torch.nn.functional.one_hot(nearest, num_classes=v_bins.numel()).float()
 
 
 def batched_gather(data, inds, dim=0, no_batch_dims=0):
-    ranges = []
-    for i, s in enumerate(data.shape[:no_batch_dims]):
-        r = torch.arange(s, device=inds.device)
-        r = r.view(*(*((1,) * i), -1, *((1,) * (len(inds.shape) - i - 1))))
-        ranges.append(r)
-    remaining = [slice(None) for _ in range(len(data.shape) - no_batch_dims)]
-    remaining[dim - no_batch_dims if dim >= 0 else dim] = inds
-    ranges.extend(remaining)
-    return data[tuple(ranges)]
+    """``data`` indexed with ``inds`` along ``dim``, separately for every entry of the first ``no_batch_dims`` dims, which
+    ``data`` and ``inds`` share: ``out[b, ..., j, ...] = data[b, ..., inds[b, j], ...]``."""
+    batch_index = [torch.arange(n, device=inds.device).reshape((n,) + (1,) * (inds.dim() - i - 1))
+                   for i, n in enumerate(data.shape[:no_batch_dims])]
+    tail = [slice(None)] * (data.dim() - no_batch_dims)
+    tail[dim - no_batch_dims if dim >= 0 else dim] = inds
+    return data[tuple(batch_index + tail)]
 
 
 def dict_multimap(fn, dicts):
-    first = dicts[0]
-    out = {}
-    for k, v in first.items():
-        all_v = [d[k] for d in dicts]
-        out[k] = dict_multimap(fn, all_v) if isinstance(v, dict) else fn(all_v)
-    return out
+    """``fn`` applied to the list of corresponding leaves of several equally nested dicts."""
+    return {k: (dict_multimap(fn, [d[k] for d in dicts]) if isinstance(v, dict) else fn([d[k] for d in dicts])) for k, v in dicts[0].items()}
 
 
 def dict_map(fn, dic, leaf_type):
