@@ -157,8 +157,8 @@ def _raw_example(mode):
     return raw
 
 
-@pytest.mark.parametrize("mode", ["predict", "train"])
-def test_feature_pipeline(mode, tmp_path):
+@pytest.mark.parametrize("mode,crop", [("predict", None), ("train", None), ("train", 20), ("eval", None)])
+def test_feature_pipeline(mode, crop, tmp_path):
     """Every feature of the tensor pipeline - index maps, ground-truth frames and torsions, template features, MSA sampling,
     BERT-style corruption, clustering, ``msa_feat`` / ``target_feat``, cropping and padding - with equal seeds.  (With MSA
     resampling on, the reference draws a fresh random row order per recycling iteration, so that switch is off here.)"""
@@ -167,9 +167,16 @@ def test_feature_pipeline(mode, tmp_path):
     from fastfold_b200.data import data_pipeline as dp, feature_pipeline, input_pipeline
     raw = _raw_example(mode)
     edits = {"data.common.resample_msa_in_recycling": False}
+    if crop:        # shorter than the 30-residue target: the random residue window and the template subsampling are exercised
+        edits.update({"data.train.crop_size": crop, "data.train.max_msa_clusters": 16, "data.common.max_extra_msa": 8})
     ref = _oracle("features", {"name": "model_1", "train": mode == "train", "edits": edits, "raw": raw, "mode": mode, "seed": 7, "torch_seed": 5}, tmp_path)
     config = model_config("model_1", train=mode == "train")
-    config.data.common.resample_msa_in_recycling = False
+    for key, value in edits.items():
+        node = config
+        parts = key.split(".")
+        for part in parts[:-1]:
+            node = node[part]
+        node[parts[-1]] = value
     cfg, names = feature_pipeline.make_data_config(config.data, mode=mode, num_res=int(raw["seq_length"][0]))
     example = dict(raw)
     example["deletion_matrix"] = example.pop("deletion_matrix_int").astype(np.float32)
@@ -185,7 +192,9 @@ def test_feature_pipeline(mode, tmp_path):
             assert ours[k].shape == v.shape, (part, k, tuple(ours[k].shape), tuple(v.shape))
             if v.numel():
                 assert float((ours[k].float() - v.float()).abs().max()) < 2e-4, (part, k)      # torsions of random (degenerate) template atoms
-    assert len(ens) >= (45 if mode == "train" else 25)
+    assert len(ens) >= (45 if mode != "predict" else 25)
+    if crop:
+        assert ens["aatype"].shape[0] == crop and ens["msa_feat"].shape[:2] == (16, crop) and ens["extra_msa"].shape == (8, crop)
 
 
 @pytest.mark.parametrize("name", ["model_1_ptm", "model_3", "multimer"])
