@@ -80,7 +80,7 @@ class AlphaFold(nn.Module):
             m_1_prev = m.new_zeros((*batch_dims, n, self.config.input_embedder.c_m), requires_grad=False)
             z_prev = z.new_zeros(z.shape, requires_grad=False)
             x_prev = z.new_zeros((*batch_dims, n, rc.atom_type_num, 3), requires_grad=False)
-        x_prev = pseudo_beta_fn(feats["aatype"], x_prev, None).to(dtype=z.dtype)
+        x_prev = pseudo_beta_fn(feats["aatype"], x_prev, None)[0].to(dtype=z.dtype)
         if shard:
             m_1_prev_emb, z_prev_emb = self.recycling_embedder(m_1_prev, z_prev, x_prev, row0=row0)
         else:

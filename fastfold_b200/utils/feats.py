@@ -21,7 +21,8 @@ def dgram_from_positions(pos, min_bin=3.25, max_bin=50.75, no_bins=39, inf=1e8):
 
 
 def pseudo_beta_fn(aatype, all_atom_positions, all_atom_masks):
-    """CB position (CA for glycine) of every residue, and its mask when ``all_atom_masks`` is given."""
+    """``(pseudo_beta, mask)``: CB position (CA for glycine) of every residue and its mask; the mask is ``None`` when
+    ``all_atom_masks`` is (fastfold/utils/feats.py:51-71)."""
     is_gly = aatype == rc.restype_order["G"]
     ca_idx, cb_idx = rc.atom_order["CA"], rc.atom_order["CB"]
     pseudo_beta = torch.where(is_gly[..., None].expand(*((-1,) * len(is_gly.shape)), 3),
@@ -29,7 +30,7 @@ def pseudo_beta_fn(aatype, all_atom_positions, all_atom_masks):
     if all_atom_masks is not None:
         mask = torch.where(is_gly, all_atom_masks[..., ca_idx], all_atom_masks[..., cb_idx])
         return pseudo_beta, mask
-    return pseudo_beta
+    return pseudo_beta, None
 
 
 def atom14_to_atom37(atom14, batch):

@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
+``mode``: ``rigid`` (rigid-transform algebra and two feature helpers), ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
 inference runs - with its two GPU-only kernel entry points, fused LayerNorm and fused softmax, replaced by their PyTorch
 definitions so that the path runs on CPU; DAP size 1), ``data_modules`` (training-set filters, ``OpenFoldSingleDataset`` items, the batch collator), ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
@@ -71,6 +71,22 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "rigid":
+        from fastfold.utils import rigid_utils as ru
+        from fastfold.utils import feats
+        q, t, pts, upd = d["quats"], d["trans"], d["points"], d["update"]
+        r = ru.Rigid(ru.Rotation(quats=q, normalize_quats=True), t)
+        r2 = ru.Rigid.from_3_points(pts[..., 0, :], pts[..., 1, :], pts[..., 2, :], eps=1e-8)
+        out = {"t7": r.to_tensor_7(), "t4x4": r.to_tensor_4x4(), "rot_mats": r.get_rots().get_rot_mats(), "apply": r[..., None].apply(pts),
+               "invert_apply": r[..., None].invert_apply(pts), "compose": r.compose(r2).to_tensor_4x4(), "invert": r.invert().to_tensor_4x4(),
+               "update": r.compose_q_update_vec(upd).to_tensor_7(), "from_3_points": r2.to_tensor_4x4(),
+               "from_4x4": ru.Rigid.from_tensor_4x4(r2.to_tensor_4x4()).to_tensor_4x4(), "from_7": ru.Rigid.from_tensor_7(r.to_tensor_7()).to_tensor_4x4(),
+               "quat_multiply": ru.quat_multiply(q, d["quats2"]), "quat_to_rot": ru.quat_to_rot(torch.nn.functional.normalize(q, dim=-1)),
+               "rot_to_quat": ru.rot_to_quat(r.get_rots().get_rot_mats()), "scale_translation": r.scale_translation(3.0).to_tensor_7(),
+               "stop_rot_gradient": r.stop_rot_gradient().to_tensor_7(), "cat": ru.Rigid.cat([r, r2], dim=0).to_tensor_4x4(),
+               "atom14_to_atom37": feats.atom14_to_atom37(d["atom14"], d["maps"]), "pseudo_beta": feats.pseudo_beta_fn(d["aatype"], d["atom37"], None)}
+        torch.save(out, dst)
+        return
     if mode == "violations":
         from fastfold.model.hub import loss as L
         pos = d["pos"].clone().requires_grad_(True)

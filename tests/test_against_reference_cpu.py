@@ -869,3 +869,39 @@ def test_structural_violation_terms(tmp_path):
     assert set(metrics) == set(ref["metrics"])
     for k, v in ref["metrics"].items():
         _close(metrics[k].float(), v.float(), 1e-6, k)
+
+
+def test_rigid_transform_algebra(tmp_path):
+    """``Rigid`` / ``Rotation``: quaternion and matrix forms, application and inverse application, composition, inversion,
+    the structure module's quaternion update, frames from three points, tensor round trips, quaternion helpers."""
+    from fastfold_b200.common import residue_constants as rc
+    from fastfold_b200.utils import feats
+    from fastfold_b200.utils import rigid_utils as ru
+    g = torch.Generator().manual_seed(0)
+    n = 9
+    q, q2, t = torch.randn(n, 4, generator=g), torch.randn(n, 4, generator=g), torch.randn(n, 3, generator=g) * 5
+    pts, upd = torch.randn(n, 3, 3, generator=g) * 4, torch.randn(n, 6, generator=g) * 0.3
+    aatype = torch.randint(0, 20, (n,), generator=g)
+    maps = {"residx_atom37_to_atom14": torch.tensor(rc.restype_atom37_to_atom14)[aatype], "atom37_atom_exists": torch.tensor(rc.restype_atom37_mask)[aatype].float()}
+    atom14, atom37 = torch.randn(n, 14, 3, generator=g), torch.randn(n, 37, 3, generator=g)
+    ref = _oracle("rigid", {"quats": q, "quats2": q2, "trans": t, "points": pts, "update": upd, "aatype": aatype, "maps": maps, "atom14": atom14,
+                            "atom37": atom37}, tmp_path)
+    r = ru.Rigid(ru.Rotation(quats=q, normalize_quats=True), t)
+    r2 = ru.Rigid.from_3_points(pts[..., 0, :], pts[..., 1, :], pts[..., 2, :], eps=1e-8)
+    ours = {"t7": r.to_tensor_7(), "t4x4": r.to_tensor_4x4(), "rot_mats": r.get_rots().get_rot_mats(), "apply": r[..., None].apply(pts),
+            "invert_apply": r[..., None].invert_apply(pts), "compose": r.compose(r2).to_tensor_4x4(), "invert": r.invert().to_tensor_4x4(),
+            "update": r.compose_q_update_vec(upd).to_tensor_7(), "from_3_points": r2.to_tensor_4x4(),
+            "from_4x4": ru.Rigid.from_tensor_4x4(r2.to_tensor_4x4()).to_tensor_4x4(), "from_7": ru.Rigid.from_tensor_7(r.to_tensor_7()).to_tensor_4x4(),
+            "quat_multiply": ru.quat_multiply(q, q2), "quat_to_rot": ru.quat_to_rot(torch.nn.functional.normalize(q, dim=-1)),
+            "rot_to_quat": ru.rot_to_quat(r.get_rots().get_rot_mats()), "scale_translation": r.scale_translation(3.0).to_tensor_7(),
+            "stop_rot_gradient": r.stop_rot_gradient().to_tensor_7(), "cat": ru.Rigid.cat([r, r2], dim=0).to_tensor_4x4(),
+            "atom14_to_atom37": feats.atom14_to_atom37(atom14, maps), "pseudo_beta": feats.pseudo_beta_fn(aatype, atom37, None)}
+    assert ours["pseudo_beta"][1] is None and ref["pseudo_beta"][1] is None
+    ours["pseudo_beta"], ref["pseudo_beta"] = ours["pseudo_beta"][0], ref["pseudo_beta"][0]
+    assert set(ours) == set(ref)
+    for k, v in ref.items():
+        a = ours[k]
+        if k == "rot_to_quat":                     # a quaternion and its negative are the same rotation
+            sign = torch.sign((a * v).sum(-1, keepdim=True))
+            a = a * sign
+        _close(a, v, 1e-5, k)
