@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``rigid`` (rigid-transform algebra and two feature helpers), ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
+``mode``: ``geometry`` (the struct-of-arrays vectors, rotations and rigids of the multimer model), ``rigid`` (rigid-transform algebra and two feature helpers), ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
 inference runs - with its two GPU-only kernel entry points, fused LayerNorm and fused softmax, replaced by their PyTorch
 definitions so that the path runs on CPU; DAP size 1), ``data_modules`` (training-set filters, ``OpenFoldSingleDataset`` items, the batch collator), ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
@@ -71,6 +71,30 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "geometry":
+        from fastfold.utils import geometry as g
+        from fastfold.utils.geometry import vector as gv
+        from fastfold.utils.geometry.quat_rigid import QuatRigid
+        a, b, c, e = (g.Vec3Array.from_array(x) for x in (d["a"], d["b"], d["c"], d["e"]))
+        rot = g.Rot3Array.from_two_vectors(a, b)
+        rotq = g.Rot3Array.from_quaternion(*torch.unbind(d["q"], dim=-1))
+        rig, rig2 = g.Rigid3Array(rot, c), g.Rigid3Array(rotq, e)
+        lin = QuatRigid(d["act"].shape[-1], full_quat=False)
+        lin.load_state_dict(d["quat_state"])
+        with torch.no_grad():
+            from_act = lin(d["act"])
+        out = {"add": (a + b).to_tensor(), "sub": (a - b).to_tensor(), "scale": (a * 2.5).to_tensor(), "div": (a / 2.0).to_tensor(), "neg": (-a).to_tensor(),
+               "dot": a.dot(b), "cross": a.cross(b).to_tensor(), "norm": a.norm(), "norm2": a.norm2(), "normalized": a.normalized().to_tensor(),
+               "dihedral": gv.dihedral_angle(a, b, c, e),       # its two distance helpers fail on a float epsilon and are left out
+               "rot": rot.to_tensor(), "rotq": rotq.to_tensor(), "rot_apply": rot.apply_to_point(c).to_tensor(),
+               "rot_inv_apply": rot.apply_inverse_to_point(c).to_tensor(), "rot_inverse": rot.inverse().to_tensor(), "rot_matmul": (rot @ rotq).to_tensor(),
+               "rigid_4x4": rig.to_tensor_4x4(), "rigid_compose": (rig @ rig2).to_tensor_4x4(), "rigid_inverse": rig.inverse().to_tensor_4x4(),
+               "rigid_apply": rig.apply_to_point(e).to_tensor(), "rigid_inv_apply": rig.apply_inverse_to_point(e).to_tensor(),
+               "rigid_from_4x4": g.Rigid3Array.from_tensor_4x4(rig.to_tensor_4x4()).to_tensor_4x4(),
+               "rigid_scale": rig.scale_translation(0.1).to_tensor_4x4(), "identity": g.Rigid3Array.identity((3,), "cpu").to_tensor_4x4(),
+               "quat_rigid": from_act.to_tensor_4x4()}
+        torch.save(out, dst)
+        return
     if mode == "rigid":
         from fastfold.utils import rigid_utils as ru
         from fastfold.utils import feats

@@ -905,3 +905,37 @@ def test_rigid_transform_algebra(tmp_path):
             sign = torch.sign((a * v).sum(-1, keepdim=True))
             a = a * sign
         _close(a, v, 1e-5, k)
+
+
+def test_struct_of_arrays_geometry(tmp_path):
+    """``Vec3Array`` / ``Rot3Array`` / ``Rigid3Array`` / ``QuatRigid`` (the multimer model's geometry): arithmetic, products,
+    norms, distances, dihedrals, rotations from two vectors and from quaternions, composition, inversion, application."""
+    from fastfold_b200.utils import geometry as g
+    gen = torch.Generator().manual_seed(0)
+    n = 11
+    a, b, c, e = (torch.randn(n, 3, generator=gen) * 3 for _ in range(4))
+    q, act = torch.randn(n, 4, generator=gen), torch.randn(n, 16, generator=gen)
+    lin = g.QuatRigid(16, full_quat=False)
+    with torch.no_grad():
+        lin.linear.weight.copy_(torch.randn(6, 16, generator=gen) * 0.3)
+        lin.linear.bias.copy_(torch.randn(6, generator=gen) * 0.3)
+    ref = _oracle("geometry", {"a": a, "b": b, "c": c, "e": e, "q": q, "act": act, "quat_state": lin.state_dict()}, tmp_path)
+    va, vb, vc, ve = (g.Vec3Array.from_array(x) for x in (a, b, c, e))
+    rot = g.Rot3Array.from_two_vectors(va, vb)
+    rotq = g.Rot3Array.from_quaternion(*torch.unbind(q, dim=-1))
+    rig, rig2 = g.Rigid3Array(rot, vc), g.Rigid3Array(rotq, ve)
+    with torch.no_grad():
+        from_act = lin(act)
+    ours = {"add": (va + vb).to_tensor(), "sub": (va - vb).to_tensor(), "scale": (va * 2.5).to_tensor(), "div": (va / 2.0).to_tensor(), "neg": (-va).to_tensor(),
+            "dot": va.dot(vb), "cross": va.cross(vb).to_tensor(), "norm": va.norm(), "norm2": va.norm2(), "normalized": va.normalized().to_tensor(),
+            "dihedral": g.dihedral_angle(va, vb, vc, ve),
+            "rot": rot.to_tensor(), "rotq": rotq.to_tensor(), "rot_apply": rot.apply_to_point(vc).to_tensor(),
+            "rot_inv_apply": rot.apply_inverse_to_point(vc).to_tensor(), "rot_inverse": rot.inverse().to_tensor(), "rot_matmul": (rot @ rotq).to_tensor(),
+            "rigid_4x4": rig.to_tensor_4x4(), "rigid_compose": (rig @ rig2).to_tensor_4x4(), "rigid_inverse": rig.inverse().to_tensor_4x4(),
+            "rigid_apply": rig.apply_to_point(ve).to_tensor(), "rigid_inv_apply": rig.apply_inverse_to_point(ve).to_tensor(),
+            "rigid_from_4x4": g.Rigid3Array.from_tensor_4x4(rig.to_tensor_4x4()).to_tensor_4x4(),
+            "rigid_scale": rig.scale_translation(0.1).to_tensor_4x4(), "identity": g.Rigid3Array.identity((3,), "cpu").to_tensor_4x4(),
+            "quat_rigid": from_act.to_tensor_4x4()}
+    assert set(ours) == set(ref)
+    for k, v in ref.items():
+        _close(ours[k], v, 1e-5, k)
