@@ -24,3 +24,30 @@ def test_train_py_on_pdb_files(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     log = (tmp_path / "log.log").read_text()
     assert log.count(" loss ") >= 2 and "nan" not in log.lower(), log[-1500:]
+
+
+def _free_port():
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(tmp_path, tag, dap):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
+           str(_free_port()), os.path.join(ROOT, "train.py"), "--dap_size", str(dap), "--blocks", "1", "--n_res", "16", "--n_seq", "4", "--n_extra", "4",
+           "--max_steps", "2", "--train_epoch_len", "4", "--max_epochs", "1", "--val_epoch_len", "0", "--log_interval", "1",
+           "--log_path", str(tmp_path / tag), "--seed", "3"]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=900, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    return (tmp_path / (tag + ".log")).read_text()
+
+
+def test_train_py_on_two_ranks_dap_and_dp(tmp_path):
+    """Two Gloo ranks on synthetic data: as one DAP group (one replica, sharded activations) and as two data-parallel
+    replicas (the epoch summary counts the replicas)."""
+    dap = _launch(tmp_path, "dap", 2)
+    assert dap.count(" loss ") >= 2 and "nan" not in dap.lower() and "over 1 replica(s)" in dap, dap[-1500:]
+    dp = _launch(tmp_path, "dp", 1)
+    assert dp.count(" loss ") >= 2 and "nan" not in dp.lower() and "over 2 replica(s)" in dp, dp[-1500:]
