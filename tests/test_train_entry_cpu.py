@@ -37,7 +37,7 @@ def _launch(tmp_path, tag, dap):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
            str(_free_port()), os.path.join(ROOT, "train.py"), "--dap_size", str(dap), "--blocks", "1", "--n_res", "16", "--n_seq", "4", "--n_extra", "4",
-           "--max_steps", "2", "--train_epoch_len", "4", "--max_epochs", "1", "--val_epoch_len", "0", "--log_interval", "1",
+           "--max_steps", "2", "--train_epoch_len", "4", "--max_epochs", "1", "--val_epoch_len", "2", "--log_interval", "1",
            "--log_path", str(tmp_path / tag), "--seed", "3"]
     r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=900, cwd=str(tmp_path))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
@@ -49,5 +49,7 @@ def test_train_py_on_two_ranks_dap_and_dp(tmp_path):
     replicas (the epoch summary counts the replicas)."""
     dap = _launch(tmp_path, "dap", 2)
     assert dap.count(" loss ") >= 2 and "nan" not in dap.lower() and "over 1 replica(s)" in dap, dap[-1500:]
+    assert "validation epoch 0 (2 samples)" in dap and "gdt_ts" in dap, dap[-1500:]
     dp = _launch(tmp_path, "dp", 1)
     assert dp.count(" loss ") >= 2 and "nan" not in dp.lower() and "over 2 replica(s)" in dp, dp[-1500:]
+    assert "validation epoch 0 (4 samples)" in dp, dp[-1500:]           # two synthetic samples per replica, summed over the replicas

@@ -187,7 +187,7 @@ def main():
         from fastfold_b200.data.data_modules import StructureDataset
         val_dataset = StructureDataset(args.val_data_dir, args.val_alignment_dir, config.data, mode="eval", seed=args.seed,
                                        dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size())
-    elif args.synthetic and args.val_epoch_len > 0:
+    elif (args.synthetic or not args.train_data_dir) and args.val_epoch_len > 0:      # same condition as the synthetic training set
         from fastfold_b200.data.data_modules import SyntheticDataset
         val_dataset = SyntheticDataset(n_res, n_seq, n_extra, n_recycle=config.data.common.max_recycling_iters, length=args.val_epoch_len,
                                        seed=args.seed + 7919, dp_rank=core.get_dp_rank(), dp_size=core.get_dp_size(), uniform_recycling=False,
@@ -222,7 +222,8 @@ def main():
             torch.distributed.all_reduce(t)
         means = {k: float(t[j] / t[-1].clamp(min=1)) for j, k in enumerate(keys)}
         if rank == 0:
-            log.info("validation epoch %d (%d samples) | %s", epoch, int(t[-1]), " ".join("%s %.4f" % (k, v) for k, v in means.items()))
+            # the sum runs over the whole world; the ranks of one DAP group hold the same samples
+            log.info("validation epoch %d (%d samples) | %s", epoch, int(t[-1]) // core.get_dap_size(), " ".join("%s %.4f" % (k, v) for k, v in means.items()))
         return means
 
     steps_done = 0
