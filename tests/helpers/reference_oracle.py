@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``geometry`` (the struct-of-arrays vectors, rotations and rigids of the multimer model), ``rigid`` (rigid-transform algebra and two feature helpers), ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
+``mode``: ``tools`` (runs every alignment-tool wrapper against recording stand-in executables), ``geometry`` (the struct-of-arrays vectors, rotations and rigids of the multimer model), ``rigid`` (rigid-transform algebra and two feature helpers), ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
 inference runs - with its two GPU-only kernel entry points, fused LayerNorm and fused softmax, replaced by their PyTorch
 definitions so that the path runs on CPU; DAP size 1), ``data_modules`` (training-set filters, ``OpenFoldSingleDataset`` items, the batch collator), ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
@@ -71,6 +71,21 @@ def _tensors(tree):
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
+    if mode == "tools":
+        from fastfold.data.tools import hhblits, hhsearch, hmmbuild, hmmsearch, jackhmmer, kalign
+        b = d["bin"]
+        jackhmmer.Jackhmmer(binary_path=b["jackhmmer"], database_path=d["db"]).query(d["fasta"])
+        jackhmmer.Jackhmmer(binary_path=b["jackhmmer"], database_path=d["db"], n_cpu=3, n_iter=2, e_value=0.01, z_value=1000, get_tblout=True,
+                            dom_e=0.1, incdom_e=0.2).query(d["fasta"])
+        hhblits.HHBlits(binary_path=b["hhblits"], databases=[d["hhdb"]]).query(d["fasta"])
+        hhblits.HHBlits(binary_path=b["hhblits"], databases=[d["hhdb"], d["hhdb"]], n_cpu=2, n_iter=1, all_seqs=True, alt=3, p=30, z=100).query(d["fasta"])
+        hhsearch.HHSearch(binary_path=b["hhsearch"], databases=[d["hhdb"]]).query(d["a3m"])
+        hmmbuild.Hmmbuild(binary_path=b["hmmbuild"]).build_profile_from_sto(d["sto"], model_construction="hand")
+        hmmbuild.Hmmbuild(binary_path=b["hmmbuild"], singlemx=True).build_profile_from_a3m(d["a3m"])
+        hmmsearch.Hmmsearch(binary_path=b["hmmsearch"], hmmbuild_binary_path=b["hmmbuild"], database_path=d["db"]).query(d["sto"])
+        kalign.Kalign(binary_path=b["kalign"]).align(d["seqs"])
+        torch.save({}, dst)
+        return
     if mode == "geometry":
         from fastfold.utils import geometry as g
         from fastfold.utils.geometry import vector as gv

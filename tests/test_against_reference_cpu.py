@@ -939,3 +939,81 @@ def test_struct_of_arrays_geometry(tmp_path):
     assert set(ours) == set(ref)
     for k, v in ref.items():
         _close(ours[k], v, 1e-5, k)
+
+
+_RECORDER = r"""#!/bin/bash
+# stand-in for an alignment tool: records its command line, then writes the output files the wrapper will read
+echo "$(basename "$0") $*" >> "$RECORD"
+args=("$@")
+last=${args[$((${#args[@]}-1))]}
+prev=${args[$((${#args[@]}-2))]}
+case "$(basename "$0")" in
+  hmmbuild) printf 'HMMER3/f [stand-in]\n//\n' > "$prev" ;;
+esac
+while [ $# -gt 0 ]; do
+  case "$1" in
+    -A) printf '# STOCKHOLM 1.0\n\nquery ACDEFGHIKL\nhit1  ACDEFGHIKV\n//\n' > "$2" ;;
+    --tblout) printf '# target\nhit1 - query - 1e-5 10 0\n' > "$2" ;;
+    -oa3m) printf '>query\nACDEFGHIKL\n>hit1\nACDEFGHIKV\n' > "$2" ;;
+    -o) if [ "$2" != "/dev/null" ]; then
+          case "$(basename "$0")" in
+            kalign) printf '>a\nACDEFGHIKL\n>b\nACDE-GHIKL\n' > "$2" ;;
+            *) printf 'Query         query\nMatch_columns 10\n\n' > "$2" ;;
+          esac
+        fi ;;
+  esac
+  shift
+done
+"""
+
+
+def test_alignment_tool_command_lines(tmp_path):
+    """Every wrapper (jackhmmer, hhblits, hhsearch, hmmbuild, hmmsearch, kalign) is run against a stand-in executable that
+    records its arguments; default and non-default settings; the command lines must equal the reference's, flag by flag."""
+    import re
+    import stat
+    from fastfold_b200.data import tools
+    bins = {}
+    for name in ("jackhmmer", "hhblits", "hhsearch", "hmmbuild", "hmmsearch", "kalign"):
+        path = tmp_path / "bin" / name
+        path.parent.mkdir(exist_ok=True)
+        path.write_text(_RECORDER)
+        path.chmod(path.stat().st_mode | stat.S_IEXEC)
+        bins[name] = str(path)
+    (tmp_path / "db.fasta").write_text(">x\nACDEFGHIKL\n")
+    for suffix in ("_hhm.ffdata", "_a3m.ffdata", "_cs219.ffdata"):
+        (tmp_path / ("hhdb" + suffix)).write_text("")
+    fasta = tmp_path / "q.fasta"
+    fasta.write_text(">query\nACDEFGHIKL\n")
+    a3m = ">query\nACDEFGHIKL\n>hit\nACDEfgFGHIKV\n"
+    sto = "# STOCKHOLM 1.0\n\nquery ACDEFGHIKL\nhit1  ACDEFGHIKV\n//\n"
+    payload = {"bin": bins, "db": str(tmp_path / "db.fasta"), "hhdb": str(tmp_path / "hhdb"), "fasta": str(fasta), "a3m": a3m, "sto": sto,
+               "seqs": ["ACDEFGHIKL", "ACDEGHIKL"]}
+
+    def lines(path):
+        out = []
+        for ln in open(path).read().splitlines():
+            ln = re.sub(r"/tmp/[A-Za-z0-9_]+/", "<TMP>/", ln)              # the wrappers' scratch directories
+            out.append(ln)
+        return out
+    os.environ["RECORD"] = str(tmp_path / "ref.txt")
+    try:
+        _oracle("tools", payload, tmp_path)
+        os.environ["RECORD"] = str(tmp_path / "ours.txt")
+        b = bins
+        tools.Jackhmmer(binary_path=b["jackhmmer"], database_path=payload["db"]).query(str(fasta))
+        tools.Jackhmmer(binary_path=b["jackhmmer"], database_path=payload["db"], n_cpu=3, n_iter=2, e_value=0.01, z_value=1000, get_tblout=True,
+                        dom_e=0.1, incdom_e=0.2).query(str(fasta))
+        tools.HHBlits(binary_path=b["hhblits"], databases=[payload["hhdb"]]).query(str(fasta))
+        tools.HHBlits(binary_path=b["hhblits"], databases=[payload["hhdb"], payload["hhdb"]], n_cpu=2, n_iter=1, all_seqs=True, alt=3, p=30, z=100).query(str(fasta))
+        tools.HHSearch(binary_path=b["hhsearch"], databases=[payload["hhdb"]]).query(a3m)
+        tools.Hmmbuild(binary_path=b["hmmbuild"]).build_profile_from_sto(sto, model_construction="hand")
+        tools.Hmmbuild(binary_path=b["hmmbuild"], singlemx=True).build_profile_from_a3m(a3m)
+        tools.Hmmsearch(binary_path=b["hmmsearch"], hmmbuild_binary_path=b["hmmbuild"], database_path=payload["db"]).query(sto)
+        tools.Kalign(binary_path=b["kalign"]).align(payload["seqs"])
+    finally:
+        os.environ.pop("RECORD", None)
+    theirs, ours = lines(tmp_path / "ref.txt"), lines(tmp_path / "ours.txt")
+    assert len(theirs) == len(ours) == 10, (len(theirs), len(ours))
+    for a, b_ in zip(ours, theirs):
+        assert a == b_, "\nours: %s\nref:  %s" % (a, b_)
