@@ -459,8 +459,8 @@ class AlignmentRunnerMultimer(AlignmentRunner):
             f.write(sto)
         if self.hmmsearch_pdb_runner is not None:
             clean = parsers.remove_empty_columns_from_stockholm_msa(parsers.deduplicate_stockholm_msa(sto))
-            with open(os.path.join(output_dir, "pdb_hits.sto"), "w") as f:
-                f.write(self.hmmsearch_pdb_runner.query(clean))
+            # the search writes <output_dir>/hmm_output.sto, the name under which the data pipeline looks for template hits
+            self.hmmsearch_pdb_runner.query(clean, output_dir=output_dir)
 
     def _mgnify(self, fasta_path, output_dir):
         if self.jackhmmer_mgnify_runner is None:

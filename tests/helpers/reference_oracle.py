@@ -84,6 +84,21 @@ def main(mode, src, dst):
         hmmbuild.Hmmbuild(binary_path=b["hmmbuild"], singlemx=True).build_profile_from_a3m(d["a3m"])
         hmmsearch.Hmmsearch(binary_path=b["hmmsearch"], hmmbuild_binary_path=b["hmmbuild"], database_path=d["db"]).query(d["sto"])
         kalign.Kalign(binary_path=b["kalign"]).align(d["seqs"])
+        from fastfold.data import data_pipeline
+        os.environ["RECORD"] = d["record_runner"]
+        for tag, small in (("full", False), ("small", True)):
+            out_dir = os.path.join(d["out"], "mono_" + tag)
+            os.makedirs(out_dir)
+            data_pipeline.AlignmentRunner(jackhmmer_binary_path=b["jackhmmer"], hhblits_binary_path=b["hhblits"], hhsearch_binary_path=b["hhsearch"],
+                                          uniref90_database_path=d["db"], mgnify_database_path=d["db"], bfd_database_path=d["db"] if small else d["hhdb"],
+                                          uniref30_database_path=None if small else d["hhdb"], pdb70_database_path=d["hhdb"], use_small_bfd=small,
+                                          no_cpus=4).run(d["fasta"], out_dir)
+        out_dir = os.path.join(d["out"], "multi")
+        os.makedirs(out_dir)
+        data_pipeline.AlignmentRunnerMultimer(jackhmmer_binary_path=b["jackhmmer"], hhblits_binary_path=b["hhblits"], hmmsearch_binary_path=b["hmmsearch"],
+                                              hmmbuild_binary_path=b["hmmbuild"], uniref90_database_path=d["db"], mgnify_database_path=d["db"],
+                                              bfd_database_path=d["hhdb"], uniref30_database_path=d["hhdb"], uniprot_database_path=d["db"],
+                                              pdb_seqres_database_path=d["db"], use_small_bfd=False, no_cpus=8).run(d["fasta"], out_dir)
         torch.save({}, dst)
         return
     if mode == "geometry":

@@ -952,7 +952,7 @@ case "$(basename "$0")" in
 esac
 while [ $# -gt 0 ]; do
   case "$1" in
-    -A) printf '# STOCKHOLM 1.0\n\nquery ACDEFGHIKL\nhit1  ACDEFGHIKV\n//\n' > "$2" ;;
+    -A) printf '# STOCKHOLM 1.0\n\nquery ACDEFGHIKL\nhit1  ACDEFGHIKV\n#=GC RF xxxxxxxxxx\n//\n' > "$2" ;;
     --tblout) printf '# target\nhit1 - query - 1e-5 10 0\n' > "$2" ;;
     -oa3m) printf '>query\nACDEFGHIKL\n>hit1\nACDEFGHIKV\n' > "$2" ;;
     -o) if [ "$2" != "/dev/null" ]; then
@@ -988,11 +988,12 @@ def test_alignment_tool_command_lines(tmp_path):
     a3m = ">query\nACDEFGHIKL\n>hit\nACDEfgFGHIKV\n"
     sto = "# STOCKHOLM 1.0\n\nquery ACDEFGHIKL\nhit1  ACDEFGHIKV\n//\n"
     payload = {"bin": bins, "db": str(tmp_path / "db.fasta"), "hhdb": str(tmp_path / "hhdb"), "fasta": str(fasta), "a3m": a3m, "sto": sto,
-               "seqs": ["ACDEFGHIKL", "ACDEGHIKL"]}
+               "seqs": ["ACDEFGHIKL", "ACDEGHIKL"], "record_runner": str(tmp_path / "ref_runner.txt"), "out": str(tmp_path / "ref_out")}
 
     def lines(path):
         out = []
         for ln in open(path).read().splitlines():
+            ln = re.sub(r"\S*/(ref_out|ours_out)/", "<OUT>/", ln)          # this test's two output trees
             ln = re.sub(r"/tmp/[A-Za-z0-9_]+/", "<TMP>/", ln)              # the wrappers' scratch directories
             out.append(ln)
         return out
@@ -1017,3 +1018,27 @@ def test_alignment_tool_command_lines(tmp_path):
     assert len(theirs) == len(ours) == 10, (len(theirs), len(ours))
     for a, b_ in zip(ours, theirs):
         assert a == b_, "\nours: %s\nref:  %s" % (a, b_)
+    # the alignment runners: which searches run against which databases, and the files they leave behind (searches run
+    # concurrently here, so the recorded commands are compared as sorted lists)
+    from fastfold_b200.data.data_pipeline import AlignmentRunner, AlignmentRunnerMultimer
+    os.environ["RECORD"] = str(tmp_path / "ours_runner.txt")
+    try:
+        for tag, small in (("full", False), ("small", True)):
+            out_dir = tmp_path / "ours_out" / ("mono_" + tag)
+            out_dir.mkdir(parents=True)
+            AlignmentRunner(jackhmmer_binary_path=b["jackhmmer"], hhblits_binary_path=b["hhblits"], hhsearch_binary_path=b["hhsearch"],
+                            uniref90_database_path=payload["db"], mgnify_database_path=payload["db"], bfd_database_path=payload["db"] if small else payload["hhdb"],
+                            uniref30_database_path=None if small else payload["hhdb"], pdb70_database_path=payload["hhdb"], use_small_bfd=small,
+                            no_cpus=4).run(str(fasta), str(out_dir))
+        out_dir = tmp_path / "ours_out" / "multi"
+        out_dir.mkdir(parents=True)
+        AlignmentRunnerMultimer(jackhmmer_binary_path=b["jackhmmer"], hhblits_binary_path=b["hhblits"], hmmsearch_binary_path=b["hmmsearch"],
+                                hmmbuild_binary_path=b["hmmbuild"], uniref90_database_path=payload["db"], mgnify_database_path=payload["db"],
+                                bfd_database_path=payload["hhdb"], uniref30_database_path=payload["hhdb"], uniprot_database_path=payload["db"],
+                                pdb_seqres_database_path=payload["db"], use_small_bfd=False, no_cpus=8).run(str(fasta), str(out_dir))     # 8: the
+        # reference's UniProt search ignores no_cpus and runs with its default of 8 threads; here it honours the setting
+    finally:
+        os.environ.pop("RECORD", None)
+    assert sorted(lines(tmp_path / "ours_runner.txt")) == sorted(lines(tmp_path / "ref_runner.txt"))
+    for sub in ("mono_full", "mono_small", "multi"):
+        assert sorted(os.listdir(tmp_path / "ours_out" / sub)) == sorted(os.listdir(tmp_path / "ref_out" / sub)), sub
