@@ -57,6 +57,49 @@ def parse_overrides(items):
     return out
 
 
+def run_alignments(args, seqs, tags, multimer):
+    """Runs the sequence searches and returns the alignment directory the data pipeline reads.  Monomer: one directory
+    ``<output_dir>/alignments/<tag>``; multimer: one sub-directory per chain under ``<output_dir>/alignments``, each filled
+    from a one-sequence FASTA file of that chain (fastfold inference.py:184-277).  ``--enable_workflow`` runs the searches of
+    a chain concurrently through the workflow scheduler instead of the plain runner."""
+    import shutil
+    from fastfold_b200.data.data_pipeline import AlignmentRunner, AlignmentRunnerMultimer, temp_fasta_file
+    from fastfold_b200.workflow.template import FastFoldDataWorkFlow, FastFoldMultimerDataWorkFlow
+    common = dict(jackhmmer_binary_path=args.jackhmmer_binary_path, hhblits_binary_path=args.hhblits_binary_path,
+                  uniref90_database_path=args.uniref90_database_path, mgnify_database_path=args.mgnify_database_path,
+                  bfd_database_path=args.bfd_database_path, uniref30_database_path=args.uniclust30_database_path, no_cpus=args.cpus)
+    base = os.path.join(args.output_dir, "alignments")
+    t0 = time.perf_counter()
+    if not multimer:
+        cls = FastFoldDataWorkFlow if args.enable_workflow else AlignmentRunner
+        runner = cls(hhsearch_binary_path=args.hhsearch_binary_path, pdb70_database_path=args.pdb70_database_path,
+                     use_small_bfd=(args.preset == "reduced_dbs"), **common)
+        out = os.path.join(base, tags[0].split()[0] if tags else "query")
+        os.makedirs(out, exist_ok=True)
+        runner.run(args.fasta_path, out)
+    else:
+        cls = FastFoldMultimerDataWorkFlow if args.enable_workflow else AlignmentRunnerMultimer
+        runner = cls(hmmsearch_binary_path=args.hmmsearch_binary_path, hmmbuild_binary_path=args.hmmbuild_binary_path,
+                     uniprot_database_path=args.uniprot_database_path, pdb_seqres_database_path=args.pdb_seqres_database_path,
+                     use_small_bfd=(args.preset == "reduced_dbs" or args.bfd_database_path is None), **common)
+        done = {}
+        for tag, seq in zip(tags, seqs):
+            chain_dir = os.path.join(base, tag.split()[0])
+            if os.path.exists(chain_dir):
+                shutil.rmtree(chain_dir)
+            if seq in done:                              # copies of one chain share their searches
+                shutil.copytree(done[seq], chain_dir)
+                continue
+            os.makedirs(chain_dir)
+            with temp_fasta_file(">chain_%s\n%s\n" % (tag.split()[0], seq)) as chain_fasta:
+                runner.run(chain_fasta, chain_dir)
+            done[seq] = chain_dir
+            print("Finished running alignment for %s" % tag.split()[0])
+        out = base
+    print("Alignment data workflow time: %.1f s" % (time.perf_counter() - t0))
+    return out
+
+
 def main(args):
     import numpy as np
     from fastfold_b200.common import protein
@@ -72,28 +115,21 @@ def main(args):
         raise ValueError("monomer preset expects one sequence in the FASTA file; use --model_preset multimer")
     config = model_config(args.model_name)
     tag = tags[0].split()[0] if tags else "query"
+    multimer = args.model_preset == "multimer"
     alignment_dir = None
     if args.use_precomputed_alignments:
         cand = os.path.join(args.use_precomputed_alignments, tag)
-        alignment_dir = cand if os.path.isdir(cand) else args.use_precomputed_alignments
+        alignment_dir = args.use_precomputed_alignments if multimer or not os.path.isdir(cand) else cand
     elif args.uniref90_database_path:
-        from fastfold_b200.data.tools import AlignmentRunner
-        from fastfold_b200.workflow import FastFoldDataWorkFlow
-        alignment_dir = os.path.join(args.output_dir, "alignments", tag)
-        os.makedirs(alignment_dir, exist_ok=True)
-        t0 = time.perf_counter()
-        cls = FastFoldDataWorkFlow if args.enable_workflow else AlignmentRunner
-        cls(jackhmmer_binary_path=args.jackhmmer_binary_path, hhblits_binary_path=args.hhblits_binary_path,
-            hhsearch_binary_path=args.hhsearch_binary_path, uniref90_database_path=args.uniref90_database_path,
-            mgnify_database_path=args.mgnify_database_path, bfd_database_path=args.bfd_database_path,
-            uniclust30_database_path=args.uniclust30_database_path, pdb70_database_path=args.pdb70_database_path,
-            use_small_bfd=(args.preset == "reduced_dbs"), no_cpus=args.cpus).run(args.fasta_path, alignment_dir)
-        print("Alignment data workflow time: %.1f s" % (time.perf_counter() - t0))
+        alignment_dir = run_alignments(args, seqs, tags, multimer)
     featurizer = None
     if args.template_mmcif_dir and os.path.isdir(args.template_mmcif_dir) and config.model.template.enabled:
-        from fastfold_b200.data.templates import TemplateHitFeaturizer
-        featurizer = TemplateHitFeaturizer(mmcif_dir=args.template_mmcif_dir, max_template_date=args.max_template_date, max_hits=4,
-                                           kalign_binary_path=args.kalign_binary_path)
+        # monomer: hhsearch hits against PDB70 (pdb70_hits.hhr); multimer: hmmsearch hits against the PDB sequences
+        # (hmm_output.sto), which carry no alignment score and are used in search order (fastfold inference.py:175-182, 344-351)
+        from fastfold_b200.data.templates import HmmsearchHitFeaturizer, TemplateHitFeaturizer
+        featurizer = (HmmsearchHitFeaturizer if multimer else TemplateHitFeaturizer)(
+            mmcif_dir=args.template_mmcif_dir, max_template_date=args.max_template_date, max_hits=4, kalign_binary_path=args.kalign_binary_path,
+            release_dates_path=args.release_dates_path, obsolete_pdbs_path=args.obsolete_pdbs_path)
     if args.model_preset == "multimer":
         # every chain of the FASTA goes through the monomer pipeline (alignments under <alignment_dir>/<chain id>/), the
         # chains are paired by species and merged (fastfold inference.py:169-338)

@@ -941,45 +941,14 @@ def test_struct_of_arrays_geometry(tmp_path):
         _close(ours[k], v, 1e-5, k)
 
 
-_RECORDER = r"""#!/bin/bash
-# stand-in for an alignment tool: records its command line, then writes the output files the wrapper will read
-echo "$(basename "$0") $*" >> "$RECORD"
-args=("$@")
-last=${args[$((${#args[@]}-1))]}
-prev=${args[$((${#args[@]}-2))]}
-case "$(basename "$0")" in
-  hmmbuild) printf 'HMMER3/f [stand-in]\n//\n' > "$prev" ;;
-esac
-while [ $# -gt 0 ]; do
-  case "$1" in
-    -A) printf '# STOCKHOLM 1.0\n\nquery ACDEFGHIKL\nhit1  ACDEFGHIKV\n#=GC RF xxxxxxxxxx\n//\n' > "$2" ;;
-    --tblout) printf '# target\nhit1 - query - 1e-5 10 0\n' > "$2" ;;
-    -oa3m) printf '>query\nACDEFGHIKL\n>hit1\nACDEFGHIKV\n' > "$2" ;;
-    -o) if [ "$2" != "/dev/null" ]; then
-          case "$(basename "$0")" in
-            kalign) printf '>a\nACDEFGHIKL\n>b\nACDE-GHIKL\n' > "$2" ;;
-            *) printf 'Query         query\nMatch_columns 10\n\n' > "$2" ;;
-          esac
-        fi ;;
-  esac
-  shift
-done
-"""
-
-
 def test_alignment_tool_command_lines(tmp_path):
     """Every wrapper (jackhmmer, hhblits, hhsearch, hmmbuild, hmmsearch, kalign) is run against a stand-in executable that
     records its arguments; default and non-default settings; the command lines must equal the reference's, flag by flag."""
     import re
-    import stat
     from fastfold_b200.data import tools
-    bins = {}
-    for name in ("jackhmmer", "hhblits", "hhsearch", "hmmbuild", "hmmsearch", "kalign"):
-        path = tmp_path / "bin" / name
-        path.parent.mkdir(exist_ok=True)
-        path.write_text(_RECORDER)
-        path.chmod(path.stat().st_mode | stat.S_IEXEC)
-        bins[name] = str(path)
+    sys.path.insert(0, os.path.join(ROOT, "tests", "helpers"))
+    from standins import make_tool_standins
+    bins = make_tool_standins(tmp_path / "bin")
     (tmp_path / "db.fasta").write_text(">x\nACDEFGHIKL\n")
     for suffix in ("_hhm.ffdata", "_a3m.ffdata", "_cs219.ffdata"):
         (tmp_path / ("hhdb" + suffix)).write_text("")

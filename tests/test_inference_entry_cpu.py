@@ -104,3 +104,51 @@ def test_config_override_parsing():
     assert inference.parse_overrides(["a.b=3", "c=True", "d=model_1", "e=[1, 2]"]) == {"a.b": 3, "c": True, "d": "model_1", "e": [1, 2]}
     with pytest.raises(ValueError):
         inference.parse_overrides(["novalue"])
+
+
+def _entry_with_searches(tmp_path, preset, fasta_text, extra):
+    """``inference.py`` with database flags: the searches run (against recording stand-in executables), the alignments
+    land where the data pipeline reads them, and the reduced model folds the result."""
+    sys.path.insert(0, os.path.join(ROOT, "tests", "helpers"))
+    from standins import make_tool_standins
+    bins = make_tool_standins(tmp_path / "bin")
+    (tmp_path / "db.fasta").write_text(">x\nACDEFGHIKL\n")
+    for suffix in ("_hhm.ffdata", "_a3m.ffdata", "_cs219.ffdata"):
+        (tmp_path / ("hhdb" + suffix)).write_text("")
+    (tmp_path / "q.fasta").write_text(fasta_text)
+    record = tmp_path / "commands.txt"
+    cmd = [sys.executable, os.path.join(ROOT, "inference.py"), "q.fasta", "none", "--output_dir", "out", "--gpus", "1", "--model_preset", preset,
+           "--uniref90_database_path", str(tmp_path / "db.fasta"), "--mgnify_database_path", str(tmp_path / "db.fasta"),
+           "--bfd_database_path", str(tmp_path / "hhdb"), "--uniclust30_database_path", str(tmp_path / "hhdb"), "--cpus", "2", "--data_random_seed", "1"]
+    for tool in ("jackhmmer", "hhblits", "hhsearch", "hmmsearch", "hmmbuild", "kalign"):
+        cmd += ["--%s_binary_path" % tool, bins[tool]]
+    for k, v in OVERRIDES.items():
+        cmd += ["--config_override", "%s=%s" % (k, v)]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", RECORD=str(record), MASTER_PORT=str(21000 + os.getpid() % 2000))
+    r = subprocess.run(cmd + list(extra), cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    return record.read_text().splitlines(), r.stdout
+
+
+def test_entry_point_runs_the_monomer_searches(tmp_path):
+    commands, log = _entry_with_searches(tmp_path, "monomer", ">q1 test\n%s\n" % SEQ,
+                                         ["--model_name", "model_3", "--pdb70_database_path", str(tmp_path / "hhdb")])
+    tools = sorted(c.split()[0] for c in commands)
+    assert tools == ["hhblits", "hhsearch", "jackhmmer", "jackhmmer"], tools
+    assert sorted(os.listdir(tmp_path / "out" / "alignments" / "q1")) == ["bfd_uniref_hits.a3m", "mgnify_hits.a3m", "pdb70_hits.hhr", "uniref90_hits.a3m"]
+    assert "Alignment data workflow time" in log and os.path.exists(tmp_path / "out" / "q1_model_3_unrelaxed.pdb")
+
+
+def test_entry_point_runs_the_multimer_searches_per_chain(tmp_path):
+    fasta = ">A first\n%s\n>B second\n%s\n>C copy of the first\n%s\n" % (SEQ, SEQ[::-1], SEQ)
+    commands, log = _entry_with_searches(tmp_path, "multimer", fasta, ["--uniprot_database_path", str(tmp_path / "db.fasta"),
+                                                                       "--pdb_seqres_database_path", str(tmp_path / "db.fasta"), "--enable_workflow"])
+    tools = sorted(c.split()[0] for c in commands)
+    # two distinct chains: uniref90, mgnify and uniprot searches, one hhblits and one template search (profile + search) each
+    assert tools == sorted(["jackhmmer"] * 6 + ["hhblits"] * 2 + ["hmmbuild"] * 2 + ["hmmsearch"] * 2), tools
+    for chain in ("A", "B", "C"):
+        files = sorted(os.listdir(tmp_path / "out" / "alignments" / chain))
+        assert files == ["bfd_uniref_hits.a3m", "hmm_output.sto", "mgnify_hits.sto", "uniprot_hits.sto", "uniref90_hits.sto"], (chain, files)
+    from fastfold_b200.common import protein
+    prot = protein.from_pdb_string(open(tmp_path / "out" / "A_multimer_unrelaxed.pdb").read())
+    assert prot.aatype.shape[0] == 3 * len(SEQ) and len(set(prot.chain_index.tolist())) == 3
