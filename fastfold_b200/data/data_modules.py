@@ -143,7 +143,10 @@ class OpenFoldSingleDataset(torch.utils.data.Dataset):
         data = self.raw(idx)
         if self._output_raw:
             return data
-        return self.feature_pipeline.process_features(data, self.mode)
+        # a fresh seed per item (from the global generator, so torch.manual_seed makes a run repeatable): row sampling, masking,
+        # cropping and template subsampling must differ from sample to sample and from epoch to epoch
+        seed = int(torch.randint(0, 2 ** 31 - 1, (1,)))
+        return self.feature_pipeline.process_features(data, self.mode, seed=seed)
 
 
 def deterministic_train_filter(entry, max_resolution=9.0, max_single_aa_prop=0.8):
