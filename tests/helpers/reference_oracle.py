@@ -238,6 +238,7 @@ def main(mode, src, dst):
         out["gdt_ts"], out["gdt_ha"] = vu.gdt_ts(a, b, mask), vu.gdt_ha(a, b, mask)
         from fastfold.utils.superimposition import superimpose
         out["superimposed"], out["rmsd"] = superimpose(a, b, mask)
+        out["validation_metrics"] = vu.compute_validation_metrics(d["val_batch"], d["val_outputs"], superimposition_metrics=True)
         opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.1)
         # its constructor passes ``verbose`` to a base class that no longer takes it: evaluate the schedule itself
         sched = AlphaFoldLRScheduler.__new__(AlphaFoldLRScheduler)

@@ -427,8 +427,15 @@ def test_pdb_writer_metrics_and_schedule(tmp_path):
     schedule = {"base_lr": 0.0, "max_lr": 1e-3, "warmup_no_steps": 5, "start_decay_after_n_steps": 12, "decay_every_n_steps": 4, "decay_factor": 0.9}
     # chain letters: the reference indexes the letters with the 1-based ``asym_id`` (first chain "B"); here the first chain is "A"
     shifted = dict(features, asym_id=features["asym_id"] - 1)
-    ref = _oracle("utils", {"features": shifted, "result": result, "b_factors": b_factors, "structures": (a, b, m), "schedule": schedule, "steps": 30},
-                  tmp_path)
+    gt37 = torch.cumsum(torch.randn(n, 1, 3, generator=g) * 2.0, 0) + torch.randn(n, 37, 3, generator=g)
+    val_batch = {"all_atom_positions": gt37, "all_atom_mask": torch.tensor(mask) * (torch.rand(n, 37, generator=g) > 0.1)}
+    val_outputs = {"final_atom_positions": gt37 + torch.randn(n, 37, 3, generator=g) * 1.5}
+    ref = _oracle("utils", {"features": shifted, "result": result, "b_factors": b_factors, "structures": (a, b, m), "schedule": schedule, "steps": 30,
+                            "val_batch": val_batch, "val_outputs": val_outputs}, tmp_path)
+    metrics = vu.compute_validation_metrics(val_batch, val_outputs, superimposition_metrics=True)
+    assert set(metrics) == set(ref["validation_metrics"]) == {"lddt_ca", "drmsd_ca", "alignment_rmsd", "gdt_ts", "gdt_ha"}
+    for k, v in ref["validation_metrics"].items():
+        assert abs(float(metrics[k]) - float(v)) < 1e-4 * max(1.0, abs(float(v))), (k, float(metrics[k]), float(v))
     prot = protein.from_prediction(features, result, b_factors=b_factors)
     assert protein.to_pdb(prot) == ref["pdb"]                       # byte for byte: chains, TER records, numbering, B-factors
     assert np.array_equal(protein.ideal_atom_mask(prot), ref["ideal_atom_mask"])
