@@ -44,7 +44,7 @@ REQUIRED_FEATURES = frozenset({
 # identifiers (fastfold/data/msa_identifiers.py)
 # ---------------------------------------------------------------------------
 _UNIPROT_PATTERN = re.compile(
-    r"""^(?:tr|sp)\|(?:[A-Za-z0-9]{6,10})(?:_\d)?\|(?:[A-Za-z0-9]+)_(?P<SpeciesIdentifier>[A-Za-z0-9]{1,5})(?:_\d+)?(?:/\d+-\d+)?$""")
+    r"""^(?:tr|sp)\|(?:[A-Za-z0-9]{6,10})(?:_\d)?\|(?:[A-Za-z0-9]+)_(?P<SpeciesIdentifier>[A-Za-z0-9]{1,5})(?:_\d+)?$""")
 
 
 @dataclasses.dataclass(frozen=True)
@@ -54,7 +54,7 @@ class Identifiers:
 
 def get_identifiers(description: str) -> Identifiers:
     """Species identifier from a UniProt-style MSA row description (``tr|A0A146SKV9|A0A146SKV9_FUNHE/2-98``)."""
-    first = description.split()[0] if description.split() else ""
+    first = description.split()[0].partition("/")[0] if description.split() else ""     # drop the residue range
     m = _UNIPROT_PATTERN.match(first.strip())
     return Identifiers(species_id=m.group("SpeciesIdentifier")) if m else Identifiers()
 

@@ -38,6 +38,8 @@ def atom37_to_atom14(atom37_data, aatype, all_atom_mask=None):
     if all_atom_mask is not None:
         aatype, positions = atom37_data, aatype
         mask14 = atom37_to_atom14(all_atom_mask.to(torch.float32), aatype)
+        if isinstance(positions, Vec3Array):                  # struct-of-arrays in, struct-of-arrays out
+            return Vec3Array.from_array(atom37_to_atom14(positions.to_tensor(), aatype) * mask14[..., None]), mask14
         return atom37_to_atom14(positions, aatype) * mask14[..., None].to(positions.dtype), mask14
     idx = _table(rc.restype_atom14_to_atom37, aatype).long()
     mask = get_atom14_mask(aatype)

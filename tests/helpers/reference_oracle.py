@@ -4,7 +4,7 @@ interpreter with this repository's ``fastfold`` compatibility namespace:
 
     python reference_oracle.py <mode> <input.pt> <output.pt>
 
-``mode``: ``tools`` (runs every alignment-tool wrapper against recording stand-in executables), ``geometry`` (the struct-of-arrays vectors, rotations and rigids of the multimer model), ``rigid`` (rigid-transform algebra and two feature helpers), ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
+``mode``: ``tools`` (runs every alignment-tool wrapper against recording stand-in executables), ``geometry`` (the struct-of-arrays vectors, rotations and rigids of the multimer model), ``all_atom_multimer`` (torsions to frames to atoms, ground-truth frames, chi angles on the struct-of-arrays types), ``rigid`` (rigid-transform algebra and two feature helpers), ``violations`` (the structural-violation terms and their gradients, bounds supplied by the caller), ``fast_model`` (full forward through the reference's own ``inject_fastnn`` and fast modules - the path its
 inference runs - with its two GPU-only kernel entry points, fused LayerNorm and fused softmax, replaced by their PyTorch
 definitions so that the path runs on CPU; DAP size 1), ``data_modules`` (training-set filters, ``OpenFoldSingleDataset`` items, the batch collator), ``multimer_pipeline`` (``DataPipelineMultimer.process_fasta`` on per-chain alignment directories), ``pipeline`` (``DataPipeline.process_fasta`` / ``process_mmcif`` on an alignment directory), ``mmcif`` (its mmCIF reader - on the BioPython stand-in of ``baseline/stubs`` - and its template featuriser on
 the files of a directory), ``utils`` (PDB writer, dRMSD / GDT, learning-rate schedule), ``parsers`` (FASTA / A3M / Stockholm / HHR / hmmsearch / tblout parsers on the given texts), ``config`` (every preset of ``model_config`` flattened to ``{dotted key: repr(value)}``), ``multimer_merge`` (``feature_processing_multimer.pair_and_merge`` on per-chain feature dicts),
@@ -68,6 +68,55 @@ def _tensors(tree):
     return tree
 
 
+def all_atom_multimer_case(aam, g, d):
+    """The struct-of-arrays all-atom helpers of the multimer model on one chain; ``aam`` / ``g`` are the
+    ``all_atom_multimer`` and ``geometry`` modules of the implementation under test, so both sides run this very code."""
+    aatype, torsions = d["aatype"], d["torsions"]
+    pos37, mask37 = g.Vec3Array.from_array(d["pos37"]), d["mask37"]
+    out, failed = {}, []
+
+    def attempt(name, fn):
+        try:
+            out.update(fn())
+        except Exception as e:                      # a helper the implementation cannot run is reported, not fatal
+            failed.append("%s: %s" % (name, type(e).__name__))
+
+    def frames():
+        f = aam.torsion_angles_to_frames(aatype, g.Rigid3Array.from_tensor_4x4(d["backbone"]), torsions)
+        return {"frames8": f.to_tensor_4x4()}
+
+    def atoms():
+        p = aam.frames_and_literature_positions_to_atom14_pos(aatype, g.Rigid3Array.from_tensor_4x4(d["frames8"]))
+        return {"pos14": p.to_tensor(), "atom37_from_14": aam.atom14_to_atom37(p.to_tensor(), aatype)}
+
+    def gt_frames():
+        gt = aam.atom37_to_frames(aatype, pos37, mask37)
+        return {"gt_frames": gt["rigidgroups_gt_frames"].to_tensor_4x4(), "alt_gt_frames": gt["rigidgroups_alt_gt_frames"].to_tensor_4x4(),
+                "gt_exists": gt["rigidgroups_gt_exists"].float(), "group_exists": gt["rigidgroups_group_exists"].float(),
+                "is_ambiguous": gt["rigidgroups_group_is_ambiguous"].float()}
+
+    def chi():
+        angles, mask = aam.compute_chi_angles(pos37, mask37, aatype)
+        return {"chi": angles, "chi_mask": mask.float()}
+
+    def backbone():
+        rigid, mask = aam.make_backbone_affine(pos37, mask37, aatype)
+        return {"backbone": rigid.to_tensor_4x4(), "backbone_mask": mask.float()}
+
+    def to14():
+        p, m = aam.atom37_to_atom14(aatype, pos37, mask37)
+        return {"atom14_from_37": p.to_tensor() if hasattr(p, "to_tensor") else p, "atom14_mask": m.float()}
+
+    def chi_indices():
+        return {"chi_atom_indices": torch.as_tensor(aam.get_chi_atom_indices(torch.device("cpu"))).long()}
+
+    for name, fn in (("torsion_angles_to_frames", frames), ("frames_and_literature_positions_to_atom14_pos", atoms), ("atom37_to_frames", gt_frames),
+                     ("compute_chi_angles", chi), ("make_backbone_affine", backbone), ("atom37_to_atom14", to14), ("get_chi_atom_indices", chi_indices)):
+        attempt(name, fn)
+    out["failed"] = failed
+    return out
+
+
 def main(mode, src, dst):
     _setup()
     d = torch.load(src, weights_only=False)
@@ -124,6 +173,10 @@ def main(mode, src, dst):
                "rigid_scale": rig.scale_translation(0.1).to_tensor_4x4(), "identity": g.Rigid3Array.identity((3,), "cpu").to_tensor_4x4(),
                "quat_rigid": from_act.to_tensor_4x4()}
         torch.save(out, dst)
+        return
+    if mode == "all_atom_multimer":
+        from fastfold.utils import all_atom_multimer, geometry
+        torch.save(all_atom_multimer_case(all_atom_multimer, geometry, d), dst)
         return
     if mode == "rigid":
         from fastfold.utils import rigid_utils as ru
@@ -273,6 +326,8 @@ def main(mode, src, dst):
                "sto_no_empty": parsers.remove_empty_columns_from_stockholm_msa(t["sto_gappy"]),
                "hhr": plain(parsers.parse_hhr(t["hhr"])), "tblout": plain(parsers.parse_e_values_from_tblout(t["tblout"])),
                "hmmsearch": plain(parsers.parse_hmmsearch_sto(t["hmmsearch_sto"], t["query"]))}
+        from fastfold.data import msa_identifiers
+        out["species"] = [msa_identifiers.get_identifiers(x).species_id for x in d.get("descriptions", [])]
         torch.save(out, dst)
         return
     if mode == "config":

@@ -385,7 +385,13 @@ PARSER_TEXTS = {
 def test_alignment_parsers(tmp_path):
     from fastfold_b200.data import parsers
     t = PARSER_TEXTS
-    ref = _oracle("parsers", {"texts": t}, tmp_path)
+    descriptions = ["tr|A0A146SKV9|A0A146SKV9_FUNHE/2-98 some text", "sp|P0C2L1|A3X1_LOXLA", "tr|A0A146SKV9_1|A0A146SKV9_FUNHE_12/3-4",
+                    "tr|A0A146SKV9|A0A146SKV9_FUNHE/x", "", "   ", "tr|Q|Q_H", "UniRef90_A0A146SKV9", "sp|P0C2L1|A3X1_LOXLAXX", "query",
+                    " sp|P0C2L1|A3X1_HUMAN\tn=3", "tr|A0A146SKV9|A0A146SKV9_9BACT_7"]
+    ref = _oracle("parsers", {"texts": t, "descriptions": descriptions}, tmp_path)
+    from fastfold_b200.data import msa_identifiers
+    assert [msa_identifiers.get_identifiers(x).species_id for x in descriptions] == ref["species"]
+    assert ref["species"][0] == "FUNHE" and ref["species"][-1] == "9BACT"
 
     def hits(seq):
         import dataclasses
@@ -986,3 +992,39 @@ def test_alignment_tool_command_lines(tmp_path):
     assert sorted(lines(tmp_path / "ours_runner.txt")) == sorted(lines(tmp_path / "ref_runner.txt"))
     for sub in ("mono_full", "mono_small", "multi"):
         assert sorted(os.listdir(tmp_path / "ours_out" / sub)) == sorted(os.listdir(tmp_path / "ref_out" / sub)), sub
+
+
+def test_all_atom_multimer_helpers(tmp_path):
+    """Chi angles, backbone frames and the chi-atom table from atom37 coordinates (plus whatever else of torsions -> group
+    frames -> atoms and ground-truth frames the reference can run): the same driver code runs on both implementations'
+    struct-of-arrays types."""
+    from reference_oracle import all_atom_multimer_case
+    from fastfold_b200.utils import all_atom_multimer as aam, geometry as g
+    gen = torch.Generator().manual_seed(3)
+    aatype = torch.cat([torch.arange(21), torch.randint(0, 20, (9,), generator=gen)])
+    n = aatype.shape[0]
+    q = torch.randn(n, 4, generator=gen)
+    backbone = g.Rigid3Array(g.Rot3Array.from_quaternion(*torch.unbind(q, dim=-1)), g.Vec3Array.from_array(torch.randn(n, 3, generator=gen) * 10))
+    torsions = torch.nn.functional.normalize(torch.randn(n, 7, 2, generator=gen), dim=-1)
+    pos14 = aam.frames_and_literature_positions_to_atom14_pos(aatype, aam.torsion_angles_to_frames(aatype, backbone, torsions))
+    pos37 = aam.atom14_to_atom37(pos14.to_tensor(), aatype)
+    mask37 = aam.get_atom37_mask(aatype) * (torch.rand(n, 37, generator=gen) > 0.1)
+    frames8 = aam.torsion_angles_to_frames(aatype, backbone, torsions).to_tensor_4x4()
+    payload = {"aatype": aatype, "backbone": backbone.to_tensor_4x4(), "torsions": torsions, "frames8": frames8, "pos37": pos37, "mask37": mask37}
+    ref = _oracle("all_atom_multimer", payload, tmp_path)
+    ours = all_atom_multimer_case(aam, g, payload)
+    assert ours.pop("failed") == []
+    # the reference's torsion_angles_to_frames, frames_and_literature_positions_to_atom14_pos, atom37_to_frames and
+    # atom37_to_atom14 raise on any input (its multimer model never calls them); those four are checked against the tensor
+    # versions in tests/test_geometry_cpu.py, which this file in turn checks against the reference
+    print("helpers the reference cannot run:", ref.pop("failed"))
+    assert {"chi", "chi_mask", "backbone", "backbone_mask", "chi_atom_indices"} <= set(ref)
+    for k, v in ref.items():
+        a = ours[k]
+        if k in ("gt_frames", "alt_gt_frames"):            # frames of groups without all three atoms are arbitrary
+            keep = ref["gt_exists"].bool()
+            a, v = a[keep], v[keep]
+        if k == "chi":                                     # angles of incomplete side chains likewise
+            keep = ref["chi_mask"].bool()
+            a, v = a[keep], v[keep]
+        _close(a, v, 2e-4, k)
